@@ -1,0 +1,154 @@
+/*
+ * CPU oracle for the quantized decode hot path of microkimi.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This is a plain-C restatement of the reference's
+ * CPU arithmetic (Rust sources, cited per function as file:line relative to the
+ * reference project).  It exists so the CUDA kernels can be checked against the
+ * reference's own numbers and so a CPU baseline can be timed beside the GPU.
+ * Nothing in the shipped product path may call into it.
+ *
+ * Every function keeps the reference's operation ORDER (mul then add, never a
+ * fused multiply-add; fixed reduction trees) - build with -ffp-contract=off.
+ */
+#ifndef MK_ORACLE_H
+#define MK_ORACLE_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- build.rs RNG (src/build.rs:21-51) ---- */
+typedef struct { uint64_t s; } or_rng;
+void     or_rng_for_tensor(or_rng *r, const char *name);
+uint64_t or_rng_next_u64(or_rng *r);
+double   or_rng_uniform(or_rng *r);
+float    or_rng_gauss(or_rng *r);
+void     or_rng_fill_gauss(const char *name, float sigma, float *out, size_t n);
+
+/* ---- MXFP4 (src/mxfp4.rs) ---- */
+float or_exp2_i(int e);                                   /* mxfp4.rs:10-16  */
+float or_scale_from_byte(uint8_t sb);                     /* mxfp4.rs:340-346 */
+void  or_mxfp4_dequant(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols, float *out); /* :19-31 */
+void  or_mxfp4_quantize(const float *w, size_t rows, size_t cols, int search, uint8_t *packed, uint8_t *scales); /* :38-138 */
+void  or_mxfp4_matvec_f32(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols,
+                          const float *x, float *out, int n_threads);                    /* :488-539 */
+void  or_mxfp4_matvec_q8(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols,
+                         const int8_t *xq, const float *xs, float *out, int n_threads);  /* :405-443 */
+void  or_mxfp4_matvec(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols,
+                      const float *x, float *out, int n_threads, int use_q8);            /* :458-539 */
+void  or_mxfp4_matvec_shader_emul(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols,
+                                  const float *x, float *out, size_t lanes);             /* :357-393 */
+/* model.rs:2412-2447: batched order, xt = [cols*m] transposed, out = [m*rows] */
+void  or_mxfp4_matvec_nt(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols,
+                         const float *xt, size_t m, float *out);
+
+/* ---- q8_0 (src/q8.rs) ---- */
+void    or_q8_quantize(const float *x, size_t n, int8_t *q, float *scales);  /* q8.rs:49-69 */
+int32_t or_block_dot(const uint8_t *packed16, const int8_t *x32);            /* q8.rs:194-202 */
+int32_t or_block_dot_i8(const int8_t *w32, const int8_t *x32);               /* q8.rs:119-125 */
+
+/* ---- f32 kernels (src/model.rs) ---- */
+float or_dot(const float *a, const float *b, size_t n);                      /* model.rs:63-82 */
+void  or_matvec_f32(const float *w, size_t rows, size_t cols, const float *x, float *out, int n_threads); /* :199-247 */
+void  or_rmsnorm(const float *x, const float *w, size_t n, float eps, float *out); /* :599-605 */
+float or_sigmoid(float x);                                                   /* :607-610 */
+float or_situ(float g, float u);                                             /* :617-621 */
+int   or_argmax(const float *v, size_t n);                                   /* :3271-3291 (first strict maximum) */
+
+/* ---- q8_0 lm_head (model.rs:261-348) ---- */
+void or_q8head_from_f32(const float *w, size_t rows, size_t cols, int8_t *q, float *scales);
+void or_q8head_matvec(const int8_t *q, const float *scales, size_t rows, size_t cols,
+                      const float *x, float *out, int n_threads);
+/* variant with the weight scales rounded to IEEE half before use (layout the
+ * benchmark spec words as "f16 scales"; no counterpart in the reference). */
+void or_q8head_from_f32_f16s(const float *w, size_t rows, size_t cols, int8_t *q, uint16_t *scales_h);
+void or_q8head_matvec_f16s(const int8_t *q, const uint16_t *scales_h, size_t rows, size_t cols,
+                           const float *x, float *out, int n_threads);
+
+/* ---- routers ---- */
+/* K3 noaux_tc router (model.rs:2153-2173): ids/weights in final slot order. */
+void or_router_k3(const float *gate_w, const float *gate_b, size_t n_experts, size_t d, size_t top_k,
+                  const float *x, int32_t *ids, float *weights, float *logits_out /* nullable */);
+/* DeepSeek sqrtsoftplus gate (deepseek.rs:16-58), no hash routing. */
+void or_gate_ds(const float *gate_w, const float *bias /* nullable */, size_t n_experts, size_t d, size_t top_k,
+                float route_scale, const float *x, int32_t *ids, float *weights);
+
+/* ---- experts ---- */
+/* deepseek.rs:74-95 : f32 SwiGLU-clamp expert. */
+void or_expert_ds_f32(const float *w1, const float *w2, const float *w3, const float *x,
+                      size_t d, size_t inter, float limit, float *out);
+
+typedef struct {
+    size_t d, inter, n_experts, top_k;
+    float  limit;                 /* swiglu clamp (deepseek.rs:1082) */
+    int    use_q8;                /* 1: matvec_packed default path; 0: exact f32 path */
+    const float   *gate_w;        /* [n_experts, d] */
+    const float   *gate_b;        /* [n_experts] */
+    /* routed experts: expert e, matrix m in {0:w1,1:w2,2:w3}: packed at
+     * packed[(e*3+m)] (pointer table), scales likewise */
+    const uint8_t *const *packed; /* [n_experts*3] */
+    const uint8_t *const *scales; /* [n_experts*3] */
+    /* one shared expert, MXFP4 (w1,w2,w3) */
+    const uint8_t *sh_packed[3];
+    const uint8_t *sh_scales[3];
+} or_moe_ds_desc;
+/* K3 router (model.rs:2153-2173) feeding the DeepSeek expert body
+ * (deepseek.rs:1038-1108): routing weight folded into the activation before w2,
+ * outputs summed in slot order, plus one unweighted shared expert. One token. */
+void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
+                       int32_t *ids_out /* [top_k], nullable */, float *w_out /* nullable */, int n_threads);
+
+/* ---- MLA q8_0 cache, reference per-head layout (model.rs:765-781) ---- */
+typedef struct {
+    size_t nh, nope, rope, vd;
+    size_t n;       /* positions held */
+    size_t cap;
+    int8_t *kq;     /* [n][nh][nope] */
+    float  *ks;     /* [n][nh][nope/32] */
+    float  *kr;     /* [n][rope] */
+    int8_t *vq;     /* [n][nh][vd] */
+    float  *vs;     /* [n][nh][vd/32] */
+} or_mla_cache;
+or_mla_cache *or_mla_new(size_t nh, size_t nope, size_t rope, size_t vd, size_t cap);
+void or_mla_free(or_mla_cache *c);
+void or_mla_push(or_mla_cache *c, const float *k_row, const float *v_row);             /* :1583-1618 (no Hadamard) */
+void or_mla_to_f32(const or_mla_cache *c, float *k, float *v);                         /* :1623-1676 */
+void or_mla_attn_flash_q8(const or_mla_cache *c, const float *qh, size_t h, size_t pos, float scale, float *oh); /* :1706-1786 */
+void or_mla_attn_flash_q8_mqa(const or_mla_cache *c, const float *q, size_t pos, float scale, float *attn);      /* :1804-1908 */
+void or_mla_attn_ref_q8(const or_mla_cache *c, const float *qh, size_t h, size_t pos, float scale, float *oh);   /* :1914-1937 */
+/* f32-cache kernels (model.rs:1353-1500) used by the reference's own A/B tests */
+void or_mla_attn_ref_f32(const float *k, const float *v, size_t nh, size_t hd, size_t vd,
+                         const float *qh, size_t h, size_t pos, float scale, float *oh);
+void or_mla_attn_flash_f32(const float *k, const float *v, size_t nh, size_t hd, size_t vd,
+                           const float *qh, size_t h, size_t pos, float scale, float *oh);
+
+/* ---- MLA q8_0 cache, absorbed shared-latent layout (no reference function:
+ *      the per-position recipe of model.rs:1833-1890 applied to ONE q8 row of
+ *      width `lat` (= kv_lora + rope) shared by all heads; V = first `vd`
+ *      columns of the same row). ---- */
+typedef struct {
+    size_t lat, vd, n, cap;
+    int8_t *q;      /* [n][lat] */
+    float  *s;      /* [n][lat/32] */
+} or_mla_abs_cache;
+or_mla_abs_cache *or_mla_abs_new(size_t lat, size_t vd, size_t cap);
+void or_mla_abs_free(or_mla_abs_cache *c);
+void or_mla_abs_push(or_mla_abs_cache *c, const float *row);
+void or_mla_abs_attn(const or_mla_abs_cache *c, const float *q /* [nh][lat] */, size_t nh,
+                     size_t pos, float scale, float *out /* [nh][vd] */);
+/* f64 dense-softmax check of the same quantities (dequantized cache, f32 query). */
+void or_mla_abs_attn_f64(const or_mla_abs_cache *c, const float *q, size_t nh,
+                         size_t pos, float scale, double *out);
+
+/* IEEE half helpers (round-to-nearest-even), used only by the f16-scale variant */
+uint16_t or_f32_to_f16(float f);
+float    or_f16_to_f32(uint16_t h);
+
+int or_num_threads(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,429 @@
+"""ctypes loader for the CPU oracle (libmk_oracle.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+CPU-baseline leg of the benchmark.  The product package never imports it.
+Each wrapper takes and returns numpy arrays; the C function it calls cites the
+reference source lines it restates (see mk_oracle.h / mk_oracle.c).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libmk_oracle.so")
+
+
+def build(force=False):
+    src = os.path.join(_HERE, "mk_oracle.c")
+    hdr = os.path.join(_HERE, "mk_oracle.h")
+    if (not force and os.path.exists(_SO)
+            and os.path.getmtime(_SO) >= max(os.path.getmtime(src), os.path.getmtime(hdr))):
+        return _SO
+    subprocess.check_call(["make", "-C", _HERE, "-B", "libmk_oracle.so"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _declare(_lib)
+    return _lib
+
+
+_f32p = C.POINTER(C.c_float)
+_f64p = C.POINTER(C.c_double)
+_u8p = C.POINTER(C.c_uint8)
+_i8p = C.POINTER(C.c_int8)
+_u16p = C.POINTER(C.c_uint16)
+_i32p = C.POINTER(C.c_int32)
+_sz = C.c_size_t
+
+
+class _MoeDesc(C.Structure):
+    _fields_ = [("d", _sz), ("inter", _sz), ("n_experts", _sz), ("top_k", _sz),
+                ("limit", C.c_float), ("use_q8", C.c_int),
+                ("gate_w", _f32p), ("gate_b", _f32p),
+                ("packed", C.POINTER(_u8p)), ("scales", C.POINTER(_u8p)),
+                ("sh_packed", _u8p * 3), ("sh_scales", _u8p * 3)]
+
+
+def _declare(L):
+    def sig(name, res, *args):
+        f = getattr(L, name)
+        f.restype = res
+        f.argtypes = list(args)
+    sig("or_num_threads", C.c_int)
+    sig("or_rng_fill_gauss", None, C.c_char_p, C.c_float, _f32p, _sz)
+    sig("or_exp2_i", C.c_float, C.c_int)
+    sig("or_scale_from_byte", C.c_float, C.c_uint8)
+    sig("or_mxfp4_dequant", None, _u8p, _u8p, _sz, _sz, _f32p)
+    sig("or_mxfp4_quantize", None, _f32p, _sz, _sz, C.c_int, _u8p, _u8p)
+    sig("or_mxfp4_matvec_f32", None, _u8p, _u8p, _sz, _sz, _f32p, _f32p, C.c_int)
+    sig("or_mxfp4_matvec_q8", None, _u8p, _u8p, _sz, _sz, _i8p, _f32p, _f32p, C.c_int)
+    sig("or_mxfp4_matvec", None, _u8p, _u8p, _sz, _sz, _f32p, _f32p, C.c_int, C.c_int)
+    sig("or_mxfp4_matvec_shader_emul", None, _u8p, _u8p, _sz, _sz, _f32p, _f32p, _sz)
+    sig("or_mxfp4_matvec_nt", None, _u8p, _u8p, _sz, _sz, _f32p, _sz, _f32p)
+    sig("or_q8_quantize", None, _f32p, _sz, _i8p, _f32p)
+    sig("or_block_dot", C.c_int32, _u8p, _i8p)
+    sig("or_block_dot_i8", C.c_int32, _i8p, _i8p)
+    sig("or_dot", C.c_float, _f32p, _f32p, _sz)
+    sig("or_matvec_f32", None, _f32p, _sz, _sz, _f32p, _f32p, C.c_int)
+    sig("or_rmsnorm", None, _f32p, _f32p, _sz, C.c_float, _f32p)
+    sig("or_sigmoid", C.c_float, C.c_float)
+    sig("or_situ", C.c_float, C.c_float, C.c_float)
+    sig("or_argmax", C.c_int, _f32p, _sz)
+    sig("or_q8head_from_f32", None, _f32p, _sz, _sz, _i8p, _f32p)
+    sig("or_q8head_matvec", None, _i8p, _f32p, _sz, _sz, _f32p, _f32p, C.c_int)
+    sig("or_q8head_from_f32_f16s", None, _f32p, _sz, _sz, _i8p, _u16p)
+    sig("or_q8head_matvec_f16s", None, _i8p, _u16p, _sz, _sz, _f32p, _f32p, C.c_int)
+    sig("or_router_k3", None, _f32p, _f32p, _sz, _sz, _sz, _f32p, _i32p, _f32p, _f32p)
+    sig("or_gate_ds", None, _f32p, _f32p, _sz, _sz, _sz, C.c_float, _f32p, _i32p, _f32p)
+    sig("or_expert_ds_f32", None, _f32p, _f32p, _f32p, _f32p, _sz, _sz, C.c_float, _f32p)
+    sig("or_moe_ds_forward", None, C.POINTER(_MoeDesc), _f32p, _f32p, _i32p, _f32p, C.c_int)
+    sig("or_mla_new", C.c_void_p, _sz, _sz, _sz, _sz, _sz)
+    sig("or_mla_free", None, C.c_void_p)
+    sig("or_mla_push", None, C.c_void_p, _f32p, _f32p)
+    sig("or_mla_to_f32", None, C.c_void_p, _f32p, _f32p)
+    sig("or_mla_attn_flash_q8", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f32p)
+    sig("or_mla_attn_flash_q8_mqa", None, C.c_void_p, _f32p, _sz, C.c_float, _f32p)
+    sig("or_mla_attn_ref_q8", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f32p)
+    sig("or_mla_attn_ref_f32", None, _f32p, _f32p, _sz, _sz, _sz, _f32p, _sz, _sz, C.c_float, _f32p)
+    sig("or_mla_attn_flash_f32", None, _f32p, _f32p, _sz, _sz, _sz, _f32p, _sz, _sz, C.c_float, _f32p)
+    sig("or_mla_abs_new", C.c_void_p, _sz, _sz, _sz)
+    sig("or_mla_abs_free", None, C.c_void_p)
+    sig("or_mla_abs_push", None, C.c_void_p, _f32p)
+    sig("or_mla_abs_attn", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f32p)
+    sig("or_mla_abs_attn_f64", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f64p)
+    sig("or_f32_to_f16", C.c_uint16, C.c_float)
+    sig("or_f16_to_f32", C.c_float, C.c_uint16)
+
+
+def _p(a, t):
+    return a.ctypes.data_as(t)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def num_threads():
+    return int(lib().or_num_threads())
+
+
+# ---------------------------------------------------------------- RNG
+def fill_gauss(name, sigma, n):
+    out = np.empty(n, np.float32)
+    lib().or_rng_fill_gauss(name.encode(), float(sigma), _p(out, _f32p), n)
+    return out
+
+
+# ---------------------------------------------------------------- MXFP4
+def mxfp4_dequant(packed, scales, rows, cols):
+    packed, scales = _c(packed, np.uint8), _c(scales, np.uint8)
+    out = np.empty((rows, cols), np.float32)
+    lib().or_mxfp4_dequant(_p(packed, _u8p), _p(scales, _u8p), rows, cols, _p(out, _f32p))
+    return out
+
+
+def mxfp4_quantize(w, search=True):
+    w = _c(w, np.float32)
+    rows, cols = w.shape
+    packed = np.empty((rows, cols // 2), np.uint8)
+    scales = np.empty((rows, cols // 32), np.uint8)
+    lib().or_mxfp4_quantize(_p(w, _f32p), rows, cols, int(search), _p(packed, _u8p), _p(scales, _u8p))
+    return packed, scales
+
+
+def mxfp4_matvec(packed, scales, x, use_q8, n_threads=1):
+    packed, scales, x = _c(packed, np.uint8), _c(scales, np.uint8), _c(x, np.float32)
+    rows, cols = packed.shape[0], packed.shape[1] * 2
+    out = np.empty(rows, np.float32)
+    lib().or_mxfp4_matvec(_p(packed, _u8p), _p(scales, _u8p), rows, cols, _p(x, _f32p), _p(out, _f32p),
+                          n_threads, int(use_q8))
+    return out
+
+
+def mxfp4_matvec_shader_emul(packed, scales, x, lanes=256):
+    packed, scales, x = _c(packed, np.uint8), _c(scales, np.uint8), _c(x, np.float32)
+    rows, cols = packed.shape[0], packed.shape[1] * 2
+    out = np.empty(rows, np.float32)
+    lib().or_mxfp4_matvec_shader_emul(_p(packed, _u8p), _p(scales, _u8p), rows, cols, _p(x, _f32p),
+                                      _p(out, _f32p), lanes)
+    return out
+
+
+def mxfp4_matvec_nt(packed, scales, xs):
+    """xs: [m, cols] (m % 8 == 0). Returns [m, rows] in the batched order of model.rs:2412."""
+    packed, scales = _c(packed, np.uint8), _c(scales, np.uint8)
+    xs = _c(xs, np.float32)
+    m, cols = xs.shape
+    rows = packed.shape[0]
+    xt = np.ascontiguousarray(xs.T)
+    out = np.empty((m, rows), np.float32)
+    lib().or_mxfp4_matvec_nt(_p(packed, _u8p), _p(scales, _u8p), rows, cols, _p(xt, _f32p), m, _p(out, _f32p))
+    return out
+
+
+# ---------------------------------------------------------------- q8_0
+def q8_quantize(x):
+    x = _c(x, np.float32).ravel()
+    q = np.empty(x.size, np.int8)
+    s = np.empty(x.size // 32, np.float32)
+    lib().or_q8_quantize(_p(x, _f32p), x.size, _p(q, _i8p), _p(s, _f32p))
+    return q, s
+
+
+def block_dot(packed16, x32):
+    return int(lib().or_block_dot(_p(_c(packed16, np.uint8), _u8p), _p(_c(x32, np.int8), _i8p)))
+
+
+def block_dot_i8(w32, x32):
+    return int(lib().or_block_dot_i8(_p(_c(w32, np.int8), _i8p), _p(_c(x32, np.int8), _i8p)))
+
+
+def dot(a, b):
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    return float(np.float32(lib().or_dot(_p(a, _f32p), _p(b, _f32p), a.size)))
+
+
+def matvec_f32(w, x, n_threads=1):
+    w, x = _c(w, np.float32), _c(x, np.float32)
+    out = np.empty(w.shape[0], np.float32)
+    lib().or_matvec_f32(_p(w, _f32p), w.shape[0], w.shape[1], _p(x, _f32p), _p(out, _f32p), n_threads)
+    return out
+
+
+def rmsnorm(x, w, eps):
+    x, w = _c(x, np.float32), _c(w, np.float32)
+    out = np.empty_like(x)
+    lib().or_rmsnorm(_p(x, _f32p), _p(w, _f32p), x.size, float(eps), _p(out, _f32p))
+    return out
+
+
+def argmax(v):
+    v = _c(v, np.float32)
+    return int(lib().or_argmax(_p(v, _f32p), v.size))
+
+
+def q8head_from_f32(w):
+    w = _c(w, np.float32)
+    rows, cols = w.shape
+    q = np.empty((rows, cols), np.int8)
+    s = np.empty((rows, cols // 32), np.float32)
+    lib().or_q8head_from_f32(_p(w, _f32p), rows, cols, _p(q, _i8p), _p(s, _f32p))
+    return q, s
+
+
+def q8head_matvec(q, s, x, n_threads=1):
+    q, s, x = _c(q, np.int8), _c(s, np.float32), _c(x, np.float32)
+    out = np.empty(q.shape[0], np.float32)
+    lib().or_q8head_matvec(_p(q, _i8p), _p(s, _f32p), q.shape[0], q.shape[1], _p(x, _f32p), _p(out, _f32p), n_threads)
+    return out
+
+
+def q8head_from_f32_f16s(w):
+    w = _c(w, np.float32)
+    rows, cols = w.shape
+    q = np.empty((rows, cols), np.int8)
+    s = np.empty((rows, cols // 32), np.uint16)
+    lib().or_q8head_from_f32_f16s(_p(w, _f32p), rows, cols, _p(q, _i8p), _p(s, _u16p))
+    return q, s
+
+
+def q8head_matvec_f16s(q, s, x, n_threads=1):
+    q, s, x = _c(q, np.int8), _c(s, np.uint16), _c(x, np.float32)
+    out = np.empty(q.shape[0], np.float32)
+    lib().or_q8head_matvec_f16s(_p(q, _i8p), _p(s, _u16p), q.shape[0], q.shape[1], _p(x, _f32p), _p(out, _f32p),
+                                n_threads)
+    return out
+
+
+# ---------------------------------------------------------------- routers / experts
+def router_k3(gate_w, gate_b, x, top_k):
+    gate_w, gate_b, x = _c(gate_w, np.float32), _c(gate_b, np.float32), _c(x, np.float32)
+    n, d = gate_w.shape
+    ids = np.empty(top_k, np.int32)
+    w = np.empty(top_k, np.float32)
+    logits = np.empty(n, np.float32)
+    lib().or_router_k3(_p(gate_w, _f32p), _p(gate_b, _f32p), n, d, top_k, _p(x, _f32p), _p(ids, _i32p),
+                       _p(w, _f32p), _p(logits, _f32p))
+    return ids, w, logits
+
+
+def gate_ds(gate_w, bias, x, top_k, route_scale):
+    gate_w, x = _c(gate_w, np.float32), _c(x, np.float32)
+    n, d = gate_w.shape
+    ids = np.empty(top_k, np.int32)
+    w = np.empty(top_k, np.float32)
+    bp = _p(_c(bias, np.float32), _f32p) if bias is not None else None
+    lib().or_gate_ds(_p(gate_w, _f32p), bp, n, d, top_k, float(route_scale), _p(x, _f32p), _p(ids, _i32p), _p(w, _f32p))
+    return ids, w
+
+
+def expert_ds_f32(w1, w2, w3, x, limit):
+    w1, w2, w3, x = (_c(a, np.float32) for a in (w1, w2, w3, x))
+    inter, d = w1.shape
+    out = np.empty(d, np.float32)
+    lib().or_expert_ds_f32(_p(w1, _f32p), _p(w2, _f32p), _p(w3, _f32p), _p(x, _f32p), d, inter, float(limit),
+                           _p(out, _f32p))
+    return out
+
+
+class MoeDs:
+    """K3 router + DeepSeek expert body over MXFP4 experts (one token at a time).
+
+    experts: list of (w1, w2, w3) with each = (packed, scales) uint8 arrays;
+    shared: one such triple.
+    """
+
+    def __init__(self, gate_w, gate_b, experts, shared, top_k, limit=10.0):
+        self.gate_w = _c(gate_w, np.float32)
+        self.gate_b = _c(gate_b, np.float32)
+        self.n_experts, self.d = self.gate_w.shape
+        self.top_k = top_k
+        self.limit = float(limit)
+        self._keep = []
+        n = self.n_experts
+        self._pp = (_u8p * (3 * n))()
+        self._sp = (_u8p * (3 * n))()
+        for e, tri in enumerate(experts):
+            for j, (p, s) in enumerate(tri):
+                p, s = _c(p, np.uint8), _c(s, np.uint8)
+                self._keep += [p, s]
+                self._pp[3 * e + j] = _p(p, _u8p)
+                self._sp[3 * e + j] = _p(s, _u8p)
+        self.inter = experts[0][0][0].shape[0]
+        self._sh = []
+        for (p, s) in shared:
+            p, s = _c(p, np.uint8), _c(s, np.uint8)
+            self._sh.append((p, s))
+
+    def forward(self, x, use_q8=True, n_threads=1):
+        x = _c(x, np.float32)
+        d = _MoeDesc()
+        d.d, d.inter, d.n_experts, d.top_k = self.d, self.inter, self.n_experts, self.top_k
+        d.limit, d.use_q8 = self.limit, int(use_q8)
+        d.gate_w, d.gate_b = _p(self.gate_w, _f32p), _p(self.gate_b, _f32p)
+        d.packed = C.cast(self._pp, C.POINTER(_u8p))
+        d.scales = C.cast(self._sp, C.POINTER(_u8p))
+        for j in range(3):
+            d.sh_packed[j] = _p(self._sh[j][0], _u8p)
+            d.sh_scales[j] = _p(self._sh[j][1], _u8p)
+        out = np.empty(self.d, np.float32)
+        ids = np.empty(self.top_k, np.int32)
+        w = np.empty(self.top_k, np.float32)
+        lib().or_moe_ds_forward(C.byref(d), _p(x, _f32p), _p(out, _f32p), _p(ids, _i32p), _p(w, _f32p), n_threads)
+        return out, ids, w
+
+
+# ---------------------------------------------------------------- MLA
+class MlaCache:
+    """q8_0 MLA cache in the reference's per-head layout (model.rs:765-781)."""
+
+    def __init__(self, nh, nope, rope, vd, cap):
+        self.nh, self.nope, self.rope, self.vd, self.cap = nh, nope, rope, vd, cap
+        self.n = 0
+        self._h = lib().or_mla_new(nh, nope, rope, vd, cap)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().or_mla_free(self._h)
+            self._h = None
+
+    def push(self, k_row, v_row):
+        k_row, v_row = _c(k_row, np.float32), _c(v_row, np.float32)
+        assert self.n < self.cap
+        lib().or_mla_push(self._h, _p(k_row, _f32p), _p(v_row, _f32p))
+        self.n += 1
+
+    def to_f32(self):
+        k = np.empty((self.n, self.nh, self.nope + self.rope), np.float32)
+        v = np.empty((self.n, self.nh, self.vd), np.float32)
+        lib().or_mla_to_f32(self._h, _p(k, _f32p), _p(v, _f32p))
+        return k, v
+
+    def attn_mqa(self, q, pos, scale):
+        q = _c(q, np.float32)
+        out = np.empty((self.nh, self.vd), np.float32)
+        lib().or_mla_attn_flash_q8_mqa(self._h, _p(q, _f32p), pos, float(scale), _p(out, _f32p))
+        return out
+
+    def attn_head(self, qh, h, pos, scale):
+        qh = _c(qh, np.float32)
+        out = np.empty(self.vd, np.float32)
+        lib().or_mla_attn_flash_q8(self._h, _p(qh, _f32p), h, pos, float(scale), _p(out, _f32p))
+        return out
+
+    def attn_ref_head(self, qh, h, pos, scale):
+        qh = _c(qh, np.float32)
+        out = np.zeros(self.vd, np.float32)
+        lib().or_mla_attn_ref_q8(self._h, _p(qh, _f32p), h, pos, float(scale), _p(out, _f32p))
+        return out
+
+
+def mla_attn_ref_f32(k, v, qh, h, pos, scale):
+    k, v, qh = _c(k, np.float32), _c(v, np.float32), _c(qh, np.float32)
+    _, nh, hd = k.shape
+    vd = v.shape[2]
+    out = np.empty(vd, np.float32)
+    lib().or_mla_attn_ref_f32(_p(k, _f32p), _p(v, _f32p), nh, hd, vd, _p(qh, _f32p), h, pos, float(scale), _p(out, _f32p))
+    return out
+
+
+def mla_attn_flash_f32(k, v, qh, h, pos, scale):
+    k, v, qh = _c(k, np.float32), _c(v, np.float32), _c(qh, np.float32)
+    _, nh, hd = k.shape
+    vd = v.shape[2]
+    out = np.empty(vd, np.float32)
+    lib().or_mla_attn_flash_f32(_p(k, _f32p), _p(v, _f32p), nh, hd, vd, _p(qh, _f32p), h, pos, float(scale), _p(out, _f32p))
+    return out
+
+
+class MlaAbsCache:
+    """q8_0 cache of one shared latent row per position (absorbed form)."""
+
+    def __init__(self, lat, vd, cap):
+        self.lat, self.vd, self.cap, self.n = lat, vd, cap, 0
+        self._h = lib().or_mla_abs_new(lat, vd, cap)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().or_mla_abs_free(self._h)
+            self._h = None
+
+    def push(self, row):
+        row = _c(row, np.float32)
+        assert self.n < self.cap
+        lib().or_mla_abs_push(self._h, _p(row, _f32p))
+        self.n += 1
+
+    def push_many(self, rows):
+        for r in _c(rows, np.float32):
+            self.push(r)
+
+    def attn(self, q, pos, scale):
+        q = _c(q, np.float32)
+        nh = q.shape[0]
+        out = np.empty((nh, self.vd), np.float32)
+        lib().or_mla_abs_attn(self._h, _p(q, _f32p), nh, pos, float(scale), _p(out, _f32p))
+        return out
+
+    def attn_f64(self, q, pos, scale):
+        q = _c(q, np.float32)
+        nh = q.shape[0]
+        out = np.empty((nh, self.vd), np.float64)
+        lib().or_mla_abs_attn_f64(self._h, _p(q, _f32p), nh, pos, float(scale), _p(out, _f64p))
+        return out
+
+
+def f32_to_f16_bits(a):
+    a = _c(a, np.float32).ravel()
+    return np.array([lib().or_f32_to_f16(float(v)) for v in a], np.uint16)

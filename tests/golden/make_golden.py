@@ -1,0 +1,82 @@
+"""Generates the committed golden fixtures from the reference checkout.
+
+Run once where the reference project is mounted (default /root/reference):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+It (1) extracts the vectors the reference's own `selftest` consumes for this
+path from ref/ds_golden.json (fp4 block, src/selftest.rs:226-234) and
+ref/ds_golden2.json (gate + expert, src/selftest.rs:259-323), and (2) imports
+the two reference Python helpers that touch this path - ref/mxfp4_numpy.py
+(dequant) and nano/export.py::quantize_mxfp4 (naive-scale quantizer) - and
+records their outputs on seeded random inputs.  The fixtures are small .npz
+files next to this script; tests never read the reference checkout.
+"""
+import importlib.util
+import json
+import os
+import sys
+
+import numpy as np
+
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def _load(path, name):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main():
+    # 1. torch-generated fp4 block the reference selftest checks dequant against
+    g = json.load(open(os.path.join(REF, "ref/ds_golden.json")))["fp4"]
+    np.savez(os.path.join(OUT, "ds_fp4.npz"),
+             rows=np.int64(g["rows"]), cols=np.int64(g["cols"]),
+             packed=np.array(g["packed"], np.uint8), scales=np.array(g["scales"], np.uint8),
+             dequant=np.array(g["dequant"], np.float32))
+
+    # 2. DeepSeek gate (3 tokens x 32 experts, top-6, route_scale 1.5) and SwiGLU-clamp expert
+    g2 = json.load(open(os.path.join(REF, "ref/ds_golden2.json")))
+    gate, ex = g2["gate"], g2["expert"]
+    np.savez(os.path.join(OUT, "ds_gate_expert.npz"),
+             gate_x=np.array(gate["x"], np.float32).reshape(3, 16),
+             gate_w=np.array(gate["gate_w"], np.float32).reshape(32, 16),
+             gate_bias=np.array(gate["bias"], np.float32),
+             gate_indices=np.array(gate["indices"], np.int32).reshape(3, 6),
+             gate_weights=np.array(gate["weights"], np.float32).reshape(3, 6),
+             ex_x=np.array(ex["x"], np.float32),
+             ex_w1=np.array(ex["w1"], np.float32).reshape(16, 8),
+             ex_w2=np.array(ex["w2"], np.float32).reshape(8, 16),
+             ex_w3=np.array(ex["w3"], np.float32).reshape(16, 8),
+             ex_out=np.array(ex["out"], np.float32))
+
+    # 3. reference numpy dequant on random blobs (all 16 codes, scale bytes 90..139 plus 0 and 1)
+    mx = _load(os.path.join(REF, "ref/mxfp4_numpy.py"), "ref_mxfp4_numpy")
+    rng = np.random.default_rng(20240601)
+    rows, cols = 24, 256
+    packed = rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8)
+    scales = rng.integers(90, 140, (rows, cols // 32), dtype=np.uint8)
+    # bytes 0 and 1 exercise the subnormal scales.  Bytes near 254 are left out:
+    # numpy's float32 exp2 is off by an ulp there, while the engine's exp2_i
+    # (src/mxfp4.rs:10-16) builds the power of two from its bit pattern.
+    scales[0, 0], scales[1, 1] = 0, 1
+    with np.errstate(all="ignore"):
+        deq = mx.dequant_mxfp4(packed, scales).astype(np.float32)
+    np.savez(os.path.join(OUT, "mxfp4_numpy_dequant.npz"), packed=packed, scales=scales, dequant=deq)
+
+    # 4. reference naive-rule quantizer (nano/export.py) on seeded gaussian + edge rows
+    ex_mod = _load(os.path.join(REF, "nano/export.py"), "ref_nano_export")
+    w = (rng.standard_normal((16, 128)) * 0.02).astype(np.float32)
+    w[3, :32] = 0.0                      # all-zero block -> scale byte 0
+    w[4, 32:64] = np.float32(6.0 * 0.25) * np.sign(rng.standard_normal(32)).astype(np.float32)
+    w[5, 0] = -0.0
+    p, s = ex_mod.quantize_mxfp4(w)
+    np.savez(os.path.join(OUT, "export_quantize_naive.npz"), w=w, packed=p.astype(np.uint8), scales=s.astype(np.uint8))
+    print("wrote fixtures to", OUT)
+
+
+if __name__ == "__main__":
+    main()

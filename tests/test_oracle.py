@@ -1,0 +1,389 @@
+"""CPU tests that pin the oracle (oracle/mk_oracle.c) against the reference:
+committed golden vectors first, then the reference's own unit tests and
+selftest sections restated (file:line cited per test)."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN, bits, pattern, pattern_matrix
+from oracle import oracle as O
+
+
+# ------------------------------------------------------------------ golden vectors
+def test_dequant_matches_torch_golden_fp4_block():
+    """ref/ds_golden.json 'fp4' (src/selftest.rs:226-234): 8x64 block, torch dequant."""
+    g = np.load(os.path.join(GOLDEN, "ds_fp4.npz"))
+    rows, cols = int(g["rows"]), int(g["cols"])
+    got = O.mxfp4_dequant(g["packed"].reshape(rows, cols // 2), g["scales"].reshape(rows, cols // 32), rows, cols)
+    want = g["dequant"].reshape(rows, cols)
+    assert np.array_equal(got, want)  # selftest tolerance is 1e-4; the values are exact
+
+
+def test_dequant_matches_reference_numpy_bitwise():
+    """ref/mxfp4_numpy.py::dequant_mxfp4 on random blobs incl. scale bytes 0 and 1."""
+    g = np.load(os.path.join(GOLDEN, "mxfp4_numpy_dequant.npz"))
+    rows, cols = g["packed"].shape[0], g["packed"].shape[1] * 2
+    got = O.mxfp4_dequant(g["packed"], g["scales"], rows, cols)
+    assert np.array_equal(bits(got), bits(g["dequant"]))  # bit-exact incl. -0.0 and subnormals
+
+
+def test_quantize_naive_matches_reference_export():
+    """nano/export.py::quantize_mxfp4 == mxfp4::quantize_naive (src/mxfp4.rs:45-47)."""
+    g = np.load(os.path.join(GOLDEN, "export_quantize_naive.npz"))
+    p, s = O.mxfp4_quantize(g["w"], search=False)
+    assert np.array_equal(s, g["scales"])
+    assert np.array_equal(p, g["packed"])
+
+
+def test_ds_gate_matches_golden():
+    """ref/ds_golden2.json 'gate' (src/selftest.rs:259-311): ids exact as sets, weights 1e-5+1e-3*scale."""
+    g = np.load(os.path.join(GOLDEN, "ds_gate_expert.npz"))
+    scale = np.abs(g["gate_weights"]).max()
+    for t in range(3):
+        ids, w = O.gate_ds(g["gate_w"], g["gate_bias"], g["gate_x"][t], 6, 1.5)
+        assert sorted(ids.tolist()) == sorted(g["gate_indices"][t].tolist())
+        want = dict(zip(g["gate_indices"][t].tolist(), g["gate_weights"][t].tolist()))
+        for i, wi in zip(ids.tolist(), w.tolist()):
+            assert abs(wi - want[i]) <= 1e-5 + 1e-3 * scale
+
+
+def test_ds_expert_matches_golden():
+    """ref/ds_golden2.json 'expert' (src/selftest.rs:314-323), swiglu_limit 10, tol 1e-4."""
+    g = np.load(os.path.join(GOLDEN, "ds_gate_expert.npz"))
+    out = O.expert_ds_f32(g["ex_w1"], g["ex_w2"], g["ex_w3"], g["ex_x"], 10.0)
+    assert np.abs(out - g["ex_out"]).max() <= 1e-4
+
+
+# ------------------------------------------------------------------ src/q8.rs tests
+def test_block_dot_extremes():
+    """q8.rs:290-295: max-magnitude weights against 127s."""
+    x = np.full(32, 127, np.int8)
+    assert O.block_dot(np.full(16, 0x77, np.uint8), x) == 32 * 12 * 127
+    assert O.block_dot(np.full(16, 0xFF, np.uint8), x) == -32 * 12 * 127
+
+
+def test_block_dot_matches_lut_definition():
+    rng = np.random.default_rng(1)
+    lut2 = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12])
+    for _ in range(200):
+        p = rng.integers(0, 256, 16, dtype=np.uint8)
+        x = rng.integers(-127, 128, 32).astype(np.int8)
+        w = np.empty(32, np.int64)
+        w[0::2] = lut2[p & 15]
+        w[1::2] = lut2[p >> 4]
+        assert O.block_dot(p, x) == int((w * x.astype(np.int64)).sum())
+        a = rng.integers(-127, 128, 32).astype(np.int8)
+        assert O.block_dot_i8(a, x) == int((a.astype(np.int64) * x.astype(np.int64)).sum())
+    for sa in (127, -127):
+        for sx in (127, -127):
+            assert O.block_dot_i8(np.full(32, sa, np.int8), np.full(32, sx, np.int8)) == 32 * sa * sx
+
+
+def test_q8_quantize_conventions():
+    """q8.rs:320-334."""
+    x = np.zeros(64, np.float32)
+    x[3], x[40] = 12.7, -3.3
+    q, s = O.q8_quantize(x)
+    assert s[0] == np.float32(12.7) / np.float32(127.0)
+    assert s[1] == np.float32(3.3) / np.float32(127.0)
+    assert q[3] == 127 and q.min() >= -127
+    q, s = O.q8_quantize(np.zeros(32, np.float32))
+    assert s[0] == 0.0 and not q.any()
+
+
+def test_q8_quantize_matches_numpy_definition():
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal(4096).astype(np.float32)
+    q, s = O.q8_quantize(x)
+    xb = x.reshape(-1, 32)
+    dx = np.abs(xb).max(axis=1) / np.float32(127.0)
+    assert np.array_equal(s, dx.astype(np.float32))
+    r = xb / dx[:, None]
+    want = np.clip(np.sign(r) * np.floor(np.abs(r) + np.float32(0.5)), -127, 127).astype(np.int8)
+    assert np.array_equal(q.reshape(-1, 32), want)
+    assert np.abs(q.reshape(-1, 32).astype(np.float32) * dx[:, None] - xb).max() <= dx.max() / 2 * 1.0001
+
+
+# ------------------------------------------------------------------ src/mxfp4.rs tests
+E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+
+
+def _block_errors(w, p, s):
+    rows, cols = w.shape
+    wq = O.mxfp4_dequant(p, s, rows, cols)
+    d = (w.astype(np.float64) - wq.astype(np.float64)) ** 2
+    return d.reshape(-1, 32).sum(axis=1)
+
+
+def _never_worse(w):
+    p0, s0 = O.mxfp4_quantize(w, search=False)
+    p1, s1 = O.mxfp4_quantize(w, search=True)
+    e0, e1 = _block_errors(w, p0, s0), _block_errors(w, p1, s1)
+    assert (e1 <= e0 * (1 + 1e-9) + 1e-20).all()
+
+
+def test_search_never_worse_synthetic():
+    """mxfp4.rs:575-598."""
+    for rows, cols in [(64, 128), (128, 64), (3, 64), (1, 32), (256, 1024)]:
+        _never_worse(pattern_matrix(rows, cols))
+    w = np.full((16, 64), 0.01, np.float32)
+    for g in range(16 * 64 // 32):
+        w.reshape(-1)[g * 32] = 3.7 if g % 2 == 0 else -5.9
+    _never_worse(w)
+    _never_worse(np.zeros((2, 32), np.float32))
+    _never_worse((E2M1[np.arange(64) % 16] * np.float32(0.125)).reshape(2, 32))
+
+
+def test_roundtrip_exact_levels():
+    """mxfp4.rs:600-611."""
+    w = (E2M1[np.arange(4 * 64) % 16] * np.float32(0.25)).reshape(4, 64)
+    p, s = O.mxfp4_quantize(w)
+    wq = O.mxfp4_dequant(p, s, 4, 64)
+    assert np.array_equal(w, wq)
+
+
+def test_all_zero_block_gets_scale_byte_zero_and_negative_zero_code():
+    w = np.zeros((1, 64), np.float32)
+    w[0, 5] = -0.0
+    w[0, 40] = 1.0
+    p, s = O.mxfp4_quantize(w)
+    assert s[0, 0] == 0
+    assert (p[0, 2] >> 4) == 8  # -0.0 keeps its sign: code 8 (mxfp4.rs:124-126)
+    assert O.lib().or_exp2_i(-127) == np.float32(2.0) ** -127
+    assert O.lib().or_scale_from_byte(0) == O.lib().or_exp2_i(-127)
+
+
+SHAPES = [(128, 512), (512, 128), (64, 128), (3, 64), (1, 32), (256, 1024), (2048, 4096), (4096, 2048)]
+
+
+def _case(rows, cols, zero_rows=None):
+    w = pattern_matrix(rows, cols)
+    if zero_rows:
+        w[zero_rows[0]:zero_rows[1]] = 0.0
+    p, s = O.mxfp4_quantize(w)
+    x = pattern(np.arange(cols, dtype=np.uint64) + np.uint64(4242))
+    return p, s, x
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_packed_emul_within_1e3(rows, cols):
+    """selftest.rs:534-595 PACKED-EMUL: GPU-order emulation vs the exact f32 path, 1e-3 rel."""
+    p, s, x = _case(rows, cols)
+    y_ref = O.mxfp4_matvec(p, s, x, use_q8=False)
+    y_emul = O.mxfp4_matvec_shader_emul(p, s, x, 256)
+    scale = max(np.abs(y_ref).max(), 1e-12)
+    assert np.abs(y_emul.astype(np.float64) - y_ref).max() / scale <= 1e-3
+
+
+def test_packed_emul_zero_block():
+    p, s, x = _case(64, 128, zero_rows=(2, 4))
+    assert (s[2:4] == 0).all()
+    y_ref = O.mxfp4_matvec(p, s, x, use_q8=False)
+    y_emul = O.mxfp4_matvec_shader_emul(p, s, x, 256)
+    assert np.abs(y_emul - y_ref).max() / max(np.abs(y_ref).max(), 1e-12) <= 1e-3
+    assert (y_ref[2:4] == 0).all()
+
+
+@pytest.mark.parametrize("rows,cols,nt", [(128, 512, 1), (512, 128, 1), (64, 128, 1), (3, 64, 1), (1, 32, 1),
+                                          (256, 1024, 1), (2048, 4096, 1), (333, 1024, 4)])
+def test_q8_emul_within_1e3(rows, cols, nt):
+    """selftest.rs:601-646 Q8-EMUL: integer q8 path vs exact f32 path, 1e-3 rel."""
+    p, s, x = _case(rows, cols)
+    y_ref = O.mxfp4_matvec(p, s, x, use_q8=False, n_threads=nt)
+    y_q8 = O.mxfp4_matvec(p, s, x, use_q8=True, n_threads=nt)
+    scale = max(np.abs(y_ref).max(), 1e-12)
+    assert np.abs(y_q8.astype(np.float64) - y_ref).max() / scale <= 1e-3
+    # threaded == single-threaded, bit for bit
+    assert np.array_equal(bits(O.mxfp4_matvec(p, s, x, use_q8=True, n_threads=1)), bits(y_q8))
+
+
+def test_matvec_f32_equals_dequant_times_x_in_reference_order():
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((8, 96)) * 0.02).astype(np.float32)
+    p, s = O.mxfp4_quantize(w)
+    x = rng.standard_normal(96).astype(np.float32)
+    y = O.mxfp4_matvec(p, s, x, use_q8=False)
+    codes = np.empty((8, 96), np.uint8)
+    codes[:, 0::2], codes[:, 1::2] = p & 15, p >> 4
+    for r in range(8):
+        tot = np.float32(0)
+        for g in range(3):
+            gs = np.float32(0)
+            for j in range(32):
+                gs = np.float32(gs + np.float32(E2M1[codes[r, g * 32 + j]] * x[g * 32 + j]))
+            tot = np.float32(tot + np.float32(gs * np.float32(2.0) ** (int(s[r, g]) - 127)))
+        assert bits(y[r:r + 1])[0] == bits(np.array([tot]))[0]
+
+
+def test_matvec_nt_bit_identical_to_single():
+    """model.rs:2398-2411: batched order == per-position matvec_packed (f32 path), bit for bit."""
+    rng = np.random.default_rng(4)
+    w = (rng.standard_normal((40, 128)) * 0.02).astype(np.float32)
+    p, s = O.mxfp4_quantize(w)
+    xs = rng.standard_normal((8, 128)).astype(np.float32)
+    out = O.mxfp4_matvec_nt(p, s, xs)
+    for t in range(8):
+        assert np.array_equal(bits(out[t]), bits(O.mxfp4_matvec(p, s, xs[t], use_q8=False)))
+
+
+# ------------------------------------------------------------------ src/model.rs tests
+def test_dot_order():
+    """model.rs:63-82: 8 lanes, mul then add, ((p01+p23)+p45)+p67, tail sequential."""
+    rng = np.random.default_rng(5)
+    for n in (1, 7, 8, 9, 64, 67, 7168):
+        a, b = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+        acc = np.zeros(8, np.float32)
+        full = n // 8 * 8
+        for i in range(0, full, 8):
+            acc = (acc + a[i:i + 8] * b[i:i + 8]).astype(np.float32)
+        s = np.float32(np.float32(np.float32(acc[0] + acc[1]) + np.float32(acc[2] + acc[3]))
+                       + np.float32(acc[4] + acc[5]))
+        s = np.float32(s + np.float32(acc[6] + acc[7]))
+        for i in range(full, n):
+            s = np.float32(s + np.float32(a[i] * b[i]))
+        assert np.float32(O.dot(a, b)) == s
+
+
+def test_q8_head_close_to_f32_and_same_argmax():
+    """model.rs:3866-3881: err/span < 1e-2 and identical argmax."""
+    rng = np.random.default_rng(6)
+    rows, cols = 512, 256
+    w = (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32)
+    x = rng.standard_normal(cols).astype(np.float32)
+    q, s = O.q8head_from_f32(w)
+    y8 = O.q8head_matvec(q, s, x, n_threads=4)
+    y = O.matvec_f32(w, x)
+    span = y.max() - y.min()
+    assert np.abs(y8 - y).max() / span < 1e-2
+    assert O.argmax(y8) == O.argmax(y) == int(np.argmax(y))
+    assert np.array_equal(bits(y8), bits(O.q8head_matvec(q, s, x, n_threads=1)))
+
+
+def test_f16_helpers_match_numpy():
+    rng = np.random.default_rng(7)
+    v = np.concatenate([rng.standard_normal(2000).astype(np.float32) * np.float32(1e-3),
+                        np.array([0, -0.0, 6e-8, 5.9e-8, 3e-8, 2.98e-8, 65504, 65520, 1e-5, 6.1e-5, 6.2e-5], np.float32)])
+    got = O.f32_to_f16_bits(v)
+    assert np.array_equal(got, v.astype(np.float16).view(np.uint16))
+    back = np.array([O.lib().or_f16_to_f32(int(h)) for h in got], np.float32)
+    assert np.array_equal(bits(back), bits(got.view(np.float16).astype(np.float32)))
+
+
+def test_q8_head_f16_scale_variant():
+    rng = np.random.default_rng(8)
+    w = (rng.standard_normal((64, 128)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(128).astype(np.float32)
+    q, sh = O.q8head_from_f32_f16s(w)
+    y = O.q8head_matvec_f16s(q, sh, x)
+    ref = O.matvec_f32(w, x)
+    assert np.abs(y - ref).max() / (ref.max() - ref.min()) < 1e-2
+    dx = sh.view(np.float16).astype(np.float32)
+    assert np.abs(q.reshape(64, 4, 32) * dx[:, :, None] - w.reshape(64, 4, 32)).max() <= dx.max() * 0.5 * 1.001 + dx.max() / 127
+
+
+def test_router_k3_properties():
+    """model.rs:2153-2173: slot order = key descending, earlier index wins ties, weights sum to 1."""
+    rng = np.random.default_rng(9)
+    n, d, k = 64, 48, 8
+    gw = (rng.standard_normal((n, d)) * 0.02).astype(np.float32)
+    gb = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    x = rng.standard_normal(d).astype(np.float32)
+    ids, w, logits = O.router_k3(gw, gb, x, k)
+    sc = np.array([O.lib().or_sigmoid(float(l)) for l in logits], np.float32)
+    key = (sc + gb).astype(np.float32)
+    order = sorted(range(n), key=lambda i: (-key[i], i))[:k]
+    assert ids.tolist() == order
+    assert abs(w.sum() - 1) < 1e-6
+    # exact ties: duplicate rows -> the lower index must come first
+    gw[10] = gw[3]
+    gb[:] = 0
+    ids, w, _ = O.router_k3(gw, gb, (gw[3] * 50).astype(np.float32), k)
+    assert ids[0] == 3 and ids[1] == 10
+
+
+# ------------------------------------------------------------------ selftest FLASH / KVQ8
+MICRO = dict(nh=4, nope=128, rope=64, vd=128)  # src/config.rs:47-79 micro MLA dims
+
+
+@pytest.mark.parametrize("length", [1, 7, 64, 65, 512])
+def test_flash_vs_materialized_f32(length):
+    """selftest.rs:656-704 FLASH: online softmax vs materialized, 1e-5 abs."""
+    nh, hd, vd = MICRO["nh"], MICRO["nope"] + MICRO["rope"], MICRO["vd"]
+    k = pattern_matrix(length * nh, hd).reshape(length, nh, hd)
+    v = pattern_matrix(length * nh, vd, offset=99991).reshape(length, nh, vd)
+    q = pattern(np.arange(nh * hd, dtype=np.uint64) + np.uint64(777)).reshape(nh, hd)
+    scale = np.float32(hd) ** np.float32(-0.5)
+    for h in range(nh):
+        a = O.mla_attn_ref_f32(k, v, q[h], h, length - 1, scale)
+        b = O.mla_attn_flash_f32(k, v, q[h], h, length - 1, scale)
+        assert np.abs(a.astype(np.float64) - b).max() <= 1e-5
+
+
+def _kv_rows(j, nh, hd, vd, nope, rope, spike):
+    kr = pattern(np.arange(nh * hd, dtype=np.uint64) + np.uint64(j * 7919)).copy()
+    vr = pattern(np.arange(nh * vd, dtype=np.uint64) + np.uint64(j * 5449 + 313)).copy()
+    for h in range(1, nh):
+        kr[h * hd + nope:h * hd + nope + rope] = kr[nope:nope + rope]
+    if spike and j % 3 == 0:
+        for h in range(nh):
+            kr[h * hd + 5] = np.float32(30.0) * pattern(j + 17)
+            vr[h * vd + 9] = np.float32(30.0) * pattern(j + 23)
+    return kr, vr
+
+
+@pytest.mark.parametrize("length,spike", [(1, False), (7, False), (64, False), (65, False), (512, False), (512, True)])
+def test_kvq8(length, spike):
+    """selftest.rs:716-900 KVQ8 (Hadamard off): MQA kernel bit-identical to the per-head
+    loop, roundtrip within dx/2, rope exact, attention rel <= 1e-2 (3e-2 spiked)."""
+    nh, nope, rope, vd = MICRO["nh"], MICRO["nope"], MICRO["rope"], MICRO["vd"]
+    hd = nope + rope
+    c = O.MlaCache(nh, nope, rope, vd, length)
+    kf = np.empty((length, nh, hd), np.float32)
+    vf = np.empty((length, nh, vd), np.float32)
+    for j in range(length):
+        kr, vr = _kv_rows(j, nh, hd, vd, nope, rope, spike)
+        kf[j], vf[j] = kr.reshape(nh, hd), vr.reshape(nh, vd)
+        c.push(kr, vr)
+    q = pattern(np.arange(nh * hd, dtype=np.uint64) + np.uint64(4242)).reshape(nh, hd)
+    scale = np.float32(hd) ** np.float32(-0.5)
+    pos = length - 1
+    mqa = c.attn_mqa(q, pos, scale)
+    per_head = np.stack([c.attn_head(q[h], h, pos, scale) for h in range(nh)])
+    assert np.array_equal(bits(mqa), bits(per_head))
+    k2, v2 = c.to_f32()
+    assert np.array_equal(k2[:, :, nope:], kf[:, :, nope:])  # rope stays exact
+    bound = max(np.abs(kf[:, :, :nope]).reshape(-1, 32).max(axis=1).max(),
+                np.abs(vf).reshape(-1, 32).max(axis=1).max()) / 254.0
+    err = max(np.abs(k2[:, :, :nope] - kf[:, :, :nope]).max(), np.abs(v2 - vf).max())
+    assert err <= bound * 1.02
+    worst = 0.0
+    for h in range(nh):
+        a = O.mla_attn_flash_f32(kf, vf, q[h], h, pos, scale)
+        worst = max(worst, np.abs(a.astype(np.float64) - per_head[h]).max() / max(np.abs(a).max(), 1e-12))
+    assert worst <= (3e-2 if spike else 1e-2)
+
+
+def test_absorbed_attention_against_f64_dense():
+    """No reference function for the shared-latent layout: the tiled f32 restatement is
+    checked against an f64 dense softmax over the same dequantized cache."""
+    rng = np.random.default_rng(10)
+    lat, vd, nh, n = 576, 512, 8, 200
+    c = O.MlaAbsCache(lat, vd, n)
+    c.push_many(rng.standard_normal((n, lat)).astype(np.float32))
+    q = rng.standard_normal((nh, lat)).astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(192.0))
+    for pos in (0, 63, 64, n - 1):
+        a = c.attn(q, pos, scale)
+        b = c.attn_f64(q, pos, scale)
+        # the gap is the q8 rounding of the query (selftest.rs:849-858 'q-rounding')
+        assert np.abs(a - b).max() / np.abs(b).max() < 2e-2
+
+
+def test_rng_is_deterministic_and_gaussian():
+    """build.rs:21-51. No vector of this generator is committed in the reference: statistical check only."""
+    a = O.fill_gauss("bench.cfg1.w", 0.02, 20000)
+    b = O.fill_gauss("bench.cfg1.w", 0.02, 20000)
+    c = O.fill_gauss("bench.cfg1.x", 0.02, 20000)
+    assert np.array_equal(a, b) and not np.array_equal(a, c)
+    assert abs(a.mean()) < 1e-3 and abs(a.std() - 0.02) < 1e-3
