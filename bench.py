@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized decode hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (this library)
+    python bench.py --impl reference --gpus N --steps K ...  (CPU restatement of the reference path)
+
+Workload: the q8_0 lm_head GEMV - W is vocab 163840 x hidden 7168 drawn from
+N(0, 0.02) and quantized row-wise to q8_0 (32-wide blocks, int8 values + one f32
+scale per block, the engine's layout); x is f32[7168] from N(0, 1); batch 1.  A
+step is one logits projection (activation quantization + GEMV + greedy argmax).
+With N > 1 GPUs the vocabulary is sharded V/N rows per rank and the f32 logits
+are all-gathered (NCCL); total work is fixed, so scaling is "strong".
+
+metric = quantized GB/s: algorithmic bytes of one step (int8 values + block
+scales + x + logits) divided by the step time, summed over all ranks.
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+VOCAB, HIDDEN = 163840, 7168
+SIGMA_W = 0.02
+L2_BYTES = 126 * 1024 * 1024
+CPU_SAMPLE_ROWS = 32768  # bounded sample of the workload for the CPU legs (235 MB of int8, > any LLC)
+
+
+def algorithmic_bytes(rows, cols, batch, scale_bytes=4):
+    """int8 values + block scales + x (f32) + logits (f32), per step."""
+    return rows * cols + rows * (cols // 32) * scale_bytes + batch * cols * 4 + batch * rows * 4
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------- CPU legs (the oracle is the thing timed here)
+def cpu_leg(steps, warmup, rows=CPU_SAMPLE_ROWS):
+    """Times the CPU restatement of Q8Head::matvec (all host threads) on a bounded
+    sample of the workload: the first `rows` vocabulary rows."""
+    from oracle import oracle as O
+    threads = O.num_threads()
+    rng = np.random.default_rng(1234)
+    w = rng.standard_normal((rows, HIDDEN), dtype=np.float32) * np.float32(SIGMA_W)
+    q, s = O.q8head_from_f32(w)
+    del w
+    x = rng.standard_normal(HIDDEN).astype(np.float32)
+    for _ in range(max(1, warmup)):
+        O.q8head_matvec(q, s, x, n_threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.q8head_matvec(q, s, x, n_threads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    gbs = algorithmic_bytes(rows, HIDDEN, 1) / dt / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"first {rows} of {VOCAB} vocabulary rows x {HIDDEN}, batch 1, {steps} steps, "
+                      f"C restatement of Q8Head::matvec with {threads} OpenMP threads"}, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = min(args.steps, 40)
+    cb, dt = cpu_leg(steps, min(args.warmup, 3))
+    line = {
+        "impl": "reference", "metric": "quantized GB/s, q8_0 lm_head GEMV", "value": cb["value"], "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "q8_0 lm_head GEMV 163840x7168 batch 1 (CPU: bounded sample of the rows)",
+                   "rows_sampled": CPU_SAMPLE_ROWS},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- GPU arm
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import microkimi_b200 as mk
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ctx = mk.Context(local)
+    mk.Context._default = ctx
+    ctx.use_torch_stream()
+
+    batch = args.batch
+    rows = VOCAB // world
+    shard_bytes = rows * HIDDEN + rows * (HIDDEN // 32) * 4
+    # keep every timed pass cold in L2: rotate over copies when a shard is small
+    copies = 1 if shard_bytes >= 4 * L2_BYTES else int(np.ceil(4 * L2_BYTES / shard_bytes))
+    heads = []
+    gen = torch.Generator(device=dev)
+    for c in range(copies):
+        gen.manual_seed(1000 + 17 * rank + c)
+        wf = torch.empty((rows, HIDDEN), dtype=torch.float32, device=dev)
+        wf.normal_(0.0, SIGMA_W, generator=gen)
+        heads.append(mk.Q8Head.from_f32(wf, rows, HIDDEN, ctx=ctx))
+        del wf
+    torch.cuda.empty_cache()
+    gen.manual_seed(7)
+    x = torch.randn((batch, HIDDEN), dtype=torch.float32, device=dev, generator=gen)
+    logits = torch.empty((batch, VOCAB), dtype=torch.float32, device=dev) if world > 1 else None
+
+    def step(i):
+        if world == 1:
+            y, _ = heads[i % copies].matvec(x, want_argmax=True)
+            return y
+        y = heads[i % copies].matvec(x)
+        if world > 1:
+            # vocab-sharded logits -> full logits on every rank
+            if batch == 1:
+                dist.all_gather_into_tensor(logits.view(-1), y.view(-1))
+            else:
+                parts = [logits[:, r * rows:(r + 1) * rows] for r in range(world)]
+                dist.all_gather(parts, y)  # strided destination views
+            return logits
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launches
+    ctx.prof_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    kn, kms = ctx.prof_read("lm_head")
+    ctx.prof_enable(False)
+    launches = ctx.launches - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # ---- end to end through the host-pointer entry point (pinned host buffers)
+    xh = torch.empty((batch, HIDDEN), dtype=torch.float32).pin_memory()
+    xh.copy_(x.cpu())
+    xn = xh.numpy()
+    e2e_steps = max(10, min(args.steps, 100))
+    heads[0].matvec(xn, want_argmax=True)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        yh, amh = heads[i % copies].matvec(xn, want_argmax=True)
+    torch.cuda.synchronize()
+    e2e_dt = (time.perf_counter() - t0) / e2e_steps
+    te = torch.tensor([e2e_dt], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_dt = float(te.item())
+
+    alg_step = algorithmic_bytes(rows, HIDDEN, batch) * world
+    value = alg_step / (ms_step * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    kern_ms = kms / max(kn, 1)
+    achieved = algorithmic_bytes(rows, HIDDEN, batch) / (kern_ms * 1e-3) / 1e9 if kn else None
+
+    if rank == 0:
+        cb = None
+        if world == 1 and not args.no_cpu:
+            cb, _ = cpu_leg(8, 2)
+        line = {
+            "metric": "quantized GB/s, q8_0 lm_head GEMV", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"q8_0 lm_head GEMV {VOCAB}x{HIDDEN} (f32 block scales), batch {batch}, "
+                                   f"vocab-sharded {world} way(s) + f32 logits all-gather",
+                       "batch": batch, "rows_per_gpu": rows,
+                       "l2": f"inputs larger than L2: {shard_bytes * copies / 1e6:.0f} MB of weights per GPU"
+                             + (f" ({copies} rotating copies of the shard)" if copies > 1 else ""),
+                       "algorithmic_bytes_per_step": alg_step},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "peak_kind": peak_kind, "kernel": "qgemv_spread_kernel<q8_0>",
+                         "kernel_ms": kern_ms, "kernel_launches": kn, "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
+            "cpu_baseline": cb,
+            "e2e": {"value": alg_step / e2e_dt / 1e9, "unit": "GB/s", "ms_per_step": e2e_dt * 1e3,
+                    "h2d_bytes_per_step": batch * HIDDEN * 4, "d2h_bytes_per_step": batch * rows * 4 + batch * 4,
+                    "api": "mk_matvec_q8 (host pointers, pinned)"},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

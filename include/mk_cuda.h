@@ -1,0 +1,147 @@
+/*
+ * mk_cuda.h - C ABI of libmk_b200.so: the quantized decode hot path of the
+ * microkimi engine as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * This is the surface a `src/cuda.rs` `extern "C"` block binds.  It takes the
+ * place of the engine's Metal hook (src/metal.rs) and of the CPU operators that
+ * hook stands in for; each entry point names the reference interface it
+ * replaces (file:line within the reference project).
+ *
+ * Conventions
+ *  - every function returns an int32 status: MK_OK (0) or a negative MK_ERR_*;
+ *    nothing throws, aborts or falls back to a CPU path.  mk_last_error()
+ *    gives a thread-local message for the last failure on this thread.
+ *  - plain pointers and sizes only.  `_dev` variants take DEVICE pointers of the
+ *    context's GPU and enqueue on the context's stream without synchronizing;
+ *    the others take HOST pointers, copy in, run, copy out and synchronize, like
+ *    metal::gpu_matvec_fp4 does (src/metal.rs:943-1018).
+ *  - a context is bound to one GPU and is thread-compatible, not re-entrant:
+ *    concurrent callers must serialize, as the Metal path does on its io mutex
+ *    (src/metal.rs:432-437).
+ *  - weights are uploaded (and re-tiled for the tensor-core fragment order)
+ *    ONCE at registration, like the Metal weight cache (src/metal.rs:387-396);
+ *    the caller keeps ownership of the host bytes.  Values are unchanged:
+ *    mk_weight_export() returns the registered bytes in their original layout.
+ */
+#ifndef MK_CUDA_H
+#define MK_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_OK            0
+#define MK_ERR_ARG      -1   /* bad pointer, size or handle                     */
+#define MK_ERR_CUDA     -2   /* a CUDA runtime call failed                      */
+#define MK_ERR_OOM      -3   /* device allocation failed                        */
+#define MK_ERR_STATE    -4   /* call not valid in the object's current state    */
+#define MK_ERR_TIMEOUT  -5   /* a bounded device-side wait ran out              */
+#define MK_ERR_UNSUPPORTED -6
+
+typedef struct mk_ctx    mk_ctx;
+typedef struct mk_weight mk_weight;
+typedef struct mk_moe    mk_moe;
+typedef struct mk_mla    mk_mla;
+
+/* How the f32 activation enters the integer block dot.
+ * MK_ACT_Q8   : q8_0, one int8 per element - the engine's default path
+ *               (src/mxfp4.rs:480-487 -> src/q8.rs:49-69).
+ * MK_ACT_Q8X2 : two int8 limbs per element (15-bit activation), for callers
+ *               that want to stay close to the exact-f32 path
+ *               (src/mxfp4.rs:488-539) at the same memory traffic. */
+#define MK_ACT_Q8    0
+#define MK_ACT_Q8X2  1
+/* OR into act_mode: accumulate the per-block terms of every output strictly in
+ * ascending block order with separate multiply and add, reproducing the CPU
+ * result of src/mxfp4.rs:409-418 / src/model.rs:337-347 bit for bit (slower). */
+#define MK_ACT_STRICT 0x100
+
+/* q8_0 scale storage.  F32 is the engine's layout (src/q8.rs:26-29,
+ * src/model.rs:261-266); F16 halves the scale stream. */
+#define MK_SCALE_F32 0
+#define MK_SCALE_F16 1
+
+/* ---- context ---------------------------------------------------------- */
+/* Replaces metal::gpu_available / init_ctx (src/metal.rs:445-452): binds GPU
+ * `device`; fails (no fallback) when it is not an sm_100 part. */
+int32_t mk_init(int32_t device, mk_ctx **out);
+int32_t mk_shutdown(mk_ctx *ctx);
+const char *mk_last_error(void);
+/* Stream used by every call on this context (a cudaStream_t); NULL selects the
+ * context's own stream. */
+int32_t mk_set_stream(mk_ctx *ctx, void *cuda_stream);
+int32_t mk_sync(mk_ctx *ctx);
+/* Number of kernels this context has launched since mk_init. */
+int64_t mk_launch_count(mk_ctx *ctx);
+int32_t mk_device_info(mk_ctx *ctx, int32_t *sm_count, int32_t *cc_major, int32_t *cc_minor, uint64_t *mem_bytes);
+/* Device-side status word: 0, or the first MK_ERR_* a kernel recorded (bounded
+ * waits, range checks).  Reading it synchronizes the stream. */
+int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
+
+/* Tuning knobs, for measurement only (defaults are chosen per shape):
+ *   "force_ks" : K split of the matvec kernels, one of 0 (auto), 1, 2, 4, 8. */
+int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value);
+
+/* Per-category kernel timing with CUDA events on the context's stream, the
+ * counterpart of the engine's Prof accumulators (src/model.rs:791-835).
+ * Categories: MK_PROF_*.  mk_prof_read synchronizes the stream, then returns the
+ * number of timed launches and their summed device time since the last enable. */
+#define MK_PROF_MATVEC_MXFP4 0
+#define MK_PROF_LM_HEAD      1
+#define MK_PROF_ROUTER       2
+#define MK_PROF_EXPERTS      3
+#define MK_PROF_MLA          4
+#define MK_PROF_OTHER        5
+#define MK_PROF_NCAT         6
+int32_t mk_prof_enable(mk_ctx *ctx, int32_t on);
+int32_t mk_prof_read(mk_ctx *ctx, int32_t category, int64_t *launches, double *total_ms);
+
+/* ---- weights ---------------------------------------------------------- */
+/* MXFP4 matrix: packed u8 [rows, cols/2] (low nibble = even column) and ue8m0
+ * scales u8 [rows, cols/32] - BinFile::mxfp4_parts (src/weights.rs:619-626),
+ * the arguments of mxfp4::matvec_packed (src/mxfp4.rs:458).  cols % 32 == 0.
+ * src_on_device != 0: the pointers are device pointers (copied, not adopted). */
+int32_t mk_weight_mxfp4(mk_ctx *ctx, const uint8_t *packed, const uint8_t *scales,
+                        int64_t rows, int64_t cols, int32_t src_on_device, mk_weight **out);
+/* Row-wise q8_0 copy of an f32 matrix, built on the GPU, bit-identical to
+ * Q8Head::from_f32 (src/model.rs:274-286) for MK_SCALE_F32. */
+int32_t mk_weight_q8_from_f32(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols,
+                              int32_t scale_type, int32_t src_on_device, mk_weight **out);
+/* Already-quantized q8_0 rows: q i8 [rows, cols], scales [rows, cols/32]
+ * (f32 or IEEE half according to scale_type). */
+int32_t mk_weight_q8(mk_ctx *ctx, const int8_t *q, const void *scales, int64_t rows, int64_t cols,
+                     int32_t scale_type, int32_t src_on_device, mk_weight **out);
+int32_t mk_weight_free(mk_ctx *ctx, mk_weight *w);
+/* Bytes held on the device for this weight (values + scales). */
+int64_t mk_weight_bytes(const mk_weight *w);
+/* Copies the registered bytes back to HOST memory in their original layout
+ * (packed/q first, then scales); either pointer may be NULL. */
+int32_t mk_weight_export(mk_ctx *ctx, const mk_weight *w, void *values, void *scales);
+/* mxfp4::dequant (src/mxfp4.rs:19-31) on the GPU: f32 [rows, cols] to HOST. */
+int32_t mk_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out);
+
+/* ---- activations ------------------------------------------------------ */
+/* q8::quantize_q8_into (src/q8.rs:49-69) on the GPU, HOST in / HOST out:
+ * x f32 [n] (n % 32 == 0) -> q i8 [n], scales f32 [n/32].  Bit-identical. */
+int32_t mk_quantize_q8(mk_ctx *ctx, const float *x, int64_t n, int8_t *q, float *scales);
+
+/* ---- matrix x vector -------------------------------------------------- */
+/* mxfp4::matvec_packed / metal::gpu_matvec_fp4 (src/mxfp4.rs:458-539,
+ * src/metal.rs:943-1018): y[b, r] = sum_c W[r, c] * x[b, c] for b < batch.
+ * x f32 [batch, cols], y f32 [batch, rows]. */
+int32_t mk_matvec_mxfp4(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch, int32_t act_mode);
+int32_t mk_matvec_mxfp4_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch, int32_t act_mode);
+/* Q8Head::matvec + the greedy pick of top_k_probs (src/model.rs:290-335,
+ * 3271-3291): y f32 [batch, rows]; argmax (optional, int32 [batch]) = first
+ * index attaining the maximum of each row of y. */
+int32_t mk_matvec_q8(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch,
+                     int32_t act_mode, int32_t *argmax);
+int32_t mk_matvec_q8_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch,
+                         int32_t act_mode, int32_t *argmax);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

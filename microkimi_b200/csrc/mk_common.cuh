@@ -1,0 +1,158 @@
+// Shared declarations for libmk_b200: context, weight records, error plumbing
+// and the small device helpers every kernel file uses (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/mk_cuda.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "libmk_b200 is written for sm_100a only"
+#endif
+
+// ---------------------------------------------------------------- errors
+void mk_set_error(const char *fmt, ...);
+
+#define MK_CHECK_ARG(cond, msg)                                   \
+    do {                                                          \
+        if (!(cond)) {                                            \
+            mk_set_error("%s: %s", __func__, msg);                \
+            return MK_ERR_ARG;                                    \
+        }                                                         \
+    } while (0)
+
+#define MK_CUDA(call)                                                                  \
+    do {                                                                               \
+        cudaError_t e_ = (call);                                                       \
+        if (e_ != cudaSuccess) {                                                       \
+            mk_set_error("%s: %s failed: %s", __func__, #call, cudaGetErrorString(e_)); \
+            return (e_ == cudaErrorMemoryAllocation) ? MK_ERR_OOM : MK_ERR_CUDA;       \
+        }                                                                              \
+    } while (0)
+
+// ---------------------------------------------------------------- records
+enum { MK_FMT_MXFP4 = 0, MK_FMT_Q8 = 1 };
+
+// A registered weight matrix in the fragment-major ("tiled") device layout.
+//
+// Rows are cut into tiles of 16, columns into q8/mxfp4 blocks of 32.  The block
+// count is padded to a multiple of 4 (nbp) and the row count to a multiple of 16
+// (padding holds zero codes / zero scales, which contribute exactly 0).
+//
+// One 512-byte CHUNK is what a warp loads with one 16-byte load per lane; lane
+// L = 4*g + t (g = L>>2, t = L&3) holds the A fragment of mma.m16n8k32 for
+// rows {g, g+8} of the tile and the real columns [8t, 8t+8) of a block:
+//   q8   : chunk (rt, b)      = [row g: cols 8t..8t+3][row g+8: same][row g: cols 8t+4..8t+7][row g+8: same]
+//   mxfp4: chunk (rt, bp)     = [row g, block 2bp: 8 codes of cols 8t..8t+7][row g+8, block 2bp]
+//                               [row g, block 2bp+1][row g+8, block 2bp+1]   (natural nibble order in each word)
+// Scales are tiled as [rt][block][16 rows] so a warp's scales are contiguous.
+struct mk_weight {
+    int fmt;            // MK_FMT_*
+    int scale_type;     // MK_SCALE_* (q8 only)
+    int64_t rows, cols;
+    int64_t nrt;        // row tiles = ceil(rows/16)
+    int64_t nb;         // blocks per row = cols/32
+    int64_t nbp;        // padded to a multiple of 4
+    void *values;       // tiled values
+    void *scales;       // tiled scales (u8 for mxfp4, f32/f16 for q8)
+    size_t values_bytes, scales_bytes;
+};
+
+struct mk_ctx {
+    int device;
+    int sm_count;
+    int cc_major, cc_minor;
+    size_t mem_bytes;
+    cudaStream_t own_stream;
+    cudaStream_t stream;
+    int64_t launches;
+    int32_t *status_dev;    // device status word
+    // activation workspace (grown on demand, never per call once warm)
+    void *ws;
+    size_t ws_bytes;
+    // host-call staging
+    void *io_dev;
+    size_t io_bytes;
+    void *io_pinned;
+    size_t io_pinned_bytes;
+    int force_ks;           // 0 = choose per shape
+    // optional per-category event timing (mk_prof_*)
+    int prof_on;
+    struct mk_prof_pair *prof_pairs; // pool of event pairs
+    int prof_cap, prof_used;
+    int64_t prof_count[MK_PROF_NCAT];
+    double prof_ms[MK_PROF_NCAT];
+};
+struct mk_prof_pair { cudaEvent_t a, b; int cat; };
+// Brackets one kernel launch with an event pair when profiling is on.
+struct mk_prof_scope {
+    mk_ctx *ctx;
+    mk_prof_pair *p;
+    mk_prof_scope(mk_ctx *c, int cat);
+    ~mk_prof_scope();
+};
+int32_t mk_prof_drain(mk_ctx *ctx); // folds finished pairs into the accumulators (synchronizes)
+
+int32_t mk_ws_reserve(mk_ctx *ctx, size_t bytes);      // activation workspace
+int32_t mk_io_reserve(mk_ctx *ctx, size_t bytes);      // device staging for host-pointer calls
+int32_t mk_pinned_reserve(mk_ctx *ctx, size_t bytes);  // pinned host staging
+
+static inline int64_t mk_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline size_t mk_align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
+
+// ---------------------------------------------------------------- kernel launchers (defined in the .cu files)
+// activation quantization: x f32 [ntok, cols] -> xq i8 [limbs][ntok][ldq], xs f32 [ntok][nbp]
+int32_t mk_launch_quantize_act(mk_ctx *ctx, const float *x, int ntok, int64_t cols, int64_t ldx, int64_t nbp,
+                               int x2, int8_t *xq, float *xs);
+// the fused dequant + GEMV
+int32_t mk_launch_qgemv(mk_ctx *ctx, const mk_weight *w, const int8_t *xq, const float *xs, int ntok,
+                        int x2, int strict, float *y, int64_t ldy);
+int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, int batch, int32_t *out, void *scratch);
+size_t mk_argmax_scratch_bytes(int batch);
+// weight (re)tiling
+int32_t mk_launch_retile_mxfp4(mk_ctx *ctx, const uint8_t *packed, const uint8_t *scales, mk_weight *w);
+int32_t mk_launch_untile_mxfp4(mk_ctx *ctx, const mk_weight *w, uint8_t *packed, uint8_t *scales);
+int32_t mk_launch_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out);
+int32_t mk_launch_quantize_weight_q8(mk_ctx *ctx, const float *wf32, int64_t row0, int64_t nrows, mk_weight *w);
+int32_t mk_launch_retile_q8(mk_ctx *ctx, const int8_t *q, const void *scales, mk_weight *w);
+int32_t mk_launch_untile_q8(mk_ctx *ctx, const mk_weight *w, int8_t *q, void *scales);
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------- device helpers
+// 2^(sb-127) from a ue8m0 byte as an exact bit pattern; sb == 0 is the subnormal 2^-127.
+__device__ __forceinline__ float mk_e8m0(uint32_t sb) {
+    return __uint_as_float(sb == 0 ? 0x00400000u : (sb << 23));
+}
+// 2^(sb-128): the scale of the integer LUT (E2M1 x 2) convention.
+__device__ __forceinline__ float mk_e8m0_half(uint32_t sb) {
+    return __uint_as_float(sb >= 2 ? ((sb - 1) << 23) : (0x00200000u << sb));
+}
+// prmt.b32 in its generic form: selector nibble n picks byte (n & 7) of {b,a};
+// a selector nibble with bit 3 set yields 0x00/0xFF from that byte's sign bit.
+__device__ __forceinline__ uint32_t mk_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// D += A(16x32, s8, row) * B(32x8, s8, col), int32 accumulate.
+__device__ __forceinline__ void mk_mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16-byte streaming load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 mk_ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+// E2M1 x 2 magnitudes as two prmt pool registers: bytes {0,1,2,3} and {4,6,8,12}.
+#define MK_LUT2_LO 0x03020100u
+#define MK_LUT2_HI 0x0C080604u
+#endif

@@ -1,0 +1,506 @@
+// Dequant-fused quantized matrix x vector for MXFP4 and q8_0 weights (sm_100a).
+//
+// What it computes, per output row r and token:
+//   MXFP4 : sum_g  idot(r,g) * (2^(sb[r,g]-128) * xs[g])      (src/mxfp4.rs:409-418)
+//   q8_0  : sum_g (ws[r,g] * xs[g]) * idot(r,g)                (src/model.rs:337-347)
+// where idot is the EXACT int32 dot of one 32-wide block of the weight row with
+// the q8_0-quantized activation (src/q8.rs:119-125, 194-202).
+//
+// How: the weights sit in HBM in mma.m16n8k32 fragment order (see mk_weight), so
+// one warp streams a 16-row tile with one coalesced 16-byte load per lane.  The
+// block dot runs on the tensor cores as int8 x int8 -> int32 (exact).  E2M1
+// codes are decoded in registers with byte permutes: a code's 3 magnitude bits
+// select one of the 8 bytes {0,1,2,3,4,6,8,12} (= E2M1 x 2); a set sign bit makes
+// the permute return 0, so one pass yields the positive part and a second pass
+// over the sign-flipped word yields the negative part; idot = dot(pos) - dot(neg).
+//
+// Two schedules:
+//   "spread"  (<= 2 activation columns): the MMA's 8 output columns are used for
+//             4 consecutive weight blocks x 2 columns, so the per-block scaling
+//             runs once per 4 blocks with all lanes busy.
+//   "batched" (<= 8 tokens): the 8 columns are 8 tokens; each lane owns 4 outputs
+//             and adds the block terms in ascending block order with separate
+//             multiply and add.  With no K split that reproduces the CPU sums
+//             bit for bit (MK_ACT_STRICT).
+#include <cuda_fp16.h>
+
+#include "mk_common.cuh"
+
+namespace {
+
+enum { W_MXFP4 = 0, W_Q8_F32 = 1, W_Q8_F16 = 2 };
+
+template <int WF> struct Group;
+template <> struct Group<W_MXFP4> { uint4 a[2]; };  // 4 blocks = 2 chunks
+template <> struct Group<W_Q8_F32> { uint4 a[4]; }; // 4 blocks = 4 chunks
+template <> struct Group<W_Q8_F16> { uint4 a[4]; };
+
+template <int WF> __device__ __forceinline__ constexpr int chunks_per_group() { return WF == W_MXFP4 ? 2 : 4; }
+
+template <int WF>
+__device__ __forceinline__ void load_group(Group<WF> &g, const uint4 *tile_base, int64_t group, int lane) {
+    constexpr int C = chunks_per_group<WF>();
+    const uint4 *p = tile_base + (group * C) * 32 + lane;
+#pragma unroll
+    for (int c = 0; c < C; ++c) g.a[c] = mk_ldg_stream(p + c * 32);
+}
+
+// int32 block dots of block m (0..3) of a group: accumulates into c (pos) / cn (neg)
+template <int WF>
+__device__ __forceinline__ void block_mma(const Group<WF> &g, int m, uint32_t b0, uint32_t b1, int (&cp)[4], int (&cn)[4]) {
+    if constexpr (WF == W_MXFP4) {
+        const uint4 &ch = g.a[m >> 1];
+        uint32_t wg = (m & 1) ? ch.z : ch.x; // row g
+        uint32_t wh = (m & 1) ? ch.w : ch.y; // row g+8
+        uint32_t wgx = wg ^ 0x88888888u, whx = wh ^ 0x88888888u;
+        mk_mma_s8(cp, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh),
+                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh >> 16), b0, b1);
+        mk_mma_s8(cn, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx),
+                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx >> 16), b0, b1);
+    } else {
+        const uint4 &ch = g.a[m];
+        mk_mma_s8(cp, ch.x, ch.y, ch.z, ch.w, b0, b1);
+    }
+}
+
+// weight scales of block b for rows g and g+8 of row tile rt
+template <int WF>
+__device__ __forceinline__ void load_wscale(const void *wscale, int64_t rt, int64_t nbp, int64_t b, int g, float &sg, float &sh) {
+    int64_t base = (rt * nbp + b) * 16;
+    if constexpr (WF == W_MXFP4) {
+        const uint8_t *s = (const uint8_t *)wscale + base;
+        sg = mk_e8m0_half(__ldg(s + g));
+        sh = mk_e8m0_half(__ldg(s + g + 8));
+    } else if constexpr (WF == W_Q8_F32) {
+        const float *s = (const float *)wscale + base;
+        sg = __ldg(s + g);
+        sh = __ldg(s + g + 8);
+    } else {
+        const __half *s = (const __half *)wscale + base;
+        sg = __half2float(__ldg(s + g));
+        sh = __half2float(__ldg(s + g + 8));
+    }
+}
+
+// acc += idot * (sw * sx) with separate multiply and add, in the reference's order.
+__device__ __forceinline__ float acc_term(float acc, int idot, float sw, float sx) {
+    return __fadd_rn(acc, __fmul_rn(__fmul_rn(sw, sx), (float)idot));
+}
+
+// ------------------------------------------------------------------ "spread" schedule
+// NSLOT activation columns (1 or 2).  X2: the two columns are the high and low
+// limb of ONE token (idot = 128*hi + lo).
+template <int WF, int KS, int NSLOT, bool X2>
+__global__ void __launch_bounds__(256)
+qgemv_spread_kernel(const uint4 *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
+                    const float *__restrict__ xs, int64_t ldq, int64_t nbp, float *__restrict__ y, int64_t ldy,
+                    int64_t rows, int64_t nrt) {
+    constexpr int RT = 8 / KS;
+    constexpr int C = chunks_per_group<WF>();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_local = warp / KS, ks = warp % KS;
+    const int64_t rt = (int64_t)blockIdx.x * RT + rt_local;
+    const int64_t ngroups = nbp >> 2;
+    constexpr int NOUT = X2 ? 1 : NSLOT;
+    float acc[2][NOUT];
+#pragma unroll
+    for (int o = 0; o < NOUT; ++o) acc[0][o] = acc[1][o] = 0.0f;
+
+    if (rt < nrt) {
+        const uint4 *tile = wt + rt * (ngroups * C) * 32;
+        // lane (g,t) feeds MMA column g: slot g&1 of block (g>>1) of the group
+        const int slot = g & 1, sub = g >> 1;
+        const bool xvalid = slot < NSLOT;
+        const int8_t *xp = xq + (int64_t)slot * ldq + sub * 32 + t * 8;
+        uint32_t mask[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) mask[m] = (sub == m && xvalid) ? 0xFFFFFFFFu : 0u;
+
+        Group<WF> cur, nxt;
+        int64_t i = ks;
+        if (i < ngroups) load_group<WF>(cur, tile, i, lane);
+        for (; i < ngroups; i += KS) {
+            const int64_t inext = i + KS;
+            if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
+            uint2 xv = make_uint2(0u, 0u);
+            if (xvalid) xv = __ldg((const uint2 *)(xp + i * 128));
+            int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int m = 0; m < 4; ++m) block_mma<WF>(cur, m, xv.x & mask[m], xv.y & mask[m], cp, cn);
+            // lane t now holds block 4i+t: c0/c1 = row g (slot 0/1), c2/c3 = row g+8
+            const int64_t b = i * 4 + t;
+            float sg, sh;
+            load_wscale<WF>(wscale, rt, nbp, b, g, sg, sh);
+            int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
+            if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
+            if constexpr (X2) {
+                const float sx = __ldg(xs + b);
+                acc[0][0] = acc_term(acc[0][0], d0 * 128 + d1, sg, sx);
+                acc[1][0] = acc_term(acc[1][0], d2 * 128 + d3, sh, sx);
+            } else {
+                const float sx0 = __ldg(xs + b);
+                acc[0][0] = acc_term(acc[0][0], d0, sg, sx0);
+                acc[1][0] = acc_term(acc[1][0], d2, sh, sx0);
+                if constexpr (NSLOT == 2) {
+                    const float sx1 = __ldg(xs + nbp + b);
+                    acc[0][1] = acc_term(acc[0][1], d1, sg, sx1);
+                    acc[1][1] = acc_term(acc[1][1], d3, sh, sx1);
+                }
+            }
+            cur = nxt;
+        }
+    }
+    // sum the 4 lanes of a row group (they hold blocks = t mod 4)
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o) {
+            float v = acc[h][o];
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+            acc[h][o] = v;
+        }
+    if constexpr (KS > 1) {
+        __shared__ float red[8][16][NOUT];
+        if (t == 0) {
+#pragma unroll
+            for (int o = 0; o < NOUT; ++o) {
+                red[warp][g][o] = acc[0][o];
+                red[warp][g + 8][o] = acc[1][o];
+            }
+        }
+        __syncthreads();
+        if (ks == 0 && t == 0 && rt < nrt) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r16 = g + 8 * h;
+                const int64_t row = rt * 16 + r16;
+                if (row < rows) {
+#pragma unroll
+                    for (int o = 0; o < NOUT; ++o) {
+                        float v = red[warp][r16][o];
+                        for (int k = 1; k < KS; ++k) v += red[warp + k][r16][o];
+                        y[(int64_t)o * ldy + row] = v;
+                    }
+                }
+            }
+        }
+    } else {
+        if (t == 0 && rt < nrt) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int64_t row = rt * 16 + g + 8 * h;
+                if (row < rows) {
+#pragma unroll
+                    for (int o = 0; o < NOUT; ++o) y[(int64_t)o * ldy + row] = acc[h][o];
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ "batched" schedule
+// MMA columns = tokens (X2: column 2k / 2k+1 = high / low limb of token k).
+template <int WF, int KS, bool X2>
+__global__ void __launch_bounds__(256)
+qgemv_batched_kernel(const uint4 *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
+                     const float *__restrict__ xs, int64_t ldq, int64_t nbp, int ntok, float *__restrict__ y,
+                     int64_t ldy, int64_t rows, int64_t nrt) {
+    constexpr int RT = 8 / KS;
+    constexpr int C = chunks_per_group<WF>();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_local = warp / KS, ks = warp % KS;
+    const int64_t rt = (int64_t)blockIdx.x * RT + rt_local;
+    const int64_t ngroups = nbp >> 2;
+    // outputs owned by this lane: !X2: (row g|g+8) x (token 2t | 2t+1); X2: (row g|g+8) x token t
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int tok_a = X2 ? t : 2 * t, tok_b = X2 ? t : 2 * t + 1;
+
+    if (rt < nrt) {
+        const uint4 *tile = wt + rt * (ngroups * C) * 32;
+        // column g of the B fragment
+        const int ctok = X2 ? (g >> 1) : g;
+        const bool xvalid = ctok < ntok;
+        const int8_t *xp = xq + (X2 ? (int64_t)(g & 1) * ntok * ldq : 0) + (int64_t)ctok * ldq + t * 8;
+        const float *xsa = xs + (int64_t)tok_a * nbp;
+        const float *xsb = xs + (int64_t)tok_b * nbp;
+        const bool va = tok_a < ntok, vb = tok_b < ntok;
+
+        Group<WF> cur, nxt;
+        int64_t i = ks;
+        if (i < ngroups) load_group<WF>(cur, tile, i, lane);
+        for (; i < ngroups; i += KS) {
+            const int64_t inext = i + KS;
+            if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int64_t b = i * 4 + m;
+                uint2 xv = make_uint2(0u, 0u);
+                if (xvalid) xv = __ldg((const uint2 *)(xp + b * 32));
+                int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+                block_mma<WF>(cur, m, xv.x, xv.y, cp, cn);
+                float sg, sh;
+                load_wscale<WF>(wscale, rt, nbp, b, g, sg, sh);
+                int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
+                if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
+                if constexpr (X2) {
+                    const float sx = va ? __ldg(xsa + b) : 0.0f;
+                    acc[0] = acc_term(acc[0], d0 * 128 + d1, sg, sx);
+                    acc[2] = acc_term(acc[2], d2 * 128 + d3, sh, sx);
+                } else {
+                    const float sxa = va ? __ldg(xsa + b) : 0.0f;
+                    const float sxb = vb ? __ldg(xsb + b) : 0.0f;
+                    acc[0] = acc_term(acc[0], d0, sg, sxa);
+                    acc[1] = acc_term(acc[1], d1, sg, sxb);
+                    acc[2] = acc_term(acc[2], d2, sh, sxa);
+                    acc[3] = acc_term(acc[3], d3, sh, sxb);
+                }
+            }
+            cur = nxt;
+        }
+    }
+    if constexpr (KS > 1) {
+        __shared__ float red[8][32][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) red[warp][lane][j] = acc[j];
+        __syncthreads();
+        if (ks == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v = red[warp][lane][j];
+                for (int k = 1; k < KS; ++k) v += red[warp + k][lane][j];
+                acc[j] = v;
+            }
+        }
+    }
+    if (ks == 0 && rt < nrt) {
+        const int64_t row_g = rt * 16 + g, row_h = row_g + 8;
+        if constexpr (X2) {
+            if (tok_a < ntok) {
+                if (row_g < rows) y[(int64_t)tok_a * ldy + row_g] = acc[0];
+                if (row_h < rows) y[(int64_t)tok_a * ldy + row_h] = acc[2];
+            }
+        } else {
+            if (tok_a < ntok) {
+                if (row_g < rows) y[(int64_t)tok_a * ldy + row_g] = acc[0];
+                if (row_h < rows) y[(int64_t)tok_a * ldy + row_h] = acc[2];
+            }
+            if (tok_b < ntok) {
+                if (row_g < rows) y[(int64_t)tok_b * ldy + row_g] = acc[1];
+                if (row_h < rows) y[(int64_t)tok_b * ldy + row_h] = acc[3];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ activation quantization
+// One warp per (token, block): q8::quantize_q8_into (src/q8.rs:49-69), bit-exact:
+// dx = max|x| / 127 (IEEE divide), q = clamp(round-half-away(x / dx), -127, 127).
+// X2: d = max|x| / 16256, q16 = round(x / d); hi = round(q16 / 128), lo = q16 - 128 hi.
+template <bool X2>
+__global__ void __launch_bounds__(256)
+quantize_act_kernel(const float *__restrict__ x, int ntok, int64_t cols, int64_t ldx, int64_t nbp,
+                    int8_t *__restrict__ xq, float *__restrict__ xs) {
+    const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (int64_t)ntok * nbp) return;
+    const int64_t tok = w / nbp, b = w % nbp;
+    const int64_t c = b * 32 + lane;
+    const float v = (c < cols) ? x[tok * ldx + c] : 0.0f;
+    float mx = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    const int64_t ldq = nbp * 32;
+    if constexpr (!X2) {
+        const float dx = __fdiv_rn(mx, 127.0f);
+        int q = 0;
+        if (dx != 0.0f) q = (int)fminf(fmaxf(roundf(__fdiv_rn(v, dx)), -127.0f), 127.0f);
+        uint32_t qb = (uint32_t)q & 0xFFu;
+        uint32_t pk = qb | (__shfl_down_sync(0xFFFFFFFFu, qb, 1) << 8) | (__shfl_down_sync(0xFFFFFFFFu, qb, 2) << 16) |
+                      (__shfl_down_sync(0xFFFFFFFFu, qb, 3) << 24);
+        if ((lane & 3) == 0) ((uint32_t *)(xq + tok * ldq + b * 32))[lane >> 2] = pk;
+        if (lane == 0) xs[tok * nbp + b] = dx;
+    } else {
+        const float d = __fdiv_rn(mx, 16256.0f);
+        int q16 = 0;
+        if (d != 0.0f) q16 = (int)fminf(fmaxf(roundf(__fdiv_rn(v, d)), -16256.0f), 16256.0f);
+        int hi = (q16 + (q16 >= 0 ? 64 : -64)) / 128;
+        int lo = q16 - 128 * hi;
+        uint32_t hb = (uint32_t)hi & 0xFFu, lb = (uint32_t)lo & 0xFFu;
+        uint32_t ph = hb | (__shfl_down_sync(0xFFFFFFFFu, hb, 1) << 8) | (__shfl_down_sync(0xFFFFFFFFu, hb, 2) << 16) |
+                      (__shfl_down_sync(0xFFFFFFFFu, hb, 3) << 24);
+        uint32_t pl = lb | (__shfl_down_sync(0xFFFFFFFFu, lb, 1) << 8) | (__shfl_down_sync(0xFFFFFFFFu, lb, 2) << 16) |
+                      (__shfl_down_sync(0xFFFFFFFFu, lb, 3) << 24);
+        if ((lane & 3) == 0) {
+            ((uint32_t *)(xq + tok * ldq + b * 32))[lane >> 2] = ph;
+            ((uint32_t *)(xq + ((int64_t)ntok + tok) * ldq + b * 32))[lane >> 2] = pl;
+        }
+        if (lane == 0) xs[tok * nbp + b] = d;
+    }
+}
+
+// ------------------------------------------------------------------ argmax (first index of the maximum)
+struct ArgPair { float v; int32_t i; };
+__device__ __forceinline__ ArgPair arg_better(ArgPair a, ArgPair b) {
+    // strict '>' keeps the earlier index on ties (src/model.rs:3277-3290); i < 0 marks "empty"
+    if (b.i < 0) return a;
+    if (a.i < 0) return b;
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+__device__ __forceinline__ ArgPair arg_block_reduce(ArgPair p) {
+    __shared__ float sv[32];
+    __shared__ int32_t si[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgPair q;
+        q.v = __shfl_xor_sync(0xFFFFFFFFu, p.v, o);
+        q.i = __shfl_xor_sync(0xFFFFFFFFu, p.i, o);
+        p = arg_better(p, q);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[warp] = p.v; si[warp] = p.i; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        p.v = lane < nw ? sv[lane] : 0.0f;
+        p.i = lane < nw ? si[lane] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgPair q;
+            q.v = __shfl_xor_sync(0xFFFFFFFFu, p.v, o);
+            q.i = __shfl_xor_sync(0xFFFFFFFFu, p.i, o);
+            p = arg_better(p, q);
+        }
+    }
+    return p;
+}
+#define ARGMAX_PARTS 128
+__global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restrict__ y, int64_t n, int64_t ldy,
+                                                         float *__restrict__ pv, int32_t *__restrict__ pi) {
+    const int row = blockIdx.y;
+    const float *yr = y + (int64_t)row * ldy;
+    ArgPair p = {0.0f, -1};
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        ArgPair q = {yr[i], (int32_t)i};
+        p = arg_better(p, q);
+    }
+    p = arg_block_reduce(p);
+    if (threadIdx.x == 0) {
+        pv[row * ARGMAX_PARTS + blockIdx.x] = p.v;
+        pi[row * ARGMAX_PARTS + blockIdx.x] = p.i;
+    }
+}
+__global__ void __launch_bounds__(128) argmax_final_kernel(const float *__restrict__ pv, const int32_t *__restrict__ pi,
+                                                          int32_t *__restrict__ out) {
+    const int row = blockIdx.x;
+    ArgPair p = {pv[row * ARGMAX_PARTS + threadIdx.x], pi[row * ARGMAX_PARTS + threadIdx.x]};
+    p = arg_block_reduce(p);
+    if (threadIdx.x == 0) out[row] = p.i;
+}
+
+// ------------------------------------------------------------------ dispatch
+template <int WF, int KS>
+void launch_spread(const mk_weight *w, cudaStream_t st, const int8_t *xq, const float *xs, int nslot, bool x2, float *y,
+                   int64_t ldy) {
+    constexpr int RT = 8 / KS;
+    const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
+    const int64_t ldq = w->nbp * 32;
+    const uint4 *wt = (const uint4 *)w->values;
+    if (x2)
+        qgemv_spread_kernel<WF, KS, 2, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
+    else if (nslot == 2)
+        qgemv_spread_kernel<WF, KS, 2, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
+    else
+        qgemv_spread_kernel<WF, KS, 1, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
+}
+template <int WF, int KS>
+void launch_batched(const mk_weight *w, cudaStream_t st, const int8_t *xq, const float *xs, int ntok, bool x2, float *y,
+                    int64_t ldy) {
+    constexpr int RT = 8 / KS;
+    const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
+    const int64_t ldq = w->nbp * 32;
+    const uint4 *wt = (const uint4 *)w->values;
+    if (x2)
+        qgemv_batched_kernel<WF, KS, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt);
+    else
+        qgemv_batched_kernel<WF, KS, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt);
+}
+template <int WF>
+void launch_wf(const mk_weight *w, cudaStream_t st, int ks, bool spread, const int8_t *xq, const float *xs, int ntok,
+               bool x2, float *y, int64_t ldy) {
+#define MK_KS_CASE(K)                                                         \
+    case K:                                                                   \
+        if (spread) launch_spread<WF, K>(w, st, xq, xs, ntok, x2, y, ldy);    \
+        else launch_batched<WF, K>(w, st, xq, xs, ntok, x2, y, ldy);          \
+        break;
+    switch (ks) {
+        MK_KS_CASE(1)
+        MK_KS_CASE(2)
+        MK_KS_CASE(4)
+        MK_KS_CASE(8)
+    }
+#undef MK_KS_CASE
+}
+
+} // namespace
+
+// K split: enough CTAs to fill the GPU several times over, but at least a few
+// block groups per warp.
+static int pick_ks(const mk_ctx *ctx, const mk_weight *w, bool strict) {
+    if (strict) return 1;
+    if (ctx->force_ks) return ctx->force_ks;
+    const int64_t ngroups = w->nbp / 4;
+    int ks = 1;
+    while (ks < 8) {
+        const int64_t ctas = mk_ceil_div(w->nrt, 8 / ks);
+        const int64_t groups_per_warp = ngroups / (ks * 2);
+        if (ctas >= (int64_t)ctx->sm_count * 16 || groups_per_warp < 3) break;
+        ks *= 2;
+    }
+    return ks;
+}
+
+int32_t mk_launch_quantize_act(mk_ctx *ctx, const float *x, int ntok, int64_t cols, int64_t ldx, int64_t nbp, int x2,
+                               int8_t *xq, float *xs) {
+    const int64_t warps = (int64_t)ntok * nbp;
+    const unsigned grid = (unsigned)mk_ceil_div(warps * 32, 256);
+    if (x2)
+        quantize_act_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, ntok, cols, ldx, nbp, xq, xs);
+    else
+        quantize_act_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, ntok, cols, ldx, nbp, xq, xs);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+int32_t mk_launch_qgemv(mk_ctx *ctx, const mk_weight *w, const int8_t *xq, const float *xs, int ntok, int x2, int strict,
+                        float *y, int64_t ldy) {
+    MK_CHECK_ARG(ntok >= 1 && ntok <= (x2 ? 4 : 8), "token count out of range for one pass");
+    const bool spread = !strict && (x2 ? ntok == 1 : ntok <= 2);
+    const int ks = pick_ks(ctx, w, strict != 0);
+    const int wf = w->fmt == MK_FMT_MXFP4 ? W_MXFP4 : (w->scale_type == MK_SCALE_F16 ? W_Q8_F16 : W_Q8_F32);
+    mk_prof_scope prof(ctx, w->fmt == MK_FMT_MXFP4 ? MK_PROF_MATVEC_MXFP4 : MK_PROF_LM_HEAD);
+    switch (wf) {
+    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    default: launch_wf<W_Q8_F16>(w, ctx->stream, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    }
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+size_t mk_argmax_scratch_bytes(int batch) { return (size_t)batch * ARGMAX_PARTS * (sizeof(float) + sizeof(int32_t)); }
+
+int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, int batch, int32_t *out, void *scratch) {
+    float *pv = (float *)scratch;
+    int32_t *pi = (int32_t *)(pv + (size_t)batch * ARGMAX_PARTS);
+    argmax_part_kernel<<<dim3(ARGMAX_PARTS, batch), 256, 0, ctx->stream>>>(y, n, ldy, pv, pi);
+    argmax_final_kernel<<<batch, ARGMAX_PARTS, 0, ctx->stream>>>(pv, pi, out);
+    ctx->launches += 2;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}

@@ -1,0 +1,213 @@
+// Weight registration kernels: natural row-major blobs <-> the fragment-major
+// device layout described at mk_weight (mk_common.cuh), the bit-exact q8_0 row
+// quantizer (Q8Head::from_f32, src/model.rs:274-286) and the MXFP4 dequantizer
+// (mxfp4::dequant, src/mxfp4.rs:19-31).  All of them only move or re-encode
+// bytes; values are unchanged and mk_weight_export() undoes the tiling.
+#include <cuda_fp16.h>
+
+#include "mk_common.cuh"
+
+namespace {
+
+__constant__ float c_e2m1[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+                                 -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+
+// ---- MXFP4: one thread per tiled 32-bit word (8 codes)
+__global__ void retile_mxfp4_kernel(const uint8_t *__restrict__ packed, const uint8_t *__restrict__ scales,
+                                    uint32_t *__restrict__ tv, uint8_t *__restrict__ ts, int64_t rows, int64_t cols,
+                                    int64_t nrt, int64_t nb, int64_t nbp) {
+    const int64_t nwords = nrt * (nbp / 2) * 128;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < nwords) {
+        const int64_t chunk = idx >> 7;
+        const int within = (int)(idx & 127);
+        const int lane = within >> 2, j = within & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const int64_t rt = chunk / (nbp / 2), bp = chunk % (nbp / 2);
+        const int64_t row = rt * 16 + g + ((j & 1) ? 8 : 0);
+        const int64_t b = bp * 2 + (j >> 1);
+        uint32_t v = 0;
+        if (row < rows && b < nb) v = *(const uint32_t *)(packed + row * (cols / 2) + b * 16 + t * 4);
+        tv[idx] = v;
+    }
+    const int64_t nsc = nrt * nbp * 16;
+    if (idx < nsc) {
+        const int r16 = (int)(idx & 15);
+        const int64_t rb = idx >> 4;
+        const int64_t rt = rb / nbp, b = rb % nbp;
+        const int64_t row = rt * 16 + r16;
+        ts[idx] = (row < rows && b < nb) ? scales[row * nb + b] : (uint8_t)0;
+    }
+}
+__global__ void untile_mxfp4_kernel(const uint32_t *__restrict__ tv, const uint8_t *__restrict__ ts,
+                                    uint8_t *__restrict__ packed, uint8_t *__restrict__ scales, int64_t rows,
+                                    int64_t cols, int64_t nrt, int64_t nb, int64_t nbp) {
+    const int64_t nwords = nrt * (nbp / 2) * 128;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < nwords) {
+        const int64_t chunk = idx >> 7;
+        const int within = (int)(idx & 127);
+        const int lane = within >> 2, j = within & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const int64_t rt = chunk / (nbp / 2), bp = chunk % (nbp / 2);
+        const int64_t row = rt * 16 + g + ((j & 1) ? 8 : 0);
+        const int64_t b = bp * 2 + (j >> 1);
+        if (row < rows && b < nb) *(uint32_t *)(packed + row * (cols / 2) + b * 16 + t * 4) = tv[idx];
+    }
+    const int64_t nsc = nrt * nbp * 16;
+    if (idx < nsc) {
+        const int r16 = (int)(idx & 15);
+        const int64_t rb = idx >> 4;
+        const int64_t rt = rb / nbp, b = rb % nbp;
+        const int64_t row = rt * 16 + r16;
+        if (row < rows && b < nb) scales[row * nb + b] = ts[idx];
+    }
+}
+// one thread per element: W[r,c] = E2M1[code] * 2^(sb-127), bit-exact (-0.0 and subnormals included)
+__global__ void dequant_mxfp4_kernel(const uint32_t *__restrict__ tv, const uint8_t *__restrict__ ts,
+                                     float *__restrict__ out, int64_t rows, int64_t cols, int64_t nbp) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * cols) return;
+    const int64_t row = idx / cols, col = idx % cols;
+    const int64_t rt = row >> 4;
+    const int r16 = (int)(row & 15), g = r16 & 7, hi = r16 >> 3;
+    const int64_t b = col >> 5;
+    const int jc = (int)(col & 31), t = jc >> 3, jj = jc & 7;
+    const int64_t chunk = rt * (nbp / 2) + (b >> 1);
+    const uint32_t w = tv[chunk * 128 + (g * 4 + t) * 4 + (int)(b & 1) * 2 + hi];
+    const uint32_t code = (w >> (4 * jj)) & 15u;
+    const uint32_t sb = ts[(rt * nbp + b) * 16 + r16];
+    out[idx] = c_e2m1[code] * mk_e8m0(sb);
+}
+
+// ---- q8_0
+// byte offset of element (r16, column j of the block) inside its 512-byte chunk
+__device__ __forceinline__ int q8_chunk_off(int r16, int j) {
+    const int g = r16 & 7, hi = r16 >> 3, t = j >> 3, jj = j & 7;
+    return (g * 4 + t) * 16 + ((jj >> 2) * 2 + hi) * 4 + (jj & 3);
+}
+template <typename ST> __device__ __forceinline__ ST to_scale(float v);
+template <> __device__ __forceinline__ float to_scale<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half to_scale<__half>(float v) { return __float2half_rn(v); }
+__device__ __forceinline__ float from_scale(float v) { return v; }
+__device__ __forceinline__ float from_scale(__half v) { return __half2float(v); }
+
+// One warp per (row, block) of the f32 source: q8::quantize_q8_into per row
+// (src/q8.rs:49-69).  With half scales the scale is rounded to half FIRST and the
+// values are quantized against the rounded scale.
+template <typename ST>
+__global__ void __launch_bounds__(256)
+quantize_weight_q8_kernel(const float *__restrict__ w, int64_t row0, int64_t nrows, int64_t cols, int64_t nb,
+                          int64_t nbp, int8_t *__restrict__ tv, ST *__restrict__ ts) {
+    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= nrows * nb) return;
+    const int64_t rl = wid / nb, b = wid % nb;
+    const int64_t row = row0 + rl;
+    const float v = w[rl * cols + b * 32 + lane];
+    float mx = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    const ST st = to_scale<ST>(__fdiv_rn(mx, 127.0f));
+    const float dx = from_scale(st);
+    int q = 0;
+    if (dx != 0.0f) q = (int)fminf(fmaxf(roundf(__fdiv_rn(v, dx)), -127.0f), 127.0f);
+    const uint32_t qb = (uint32_t)q & 0xFFu;
+    const uint32_t pk = qb | (__shfl_down_sync(0xFFFFFFFFu, qb, 1) << 8) | (__shfl_down_sync(0xFFFFFFFFu, qb, 2) << 16) |
+                        (__shfl_down_sync(0xFFFFFFFFu, qb, 3) << 24);
+    const int64_t rt = row >> 4;
+    const int r16 = (int)(row & 15);
+    if ((lane & 3) == 0) *(uint32_t *)(tv + (rt * nbp + b) * 512 + q8_chunk_off(r16, lane)) = pk;
+    if (lane == 0) ts[(rt * nbp + b) * 16 + r16] = st;
+}
+// natural q8 rows -> tiled; one thread per 4 bytes
+template <typename ST>
+__global__ void retile_q8_kernel(const int8_t *__restrict__ q, const ST *__restrict__ s, int8_t *__restrict__ tv,
+                                 ST *__restrict__ ts, int64_t rows, int64_t cols, int64_t nb, int64_t nbp, bool inverse,
+                                 int8_t *__restrict__ q_out, ST *__restrict__ s_out) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nquads = rows * (cols / 4);
+    if (idx < nquads) {
+        const int64_t row = idx / (cols / 4);
+        const int64_t c4 = (idx % (cols / 4)) * 4;
+        const int64_t b = c4 >> 5;
+        const int j = (int)(c4 & 31);
+        const int64_t off = ((row >> 4) * nbp + b) * 512 + q8_chunk_off((int)(row & 15), j);
+        if (!inverse) *(uint32_t *)(tv + off) = *(const uint32_t *)(q + row * cols + c4);
+        else *(uint32_t *)(q_out + row * cols + c4) = *(const uint32_t *)(tv + off);
+    }
+    if (idx < rows * nb) {
+        const int64_t row = idx / nb, b = idx % nb;
+        const int64_t off = ((row >> 4) * nbp + b) * 16 + (row & 15);
+        if (!inverse) ts[off] = s[idx];
+        else s_out[idx] = ts[off];
+    }
+}
+
+} // namespace
+
+static unsigned grid_for(int64_t n, int block) { return (unsigned)mk_ceil_div(n > 0 ? n : 1, block); }
+
+int32_t mk_launch_retile_mxfp4(mk_ctx *ctx, const uint8_t *packed, const uint8_t *scales, mk_weight *w) {
+    const int64_t n = w->nrt * (w->nbp / 2) * 128; // >= nrt*nbp*16
+    retile_mxfp4_kernel<<<grid_for(n, 256), 256, 0, ctx->stream>>>(packed, scales, (uint32_t *)w->values,
+                                                                  (uint8_t *)w->scales, w->rows, w->cols, w->nrt, w->nb, w->nbp);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+int32_t mk_launch_untile_mxfp4(mk_ctx *ctx, const mk_weight *w, uint8_t *packed, uint8_t *scales) {
+    const int64_t n = w->nrt * (w->nbp / 2) * 128;
+    untile_mxfp4_kernel<<<grid_for(n, 256), 256, 0, ctx->stream>>>((const uint32_t *)w->values, (const uint8_t *)w->scales,
+                                                                  packed, scales, w->rows, w->cols, w->nrt, w->nb, w->nbp);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+int32_t mk_launch_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out) {
+    dequant_mxfp4_kernel<<<grid_for(w->rows * w->cols, 256), 256, 0, ctx->stream>>>(
+        (const uint32_t *)w->values, (const uint8_t *)w->scales, out, w->rows, w->cols, w->nbp);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+int32_t mk_launch_quantize_weight_q8(mk_ctx *ctx, const float *wf32, int64_t row0, int64_t nrows, mk_weight *w) {
+    const int64_t warps = nrows * w->nb;
+    if (w->scale_type == MK_SCALE_F16)
+        quantize_weight_q8_kernel<__half><<<grid_for(warps * 32, 256), 256, 0, ctx->stream>>>(
+            wf32, row0, nrows, w->cols, w->nb, w->nbp, (int8_t *)w->values, (__half *)w->scales);
+    else
+        quantize_weight_q8_kernel<float><<<grid_for(warps * 32, 256), 256, 0, ctx->stream>>>(
+            wf32, row0, nrows, w->cols, w->nb, w->nbp, (int8_t *)w->values, (float *)w->scales);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+int32_t mk_launch_retile_q8(mk_ctx *ctx, const int8_t *q, const void *scales, mk_weight *w) {
+    const int64_t n = w->rows * (w->cols / 4);
+    if (w->scale_type == MK_SCALE_F16)
+        retile_q8_kernel<__half><<<grid_for(n, 256), 256, 0, ctx->stream>>>(q, (const __half *)scales, (int8_t *)w->values,
+                                                                         (__half *)w->scales, w->rows, w->cols, w->nb,
+                                                                         w->nbp, false, nullptr, nullptr);
+    else
+        retile_q8_kernel<float><<<grid_for(n, 256), 256, 0, ctx->stream>>>(q, (const float *)scales, (int8_t *)w->values,
+                                                                        (float *)w->scales, w->rows, w->cols, w->nb, w->nbp,
+                                                                        false, nullptr, nullptr);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+int32_t mk_launch_untile_q8(mk_ctx *ctx, const mk_weight *w, int8_t *q, void *scales) {
+    const int64_t n = w->rows * (w->cols / 4);
+    if (w->scale_type == MK_SCALE_F16)
+        retile_q8_kernel<__half><<<grid_for(n, 256), 256, 0, ctx->stream>>>(nullptr, nullptr, (int8_t *)w->values,
+                                                                         (__half *)w->scales, w->rows, w->cols, w->nb,
+                                                                         w->nbp, true, q, (__half *)scales);
+    else
+        retile_q8_kernel<float><<<grid_for(n, 256), 256, 0, ctx->stream>>>(nullptr, nullptr, (int8_t *)w->values,
+                                                                        (float *)w->scales, w->rows, w->cols, w->nb, w->nbp,
+                                                                        true, q, (float *)scales);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}

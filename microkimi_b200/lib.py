@@ -1,0 +1,79 @@
+"""ctypes binding of libmk_b200.so (the C ABI declared in include/mk_cuda.h).
+
+There is no CPU fallback: a missing library or a missing GPU raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "libmk_b200.so")
+
+MK_OK = 0
+MK_ACT_Q8 = 0
+MK_ACT_Q8X2 = 1
+MK_ACT_STRICT = 0x100
+MK_SCALE_F32 = 0
+MK_SCALE_F16 = 1
+PROF_CATEGORIES = {"matvec_mxfp4": 0, "lm_head": 1, "router": 2, "experts": 3, "mla": 4, "other": 5}
+
+
+class MkError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"libmk_b200 error {code}: {msg}")
+        self.code = code
+
+
+_lib = None
+
+_vp = C.c_void_p
+_i32 = C.c_int32
+_i64 = C.c_int64
+
+# name -> (restype, argtypes); every symbol include/mk_cuda.h declares
+SIGNATURES = {
+    "mk_init": (_i32, [_i32, C.POINTER(_vp)]),
+    "mk_shutdown": (_i32, [_vp]),
+    "mk_last_error": (C.c_char_p, []),
+    "mk_set_stream": (_i32, [_vp, _vp]),
+    "mk_sync": (_i32, [_vp]),
+    "mk_launch_count": (_i64, [_vp]),
+    "mk_device_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32), C.POINTER(C.c_uint64)]),
+    "mk_status_word": (_i32, [_vp, C.POINTER(_i32)]),
+    "mk_set_option": (_i32, [_vp, C.c_char_p, _i64]),
+    "mk_prof_enable": (_i32, [_vp, _i32]),
+    "mk_prof_read": (_i32, [_vp, _i32, C.POINTER(_i64), C.POINTER(C.c_double)]),
+    "mk_weight_mxfp4": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, C.POINTER(_vp)]),
+    "mk_weight_q8_from_f32": (_i32, [_vp, _vp, _i64, _i64, _i32, _i32, C.POINTER(_vp)]),
+    "mk_weight_q8": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, C.POINTER(_vp)]),
+    "mk_weight_free": (_i32, [_vp, _vp]),
+    "mk_weight_bytes": (_i64, [_vp]),
+    "mk_weight_export": (_i32, [_vp, _vp, _vp, _vp]),
+    "mk_dequant_mxfp4": (_i32, [_vp, _vp, _vp]),
+    "mk_quantize_q8": (_i32, [_vp, _vp, _i64, _vp, _vp]),
+    "mk_matvec_mxfp4": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "mk_matvec_mxfp4_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "mk_matvec_q8": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "mk_matvec_q8_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
+}
+
+
+def load():
+    """Loads the shared library (no GPU needed for this step)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise ImportError(
+                f"{SO_PATH} is missing: build it with `python -m microkimi_b200._build` "
+                "(nvcc, sm_100a). There is no CPU fallback.")
+        lib = C.CDLL(SO_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(lib, name)
+            f.restype = res
+            f.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc):
+    if rc != MK_OK:
+        raise MkError(rc, load().mk_last_error().decode(errors="replace"))

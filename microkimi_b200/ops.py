@@ -1,0 +1,254 @@
+"""Host-side mirror of the engine's operator interface for the quantized decode
+path, on top of the C ABI.  Names and argument meaning follow the Rust
+functions they stand in for:
+
+    matvec_packed(packed, scales, rows, cols, x)        src/mxfp4.rs:458
+    Q8Head.from_f32(w, rows, cols) / .matvec(x)         src/model.rs:274, 290
+    quantize_q8(x)                                      src/q8.rs:40
+
+Like the engine's operators, size mismatches raise (the Rust code asserts).
+numpy arrays go through the host-pointer entry points (copies inside the
+call); torch CUDA tensors go through the `_dev` entry points on torch's
+current stream.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import lib as _l
+
+
+def _np_ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _is_torch_cuda(x):
+    return type(x).__module__.startswith("torch") and getattr(x, "is_cuda", False)
+
+
+class Context:
+    """One GPU binding (mk_init). Thread-compatible, not re-entrant."""
+
+    _default = None
+
+    def __init__(self, device=0):
+        L = _l.load()
+        h = C.c_void_p()
+        _l.check(L.mk_init(int(device), C.byref(h)))
+        self._h = h
+        self.device = int(device)
+        self._L = L
+
+    @classmethod
+    def default(cls):
+        if cls._default is None:
+            cls._default = cls(0)
+        return cls._default
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.mk_shutdown(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def use_torch_stream(self):
+        """Run subsequent calls on torch's current CUDA stream of this device."""
+        import torch
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        _l.check(self._L.mk_set_stream(self._h, C.c_void_p(s)))
+
+    def sync(self):
+        _l.check(self._L.mk_sync(self._h))
+
+    @property
+    def launches(self):
+        return int(self._L.mk_launch_count(self._h))
+
+    def device_info(self):
+        sm, ma, mi, mem = C.c_int32(), C.c_int32(), C.c_int32(), C.c_uint64()
+        _l.check(self._L.mk_device_info(self._h, C.byref(sm), C.byref(ma), C.byref(mi), C.byref(mem)))
+        return {"sm_count": sm.value, "cc": (ma.value, mi.value), "mem_bytes": mem.value}
+
+    def set_option(self, name, value):
+        _l.check(self._L.mk_set_option(self._h, name.encode(), int(value)))
+
+    def prof_enable(self, on=True):
+        _l.check(self._L.mk_prof_enable(self._h, int(bool(on))))
+
+    def prof_read(self, category):
+        """(launches, total device ms) of one kernel category since prof_enable(True)."""
+        n, ms = C.c_int64(), C.c_double()
+        _l.check(self._L.mk_prof_read(self._h, _l.PROF_CATEGORIES[category], C.byref(n), C.byref(ms)))
+        return n.value, ms.value
+
+    def status_word(self):
+        v = C.c_int32()
+        _l.check(self._L.mk_status_word(self._h, C.byref(v)))
+        return v.value
+
+
+def _act_mode(act, strict):
+    m = {"q8": _l.MK_ACT_Q8, "q8x2": _l.MK_ACT_Q8X2}[act]
+    return m | (_l.MK_ACT_STRICT if strict else 0)
+
+
+class _Weight:
+    def __init__(self, ctx, handle, rows, cols):
+        self.ctx, self._h, self.rows, self.cols = ctx, handle, int(rows), int(cols)
+
+    def free(self):
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._L.mk_weight_free(self.ctx._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    @property
+    def device_bytes(self):
+        return int(self.ctx._L.mk_weight_bytes(self._h))
+
+    def _run(self, fn_host, fn_dev, x, act, strict, extra=()):
+        import_torch = _is_torch_cuda(x)
+        mode = _act_mode(act, strict)
+        if import_torch:
+            import torch
+            assert x.dtype == torch.float32 and x.is_contiguous()
+            batch = 1 if x.dim() == 1 else x.shape[0]
+            assert x.shape[-1] == self.cols, "x length must equal cols"
+            y = torch.empty((batch, self.rows), dtype=torch.float32, device=x.device)
+            return batch, y, fn_dev, (C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), batch, mode)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        batch = 1 if x.ndim == 1 else x.shape[0]
+        assert x.shape[-1] == self.cols, "x length must equal cols"
+        y = np.empty((batch, self.rows), np.float32)
+        return batch, y, fn_host, (_np_ptr(x), _np_ptr(y), batch, mode)
+
+
+class MxFp4Weight(_Weight):
+    """An MXFP4 matrix resident on the GPU: packed u8 [rows, cols/2] + ue8m0 scales
+    u8 [rows, cols/32] (BinFile::mxfp4_parts, src/weights.rs:619-626)."""
+
+    def __init__(self, packed, scales, rows, cols, ctx=None):
+        ctx = ctx or Context.default()
+        h = C.c_void_p()
+        if _is_torch_cuda(packed):
+            assert packed.numel() == rows * cols // 2 and scales.numel() == rows * cols // 32
+            _l.check(ctx._L.mk_weight_mxfp4(ctx._h, C.c_void_p(packed.data_ptr()), C.c_void_p(scales.data_ptr()),
+                                            rows, cols, 1, C.byref(h)))
+        else:
+            packed = np.ascontiguousarray(packed, dtype=np.uint8)
+            scales = np.ascontiguousarray(scales, dtype=np.uint8)
+            assert packed.size == rows * cols // 2, "packed must hold rows*cols/2 bytes"
+            assert scales.size == rows * cols // 32, "scales must hold rows*cols/32 bytes"
+            _l.check(ctx._L.mk_weight_mxfp4(ctx._h, _np_ptr(packed), _np_ptr(scales), rows, cols, 0, C.byref(h)))
+        super().__init__(ctx, h, rows, cols)
+
+    def matvec(self, x, act="q8", strict=False):
+        """y = W x (mxfp4::matvec_packed). x: [cols] or [batch, cols]."""
+        L = self.ctx._L
+        batch, y, fn, args = self._run(L.mk_matvec_mxfp4, L.mk_matvec_mxfp4_dev, x, act, strict)
+        _l.check(fn(self.ctx._h, self._h, *args))
+        return y[0] if (x.ndim if hasattr(x, "ndim") else x.dim()) == 1 else y
+
+    def dequant(self):
+        """mxfp4::dequant on the GPU -> f32 [rows, cols] (numpy)."""
+        out = np.empty((self.rows, self.cols), np.float32)
+        _l.check(self.ctx._L.mk_dequant_mxfp4(self.ctx._h, self._h, _np_ptr(out)))
+        return out
+
+    def export(self):
+        p = np.empty((self.rows, self.cols // 2), np.uint8)
+        s = np.empty((self.rows, self.cols // 32), np.uint8)
+        _l.check(self.ctx._L.mk_weight_export(self.ctx._h, self._h, _np_ptr(p), _np_ptr(s)))
+        return p, s
+
+
+def matvec_packed(packed, scales, rows, cols, x, act="q8", strict=False, ctx=None):
+    """Drop-in for mxfp4::matvec_packed / metal::gpu_matvec_fp4 with borrowed host
+    slices: registers the matrix, multiplies, frees.  Callers that reuse a matrix
+    keep an MxFp4Weight instead (the engine's device weight cache)."""
+    w = MxFp4Weight(packed, scales, rows, cols, ctx)
+    try:
+        return w.matvec(x, act=act, strict=strict)
+    finally:
+        w.free()
+
+
+class Q8Head(_Weight):
+    """Row-wise q8_0 matrix (model::Q8Head, src/model.rs:261-348)."""
+
+    def __init__(self, ctx, handle, rows, cols, scale_type):
+        super().__init__(ctx, handle, rows, cols)
+        self.scale_type = scale_type
+
+    @classmethod
+    def from_f32(cls, w, rows, cols, scale="f32", ctx=None):
+        """Q8Head::from_f32: quantizes on the GPU (bit-identical for f32 scales)."""
+        ctx = ctx or Context.default()
+        st = {"f32": _l.MK_SCALE_F32, "f16": _l.MK_SCALE_F16}[scale]
+        h = C.c_void_p()
+        if _is_torch_cuda(w):
+            assert w.numel() == rows * cols and w.is_contiguous()
+            _l.check(ctx._L.mk_weight_q8_from_f32(ctx._h, C.c_void_p(w.data_ptr()), rows, cols, st, 1, C.byref(h)))
+        else:
+            w = np.ascontiguousarray(w, dtype=np.float32)
+            assert w.size == rows * cols
+            _l.check(ctx._L.mk_weight_q8_from_f32(ctx._h, _np_ptr(w), rows, cols, st, 0, C.byref(h)))
+        return cls(ctx, h, rows, cols, st)
+
+    @classmethod
+    def from_q8(cls, q, scales, rows, cols, ctx=None):
+        ctx = ctx or Context.default()
+        q = np.ascontiguousarray(q, dtype=np.int8)
+        st = _l.MK_SCALE_F16 if scales.dtype in (np.float16, np.uint16) else _l.MK_SCALE_F32
+        scales = np.ascontiguousarray(scales)
+        assert q.size == rows * cols and scales.size == rows * cols // 32
+        h = C.c_void_p()
+        _l.check(ctx._L.mk_weight_q8(ctx._h, _np_ptr(q), _np_ptr(scales), rows, cols, st, 0, C.byref(h)))
+        return cls(ctx, h, rows, cols, st)
+
+    def matvec(self, x, act="q8", strict=False, want_argmax=False):
+        """Q8Head::matvec: logits [rows] (or [batch, rows]); optionally the greedy pick."""
+        L = self.ctx._L
+        batch, y, fn, args = self._run(L.mk_matvec_q8, L.mk_matvec_q8_dev, x, act, strict)
+        am = None
+        if want_argmax:
+            if _is_torch_cuda(x):
+                import torch
+                am = torch.empty(batch, dtype=torch.int32, device=x.device)
+                amp = C.c_void_p(am.data_ptr())
+            else:
+                am = np.empty(batch, np.int32)
+                amp = _np_ptr(am)
+        else:
+            amp = C.c_void_p(0)
+        _l.check(fn(self.ctx._h, self._h, *args, amp))
+        one = (x.ndim if hasattr(x, "ndim") else x.dim()) == 1
+        y = y[0] if one else y
+        return (y, am) if want_argmax else y
+
+    def export(self):
+        q = np.empty((self.rows, self.cols), np.int8)
+        s = np.empty((self.rows, self.cols // 32), np.float16 if self.scale_type == _l.MK_SCALE_F16 else np.float32)
+        _l.check(self.ctx._L.mk_weight_export(self.ctx._h, self._h, _np_ptr(q), _np_ptr(s)))
+        return q, s
+
+
+def quantize_q8(x, ctx=None):
+    """q8::quantize_q8 on the GPU: (q int8 [n], scales f32 [n/32])."""
+    ctx = ctx or Context.default()
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    assert x.size % 32 == 0, "q8 blocks are 32 wide"
+    q = np.empty(x.size, np.int8)
+    s = np.empty(x.size // 32, np.float32)
+    _l.check(ctx._L.mk_quantize_q8(ctx._h, _np_ptr(x), x.size, _np_ptr(q), _np_ptr(s)))
+    return q, s
