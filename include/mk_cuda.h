@@ -69,8 +69,9 @@ typedef struct mk_mla    mk_mla;
 int32_t mk_init(int32_t device, mk_ctx **out);
 int32_t mk_shutdown(mk_ctx *ctx);
 const char *mk_last_error(void);
-/* Stream used by every call on this context (a cudaStream_t); NULL selects the
- * context's own stream. */
+/* Stream used by every later call on this context (a cudaStream_t; NULL is the
+ * CUDA legacy default stream).  Until this is called the context runs on a
+ * non-blocking stream of its own. */
 int32_t mk_set_stream(mk_ctx *ctx, void *cuda_stream);
 int32_t mk_sync(mk_ctx *ctx);
 /* Number of kernels this context has launched since mk_init. */

@@ -75,7 +75,7 @@ extern "C" int32_t mk_shutdown(mk_ctx *ctx) {
 
 extern "C" int32_t mk_set_stream(mk_ctx *ctx, void *cuda_stream) {
     MK_CHECK_ARG(ctx != nullptr, "ctx is NULL");
-    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    ctx->stream = (cudaStream_t)cuda_stream;
     return MK_OK;
 }
 extern "C" int32_t mk_sync(mk_ctx *ctx) {

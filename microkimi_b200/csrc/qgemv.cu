@@ -22,145 +22,33 @@
 //             and adds the block terms in ascending block order with separate
 //             multiply and add.  With no K split that reproduces the CPU sums
 //             bit for bit (MK_ACT_STRICT).
-#include <cuda_fp16.h>
-
-#include "mk_common.cuh"
+#include "qgemv_core.cuh"
 
 namespace {
+using namespace mkq;
 
-enum { W_MXFP4 = 0, W_Q8_F32 = 1, W_Q8_F16 = 2 };
-
-template <int WF> struct Group;
-template <> struct Group<W_MXFP4> { uint4 a[2]; };  // 4 blocks = 2 chunks
-template <> struct Group<W_Q8_F32> { uint4 a[4]; }; // 4 blocks = 4 chunks
-template <> struct Group<W_Q8_F16> { uint4 a[4]; };
-
-template <int WF> __device__ __forceinline__ constexpr int chunks_per_group() { return WF == W_MXFP4 ? 2 : 4; }
-
-template <int WF>
-__device__ __forceinline__ void load_group(Group<WF> &g, const uint4 *tile_base, int64_t group, int lane) {
-    constexpr int C = chunks_per_group<WF>();
-    const uint4 *p = tile_base + (group * C) * 32 + lane;
-#pragma unroll
-    for (int c = 0; c < C; ++c) g.a[c] = mk_ldg_stream(p + c * 32);
-}
-
-// int32 block dots of block m (0..3) of a group: accumulates into c (pos) / cn (neg)
-template <int WF>
-__device__ __forceinline__ void block_mma(const Group<WF> &g, int m, uint32_t b0, uint32_t b1, int (&cp)[4], int (&cn)[4]) {
-    if constexpr (WF == W_MXFP4) {
-        const uint4 &ch = g.a[m >> 1];
-        uint32_t wg = (m & 1) ? ch.z : ch.x; // row g
-        uint32_t wh = (m & 1) ? ch.w : ch.y; // row g+8
-        uint32_t wgx = wg ^ 0x88888888u, whx = wh ^ 0x88888888u;
-        mk_mma_s8(cp, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh),
-                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh >> 16), b0, b1);
-        mk_mma_s8(cn, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx),
-                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx >> 16), b0, b1);
-    } else {
-        const uint4 &ch = g.a[m];
-        mk_mma_s8(cp, ch.x, ch.y, ch.z, ch.w, b0, b1);
-    }
-}
-
-// weight scales of block b for rows g and g+8 of row tile rt
-template <int WF>
-__device__ __forceinline__ void load_wscale(const void *wscale, int64_t rt, int64_t nbp, int64_t b, int g, float &sg, float &sh) {
-    int64_t base = (rt * nbp + b) * 16;
-    if constexpr (WF == W_MXFP4) {
-        const uint8_t *s = (const uint8_t *)wscale + base;
-        sg = mk_e8m0_half(__ldg(s + g));
-        sh = mk_e8m0_half(__ldg(s + g + 8));
-    } else if constexpr (WF == W_Q8_F32) {
-        const float *s = (const float *)wscale + base;
-        sg = __ldg(s + g);
-        sh = __ldg(s + g + 8);
-    } else {
-        const __half *s = (const __half *)wscale + base;
-        sg = __half2float(__ldg(s + g));
-        sh = __half2float(__ldg(s + g + 8));
-    }
-}
-
-// acc += idot * (sw * sx) with separate multiply and add, in the reference's order.
-__device__ __forceinline__ float acc_term(float acc, int idot, float sw, float sx) {
-    return __fadd_rn(acc, __fmul_rn(__fmul_rn(sw, sx), (float)idot));
-}
-
-// ------------------------------------------------------------------ "spread" schedule
-// NSLOT activation columns (1 or 2).  X2: the two columns are the high and low
-// limb of ONE token (idot = 128*hi + lo).
+// ------------------------------------------------------------------ one matrix, "spread" schedule
+// CTA = 8 warps = (8/KS) row tiles x KS K-slices.
 template <int WF, int KS, int NSLOT, bool X2>
 __global__ void __launch_bounds__(256)
-qgemv_spread_kernel(const uint4 *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
+qgemv_spread_kernel(const void *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
                     const float *__restrict__ xs, int64_t ldq, int64_t nbp, float *__restrict__ y, int64_t ldy,
                     int64_t rows, int64_t nrt) {
     constexpr int RT = 8 / KS;
-    constexpr int C = chunks_per_group<WF>();
+    constexpr int NOUT = X2 ? 1 : NSLOT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int rt_local = warp / KS, ks = warp % KS;
     const int64_t rt = (int64_t)blockIdx.x * RT + rt_local;
-    const int64_t ngroups = nbp >> 2;
-    constexpr int NOUT = X2 ? 1 : NSLOT;
     float acc[2][NOUT];
 #pragma unroll
     for (int o = 0; o < NOUT; ++o) acc[0][o] = acc[1][o] = 0.0f;
-
     if (rt < nrt) {
-        const uint4 *tile = wt + rt * (ngroups * C) * 32;
-        // lane (g,t) feeds MMA column g: slot g&1 of block (g>>1) of the group
-        const int slot = g & 1, sub = g >> 1;
-        const bool xvalid = slot < NSLOT;
-        const int8_t *xp = xq + (int64_t)slot * ldq + sub * 32 + t * 8;
-        uint32_t mask[4];
-#pragma unroll
-        for (int m = 0; m < 4; ++m) mask[m] = (sub == m && xvalid) ? 0xFFFFFFFFu : 0u;
-
-        Group<WF> cur, nxt;
-        int64_t i = ks;
-        if (i < ngroups) load_group<WF>(cur, tile, i, lane);
-        for (; i < ngroups; i += KS) {
-            const int64_t inext = i + KS;
-            if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
-            uint2 xv = make_uint2(0u, 0u);
-            if (xvalid) xv = __ldg((const uint2 *)(xp + i * 128));
-            int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
-#pragma unroll
-            for (int m = 0; m < 4; ++m) block_mma<WF>(cur, m, xv.x & mask[m], xv.y & mask[m], cp, cn);
-            // lane t now holds block 4i+t: c0/c1 = row g (slot 0/1), c2/c3 = row g+8
-            const int64_t b = i * 4 + t;
-            float sg, sh;
-            load_wscale<WF>(wscale, rt, nbp, b, g, sg, sh);
-            int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
-            if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
-            if constexpr (X2) {
-                const float sx = __ldg(xs + b);
-                acc[0][0] = acc_term(acc[0][0], d0 * 128 + d1, sg, sx);
-                acc[1][0] = acc_term(acc[1][0], d2 * 128 + d3, sh, sx);
-            } else {
-                const float sx0 = __ldg(xs + b);
-                acc[0][0] = acc_term(acc[0][0], d0, sg, sx0);
-                acc[1][0] = acc_term(acc[1][0], d2, sh, sx0);
-                if constexpr (NSLOT == 2) {
-                    const float sx1 = __ldg(xs + nbp + b);
-                    acc[0][1] = acc_term(acc[0][1], d1, sg, sx1);
-                    acc[1][1] = acc_term(acc[1][1], d3, sh, sx1);
-                }
-            }
-            cur = nxt;
-        }
+        const int slot = g & 1;
+        const int8_t *xrow = slot < NSLOT ? xq + (int64_t)slot * ldq : nullptr;
+        warp_tile_spread<WF, NSLOT, X2>(tile_values<WF>(wt, rt, nbp), tile_scales<WF>(wscale, rt, nbp), nbp >> 2, ks, KS,
+                                        lane, xrow, xs, xs + nbp, acc);
     }
-    // sum the 4 lanes of a row group (they hold blocks = t mod 4)
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int o = 0; o < NOUT; ++o) {
-            float v = acc[h][o];
-            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-            acc[h][o] = v;
-        }
     if constexpr (KS > 1) {
         __shared__ float red[8][16][NOUT];
         if (t == 0) {
@@ -200,66 +88,26 @@ qgemv_spread_kernel(const uint4 *__restrict__ wt, const void *__restrict__ wscal
     }
 }
 
-// ------------------------------------------------------------------ "batched" schedule
-// MMA columns = tokens (X2: column 2k / 2k+1 = high / low limb of token k).
+// ------------------------------------------------------------------ one matrix, "batched" schedule
 template <int WF, int KS, bool X2>
 __global__ void __launch_bounds__(256)
-qgemv_batched_kernel(const uint4 *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
+qgemv_batched_kernel(const void *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
                      const float *__restrict__ xs, int64_t ldq, int64_t nbp, int ntok, float *__restrict__ y,
                      int64_t ldy, int64_t rows, int64_t nrt) {
     constexpr int RT = 8 / KS;
-    constexpr int C = chunks_per_group<WF>();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int rt_local = warp / KS, ks = warp % KS;
     const int64_t rt = (int64_t)blockIdx.x * RT + rt_local;
-    const int64_t ngroups = nbp >> 2;
-    // outputs owned by this lane: !X2: (row g|g+8) x (token 2t | 2t+1); X2: (row g|g+8) x token t
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const int tok_a = X2 ? t : 2 * t, tok_b = X2 ? t : 2 * t + 1;
-
     if (rt < nrt) {
-        const uint4 *tile = wt + rt * (ngroups * C) * 32;
-        // column g of the B fragment
         const int ctok = X2 ? (g >> 1) : g;
-        const bool xvalid = ctok < ntok;
-        const int8_t *xp = xq + (X2 ? (int64_t)(g & 1) * ntok * ldq : 0) + (int64_t)ctok * ldq + t * 8;
-        const float *xsa = xs + (int64_t)tok_a * nbp;
-        const float *xsb = xs + (int64_t)tok_b * nbp;
-        const bool va = tok_a < ntok, vb = tok_b < ntok;
-
-        Group<WF> cur, nxt;
-        int64_t i = ks;
-        if (i < ngroups) load_group<WF>(cur, tile, i, lane);
-        for (; i < ngroups; i += KS) {
-            const int64_t inext = i + KS;
-            if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                const int64_t b = i * 4 + m;
-                uint2 xv = make_uint2(0u, 0u);
-                if (xvalid) xv = __ldg((const uint2 *)(xp + b * 32));
-                int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
-                block_mma<WF>(cur, m, xv.x, xv.y, cp, cn);
-                float sg, sh;
-                load_wscale<WF>(wscale, rt, nbp, b, g, sg, sh);
-                int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
-                if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
-                if constexpr (X2) {
-                    const float sx = va ? __ldg(xsa + b) : 0.0f;
-                    acc[0] = acc_term(acc[0], d0 * 128 + d1, sg, sx);
-                    acc[2] = acc_term(acc[2], d2 * 128 + d3, sh, sx);
-                } else {
-                    const float sxa = va ? __ldg(xsa + b) : 0.0f;
-                    const float sxb = vb ? __ldg(xsb + b) : 0.0f;
-                    acc[0] = acc_term(acc[0], d0, sg, sxa);
-                    acc[1] = acc_term(acc[1], d1, sg, sxb);
-                    acc[2] = acc_term(acc[2], d2, sh, sxa);
-                    acc[3] = acc_term(acc[3], d3, sh, sxb);
-                }
-            }
-            cur = nxt;
-        }
+        const int8_t *xcol = ctok < ntok ? xq + (X2 ? (int64_t)(g & 1) * ntok * ldq : 0) + (int64_t)ctok * ldq : nullptr;
+        const float *xsa = tok_a < ntok ? xs + (int64_t)tok_a * nbp : nullptr;
+        const float *xsb = tok_b < ntok ? xs + (int64_t)tok_b * nbp : nullptr;
+        warp_tile_batched<WF, X2>(tile_values<WF>(wt, rt, nbp), tile_scales<WF>(wscale, rt, nbp), nbp >> 2, ks, KS, lane,
+                                  xcol, xsa, xsb, acc);
     }
     if constexpr (KS > 1) {
         __shared__ float red[8][32][4];
@@ -277,20 +125,13 @@ qgemv_batched_kernel(const uint4 *__restrict__ wt, const void *__restrict__ wsca
     }
     if (ks == 0 && rt < nrt) {
         const int64_t row_g = rt * 16 + g, row_h = row_g + 8;
-        if constexpr (X2) {
-            if (tok_a < ntok) {
-                if (row_g < rows) y[(int64_t)tok_a * ldy + row_g] = acc[0];
-                if (row_h < rows) y[(int64_t)tok_a * ldy + row_h] = acc[2];
-            }
-        } else {
-            if (tok_a < ntok) {
-                if (row_g < rows) y[(int64_t)tok_a * ldy + row_g] = acc[0];
-                if (row_h < rows) y[(int64_t)tok_a * ldy + row_h] = acc[2];
-            }
-            if (tok_b < ntok) {
-                if (row_g < rows) y[(int64_t)tok_b * ldy + row_g] = acc[1];
-                if (row_h < rows) y[(int64_t)tok_b * ldy + row_h] = acc[3];
-            }
+        if (tok_a < ntok) {
+            if (row_g < rows) y[(int64_t)tok_a * ldy + row_g] = acc[0];
+            if (row_h < rows) y[(int64_t)tok_a * ldy + row_h] = acc[2];
+        }
+        if (!X2 && tok_b < ntok) {
+            if (row_g < rows) y[(int64_t)tok_b * ldy + row_g] = acc[1];
+            if (row_h < rows) y[(int64_t)tok_b * ldy + row_h] = acc[3];
         }
     }
 }
@@ -408,7 +249,7 @@ void launch_spread(const mk_weight *w, cudaStream_t st, const int8_t *xq, const 
     constexpr int RT = 8 / KS;
     const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
     const int64_t ldq = w->nbp * 32;
-    const uint4 *wt = (const uint4 *)w->values;
+    const void *wt = w->values;
     if (x2)
         qgemv_spread_kernel<WF, KS, 2, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
     else if (nslot == 2)
@@ -422,7 +263,7 @@ void launch_batched(const mk_weight *w, cudaStream_t st, const int8_t *xq, const
     constexpr int RT = 8 / KS;
     const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
     const int64_t ldq = w->nbp * 32;
-    const uint4 *wt = (const uint4 *)w->values;
+    const void *wt = w->values;
     if (x2)
         qgemv_batched_kernel<WF, KS, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt);
     else

@@ -1,0 +1,215 @@
+// Warp-level building blocks of the dequant-fused quantized matvec (sm_100a).
+//
+// One warp owns one 16-row weight tile (optionally one K slice of it) and streams
+// it from HBM in mma.m16n8k32 fragment order (see mk_weight in mk_common.cuh).
+// Per 32-wide block the dot of the weight row with the q8_0 activation is an
+// EXACT int32 (tensor cores, s8 x s8); it is then scaled and accumulated in f32:
+//   MXFP4 : acc += idot * (2^(sb-128) * xs)      (src/mxfp4.rs:409-418)
+//   q8_0  : acc += (ws * xs) * idot               (src/model.rs:337-347)
+// E2M1 codes are decoded in registers with byte permutes: the 3 magnitude bits of
+// a code select one of the bytes {0,1,2,3,4,6,8,12} (= E2M1 x 2, src/q8.rs:22); a
+// set sign bit makes the permute return 0.  One pass gives the positive part, a
+// pass over the sign-flipped word the negative part; idot = dot(pos) - dot(neg).
+//
+// Two schedules:
+//   spread  : <= 2 activation columns.  The 8 MMA columns carry 4 consecutive
+//             blocks x 2 columns, so the scaling runs once per 4 blocks with every
+//             lane busy; lane t accumulates blocks = t (mod 4).
+//   batched : the 8 MMA columns are 8 tokens; a lane owns 4 outputs and adds the
+//             block terms in ascending block order with separate multiply and add
+//             (bit-identical to the CPU sums when K is not split).
+#pragma once
+#include <cuda_fp16.h>
+
+#include "mk_common.cuh"
+
+namespace mkq {
+
+enum { W_MXFP4 = 0, W_Q8_F32 = 1, W_Q8_F16 = 2 };
+
+template <int WF> struct Group;
+template <> struct Group<W_MXFP4> { uint4 a[2]; };  // 4 blocks = 2 chunks of 512 B
+template <> struct Group<W_Q8_F32> { uint4 a[4]; }; // 4 blocks = 4 chunks
+template <> struct Group<W_Q8_F16> { uint4 a[4]; };
+
+template <int WF> __host__ __device__ constexpr int chunks_per_group() { return WF == W_MXFP4 ? 2 : 4; }
+// bytes of tiled values of one 16-row tile per 4-block group
+template <int WF> __host__ __device__ constexpr int group_bytes() { return chunks_per_group<WF>() * 512; }
+
+template <int WF>
+__device__ __forceinline__ void load_group(Group<WF> &g, const uint4 *tile_base, int64_t group, int lane) {
+    constexpr int C = chunks_per_group<WF>();
+    const uint4 *p = tile_base + (group * C) * 32 + lane;
+#pragma unroll
+    for (int c = 0; c < C; ++c) g.a[c] = mk_ldg_stream(p + c * 32);
+}
+
+// int32 block dots of block m (0..3) of a group, accumulated into cp (and cn for MXFP4)
+template <int WF>
+__device__ __forceinline__ void block_mma(const Group<WF> &g, int m, uint32_t b0, uint32_t b1, int (&cp)[4], int (&cn)[4]) {
+    if constexpr (WF == W_MXFP4) {
+        const uint4 &ch = g.a[m >> 1];
+        const uint32_t wg = (m & 1) ? ch.z : ch.x; // row g
+        const uint32_t wh = (m & 1) ? ch.w : ch.y; // row g+8
+        const uint32_t wgx = wg ^ 0x88888888u, whx = wh ^ 0x88888888u;
+        mk_mma_s8(cp, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh),
+                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh >> 16), b0, b1);
+        mk_mma_s8(cn, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx),
+                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx >> 16), b0, b1);
+    } else {
+        const uint4 &ch = g.a[m];
+        mk_mma_s8(cp, ch.x, ch.y, ch.z, ch.w, b0, b1);
+    }
+}
+
+// weight scales of block b for rows g and g+8; `sc` points at the tile's scales ([block][16 rows])
+template <int WF>
+__device__ __forceinline__ void load_wscale(const void *sc, int64_t b, int g, float &sg, float &sh) {
+    if constexpr (WF == W_MXFP4) {
+        const uint8_t *s = (const uint8_t *)sc + b * 16;
+        sg = mk_e8m0_half(__ldg(s + g));
+        sh = mk_e8m0_half(__ldg(s + g + 8));
+    } else if constexpr (WF == W_Q8_F32) {
+        const float *s = (const float *)sc + b * 16;
+        sg = __ldg(s + g);
+        sh = __ldg(s + g + 8);
+    } else {
+        const __half *s = (const __half *)sc + b * 16;
+        sg = __half2float(__ldg(s + g));
+        sh = __half2float(__ldg(s + g + 8));
+    }
+}
+template <int WF> __host__ __device__ constexpr int scale_elem_bytes() { return WF == W_MXFP4 ? 1 : (WF == W_Q8_F32 ? 4 : 2); }
+
+// acc + idot * (sw * sx), separate multiply and add, in the reference's order
+__device__ __forceinline__ float acc_term(float acc, int idot, float sw, float sx) {
+    return __fadd_rn(acc, __fmul_rn(__fmul_rn(sw, sx), (float)idot));
+}
+
+// ---- spread schedule.  `tile`: tiled values of this row tile; `sc`: its scales;
+// groups ks, ks+KS, ... < ngroups are processed.  Lane (g,t) feeds MMA column g =
+// slot (g&1) of block (g>>1): `xrow` is the q8 row of this lane's slot (nullptr
+// when the slot is unused), xs0/xs1 the block scales of slot 0/1.
+// Result: out[h][o] for rows g + 8h, already summed over the 4 lanes of a row
+// group (every lane of the group holds the total).  X2: slots are the high/low
+// limb of one token, one output.
+template <int WF, int NSLOT, bool X2>
+__device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile, const void *__restrict__ sc, int64_t ngroups,
+                                                 int ks, int KS, int lane, const int8_t *__restrict__ xrow,
+                                                 const float *__restrict__ xs0, const float *__restrict__ xs1,
+                                                 float (&out)[2][X2 ? 1 : NSLOT]) {
+    constexpr int NOUT = X2 ? 1 : NSLOT;
+    const int g = lane >> 2, t = lane & 3;
+    const int sub = g >> 1;
+    float acc[2][NOUT];
+#pragma unroll
+    for (int o = 0; o < NOUT; ++o) acc[0][o] = acc[1][o] = 0.0f;
+    const bool xvalid = xrow != nullptr;
+    const int8_t *xp = xrow + sub * 32 + t * 8;
+    uint32_t mask[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) mask[m] = (sub == m && xvalid) ? 0xFFFFFFFFu : 0u;
+
+    Group<WF> cur, nxt;
+    int64_t i = ks;
+    if (i < ngroups) load_group<WF>(cur, tile, i, lane);
+    for (; i < ngroups; i += KS) {
+        const int64_t inext = i + KS;
+        if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
+        uint2 xv = make_uint2(0u, 0u);
+        if (xvalid) xv = __ldg((const uint2 *)(xp + i * 128));
+        int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int m = 0; m < 4; ++m) block_mma<WF>(cur, m, xv.x & mask[m], xv.y & mask[m], cp, cn);
+        // lane t now holds block 4i+t: c0/c1 = row g (slot 0/1), c2/c3 = row g+8
+        const int64_t b = i * 4 + t;
+        float sg, sh;
+        load_wscale<WF>(sc, b, g, sg, sh);
+        int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
+        if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
+        if constexpr (X2) {
+            const float sx = __ldg(xs0 + b);
+            acc[0][0] = acc_term(acc[0][0], d0 * 128 + d1, sg, sx);
+            acc[1][0] = acc_term(acc[1][0], d2 * 128 + d3, sh, sx);
+        } else {
+            const float sx0 = __ldg(xs0 + b);
+            acc[0][0] = acc_term(acc[0][0], d0, sg, sx0);
+            acc[1][0] = acc_term(acc[1][0], d2, sh, sx0);
+            if constexpr (NSLOT == 2) {
+                const float sx1 = __ldg(xs1 + b);
+                acc[0][1] = acc_term(acc[0][1], d1, sg, sx1);
+                acc[1][1] = acc_term(acc[1][1], d3, sh, sx1);
+            }
+        }
+        cur = nxt;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o) {
+            float v = acc[h][o];
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+            out[h][o] = v;
+        }
+}
+
+// ---- batched schedule.  Lane (g,t) feeds MMA column g from `xcol` (q8 row of that
+// column, nullptr = unused) and owns outputs
+//   !X2: acc[0] (row g, col 2t) acc[1] (row g, col 2t+1) acc[2] (row g+8, col 2t) acc[3] (row g+8, col 2t+1)
+//    X2: columns 2k / 2k+1 are the limbs of token k: acc[0] (row g, token t), acc[2] (row g+8, token t)
+// xs_a / xs_b: block scales of this lane's two columns (tokens), nullptr = unused.
+template <int WF, bool X2>
+__device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile, const void *__restrict__ sc, int64_t ngroups,
+                                                  int ks, int KS, int lane, const int8_t *__restrict__ xcol,
+                                                  const float *__restrict__ xs_a, const float *__restrict__ xs_b,
+                                                  float (&acc)[4]) {
+    const int g = lane >> 2, t = lane & 3;
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+    const bool xvalid = xcol != nullptr;
+    const int8_t *xp = xcol + t * 8;
+    Group<WF> cur, nxt;
+    int64_t i = ks;
+    if (i < ngroups) load_group<WF>(cur, tile, i, lane);
+    for (; i < ngroups; i += KS) {
+        const int64_t inext = i + KS;
+        if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int64_t b = i * 4 + m;
+            uint2 xv = make_uint2(0u, 0u);
+            if (xvalid) xv = __ldg((const uint2 *)(xp + b * 32));
+            int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+            block_mma<WF>(cur, m, xv.x, xv.y, cp, cn);
+            float sg, sh;
+            load_wscale<WF>(sc, b, g, sg, sh);
+            int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
+            if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
+            if constexpr (X2) {
+                const float sx = xs_a ? __ldg(xs_a + b) : 0.0f;
+                acc[0] = acc_term(acc[0], d0 * 128 + d1, sg, sx);
+                acc[2] = acc_term(acc[2], d2 * 128 + d3, sh, sx);
+            } else {
+                const float sxa = xs_a ? __ldg(xs_a + b) : 0.0f;
+                const float sxb = xs_b ? __ldg(xs_b + b) : 0.0f;
+                acc[0] = acc_term(acc[0], d0, sg, sxa);
+                acc[1] = acc_term(acc[1], d1, sg, sxb);
+                acc[2] = acc_term(acc[2], d2, sh, sxa);
+                acc[3] = acc_term(acc[3], d3, sh, sxb);
+            }
+        }
+        cur = nxt;
+    }
+}
+
+// pointers into a registered weight for row tile rt
+template <int WF>
+__device__ __forceinline__ const uint4 *tile_values(const void *values, int64_t rt, int64_t nbp) {
+    return (const uint4 *)values + rt * ((nbp >> 2) * chunks_per_group<WF>()) * 32;
+}
+template <int WF>
+__device__ __forceinline__ const void *tile_scales(const void *scales, int64_t rt, int64_t nbp) {
+    return (const char *)scales + rt * nbp * 16 * scale_elem_bytes<WF>();
+}
+
+} // namespace mkq

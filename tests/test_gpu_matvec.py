@@ -175,7 +175,7 @@ def test_mxfp4_matvec_linearity_property(mk):
     s = rng.integers(118, 124, (rows, cols // 32), dtype=np.uint8)
     a = rng.integers(-31, 32, cols).astype(np.float32)
     b = rng.integers(-31, 32, cols).astype(np.float32)
-    a[::32], b[::32] = 127, 0   # block max 127 -> dx = 1 exactly, integers survive q8
+    a[::32], b[::32] = 127, -127   # block max 127 -> dx = 1 exactly, integers survive q8
     w = mk.MxFp4Weight(p, s, rows, cols)
     ya, yb = w.matvec(a), w.matvec(b)
     dense = O.mxfp4_dequant(p, s, rows, cols).astype(np.float64)
