@@ -275,8 +275,56 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_case_mxfp4(args):
+    """Side workload for kernel studies and profiler captures: one MXFP4 matvec
+    (rows x cols, synthetic codes) over `copies` rotating matrices.  One JSON line."""
+    import torch
+
+    import microkimi_b200 as mk
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ctx = mk.Context(0)
+    mk.Context._default = ctx
+    ctx.use_torch_stream()
+    rows, cols, batch = args.rows, args.cols, args.batch
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    ws = []
+    for _ in range(args.copies):
+        p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
+        s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
+        ws.append(mk.MxFp4Weight(p, s, rows, cols, ctx=ctx))
+    x = torch.randn((batch, cols), dtype=torch.float32, device=dev, generator=gen)
+    for i in range(args.warmup):
+        ws[i % args.copies].matvec(x, act=args.act)
+    torch.cuda.synchronize()
+    ctx.prof_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        ws[i % args.copies].matvec(x, act=args.act)
+    e1.record()
+    torch.cuda.synchronize()
+    n, kms = ctx.prof_read("matvec_mxfp4")
+    ctx.prof_enable(False)
+    alg = rows * cols // 2 + rows * cols // 32 + batch * (cols + rows) * 4
+    peak, kind = measured_peaks()
+    ach = alg / (kms / n * 1e-3) / 1e9
+    print(json.dumps({"case": "mxfp4_gemv", "rows": rows, "cols": cols, "batch": batch, "copies": args.copies,
+                      "act": args.act, "ms_per_step": e0.elapsed_time(e1) / args.steps, "kernel_us": kms / n * 1e3,
+                      "algorithmic_bytes": alg,
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                                   "peak_kind": kind}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv"],
+                    help="lm_head is the benchmark proper; the others are side workloads for kernel studies")
+    ap.add_argument("--rows", type=int, default=7168)
+    ap.add_argument("--cols", type=int, default=2048)
+    ap.add_argument("--copies", type=int, default=1)
+    ap.add_argument("--act", default="q8", choices=["q8", "q8x2"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
@@ -287,6 +335,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.case == "mxfp4_gemv":
+        run_case_mxfp4(args)
     else:
         run_gpu(args)
 

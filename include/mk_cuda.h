@@ -78,7 +78,7 @@ int32_t mk_sync(mk_ctx *ctx);
 int64_t mk_launch_count(mk_ctx *ctx);
 int32_t mk_device_info(mk_ctx *ctx, int32_t *sm_count, int32_t *cc_major, int32_t *cc_minor, uint64_t *mem_bytes);
 /* Device-side status word: 0, or the first MK_ERR_* a kernel recorded (bounded
- * waits, range checks).  Reading it synchronizes the stream. */
+ * waits, range checks).  Reading it synchronizes the stream and clears the word. */
 int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
 
 /* Tuning knobs, for measurement only (defaults are chosen per shape):
@@ -141,6 +141,46 @@ int32_t mk_matvec_q8(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, 
                      int32_t act_mode, int32_t *argmax);
 int32_t mk_matvec_q8_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch,
                          int32_t act_mode, int32_t *argmax);
+
+/* ---- MoE layer ---------------------------------------------------------
+ * One call per layer instead of 3 matvecs per selected expert: replaces
+ * moe_forward / ds_moe wholesale (src/model.rs:2150-2380, src/deepseek.rs:1038-1108).
+ *   router     : noaux_tc - logits = gate_w x in the engine's dot() order (bit-exact),
+ *                sigmoid, +bias for selection only, top-k by (key desc, index asc),
+ *                weights = score / (sum + 1e-20)            (src/model.rs:2153-2173)
+ *   experts    : MXFP4 w1/w3 -> act -> w2 through the q8 integer path
+ *   MK_MOE_SWIGLU_CLAMP: act = (wgt * silu(min(g, limit))) * clamp(u, +-limit), the
+ *                routing weight folded in BEFORE w2, outputs summed in slot order,
+ *                plus one unweighted shared expert        (src/deepseek.rs:1083-1106)
+ * Expert index n_experts names the shared expert. */
+#define MK_MOE_SWIGLU_CLAMP 0
+typedef struct {
+    int32_t n_experts, top_k, d, inter;
+    float   swiglu_limit;
+    int32_t activation;              /* MK_MOE_* */
+    const float *gate_w;             /* HOST f32 [n_experts, d]; NULL: no router (experts only) */
+    const float *gate_b;             /* HOST f32 [n_experts]; NULL = zeros */
+    const mk_weight *const *experts; /* [n_experts * 3] = w1 [inter,d], w2 [d,inter], w3 [inter,d] per expert;
+                                        NULL entries = expert not resident on this GPU (expert parallel) */
+    const mk_weight *shared[3];      /* shared expert w1, w2, w3; all NULL = none here */
+} mk_moe_desc;
+int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out);
+int32_t mk_moe_free(mk_ctx *ctx, mk_moe *moe);
+/* Router only: ids int32 [n, top_k] and weights f32 [n, top_k] in slot order;
+ * logits (optional) f32 [n, n_experts]. */
+int32_t mk_moe_route(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_tokens, int32_t *ids, float *weights, float *logits);
+int32_t mk_moe_route_dev(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_tokens, int32_t *ids, float *weights, float *logits);
+/* Whole layer for n_tokens rows x f32 [n, d] -> out f32 [n, d]; ids / weights optional outputs. */
+int32_t mk_moe_forward(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_tokens, float *out, int32_t *ids, float *weights);
+int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_tokens, float *out, int32_t *ids, float *weights);
+/* Grouped experts on an explicit list of (row of x, expert, routing weight) pairs -
+ * the piece that runs on the expert's owner under expert parallelism:
+ * outs f32 [n_pairs, d] = expert(pair_expert[p]) applied to x[pair_row[p]].  DEVICE pointers. */
+int32_t mk_moe_experts_dev(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_rows, const int32_t *pair_row,
+                           const int32_t *pair_expert, const float *pair_weight, int32_t n_pairs, float *outs);
+/* out[t] = sum over slots (in slot order) of outs[t * slots + s]: the fixed-order
+ * combination after the expert jobs (src/deepseek.rs:1095-1106).  DEVICE pointers. */
+int32_t mk_moe_combine_dev(mk_ctx *ctx, const float *outs, int32_t n_tokens, int32_t slots, int32_t d, float *out);
 
 #ifdef __cplusplus
 }

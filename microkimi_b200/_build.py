@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmk_b200.so")
-SOURCES = ["mk_api.cu", "qgemv.cu", "weights.cu"]
+SOURCES = ["mk_api.cu", "qgemv.cu", "weights.cu", "moe.cu"]
 HEADERS = [os.path.join(CSRC, "mk_common.cuh"), os.path.join(HERE, "..", "include", "mk_cuda.h")]
 
 NVCC_FLAGS = [
@@ -33,6 +33,14 @@ def _stale(target, deps):
         return True
     t = os.path.getmtime(target)
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+
+
+def build_variant(out, defines):
+    """Side build with extra -D flags (kernel studies); objects go next to `out`."""
+    nvcc = _nvcc()
+    srcs = [os.path.join(CSRC, s) for s in SOURCES]
+    subprocess.check_call([nvcc] + NVCC_FLAGS + ["-D" + d for d in defines] + ["-shared", "-o", out] + srcs)
+    return out
 
 
 def build(force=False, verbose=False):

@@ -43,6 +43,8 @@ extern "C" int32_t mk_init(int32_t device, mk_ctx **out) {
     cudaError_t e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int32_t));
     if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&c->zeros_dev, 256);
+    if (e == cudaSuccess) e = cudaMemset(c->zeros_dev, 0, 256);
     if (e != cudaSuccess) {
         mk_set_error("mk_init: %s", cudaGetErrorString(e));
         delete c;
@@ -61,6 +63,7 @@ extern "C" int32_t mk_shutdown(mk_ctx *ctx) {
     if (ctx->io_dev) cudaFree(ctx->io_dev);
     if (ctx->io_pinned) cudaFreeHost(ctx->io_pinned);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->zeros_dev) cudaFree(ctx->zeros_dev);
     if (ctx->prof_pairs) {
         for (int i = 0; i < ctx->prof_cap; ++i) {
             cudaEventDestroy(ctx->prof_pairs[i].a);
@@ -95,6 +98,7 @@ extern "C" int32_t mk_device_info(mk_ctx *ctx, int32_t *sm_count, int32_t *cc_ma
 extern "C" int32_t mk_status_word(mk_ctx *ctx, int32_t *out) {
     MK_CHECK_ARG(ctx != nullptr && out != nullptr, "NULL argument");
     MK_CUDA(cudaMemcpyAsync(out, ctx->status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaMemsetAsync(ctx->status_dev, 0, sizeof(int32_t), ctx->stream));
     MK_CUDA(cudaStreamSynchronize(ctx->stream));
     return MK_OK;
 }

@@ -69,6 +69,7 @@ struct mk_ctx {
     cudaStream_t stream;
     int64_t launches;
     int32_t *status_dev;    // device status word
+    int8_t *zeros_dev;      // 256 zero bytes (B operand of unused MMA columns)
     // activation workspace (grown on demand, never per call once warm)
     void *ws;
     size_t ws_bytes;
@@ -127,7 +128,8 @@ __device__ __forceinline__ float mk_e8m0(uint32_t sb) {
 }
 // 2^(sb-128): the scale of the integer LUT (E2M1 x 2) convention.
 __device__ __forceinline__ float mk_e8m0_half(uint32_t sb) {
-    return __uint_as_float(sb >= 2 ? ((sb - 1) << 23) : (0x00200000u << sb));
+    // 2^(sb-127) * 0.5: exact for every byte (sb == 1 gives the subnormal 2^-127)
+    return mk_e8m0(sb) * 0.5f;
 }
 // prmt.b32 in its generic form: selector nibble n picks byte (n & 7) of {b,a};
 // a selector nibble with bit 3 set yields 0x00/0xFF from that byte's sign bit.

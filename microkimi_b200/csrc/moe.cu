@@ -1,0 +1,619 @@
+// MoE layer on the GPU: router, top-k, expert grouping, grouped MXFP4 expert
+// matvecs with fused activation, fixed-order combine (sm_100a).
+//
+// Reference: moe_forward (src/model.rs:2150-2380) for the router and the slot-order
+// combination, ds_moe / expert_forward (src/deepseek.rs:1038-1108, 74-95) for the
+// expert body (SwiGLU with clamp, routing weight folded in before w2), and
+// matvec_packed_nt (src/model.rs:2412-2447) for what batching means: every
+// (token, expert) result is what a single-token call would give.
+//
+// Launches per layer call: router logits, activation quantization, top-k (+ pair
+// list), plan (group pairs by expert), gate/up (+ activation + q8 of the
+// activation), down, combine.
+#include "qgemv_core.cuh"
+
+using namespace mkq;
+
+struct mk_moe {
+    int n_experts, top_k, d, inter, activation;
+    float limit;
+    bool has_router, has_shared;
+    float *gate_w, *gate_b;        // device
+    const void **wv, **wsc;        // device tables [(n_experts+1)*3] of tiled values / scales (nullptr = not resident)
+    int64_t nbp_d, nbp_i;          // padded block counts of d and inter
+    // workspace, sized for cap_rows activation rows and cap_pairs pairs
+    int cap_rows, cap_pairs;
+    float *logits;                 // [rows][n_experts]
+    int32_t *ids;                  // [rows][top_k]
+    float *wts;                    // [rows][top_k]
+    int8_t *xq; float *xs;         // q8 activations of the rows
+    int32_t *pair_row, *pair_expert; float *pair_weight;   // forward path pair list
+    int32_t *sorted;               // pair ids grouped by expert
+    int32_t *items;                // [max_items][3] = expert, offset into sorted, count (<= 8)
+    int32_t *n_items;              // device scalar
+    int8_t *actq; float *acts;     // q8 of the expert activations, per pair
+    float *outs;                   // [pairs][d]
+    int max_items;
+};
+
+namespace {
+
+// ------------------------------------------------------------------ router logits
+// logits[t][e] = dot(gate_w[e], x[t]) in the engine's order (src/model.rs:63-82):
+// 8 accumulators, element j of each 8-chunk into accumulator j with a separate
+// multiply and add, then ((a0+a1)+(a2+a3))+(a4+a5))+(a6+a7), tail sequential.
+// 8 lanes own the 8 accumulators of one (expert, token tile); a warp = 4 experts.
+template <int T>
+__global__ void __launch_bounds__(256)
+moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restrict__ x, float *__restrict__ logits,
+                         int n_experts, int d, int n_tokens) {
+    const int warp_g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
+    const int ewarps = (n_experts + 3) / 4;
+    const int tile = warp_g / ewarps;
+    const int e = (warp_g % ewarps) * 4 + sub;
+    const int tok0 = tile * T;
+    if (tok0 >= n_tokens) return;
+    const bool ev = e < n_experts;
+    const float *w = gate_w + (size_t)(ev ? e : 0) * d;
+    float acc[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) acc[t] = 0.0f;
+    const int full = d & ~7;
+#pragma unroll 4
+    for (int c = 0; c < full; c += 8) {
+        const float wv = __ldg(w + c + j);
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            const int tok = min(tok0 + t, n_tokens - 1);
+            acc[t] = __fadd_rn(acc[t], __fmul_rn(wv, __ldg(x + (size_t)tok * d + c + j)));
+        }
+    }
+    const int base = lane & ~7;
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        const float v1 = __fadd_rn(acc[t], __shfl_xor_sync(0xFFFFFFFFu, acc[t], 1)); // a(2i) + a(2i+1)
+        const float p01 = __shfl_sync(0xFFFFFFFFu, v1, base + 0), p23 = __shfl_sync(0xFFFFFFFFu, v1, base + 2);
+        const float p45 = __shfl_sync(0xFFFFFFFFu, v1, base + 4), p67 = __shfl_sync(0xFFFFFFFFu, v1, base + 6);
+        float s = __fadd_rn(__fadd_rn(__fadd_rn(p01, p23), p45), p67);
+        if (j == 0 && ev && tok0 + t < n_tokens) {
+            for (int c = full; c < d; ++c) s = __fadd_rn(s, __fmul_rn(__ldg(w + c), __ldg(x + (size_t)(tok0 + t) * d + c)));
+            logits[(size_t)(tok0 + t) * n_experts + e] = s;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ top-k
+// One warp per token.  score = 1/(1+exp(-l)), key = score + bias; the top_k by
+// (key descending, index ascending) in that order is what the engine's running
+// selection ends with (src/model.rs:2157-2171); weights = score / (sum + 1e-20)
+// with the sum taken in slot order (src/model.rs:2172-2173).  exp() runs in double
+// and is rounded once, which agrees with a correctly rounded expf.
+__global__ void __launch_bounds__(128)
+moe_topk_kernel(const float *__restrict__ logits, const float *__restrict__ gate_b, int n_experts, int top_k, int n_tokens,
+                int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
+                int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * (blockDim.x >> 5) + warp;
+    float *sc = sm + (size_t)warp * 2 * n_experts, *key = sc + n_experts;
+    if (tok >= n_tokens) return;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float l = logits[(size_t)tok * n_experts + e];
+        const float ex = (float)exp((double)(-l));
+        const float s = __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
+        sc[e] = s;
+        key[e] = __fadd_rn(s, gate_b ? gate_b[e] : 0.0f);
+    }
+    __syncwarp();
+    float sumw = 0.0f;
+    float my_sc = 0.0f;
+    int my_id = -1;
+    for (int r = 0; r < top_k; ++r) {
+        float bk = -INFINITY;
+        int bi = 0x7FFFFFFF;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float kv = key[e];
+            if (kv > bk || (kv == bk && e < bi)) { bk = kv; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ok = __shfl_xor_sync(0xFFFFFFFFu, bk, o);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+            if (ok > bk || (ok == bk && oi < bi)) { bk = ok; bi = oi; }
+        }
+        if (bi == 0x7FFFFFFF) bi = 0;
+        const float s = sc[bi];
+        sumw = __fadd_rn(sumw, s);
+        if (lane == r) { my_sc = s; my_id = bi; }
+        __syncwarp();
+        if (lane == 0) key[bi] = -INFINITY; // taken (ties among -inf resolve to the lowest index, never re-taken before real keys)
+        __syncwarp();
+    }
+    sumw = __fadd_rn(sumw, 1e-20f);
+    const int slots = top_k + (shared_slot ? 1 : 0);
+    if (lane < top_k) {
+        const float w = __fdiv_rn(my_sc, sumw);
+        ids[(size_t)tok * top_k + lane] = my_id;
+        wts[(size_t)tok * top_k + lane] = w;
+        if (pair_row) {
+            const int p = tok * slots + lane;
+            pair_row[p] = tok;
+            pair_expert[p] = my_id;
+            pair_weight[p] = w;
+        }
+    }
+    if (pair_row && shared_slot && lane == 31) {
+        const int p = tok * slots + top_k;
+        pair_row[p] = tok;
+        pair_expert[p] = n_experts; // the shared expert, unweighted
+        pair_weight[p] = 1.0f;
+    }
+}
+
+// ------------------------------------------------------------------ plan
+// Single block: counting sort of the pairs by expert, then one work item per
+// (expert, chunk of <= 8 pairs).  Pairs naming an expert that is not resident are
+// dropped and flagged in the status word.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots /* n_experts + 1 */,
+                const void *const *__restrict__ wv, int32_t *__restrict__ sorted, int32_t *__restrict__ items,
+                int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status) {
+    extern __shared__ int sh[];
+    int *cnt = sh, *off = sh + n_slots, *ioff = off + n_slots, *cur = ioff + n_slots;
+    for (int e = threadIdx.x; e < n_slots; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = pair_expert[p];
+        if (e < 0 || e >= n_slots || wv[e * 3] == nullptr) { atomicCAS(status, 0, MK_ERR_ARG); continue; }
+        atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, io = 0;
+        for (int e = 0; e < n_slots; ++e) {
+            off[e] = o;
+            ioff[e] = io;
+            o += cnt[e];
+            io += (cnt[e] + 7) >> 3;
+        }
+        *n_items = io < max_items ? io : max_items;
+        if (io > max_items) atomicCAS(status, 0, MK_ERR_STATE);
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = pair_expert[p];
+        if (e < 0 || e >= n_slots || wv[e * 3] == nullptr) continue;
+        sorted[off[e] + atomicAdd(&cur[e], 1)] = p;
+    }
+    for (int e = threadIdx.x; e < n_slots; e += blockDim.x) {
+        const int nch = (cnt[e] + 7) >> 3;
+        for (int c = 0; c < nch; ++c) {
+            const int it = ioff[e] + c;
+            if (it < max_items) {
+                items[it * 3 + 0] = e;
+                items[it * 3 + 1] = off[e] + c * 8;
+                items[it * 3 + 2] = min(8, cnt[e] - c * 8);
+            }
+        }
+    }
+}
+
+} // namespace
+
+namespace {
+
+struct MoeArgs {
+    const void *const *wv;       // [(E+1)*3] tiled values
+    const void *const *wsc;      // [(E+1)*3] tiled scales
+    const int32_t *items;        // [n][3]
+    const int32_t *n_items;
+    const int32_t *sorted;       // pair ids
+    const int32_t *pair_row;
+    const float *pair_weight;
+    const int8_t *xq;            // [rows][ldq_d]
+    const float *xs;             // [rows][nbp_d]
+    int8_t *actq;                // [pairs][ldq_i]
+    float *acts;                 // [pairs][nbp_i]
+    float *outs;                 // [pairs][d]
+    int64_t nbp_d, nbp_i;
+    int d, inter;
+    float limit;
+    Consts k;
+};
+
+// Partial sums of one warp for a 16-row tile and up to 8 columns, into smem part[16][8].
+// n <= 2 columns use the spread schedule, more the batched one.
+template <int WF>
+__device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc, int64_t ngroups, int ks, int KS, int lane,
+                                              int n, const int8_t *const *xrow /* [n] */, const float *const *xsrow /* [n] */,
+                                              const Consts &k, float (*part)[8]) {
+    const int g = lane >> 2, t = lane & 3;
+    if (n <= 2) {
+        const int slot = g & 1;
+        const int8_t *xr = slot < n ? xrow[slot] : nullptr;
+        if (n == 1) {
+            float o[2][1];
+            warp_tile_spread<WF, 1, false>(tile, sc, ngroups, ks, KS, lane, xr, xsrow[0], xsrow[0], k, o);
+            if (t == 0) { part[g][0] = o[0][0]; part[g + 8][0] = o[1][0]; }
+        } else {
+            float o[2][2];
+            warp_tile_spread<WF, 2, false>(tile, sc, ngroups, ks, KS, lane, xr, xsrow[0], xsrow[1], k, o);
+            if (t == 0) {
+                part[g][0] = o[0][0]; part[g][1] = o[0][1];
+                part[g + 8][0] = o[1][0]; part[g + 8][1] = o[1][1];
+            }
+        }
+    } else {
+        float acc[4];
+        const int ca = 2 * t, cb = 2 * t + 1;
+        warp_tile_batched<WF, false>(tile, sc, ngroups, ks, KS, lane, g < n ? xrow[g] : nullptr, ca < n ? xsrow[ca] : nullptr,
+                                     cb < n ? xsrow[cb] : nullptr, k, acc);
+        part[g][ca] = acc[0]; part[g][cb] = acc[1];
+        part[g + 8][ca] = acc[2]; part[g + 8][cb] = acc[3];
+    }
+}
+
+// ------------------------------------------------------------------ gate / up + activation + q8 of the activation
+// grid = (inter/32, max_items).  CTA: 32 rows of w1 and the same 32 rows of w3 of
+// one expert for <= 8 pairs: warp = (matrix, 16-row half, K half).  Then warp c
+// turns column c into the activation (src/deepseek.rs:1083-1087) and quantizes
+// its 32 values as one q8_0 block (src/q8.rs:49-69): the input of the w2 matvec.
+__global__ void __launch_bounds__(256) moe_gate_up_kernel(const MoeArgs a) {
+    const int item = blockIdx.y;
+    if (item >= *a.n_items) return;
+    const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float part[8][16][8];
+    __shared__ const int8_t *xrow[8];
+    __shared__ const float *xsrow[8];
+    __shared__ int pair_s[8];
+    __shared__ float wgt_s[8];
+    if (threadIdx.x < 8) {
+        const int c = threadIdx.x;
+        const int p = c < n ? a.sorted[off + c] : -1;
+        pair_s[c] = p;
+        const int row = p >= 0 ? a.pair_row[p] : 0;
+        xrow[c] = a.xq + (int64_t)row * a.nbp_d * 32;
+        xsrow[c] = a.xs + (int64_t)row * a.nbp_d;
+        wgt_s[c] = p >= 0 ? a.pair_weight[p] : 0.0f;
+    }
+    __syncthreads();
+    {
+        const int job = warp >> 1, ks = warp & 1;
+        const int mat = (job >> 1) ? 2 : 0, half = job & 1;
+        const int64_t rt = (int64_t)blockIdx.x * 2 + half;
+        const void *wv = a.wv[e * 3 + mat], *ws = a.wsc[e * 3 + mat];
+        warp_tile_any<W_MXFP4>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, 2,
+                               lane, n, xrow, xsrow, a.k, part[warp]);
+    }
+    __syncthreads();
+    const int c = warp; // column
+    if (c < n) {
+        const int half = lane >> 4, r16 = lane & 15;
+        const float gate = part[(0 + half) * 2][r16][c] + part[(0 + half) * 2 + 1][r16][c];
+        const float up = part[(2 + half) * 2][r16][c] + part[(2 + half) * 2 + 1][r16][c];
+        const float gl = fminf(gate, a.limit);
+        const float ul = fminf(fmaxf(up, -a.limit), a.limit);
+        const float ex = (float)exp((double)(-gl));
+        const float silu = __fdiv_rn(gl, __fadd_rn(1.0f, ex));
+        const float act = __fmul_rn(__fmul_rn(wgt_s[c], silu), ul);
+        float mx = fabsf(act);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        const float dx = __fdiv_rn(mx, 127.0f);
+        int q = 0;
+        if (dx != 0.0f) q = (int)fminf(fmaxf(roundf(__fdiv_rn(act, dx)), -127.0f), 127.0f);
+        const int p = pair_s[c];
+        a.actq[(int64_t)p * a.nbp_i * 32 + (int64_t)blockIdx.x * 32 + lane] = (int8_t)q;
+        if (lane == 0) a.acts[(int64_t)p * a.nbp_i + blockIdx.x] = dx;
+    }
+}
+
+// ------------------------------------------------------------------ down projection
+// grid = (ceil(d/32), max_items).  CTA: 2 row tiles of w2 x 4 K slices.
+__global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
+    const int item = blockIdx.y;
+    if (item >= *a.n_items) return;
+    const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float part[8][16][8];
+    __shared__ const int8_t *xrow[8];
+    __shared__ const float *xsrow[8];
+    __shared__ int pair_s[8];
+    if (threadIdx.x < 8) {
+        const int c = threadIdx.x;
+        const int p = c < n ? a.sorted[off + c] : -1;
+        pair_s[c] = p;
+        const int pp = p >= 0 ? p : 0;
+        xrow[c] = a.actq + (int64_t)pp * a.nbp_i * 32;
+        xsrow[c] = a.acts + (int64_t)pp * a.nbp_i;
+    }
+    __syncthreads();
+    const int64_t nrt = (a.d + 15) >> 4;
+    const int rt_local = warp >> 2, ks = warp & 3;
+    const int64_t rt = (int64_t)blockIdx.x * 2 + rt_local;
+    if (rt < nrt) {
+        const void *wv = a.wv[e * 3 + 1], *ws = a.wsc[e * 3 + 1];
+        warp_tile_any<W_MXFP4>(tile_values<W_MXFP4>(wv, rt, a.nbp_i), tile_scales<W_MXFP4>(ws, rt, a.nbp_i), a.nbp_i >> 2, ks, 4,
+                               lane, n, xrow, xsrow, a.k, part[warp]);
+    }
+    __syncthreads();
+    // 2 tiles x 16 rows x 8 columns = 256 outputs, one per thread
+    const int tl = threadIdx.x >> 7, r16 = (threadIdx.x >> 3) & 15, c = threadIdx.x & 7;
+    const int64_t row = ((int64_t)blockIdx.x * 2 + tl) * 16 + r16;
+    if (c < n && row < a.d) {
+        const float v = ((part[tl * 4 + 0][r16][c] + part[tl * 4 + 1][r16][c]) + part[tl * 4 + 2][r16][c]) + part[tl * 4 + 3][r16][c];
+        a.outs[(int64_t)pair_s[c] * a.d + row] = v;
+    }
+}
+
+// out[t][j] = ((0 + outs[t,0][j]) + outs[t,1][j]) + ... in slot order (src/deepseek.rs:1095-1106)
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ outs, int n_tokens, int slots, int d,
+                                                         float *__restrict__ out) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)n_tokens * d) return;
+    const int64_t t = idx / d, j = idx % d;
+    float v = 0.0f;
+    for (int s = 0; s < slots; ++s) v = __fadd_rn(v, outs[(t * slots + s) * d + j]);
+    out[idx] = v;
+}
+
+} // namespace
+
+// ====================================================================== host side
+#include <new>
+#include <vector>
+
+static void moe_free_ws(mk_moe *m) {
+    void *ptrs[] = {m->logits, m->ids, m->wts, m->xq, m->xs, m->pair_row, m->pair_expert, m->pair_weight,
+                    m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs};
+    for (void *p : ptrs) if (p) cudaFree(p);
+    m->logits = nullptr; m->ids = nullptr; m->wts = nullptr; m->xq = nullptr; m->xs = nullptr;
+    m->pair_row = m->pair_expert = nullptr; m->pair_weight = nullptr; m->sorted = m->items = m->n_items = nullptr;
+    m->actq = nullptr; m->acts = nullptr; m->outs = nullptr;
+    m->cap_rows = m->cap_pairs = 0;
+}
+
+// (Re)allocates the per-call buffers for `rows` activation rows and `pairs` pairs.
+// Grows geometrically; steady-state calls allocate nothing.
+static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
+    if (rows <= m->cap_rows && pairs <= m->cap_pairs) return MK_OK;
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    int nr = m->cap_rows > 0 ? m->cap_rows : 1, np = m->cap_pairs > 0 ? m->cap_pairs : 1;
+    while (nr < rows) nr *= 2;
+    while (np < pairs) np *= 2;
+    moe_free_ws(m);
+    const int E = m->n_experts, k = m->top_k;
+    m->max_items = np / 8 + (np < E + 1 ? np : E + 1) + 1;
+    const size_t ldq_d = (size_t)m->nbp_d * 32, ldq_i = (size_t)m->nbp_i * 32;
+    MK_CUDA(cudaMalloc(&m->logits, (size_t)nr * E * 4));
+    MK_CUDA(cudaMalloc(&m->ids, (size_t)nr * k * 4));
+    MK_CUDA(cudaMalloc(&m->wts, (size_t)nr * k * 4));
+    MK_CUDA(cudaMalloc(&m->xq, (size_t)nr * ldq_d));
+    MK_CUDA(cudaMalloc(&m->xs, (size_t)nr * m->nbp_d * 4));
+    MK_CUDA(cudaMalloc(&m->pair_row, (size_t)np * 4));
+    MK_CUDA(cudaMalloc(&m->pair_expert, (size_t)np * 4));
+    MK_CUDA(cudaMalloc(&m->pair_weight, (size_t)np * 4));
+    MK_CUDA(cudaMalloc(&m->sorted, (size_t)np * 4));
+    MK_CUDA(cudaMalloc(&m->items, (size_t)m->max_items * 3 * 4));
+    MK_CUDA(cudaMalloc(&m->n_items, 4));
+    MK_CUDA(cudaMalloc(&m->actq, (size_t)np * ldq_i));
+    MK_CUDA(cudaMalloc(&m->acts, (size_t)np * m->nbp_i * 4));
+    MK_CUDA(cudaMalloc(&m->outs, (size_t)np * m->d * 4));
+    // padded tails of the q8 rows must read as zero
+    MK_CUDA(cudaMemsetAsync(m->actq, 0, (size_t)np * ldq_i, ctx->stream));
+    MK_CUDA(cudaMemsetAsync(m->acts, 0, (size_t)np * m->nbp_i * 4, ctx->stream));
+    m->cap_rows = nr;
+    m->cap_pairs = np;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out) {
+    MK_CHECK_ARG(ctx != nullptr && desc != nullptr && out != nullptr, "NULL argument");
+    *out = nullptr;
+    const int E = desc->n_experts, k = desc->top_k, d = desc->d, I = desc->inter;
+    MK_CHECK_ARG(E >= 1 && E <= 4095 && k >= 1 && k <= 31 && k <= E, "need 1 <= top_k <= min(31, n_experts) and n_experts <= 4095");
+    MK_CHECK_ARG(d > 0 && d % 32 == 0 && I > 0 && I % 32 == 0, "d and inter must be positive multiples of 32");
+    MK_CHECK_ARG(desc->activation == MK_MOE_SWIGLU_CLAMP, "unknown activation");
+    MK_CHECK_ARG(desc->experts != nullptr, "experts table is NULL");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    std::vector<const void *> hv((size_t)(E + 1) * 3, nullptr), hs((size_t)(E + 1) * 3, nullptr);
+    auto check = [&](const mk_weight *w, int rows, int cols) {
+        return w && w->fmt == MK_FMT_MXFP4 && w->rows == rows && w->cols == cols;
+    };
+    for (int e = 0; e <= E; ++e) {
+        const mk_weight *t[3];
+        for (int j = 0; j < 3; ++j) t[j] = e < E ? desc->experts[(size_t)e * 3 + j] : desc->shared[j];
+        if (!t[0] && !t[1] && !t[2]) continue;
+        if (!check(t[0], I, d) || !check(t[1], d, I) || !check(t[2], I, d)) {
+            mk_set_error("mk_moe_create: expert %d needs MXFP4 w1 [inter,d], w2 [d,inter], w3 [inter,d]", e);
+            return MK_ERR_ARG;
+        }
+        for (int j = 0; j < 3; ++j) {
+            hv[(size_t)e * 3 + j] = t[j]->values;
+            hs[(size_t)e * 3 + j] = t[j]->scales;
+        }
+    }
+    mk_moe *m = new (std::nothrow) mk_moe();
+    if (!m) return MK_ERR_OOM;
+    memset(m, 0, sizeof(*m));
+    m->n_experts = E; m->top_k = k; m->d = d; m->inter = I; m->activation = desc->activation;
+    m->limit = desc->swiglu_limit;
+    m->has_router = desc->gate_w != nullptr;
+    m->has_shared = hv[(size_t)E * 3] != nullptr;
+    m->nbp_d = mk_ceil_div(d / 32, 4) * 4;
+    m->nbp_i = mk_ceil_div(I / 32, 4) * 4;
+    cudaError_t e_ = cudaSuccess;
+    const size_t tb = hv.size() * sizeof(void *);
+    e_ = cudaMalloc((void **)&m->wv, tb);
+    if (e_ == cudaSuccess) e_ = cudaMalloc((void **)&m->wsc, tb);
+    if (e_ == cudaSuccess) e_ = cudaMemcpyAsync((void *)m->wv, hv.data(), tb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e_ == cudaSuccess) e_ = cudaMemcpyAsync((void *)m->wsc, hs.data(), tb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e_ == cudaSuccess && m->has_router) {
+        e_ = cudaMalloc(&m->gate_w, (size_t)E * d * 4);
+        if (e_ == cudaSuccess) e_ = cudaMalloc(&m->gate_b, (size_t)E * 4);
+        if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->gate_w, desc->gate_w, (size_t)E * d * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e_ == cudaSuccess) {
+            if (desc->gate_b) e_ = cudaMemcpyAsync(m->gate_b, desc->gate_b, (size_t)E * 4, cudaMemcpyHostToDevice, ctx->stream);
+            else e_ = cudaMemsetAsync(m->gate_b, 0, (size_t)E * 4, ctx->stream);
+        }
+    }
+    if (e_ == cudaSuccess) e_ = cudaStreamSynchronize(ctx->stream);
+    if (e_ != cudaSuccess) {
+        mk_set_error("mk_moe_create: %s", cudaGetErrorString(e_));
+        mk_moe_free(ctx, m);
+        return e_ == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA;
+    }
+    *out = m;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_free(mk_ctx *ctx, mk_moe *m) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr, "NULL argument");
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    moe_free_ws(m);
+    if (m->wv) cudaFree((void *)m->wv);
+    if (m->wsc) cudaFree((void *)m->wsc);
+    if (m->gate_w) cudaFree(m->gate_w);
+    if (m->gate_b) cudaFree(m->gate_b);
+    delete m;
+    return MK_OK;
+}
+
+// router logits + top-k on device rows x [n][d]; fills m->ids / m->wts (and the
+// forward pair list when with_pairs).
+static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, bool with_pairs) {
+    const int E = m->n_experts;
+    {
+        mk_prof_scope prof(ctx, MK_PROF_ROUTER);
+        const int ewarps = (E + 3) / 4;
+        if (n >= 4) {
+            const int64_t warps = (int64_t)ewarps * mk_ceil_div(n, 4);
+            moe_router_logits_kernel<4><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+        } else {
+            const int64_t warps = (int64_t)ewarps * n;
+            moe_router_logits_kernel<1><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+        }
+        const size_t smem = (size_t)4 * 2 * E * sizeof(float);
+        moe_topk_kernel<<<(unsigned)mk_ceil_div(n, 4), 128, smem, ctx->stream>>>(
+            m->logits, m->gate_b, E, m->top_k, n, m->ids, m->wts, with_pairs ? m->pair_row : nullptr, m->pair_expert,
+            m->pair_weight, m->has_shared ? 1 : 0);
+        ctx->launches += 2;
+    }
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+// grouped experts over an explicit pair list (device arrays); x rows already on device
+static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_rows, const int32_t *pair_row,
+                                  const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs) {
+    int32_t rc = mk_launch_quantize_act(ctx, x, n_rows, m->d, m->d, m->nbp_d, 0, m->xq, m->xs);
+    if (rc != MK_OK) return rc;
+    mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
+    const int slots = m->n_experts + 1;
+    moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted,
+                                                                              m->items, m->n_items, m->max_items, ctx->status_dev);
+    MoeArgs a;
+    a.wv = m->wv; a.wsc = m->wsc; a.items = m->items; a.n_items = m->n_items; a.sorted = m->sorted;
+    a.pair_row = pair_row; a.pair_weight = pair_weight; a.xq = m->xq; a.xs = m->xs; a.actq = m->actq; a.acts = m->acts;
+    a.outs = outs; a.nbp_d = m->nbp_d; a.nbp_i = m->nbp_i; a.d = m->d; a.inter = m->inter; a.limit = m->limit;
+    a.k = Consts{65536u, 0xFFFFFFFFu, ctx->zeros_dev};
+    // an upper bound on the work items of this call (the kernels exit early past *n_items)
+    int items_ub = n_pairs / 8 + (n_pairs < slots ? n_pairs : slots);
+    if (items_ub > m->max_items) items_ub = m->max_items;
+    if (items_ub < 1) items_ub = 1;
+    moe_gate_up_kernel<<<dim3((unsigned)(m->inter / 32), (unsigned)items_ub), 256, 0, ctx->stream>>>(a);
+    moe_down_kernel<<<dim3((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub), 256, 0, ctx->stream>>>(a);
+    ctx->launches += 3;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_combine_dev(mk_ctx *ctx, const float *outs, int32_t n_tokens, int32_t slots, int32_t d, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && outs != nullptr && out != nullptr && n_tokens > 0 && slots > 0 && d > 0, "bad argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
+    moe_combine_kernel<<<(unsigned)mk_ceil_div((int64_t)n_tokens * d, 256), 256, 0, ctx->stream>>>(outs, n_tokens, slots, d, out);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_route_dev(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, int32_t *ids, float *weights, float *logits) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && n > 0, "bad argument");
+    MK_CHECK_ARG(m->has_router, "this MoE object was created without a router");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = moe_reserve(ctx, m, n, n * (m->top_k + 1));
+    if (rc != MK_OK) return rc;
+    rc = moe_route_launch(ctx, m, x, n, false);
+    if (rc != MK_OK) return rc;
+    if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (logits) MK_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)n * m->n_experts * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_experts_dev(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n_rows, const int32_t *pair_row,
+                                      const int32_t *pair_expert, const float *pair_weight, int32_t n_pairs, float *outs) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && pair_row != nullptr && pair_expert != nullptr &&
+                     pair_weight != nullptr && outs != nullptr, "NULL argument");
+    MK_CHECK_ARG(n_rows > 0 && n_pairs > 0, "n_rows and n_pairs must be positive");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = moe_reserve(ctx, m, n_rows, n_pairs);
+    if (rc != MK_OK) return rc;
+    return moe_experts_launch(ctx, m, x, n_rows, pair_row, pair_expert, pair_weight, n_pairs, outs);
+}
+
+extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && out != nullptr && n > 0, "bad argument");
+    MK_CHECK_ARG(m->has_router, "this MoE object was created without a router");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const int slots = m->top_k + (m->has_shared ? 1 : 0);
+    int32_t rc = moe_reserve(ctx, m, n, n * slots);
+    if (rc != MK_OK) return rc;
+    rc = moe_route_launch(ctx, m, x, n, true);
+    if (rc != MK_OK) return rc;
+    rc = moe_experts_launch(ctx, m, x, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, m->outs);
+    if (rc != MK_OK) return rc;
+    rc = mk_moe_combine_dev(ctx, m->outs, n, slots, m->d, out);
+    if (rc != MK_OK) return rc;
+    if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return MK_OK;
+}
+
+// host-pointer variants: stage through the context's device buffer
+extern "C" int32_t mk_moe_route(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, int32_t *ids, float *weights, float *logits) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && n > 0, "bad argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const size_t xb = (size_t)n * m->d * 4;
+    int32_t rc = mk_io_reserve(ctx, mk_align_up(xb, 256));
+    if (rc != MK_OK) return rc;
+    MK_CUDA(cudaMemcpyAsync(ctx->io_dev, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = mk_moe_route_dev(ctx, m, (const float *)ctx->io_dev, n, nullptr, nullptr, nullptr);
+    if (rc != MK_OK) return rc;
+    if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (logits) MK_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)n * m->n_experts * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_forward(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && out != nullptr && n > 0, "bad argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const size_t xb = mk_align_up((size_t)n * m->d * 4, 256);
+    int32_t rc = mk_io_reserve(ctx, 2 * xb);
+    if (rc != MK_OK) return rc;
+    float *dx = (float *)ctx->io_dev, *dout = (float *)((char *)ctx->io_dev + xb);
+    MK_CUDA(cudaMemcpyAsync(dx, x, (size_t)n * m->d * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = mk_moe_forward_dev(ctx, m, dx, n, dout, nullptr, nullptr);
+    if (rc != MK_OK) return rc;
+    MK_CUDA(cudaMemcpyAsync(out, dout, (size_t)n * m->d * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}

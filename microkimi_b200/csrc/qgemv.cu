@@ -33,7 +33,7 @@ template <int WF, int KS, int NSLOT, bool X2>
 __global__ void __launch_bounds__(256)
 qgemv_spread_kernel(const void *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
                     const float *__restrict__ xs, int64_t ldq, int64_t nbp, float *__restrict__ y, int64_t ldy,
-                    int64_t rows, int64_t nrt) {
+                    int64_t rows, int64_t nrt, const Consts k) {
     constexpr int RT = 8 / KS;
     constexpr int NOUT = X2 ? 1 : NSLOT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -47,7 +47,7 @@ qgemv_spread_kernel(const void *__restrict__ wt, const void *__restrict__ wscale
         const int slot = g & 1;
         const int8_t *xrow = slot < NSLOT ? xq + (int64_t)slot * ldq : nullptr;
         warp_tile_spread<WF, NSLOT, X2>(tile_values<WF>(wt, rt, nbp), tile_scales<WF>(wscale, rt, nbp), nbp >> 2, ks, KS,
-                                        lane, xrow, xs, xs + nbp, acc);
+                                        lane, xrow, xs, xs + nbp, k, acc);
     }
     if constexpr (KS > 1) {
         __shared__ float red[8][16][NOUT];
@@ -93,7 +93,7 @@ template <int WF, int KS, bool X2>
 __global__ void __launch_bounds__(256)
 qgemv_batched_kernel(const void *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
                      const float *__restrict__ xs, int64_t ldq, int64_t nbp, int ntok, float *__restrict__ y,
-                     int64_t ldy, int64_t rows, int64_t nrt) {
+                     int64_t ldy, int64_t rows, int64_t nrt, const Consts k) {
     constexpr int RT = 8 / KS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -107,7 +107,7 @@ qgemv_batched_kernel(const void *__restrict__ wt, const void *__restrict__ wscal
         const float *xsa = tok_a < ntok ? xs + (int64_t)tok_a * nbp : nullptr;
         const float *xsb = tok_b < ntok ? xs + (int64_t)tok_b * nbp : nullptr;
         warp_tile_batched<WF, X2>(tile_values<WF>(wt, rt, nbp), tile_scales<WF>(wscale, rt, nbp), nbp >> 2, ks, KS, lane,
-                                  xcol, xsa, xsb, acc);
+                                  xcol, xsa, xsb, k, acc);
     }
     if constexpr (KS > 1) {
         __shared__ float red[8][32][4];
@@ -244,38 +244,38 @@ __global__ void __launch_bounds__(128) argmax_final_kernel(const float *__restri
 
 // ------------------------------------------------------------------ dispatch
 template <int WF, int KS>
-void launch_spread(const mk_weight *w, cudaStream_t st, const int8_t *xq, const float *xs, int nslot, bool x2, float *y,
+void launch_spread(const mk_weight *w, cudaStream_t st, const Consts &k, const int8_t *xq, const float *xs, int nslot, bool x2, float *y,
                    int64_t ldy) {
     constexpr int RT = 8 / KS;
     const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
     const int64_t ldq = w->nbp * 32;
     const void *wt = w->values;
     if (x2)
-        qgemv_spread_kernel<WF, KS, 2, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
+        qgemv_spread_kernel<WF, KS, 2, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt, k);
     else if (nslot == 2)
-        qgemv_spread_kernel<WF, KS, 2, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
+        qgemv_spread_kernel<WF, KS, 2, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt, k);
     else
-        qgemv_spread_kernel<WF, KS, 1, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt);
+        qgemv_spread_kernel<WF, KS, 1, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt, k);
 }
 template <int WF, int KS>
-void launch_batched(const mk_weight *w, cudaStream_t st, const int8_t *xq, const float *xs, int ntok, bool x2, float *y,
+void launch_batched(const mk_weight *w, cudaStream_t st, const Consts &k, const int8_t *xq, const float *xs, int ntok, bool x2, float *y,
                     int64_t ldy) {
     constexpr int RT = 8 / KS;
     const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
     const int64_t ldq = w->nbp * 32;
     const void *wt = w->values;
     if (x2)
-        qgemv_batched_kernel<WF, KS, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt);
+        qgemv_batched_kernel<WF, KS, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
     else
-        qgemv_batched_kernel<WF, KS, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt);
+        qgemv_batched_kernel<WF, KS, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
 }
 template <int WF>
-void launch_wf(const mk_weight *w, cudaStream_t st, int ks, bool spread, const int8_t *xq, const float *xs, int ntok,
+void launch_wf(const mk_weight *w, cudaStream_t st, const Consts &k, int ks, bool spread, const int8_t *xq, const float *xs, int ntok,
                bool x2, float *y, int64_t ldy) {
 #define MK_KS_CASE(K)                                                         \
     case K:                                                                   \
-        if (spread) launch_spread<WF, K>(w, st, xq, xs, ntok, x2, y, ldy);    \
-        else launch_batched<WF, K>(w, st, xq, xs, ntok, x2, y, ldy);          \
+        if (spread) launch_spread<WF, K>(w, st, k, xq, xs, ntok, x2, y, ldy);    \
+        else launch_batched<WF, K>(w, st, k, xq, xs, ntok, x2, y, ldy);          \
         break;
     switch (ks) {
         MK_KS_CASE(1)
@@ -324,10 +324,11 @@ int32_t mk_launch_qgemv(mk_ctx *ctx, const mk_weight *w, const int8_t *xq, const
     const int ks = pick_ks(ctx, w, strict != 0);
     const int wf = w->fmt == MK_FMT_MXFP4 ? W_MXFP4 : (w->scale_type == MK_SCALE_F16 ? W_Q8_F16 : W_Q8_F32);
     mk_prof_scope prof(ctx, w->fmt == MK_FMT_MXFP4 ? MK_PROF_MATVEC_MXFP4 : MK_PROF_LM_HEAD);
+    const Consts k = {65536u, 0xFFFFFFFFu, ctx->zeros_dev};
     switch (wf) {
-    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
-    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
-    default: launch_wf<W_Q8_F16>(w, ctx->stream, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, k, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, k, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    default: launch_wf<W_Q8_F16>(w, ctx->stream, k, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
     }
     ctx->launches++;
     MK_CUDA(cudaGetLastError());

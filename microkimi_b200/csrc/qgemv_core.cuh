@@ -44,18 +44,57 @@ __device__ __forceinline__ void load_group(Group<WF> &g, const uint4 *tile_base,
     for (int c = 0; c < C; ++c) g.a[c] = mk_ldg_stream(p + c * 32);
 }
 
-// int32 block dots of block m (0..3) of a group, accumulated into cp (and cn for MXFP4)
+// Values the kernels receive as launch arguments so that the compiler keeps the
+// shift and the bitwise NOT below as integer multiply-adds, which issue on the
+// FMA pipe: the ALU pipe, which executes the byte permutes, is the bottleneck of
+// the MXFP4 decode.  k16 = 65536 (x >> 16 == mulhi(x, k16)), km1 = 0xFFFFFFFF
+// (~x == x * km1 + km1).  zeros: >= 16 zero bytes of device memory.
+#ifndef MK_DEC
+#define MK_DEC 1      // 0: xor + shifts on the ALU pipe; 1: NOT as a multiply-add (measured fastest); 2: NOT and shifts as multiply-adds
+#endif
+#ifndef MK_BZERO
+#define MK_BZERO 0    // B operand of foreign MMA columns: 0 = AND with a lane mask, 1 = load from a page of zeros
+#endif
+struct Consts {
+    uint32_t k16, km1;
+    const int8_t *zeros;
+};
+// E2M1 x 2 magnitudes in reverse order, bytes {12,8,6,4} and {3,2,1,0}: indexed by
+// the complemented magnitude bits of a complemented word.
+#define MK_LUT2R_LO 0x0406080Cu
+#define MK_LUT2R_HI 0x00010203u
+
+// int32 block dots of block m (0..3) of a group, accumulated into cp (and cn for MXFP4).
+// Positive part: selector nibbles with the sign bit set read as 0.  Negative part:
+// the same permute over ~w with the reversed table (sign bit cleared <=> negative).
 template <int WF>
-__device__ __forceinline__ void block_mma(const Group<WF> &g, int m, uint32_t b0, uint32_t b1, int (&cp)[4], int (&cn)[4]) {
+__device__ __forceinline__ void block_mma(const Group<WF> &g, int m, uint32_t b0, uint32_t b1, int (&cp)[4], int (&cn)[4],
+                                          const Consts &k) {
     if constexpr (WF == W_MXFP4) {
         const uint4 &ch = g.a[m >> 1];
         const uint32_t wg = (m & 1) ? ch.z : ch.x; // row g
         const uint32_t wh = (m & 1) ? ch.w : ch.y; // row g+8
+#if MK_DEC == 0
         const uint32_t wgx = wg ^ 0x88888888u, whx = wh ^ 0x88888888u;
         mk_mma_s8(cp, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh),
                   mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh >> 16), b0, b1);
         mk_mma_s8(cn, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx),
                   mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wgx >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, whx >> 16), b0, b1);
+#elif MK_DEC == 1
+        const uint32_t wgn = wg * k.km1 + k.km1, whn = wh * k.km1 + k.km1;
+        mk_mma_s8(cp, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh),
+                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg >> 16), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh >> 16), b0, b1);
+        mk_mma_s8(cn, mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, wgn), mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, whn),
+                  mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, wgn >> 16), mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, whn >> 16), b0, b1);
+#else
+        const uint32_t wgn = wg * k.km1 + k.km1, whn = wh * k.km1 + k.km1;
+        mk_mma_s8(cp, mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wg), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, wh),
+                  mk_prmt(MK_LUT2_LO, MK_LUT2_HI, __umulhi(wg, k.k16)), mk_prmt(MK_LUT2_LO, MK_LUT2_HI, __umulhi(wh, k.k16)),
+                  b0, b1);
+        mk_mma_s8(cn, mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, wgn), mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, whn),
+                  mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, __umulhi(wgn, k.k16)),
+                  mk_prmt(MK_LUT2R_LO, MK_LUT2R_HI, __umulhi(whn, k.k16)), b0, b1);
+#endif
     } else {
         const uint4 &ch = g.a[m];
         mk_mma_s8(cp, ch.x, ch.y, ch.z, ch.w, b0, b1);
@@ -97,30 +136,45 @@ template <int WF, int NSLOT, bool X2>
 __device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile, const void *__restrict__ sc, int64_t ngroups,
                                                  int ks, int KS, int lane, const int8_t *__restrict__ xrow,
                                                  const float *__restrict__ xs0, const float *__restrict__ xs1,
-                                                 float (&out)[2][X2 ? 1 : NSLOT]) {
+                                                 const Consts &k, float (&out)[2][X2 ? 1 : NSLOT]) {
     constexpr int NOUT = X2 ? 1 : NSLOT;
     const int g = lane >> 2, t = lane & 3;
     const int sub = g >> 1;
     float acc[2][NOUT];
 #pragma unroll
     for (int o = 0; o < NOUT; ++o) acc[0][o] = acc[1][o] = 0.0f;
+    // B operand of block m of a group: the real activation bytes in the lanes whose
+    // column belongs to block m, a page of zeros (stride 0) in all other lanes
+#if MK_BZERO
+    const int8_t *xb[4];
+    uint32_t xstep[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const bool real = (sub == m) && (xrow != nullptr);
+        xb[m] = real ? xrow + m * 32 + t * 8 : k.zeros;
+        xstep[m] = real ? 128u : 0u;
+    }
+#else
     const bool xvalid = xrow != nullptr;
-    const int8_t *xp = xrow + sub * 32 + t * 8;
+    const int8_t *xp = xvalid ? xrow + sub * 32 + t * 8 : k.zeros;
+    const uint32_t xstep1 = xvalid ? 128u : 0u;
     uint32_t mask[4];
 #pragma unroll
     for (int m = 0; m < 4; ++m) mask[m] = (sub == m && xvalid) ? 0xFFFFFFFFu : 0u;
-
-    Group<WF> cur, nxt;
-    int64_t i = ks;
-    if (i < ngroups) load_group<WF>(cur, tile, i, lane);
-    for (; i < ngroups; i += KS) {
-        const int64_t inext = i + KS;
-        if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
-        uint2 xv = make_uint2(0u, 0u);
-        if (xvalid) xv = __ldg((const uint2 *)(xp + i * 128));
+#endif
+    auto process = [&](const Group<WF> &grp, int64_t i) {
         int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+#if MK_BZERO
 #pragma unroll
-        for (int m = 0; m < 4; ++m) block_mma<WF>(cur, m, xv.x & mask[m], xv.y & mask[m], cp, cn);
+        for (int m = 0; m < 4; ++m) {
+            const uint2 xv = __ldg((const uint2 *)(xb[m] + (uint64_t)((uint32_t)i * xstep[m])));
+            block_mma<WF>(grp, m, xv.x, xv.y, cp, cn, k);
+        }
+#else
+        const uint2 xv = __ldg((const uint2 *)(xp + (uint64_t)((uint32_t)i * xstep1)));
+#pragma unroll
+        for (int m = 0; m < 4; ++m) block_mma<WF>(grp, m, xv.x & mask[m], xv.y & mask[m], cp, cn, k);
+#endif
         // lane t now holds block 4i+t: c0/c1 = row g (slot 0/1), c2/c3 = row g+8
         const int64_t b = i * 4 + t;
         float sg, sh;
@@ -141,7 +195,20 @@ __device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile,
                 acc[1][1] = acc_term(acc[1][1], d3, sh, sx1);
             }
         }
-        cur = nxt;
+    };
+    // two register buffers, alternating: the next group is in flight while one is consumed
+    Group<WF> ga, gb;
+    int64_t i = ks;
+    if (i < ngroups) load_group<WF>(ga, tile, i, lane);
+    while (i < ngroups) {
+        const int64_t i1 = i + KS;
+        if (i1 < ngroups) load_group<WF>(gb, tile, i1, lane);
+        process(ga, i);
+        if (i1 >= ngroups) break;
+        const int64_t i2 = i1 + KS;
+        if (i2 < ngroups) load_group<WF>(ga, tile, i2, lane);
+        process(gb, i1);
+        i = i2;
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h)
@@ -163,24 +230,19 @@ template <int WF, bool X2>
 __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile, const void *__restrict__ sc, int64_t ngroups,
                                                   int ks, int KS, int lane, const int8_t *__restrict__ xcol,
                                                   const float *__restrict__ xs_a, const float *__restrict__ xs_b,
-                                                  float (&acc)[4]) {
+                                                  const Consts &k, float (&acc)[4]) {
     const int g = lane >> 2, t = lane & 3;
     acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
     const bool xvalid = xcol != nullptr;
-    const int8_t *xp = xcol + t * 8;
-    Group<WF> cur, nxt;
-    int64_t i = ks;
-    if (i < ngroups) load_group<WF>(cur, tile, i, lane);
-    for (; i < ngroups; i += KS) {
-        const int64_t inext = i + KS;
-        if (inext < ngroups) load_group<WF>(nxt, tile, inext, lane);
+    const int8_t *xp = xvalid ? xcol + t * 8 : k.zeros;
+    const uint32_t xstep = xvalid ? 32u : 0u;
+    auto process = [&](const Group<WF> &grp, int64_t i) {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
             const int64_t b = i * 4 + m;
-            uint2 xv = make_uint2(0u, 0u);
-            if (xvalid) xv = __ldg((const uint2 *)(xp + b * 32));
+            const uint2 xv = __ldg((const uint2 *)(xp + (uint64_t)((uint32_t)b * xstep)));
             int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
-            block_mma<WF>(cur, m, xv.x, xv.y, cp, cn);
+            block_mma<WF>(grp, m, xv.x, xv.y, cp, cn, k);
             float sg, sh;
             load_wscale<WF>(sc, b, g, sg, sh);
             int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
@@ -198,7 +260,19 @@ __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile
                 acc[3] = acc_term(acc[3], d3, sh, sxb);
             }
         }
-        cur = nxt;
+    };
+    Group<WF> ga, gb;
+    int64_t i = ks;
+    if (i < ngroups) load_group<WF>(ga, tile, i, lane);
+    while (i < ngroups) {
+        const int64_t i1 = i + KS;
+        if (i1 < ngroups) load_group<WF>(gb, tile, i1, lane);
+        process(ga, i);
+        if (i1 >= ngroups) break;
+        const int64_t i2 = i1 + KS;
+        if (i2 < ngroups) load_group<WF>(ga, tile, i2, lane);
+        process(gb, i1);
+        i = i2;
     }
 }
 

@@ -29,6 +29,13 @@ _vp = C.c_void_p
 _i32 = C.c_int32
 _i64 = C.c_int64
 
+class MoeDesc(C.Structure):
+    """mk_moe_desc"""
+    _fields_ = [("n_experts", _i32), ("top_k", _i32), ("d", _i32), ("inter", _i32),
+                ("swiglu_limit", C.c_float), ("activation", _i32),
+                ("gate_w", _vp), ("gate_b", _vp), ("experts", C.POINTER(_vp)), ("shared", _vp * 3)]
+
+
 # name -> (restype, argtypes); every symbol include/mk_cuda.h declares
 SIGNATURES = {
     "mk_init": (_i32, [_i32, C.POINTER(_vp)]),
@@ -54,6 +61,14 @@ SIGNATURES = {
     "mk_matvec_mxfp4_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_q8": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_matvec_q8_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "mk_moe_create": (_i32, [_vp, C.POINTER(MoeDesc), C.POINTER(_vp)]),
+    "mk_moe_free": (_i32, [_vp, _vp]),
+    "mk_moe_route": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "mk_moe_route_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "mk_moe_forward": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "mk_moe_forward_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "mk_moe_experts_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp]),
+    "mk_moe_combine_dev": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
 }
 
 

@@ -243,6 +243,110 @@ class Q8Head(_Weight):
         return q, s
 
 
+class MoeLayer:
+    """One MoE layer resident on the GPU: the noaux_tc router of moe_forward
+    (src/model.rs:2153-2173) feeding MXFP4 experts with the SwiGLU-clamp body of ds_moe
+    (src/deepseek.rs:1038-1108), plus one unweighted shared expert.
+
+    experts: list over expert ids of (w1, w2, w3) MxFp4Weight triples, or None for an
+    expert that lives on another GPU (expert parallel); shared: one triple or None.
+    """
+
+    def __init__(self, gate_w, gate_b, experts, shared, top_k, swiglu_limit=10.0, ctx=None):
+        ctx = ctx or Context.default()
+        self.ctx = ctx
+        self.n_experts = len(experts)
+        self.top_k = int(top_k)
+        first = next(t for t in list(experts) + [shared] if t is not None)
+        self.inter, self.d = first[0].rows, first[0].cols
+        self.has_shared = shared is not None
+        self._keep = (experts, shared)
+        tbl = (C.c_void_p * (3 * self.n_experts))()
+        for e, tri in enumerate(experts):
+            for j in range(3):
+                tbl[3 * e + j] = tri[j]._h if tri is not None else None
+        desc = _l.MoeDesc()
+        desc.n_experts, desc.top_k, desc.d, desc.inter = self.n_experts, self.top_k, self.d, self.inter
+        desc.swiglu_limit, desc.activation = float(swiglu_limit), 0
+        if gate_w is not None:
+            gw = np.ascontiguousarray(gate_w, dtype=np.float32)
+            assert gw.shape == (self.n_experts, self.d)
+            gb = np.ascontiguousarray(gate_b if gate_b is not None else np.zeros(self.n_experts), dtype=np.float32)
+            desc.gate_w, desc.gate_b = _np_ptr(gw), _np_ptr(gb)
+        desc.experts = C.cast(tbl, C.POINTER(C.c_void_p))
+        for j in range(3):
+            desc.shared[j] = shared[j]._h if shared is not None else None
+        h = C.c_void_p()
+        _l.check(ctx._L.mk_moe_create(ctx._h, C.byref(desc), C.byref(h)))
+        self._h = h
+
+    def free(self):
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._L.mk_moe_free(self.ctx._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def route(self, x, want_logits=False):
+        """Router only: (ids [n, top_k] int32, weights [n, top_k] f32[, logits [n, E]])."""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.d)
+        n = x.shape[0]
+        ids = np.empty((n, self.top_k), np.int32)
+        w = np.empty((n, self.top_k), np.float32)
+        lg = np.empty((n, self.n_experts), np.float32) if want_logits else None
+        _l.check(self.ctx._L.mk_moe_route(self.ctx._h, self._h, _np_ptr(x), n, _np_ptr(ids), _np_ptr(w),
+                                          _np_ptr(lg) if want_logits else None))
+        return (ids, w, lg) if want_logits else (ids, w)
+
+    def moe_forward(self, x, want_routing=False):
+        """moe_forward / ds_moe for n token rows: x [n, d] (or [d]) -> out of the same shape."""
+        L = self.ctx._L
+        if _is_torch_cuda(x):
+            import torch
+            xs = x.reshape(-1, self.d)
+            assert xs.dtype == torch.float32 and xs.is_contiguous()
+            n = xs.shape[0]
+            out = torch.empty_like(xs)
+            ids = torch.empty((n, self.top_k), dtype=torch.int32, device=x.device) if want_routing else None
+            w = torch.empty((n, self.top_k), dtype=torch.float32, device=x.device) if want_routing else None
+            _l.check(L.mk_moe_forward_dev(self.ctx._h, self._h, C.c_void_p(xs.data_ptr()), n, C.c_void_p(out.data_ptr()),
+                                          C.c_void_p(ids.data_ptr()) if want_routing else None,
+                                          C.c_void_p(w.data_ptr()) if want_routing else None))
+            out = out.reshape(x.shape)
+        else:
+            xa = np.ascontiguousarray(x, dtype=np.float32)
+            xs = xa.reshape(-1, self.d)
+            n = xs.shape[0]
+            out = np.empty_like(xs)
+            ids = np.empty((n, self.top_k), np.int32) if want_routing else None
+            w = np.empty((n, self.top_k), np.float32) if want_routing else None
+            _l.check(L.mk_moe_forward(self.ctx._h, self._h, _np_ptr(xs), n, _np_ptr(out),
+                                      _np_ptr(ids) if want_routing else None, _np_ptr(w) if want_routing else None))
+            out = out.reshape(xa.shape)
+        return (out, ids, w) if want_routing else out
+
+    def experts_dev(self, x, pair_row, pair_expert, pair_weight):
+        """Grouped experts on explicit pairs (torch CUDA tensors): outs [n_pairs, d]."""
+        import torch
+        n_pairs = pair_row.numel()
+        outs = torch.empty((n_pairs, self.d), dtype=torch.float32, device=x.device)
+        _l.check(self.ctx._L.mk_moe_experts_dev(self.ctx._h, self._h, C.c_void_p(x.data_ptr()), x.shape[0],
+                                                C.c_void_p(pair_row.data_ptr()), C.c_void_p(pair_expert.data_ptr()),
+                                                C.c_void_p(pair_weight.data_ptr()), n_pairs, C.c_void_p(outs.data_ptr())))
+        return outs
+
+    def combine_dev(self, outs, n_tokens, slots):
+        import torch
+        out = torch.empty((n_tokens, self.d), dtype=torch.float32, device=outs.device)
+        _l.check(self.ctx._L.mk_moe_combine_dev(self.ctx._h, C.c_void_p(outs.data_ptr()), n_tokens, slots, self.d,
+                                                C.c_void_p(out.data_ptr())))
+        return out
+
+
 def quantize_q8(x, ctx=None):
     """q8::quantize_q8 on the GPU: (q int8 [n], scales f32 [n/32])."""
     ctx = ctx or Context.default()

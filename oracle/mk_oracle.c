@@ -130,7 +130,9 @@ static int search_mx_scale(const float *group, int e) {
 /* mxfp4.rs:94-138 */
 void or_mxfp4_quantize(const float *w, size_t rows, size_t cols, int search, uint8_t *packed, uint8_t *scales) {
     memset(packed, 0, rows * cols / 2);
-    for (size_t r = 0; r < rows; ++r) {
+    /* rows are independent: the split over threads does not change any byte */
+#pragma omp parallel for schedule(static)
+    for (long r = 0; r < (long)rows; ++r) {
         const float *row = w + r * cols;
         for (size_t g = 0; g < cols / 32; ++g) {
             const float *group = row + g * 32;
