@@ -247,7 +247,7 @@ __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc,
     } else {
         float acc[4];
         const int ca = 2 * t, cb = 2 * t + 1;
-        warp_tile_batched<WF, false>(tile, sc, ngroups, ks, KS, lane, g < n ? xrow[g] : nullptr, ca < n ? xsrow[ca] : nullptr,
+        warp_tile_batched<WF, false, false>(tile, sc, ngroups, ks, KS, lane, g < n ? xrow[g] : nullptr, ca < n ? xsrow[ca] : nullptr,
                                      cb < n ? xsrow[cb] : nullptr, k, acc);
         part[g][ca] = acc[0]; part[g][cb] = acc[1];
         part[g + 8][ca] = acc[2]; part[g + 8][cb] = acc[3];

@@ -89,7 +89,7 @@ qgemv_spread_kernel(const void *__restrict__ wt, const void *__restrict__ wscale
 }
 
 // ------------------------------------------------------------------ one matrix, "batched" schedule
-template <int WF, int KS, bool X2>
+template <int WF, int KS, bool X2, bool ORDERED>
 __global__ void __launch_bounds__(256)
 qgemv_batched_kernel(const void *__restrict__ wt, const void *__restrict__ wscale, const int8_t *__restrict__ xq,
                      const float *__restrict__ xs, int64_t ldq, int64_t nbp, int ntok, float *__restrict__ y,
@@ -106,7 +106,7 @@ qgemv_batched_kernel(const void *__restrict__ wt, const void *__restrict__ wscal
         const int8_t *xcol = ctok < ntok ? xq + (X2 ? (int64_t)(g & 1) * ntok * ldq : 0) + (int64_t)ctok * ldq : nullptr;
         const float *xsa = tok_a < ntok ? xs + (int64_t)tok_a * nbp : nullptr;
         const float *xsb = tok_b < ntok ? xs + (int64_t)tok_b * nbp : nullptr;
-        warp_tile_batched<WF, X2>(tile_values<WF>(wt, rt, nbp), tile_scales<WF>(wscale, rt, nbp), nbp >> 2, ks, KS, lane,
+        warp_tile_batched<WF, X2, ORDERED>(tile_values<WF>(wt, rt, nbp), tile_scales<WF>(wscale, rt, nbp), nbp >> 2, ks, KS, lane,
                                   xcol, xsa, xsb, k, acc);
     }
     if constexpr (KS > 1) {
@@ -258,24 +258,33 @@ void launch_spread(const mk_weight *w, cudaStream_t st, const Consts &k, const i
         qgemv_spread_kernel<WF, KS, 1, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt, k);
 }
 template <int WF, int KS>
-void launch_batched(const mk_weight *w, cudaStream_t st, const Consts &k, const int8_t *xq, const float *xs, int ntok, bool x2, float *y,
-                    int64_t ldy) {
+void launch_batched(const mk_weight *w, cudaStream_t st, const Consts &k, const int8_t *xq, const float *xs, int ntok, bool x2,
+                    bool ordered, float *y, int64_t ldy) {
     constexpr int RT = 8 / KS;
     const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
     const int64_t ldq = w->nbp * 32;
     const void *wt = w->values;
+    if constexpr (KS == 1) {
+        if (ordered) {
+            if (x2)
+                qgemv_batched_kernel<WF, 1, true, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
+            else
+                qgemv_batched_kernel<WF, 1, false, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
+            return;
+        }
+    }
     if (x2)
-        qgemv_batched_kernel<WF, KS, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
+        qgemv_batched_kernel<WF, KS, true, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
     else
-        qgemv_batched_kernel<WF, KS, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
+        qgemv_batched_kernel<WF, KS, false, false><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, ntok, y, ldy, w->rows, w->nrt, k);
 }
 template <int WF>
-void launch_wf(const mk_weight *w, cudaStream_t st, const Consts &k, int ks, bool spread, const int8_t *xq, const float *xs, int ntok,
-               bool x2, float *y, int64_t ldy) {
+void launch_wf(const mk_weight *w, cudaStream_t st, const Consts &k, int ks, bool spread, bool ordered, const int8_t *xq,
+               const float *xs, int ntok, bool x2, float *y, int64_t ldy) {
 #define MK_KS_CASE(K)                                                         \
     case K:                                                                   \
         if (spread) launch_spread<WF, K>(w, st, k, xq, xs, ntok, x2, y, ldy);    \
-        else launch_batched<WF, K>(w, st, k, xq, xs, ntok, x2, y, ldy);          \
+        else launch_batched<WF, K>(w, st, k, xq, xs, ntok, x2, ordered, y, ldy);          \
         break;
     switch (ks) {
         MK_KS_CASE(1)
@@ -326,9 +335,9 @@ int32_t mk_launch_qgemv(mk_ctx *ctx, const mk_weight *w, const int8_t *xq, const
     mk_prof_scope prof(ctx, w->fmt == MK_FMT_MXFP4 ? MK_PROF_MATVEC_MXFP4 : MK_PROF_LM_HEAD);
     const Consts k = {65536u, 0xFFFFFFFFu, ctx->zeros_dev};
     switch (wf) {
-    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, k, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
-    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, k, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
-    default: launch_wf<W_Q8_F16>(w, ctx->stream, k, ks, spread, xq, xs, ntok, x2 != 0, y, ldy); break;
+    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy); break;
+    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy); break;
+    default: launch_wf<W_Q8_F16>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy); break;
     }
     ctx->launches++;
     MK_CUDA(cudaGetLastError());

@@ -226,13 +226,22 @@ __device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile,
 //   !X2: acc[0] (row g, col 2t) acc[1] (row g, col 2t+1) acc[2] (row g+8, col 2t) acc[3] (row g+8, col 2t+1)
 //    X2: columns 2k / 2k+1 are the limbs of token k: acc[0] (row g, token t), acc[2] (row g+8, token t)
 // xs_a / xs_b: block scales of this lane's two columns (tokens), nullptr = unused.
-template <int WF, bool X2>
+// ORDERED = true : one accumulator per output, terms added in ascending block order
+//                  (the CPU order when K is not split).
+// ORDERED = false: four partial sums per output, one per block position in a group,
+//                  combined as (p0+p1)+(p2+p3) - the same association the spread
+//                  schedule uses, so a (token, expert) result does not depend on how
+//                  many tokens share the pass.
+template <int WF, bool X2, bool ORDERED>
 __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile, const void *__restrict__ sc, int64_t ngroups,
                                                   int ks, int KS, int lane, const int8_t *__restrict__ xcol,
                                                   const float *__restrict__ xs_a, const float *__restrict__ xs_b,
                                                   const Consts &k, float (&acc)[4]) {
     const int g = lane >> 2, t = lane & 3;
-    acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+    constexpr int NP = ORDERED ? 1 : 4;
+    float part[NP][4];
+#pragma unroll
+    for (int p = 0; p < NP; ++p) part[p][0] = part[p][1] = part[p][2] = part[p][3] = 0.0f;
     const bool xvalid = xcol != nullptr;
     const int8_t *xp = xvalid ? xcol + t * 8 : k.zeros;
     const uint32_t xstep = xvalid ? 32u : 0u;
@@ -247,17 +256,18 @@ __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile
             load_wscale<WF>(sc, b, g, sg, sh);
             int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
             if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
+            float(&a)[4] = part[ORDERED ? 0 : m];
             if constexpr (X2) {
                 const float sx = xs_a ? __ldg(xs_a + b) : 0.0f;
-                acc[0] = acc_term(acc[0], d0 * 128 + d1, sg, sx);
-                acc[2] = acc_term(acc[2], d2 * 128 + d3, sh, sx);
+                a[0] = acc_term(a[0], d0 * 128 + d1, sg, sx);
+                a[2] = acc_term(a[2], d2 * 128 + d3, sh, sx);
             } else {
                 const float sxa = xs_a ? __ldg(xs_a + b) : 0.0f;
                 const float sxb = xs_b ? __ldg(xs_b + b) : 0.0f;
-                acc[0] = acc_term(acc[0], d0, sg, sxa);
-                acc[1] = acc_term(acc[1], d1, sg, sxb);
-                acc[2] = acc_term(acc[2], d2, sh, sxa);
-                acc[3] = acc_term(acc[3], d3, sh, sxb);
+                a[0] = acc_term(a[0], d0, sg, sxa);
+                a[1] = acc_term(a[1], d1, sg, sxb);
+                a[2] = acc_term(a[2], d2, sh, sxa);
+                a[3] = acc_term(a[3], d3, sh, sxb);
             }
         }
     };
@@ -273,6 +283,11 @@ __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile
         if (i2 < ngroups) load_group<WF>(ga, tile, i2, lane);
         process(gb, i1);
         i = i2;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if constexpr (ORDERED) acc[j] = part[0][j];
+        else acc[j] = __fadd_rn(__fadd_rn(part[0][j], part[1][j]), __fadd_rn(part[2][j], part[3][j]));
     }
 }
 

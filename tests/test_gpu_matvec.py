@@ -138,9 +138,11 @@ def test_mxfp4_matvec_batched_equals_single_token(mk, batch):
         ref = O.mxfp4_matvec(p, s, xs[t], use_q8=True)
         assert np.array_equal(bits(ys[t]), bits(ref))
         assert rel(yd[t], ref) <= 1e-5
+        assert np.array_equal(bits(yd[t]), bits(w.matvec(xs[t]))), "a batch must equal single-token calls bit for bit"
     y2 = w.matvec(xs, act="q8x2")
     for t in range(batch):
         assert rel(y2[t], O.mxfp4_matvec(p, s, xs[t], use_q8=False)) <= 1e-4
+        assert np.array_equal(bits(y2[t]), bits(w.matvec(xs[t], act="q8x2")))
 
 
 def test_mxfp4_expert_down_projection_full_size(mk):

@@ -4,8 +4,11 @@ through the C ABI against the CPU oracle.
   router logits ................ bit-exact (same dot() order as src/model.rs:63-82)
   selected expert ids .......... identical, in slot order (src/parity.rs:215-241 asks for exact ids)
   routing weights .............. 1e-6 relative (one exp() per score; last-ulp freedom)
-  layer output ................. 2e-4 * max|ref| against the CPU q8 path (f32 summation order,
-                                 exp() ulps feeding a q8 rounding); the spec's bound is 1e-3
+  layer output ................. 1e-3 * max|ref| against the CPU q8 path (the spec's bound).  The gap is
+                                 not smooth: gate/up sums differ from the CPU in the last bit (f32
+                                 summation order), which now and then flips the q8 rounding of one
+                                 activation element by one step; one flip moves the w2 output by
+                                 ~5e-4 of its maximum at d=7168, inter=2048 (measured), 0 otherwise.
 """
 import numpy as np
 import pytest
@@ -63,7 +66,7 @@ def test_moe_forward_against_oracle(mk, n_experts, top_k, d, inter, batches):
             assert np.array_equal(bits(lg[t]), bits(lg_ref)), "router logits must be bit-exact"
             assert np.array_equal(ids[t], ids_ref), "expert ids must match in slot order"
             assert np.abs(w[t] - w_ref).max() <= 1e-6 * np.abs(w_ref).max()
-            assert rel(out[t], o_ref) <= 2e-4
+            assert rel(out[t], o_ref) <= 1e-3
         # a batch is, per token, what single-token calls give (src/model.rs:2449-2456)
         single = np.stack([layer.moe_forward(x[t]) for t in range(b)])
         assert np.array_equal(bits(single), bits(out))
@@ -113,7 +116,7 @@ def test_explicit_pairs_and_missing_experts(mk):
         silu = (gl / (np.float32(1.0) + np.exp(-gl).astype(np.float32))).astype(np.float32)
         act = ((pw[p] * silu).astype(np.float32) * ul).astype(np.float32)
         o = O.mxfp4_matvec(tri[1][0], tri[1][1], act, use_q8=True)
-        assert rel(outs[p], o) <= 2e-4
+        assert rel(outs[p], o) <= 1e-3
     assert ctx.status_word() == 0
     # an expert that is not resident
     experts = list(layer._keep[0])
