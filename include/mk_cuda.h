@@ -182,6 +182,49 @@ int32_t mk_moe_experts_dev(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_r
  * combination after the expert jobs (src/deepseek.rs:1095-1106).  DEVICE pointers. */
 int32_t mk_moe_combine_dev(mk_ctx *ctx, const float *outs, int32_t n_tokens, int32_t slots, int32_t d, float *out);
 
+/* ---- q8_0 MLA KV cache and decode attention ------------------------------
+ * Replaces MlaCache::push and mla_attn_flash_q8_mqa (src/model.rs:1583-1618,
+ * 1804-1908).  One object holds n_seqs independent caches of max_positions each.
+ *
+ * MK_MLA_PER_HEAD (the engine's layout, src/model.rs:765-781): per position the
+ *   nope part of K and all of V are q8_0 per head (int8 + one f32 scale per 32),
+ *   the rope part of K is kept f32 and stored once (from head 0).
+ *   append: k_row f32 [n_heads, nope+rope], v_row f32 [n_heads, vd]
+ *   attend: q f32 [n_heads, nope+rope] -> out f32 [n_heads, vd]
+ * MK_MLA_ABSORBED (no counterpart in the engine): one shared q8_0 latent row of
+ *   width nope (= kv_lora_rank + rope dim, all quantized; `rope` must be 0) per
+ *   position; every head attends to the same rows and V is the first vd columns.
+ *   append: k_row f32 [nope], v_row ignored
+ *   attend: q f32 [n_heads, nope] (already absorbed) -> out f32 [n_heads, vd]
+ * Attention follows the engine's recipe: the query's nope part is quantized to
+ * q8_0, score = (rope dot + sum_g (qs*ks)*idot) * scale, softmax over positions
+ * 0..=pos, V dequantized as int8 * scale. */
+#define MK_MLA_PER_HEAD 0
+#define MK_MLA_ABSORBED 1
+typedef struct {
+    int32_t layout;         /* MK_MLA_* */
+    int32_t n_heads, nope, rope, vd;
+    int32_t max_positions;  /* per sequence */
+    int32_t n_seqs;
+} mk_mla_desc;
+int32_t mk_mla_create(mk_ctx *ctx, const mk_mla_desc *desc, mk_mla **out);
+int32_t mk_mla_free(mk_ctx *ctx, mk_mla *mla);
+int32_t mk_mla_reset(mk_ctx *ctx, mk_mla *mla, int32_t seq);            /* forget the positions of one sequence (-1: all) */
+int32_t mk_mla_positions(mk_ctx *ctx, const mk_mla *mla, int32_t seq);  /* positions held, or a negative status */
+/* MlaCache::push for n consecutive positions of one sequence (rows concatenated). */
+int32_t mk_mla_append(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *k_rows, const float *v_rows, int32_t n);
+int32_t mk_mla_append_dev(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *k_rows, const float *v_rows, int32_t n);
+/* mla_attn_flash_q8_mqa over positions 0..=pos of sequence seq (pos < positions held). */
+int32_t mk_mla_attend(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *q, int32_t pos, float scale, float *out);
+/* All sequences at once, each over all the positions it holds: q f32 [n_seqs, n_heads, qdim],
+ * out f32 [n_seqs, n_heads, vd].  DEVICE pointers. */
+int32_t mk_mla_attend_batch_dev(mk_ctx *ctx, mk_mla *mla, const float *q, float scale, float *out);
+/* Cache contents of one sequence back to HOST memory in the engine's layout
+ * (src/model.rs:765-781), any pointer may be NULL:
+ *  PER_HEAD: kq i8 [n, H, nope], ks f32 [n, H, nope/32], kr f32 [n, rope], vq i8 [n, H, vd], vs f32 [n, H, vd/32]
+ *  ABSORBED: kq i8 [n, nope], ks f32 [n, nope/32]; the others are not written. */
+int32_t mk_mla_export(mk_ctx *ctx, const mk_mla *mla, int32_t seq, int8_t *kq, float *ks, float *kr, int8_t *vq, float *vs);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,6 +36,12 @@ class MoeDesc(C.Structure):
                 ("gate_w", _vp), ("gate_b", _vp), ("experts", C.POINTER(_vp)), ("shared", _vp * 3)]
 
 
+class MlaDesc(C.Structure):
+    """mk_mla_desc"""
+    _fields_ = [("layout", _i32), ("n_heads", _i32), ("nope", _i32), ("rope", _i32), ("vd", _i32),
+                ("max_positions", _i32), ("n_seqs", _i32)]
+
+
 # name -> (restype, argtypes); every symbol include/mk_cuda.h declares
 SIGNATURES = {
     "mk_init": (_i32, [_i32, C.POINTER(_vp)]),
@@ -69,6 +75,15 @@ SIGNATURES = {
     "mk_moe_forward_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "mk_moe_experts_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp]),
     "mk_moe_combine_dev": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
+    "mk_mla_create": (_i32, [_vp, C.POINTER(MlaDesc), C.POINTER(_vp)]),
+    "mk_mla_free": (_i32, [_vp, _vp]),
+    "mk_mla_reset": (_i32, [_vp, _vp, _i32]),
+    "mk_mla_positions": (_i32, [_vp, _vp, _i32]),
+    "mk_mla_append": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32]),
+    "mk_mla_append_dev": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32]),
+    "mk_mla_attend": (_i32, [_vp, _vp, _i32, _vp, _i32, C.c_float, _vp]),
+    "mk_mla_attend_batch_dev": (_i32, [_vp, _vp, _vp, C.c_float, _vp]),
+    "mk_mla_export": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp]),
 }
 
 

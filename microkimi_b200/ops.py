@@ -347,6 +347,95 @@ class MoeLayer:
         return out
 
 
+class MlaCache:
+    """q8_0 MLA KV cache on the GPU (model::MlaCache, src/model.rs:765-781) with the
+    all-heads decode attention (mla_attn_flash_q8_mqa, src/model.rs:1804-1908).
+
+    layout "per_head": the engine's layout (nope K and V q8_0 per head, rope f32 once).
+    layout "absorbed": one shared q8_0 latent row of width `nope` per position
+    (rope = 0), V = its first vd columns.  n_seqs independent sequences.
+    """
+
+    def __init__(self, n_heads, nope, rope, vd, max_positions, n_seqs=1, layout="per_head", ctx=None):
+        ctx = ctx or Context.default()
+        self.ctx = ctx
+        self.H, self.nope, self.rope, self.vd = n_heads, nope, rope, vd
+        self.cap, self.n_seqs, self.layout = max_positions, n_seqs, layout
+        d = _l.MlaDesc(0 if layout == "per_head" else 1, n_heads, nope, rope, vd, max_positions, n_seqs)
+        h = C.c_void_p()
+        _l.check(ctx._L.mk_mla_create(ctx._h, C.byref(d), C.byref(h)))
+        self._h = h
+
+    def free(self):
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._L.mk_mla_free(self.ctx._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def positions(self, seq=0):
+        n = self.ctx._L.mk_mla_positions(self.ctx._h, self._h, seq)
+        if n < 0:
+            _l.check(n)
+        return n
+
+    def reset(self, seq=-1):
+        _l.check(self.ctx._L.mk_mla_reset(self.ctx._h, self._h, seq))
+
+    def push(self, k_row, v_row=None, seq=0):
+        """MlaCache::push for one or more consecutive positions.
+        per_head: k_row [n, H, nope+rope], v_row [n, H, vd]; absorbed: k_row [n, nope]."""
+        L = self.ctx._L
+        kdim = self.nope if self.layout == "absorbed" else self.H * (self.nope + self.rope)
+        if _is_torch_cuda(k_row):
+            n = k_row.numel() // kdim
+            vp = C.c_void_p(v_row.data_ptr()) if v_row is not None else None
+            _l.check(L.mk_mla_append_dev(self.ctx._h, self._h, seq, C.c_void_p(k_row.data_ptr()), vp, n))
+            return
+        k = np.ascontiguousarray(k_row, dtype=np.float32)
+        assert k.size % kdim == 0, "k_row has the wrong size"
+        n = k.size // kdim
+        v = None
+        if self.layout != "absorbed":
+            v = np.ascontiguousarray(v_row, dtype=np.float32)
+            assert v.size == n * self.H * self.vd, "v_row has the wrong size"
+        _l.check(L.mk_mla_append(self.ctx._h, self._h, seq, _np_ptr(k), _np_ptr(v) if v is not None else None, n))
+
+    def mla_attn_flash_q8_mqa(self, q, pos, scale, seq=0):
+        """Attention of q [H, nope+rope] over positions 0..=pos -> [H, vd]."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        assert q.size == self.H * (self.nope + self.rope), "q has the wrong size"
+        out = np.empty((self.H, self.vd), np.float32)
+        _l.check(self.ctx._L.mk_mla_attend(self.ctx._h, self._h, seq, _np_ptr(q), int(pos), float(scale), _np_ptr(out)))
+        return out
+
+    def attend_batch(self, q, scale):
+        """All sequences at once (torch CUDA q [n_seqs, H, qdim]) over all positions each holds."""
+        import torch
+        assert q.is_contiguous() and q.dtype == torch.float32 and q.numel() == self.n_seqs * self.H * (self.nope + self.rope)
+        out = torch.empty((self.n_seqs, self.H, self.vd), dtype=torch.float32, device=q.device)
+        _l.check(self.ctx._L.mk_mla_attend_batch_dev(self.ctx._h, self._h, C.c_void_p(q.data_ptr()), float(scale),
+                                                     C.c_void_p(out.data_ptr())))
+        return out
+
+    def export(self, seq=0):
+        """Cache contents in the engine's layout: dict of kq, ks (, kr, vq, vs)."""
+        n = self.positions(seq)
+        kvh = 1 if self.layout == "absorbed" else self.H
+        out = {"kq": np.empty((n, kvh, self.nope), np.int8), "ks": np.empty((n, kvh, self.nope // 32), np.float32)}
+        ptr = lambda k: _np_ptr(out[k]) if k in out and out[k].size else None
+        if self.layout != "absorbed":
+            out["kr"] = np.empty((n, self.rope), np.float32)
+            out["vq"] = np.empty((n, kvh, self.vd), np.int8)
+            out["vs"] = np.empty((n, kvh, self.vd // 32), np.float32)
+        _l.check(self.ctx._L.mk_mla_export(self.ctx._h, self._h, seq, ptr("kq"), ptr("ks"), ptr("kr"), ptr("vq"), ptr("vs")))
+        return out
+
+
 def quantize_q8(x, ctx=None):
     """q8::quantize_q8 on the GPU: (q int8 [n], scales f32 [n/32])."""
     ctx = ctx or Context.default()

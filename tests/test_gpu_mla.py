@@ -1,0 +1,174 @@
+"""GPU parity tests of the q8_0 MLA cache and decode attention through the C ABI.
+
+  cache bytes, block scales, rope floats after append ... bit-exact vs the CPU oracle
+  attention output ....................................... 2e-4 * max|ref| (asserted; the spec asks 1e-3):
+        same q8 query, same exact int32 block dots; the gap is exp() ulps and f32
+        summation order (32-position tiles and KV splits instead of 64-position tiles)
+"""
+import numpy as np
+import pytest
+
+from conftest import bits, pattern
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+MICRO = dict(nh=4, nope=128, rope=64, vd=128)  # src/config.rs:47-79
+
+
+@pytest.fixture(scope="module")
+def mk():
+    import microkimi_b200 as m
+    m.Context.default()
+    return m
+
+
+def rel(a, ref):
+    return np.abs(a.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-12)
+
+
+def _kv_rows(j, nh, hd, vd, nope, rope, spike):
+    """The rows of selftest.rs:748-770 (rope shared across heads, optional 30x outliers)."""
+    kr = pattern(np.arange(nh * hd, dtype=np.uint64) + np.uint64(j * 7919)).copy()
+    vr = pattern(np.arange(nh * vd, dtype=np.uint64) + np.uint64(j * 5449 + 313)).copy()
+    for h in range(1, nh):
+        kr[h * hd + nope:h * hd + nope + rope] = kr[nope:nope + rope]
+    if spike and j % 3 == 0:
+        for h in range(nh):
+            kr[h * hd + 5] = np.float32(30.0) * pattern(j + 17)
+            vr[h * vd + 9] = np.float32(30.0) * pattern(j + 23)
+    return kr, vr
+
+
+@pytest.mark.parametrize("length,spike", [(1, False), (7, False), (64, False), (65, False), (512, False), (512, True)])
+def test_kvq8_selftest_cases(mk, length, spike):
+    """selftest.rs:716-900 (Hadamard off) on the GPU cache."""
+    nh, nope, rope, vd = MICRO["nh"], MICRO["nope"], MICRO["rope"], MICRO["vd"]
+    hd = nope + rope
+    ref = O.MlaCache(nh, nope, rope, vd, length)
+    dev = mk.MlaCache(nh, nope, rope, vd, length)
+    K = np.empty((length, nh * hd), np.float32)
+    V = np.empty((length, nh * vd), np.float32)
+    for j in range(length):
+        K[j], V[j] = _kv_rows(j, nh, hd, vd, nope, rope, spike)
+        ref.push(K[j], V[j])
+    half = length // 2
+    if half:
+        dev.push(K[:half], V[:half])         # several positions in one call ...
+    for j in range(half, length):
+        dev.push(K[j], V[j])                 # ... and one by one
+    assert dev.positions() == length
+    ex = dev.export()
+    k2, v2 = ref.to_f32()                    # dequantized reference cache
+    kdeq = ex["kq"].astype(np.float32).reshape(length, nh, nope // 32, 32) * ex["ks"][..., None]
+    vdeq = ex["vq"].astype(np.float32).reshape(length, nh, vd // 32, 32) * ex["vs"][..., None]
+    assert np.array_equal(bits(kdeq.reshape(length, nh, nope)), bits(k2[:, :, :nope]))
+    assert np.array_equal(bits(vdeq.reshape(length, nh, vd)), bits(v2))
+    assert np.array_equal(bits(ex["kr"]), bits(K.reshape(length, nh, hd)[:, 0, nope:]))  # rope stays exact
+    q = pattern(np.arange(nh * hd, dtype=np.uint64) + np.uint64(4242)).reshape(nh, hd)
+    scale = np.float32(hd) ** np.float32(-0.5)
+    for pos in sorted({0, length // 2, length - 1}):
+        want = ref.attn_mqa(q, pos, scale)
+        got = dev.mla_attn_flash_q8_mqa(q, pos, scale)
+        assert rel(got, want) <= 2e-4
+
+
+def test_quantized_bytes_bit_exact_on_gaussian_rows(mk):
+    rng = np.random.default_rng(1)
+    nh, nope, rope, vd, n = 8, 64, 32, 128, 40
+    K = rng.standard_normal((n, nh, nope + rope)).astype(np.float32)
+    V = rng.standard_normal((n, nh, vd)).astype(np.float32)
+    V[3, 2, :32] = 0.0
+    dev = mk.MlaCache(nh, nope, rope, vd, 64)
+    dev.push(K, V)
+    ex = dev.export()
+    for j in range(n):
+        for h in range(nh):
+            q, s = O.q8_quantize(K[j, h, :nope])
+            assert np.array_equal(ex["kq"][j, h], q) and np.array_equal(bits(ex["ks"][j, h]), bits(s))
+            q, s = O.q8_quantize(V[j, h])
+            assert np.array_equal(ex["vq"][j, h], q) and np.array_equal(bits(ex["vs"][j, h]), bits(s))
+
+
+def test_per_head_layout_64_heads(mk):
+    """The engine's layout at 64 heads (18,688 bytes per position), N(0,1) rows."""
+    rng = np.random.default_rng(2)
+    nh, nope, rope, vd, n = 64, 128, 64, 128, 700
+    hd = nope + rope
+    K = rng.standard_normal((n, nh, hd)).astype(np.float32)
+    K[:, 1:, nope:] = K[:, :1, nope:]
+    V = rng.standard_normal((n, nh, vd)).astype(np.float32)
+    ref = O.MlaCache(nh, nope, rope, vd, n)
+    for j in range(n):
+        ref.push(K[j], V[j])
+    dev = mk.MlaCache(nh, nope, rope, vd, n)
+    dev.push(K, V)
+    q = rng.standard_normal((nh, hd)).astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(192.0))
+    for pos in (n - 1, 300):
+        assert rel(dev.mla_attn_flash_q8_mqa(q, pos, scale), ref.attn_mqa(q, pos, scale)) <= 2e-4
+
+
+@pytest.mark.parametrize("nh,n", [(8, 200), (64, 1500)])
+def test_absorbed_layout(mk, nh, n):
+    """One shared 512+64 q8_0 latent row per position, softmax scale 1/sqrt(192)."""
+    import torch
+    rng = np.random.default_rng(nh + n)
+    lat, vd = 576, 512
+    rows = rng.standard_normal((n, lat)).astype(np.float32)
+    ref = O.MlaAbsCache(lat, vd, n)
+    ref.push_many(rows)
+    dev = mk.MlaCache(nh, lat, 0, vd, n, layout="absorbed")
+    dev.push(rows)
+    ex = dev.export()
+    for j in (0, n // 2, n - 1):
+        q8, s = O.q8_quantize(rows[j])
+        assert np.array_equal(ex["kq"][j, 0], q8) and np.array_equal(bits(ex["ks"][j, 0]), bits(s))
+    q = rng.standard_normal((nh, lat)).astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(192.0))
+    for pos in (0, 63, 64, n - 1):
+        want = ref.attn(q, pos, scale)
+        got = dev.mla_attn_flash_q8_mqa(q, pos, scale)
+        assert rel(got, want) <= 2e-4
+        assert rel(got, ref.attn_f64(q, pos, scale)) <= 2e-2   # the q8 rounding of the query
+
+
+def test_batch_of_sequences_with_different_lengths(mk):
+    import torch
+    rng = np.random.default_rng(9)
+    nh, lat, vd = 16, 576, 512
+    lens = [5, 130, 64]
+    ctx = mk.Context.default()
+    ctx.use_torch_stream()
+    dev = mk.MlaCache(nh, lat, 0, vd, 256, n_seqs=3, layout="absorbed")
+    refs = []
+    for s, n in enumerate(lens):
+        rows = rng.standard_normal((n, lat)).astype(np.float32)
+        r = O.MlaAbsCache(lat, vd, n)
+        r.push_many(rows)
+        refs.append(r)
+        dev.push(torch.from_numpy(rows).cuda(), seq=s)
+    q = rng.standard_normal((3, nh, lat)).astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(192.0))
+    out = dev.attend_batch(torch.from_numpy(q).cuda(), scale)
+    torch.cuda.synchronize()
+    out = out.cpu().numpy()
+    for s, n in enumerate(lens):
+        assert rel(out[s], refs[s].attn(q[s], n - 1, scale)) <= 2e-4
+    dev.reset(1)
+    assert dev.positions(1) == 0 and dev.positions(0) == 5
+
+
+def test_cache_errors_are_statuses(mk):
+    dev = mk.MlaCache(4, 128, 64, 128, 2)
+    k = np.zeros((1, 4, 192), np.float32)
+    v = np.zeros((1, 4, 128), np.float32)
+    dev.push(k, v)
+    dev.push(k, v)
+    with pytest.raises(mk.lib.MkError) as e:
+        dev.push(k, v)                       # full
+    assert e.value.code == -4
+    with pytest.raises(mk.lib.MkError) as e:
+        dev.mla_attn_flash_q8_mqa(np.zeros((4, 192), np.float32), 2, 1.0)   # pos beyond the cache
+    assert e.value.code == -1
+    with pytest.raises(mk.lib.MkError):
+        mk.MlaCache(4, 100, 64, 128, 2)      # nope not a multiple of 32
