@@ -1,0 +1,137 @@
+"""Multi-GPU host logic for the two paths that shard: the vocab-sharded q8_0
+lm_head (logits all-gather) and expert-parallel MoE (all-to-all token dispatch).
+
+One process per GPU, `torch.distributed` for the plumbing (NCCL on GPUs, gloo in
+the CPU tests).  The reference engine is single-process (no rank concept
+anywhere), so there is no reference code for this file; what it must preserve is
+the single-GPU RESULT: the gathered logits and the combined MoE output are the
+bits a single GPU would produce, because every (row, expert) pair is computed by
+the same kernels and combined in slot order on the token's home rank.
+
+The functions take plain callables for the per-rank compute so that the exchange
+logic can be exercised on CPU ranks.
+"""
+import torch
+import torch.distributed as dist
+
+
+# ---------------------------------------------------------------- vocab-sharded lm_head
+def vocab_shard(vocab, world, rank):
+    """Rows [lo, hi) of the lm_head owned by `rank` (block partition, remainder to the first ranks)."""
+    base, rem = divmod(vocab, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def gather_logits(local_logits, vocab, group=None):
+    """local_logits [batch, rows_of_this_rank] -> full logits [batch, vocab] on every rank."""
+    world = dist.get_world_size(group)
+    batch = local_logits.shape[0]
+    sizes = [vocab_shard(vocab, world, r) for r in range(world)]
+    if all(hi - lo == sizes[0][1] - sizes[0][0] for lo, hi in sizes):
+        rows = sizes[0][1] - sizes[0][0]
+        if batch == 1:
+            full = torch.empty((1, vocab), dtype=local_logits.dtype, device=local_logits.device)
+            dist.all_gather_into_tensor(full.view(-1), local_logits.contiguous().view(-1), group=group)
+            return full
+        stacked = torch.empty((world, batch, rows), dtype=local_logits.dtype, device=local_logits.device)
+        dist.all_gather_into_tensor(stacked.view(-1), local_logits.contiguous().view(-1), group=group)
+        return stacked.permute(1, 0, 2).reshape(batch, vocab)
+    # uneven shards: pad every shard to the widest one, gather, cut the padding off
+    widest = max(hi - lo for lo, hi in sizes)
+    padded = torch.zeros((batch, widest), dtype=local_logits.dtype, device=local_logits.device)
+    padded[:, :local_logits.shape[1]] = local_logits
+    stacked = torch.empty((world, batch, widest), dtype=local_logits.dtype, device=local_logits.device)
+    dist.all_gather_into_tensor(stacked.view(-1), padded.view(-1), group=group)
+    return torch.cat([stacked[r, :, :hi - lo] for r, (lo, hi) in enumerate(sizes)], dim=1)
+
+
+def greedy_token(full_logits):
+    """First index of the maximum per row (the engine's greedy pick, src/model.rs:3277-3290)."""
+    mx = full_logits.max(dim=1, keepdim=True).values
+    idx = torch.arange(full_logits.shape[1], device=full_logits.device).expand_as(full_logits)
+    big = torch.full_like(idx, full_logits.shape[1])
+    return torch.where(full_logits == mx, idx, big).min(dim=1).values.to(torch.int32)
+
+
+# ---------------------------------------------------------------- expert-parallel MoE
+def expert_owner(expert, n_experts, world):
+    """Block partition of the routed experts: expert e lives on rank e // (n_experts / world)."""
+    per = n_experts // world
+    return torch.clamp(expert // per, max=world - 1)
+
+
+def local_expert_range(n_experts, world, rank):
+    per = n_experts // world
+    lo = rank * per
+    return lo, (n_experts if rank == world - 1 else lo + per)
+
+
+def ep_moe_forward(x, ids, weights, n_experts, experts_fn, combine_fn, group=None, shared_expert=True):
+    """Expert-parallel MoE for the token rows this rank owns.
+
+    x        [n, d]      the rank's own token rows (n may be 0)
+    ids      [n, k] i32  routed expert ids in slot order (router is replicated, so every
+    weights  [n, k] f32  rank computes the routing of its own tokens itself)
+    experts_fn(rows [m, d], pair_row [m] i32, pair_expert [m] i32, pair_weight [m] f32) -> [m, d]
+             runs the experts RESIDENT ON THIS RANK on explicit (row, expert, weight) pairs
+    combine_fn(outs [n * slots, d], n, slots) -> [n, d]   slot-order sum
+    The shared expert (id n_experts, weight 1) runs on the token's home rank.
+
+    Exchange: one all-to-all of per-destination pair counts, one of the activation
+    rows (+ expert ids and weights), one back with the expert outputs.  The payload
+    lands in local memory before any kernel reads it.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    n, d = x.shape
+    k = ids.shape[1]
+    slots = k + (1 if shared_expert else 0)
+    dev = x.device
+
+    pe = ids.to(torch.int64)
+    pw = weights
+    if shared_expert:
+        pe = torch.cat([pe, torch.full((n, 1), n_experts, dtype=torch.int64, device=dev)], dim=1)
+        pw = torch.cat([pw, torch.ones((n, 1), dtype=weights.dtype, device=dev)], dim=1)
+    pe = pe.reshape(-1)                         # pair p = token * slots + slot
+    pw = pw.reshape(-1)
+    prow = torch.arange(n, device=dev).repeat_interleave(slots)
+    dest = expert_owner(pe, n_experts, world)
+    if shared_expert:
+        dest = torch.where(pe == n_experts, torch.full_like(dest, rank), dest)
+
+    order = torch.argsort(dest, stable=True)    # pairs grouped by destination rank
+    send_counts = torch.bincount(dest, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    s_list, r_list = send_counts.tolist(), recv_counts.tolist()
+    m = int(sum(r_list))
+
+    send_rows = x[prow[order]].contiguous()
+    send_meta = torch.stack([pe[order].to(torch.float64), pw[order].to(torch.float64)], dim=1).contiguous()
+    recv_rows = torch.empty((m, d), dtype=x.dtype, device=dev)
+    recv_meta = torch.empty((m, 2), dtype=torch.float64, device=dev)
+    dist.all_to_all_single(recv_rows, send_rows, r_list, s_list, group=group)
+    dist.all_to_all_single(recv_meta, send_meta, r_list, s_list, group=group)
+
+    if m > 0:
+        outs_here = experts_fn(recv_rows, torch.arange(m, dtype=torch.int32, device=dev),
+                               recv_meta[:, 0].to(torch.int32), recv_meta[:, 1].to(torch.float32))
+    else:
+        outs_here = torch.empty((0, d), dtype=x.dtype, device=dev)
+
+    back = torch.empty((n * slots, d), dtype=x.dtype, device=dev)
+    dist.all_to_all_single(back, outs_here.contiguous(), s_list, r_list, group=group)
+    outs = torch.empty_like(back)
+    outs[order] = back                          # undo the grouping: outs[token * slots + slot]
+    if n == 0:
+        return torch.empty((0, d), dtype=x.dtype, device=dev)
+    return combine_fn(outs, n, slots)
+
+
+def shard_tokens(n_tokens, world, rank):
+    """Token rows [lo, hi) whose home is `rank` (tokens are sharded, not replicated)."""
+    base, rem = divmod(n_tokens, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
