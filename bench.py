@@ -317,14 +317,120 @@ def run_case_mxfp4(args):
                                    "peak_kind": kind}}), flush=True)
 
 
+def _side_ctx():
+    import torch
+
+    import microkimi_b200 as mk
+    torch.cuda.set_device(0)
+    ctx = mk.Context(0)
+    mk.Context._default = ctx
+    ctx.use_torch_stream()
+    return torch, mk, ctx, torch.device("cuda", 0)
+
+
+def _timed(torch, fn, steps, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_case_moe(args):
+    """Side workload: one MoE FFN layer - `experts` routed MXFP4 experts + 1 shared, top-8,
+    hidden 7168, expert intermediate 2048, sigmoid router; tokens N(0,1), batch --batch.
+    Expert codes are synthetic (uniform codes, scale bytes 118..123): the kernels' speed does
+    not depend on the values.  `layers` rotating copies keep the timed passes cold in L2."""
+    torch, mk, ctx, dev = _side_ctx()
+    E, k, d, inter, B = args.experts, 8, 7168, 2048, args.batch
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+
+    def rand_w(rows, cols):
+        p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
+        s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
+        return mk.MxFp4Weight(p, s, rows, cols, ctx=ctx)
+
+    layers = []
+    for _ in range(args.copies):
+        experts = [(rand_w(inter, d), rand_w(d, inter), rand_w(inter, d)) for _ in range(E + 1)]
+        gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
+        layers.append(mk.MoeLayer(gw, None, experts[:-1], experts[-1], k, ctx=ctx))
+    x = torch.randn((B, d), dtype=torch.float32, device=dev, generator=gen)
+    _, ids, _ = layers[0].moe_forward(x, want_routing=True)
+    distinct = int(torch.unique(ids).numel())
+    per_expert = 3 * (inter * d // 2 + inter * d // 32)
+    alg = E * d * 4 + (distinct + 1) * per_expert + 2 * B * d * 4
+    ctx.prof_enable(True)
+    ms = _timed(torch, lambda i: layers[i % args.copies].moe_forward(x), args.steps, args.warmup)
+    n_e, ms_e = ctx.prof_read("experts")
+    n_r, ms_r = ctx.prof_read("router")
+    ctx.prof_enable(False)
+    calls = args.steps + args.warmup
+    peak, kind = measured_peaks()
+    ach = alg / (ms * 1e-3) / 1e9
+    print(json.dumps({"case": "moe", "experts": E, "top_k": k, "batch": B, "copies": args.copies,
+                      "distinct_experts_routed": distinct, "ms_per_layer": ms, "tokens_per_s": B / (ms * 1e-3),
+                      "experts_ms": ms_e / calls * (n_e / max(n_e, 1)) if n_e else None, "router_ms": ms_r / calls if n_r else None,
+                      "algorithmic_bytes": alg,
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                                   "peak_kind": kind, "note": "whole layer call (7 launches), not one kernel"}}), flush=True)
+
+
+def run_case_mla(args):
+    """Side workload: q8_0 MLA decode attention, 64 heads.  --layout absorbed: one shared
+    512+64 latent row per position (648 B with f32 scales); --layout per_head: the engine's
+    layout at nope 128 / rope 64 / v 128 (18,688 B per position).  Cache rows N(0,1), context
+    --ctx, --batch independent sequences, softmax scale 1/sqrt(192)."""
+    torch, mk, ctx, dev = _side_ctx()
+    H, B, n = 64, args.batch, args.ctx
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4)
+    if args.layout == "absorbed":
+        cache = mk.MlaCache(H, 576, 0, 512, n, n_seqs=B, layout="absorbed", ctx=ctx)
+        qdim, per_pos = 576, 576 + 18 * 4
+        for s_ in range(B):
+            for lo in range(0, n, 8192):
+                m = min(8192, n - lo)
+                cache.push(torch.randn((m, 576), dtype=torch.float32, device=dev, generator=gen), seq=s_)
+    else:
+        cache = mk.MlaCache(H, 128, 64, 128, n, n_seqs=B, ctx=ctx)
+        qdim, per_pos = 192, H * 128 + H * 4 * 4 + 64 * 4 + H * 128 + H * 4 * 4
+        for s_ in range(B):
+            for lo in range(0, n, 1024):
+                m = min(1024, n - lo)
+                kk = torch.randn((m, H, 192), dtype=torch.float32, device=dev, generator=gen)
+                vv = torch.randn((m, H, 128), dtype=torch.float32, device=dev, generator=gen)
+                cache.push(kk, vv, seq=s_)
+    q = torch.randn((B, H, qdim), dtype=torch.float32, device=dev, generator=gen)
+    scale = 1.0 / np.sqrt(192.0)
+    ms = _timed(torch, lambda i: cache.attend_batch(q, scale), args.steps, args.warmup)
+    alg = B * n * per_pos + B * H * (qdim + cache.vd) * 4
+    flops = B * n * 2 * H * (qdim + cache.vd) if args.layout == "absorbed" else B * n * 2 * H * (192 + 128)
+    peak, kind = measured_peaks()
+    ach = alg / (ms * 1e-3) / 1e9
+    print(json.dumps({"case": "mla", "layout": args.layout, "heads": H, "ctx": n, "batch": B, "ms_per_call": ms,
+                      "algorithmic_bytes": alg, "tflops": flops / (ms * 1e-3) / 1e12,
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                                   "peak_kind": kind}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv"],
+    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "mla"],
                     help="lm_head is the benchmark proper; the others are side workloads for kernel studies")
     ap.add_argument("--rows", type=int, default=7168)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=1)
     ap.add_argument("--act", default="q8", choices=["q8", "q8x2"])
+    ap.add_argument("--experts", type=int, default=384)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--layout", default="absorbed", choices=["absorbed", "per_head"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
@@ -337,6 +443,10 @@ def main():
         run_reference(args)
     elif args.case == "mxfp4_gemv":
         run_case_mxfp4(args)
+    elif args.case == "moe":
+        run_case_moe(args)
+    elif args.case == "mla":
+        run_case_mla(args)
     else:
         run_gpu(args)
 

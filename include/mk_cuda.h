@@ -134,6 +134,18 @@ int32_t mk_quantize_q8(mk_ctx *ctx, const float *x, int64_t n, int8_t *q, float 
  * x f32 [batch, cols], y f32 [batch, rows]. */
 int32_t mk_matvec_mxfp4(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch, int32_t act_mode);
 int32_t mk_matvec_mxfp4_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch, int32_t act_mode);
+/* No counterpart in the reference.  Same result as mk_matvec_mxfp4_dev, for hosts that
+ * must not allocate device memory once they are running: an engine that has handed
+ * all of HBM to its own weight and KV-cache pools (a late workspace cudaMalloc can
+ * fail there), or a decode loop that cannot afford the device-wide synchronization a
+ * cudaMalloc implies.  The quantized activations go to a fixed 144 KiB array inside
+ * the library's device image instead of a grown workspace; the call makes no
+ * cudaMalloc/cudaFree.  Limits: padded cols <= 16384 and batch <= 8 (<= 4 with
+ * MK_ACT_Q8X2); larger calls return MK_ERR_ARG.  The first call on a device looks the
+ * array's device address up, so make that call before any stream capture.  All
+ * calls share the array: two calls that overlap on the GPU (different streams or
+ * contexts of one process) race; calls on one stream are ordered and safe. */
+int32_t mk_matvec_mxfp4_noalloc_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch, int32_t act_mode);
 /* Q8Head::matvec + the greedy pick of top_k_probs (src/model.rs:290-335,
  * 3271-3291): y f32 [batch, rows]; argmax (optional, int32 [batch]) = first
  * index attaining the maximum of each row of y. */

@@ -355,3 +355,50 @@ int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, in
     MK_CUDA(cudaGetLastError());
     return MK_OK;
 }
+
+// ------------------------------------------------------------------ matvec that allocates nothing
+// Scratch for the quantized activations of mk_matvec_mxfp4_noalloc_dev: a fixed
+// array in the library's device image instead of a cudaMalloc'd workspace.  Every
+// GPU that loads the library holds these 144 KiB until the process exits.
+#define MK_NOALLOC_MAX_COLS 16384
+#define MK_NOALLOC_MAX_TOKENS 8
+#define MK_NOALLOC_XQ_BYTES (MK_NOALLOC_MAX_TOKENS * MK_NOALLOC_MAX_COLS)
+#define MK_NOALLOC_XS_BYTES (MK_NOALLOC_MAX_TOKENS * (MK_NOALLOC_MAX_COLS / 32) * 4)
+static __device__ __align__(256) unsigned char mk_noalloc_scratch[MK_NOALLOC_XQ_BYTES + MK_NOALLOC_XS_BYTES];
+
+// Device address of the array above, per device ordinal.  The array's name is only
+// a host-side handle; the address a kernel can use comes from cudaGetSymbolAddress
+// with that device current.
+#define MK_NOALLOC_MAX_DEVICES 64
+static void *g_noalloc_addr[MK_NOALLOC_MAX_DEVICES];
+
+extern "C" int32_t mk_matvec_mxfp4_noalloc_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch,
+                                               int32_t act_mode) {
+    MK_CHECK_ARG(ctx != nullptr && w != nullptr && x != nullptr && y != nullptr, "NULL argument");
+    MK_CHECK_ARG(w->fmt == MK_FMT_MXFP4, "weight handle is not MXFP4");
+    const int x2 = (act_mode & 0xFF) == MK_ACT_Q8X2;
+    const int strict = (act_mode & MK_ACT_STRICT) != 0;
+    MK_CHECK_ARG((act_mode & 0xFF) == MK_ACT_Q8 || x2, "unknown act_mode");
+    const int64_t ldq = w->nbp * 32;
+    if (ldq > MK_NOALLOC_MAX_COLS || batch < 1 || batch * (x2 ? 2 : 1) > MK_NOALLOC_MAX_TOKENS) {
+        mk_set_error("mk_matvec_mxfp4_noalloc_dev: the fixed scratch holds at most %d columns (this matrix: %lld) and %d "
+                     "activation rows (asked: %d%s); use mk_matvec_mxfp4_dev for larger calls",
+                     MK_NOALLOC_MAX_COLS, (long long)ldq, MK_NOALLOC_MAX_TOKENS, batch, x2 ? " x 2 limbs" : "");
+        return MK_ERR_ARG;
+    }
+    MK_CHECK_ARG(ctx->device >= 0 && ctx->device < MK_NOALLOC_MAX_DEVICES, "device ordinal out of range");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    if (g_noalloc_addr[ctx->device] == nullptr) {
+        // set-up on the first call on this device
+        void *p = nullptr;
+        MK_CUDA(cudaGetSymbolAddress(&p, mk_noalloc_scratch));
+        g_noalloc_addr[ctx->device] = p;
+    }
+    int8_t *xq = (int8_t *)g_noalloc_addr[ctx->device];
+    float *xs = (float *)((unsigned char *)g_noalloc_addr[ctx->device] + MK_NOALLOC_XQ_BYTES);
+    // the quantizer overwrites every byte and scale the matvec reads (padding blocks
+    // included), so nothing left by an earlier call is ever consumed
+    int32_t rc = mk_launch_quantize_act(ctx, x, batch, w->cols, w->cols, w->nbp, x2, xq, xs);
+    if (rc != MK_OK) return rc;
+    return mk_launch_qgemv(ctx, w, xq, xs, batch, x2, strict, y, w->rows);
+}

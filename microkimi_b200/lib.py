@@ -65,6 +65,7 @@ SIGNATURES = {
     "mk_quantize_q8": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "mk_matvec_mxfp4": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_mxfp4_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "mk_matvec_mxfp4_noalloc_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_q8": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_matvec_q8_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_moe_create": (_i32, [_vp, C.POINTER(MoeDesc), C.POINTER(_vp)]),

@@ -159,6 +159,21 @@ class MxFp4Weight(_Weight):
         _l.check(fn(self.ctx._h, self._h, *args))
         return y[0] if (x.ndim if hasattr(x, "ndim") else x.dim()) == 1 else y
 
+    def matvec_noalloc(self, x, act="q8", strict=False):
+        """matvec for callers that must not allocate device memory while running (their
+        memory is fully budgeted, or a cudaMalloc stall is not acceptable): the activation
+        scratch is a fixed array inside the library.  x: torch CUDA tensor [batch, cols]
+        (or [cols]) with batch <= 8 and cols <= 16384; larger shapes raise.  Calls share
+        that array, so keep them on one stream."""
+        import torch
+        assert _is_torch_cuda(x) and x.dtype == torch.float32 and x.is_contiguous()
+        batch = 1 if x.dim() == 1 else x.shape[0]
+        assert x.shape[-1] == self.cols, "x length must equal cols"
+        y = torch.empty((batch, self.rows), dtype=torch.float32, device=x.device)
+        _l.check(self.ctx._L.mk_matvec_mxfp4_noalloc_dev(self.ctx._h, self._h, C.c_void_p(x.data_ptr()),
+                                                         C.c_void_p(y.data_ptr()), batch, _act_mode(act, strict)))
+        return y[0] if x.dim() == 1 else y
+
     def dequant(self):
         """mxfp4::dequant on the GPU -> f32 [rows, cols] (numpy)."""
         out = np.empty((self.rows, self.cols), np.float32)
