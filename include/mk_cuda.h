@@ -82,7 +82,9 @@ int32_t mk_device_info(mk_ctx *ctx, int32_t *sm_count, int32_t *cc_major, int32_
 int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
 
 /* Tuning knobs, for measurement only (defaults are chosen per shape):
- *   "force_ks" : K split of the matvec kernels, one of 0 (auto), 1, 2, 4, 8. */
+ *   "force_ks" : K split of the matvec kernels, one of 0 (auto), 1, 2, 4, 8.
+ *   "mla_no_tc": 1 = run absorbed-layout attention on the CUDA-core kernel instead of
+ *                the tensor-core one (exact int32 block dots, much slower). */
 int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value);
 
 /* Per-category kernel timing with CUDA events on the context's stream, the

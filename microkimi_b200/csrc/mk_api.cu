@@ -110,6 +110,10 @@ extern "C" int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value) {
         ctx->force_ks = (int)value;
         return MK_OK;
     }
+    if (strcmp(name, "mla_no_tc") == 0) {
+        ctx->mla_no_tc = value != 0;
+        return MK_OK;
+    }
     mk_set_error("mk_set_option: unknown option '%s'", name);
     return MK_ERR_ARG;
 }

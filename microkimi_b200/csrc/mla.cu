@@ -22,6 +22,7 @@
 // softmax step follows the reference's tile recipe, phase 2 accumulates p*V
 // (lane = columns).  Splits are merged by a second kernel with a log-sum-exp.
 #include "mk_common.cuh"
+#include "mla_tc.cuh"
 
 struct mk_mla {
     int layout, H, nope, rope, vd, cap, nseq;
@@ -427,6 +428,29 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     int32_t rc = mk_launch_quantize_act(ctx, q, nq * m->H, m->nope, qdim, m->q_nbp, 0, m->qq, m->qs);
     if (rc != MK_OK) return rc;
     mk_prof_scope prof(ctx, MK_PROF_MLA);
+    if (m->layout == MK_MLA_ABSORBED && m->H == mla_tc::H && m->nope == mla_tc::LAT && m->vd == mla_tc::VD && !ctx->mla_no_tc) {
+        // tensor-core kernel: one CTA per (sequence, KV split), 64 positions per tile
+        static bool attr = false;
+        if (!attr) {
+            MK_CUDA(cudaFuncSetAttribute(mla_tc::mla_absorbed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla_tc::SM_TOTAL));
+            attr = true;
+        }
+        const int nt64 = (max_n + mla_tc::TJ - 1) / mla_tc::TJ;
+        int ns = ctx->sm_count / nq;
+        if (ns > nt64) ns = nt64;
+        if (ns > m->max_split) ns = m->max_split;
+        if (ns < 1) ns = 1;
+        mla_tc::mla_absorbed_tc_kernel<<<dim3((unsigned)ns, (unsigned)nq), mla_tc::THREADS, mla_tc::SM_TOTAL, ctx->stream>>>(
+            m->vq, m->vs, m->cap, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0,
+            scale, ns, m->part_m, m->part_l, m->part_o, out);
+        ctx->launches++;
+        if (ns > 1) {
+            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
+            ctx->launches++;
+        }
+        MK_CUDA(cudaGetLastError());
+        return MK_OK;
+    }
     const int ntiles = (max_n + 31) / 32;
     int nsplit = (int)mk_ceil_div((int64_t)ctx->sm_count * 32, (int64_t)nq * m->H);
     if (nsplit > ntiles) nsplit = ntiles;

@@ -83,6 +83,47 @@ moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restri
     }
 }
 
+// Same arithmetic for small token counts, organized for latency: one CTA per
+// (expert, block of TB tokens) stages the expert's router row and the token rows in
+// shared memory with coalesced 128-bit loads (all in flight at once), then 8 lanes per
+// token run the 8 accumulator chains out of shared memory.
+template <int TB>
+__global__ void __launch_bounds__(256)
+moe_router_logits_smem_kernel(const float *__restrict__ gate_w, const float *__restrict__ x, float *__restrict__ logits,
+                              int n_experts, int d, int n_tokens) {
+    extern __shared__ __align__(16) float rsm[];
+    const int xstride = d + 8; // shifts the banks of consecutive token rows
+    float *ws = rsm, *xsm = rsm + d;
+    const int e = blockIdx.x, tok0 = blockIdx.y * TB;
+    const float4 *wsrc = (const float4 *)(gate_w + (size_t)e * d);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) ((float4 *)ws)[i] = __ldg(wsrc + i);
+#pragma unroll
+    for (int t = 0; t < TB; ++t) {
+        if (tok0 + t < n_tokens) {
+            const float4 *xsrc = (const float4 *)(x + (size_t)(tok0 + t) * d);
+            for (int i = threadIdx.x; i < d / 4; i += blockDim.x) ((float4 *)(xsm + t * xstride))[i] = __ldg(xsrc + i);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    const int lane = threadIdx.x, sub = lane >> 3, j = lane & 7;
+    const bool tv = sub < TB && tok0 + sub < n_tokens;
+    const float *xr = xsm + (tv ? sub : 0) * xstride;
+    float acc = 0.0f;
+    const int full = d & ~7;
+#pragma unroll 8
+    for (int c = 0; c < full; c += 8) acc = __fadd_rn(acc, __fmul_rn(ws[c + j], xr[c + j]));
+    const int base = lane & ~7;
+    const float v1 = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 1));
+    const float p01 = __shfl_sync(0xFFFFFFFFu, v1, base + 0), p23 = __shfl_sync(0xFFFFFFFFu, v1, base + 2);
+    const float p45 = __shfl_sync(0xFFFFFFFFu, v1, base + 4), p67 = __shfl_sync(0xFFFFFFFFu, v1, base + 6);
+    float sres = __fadd_rn(__fadd_rn(__fadd_rn(p01, p23), p45), p67);
+    if (j == 0 && tv) {
+        for (int c = full; c < d; ++c) sres = __fadd_rn(sres, __fmul_rn(ws[c], xr[c]));
+        logits[(size_t)(tok0 + sub) * n_experts + e] = sres;
+    }
+}
+
 // ------------------------------------------------------------------ top-k
 // One warp per token.  score = 1/(1+exp(-l)), key = score + bias; the top_k by
 // (key descending, index ascending) in that order is what the engine's running
@@ -489,7 +530,20 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
     {
         mk_prof_scope prof(ctx, MK_PROF_ROUTER);
         const int ewarps = (E + 3) / 4;
-        if (n >= 4) {
+        if (n <= 16 && ((size_t)m->d * 5 + 32) * sizeof(float) <= 200 * 1024) {
+            // latency path: rows staged in shared memory
+            if (n <= 2) {
+                const size_t sm1 = ((size_t)m->d + (m->d + 8)) * sizeof(float);
+                static bool attr1 = false;
+                if (!attr1) { cudaFuncSetAttribute(moe_router_logits_smem_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr1 = true; }
+                moe_router_logits_smem_kernel<1><<<dim3((unsigned)E, (unsigned)n), 256, sm1, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+            } else {
+                const size_t sm4 = ((size_t)m->d + 4 * (size_t)(m->d + 8)) * sizeof(float);
+                static bool attr4 = false;
+                if (!attr4) { cudaFuncSetAttribute(moe_router_logits_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr4 = true; }
+                moe_router_logits_smem_kernel<4><<<dim3((unsigned)E, (unsigned)mk_ceil_div(n, 4)), 256, sm4, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+            }
+        } else if (n >= 4) {
             const int64_t warps = (int64_t)ewarps * mk_ceil_div(n, 4);
             moe_router_logits_kernel<4><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
         } else {

@@ -125,6 +125,12 @@ __device__ __forceinline__ float acc_term(float acc, int idot, float sw, float s
     return __fadd_rn(acc, __fmul_rn(__fmul_rn(sw, sx), (float)idot));
 }
 
+// the same term with one fused multiply-add; used wherever the CPU's exact bits are
+// not promised (both schedules use it, so they still agree with each other)
+__device__ __forceinline__ float acc_term_fast(float acc, int idot, float sw, float sx) {
+    return fmaf((float)idot, sw * sx, acc);
+}
+
 // ---- spread schedule.  `tile`: tiled values of this row tile; `sc`: its scales;
 // groups ks, ks+KS, ... < ngroups are processed.  Lane (g,t) feeds MMA column g =
 // slot (g&1) of block (g>>1): `xrow` is the q8 row of this lane's slot (nullptr
@@ -183,16 +189,16 @@ __device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile,
         if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
         if constexpr (X2) {
             const float sx = __ldg(xs0 + b);
-            acc[0][0] = acc_term(acc[0][0], d0 * 128 + d1, sg, sx);
-            acc[1][0] = acc_term(acc[1][0], d2 * 128 + d3, sh, sx);
+            acc[0][0] = acc_term_fast(acc[0][0], d0 * 128 + d1, sg, sx);
+            acc[1][0] = acc_term_fast(acc[1][0], d2 * 128 + d3, sh, sx);
         } else {
             const float sx0 = __ldg(xs0 + b);
-            acc[0][0] = acc_term(acc[0][0], d0, sg, sx0);
-            acc[1][0] = acc_term(acc[1][0], d2, sh, sx0);
+            acc[0][0] = acc_term_fast(acc[0][0], d0, sg, sx0);
+            acc[1][0] = acc_term_fast(acc[1][0], d2, sh, sx0);
             if constexpr (NSLOT == 2) {
                 const float sx1 = __ldg(xs1 + b);
-                acc[0][1] = acc_term(acc[0][1], d1, sg, sx1);
-                acc[1][1] = acc_term(acc[1][1], d3, sh, sx1);
+                acc[0][1] = acc_term_fast(acc[0][1], d1, sg, sx1);
+                acc[1][1] = acc_term_fast(acc[1][1], d3, sh, sx1);
             }
         }
     };
@@ -245,6 +251,10 @@ __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile
     const bool xvalid = xcol != nullptr;
     const int8_t *xp = xvalid ? xcol + t * 8 : k.zeros;
     const uint32_t xstep = xvalid ? 32u : 0u;
+    auto term = [](float acc_, int idot, float sw, float sx) {
+        if constexpr (ORDERED) return acc_term(acc_, idot, sw, sx);
+        else return acc_term_fast(acc_, idot, sw, sx);
+    };
     auto process = [&](const Group<WF> &grp, int64_t i) {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -259,15 +269,15 @@ __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile
             float(&a)[4] = part[ORDERED ? 0 : m];
             if constexpr (X2) {
                 const float sx = xs_a ? __ldg(xs_a + b) : 0.0f;
-                a[0] = acc_term(a[0], d0 * 128 + d1, sg, sx);
-                a[2] = acc_term(a[2], d2 * 128 + d3, sh, sx);
+                a[0] = term(a[0], d0 * 128 + d1, sg, sx);
+                a[2] = term(a[2], d2 * 128 + d3, sh, sx);
             } else {
                 const float sxa = xs_a ? __ldg(xs_a + b) : 0.0f;
                 const float sxb = xs_b ? __ldg(xs_b + b) : 0.0f;
-                a[0] = acc_term(a[0], d0, sg, sxa);
-                a[1] = acc_term(a[1], d1, sg, sxb);
-                a[2] = acc_term(a[2], d2, sh, sxa);
-                a[3] = acc_term(a[3], d3, sh, sxb);
+                a[0] = term(a[0], d0, sg, sxa);
+                a[1] = term(a[1], d1, sg, sxb);
+                a[2] = term(a[2], d2, sh, sxa);
+                a[3] = term(a[3], d3, sh, sxb);
             }
         }
     };
