@@ -32,6 +32,9 @@ if ROOT not in sys.path:
 VOCAB, HIDDEN = 163840, 7168
 SIGMA_W = 0.02
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the lm_head kernel at N=1, from the
+# ncu capture summarised in profiles/lm_head_q8_gemv_163840x7168.md (1.321224 GB + 4.7 MB)
+NCU_TRAFFIC_PER_LAUNCH_N1 = 1.3259e9
 CPU_SAMPLE_ROWS = 32768  # bounded sample of the workload for the CPU legs (235 MB of int8, > any LLC)
 
 
@@ -196,12 +199,12 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()          # nvidia-smi needs a moment to start: begin before the warm-up
     for i in range(args.warmup):
         step(i)
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches0 = ctx.launches
     ctx.prof_enable(True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -215,7 +218,6 @@ def run_gpu(args):
     kn, kms = ctx.prof_read("lm_head")
     ctx.prof_enable(False)
     launches = ctx.launches - launches0
-    clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -238,6 +240,7 @@ def run_gpu(args):
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_dt = float(te.item())
+    clocks = sampler.stop() if rank == 0 else None   # covers warm-up, the timed region and the end-to-end loop
 
     alg_step = algorithmic_bytes(rows, HIDDEN, batch) * world
     value = alg_step / (ms_step * 1e-3) / 1e9
@@ -260,7 +263,8 @@ def run_gpu(args):
                              + (f" ({copies} rotating copies of the shard)" if copies > 1 else ""),
                        "algorithmic_bytes_per_step": alg_step},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / peak) if achieved else None,
+                         "traffic": NCU_TRAFFIC_PER_LAUNCH_N1 / world if batch == 1 else None,
                          "peak_kind": peak_kind, "kernel": "qgemv_spread_kernel<q8_0>",
                          "kernel_ms": kern_ms, "kernel_launches": kn, "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
             "cpu_baseline": cb,

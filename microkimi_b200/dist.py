@@ -135,3 +135,25 @@ def shard_tokens(n_tokens, world, rank):
     base, rem = divmod(n_tokens, world)
     lo = rank * base + min(rank, rem)
     return lo, lo + base + (1 if rank < rem else 0)
+
+
+class EpMoeLayer:
+    """Expert-parallel MoE layer on this rank's GPU: the router is replicated, routed experts
+    are block-partitioned over the ranks, the shared expert lives on every rank and serves
+    the rank's own tokens.  `layer` is an ops.MoeLayer built with None for the experts that
+    are not resident here."""
+
+    def __init__(self, layer, group=None):
+        self.layer, self.group = layer, group
+
+    def forward(self, x_local):
+        """x_local [n, d] (torch CUDA, the token rows whose home is this rank) -> [n, d]."""
+        layer = self.layer
+        if x_local.shape[0] > 0:
+            ids, w = layer.route(x_local)
+        else:
+            ids = torch.empty((0, layer.top_k), dtype=torch.int32, device=x_local.device)
+            w = torch.empty((0, layer.top_k), dtype=torch.float32, device=x_local.device)
+        return ep_moe_forward(x_local, ids, w, layer.n_experts, layer.experts_dev,
+                              lambda outs, n, slots: layer.combine_dev(outs, n, slots),
+                              group=self.group, shared_expert=layer.has_shared)

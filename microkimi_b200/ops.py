@@ -308,6 +308,16 @@ class MoeLayer:
 
     def route(self, x, want_logits=False):
         """Router only: (ids [n, top_k] int32, weights [n, top_k] f32[, logits [n, E]])."""
+        if _is_torch_cuda(x):
+            import torch
+            xs = x.reshape(-1, self.d)
+            n = xs.shape[0]
+            ids = torch.empty((n, self.top_k), dtype=torch.int32, device=x.device)
+            w = torch.empty((n, self.top_k), dtype=torch.float32, device=x.device)
+            lg = torch.empty((n, self.n_experts), dtype=torch.float32, device=x.device) if want_logits else None
+            _l.check(self.ctx._L.mk_moe_route_dev(self.ctx._h, self._h, C.c_void_p(xs.data_ptr()), n, C.c_void_p(ids.data_ptr()),
+                                                  C.c_void_p(w.data_ptr()), C.c_void_p(lg.data_ptr()) if want_logits else None))
+            return (ids, w, lg) if want_logits else (ids, w)
         x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.d)
         n = x.shape[0]
         ids = np.empty((n, self.top_k), np.int32)

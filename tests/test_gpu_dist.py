@@ -1,0 +1,78 @@
+"""Multi-GPU tests (NCCL, one process per GPU): the vocab-sharded lm_head and the
+expert-parallel MoE must give the bits a single GPU gives.  Skipped with fewer than 2 GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    import microkimi_b200 as mk
+    from microkimi_b200 import dist as mkd
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dev = torch.device("cuda", rank)
+        ctx = mk.Context(rank)
+        mk.Context._default = ctx
+        ctx.use_torch_stream()
+        g = torch.Generator(device="cpu").manual_seed(7)
+        # ---- lm_head, vocab-sharded
+        vocab, d, batch = 4096, 512, 3
+        wf = (torch.randn((vocab, d), generator=g) * 0.02).numpy()
+        x = torch.randn((batch, d), generator=g)
+        lo, hi = mkd.vocab_shard(vocab, world, rank)
+        head = mk.Q8Head.from_f32(np.ascontiguousarray(wf[lo:hi]), hi - lo, d, ctx=ctx)
+        full = mkd.gather_logits(head.matvec(x.to(dev)), vocab)
+        single = mk.Q8Head.from_f32(wf, vocab, d, ctx=ctx).matvec(x.to(dev))
+        torch.cuda.synchronize()
+        ok_head = torch.equal(full, single) and torch.equal(mkd.greedy_token(full).cpu().long(), single.argmax(1).cpu())
+        # ---- MoE, expert-parallel, tokens sharded
+        E, k, dm, inter, n_tok = 16, 4, 256, 128, 11
+        gw = (torch.randn((E, dm), generator=g) * 0.02).numpy()
+
+        def rw(rows, cols):
+            p = torch.randint(0, 256, (rows, cols // 2), generator=g, dtype=torch.uint8).numpy()
+            s = torch.randint(118, 124, (rows, cols // 32), generator=g, dtype=torch.uint8).numpy()
+            return mk.MxFp4Weight(p, s, rows, cols, ctx=ctx)
+        experts = [(rw(inter, dm), rw(dm, inter), rw(inter, dm)) for _ in range(E + 1)]
+        xt = torch.randn((n_tok, dm), generator=g).to(dev)
+        whole = mk.MoeLayer(gw, None, experts[:-1], experts[-1], k, ctx=ctx)
+        ref = whole.moe_forward(xt)
+        elo, ehi = mkd.local_expert_range(E, world, rank)
+        mine = [experts[e] if elo <= e < ehi else None for e in range(E)]
+        ep = mkd.EpMoeLayer(mk.MoeLayer(gw, None, mine, experts[-1], k, ctx=ctx))
+        tlo, thi = mkd.shard_tokens(n_tok, world, rank)
+        out = ep.forward(xt[tlo:thi].contiguous())
+        torch.cuda.synchronize()
+        ok_moe = torch.equal(out, ref[tlo:thi]) and ctx.status_word() == 0
+        ret[rank] = (bool(ok_head), bool(ok_moe))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_lm_head_and_expert_parallel_moe_match_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        assert ret[r] == (True, True), f"rank {r}: {ret[r]}"
