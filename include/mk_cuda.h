@@ -83,8 +83,9 @@ int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
 
 /* Tuning knobs, for measurement only (defaults are chosen per shape):
  *   "force_ks" : K split of the matvec kernels, one of 0 (auto), 1, 2, 4, 8.
- *   "mla_no_tc": 1 = run absorbed-layout attention on the CUDA-core kernel instead of
- *                the tensor-core one (exact int32 block dots, much slower). */
+ *   "mla_no_tc": 1 = run attention on the generic one-warp-per-head CUDA-core kernel
+ *                instead of the specialised ones (tensor-core kernel of the absorbed
+ *                layout, 8-heads-per-CTA kernel of the per-head layout at vd = 128). */
 int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value);
 
 /* Per-category kernel timing with CUDA events on the context's stream, the

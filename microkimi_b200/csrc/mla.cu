@@ -31,6 +31,8 @@ struct mk_mla {
     int nb, nbv, NC, RC; // nope/32, vd/32, nope/16, rope/4
     int8_t *kqt; float *kst; float *krt;   // position-tiled K side
     int8_t *vq; float *vs;                 // natural V side (absorbed: the full latent row, its first vd columns are V)
+    unsigned char *recs; int rec_bytes;    // per-head layout: one record per (tile, head), see MlaDev
+    float *rope_scores;                    // per-head layout: [nseq][H][T*32] rope part of the scores of the current call
     int vrow;           // bytes per (position, kv head) of vq: vd (per-head) or nope (absorbed)
     int vsrow;          // scales per (position, kv head) of vs
     int *npos_dev;      // [nseq] positions held (device copy, for the batch call)
@@ -52,6 +54,25 @@ __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
 struct MlaDev {
     int H, kvh, nope, rope, vd, cap, T, nb, nbv, NC, RC, vrow, vsrow;
     int8_t *kqt; float *kst; float *krt; int8_t *vq; float *vs;
+    // per-head layout: ONE contiguous record per (position tile, head) instead of the arrays above:
+    //   [kq: NC chunks x 32 positions x 16 B][ks: nb x 32 f32][vq: 32 positions x vd B][vs: 32 x nbv f32]
+    // so that a (tile, head) is a single bulk copy.  recs == nullptr: separate arrays (absorbed layout).
+    unsigned char *recs;
+    int rec_bytes, off_ks, off_vq, off_vs;
+    __device__ __forceinline__ int8_t *kq_tile(int64_t th) const {
+        return recs ? (int8_t *)(recs + th * rec_bytes) : kqt + th * NC * 512;
+    }
+    __device__ __forceinline__ float *ks_tile(int64_t th) const {
+        return recs ? (float *)(recs + th * rec_bytes + off_ks) : kst + th * nb * 32;
+    }
+    __device__ __forceinline__ int8_t *v_row(int seq, int j, int hk) const {
+        return recs ? (int8_t *)(recs + (((int64_t)seq * T + (j >> 5)) * kvh + hk) * rec_bytes + off_vq + (j & 31) * vd)
+                    : vq + (((int64_t)seq * cap + j) * kvh + hk) * vrow;
+    }
+    __device__ __forceinline__ float *vs_row(int seq, int j, int hk) const {
+        return recs ? (float *)(recs + (((int64_t)seq * T + (j >> 5)) * kvh + hk) * rec_bytes + off_vs) + (j & 31) * nbv
+                    : vs + (((int64_t)seq * cap + j) * kvh + hk) * vsrow;
+    }
 };
 
 // ------------------------------------------------------------------ append
@@ -90,14 +111,15 @@ mla_append_kernel(const MlaDev c, int seq, int pos0, int n, const float *__restr
     const int64_t th = ((int64_t)seq * c.T + tile) * c.kvh + h;
     if (is_k) {
         const int ch = b * 2 + (lane >> 4);
-        if ((lane & 3) == 0) *(uint32_t *)(c.kqt + ((th * c.NC + ch) * 32 + p) * 16 + (lane & 15)) = pk;
-        if (lane == 0) c.kst[(th * c.nb + b) * 32 + p] = dx;
+        if ((lane & 3) == 0) *(uint32_t *)(c.kq_tile(th) + (ch * 32 + p) * 16 + (lane & 15)) = pk;
+        if (lane == 0) c.ks_tile(th)[b * 32 + p] = dx;
     }
     if (!is_k || absorbed) {
         const int vb = absorbed ? b : b - c.nb;
-        const int64_t row = ((int64_t)seq * c.cap + j) * c.kvh + h;
-        if ((lane & 3) == 0) *(uint32_t *)(c.vq + row * c.vrow + vb * 32 + lane) = pk;
-        if (lane == 0) c.vs[row * c.vsrow + vb] = dx;
+        // records keep V as unsigned bytes (value + 128): the attention kernel converts them
+        // to f32 without a subtraction per element
+        if ((lane & 3) == 0) *(uint32_t *)(c.v_row(seq, j, h) + vb * 32 + lane) = c.recs ? (pk ^ 0x80808080u) : pk;
+        if (lane == 0) c.vs_row(seq, j, h)[vb] = dx;
     }
 }
 // rope part of K, f32, stored once per position from head 0 (src/model.rs:1592-1593)
@@ -119,8 +141,8 @@ __global__ void mla_export_kernel(const MlaDev c, int seq, int n, int8_t *kq, fl
         const int h = (int)((idx / c.nope) % c.kvh);
         const int j = (int)(idx / ((int64_t)c.nope * c.kvh));
         const int64_t th = ((int64_t)seq * c.T + (j >> 5)) * c.kvh + h;
-        if (kq) kq[idx] = c.kqt[((th * c.NC + (e >> 4)) * 32 + (j & 31)) * 16 + (e & 15)];
-        if (ks && (e & 31) == 0) ks[idx / 32] = c.kst[(th * c.nb + (e >> 5)) * 32 + (j & 31)];
+        if (kq) kq[idx] = c.kq_tile(th)[((e >> 4) * 32 + (j & 31)) * 16 + (e & 15)];
+        if (ks && (e & 31) == 0) ks[idx / 32] = c.ks_tile(th)[(e >> 5) * 32 + (j & 31)];
     }
     if (kr && idx < (int64_t)n * c.rope) {
         const int r = (int)(idx % c.rope), j = (int)(idx / c.rope);
@@ -129,9 +151,10 @@ __global__ void mla_export_kernel(const MlaDev c, int seq, int n, int8_t *kq, fl
     const int64_t nv = (int64_t)n * c.kvh * c.vd;
     if (vq && idx < nv) {
         const int e = (int)(idx % c.vd);
-        const int64_t row = (int64_t)seq * c.cap * c.kvh + idx / c.vd;
-        vq[idx] = c.vq[row * c.vrow + e];
-        if (vs && (e & 31) == 0) vs[idx / 32] = c.vs[row * c.vsrow + (e >> 5)];
+        const int hv_ = (int)((idx / c.vd) % c.kvh);
+        const int jv = (int)(idx / ((int64_t)c.vd * c.kvh));
+        vq[idx] = c.recs ? (int8_t)(c.v_row(seq, jv, hv_)[e] ^ (int8_t)0x80) : c.v_row(seq, jv, hv_)[e];
+        if (vs && (e & 31) == 0) vs[idx / 32] = c.vs_row(seq, jv, hv_)[e >> 5];
     }
 }
 
@@ -183,8 +206,8 @@ mla_attend_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__
             const int64_t th = ((int64_t)seq * c.T + tile) * c.kvh + hk;
             // ---- phase 1: lane = position
             float acc = 0.0f;
-            const uint4 *kq = (const uint4 *)c.kqt + th * c.NC * 32 + lane;
-            const float *ks = c.kst + th * c.nb * 32 + lane;
+            const uint4 *kq = (const uint4 *)c.kq_tile(th) + lane;
+            const float *ks = c.ks_tile(th) + lane;
             for (int g = 0; g < c.nb; ++g) {
                 int idot = 0;
 #pragma unroll
@@ -232,15 +255,13 @@ mla_attend_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__
             for (int i = 0; i < VW * 4; ++i) o[i] *= corr;
             // ---- phase 2: lane = 4 output columns per 128-column group
             const int cnt = min(32, n - tile * 32);
-            const int64_t row0 = ((int64_t)seq * c.cap + tile * 32) * c.kvh + hk;
             for (int i = 0; i < cnt; ++i) {
                 const float pi = __shfl_sync(0xFFFFFFFFu, p, i);
-                const int64_t row = row0 + (int64_t)i * c.kvh;
-                const uint32_t *vw = (const uint32_t *)(c.vq + row * c.vrow);
-                const float *vsc = c.vs + row * c.vsrow;
+                const uint32_t *vw = (const uint32_t *)c.v_row(seq, tile * 32 + i, hk);
+                const float *vsc = c.vs_row(seq, tile * 32 + i, hk);
 #pragma unroll
                 for (int w = 0; w < VW; ++w) {
-                    const uint32_t word = __ldg(vw + w * 32 + lane) ^ 0x80808080u; // bytes + 128
+                    const uint32_t word = __ldg(vw + w * 32 + lane) ^ (c.recs ? 0u : 0x80808080u); // bytes + 128
                     const float ps = pi * __ldg(vsc + w * 4 + (lane >> 3));
                     // int8 -> f32 without a convert: 0x4B0000xx is 8388608 + xx
                     o[w * 4 + 0] = fmaf(ps, __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7440)) - 8388736.0f, o[w * 4 + 0]);
@@ -263,6 +284,251 @@ mla_attend_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__
 #pragma unroll
         for (int w = 0; w < VW; ++w)
             ((float4 *)(part_o + pi * c.vd))[w * 32 + lane] = make_float4(o[w * 4], o[w * 4 + 1], o[w * 4 + 2], o[w * 4 + 3]);
+    }
+}
+
+// ------------------------------------------------------------------ rope scores (per-head layout)
+// The f32 rope row of a position is shared by all heads, so its dot with every head's
+// rope query is computed once per call by this small kernel instead of once per head in
+// the streaming kernel: rs[(seq_row, head)][position] = dot(q_rope[head], kr[position])
+// in the 8-accumulator order of the engine's dot() (src/model.rs:63-82).
+// grid = (position tiles, query rows); one CTA stages the 32 rope rows and all rope queries.
+__global__ void __launch_bounds__(256)
+mla_rope_scores_kernel(const MlaDev c, const float *__restrict__ q_f32, const int *__restrict__ npos_arr, int npos_fixed,
+                       int seq0, float *__restrict__ rs) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tile = blockIdx.x, bi = blockIdx.y, seq = seq0 + bi;
+    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    if (tile * 32 >= n) return;
+    float4 *kr_s = (float4 *)smem;                       // [RC][32]
+    float4 *q_s = kr_s + c.RC * 32;                      // [H][RC]
+    const int hd = c.nope + c.rope;
+    const float4 *src = (const float4 *)c.krt + ((int64_t)seq * c.T + tile) * c.RC * 32;
+    for (int i = threadIdx.x; i < c.RC * 32; i += blockDim.x) kr_s[i] = __ldg(src + i);
+    for (int i = threadIdx.x; i < c.H * c.RC; i += blockDim.x)
+        q_s[i] = *(const float4 *)(q_f32 + ((int64_t)bi * c.H + i / c.RC) * hd + c.nope + (i % c.RC) * 4);
+    __syncthreads();
+    const int p = threadIdx.x & 31;
+    for (int h = threadIdx.x >> 5; h < c.H; h += blockDim.x >> 5) {
+        float a8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int c4 = 0; c4 < c.RC; c4 += 2) {
+            const float4 k0 = kr_s[c4 * 32 + p], k1 = kr_s[(c4 + 1) * 32 + p];
+            const float4 q0 = q_s[h * c.RC + c4], q1 = q_s[h * c.RC + c4 + 1];
+            a8[0] = __fadd_rn(a8[0], __fmul_rn(q0.x, k0.x)); a8[1] = __fadd_rn(a8[1], __fmul_rn(q0.y, k0.y));
+            a8[2] = __fadd_rn(a8[2], __fmul_rn(q0.z, k0.z)); a8[3] = __fadd_rn(a8[3], __fmul_rn(q0.w, k0.w));
+            a8[4] = __fadd_rn(a8[4], __fmul_rn(q1.x, k1.x)); a8[5] = __fadd_rn(a8[5], __fmul_rn(q1.y, k1.y));
+            a8[6] = __fadd_rn(a8[6], __fmul_rn(q1.z, k1.z)); a8[7] = __fadd_rn(a8[7], __fmul_rn(q1.w, k1.w));
+        }
+        rs[((int64_t)bi * c.H + h) * c.T * 32 + tile * 32 + p] =
+            __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(a8[0], a8[1]), __fadd_rn(a8[2], a8[3])), __fadd_rn(a8[4], a8[5])),
+                      __fadd_rn(a8[6], a8[7]));
+    }
+}
+
+// ------------------------------------------------------------------ per-head layout, vd == 128
+// One warp per (sequence, head, KV split), 8 warps (8 consecutive heads, same split) per CTA.
+// The record of a (position tile, head) - 9216 contiguous bytes at the micro head dims -
+// is brought into shared memory by TWO bulk async copies (cp.async.bulk, completion on an
+// mbarrier each): its K half (int8 rows + scales) and its V half.  Each warp runs its own
+// pipeline with one buffer per half: while phase 1 reads K(t), V(t) is in flight; while
+// phase 2 reads V(t), K(t+1) is in flight - half a record per warp is always outstanding,
+// 9.2 KB of shared memory per warp let 3 CTAs share an SM, and no CTA-wide barrier is
+// needed.  Every mbarrier wait is bounded; on expiry the kernel records MK_ERR_TIMEOUT
+// and returns.
+// Phase 2 reads V with 16-byte shared loads: 8 lanes cover the 128 columns of one position,
+// the 4 lane groups take 4 positions at a time, partial accumulators are summed at the end.
+#define PH_WARPS 4
+#define PH_WAIT_LIMIT (1 << 22)
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false (and the status word set) when the copy never lands
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int32_t *status) {
+    for (int it = 0; it < PH_WAIT_LIMIT; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicCAS(status, 0, MK_ERR_TIMEOUT);
+    return false;
+}
+// global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned), no multicast
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(PH_WARPS * 32, 5)
+mla_attend_ph128_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__restrict__ qs, int64_t ldq, int64_t q_nbp,
+                        const float *__restrict__ rope_scores, const int *__restrict__ npos_arr, int npos_fixed, int seq0,
+                        float scale, int nsplit, float *__restrict__ part_m, float *__restrict__ part_l,
+                        float *__restrict__ part_o, float *__restrict__ out, int32_t *__restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * PH_WARPS + warp, bi = blockIdx.z, seq = seq0 + bi, split = blockIdx.x;
+    const bool hv = h < c.H;
+    const int hh = hv ? h : c.H - 1;
+    // shared memory: [warp][record: K half | V half] | [warp][query staging] | [warp][2] mbarriers (K, V)
+    const int rec = c.rec_bytes;
+    const int qw_bytes = c.nope + ((c.nb * 4 + 15) & ~15);
+    unsigned char *stage0 = smem + (size_t)warp * rec;
+    unsigned char *mine = smem + (size_t)PH_WARPS * rec + (size_t)warp * qw_bytes;
+    uint64_t *bars = (uint64_t *)(smem + (size_t)PH_WARPS * rec + (size_t)PH_WARPS * qw_bytes) + warp * 2;
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+    const uint32_t st0 = (uint32_t)__cvta_generic_to_shared(stage0);
+    uint4 *qq_s = (uint4 *)mine;
+    float *qs_s = (float *)(mine + c.nope);
+    if (lane == 0) {
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {
+        const int64_t qrow = (int64_t)bi * c.H + hh;
+        for (int i = lane; i < c.NC; i += 32) qq_s[i] = ((const uint4 *)(qq + qrow * ldq))[i];
+        for (int i = lane; i < c.nb; i += 32) qs_s[i] = qs[qrow * q_nbp + i];
+    }
+    __syncwarp();
+    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int ntiles = (n + 31) >> 5;
+    const int tps = (ntiles + nsplit - 1) / nsplit;
+    const int t0 = split * tps, t1 = min(t0 + tps, ntiles);
+    float m = -INFINITY, l = 0.0f;
+    float o[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = 0.0f;
+    const int cg = lane & 7, pg = lane >> 3; // column group (16 columns), position subgroup
+    const unsigned char *rec_base = c.recs + (((int64_t)seq * c.T) * c.kvh + hh) * rec;
+    const int64_t rec_step = (int64_t)c.kvh * rec; // next tile, same head
+
+    const uint32_t kbytes = (uint32_t)c.off_vq, vbytes = (uint32_t)(rec - c.off_vq); // K half, V half
+    if (lane == 0 && t0 < t1) {
+        const unsigned char *src = rec_base + (int64_t)t0 * rec_step;
+        mbar_expect_tx(bar0, kbytes);
+        bulk_g2s(st0, src, kbytes, bar0);
+        mbar_expect_tx(bar0 + 8, vbytes);
+        bulk_g2s(st0 + kbytes, src + kbytes, vbytes, bar0 + 8);
+    }
+    bool alive = true;
+    const float *rs_row = rope_scores + ((int64_t)bi * c.H + hh) * c.T * 32;
+    for (int tile = t0, it = 0; tile < t1; ++tile, ++it) {
+        const float s_rope = __ldg(rs_row + tile * 32 + lane); // issued before the wait: its latency overlaps
+        if (!mbar_wait_bounded(bar0, it & 1, status)) { alive = false; break; }
+        const unsigned char *sb = stage0;
+        const int j = tile * 32 + lane;
+        const bool valid = j < n;
+        // ---- phase 1: lane = position
+        float acc = 0.0f;
+        const uint4 *kq = (const uint4 *)sb + lane;
+        const float *ks = (const float *)(sb + c.off_ks) + lane;
+        for (int g = 0; g < c.nb; ++g) {
+            int idot = 0;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const uint4 kw = kq[(g * 2 + cc) * 32];
+                const uint4 qw = qq_s[g * 2 + cc];
+                idot = dp4a_s8(kw.x, qw.x, idot);
+                idot = dp4a_s8(kw.y, qw.y, idot);
+                idot = dp4a_s8(kw.z, qw.z, idot);
+                idot = dp4a_s8(kw.w, qw.w, idot);
+            }
+            acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(qs_s[g], ks[g * 32]), (float)idot));
+        }
+        __syncwarp(); // every lane has read the K half: refill it with the next tile's
+        if (lane == 0 && tile + 1 < t1) {
+            // order this warp's generic-proxy reads before the async-proxy write
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar0, kbytes);
+            bulk_g2s(st0, rec_base + (int64_t)(tile + 1) * rec_step, kbytes, bar0);
+        }
+        float s = s_rope;
+        s = __fmul_rn(__fadd_rn(s, acc), scale);
+        if (!valid) s = -INFINITY;
+        float tm = s;
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xFFFFFFFFu, tm, of));
+        const float m_new = fmaxf(m, tm);
+        const float corr = expf(m - m_new);
+        const float p = valid ? expf(s - m_new) : 0.0f;
+        float tl = p;
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1) tl += __shfl_xor_sync(0xFFFFFFFFu, tl, of);
+        l = l * corr + tl;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] *= corr;
+        // ---- phase 2: positions past the end have p = 0 and stale-but-finite int8 bytes
+        if (!mbar_wait_bounded(bar0 + 8, it & 1, status)) { alive = false; break; }
+        const uint4 *vq4 = (const uint4 *)(sb + c.off_vq);
+        const float *vsc = (const float *)(sb + c.off_vs);
+        // A stored byte u = v + 128 placed in the low byte of a zero word IS the f32 denormal
+        // u * 2^-149 (exact); with the weight pre-scaled by 2^100 one FMA per element
+        // accumulates p*sc*u * 2^-49 exactly as it would p*sc*u - no int->float convert and
+        // no subtraction per element.  The -128 * sum(p*sc) of the bias is removed once per tile.
+        float ssum = 0.0f;
+#pragma unroll
+        for (int i8 = 0; i8 < 8; ++i8) {
+            const int pi = i8 * 4 + pg;
+            const float pv = __shfl_sync(0xFFFFFFFFu, p, pi);
+            const uint4 vw = vq4[pi * 8 + cg];
+            const float sc = vsc[pi * c.nbv + (cg >> 1)];
+            const float ps = (pi + tile * 32 < n) ? pv * sc * 0x1p100f : 0.0f;
+            ssum += ps;
+            const uint32_t w4[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                o[w * 4 + 0] = fmaf(ps, __uint_as_float(w4[w] & 0xFFu), o[w * 4 + 0]);
+                o[w * 4 + 1] = fmaf(ps, __uint_as_float(__byte_perm(w4[w], 0u, 0x4441)), o[w * 4 + 1]);
+                o[w * 4 + 2] = fmaf(ps, __uint_as_float(__byte_perm(w4[w], 0u, 0x4442)), o[w * 4 + 2]);
+                o[w * 4 + 3] = fmaf(ps, __uint_as_float(w4[w] >> 24), o[w * 4 + 3]);
+            }
+        }
+        {
+            const float bias = ssum * 0x1p-142f; // 128 * 2^-149 per unit of the pre-scaled weight
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] -= bias;
+        }
+        __syncwarp(); // every lane has read the V half: refill it with the next tile's
+        if (lane == 0 && tile + 1 < t1) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar0 + 8, vbytes);
+            bulk_g2s(st0 + kbytes, rec_base + (int64_t)(tile + 1) * rec_step + kbytes, vbytes, bar0 + 8);
+        }
+    }
+    if (!alive) {
+        // a copy never landed: give any copy still in flight a bounded chance to finish, then leave
+        for (int k = 0; k < 2; ++k)
+            for (int itw = 0; itw < (1 << 16); ++itw)
+                if (mbar_try_wait(bar0 + 8 * k, 0) || mbar_try_wait(bar0 + 8 * k, 1)) break;
+        return;
+    }
+    // sum the 4 position subgroups (fixed order), undo the 2^-49 of the denormal trick;
+    // lanes 0..7 then hold 16 columns each
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float v = o[i];
+        v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+        v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
+        o[i] = v * 0x1p49f;
+    }
+    if (!hv || pg != 0) return;
+    if (nsplit == 1) {
+        float *dst = out + ((int64_t)bi * c.H + h) * c.vd + cg * 16;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = __fdiv_rn(o[i], l);
+    } else {
+        const int64_t pi = ((int64_t)bi * c.H + h) * nsplit + split;
+        if (cg == 0) { part_m[pi] = m; part_l[pi] = l; }
+        float4 *dst = (float4 *)(part_o + pi * c.vd + cg * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_float4(o[i * 4], o[i * 4 + 1], o[i * 4 + 2], o[i * 4 + 3]);
     }
 }
 
@@ -297,6 +563,8 @@ static MlaDev mla_dev(const mk_mla *m) {
     c.H = m->H; c.kvh = m->kvh; c.nope = m->nope; c.rope = m->rope; c.vd = m->vd; c.cap = m->cap; c.T = m->T;
     c.nb = m->nb; c.nbv = m->nbv; c.NC = m->NC; c.RC = m->RC; c.vrow = m->vrow; c.vsrow = m->vsrow;
     c.kqt = m->kqt; c.kst = m->kst; c.krt = m->krt; c.vq = m->vq; c.vs = m->vs;
+    c.recs = m->recs; c.rec_bytes = m->rec_bytes;
+    c.off_ks = m->nope * 32; c.off_vq = c.off_ks + m->nb * 128; c.off_vs = c.off_vq + m->vd * 32;
     return c;
 }
 
@@ -304,7 +572,7 @@ extern "C" int32_t mk_mla_free(mk_ctx *ctx, mk_mla *m) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr, "NULL argument");
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    void *ptrs[] = {m->kqt, m->kst, m->krt, m->vq, m->vs, m->npos_dev, m->qq, m->qs, m->part_m, m->part_l, m->part_o};
+    void *ptrs[] = {m->kqt, m->kst, m->krt, m->vq, m->vs, m->recs, m->rope_scores, m->npos_dev, m->qq, m->qs, m->part_m, m->part_l, m->part_o};
     for (void *p : ptrs) if (p) cudaFree(p);
     delete[] m->npos;
     delete m;
@@ -334,15 +602,20 @@ extern "C" int32_t mk_mla_create(mk_ctx *ctx, const mk_mla_desc *d, mk_mla **out
     m->q_nbp = mk_ceil_div(m->nb, 4) * 4;
     m->max_split = 256;
     m->npos = new (std::nothrow) int[m->nseq]();
+    const size_t bh = (size_t)m->nseq * m->H;
     const size_t tiles = (size_t)m->nseq * m->T * m->kvh;
     const size_t rows = (size_t)m->nseq * m->cap * m->kvh;
-    const size_t bh = (size_t)m->nseq * m->H;
     cudaError_t e = m->npos ? cudaSuccess : cudaErrorMemoryAllocation;
-    if (e == cudaSuccess) e = cudaMalloc(&m->kqt, tiles * m->nope * 32);
-    if (e == cudaSuccess) e = cudaMalloc(&m->kst, tiles * m->nb * 32 * 4);
+    const bool absorbed_l = d->layout == MK_MLA_ABSORBED;
+    m->rec_bytes = m->nope * 32 + m->nb * 128 + m->vd * 32 + m->nbv * 128;
+    if (e == cudaSuccess && !absorbed_l) e = cudaMalloc((void **)&m->recs, tiles * (size_t)m->rec_bytes);
+    if (e == cudaSuccess && !absorbed_l) e = cudaMemsetAsync(m->recs, 0, tiles * (size_t)m->rec_bytes, ctx->stream);
+    if (e == cudaSuccess && !absorbed_l) e = cudaMalloc(&m->rope_scores, bh * (size_t)m->T * 32 * 4);
+    if (e == cudaSuccess && absorbed_l) e = cudaMalloc(&m->kqt, tiles * m->nope * 32);
+    if (e == cudaSuccess && absorbed_l) e = cudaMalloc(&m->kst, tiles * m->nb * 32 * 4);
     if (e == cudaSuccess) e = cudaMalloc(&m->krt, (size_t)m->nseq * m->T * (m->rope > 0 ? m->rope : 4) * 32 * 4);
-    if (e == cudaSuccess) e = cudaMalloc(&m->vq, rows * m->vrow);
-    if (e == cudaSuccess) e = cudaMalloc(&m->vs, rows * m->vsrow * 4);
+    if (e == cudaSuccess && absorbed_l) e = cudaMalloc(&m->vq, rows * m->vrow);
+    if (e == cudaSuccess && absorbed_l) e = cudaMalloc(&m->vs, rows * m->vsrow * 4);
     if (e == cudaSuccess) e = cudaMalloc(&m->npos_dev, (size_t)m->nseq * 4);
     if (e == cudaSuccess) e = cudaMemsetAsync(m->npos_dev, 0, (size_t)m->nseq * 4, ctx->stream);
     if (e == cudaSuccess) e = cudaMalloc(&m->qq, bh * m->q_nbp * 32);
@@ -443,6 +716,39 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
         mla_tc::mla_absorbed_tc_kernel<<<dim3((unsigned)ns, (unsigned)nq), mla_tc::THREADS, mla_tc::SM_TOTAL, ctx->stream>>>(
             m->vq, m->vs, m->cap, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0,
             scale, ns, m->part_m, m->part_l, m->part_o, out);
+        ctx->launches++;
+        if (ns > 1) {
+            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
+            ctx->launches++;
+        }
+        MK_CUDA(cudaGetLastError());
+        return MK_OK;
+    }
+    if (m->layout == MK_MLA_PER_HEAD && m->vd == 128 && m->rope > 0 && !ctx->mla_no_tc &&
+        (size_t)PH_WARPS * m->rec_bytes + PH_WARPS * ((size_t)m->nope + m->nb * 4 + 16 + (size_t)m->rope * 4) + 256 <= 220 * 1024) {
+        const int ntiles_p = (max_n + 31) / 32;
+        const int hgroups = (int)mk_ceil_div(m->H, PH_WARPS);
+        int ns = (int)mk_ceil_div((int64_t)ctx->sm_count * 10, (int64_t)nq * hgroups);
+        if (ns > ntiles_p) ns = ntiles_p;
+        if (ns > m->max_split) ns = m->max_split;
+        if (ns < 1) ns = 1;
+        const MlaDev cph = mla_dev(m);
+        const size_t qw = (size_t)m->nope + mk_align_up((size_t)m->nb * 4, 16);
+        const size_t smem_ph = (size_t)PH_WARPS * m->rec_bytes + PH_WARPS * qw + PH_WARPS * 2 * 8 + 128;
+        {
+            const size_t smem_rs = ((size_t)m->RC * 32 + (size_t)m->H * m->RC) * 16;
+            static bool attr_rs = false;
+            if (!attr_rs) { MK_CUDA(cudaFuncSetAttribute(mla_rope_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_rs = true; }
+            MK_CHECK_ARG(smem_rs <= 200 * 1024, "rope dims too large");
+            mla_rope_scores_kernel<<<dim3((unsigned)ntiles_p, (unsigned)nq), 256, smem_rs, ctx->stream>>>(
+                cph, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, m->rope_scores);
+            ctx->launches++;
+        }
+        static bool attr_ph = false;
+        if (!attr_ph) { MK_CUDA(cudaFuncSetAttribute(mla_attend_ph128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr_ph = true; }
+        mla_attend_ph128_kernel<<<dim3((unsigned)ns, (unsigned)hgroups, (unsigned)nq), PH_WARPS * 32, smem_ph, ctx->stream>>>(
+            cph, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, m->rope_scores, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, scale, ns,
+            m->part_m, m->part_l, m->part_o, out, ctx->status_dev);
         ctx->launches++;
         if (ns > 1) {
             mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);

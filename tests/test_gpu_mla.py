@@ -104,8 +104,15 @@ def test_per_head_layout_64_heads(mk):
     dev.push(K, V)
     q = rng.standard_normal((nh, hd)).astype(np.float32)
     scale = np.float32(1.0 / np.sqrt(192.0))
+    ctx = mk.Context.default()
     for pos in (n - 1, 300):
-        assert rel(dev.mla_attn_flash_q8_mqa(q, pos, scale), ref.attn_mqa(q, pos, scale)) <= 2e-4
+        want = ref.attn_mqa(q, pos, scale)
+        assert rel(dev.mla_attn_flash_q8_mqa(q, pos, scale), want) <= 2e-4      # 8-heads-per-CTA kernel (vd = 128)
+        ctx.set_option("mla_no_tc", 1)                                          # the generic one-warp-per-head kernel
+        try:
+            assert rel(dev.mla_attn_flash_q8_mqa(q, pos, scale), want) <= 2e-4
+        finally:
+            ctx.set_option("mla_no_tc", 0)
 
 
 @pytest.mark.parametrize("nh,n", [(8, 200), (64, 1500)])
