@@ -370,7 +370,7 @@ mla_attend_ph128_kernel(const MlaDev c, const int8_t *__restrict__ qq, const flo
                         const float *__restrict__ rope_scores, const int *__restrict__ npos_arr, int npos_fixed, int seq0,
                         float scale, int nsplit, float *__restrict__ part_m, float *__restrict__ part_l,
                         float *__restrict__ part_o, float *__restrict__ out, int32_t *__restrict__ status) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y * PH_WARPS + warp, bi = blockIdx.z, seq = seq0 + bi, split = blockIdx.x;
     const bool hv = h < c.H;

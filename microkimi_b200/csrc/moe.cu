@@ -296,16 +296,19 @@ __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc,
 }
 
 // ------------------------------------------------------------------ gate / up + activation + q8 of the activation
-// grid = (inter/32, max_items).  CTA: 32 rows of w1 and the same 32 rows of w3 of
-// one expert for <= 8 pairs: warp = (matrix, 16-row half, K half).  Then warp c
+// grid = (inter/32, max_items).  CTA = 16 warps: 32 rows of w1 and the same 32 rows of w3
+// of one expert for <= 8 pairs: warp = (matrix, 16-row half, K quarter).  Then warp c
 // turns column c into the activation (src/deepseek.rs:1083-1087) and quantizes
 // its 32 values as one q8_0 block (src/q8.rs:49-69): the input of the w2 matvec.
-__global__ void __launch_bounds__(256) moe_gate_up_kernel(const MoeArgs a) {
+#ifndef MK_G1_KS
+#define MK_G1_KS 2   // K slices per 16-row tile in the gate/up kernel: CTA = 4 * MK_G1_KS warps
+#endif
+__global__ void __launch_bounds__(MK_G1_KS * 128, 8 / MK_G1_KS) moe_gate_up_kernel(const MoeArgs a) {
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __shared__ float part[8][16][8];
+    __shared__ float part[4 * MK_G1_KS][16][8];
     __shared__ const int8_t *xrow[8];
     __shared__ const float *xsrow[8];
     __shared__ int pair_s[8];
@@ -321,19 +324,21 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const MoeArgs a) {
     }
     __syncthreads();
     {
-        const int job = warp >> 1, ks = warp & 1;
+        const int job = warp / MK_G1_KS, ks = warp % MK_G1_KS;
         const int mat = (job >> 1) ? 2 : 0, half = job & 1;
         const int64_t rt = (int64_t)blockIdx.x * 2 + half;
         const void *wv = a.wv[e * 3 + mat], *ws = a.wsc[e * 3 + mat];
-        warp_tile_any<W_MXFP4>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, 2,
+        warp_tile_any<W_MXFP4>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, MK_G1_KS,
                                lane, n, xrow, xsrow, a.k, part[warp]);
     }
     __syncthreads();
     const int c = warp; // column
     if (c < n) {
         const int half = lane >> 4, r16 = lane & 15;
-        const float gate = part[(0 + half) * 2][r16][c] + part[(0 + half) * 2 + 1][r16][c];
-        const float up = part[(2 + half) * 2][r16][c] + part[(2 + half) * 2 + 1][r16][c];
+        const int jg = (0 + half) * MK_G1_KS, ju = (2 + half) * MK_G1_KS;
+        float gate = part[jg][r16][c], up = part[ju][r16][c];
+#pragma unroll
+        for (int q = 1; q < MK_G1_KS; ++q) { gate += part[jg + q][r16][c]; up += part[ju + q][r16][c]; }
         const float gl = fminf(gate, a.limit);
         const float ul = fminf(fmaxf(up, -a.limit), a.limit);
         const float ex = (float)exp((double)(-gl));
@@ -353,7 +358,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const MoeArgs a) {
 
 // ------------------------------------------------------------------ down projection
 // grid = (ceil(d/32), max_items).  CTA: 2 row tiles of w2 x 4 K slices.
-__global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
+__global__ void __launch_bounds__(256, 4) moe_down_kernel(const MoeArgs a) {
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
@@ -578,7 +583,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     int items_ub = n_pairs / 8 + (n_pairs < slots ? n_pairs : slots);
     if (items_ub > m->max_items) items_ub = m->max_items;
     if (items_ub < 1) items_ub = 1;
-    moe_gate_up_kernel<<<dim3((unsigned)(m->inter / 32), (unsigned)items_ub), 256, 0, ctx->stream>>>(a);
+    moe_gate_up_kernel<<<dim3((unsigned)(m->inter / 32), (unsigned)items_ub), MK_G1_KS * 128, 0, ctx->stream>>>(a);
     moe_down_kernel<<<dim3((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub), 256, 0, ctx->stream>>>(a);
     ctx->launches += 3;
     MK_CUDA(cudaGetLastError());
