@@ -370,20 +370,25 @@ def run_case_moe(args):
     distinct = int(torch.unique(ids).numel())
     per_expert = 3 * (inter * d // 2 + inter * d // 32)
     alg = E * d * 4 + (distinct + 1) * per_expert + 2 * B * d * 4
-    ctx.prof_enable(True)
     ms = _timed(torch, lambda i: layers[i % args.copies].moe_forward(x), args.steps, args.warmup)
+    # second pass with the per-category event pairs on (they add a few microseconds of gaps, so
+    # the headline time above is taken without them)
+    l0 = ctx.launches
+    layers[0].moe_forward(x)
+    launches = ctx.launches - l0
+    ctx.prof_enable(True)
+    _timed(torch, lambda i: layers[i % args.copies].moe_forward(x), args.steps, 0)
     n_e, ms_e = ctx.prof_read("experts")
     n_r, ms_r = ctx.prof_read("router")
     ctx.prof_enable(False)
-    calls = args.steps + args.warmup
     peak, kind = measured_peaks()
     ach = alg / (ms * 1e-3) / 1e9
     print(json.dumps({"case": "moe", "experts": E, "top_k": k, "batch": B, "copies": args.copies,
                       "distinct_experts_routed": distinct, "ms_per_layer": ms, "tokens_per_s": B / (ms * 1e-3),
-                      "experts_ms": ms_e / calls * (n_e / max(n_e, 1)) if n_e else None, "router_ms": ms_r / calls if n_r else None,
-                      "algorithmic_bytes": alg,
+                      "experts_ms": ms_e / args.steps if n_e else None, "router_ms": ms_r / args.steps if n_r else None,
+                      "launches_per_call": launches, "algorithmic_bytes": alg,
                       "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                   "peak_kind": kind, "note": "whole layer call (7 launches), not one kernel"}}), flush=True)
+                                   "peak_kind": kind, "note": "whole layer call, not one kernel"}}), flush=True)
 
 
 def run_case_mla(args):

@@ -110,6 +110,10 @@ extern "C" int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value) {
         ctx->force_ks = (int)value;
         return MK_OK;
     }
+    if (strcmp(name, "moe_no_fuse") == 0) {
+        ctx->moe_no_fuse = value != 0;
+        return MK_OK;
+    }
     if (strcmp(name, "mla_no_tc") == 0) {
         ctx->mla_no_tc = value != 0;
         return MK_OK;

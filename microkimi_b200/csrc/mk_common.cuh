@@ -79,6 +79,7 @@ struct mk_ctx {
     void *io_pinned;
     size_t io_pinned_bytes;
     int force_ks;           // 0 = choose per shape
+    int moe_no_fuse;        // 1 = separate router / top-k / plan / quantize launches also for small batches (study knob)
     int mla_no_tc;          // 1 = absorbed-layout attention on the CUDA-core kernel (study knob)
     // optional per-category event timing (mk_prof_*)
     int prof_on;

@@ -9,7 +9,8 @@
 //
 // Launches per layer call: router logits, activation quantization, top-k (+ pair
 // list), plan (group pairs by expert), gate/up (+ activation + q8 of the
-// activation), down, combine.
+// activation), down, combine.  Up to 16 tokens the first four are ONE launch
+// (moe_router_fused_kernel), 4 launches per layer call in all.
 #include "qgemv_core.cuh"
 
 using namespace mkq;
@@ -23,7 +24,7 @@ struct mk_moe {
     int64_t nbp_d, nbp_i;          // padded block counts of d and inter
     // workspace, sized for cap_rows activation rows and cap_pairs pairs
     int cap_rows, cap_pairs;
-    float *logits;                 // [rows][n_experts]
+    float *logits;                 // [3][cap_rows][n_experts]: logits, scores, selection keys
     int32_t *ids;                  // [rows][top_k]
     float *wts;                    // [rows][top_k]
     int8_t *xq; float *xs;         // q8 activations of the rows
@@ -31,6 +32,7 @@ struct mk_moe {
     int32_t *sorted;               // pair ids grouped by expert
     int32_t *items;                // [max_items][3] = expert, offset into sorted, count (<= 8)
     int32_t *n_items;              // device scalar
+    int32_t *counter;              // device scalar, 0 between calls (fused router kernel)
     int8_t *actq; float *acts;     // q8 of the expert activations, per pair
     float *outs;                   // [pairs][d]
     int max_items;
@@ -42,11 +44,25 @@ namespace {
 // logits[t][e] = dot(gate_w[e], x[t]) in the engine's order (src/model.rs:63-82):
 // 8 accumulators, element j of each 8-chunk into accumulator j with a separate
 // multiply and add, then ((a0+a1)+(a2+a3))+(a4+a5))+(a6+a7), tail sequential.
-// 8 lanes own the 8 accumulators of one (expert, token tile); a warp = 4 experts.
+// Every logits kernel also stores score = 1/(1+exp(-l)) and key = score + bias
+// (src/model.rs:2152-2156); exp() runs in double and is rounded once, which agrees
+// with a correctly rounded expf.
+__device__ __forceinline__ void router_store(float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key,
+                                             const float *__restrict__ gate_b, int64_t at, int e, float l) {
+    const float ex = (float)exp((double)(-l));
+    const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
+    logits[at] = l;
+    score[at] = sg;
+    key[at] = __fadd_rn(sg, gate_b ? gate_b[e] : 0.0f);
+}
+
+// Generic form (any d, any alignment): 8 lanes own the 8 accumulators of one
+// (expert, token tile); a warp = 4 experts.
 template <int T>
 __global__ void __launch_bounds__(256)
-moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restrict__ x, float *__restrict__ logits,
-                         int n_experts, int d, int n_tokens) {
+moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
+                         float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key, int n_experts, int d,
+                         int n_tokens) {
     const int warp_g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
     const int ewarps = (n_experts + 3) / 4;
@@ -78,99 +94,131 @@ moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restri
         float s = __fadd_rn(__fadd_rn(__fadd_rn(p01, p23), p45), p67);
         if (j == 0 && ev && tok0 + t < n_tokens) {
             for (int c = full; c < d; ++c) s = __fadd_rn(s, __fmul_rn(__ldg(w + c), __ldg(x + (size_t)(tok0 + t) * d + c)));
-            logits[(size_t)(tok0 + t) * n_experts + e] = s;
+            router_store(logits, score, key, gate_b, (int64_t)(tok0 + t) * n_experts + e, e, s);
         }
     }
 }
 
-// Same arithmetic for small token counts, organized for latency: one CTA per
-// (expert, block of TB tokens) stages the expert's router row and the token rows in
-// shared memory with coalesced 128-bit loads (all in flight at once), then 8 lanes per
-// token run the 8 accumulator chains out of shared memory.
-template <int TB>
-__global__ void __launch_bounds__(256)
-moe_router_logits_smem_kernel(const float *__restrict__ gate_w, const float *__restrict__ x, float *__restrict__ logits,
-                              int n_experts, int d, int n_tokens) {
-    extern __shared__ __align__(16) float rsm[];
-    const int xstride = d + 8; // shifts the banks of consecutive token rows
-    float *ws = rsm, *xsm = rsm + d;
-    const int e = blockIdx.x, tok0 = blockIdx.y * TB;
-    const float4 *wsrc = (const float4 *)(gate_w + (size_t)e * d);
-    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) ((float4 *)ws)[i] = __ldg(wsrc + i);
-#pragma unroll
-    for (int t = 0; t < TB; ++t) {
-        if (tok0 + t < n_tokens) {
-            const float4 *xsrc = (const float4 *)(x + (size_t)(tok0 + t) * d);
-            for (int i = threadIdx.x; i < d / 4; i += blockDim.x) ((float4 *)(xsm + t * xstride))[i] = __ldg(xsrc + i);
+// Tiled form (d a multiple of 4, rows 16-byte aligned): one CTA = NE experts x NT tokens.
+// The NE router rows and the NT token rows stream through shared memory in slices of KC
+// columns, STAGES slices in flight (cp.async); warp w owns expert (w / (NT/4)) and tokens
+// 4 (w % (NT/4)) .. +3, 8 lanes per token running the 8 accumulator chains in order.
+// Two shapes: RtBig for throughput, RtSmall (<= 4 tokens) keeps a deeper queue of the
+// router rows in flight because at small batches those come cold from HBM.
+template <int NE_, int NT_, int KC_, int STAGES_>
+struct RtShape {
+    static constexpr int NE = NE_, NT = NT_, KC = KC_, STAGES = STAGES_, ROWS = NE_ + NT_, LD = KC_ + 8;
+    static constexpr size_t SMEM = (size_t)STAGES_ * ROWS * LD * sizeof(float);
+    static_assert(NE_ * NT_ / 4 <= 8 && NT_ % 4 == 0, "one warp per (expert, 4 tokens), 8 warps");
+};
+using RtBig = RtShape<2, 16, 256, 3>;
+using RtSmall = RtShape<1, 4, 512, 6>;
+
+__device__ __forceinline__ void rt_cp16(float *dst, const float *src) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src) : "memory");
+}
+
+// returns the logit in the lanes with (lane & 7) == 0 of valid (expert, token) pairs; valid tells which
+template <class S>
+__device__ __forceinline__ float router_tile_logits(const float *__restrict__ gate_w, const float *__restrict__ x, int n_experts, int d,
+                                                    int n_tokens, int e0, int tok0, float *rsm, int *e_out, int *tok_out, bool *valid) {
+    constexpr int TG = S::NT / 4; // token groups of 4
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, sub = lane >> 3, j = lane & 7;
+    const int full = d & ~7;
+    const int nch = (full + S::KC - 1) / S::KC;
+    const int ntl = min(S::NT, n_tokens - tok0), nrows = S::NE + ntl;
+    auto issue = [&](int ch) {
+        float *stage = rsm + (size_t)(ch % S::STAGES) * S::ROWS * S::LD;
+        const int c0 = ch * S::KC;
+        for (int idx = tid; idx < nrows * (S::KC / 4); idx += 256) {
+            const int row = idx / (S::KC / 4), c = c0 + (idx % (S::KC / 4)) * 4;
+            if (c >= full) continue;                 // full is a multiple of 8, c of 4: c < full => c + 3 < full
+            const float *src = row < S::NE ? gate_w + (size_t)min(e0 + row, n_experts - 1) * d + c
+                                           : x + (size_t)(tok0 + row - S::NE) * d + c;
+            rt_cp16(stage + row * S::LD + (c - c0), src);
+        }
+    };
+    for (int sidx = 0; sidx < S::STAGES - 1; ++sidx) {
+        if (sidx < nch) issue(sidx);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    const int el = warp / TG, tl = (warp % TG) * 4 + sub;
+    const bool act = warp < S::NE * TG && (warp % TG) * 4 < ntl; // the other warps only copy
+    float acc = 0.0f;
+    for (int ch = 0; ch < nch; ++ch) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(S::STAGES - 2) : "memory");
+        __syncthreads();
+        if (ch + S::STAGES - 1 < nch) issue(ch + S::STAGES - 1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        if (act) {
+            const float *stage = rsm + (size_t)(ch % S::STAGES) * S::ROWS * S::LD;
+            const float *ws = stage + el * S::LD + j, *xr = stage + (S::NE + min(tl, ntl - 1)) * S::LD + j;
+            const int kmax = min(S::KC, full - ch * S::KC);
+#pragma unroll 32
+            for (int c = 0; c < kmax; c += 8) acc = __fadd_rn(acc, __fmul_rn(ws[c], xr[c]));
         }
     }
-    __syncthreads();
-    if (threadIdx.x >= 32) return;
-    const int lane = threadIdx.x, sub = lane >> 3, j = lane & 7;
-    const bool tv = sub < TB && tok0 + sub < n_tokens;
-    const float *xr = xsm + (tv ? sub : 0) * xstride;
-    float acc = 0.0f;
-    const int full = d & ~7;
-#pragma unroll 8
-    for (int c = 0; c < full; c += 8) acc = __fadd_rn(acc, __fmul_rn(ws[c + j], xr[c + j]));
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     const int base = lane & ~7;
     const float v1 = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 1));
     const float p01 = __shfl_sync(0xFFFFFFFFu, v1, base + 0), p23 = __shfl_sync(0xFFFFFFFFu, v1, base + 2);
     const float p45 = __shfl_sync(0xFFFFFFFFu, v1, base + 4), p67 = __shfl_sync(0xFFFFFFFFu, v1, base + 6);
     float sres = __fadd_rn(__fadd_rn(__fadd_rn(p01, p23), p45), p67);
-    if (j == 0 && tv) {
-        for (int c = full; c < d; ++c) sres = __fadd_rn(sres, __fmul_rn(ws[c], xr[c]));
-        logits[(size_t)(tok0 + sub) * n_experts + e] = sres;
-    }
+    const int e = e0 + el, tok = tok0 + tl;
+    *valid = act && j == 0 && tl < ntl && e < n_experts;
+    if (*valid)
+        for (int c = full; c < d; ++c) sres = __fadd_rn(sres, __fmul_rn(__ldg(gate_w + (size_t)e * d + c), __ldg(x + (size_t)tok * d + c)));
+    *e_out = e;
+    *tok_out = tok;
+    return sres;
+}
+
+template <class S>
+__global__ void __launch_bounds__(256)
+moe_router_tile_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
+                       float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key, int n_experts, int d,
+                       int n_tokens) {
+    extern __shared__ __align__(16) float rsm[];
+    int e, tok;
+    bool valid;
+    const float l = router_tile_logits<S>(gate_w, x, n_experts, d, n_tokens, blockIdx.x * S::NE, blockIdx.y * S::NT, rsm, &e, &tok, &valid);
+    if (valid) router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, l);
 }
 
 // ------------------------------------------------------------------ top-k
-// One warp per token.  score = 1/(1+exp(-l)), key = score + bias; the top_k by
-// (key descending, index ascending) in that order is what the engine's running
-// selection ends with (src/model.rs:2157-2171); weights = score / (sum + 1e-20)
-// with the sum taken in slot order (src/model.rs:2172-2173).  exp() runs in double
-// and is rounded once, which agrees with a correctly rounded expf.
-__global__ void __launch_bounds__(128)
-moe_topk_kernel(const float *__restrict__ logits, const float *__restrict__ gate_b, int n_experts, int top_k, int n_tokens,
-                int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
-                int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot) {
-    extern __shared__ float sm[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tok = blockIdx.x * (blockDim.x >> 5) + warp;
-    float *sc = sm + (size_t)warp * 2 * n_experts, *key = sc + n_experts;
-    if (tok >= n_tokens) return;
-    for (int e = lane; e < n_experts; e += 32) {
-        const float l = logits[(size_t)tok * n_experts + e];
-        const float ex = (float)exp((double)(-l));
-        const float s = __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
-        sc[e] = s;
-        key[e] = __fadd_rn(s, gate_b ? gate_b[e] : 0.0f);
-    }
+// One warp per token.  The top_k by (key descending, index ascending) in that order is
+// what the engine's running selection ends with (src/model.rs:2157-2171); weights =
+// score / (sum + 1e-20) with the sum taken in slot order (src/model.rs:2172-2173).
+// kb: n_experts floats of shared memory owned by this warp.
+__device__ __forceinline__ uint32_t float_order(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ void topk_token(const float *score, const float *key, int n_experts, int top_k, int tok, int lane, float *kb,
+                                           int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
+                                           int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot) {
+    for (int e = lane; e < n_experts; e += 32) kb[e] = __fadd_rn(__ldcg(key + (size_t)tok * n_experts + e), 0.0f); // -0 -> +0
     __syncwarp();
-    float sumw = 0.0f;
-    float my_sc = 0.0f;
-    int my_id = -1;
+    int my_id = 0;
     for (int r = 0; r < top_k; ++r) {
         float bk = -INFINITY;
         int bi = 0x7FFFFFFF;
         for (int e = lane; e < n_experts; e += 32) {
-            const float kv = key[e];
-            if (kv > bk || (kv == bk && e < bi)) { bk = kv; bi = e; }
+            const float kv = kb[e];
+            if (kv > bk || bi == 0x7FFFFFFF) { bk = kv; bi = e; } // ascending e: the lowest index of the lane's maximum
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ok = __shfl_xor_sync(0xFFFFFFFFu, bk, o);
-            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
-            if (ok > bk || (ok == bk && oi < bi)) { bk = ok; bi = oi; }
-        }
-        if (bi == 0x7FFFFFFF) bi = 0;
-        const float s = sc[bi];
-        sumw = __fadd_rn(sumw, s);
-        if (lane == r) { my_sc = s; my_id = bi; }
-        __syncwarp();
-        if (lane == 0) key[bi] = -INFINITY; // taken (ties among -inf resolve to the lowest index, never re-taken before real keys)
+        const uint32_t u = bi == 0x7FFFFFFF ? 0u : float_order(bk);
+        const uint32_t gmax = __reduce_max_sync(0xFFFFFFFFu, u);
+        int gi = __reduce_min_sync(0xFFFFFFFFu, (u == gmax) ? bi : 0x7FFFFFFF);
+        if (gi == 0x7FFFFFFF) gi = 0;
+        if (lane == r) my_id = gi;
+        if (lane == 0) kb[gi] = -INFINITY; // taken; real keys are finite, so they always come first
         __syncwarp();
     }
+    const float my_sc = lane < top_k ? __ldcg(score + (size_t)tok * n_experts + my_id) : 0.0f;
+    float sumw = 0.0f;
+    for (int r = 0; r < top_k; ++r) sumw = __fadd_rn(sumw, __shfl_sync(0xFFFFFFFFu, my_sc, r));
     sumw = __fadd_rn(sumw, 1e-20f);
     const int slots = top_k + (shared_slot ? 1 : 0);
     if (lane < top_k) {
@@ -190,6 +238,142 @@ moe_topk_kernel(const float *__restrict__ logits, const float *__restrict__ gate
         pair_expert[p] = n_experts; // the shared expert, unweighted
         pair_weight[p] = 1.0f;
     }
+}
+
+__global__ void __launch_bounds__(128)
+moe_topk_kernel(const float *__restrict__ score, const float *__restrict__ key, int n_experts, int top_k, int n_tokens,
+                int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
+                int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (tok >= n_tokens) return;
+    topk_token(score, key, n_experts, top_k, tok, lane, sm + (size_t)warp * n_experts, ids, wts, pair_row, pair_expert, pair_weight,
+               shared_slot);
+}
+
+// Grouping of a SMALL pair list by one CTA without per-expert arrays: the place of a pair
+// in the expert-sorted list is the number of pairs that come before it in (expert, pair id)
+// order; one work item starts at every 8th pair of an expert.  sh: 3 * n_pairs ints.
+__device__ __forceinline__ void plan_small(const int32_t *pair_expert, int n_pairs, int n_slots, const void *const *__restrict__ wv,
+                                           int32_t *__restrict__ sorted, int32_t *__restrict__ items, int32_t *__restrict__ n_items,
+                                           int max_items, int32_t *__restrict__ status, int *sh) {
+    int *sh_e = sh, *sh_rank = sh + n_pairs, *sh_start = sh + 2 * n_pairs;
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = pair_expert[p];
+        const bool ok = e >= 0 && e < n_slots && wv[e * 3] != nullptr;
+        if (!ok) atomicCAS(status, 0, MK_ERR_ARG);
+        sh_e[p] = ok ? e : -1; // pairs naming an expert that is not resident are dropped
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = sh_e[p];
+        int rank = 0, before = 0;
+        if (e >= 0) {
+            for (int q = 0; q < n_pairs; ++q) {
+                const int eq = sh_e[q];
+                if (eq < 0) continue;
+                if (eq < e || (eq == e && q < p)) ++rank;
+                if (eq == e && q < p) ++before;
+            }
+            sorted[rank] = p;
+        }
+        sh_rank[p] = e >= 0 ? rank : -1;
+        sh_start[p] = (e >= 0 && (before & 7) == 0) ? 1 : 0;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        if (!sh_start[p]) continue;
+        const int e = sh_e[p];
+        int idx = 0, after = 0;
+        for (int q = 0; q < n_pairs; ++q) {
+            if (sh_start[q] && sh_rank[q] < sh_rank[p]) ++idx;
+            if (sh_e[q] == e && q >= p) ++after; // pairs of this expert from p on
+        }
+        if (idx < max_items) {
+            items[idx * 3 + 0] = e;
+            items[idx * 3 + 1] = sh_rank[p];
+            items[idx * 3 + 2] = after < 8 ? after : 8;
+        }
+    }
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int q = 0; q < n_pairs; ++q) total += sh_start[q];
+        *n_items = total < max_items ? total : max_items;
+        if (total > max_items) atomicCAS(status, 0, MK_ERR_STATE);
+    }
+}
+
+// ------------------------------------------------------------------ whole router side in ONE launch (<= 16 tokens)
+// grid.x = ceil(n_experts / S::NE) logits CTAs (as moe_router_tile_kernel) + CTAs that quantize
+// the token rows to q8_0 (src/q8.rs:49-69) for the expert kernels.  The LAST logits CTA to
+// finish (a counter; nobody waits) runs top-k, one warp per token, and then groups the
+// (token, slot) pairs by expert.
+struct RouterFusedArgs {
+    const float *gate_w, *gate_b, *x;
+    float *logits, *score, *key;
+    int n_experts, d, n_tokens, top_k, shared_slot;
+    int32_t *ids; float *wts;
+    int32_t *pair_row, *pair_expert; float *pair_weight;
+    const void *const *wv;
+    int32_t *sorted, *items, *n_items; int max_items;
+    int32_t *status, *counter;
+    int8_t *xq; float *xs; int64_t nbp;
+};
+template <class S>
+__global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFusedArgs a) {
+    extern __shared__ __align__(16) float rsm[];
+    const int d = a.d, n_tokens = a.n_tokens, n_experts = a.n_experts;
+    const int logit_ctas = (n_experts + S::NE - 1) / S::NE;
+    if ((int)blockIdx.x >= logit_ctas) {
+        // ---- quantize role: one warp per (token, block of 32)
+        const int64_t unit = ((int64_t)(blockIdx.x - logit_ctas) * blockDim.x + threadIdx.x) >> 5;
+        const int lane = threadIdx.x & 31;
+        if (unit >= (int64_t)n_tokens * a.nbp) return;
+        const int64_t tok = unit / a.nbp, b = unit % a.nbp;
+        const int64_t c = b * 32 + lane;
+        const float v = (c < d) ? a.x[tok * d + c] : 0.0f;
+        float mx = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        const float dx = __fdiv_rn(mx, 127.0f);
+        int q = 0;
+        if (dx != 0.0f) q = (int)fminf(fmaxf(roundf(__fdiv_rn(v, dx)), -127.0f), 127.0f);
+        const uint32_t qb = (uint32_t)q & 0xFFu;
+        const uint32_t pk = qb | (__shfl_down_sync(0xFFFFFFFFu, qb, 1) << 8) | (__shfl_down_sync(0xFFFFFFFFu, qb, 2) << 16) |
+                            (__shfl_down_sync(0xFFFFFFFFu, qb, 3) << 24);
+        if ((lane & 3) == 0) ((uint32_t *)(a.xq + tok * a.nbp * 32 + b * 32))[lane >> 2] = pk;
+        if (lane == 0) a.xs[tok * a.nbp + b] = dx;
+        return;
+    }
+    {
+        int e, tok;
+        bool valid;
+        const float l = router_tile_logits<S>(a.gate_w, a.x, n_experts, d, n_tokens, blockIdx.x * S::NE, 0, rsm, &e, &tok, &valid);
+        if (valid) router_store(a.logits, a.score, a.key, a.gate_b, (int64_t)tok * n_experts + e, e, l);
+    }
+    // ---- the last logits CTA to get here does the rest
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(a.counter, 1);
+        s_last = (prev == logit_ctas - 1) ? 1 : 0;
+        if (s_last) *a.counter = 0; // ready for the next call
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        for (int tok = warp; tok < n_tokens; tok += nw)
+            topk_token(a.score, a.key, n_experts, a.top_k, tok, lane, rsm + (size_t)warp * n_experts, a.ids, a.wts, a.pair_row,
+                       a.pair_expert, a.pair_weight, a.shared_slot);
+    }
+    __threadfence_block();
+    __syncthreads();
+    const int slots = a.top_k + (a.shared_slot ? 1 : 0);
+    plan_small(a.pair_expert, n_tokens * slots, n_experts + 1, a.wv, a.sorted, a.items, a.n_items, a.max_items, a.status, (int *)rsm);
 }
 
 // ------------------------------------------------------------------ plan
@@ -433,7 +617,7 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     const int E = m->n_experts, k = m->top_k;
     m->max_items = np / 8 + (np < E + 1 ? np : E + 1) + 1;
     const size_t ldq_d = (size_t)m->nbp_d * 32, ldq_i = (size_t)m->nbp_i * 32;
-    MK_CUDA(cudaMalloc(&m->logits, (size_t)nr * E * 4));
+    MK_CUDA(cudaMalloc(&m->logits, (size_t)nr * E * 4 * 3));
     MK_CUDA(cudaMalloc(&m->ids, (size_t)nr * k * 4));
     MK_CUDA(cudaMalloc(&m->wts, (size_t)nr * k * 4));
     MK_CUDA(cudaMalloc(&m->xq, (size_t)nr * ldq_d));
@@ -505,6 +689,8 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
             else e_ = cudaMemsetAsync(m->gate_b, 0, (size_t)E * 4, ctx->stream);
         }
     }
+    if (e_ == cudaSuccess) e_ = cudaMalloc(&m->counter, 4);
+    if (e_ == cudaSuccess) e_ = cudaMemsetAsync(m->counter, 0, 4, ctx->stream);
     if (e_ == cudaSuccess) e_ = cudaStreamSynchronize(ctx->stream);
     if (e_ != cudaSuccess) {
         mk_set_error("mk_moe_create: %s", cudaGetErrorString(e_));
@@ -524,6 +710,7 @@ extern "C" int32_t mk_moe_free(mk_ctx *ctx, mk_moe *m) {
     if (m->wsc) cudaFree((void *)m->wsc);
     if (m->gate_w) cudaFree(m->gate_w);
     if (m->gate_b) cudaFree(m->gate_b);
+    if (m->counter) cudaFree(m->counter);
     delete m;
     return MK_OK;
 }
@@ -532,33 +719,36 @@ extern "C" int32_t mk_moe_free(mk_ctx *ctx, mk_moe *m) {
 // forward pair list when with_pairs).
 static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, bool with_pairs) {
     const int E = m->n_experts;
+    float *score = m->logits + (size_t)m->cap_rows * E, *key = score + (size_t)m->cap_rows * E;
     {
         mk_prof_scope prof(ctx, MK_PROF_ROUTER);
         const int ewarps = (E + 3) / 4;
-        if (n <= 16 && ((size_t)m->d * 5 + 32) * sizeof(float) <= 200 * 1024) {
-            // latency path: rows staged in shared memory
-            if (n <= 2) {
-                const size_t sm1 = ((size_t)m->d + (m->d + 8)) * sizeof(float);
-                static bool attr1 = false;
-                if (!attr1) { cudaFuncSetAttribute(moe_router_logits_smem_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr1 = true; }
-                moe_router_logits_smem_kernel<1><<<dim3((unsigned)E, (unsigned)n), 256, sm1, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
-            } else {
-                const size_t sm4 = ((size_t)m->d + 4 * (size_t)(m->d + 8)) * sizeof(float);
-                static bool attr4 = false;
-                if (!attr4) { cudaFuncSetAttribute(moe_router_logits_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr4 = true; }
-                moe_router_logits_smem_kernel<4><<<dim3((unsigned)E, (unsigned)mk_ceil_div(n, 4)), 256, sm4, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+        if (m->d % 4 == 0 && ((uintptr_t)x & 15) == 0) {
+            static bool attr = false;
+            if (!attr) {
+                cudaFuncSetAttribute(moe_router_tile_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtBig::SMEM);
+                cudaFuncSetAttribute(moe_router_tile_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtSmall::SMEM);
+                attr = true;
             }
+            if (n <= RtSmall::NT)
+                moe_router_tile_kernel<RtSmall><<<dim3((unsigned)mk_ceil_div(E, RtSmall::NE), 1), 256, RtSmall::SMEM, ctx->stream>>>(
+                    m->gate_w, m->gate_b, x, m->logits, score, key, E, m->d, n);
+            else
+                moe_router_tile_kernel<RtBig><<<dim3((unsigned)mk_ceil_div(E, RtBig::NE), (unsigned)mk_ceil_div(n, RtBig::NT)), 256,
+                                                RtBig::SMEM, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits, score, key, E, m->d, n);
         } else if (n >= 4) {
             const int64_t warps = (int64_t)ewarps * mk_ceil_div(n, 4);
-            moe_router_logits_kernel<4><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+            moe_router_logits_kernel<4><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits,
+                                                                                                       score, key, E, m->d, n);
         } else {
             const int64_t warps = (int64_t)ewarps * n;
-            moe_router_logits_kernel<1><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, x, m->logits, E, m->d, n);
+            moe_router_logits_kernel<1><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits,
+                                                                                                       score, key, E, m->d, n);
         }
-        const size_t smem = (size_t)4 * 2 * E * sizeof(float);
+        const size_t smem = (size_t)4 * E * sizeof(float);
         moe_topk_kernel<<<(unsigned)mk_ceil_div(n, 4), 128, smem, ctx->stream>>>(
-            m->logits, m->gate_b, E, m->top_k, n, m->ids, m->wts, with_pairs ? m->pair_row : nullptr, m->pair_expert,
-            m->pair_weight, m->has_shared ? 1 : 0);
+            score, key, E, m->top_k, n, m->ids, m->wts, with_pairs ? m->pair_row : nullptr, m->pair_expert, m->pair_weight,
+            m->has_shared ? 1 : 0);
         ctx->launches += 2;
     }
     MK_CUDA(cudaGetLastError());
@@ -567,13 +757,20 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
 
 // grouped experts over an explicit pair list (device arrays); x rows already on device
 static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_rows, const int32_t *pair_row,
-                                  const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs) {
-    int32_t rc = mk_launch_quantize_act(ctx, x, n_rows, m->d, m->d, m->nbp_d, 0, m->xq, m->xs);
-    if (rc != MK_OK) return rc;
+                                  const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs,
+                                  bool prepared = false) {
+    // prepared: the fused router kernel has already quantized x and grouped the pairs
+    if (!prepared) {
+        int32_t rc = mk_launch_quantize_act(ctx, x, n_rows, m->d, m->d, m->nbp_d, 0, m->xq, m->xs);
+        if (rc != MK_OK) return rc;
+    }
     mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
     const int slots = m->n_experts + 1;
-    moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted,
-                                                                              m->items, m->n_items, m->max_items, ctx->status_dev);
+    if (!prepared) {
+        moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted,
+                                                                                  m->items, m->n_items, m->max_items, ctx->status_dev);
+        ctx->launches++;
+    }
     MoeArgs a;
     a.wv = m->wv; a.wsc = m->wsc; a.items = m->items; a.n_items = m->n_items; a.sorted = m->sorted;
     a.pair_row = pair_row; a.pair_weight = pair_weight; a.xq = m->xq; a.xs = m->xs; a.actq = m->actq; a.acts = m->acts;
@@ -585,7 +782,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     if (items_ub < 1) items_ub = 1;
     moe_gate_up_kernel<<<dim3((unsigned)(m->inter / 32), (unsigned)items_ub), MK_G1_KS * 128, 0, ctx->stream>>>(a);
     moe_down_kernel<<<dim3((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub), 256, 0, ctx->stream>>>(a);
-    ctx->launches += 3;
+    ctx->launches += 2;
     MK_CUDA(cudaGetLastError());
     return MK_OK;
 }
@@ -632,9 +829,41 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
     const int slots = m->top_k + (m->has_shared ? 1 : 0);
     int32_t rc = moe_reserve(ctx, m, n, n * slots);
     if (rc != MK_OK) return rc;
-    rc = moe_route_launch(ctx, m, x, n, true);
-    if (rc != MK_OK) return rc;
-    rc = moe_experts_launch(ctx, m, x, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, m->outs);
+    // small batches: router logits, activation quantization, top-k and pair grouping in ONE launch
+    const bool small = n <= RtSmall::NT;
+    size_t smem_f = small ? RtSmall::SMEM : RtBig::SMEM;
+    if ((size_t)8 * m->n_experts * 4 > smem_f) smem_f = (size_t)8 * m->n_experts * 4;
+    if ((size_t)3 * n * slots * 4 > smem_f) smem_f = (size_t)3 * n * slots * 4;
+    const bool fused = n <= 16 && m->d % 4 == 0 && ((uintptr_t)x & 15) == 0 && smem_f <= 200 * 1024 && !ctx->moe_no_fuse;
+    if (fused) {
+        RouterFusedArgs ra;
+        ra.gate_w = m->gate_w; ra.gate_b = m->gate_b; ra.x = x; ra.logits = m->logits;
+        ra.score = m->logits + (size_t)m->cap_rows * m->n_experts; ra.key = ra.score + (size_t)m->cap_rows * m->n_experts;
+        ra.n_experts = m->n_experts; ra.d = m->d; ra.n_tokens = n; ra.top_k = m->top_k; ra.shared_slot = m->has_shared ? 1 : 0;
+        ra.ids = m->ids; ra.wts = m->wts; ra.pair_row = m->pair_row; ra.pair_expert = m->pair_expert; ra.pair_weight = m->pair_weight;
+        ra.wv = m->wv; ra.sorted = m->sorted; ra.items = m->items; ra.n_items = m->n_items; ra.max_items = m->max_items;
+        ra.status = ctx->status_dev; ra.counter = m->counter; ra.xq = m->xq; ra.xs = m->xs; ra.nbp = m->nbp_d;
+        const unsigned qctas = (unsigned)mk_ceil_div((int64_t)n * m->nbp_d, 8);
+        {
+            mk_prof_scope prof(ctx, MK_PROF_ROUTER);
+            static bool attr = false;
+            if (!attr) {
+                cudaFuncSetAttribute(moe_router_fused_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                cudaFuncSetAttribute(moe_router_fused_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                attr = true;
+            }
+            if (small)
+                moe_router_fused_kernel<RtSmall><<<(unsigned)mk_ceil_div(m->n_experts, RtSmall::NE) + qctas, 256, smem_f, ctx->stream>>>(ra);
+            else
+                moe_router_fused_kernel<RtBig><<<(unsigned)mk_ceil_div(m->n_experts, RtBig::NE) + qctas, 256, smem_f, ctx->stream>>>(ra);
+            ctx->launches++;
+        }
+        MK_CUDA(cudaGetLastError());
+    } else {
+        rc = moe_route_launch(ctx, m, x, n, true);
+        if (rc != MK_OK) return rc;
+    }
+    rc = moe_experts_launch(ctx, m, x, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, m->outs, fused);
     if (rc != MK_OK) return rc;
     rc = mk_moe_combine_dev(ctx, m->outs, n, slots, m->d, out);
     if (rc != MK_OK) return rc;
