@@ -122,6 +122,12 @@ int32_t mk_launch_quantize_weight_q8(mk_ctx *ctx, const float *wf32, int64_t row
 int32_t mk_launch_retile_q8(mk_ctx *ctx, const int8_t *q, const void *scales, mk_weight *w);
 int32_t mk_launch_untile_q8(mk_ctx *ctx, const mk_weight *w, int8_t *q, void *scales);
 
+// Element offset of the scale of (row tile rt, block b, row r16 of the tile).  Scales are
+// tiled [row tile][group of 4 blocks][16 rows][4 blocks]: the four scales one row needs for
+// a group of blocks are adjacent (one 32-bit / 64-bit / 128-bit load by scale type).
+__host__ __device__ __forceinline__ int64_t mk_scale_off(int64_t rt, int64_t nbp, int64_t b, int r16) {
+    return (rt * nbp + (b & ~(int64_t)3)) * 16 + r16 * 4 + (b & 3);
+}
 #ifdef __CUDACC__
 // ---------------------------------------------------------------- device helpers
 // 2^(sb-127) from a ue8m0 byte as an exact bit pattern; sb == 0 is the subnormal 2^-127.

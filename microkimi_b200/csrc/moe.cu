@@ -448,28 +448,32 @@ struct MoeArgs {
 };
 
 // Partial sums of one warp for a 16-row tile and up to 8 columns, into smem part[16][8].
-// n <= 2 columns use the spread schedule, more the batched one.
-template <int WF>
+// SPREAD: items of <= 2 columns (or, without BATCHED, any item by repeated passes) take the
+// spread schedule, 2 columns per pass.  BATCHED: items of more than 2 columns take the
+// batched schedule.  Both give the same bits for a column.
+template <int WF, bool SPREAD, bool BATCHED>
 __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc, int64_t ngroups, int ks, int KS, int lane,
                                               int n, const int8_t *const *xrow /* [n] */, const float *const *xsrow /* [n] */,
                                               const Consts &k, float (*part)[8]) {
     const int g = lane >> 2, t = lane & 3;
-    if (n <= 2) {
+    if (SPREAD && n == 1) {
+        float o[2][1];
+        warp_tile_spread<WF, 1, false>(tile, sc, ngroups, ks, KS, lane, (g & 1) == 0 ? xrow[0] : nullptr, xsrow[0], xsrow[0], k, o);
+        if (t == 0) { part[g][0] = o[0][0]; part[g + 8][0] = o[1][0]; }
+    } else if (SPREAD && (n == 2 || !BATCHED)) {
         const int slot = g & 1;
-        const int8_t *xr = slot < n ? xrow[slot] : nullptr;
-        if (n == 1) {
-            float o[2][1];
-            warp_tile_spread<WF, 1, false>(tile, sc, ngroups, ks, KS, lane, xr, xsrow[0], xsrow[0], k, o);
-            if (t == 0) { part[g][0] = o[0][0]; part[g + 8][0] = o[1][0]; }
-        } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < n; c0 += 2) {
+            const bool two = c0 + 1 < n; // an odd last column runs with an empty second slot
+            const int8_t *xr = (slot == 0 || two) ? xrow[c0 + slot] : nullptr;
             float o[2][2];
-            warp_tile_spread<WF, 2, false>(tile, sc, ngroups, ks, KS, lane, xr, xsrow[0], xsrow[1], k, o);
+            warp_tile_spread<WF, 2, false>(tile, sc, ngroups, ks, KS, lane, xr, xsrow[c0], xsrow[two ? c0 + 1 : c0], k, o);
             if (t == 0) {
-                part[g][0] = o[0][0]; part[g][1] = o[0][1];
-                part[g + 8][0] = o[1][0]; part[g + 8][1] = o[1][1];
+                part[g][c0] = o[0][0]; part[g + 8][c0] = o[1][0];
+                if (two) { part[g][c0 + 1] = o[0][1]; part[g + 8][c0 + 1] = o[1][1]; }
             }
         }
-    } else {
+    } else if constexpr (BATCHED) {
         float acc[4];
         const int ca = 2 * t, cb = 2 * t + 1;
         warp_tile_batched<WF, false, false>(tile, sc, ngroups, ks, KS, lane, g < n ? xrow[g] : nullptr, ca < n ? xsrow[ca] : nullptr,
@@ -487,10 +491,26 @@ __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc,
 #ifndef MK_G1_KS
 #define MK_G1_KS 2   // K slices per 16-row tile in the gate/up kernel: CTA = 4 * MK_G1_KS warps
 #endif
-__global__ void __launch_bounds__(MK_G1_KS * 128, 8 / MK_G1_KS) moe_gate_up_kernel(const MoeArgs a) {
+// MODE: which work items a launch takes and how.  MOE_ALL_SPREAD: all of them by spread
+// passes (calls of <= 2 token rows; fewest registers, 4 CTAs per SM = one wave at batch 1).
+// MOE_MIXED: all of them, each by the schedule its size asks for, still 4 CTAs per SM
+// (calls of a few tokens, where most items are small and the shared expert's big items
+// overlap them).  Large calls launch MOE_BIG_ITEMS (batched schedule with all the registers
+// it wants, 2 CTAs per SM) and MOE_SMALL_ITEMS (items of <= 2 pairs) one after the other.
+enum { MOE_ALL_SPREAD = 0, MOE_SMALL_ITEMS = 1, MOE_BIG_ITEMS = 2, MOE_MIXED = 3 };
+#ifndef MK_MOE_BIG_CTAS
+#define MK_MOE_BIG_CTAS 2
+#endif
+#ifndef MK_MOE_MIXED_MAX
+#define MK_MOE_MIXED_MAX 32   // calls of up to this many token rows use MOE_MIXED
+#endif
+template <int MODE>
+__global__ void __launch_bounds__(MK_G1_KS * 128, MODE == MOE_BIG_ITEMS ? MK_MOE_BIG_CTAS : 8 / MK_G1_KS) moe_gate_up_kernel(const MoeArgs a) {
+    constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED, SPREAD = MODE != MOE_BIG_ITEMS;
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
+    if ((MODE == MOE_SMALL_ITEMS && n > 2) || (MODE == MOE_BIG_ITEMS && n <= 2)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float part[4 * MK_G1_KS][16][8];
     __shared__ const int8_t *xrow[8];
@@ -512,7 +532,7 @@ __global__ void __launch_bounds__(MK_G1_KS * 128, 8 / MK_G1_KS) moe_gate_up_kern
         const int mat = (job >> 1) ? 2 : 0, half = job & 1;
         const int64_t rt = (int64_t)blockIdx.x * 2 + half;
         const void *wv = a.wv[e * 3 + mat], *ws = a.wsc[e * 3 + mat];
-        warp_tile_any<W_MXFP4>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, MK_G1_KS,
+        warp_tile_any<W_MXFP4, SPREAD, BATCHED>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, MK_G1_KS,
                                lane, n, xrow, xsrow, a.k, part[warp]);
     }
     __syncthreads();
@@ -542,10 +562,13 @@ __global__ void __launch_bounds__(MK_G1_KS * 128, 8 / MK_G1_KS) moe_gate_up_kern
 
 // ------------------------------------------------------------------ down projection
 // grid = (ceil(d/32), max_items).  CTA: 2 row tiles of w2 x 4 K slices.
-__global__ void __launch_bounds__(256, 4) moe_down_kernel(const MoeArgs a) {
+template <int MODE>
+__global__ void __launch_bounds__(256, MODE == MOE_BIG_ITEMS ? MK_MOE_BIG_CTAS : 4) moe_down_kernel(const MoeArgs a) {
+    constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED, SPREAD = MODE != MOE_BIG_ITEMS;
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
+    if ((MODE == MOE_SMALL_ITEMS && n > 2) || (MODE == MOE_BIG_ITEMS && n <= 2)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float part[8][16][8];
     __shared__ const int8_t *xrow[8];
@@ -565,7 +588,7 @@ __global__ void __launch_bounds__(256, 4) moe_down_kernel(const MoeArgs a) {
     const int64_t rt = (int64_t)blockIdx.x * 2 + rt_local;
     if (rt < nrt) {
         const void *wv = a.wv[e * 3 + 1], *ws = a.wsc[e * 3 + 1];
-        warp_tile_any<W_MXFP4>(tile_values<W_MXFP4>(wv, rt, a.nbp_i), tile_scales<W_MXFP4>(ws, rt, a.nbp_i), a.nbp_i >> 2, ks, 4,
+        warp_tile_any<W_MXFP4, SPREAD, BATCHED>(tile_values<W_MXFP4>(wv, rt, a.nbp_i), tile_scales<W_MXFP4>(ws, rt, a.nbp_i), a.nbp_i >> 2, ks, 4,
                                lane, n, xrow, xsrow, a.k, part[warp]);
     }
     __syncthreads();
@@ -780,8 +803,22 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     int items_ub = n_pairs / 8 + (n_pairs < slots ? n_pairs : slots);
     if (items_ub > m->max_items) items_ub = m->max_items;
     if (items_ub < 1) items_ub = 1;
-    moe_gate_up_kernel<<<dim3((unsigned)(m->inter / 32), (unsigned)items_ub), MK_G1_KS * 128, 0, ctx->stream>>>(a);
-    moe_down_kernel<<<dim3((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub), 256, 0, ctx->stream>>>(a);
+    // calls of <= 2 rows have at most 2 pairs per expert: the build without the batched schedule
+    // needs fewer registers and keeps 4 CTAs per SM, one wave at batch 1
+    const dim3 g1((unsigned)(m->inter / 32), (unsigned)items_ub), g2((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub);
+    if (n_rows <= 2) {
+        moe_gate_up_kernel<MOE_ALL_SPREAD><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
+        moe_down_kernel<MOE_ALL_SPREAD><<<g2, 256, 0, ctx->stream>>>(a);
+    } else if (n_rows <= MK_MOE_MIXED_MAX) {
+        moe_gate_up_kernel<MOE_MIXED><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
+        moe_down_kernel<MOE_MIXED><<<g2, 256, 0, ctx->stream>>>(a);
+    } else {
+        moe_gate_up_kernel<MOE_BIG_ITEMS><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
+        moe_gate_up_kernel<MOE_SMALL_ITEMS><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
+        moe_down_kernel<MOE_BIG_ITEMS><<<g2, 256, 0, ctx->stream>>>(a);
+        moe_down_kernel<MOE_SMALL_ITEMS><<<g2, 256, 0, ctx->stream>>>(a);
+        ctx->launches += 2;
+    }
     ctx->launches += 2;
     MK_CUDA(cudaGetLastError());
     return MK_OK;

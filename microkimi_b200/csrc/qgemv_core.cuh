@@ -101,23 +101,82 @@ __device__ __forceinline__ void block_mma(const Group<WF> &g, int m, uint32_t b0
     }
 }
 
-// weight scales of block b for rows g and g+8; `sc` points at the tile's scales ([block][16 rows])
+// weight scales of block b for rows g and g+8; `sc` points at the tile's scales
+// ([group of 4 blocks][16 rows][4 blocks])
 template <int WF>
 __device__ __forceinline__ void load_wscale(const void *sc, int64_t b, int g, float &sg, float &sh) {
+    const int64_t o = (b >> 2) * 64 + g * 4 + (b & 3);
     if constexpr (WF == W_MXFP4) {
-        const uint8_t *s = (const uint8_t *)sc + b * 16;
-        sg = mk_e8m0_half(__ldg(s + g));
-        sh = mk_e8m0_half(__ldg(s + g + 8));
+        const uint8_t *s = (const uint8_t *)sc + o;
+        sg = mk_e8m0_half(__ldg(s));
+        sh = mk_e8m0_half(__ldg(s + 32));
     } else if constexpr (WF == W_Q8_F32) {
-        const float *s = (const float *)sc + b * 16;
-        sg = __ldg(s + g);
-        sh = __ldg(s + g + 8);
+        const float *s = (const float *)sc + o;
+        sg = __ldg(s);
+        sh = __ldg(s + 32);
     } else {
-        const __half *s = (const __half *)sc + b * 16;
-        sg = __half2float(__ldg(s + g));
-        sh = __half2float(__ldg(s + g + 8));
+        const __half *s = (const __half *)sc + o;
+        sg = __half2float(__ldg(s));
+        sh = __half2float(__ldg(s + 32));
     }
 }
+// lane (g, t) takes block 4 i + t: element i * 64 + g * 4 + t = i * 64 + lane
+template <int WF>
+__device__ __forceinline__ void load_wscale_lane(const void *sc, int64_t i, int lane, float &sg, float &sh) {
+    if constexpr (WF == W_MXFP4) {
+        const uint8_t *s = (const uint8_t *)sc + i * 64 + lane;
+        sg = mk_e8m0_half(__ldg(s));
+        sh = mk_e8m0_half(__ldg(s + 32));
+    } else if constexpr (WF == W_Q8_F32) {
+        const float *s = (const float *)sc + i * 64 + lane;
+        sg = __ldg(s);
+        sh = __ldg(s + 32);
+    } else {
+        const __half *s = (const __half *)sc + i * 64 + lane;
+        sg = __half2float(__ldg(s));
+        sh = __half2float(__ldg(s + 32));
+    }
+}
+// the same for the four blocks of group i at once: two vector loads, decoded block by block
+template <int WF> struct WScale4;
+template <> struct WScale4<W_MXFP4> {
+    uint32_t a, b;
+    __device__ __forceinline__ void load(const void *sc, int64_t i, int g) {
+        const uint8_t *s = (const uint8_t *)sc + i * 64 + g * 4;
+        a = __ldg((const uint32_t *)s);
+        b = __ldg((const uint32_t *)(s + 32));
+    }
+    __device__ __forceinline__ void get(int m, float &sg, float &sh) const {
+        sg = mk_e8m0_half((a >> (8 * m)) & 0xFFu);
+        sh = mk_e8m0_half((b >> (8 * m)) & 0xFFu);
+    }
+};
+template <> struct WScale4<W_Q8_F32> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const void *sc, int64_t i, int g) {
+        const float *s = (const float *)sc + i * 64 + g * 4;
+        a = __ldg((const float4 *)s);
+        b = __ldg((const float4 *)(s + 32));
+    }
+    __device__ __forceinline__ void get(int m, float &sg, float &sh) const {
+        sg = m == 0 ? a.x : (m == 1 ? a.y : (m == 2 ? a.z : a.w));
+        sh = m == 0 ? b.x : (m == 1 ? b.y : (m == 2 ? b.z : b.w));
+    }
+};
+template <> struct WScale4<W_Q8_F16> {
+    uint2 a, b;
+    __device__ __forceinline__ void load(const void *sc, int64_t i, int g) {
+        const __half *s = (const __half *)sc + i * 64 + g * 4;
+        a = __ldg((const uint2 *)s);
+        b = __ldg((const uint2 *)(s + 32));
+    }
+    __device__ __forceinline__ void get(int m, float &sg, float &sh) const {
+        const uint32_t wa = m < 2 ? a.x : a.y, wb = m < 2 ? b.x : b.y;
+        const __half2 ha = *(const __half2 *)&wa, hb = *(const __half2 *)&wb;
+        sg = (m & 1) ? __high2float(ha) : __low2float(ha);
+        sh = (m & 1) ? __high2float(hb) : __low2float(hb);
+    }
+};
 template <int WF> __host__ __device__ constexpr int scale_elem_bytes() { return WF == W_MXFP4 ? 1 : (WF == W_Q8_F32 ? 4 : 2); }
 
 // acc + idot * (sw * sx), separate multiply and add, in the reference's order
@@ -184,7 +243,7 @@ __device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile,
         // lane t now holds block 4i+t: c0/c1 = row g (slot 0/1), c2/c3 = row g+8
         const int64_t b = i * 4 + t;
         float sg, sh;
-        load_wscale<WF>(sc, b, g, sg, sh);
+        load_wscale_lane<WF>(sc, i, lane, sg, sh);
         int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
         if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
         if constexpr (X2) {
@@ -255,29 +314,34 @@ __device__ __forceinline__ void warp_tile_batched(const uint4 *__restrict__ tile
         if constexpr (ORDERED) return acc_term(acc_, idot, sw, sx);
         else return acc_term_fast(acc_, idot, sw, sx);
     };
+    const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     auto process = [&](const Group<WF> &grp, int64_t i) {
+        WScale4<WF> wsc;
+        wsc.load(sc, i, g);
+        // activation scales of the group's four blocks (rows of scales are 16-byte aligned: the
+        // padded block count is a multiple of 4)
+        const float4 xa4 = xs_a ? __ldg((const float4 *)xs_a + i) : zero4;
+        const float4 xb4 = (!X2 && xs_b) ? __ldg((const float4 *)xs_b + i) : zero4;
+        const float sxa_[4] = {xa4.x, xa4.y, xa4.z, xa4.w}, sxb_[4] = {xb4.x, xb4.y, xb4.z, xb4.w};
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
             const int64_t b = i * 4 + m;
             const uint2 xv = __ldg((const uint2 *)(xp + (uint64_t)((uint32_t)b * xstep)));
             int cp[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
             block_mma<WF>(grp, m, xv.x, xv.y, cp, cn, k);
-            float sg, sh;
-            load_wscale<WF>(sc, b, g, sg, sh);
             int d0 = cp[0], d1 = cp[1], d2 = cp[2], d3 = cp[3];
             if constexpr (WF == W_MXFP4) { d0 -= cn[0]; d1 -= cn[1]; d2 -= cn[2]; d3 -= cn[3]; }
             float(&a)[4] = part[ORDERED ? 0 : m];
+            float sg, sh;
+            wsc.get(m, sg, sh);
             if constexpr (X2) {
-                const float sx = xs_a ? __ldg(xs_a + b) : 0.0f;
-                a[0] = term(a[0], d0 * 128 + d1, sg, sx);
-                a[2] = term(a[2], d2 * 128 + d3, sh, sx);
+                a[0] = term(a[0], d0 * 128 + d1, sg, sxa_[m]);
+                a[2] = term(a[2], d2 * 128 + d3, sh, sxa_[m]);
             } else {
-                const float sxa = xs_a ? __ldg(xs_a + b) : 0.0f;
-                const float sxb = xs_b ? __ldg(xs_b + b) : 0.0f;
-                a[0] = term(a[0], d0, sg, sxa);
-                a[1] = term(a[1], d1, sg, sxb);
-                a[2] = term(a[2], d2, sh, sxa);
-                a[3] = term(a[3], d3, sh, sxb);
+                a[0] = term(a[0], d0, sg, sxa_[m]);
+                a[1] = term(a[1], d1, sg, sxb_[m]);
+                a[2] = term(a[2], d2, sh, sxa_[m]);
+                a[3] = term(a[3], d3, sh, sxb_[m]);
             }
         }
     };

@@ -36,7 +36,7 @@ __global__ void retile_mxfp4_kernel(const uint8_t *__restrict__ packed, const ui
         const int64_t rb = idx >> 4;
         const int64_t rt = rb / nbp, b = rb % nbp;
         const int64_t row = rt * 16 + r16;
-        ts[idx] = (row < rows && b < nb) ? scales[row * nb + b] : (uint8_t)0;
+        ts[mk_scale_off(rt, nbp, b, r16)] = (row < rows && b < nb) ? scales[row * nb + b] : (uint8_t)0;
     }
 }
 __global__ void untile_mxfp4_kernel(const uint32_t *__restrict__ tv, const uint8_t *__restrict__ ts,
@@ -60,7 +60,7 @@ __global__ void untile_mxfp4_kernel(const uint32_t *__restrict__ tv, const uint8
         const int64_t rb = idx >> 4;
         const int64_t rt = rb / nbp, b = rb % nbp;
         const int64_t row = rt * 16 + r16;
-        if (row < rows && b < nb) scales[row * nb + b] = ts[idx];
+        if (row < rows && b < nb) scales[row * nb + b] = ts[mk_scale_off(rt, nbp, b, r16)];
     }
 }
 // one thread per element: W[r,c] = E2M1[code] * 2^(sb-127), bit-exact (-0.0 and subnormals included)
@@ -76,7 +76,7 @@ __global__ void dequant_mxfp4_kernel(const uint32_t *__restrict__ tv, const uint
     const int64_t chunk = rt * (nbp / 2) + (b >> 1);
     const uint32_t w = tv[chunk * 128 + (g * 4 + t) * 4 + (int)(b & 1) * 2 + hi];
     const uint32_t code = (w >> (4 * jj)) & 15u;
-    const uint32_t sb = ts[(rt * nbp + b) * 16 + r16];
+    const uint32_t sb = ts[mk_scale_off(rt, nbp, b, r16)];
     out[idx] = c_e2m1[code] * mk_e8m0(sb);
 }
 
@@ -118,7 +118,7 @@ quantize_weight_q8_kernel(const float *__restrict__ w, int64_t row0, int64_t nro
     const int64_t rt = row >> 4;
     const int r16 = (int)(row & 15);
     if ((lane & 3) == 0) *(uint32_t *)(tv + (rt * nbp + b) * 512 + q8_chunk_off(r16, lane)) = pk;
-    if (lane == 0) ts[(rt * nbp + b) * 16 + r16] = st;
+    if (lane == 0) ts[mk_scale_off(rt, nbp, b, r16)] = st;
 }
 // natural q8 rows -> tiled; one thread per 4 bytes
 template <typename ST>
@@ -138,7 +138,7 @@ __global__ void retile_q8_kernel(const int8_t *__restrict__ q, const ST *__restr
     }
     if (idx < rows * nb) {
         const int64_t row = idx / nb, b = idx % nb;
-        const int64_t off = ((row >> 4) * nbp + b) * 16 + (row & 15);
+        const int64_t off = mk_scale_off(row >> 4, nbp, b, (int)(row & 15));
         if (!inverse) ts[off] = s[idx];
         else s_out[idx] = ts[off];
     }
