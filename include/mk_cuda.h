@@ -119,6 +119,9 @@ int32_t mk_weight_q8_from_f32(mk_ctx *ctx, const float *w, int64_t rows, int64_t
  * (f32 or IEEE half according to scale_type). */
 int32_t mk_weight_q8(mk_ctx *ctx, const int8_t *q, const void *scales, int64_t rows, int64_t cols,
                      int32_t scale_type, int32_t src_on_device, mk_weight **out);
+/* A dense f32 matrix [rows, cols] (row-major), as the engine's matvec consumes it
+ * (src/model.rs:199; the Metal seam uploads the same bytes, src/metal.rs:750). */
+int32_t mk_weight_f32(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, int32_t src_on_device, mk_weight **out);
 int32_t mk_weight_free(mk_ctx *ctx, mk_weight *w);
 /* Bytes held on the device for this weight (values + scales). */
 int64_t mk_weight_bytes(const mk_weight *w);
@@ -158,6 +161,16 @@ int32_t mk_matvec_q8(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, 
                      int32_t act_mode, int32_t *argmax);
 int32_t mk_matvec_q8_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch,
                          int32_t act_mode, int32_t *argmax);
+
+/* model::matvec / metal::gpu_matvec (src/model.rs:199-247, src/metal.rs:750): dense
+ * f32 y[b, r] = dot(W[r], x[b]) with the engine's dot() order (src/model.rs:63-82:
+ * 8 accumulators, separate multiply and add), i.e. the CPU's bits.
+ * x f32 [batch, cols], y f32 [batch, rows]. */
+int32_t mk_matvec_f32(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch);
+int32_t mk_matvec_f32_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch);
+/* rmsnorm (src/model.rs:599-605) on DEVICE rows: out[i] = (x[i] * inv) * w[i] with
+ * inv = 1 / sqrt(dot(x, x) / len + eps); x, out f32 [n, len], w f32 [len].  Bit-identical. */
+int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, int32_t n, int32_t len, float eps, float *out);
 
 /* ---- MoE layer ---------------------------------------------------------
  * One call per layer instead of 3 matvecs per selected expert: replaces

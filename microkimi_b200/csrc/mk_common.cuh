@@ -33,7 +33,7 @@ void mk_set_error(const char *fmt, ...);
     } while (0)
 
 // ---------------------------------------------------------------- records
-enum { MK_FMT_MXFP4 = 0, MK_FMT_Q8 = 1 };
+enum { MK_FMT_MXFP4 = 0, MK_FMT_Q8 = 1, MK_FMT_F32 = 2 };
 
 // A registered weight matrix in the fragment-major ("tiled") device layout.
 //
@@ -112,6 +112,11 @@ int32_t mk_launch_quantize_act(mk_ctx *ctx, const float *x, int ntok, int64_t co
 // the fused dequant + GEMV
 int32_t mk_launch_qgemv(mk_ctx *ctx, const mk_weight *w, const int8_t *xq, const float *xs, int ntok,
                         int x2, int strict, float *y, int64_t ldy);
+// spine.cu: y[tok * ldy + row] (+)= dot(w[row], x[tok]) in the engine's dot() order; rmsnorm; SiTU
+int32_t mk_launch_f32_gemv(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, const float *x, int n, float *y, int64_t ldy,
+                           int accumulate);
+int32_t mk_launch_rmsnorm(mk_ctx *ctx, const float *x, const float *w, int n, int len, float eps, float *out);
+int32_t mk_launch_situ(mk_ctx *ctx, const float *a, const float *u, int64_t count, float *out);
 int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, int batch, int32_t *out, void *scratch);
 size_t mk_argmax_scratch_bytes(int batch);
 // weight (re)tiling
@@ -121,6 +126,15 @@ int32_t mk_launch_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out);
 int32_t mk_launch_quantize_weight_q8(mk_ctx *ctx, const float *wf32, int64_t row0, int64_t nrows, mk_weight *w);
 int32_t mk_launch_retile_q8(mk_ctx *ctx, const int8_t *q, const void *scales, mk_weight *w);
 int32_t mk_launch_untile_q8(mk_ctx *ctx, const mk_weight *w, int8_t *q, void *scales);
+
+// SiTU (src/model.rs:617-621): 4 tanh(g/4) sigmoid(g) * 25 tanh(u/25), multiplied left to
+// right as the engine writes it; tanh and exp in double precision, rounded once.
+__device__ __forceinline__ float mk_situ(float g, float u) {
+    const float tg = (float)tanh((double)__fdiv_rn(g, 4.0f));
+    const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-g))));
+    const float tu = (float)tanh((double)__fdiv_rn(u, 25.0f));
+    return __fmul_rn(__fmul_rn(__fmul_rn(4.0f, tg), sg), __fmul_rn(25.0f, tu));
+}
 
 // Element offset of the scale of (row tile rt, block b, row r16 of the tile).  Scales are
 // tiled [row tile][group of 4 blocks][16 rows][4 blocks]: the four scales one row needs for

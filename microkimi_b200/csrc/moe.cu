@@ -12,6 +12,7 @@
 // activation), down, combine.  Up to 16 tokens the first four are ONE launch
 // (moe_router_fused_kernel), 4 launches per layer call in all.
 #include "qgemv_core.cuh"
+#include "f32gemv.cuh"
 
 using namespace mkq;
 
@@ -56,8 +57,7 @@ __device__ __forceinline__ void router_store(float *__restrict__ logits, float *
     key[at] = __fadd_rn(sg, gate_b ? gate_b[e] : 0.0f);
 }
 
-// Generic form (any d, any alignment): 8 lanes own the 8 accumulators of one
-// (expert, token tile); a warp = 4 experts.
+// Generic form (any d, any alignment): a warp = 4 experts (mkf::rows_dot).
 template <int T>
 __global__ void __launch_bounds__(256)
 moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
@@ -71,108 +71,18 @@ moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restri
     const int tok0 = tile * T;
     if (tok0 >= n_tokens) return;
     const bool ev = e < n_experts;
-    const float *w = gate_w + (size_t)(ev ? e : 0) * d;
-    float acc[T];
+    float out[T];
+    mkf::rows_dot<T>(gate_w + (size_t)(ev ? e : 0) * d, x, d, n_tokens, tok0, ev, lane, out);
 #pragma unroll
-    for (int t = 0; t < T; ++t) acc[t] = 0.0f;
-    const int full = d & ~7;
-#pragma unroll 4
-    for (int c = 0; c < full; c += 8) {
-        const float wv = __ldg(w + c + j);
-#pragma unroll
-        for (int t = 0; t < T; ++t) {
-            const int tok = min(tok0 + t, n_tokens - 1);
-            acc[t] = __fadd_rn(acc[t], __fmul_rn(wv, __ldg(x + (size_t)tok * d + c + j)));
-        }
-    }
-    const int base = lane & ~7;
-#pragma unroll
-    for (int t = 0; t < T; ++t) {
-        const float v1 = __fadd_rn(acc[t], __shfl_xor_sync(0xFFFFFFFFu, acc[t], 1)); // a(2i) + a(2i+1)
-        const float p01 = __shfl_sync(0xFFFFFFFFu, v1, base + 0), p23 = __shfl_sync(0xFFFFFFFFu, v1, base + 2);
-        const float p45 = __shfl_sync(0xFFFFFFFFu, v1, base + 4), p67 = __shfl_sync(0xFFFFFFFFu, v1, base + 6);
-        float s = __fadd_rn(__fadd_rn(__fadd_rn(p01, p23), p45), p67);
-        if (j == 0 && ev && tok0 + t < n_tokens) {
-            for (int c = full; c < d; ++c) s = __fadd_rn(s, __fmul_rn(__ldg(w + c), __ldg(x + (size_t)(tok0 + t) * d + c)));
-            router_store(logits, score, key, gate_b, (int64_t)(tok0 + t) * n_experts + e, e, s);
-        }
-    }
+    for (int t = 0; t < T; ++t)
+        if (j == 0 && ev && tok0 + t < n_tokens) router_store(logits, score, key, gate_b, (int64_t)(tok0 + t) * n_experts + e, e, out[t]);
 }
 
-// Tiled form (d a multiple of 4, rows 16-byte aligned): one CTA = NE experts x NT tokens.
-// The NE router rows and the NT token rows stream through shared memory in slices of KC
-// columns, STAGES slices in flight (cp.async); warp w owns expert (w / (NT/4)) and tokens
-// 4 (w % (NT/4)) .. +3, 8 lanes per token running the 8 accumulator chains in order.
-// Two shapes: RtBig for throughput, RtSmall (<= 4 tokens) keeps a deeper queue of the
-// router rows in flight because at small batches those come cold from HBM.
-template <int NE_, int NT_, int KC_, int STAGES_>
-struct RtShape {
-    static constexpr int NE = NE_, NT = NT_, KC = KC_, STAGES = STAGES_, ROWS = NE_ + NT_, LD = KC_ + 8;
-    static constexpr size_t SMEM = (size_t)STAGES_ * ROWS * LD * sizeof(float);
-    static_assert(NE_ * NT_ / 4 <= 8 && NT_ % 4 == 0, "one warp per (expert, 4 tokens), 8 warps");
-};
-using RtBig = RtShape<2, 16, 256, 3>;
-using RtSmall = RtShape<1, 4, 512, 6>;
-
-__device__ __forceinline__ void rt_cp16(float *dst, const float *src) {
-    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src) : "memory");
-}
-
-// returns the logit in the lanes with (lane & 7) == 0 of valid (expert, token) pairs; valid tells which
-template <class S>
-__device__ __forceinline__ float router_tile_logits(const float *__restrict__ gate_w, const float *__restrict__ x, int n_experts, int d,
-                                                    int n_tokens, int e0, int tok0, float *rsm, int *e_out, int *tok_out, bool *valid) {
-    constexpr int TG = S::NT / 4; // token groups of 4
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, sub = lane >> 3, j = lane & 7;
-    const int full = d & ~7;
-    const int nch = (full + S::KC - 1) / S::KC;
-    const int ntl = min(S::NT, n_tokens - tok0), nrows = S::NE + ntl;
-    auto issue = [&](int ch) {
-        float *stage = rsm + (size_t)(ch % S::STAGES) * S::ROWS * S::LD;
-        const int c0 = ch * S::KC;
-        for (int idx = tid; idx < nrows * (S::KC / 4); idx += 256) {
-            const int row = idx / (S::KC / 4), c = c0 + (idx % (S::KC / 4)) * 4;
-            if (c >= full) continue;                 // full is a multiple of 8, c of 4: c < full => c + 3 < full
-            const float *src = row < S::NE ? gate_w + (size_t)min(e0 + row, n_experts - 1) * d + c
-                                           : x + (size_t)(tok0 + row - S::NE) * d + c;
-            rt_cp16(stage + row * S::LD + (c - c0), src);
-        }
-    };
-    for (int sidx = 0; sidx < S::STAGES - 1; ++sidx) {
-        if (sidx < nch) issue(sidx);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-    }
-    const int el = warp / TG, tl = (warp % TG) * 4 + sub;
-    const bool act = warp < S::NE * TG && (warp % TG) * 4 < ntl; // the other warps only copy
-    float acc = 0.0f;
-    for (int ch = 0; ch < nch; ++ch) {
-        asm volatile("cp.async.wait_group %0;\n" ::"n"(S::STAGES - 2) : "memory");
-        __syncthreads();
-        if (ch + S::STAGES - 1 < nch) issue(ch + S::STAGES - 1);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        if (act) {
-            const float *stage = rsm + (size_t)(ch % S::STAGES) * S::ROWS * S::LD;
-            const float *ws = stage + el * S::LD + j, *xr = stage + (S::NE + min(tl, ntl - 1)) * S::LD + j;
-            const int kmax = min(S::KC, full - ch * S::KC);
-#pragma unroll 32
-            for (int c = 0; c < kmax; c += 8) acc = __fadd_rn(acc, __fmul_rn(ws[c], xr[c]));
-        }
-    }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    const int base = lane & ~7;
-    const float v1 = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 1));
-    const float p01 = __shfl_sync(0xFFFFFFFFu, v1, base + 0), p23 = __shfl_sync(0xFFFFFFFFu, v1, base + 2);
-    const float p45 = __shfl_sync(0xFFFFFFFFu, v1, base + 4), p67 = __shfl_sync(0xFFFFFFFFu, v1, base + 6);
-    float sres = __fadd_rn(__fadd_rn(__fadd_rn(p01, p23), p45), p67);
-    const int e = e0 + el, tok = tok0 + tl;
-    *valid = act && j == 0 && tl < ntl && e < n_experts;
-    if (*valid)
-        for (int c = full; c < d; ++c) sres = __fadd_rn(sres, __fmul_rn(__ldg(gate_w + (size_t)e * d + c), __ldg(x + (size_t)tok * d + c)));
-    *e_out = e;
-    *tok_out = tok;
-    return sres;
-}
+// Tiled form (mkf::tile_dot; d a multiple of 4, rows 16-byte aligned).  Two shapes: RtBig
+// for throughput, RtSmall (<= 4 tokens) keeps a deeper queue of the router rows in flight
+// because at small batches those come cold from HBM.
+using RtBig = mkf::TileShape<2, 16, 256, 3>;
+using RtSmall = mkf::TileShape<1, 4, 512, 6>;
 
 template <class S>
 __global__ void __launch_bounds__(256)
@@ -182,7 +92,7 @@ moe_router_tile_kernel(const float *__restrict__ gate_w, const float *__restrict
     extern __shared__ __align__(16) float rsm[];
     int e, tok;
     bool valid;
-    const float l = router_tile_logits<S>(gate_w, x, n_experts, d, n_tokens, blockIdx.x * S::NE, blockIdx.y * S::NT, rsm, &e, &tok, &valid);
+    const float l = mkf::tile_dot<S>(gate_w, x, n_experts, d, n_tokens, blockIdx.x * S::NE, blockIdx.y * S::NT, rsm, &e, &tok, &valid);
     if (valid) router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, l);
 }
 
@@ -349,7 +259,7 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
     {
         int e, tok;
         bool valid;
-        const float l = router_tile_logits<S>(a.gate_w, a.x, n_experts, d, n_tokens, blockIdx.x * S::NE, 0, rsm, &e, &tok, &valid);
+        const float l = mkf::tile_dot<S>(a.gate_w, a.x, n_experts, d, n_tokens, blockIdx.x * S::NE, 0, rsm, &e, &tok, &valid);
         if (valid) router_store(a.logits, a.score, a.key, a.gate_b, (int64_t)tok * n_experts + e, e, l);
     }
     // ---- the last logits CTA to get here does the rest

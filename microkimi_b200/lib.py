@@ -65,6 +65,10 @@ SIGNATURES = {
     "mk_quantize_q8": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "mk_matvec_mxfp4": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_mxfp4_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "mk_weight_f32": (_i32, [_vp, _vp, _i64, _i64, _i32, C.POINTER(_vp)]),
+    "mk_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _i32]),
+    "mk_matvec_f32_dev": (_i32, [_vp, _vp, _vp, _vp, _i32]),
+    "mk_rmsnorm_dev": (_i32, [_vp, _vp, _vp, _i32, _i32, C.c_float, _vp]),
     "mk_matvec_mxfp4_noalloc_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_q8": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_matvec_q8_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),

@@ -187,6 +187,53 @@ class MxFp4Weight(_Weight):
         return p, s
 
 
+class F32Weight(_Weight):
+    """A dense f32 matrix [rows, cols] resident on the GPU (the operand of the engine's
+    matvec, src/model.rs:199)."""
+
+    def __init__(self, w, rows, cols, ctx=None):
+        ctx = ctx or Context.default()
+        h = C.c_void_p()
+        if _is_torch_cuda(w):
+            import torch
+            assert w.dtype == torch.float32 and w.is_contiguous() and w.numel() == rows * cols
+            _l.check(ctx._L.mk_weight_f32(ctx._h, C.c_void_p(w.data_ptr()), rows, cols, 1, C.byref(h)))
+        else:
+            w = np.ascontiguousarray(w, dtype=np.float32)
+            assert w.size == rows * cols, "w must hold rows*cols floats"
+            _l.check(ctx._L.mk_weight_f32(ctx._h, _np_ptr(w), rows, cols, 0, C.byref(h)))
+        super().__init__(ctx, h, rows, cols)
+
+    def matvec(self, x):
+        """out[r] = dot(w[r], x) with the engine's dot() order (model::matvec). x: [cols] or [batch, cols]."""
+        L = self.ctx._L
+        batch, y, fn, args = self._run(L.mk_matvec_f32, L.mk_matvec_f32_dev, x, "q8", False)
+        _l.check(fn(self.ctx._h, self._h, *args[:3]))
+        return y[0] if (x.ndim if hasattr(x, "ndim") else x.dim()) == 1 else y
+
+
+def matvec(w, rows, cols, x, ctx=None):
+    """Drop-in for model::matvec / metal::gpu_matvec with borrowed host slices."""
+    h = F32Weight(w, rows, cols, ctx)
+    try:
+        return h.matvec(x)
+    finally:
+        h.free()
+
+
+def rmsnorm(x, w, eps, ctx=None):
+    """rmsnorm (src/model.rs:599-605) on torch CUDA rows x [n, len] (or [len]) with weights w [len]."""
+    import torch
+    ctx = ctx or Context.default()
+    assert _is_torch_cuda(x) and _is_torch_cuda(w) and x.dtype == torch.float32 and w.dtype == torch.float32
+    assert x.is_contiguous() and w.is_contiguous() and x.shape[-1] == w.numel()
+    n = 1 if x.dim() == 1 else x.shape[0]
+    out = torch.empty_like(x)
+    _l.check(ctx._L.mk_rmsnorm_dev(ctx._h, C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), n, x.shape[-1], float(eps),
+                                   C.c_void_p(out.data_ptr())))
+    return out
+
+
 def matvec_packed(packed, scales, rows, cols, x, act="q8", strict=False, ctx=None):
     """Drop-in for mxfp4::matvec_packed / metal::gpu_matvec_fp4 with borrowed host
     slices: registers the matrix, multiplies, frees.  Callers that reuse a matrix
