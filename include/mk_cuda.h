@@ -175,15 +175,27 @@ int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, int32_t n, i
 /* ---- MoE layer ---------------------------------------------------------
  * One call per layer instead of 3 matvecs per selected expert: replaces
  * moe_forward / ds_moe wholesale (src/model.rs:2150-2380, src/deepseek.rs:1038-1108).
- *   router     : noaux_tc - logits = gate_w x in the engine's dot() order (bit-exact),
- *                sigmoid, +bias for selection only, top-k by (key desc, index asc),
- *                weights = score / (sum + 1e-20)            (src/model.rs:2153-2173)
+ *   router     : logits = gate_w x in the engine's dot() order (bit-exact); bias for
+ *                selection only; top-k by (key desc, index asc)
+ *     MK_ROUTER_SIGMOID      : score = sigmoid(logit), weights = score / (sum + 1e-20)
+ *                              (K3 noaux_tc, src/model.rs:2153-2173)
+ *     MK_ROUTER_SQRT_SOFTPLUS: score = sqrt(softplus(logit)), weights = score / sum * route_scale
+ *                              (DeepSeek gate_forward, src/deepseek.rs:16-58; its hash layers,
+ *                              which read the ids from a table, go through mk_moe_experts_dev)
  *   experts    : MXFP4 w1/w3 -> act -> w2 through the q8 integer path
- *   MK_MOE_SWIGLU_CLAMP: act = (wgt * silu(min(g, limit))) * clamp(u, +-limit), the
- *                routing weight folded in BEFORE w2, outputs summed in slot order,
- *                plus one unweighted shared expert        (src/deepseek.rs:1083-1106)
- * Expert index n_experts names the shared expert. */
+ *     MK_MOE_SWIGLU_CLAMP: act = (wgt * silu(min(g, limit))) * clamp(u, +-limit), the routing
+ *                weight folded in BEFORE w2, outputs summed in slot order, plus one
+ *                unweighted MXFP4 shared expert `shared`      (src/deepseek.rs:1083-1106)
+ *     MK_MOE_SITU: the K3 body (src/model.rs:2202-2380): act = situ(g, u), y = sum of
+ *                wgt_i * o_i in slot order.  With `latent` > 0 the experts work on
+ *                h = routed_down x (w1, w3: [inter, latent], w2: [latent, inter]) and the
+ *                layer returns routed_up rmsnorm(y, routed_norm, rms_eps); the f32 shared
+ *                expert `shared_f32` (SiTU MLP on the layer input) is added to the result.
+ * Expert index n_experts names the MXFP4 shared expert. */
 #define MK_MOE_SWIGLU_CLAMP 0
+#define MK_MOE_SITU         1
+#define MK_ROUTER_SIGMOID       0
+#define MK_ROUTER_SQRT_SOFTPLUS 1
 typedef struct {
     int32_t n_experts, top_k, d, inter;
     float   swiglu_limit;
@@ -192,7 +204,15 @@ typedef struct {
     const float *gate_b;             /* HOST f32 [n_experts]; NULL = zeros */
     const mk_weight *const *experts; /* [n_experts * 3] = w1 [inter,d], w2 [d,inter], w3 [inter,d] per expert;
                                         NULL entries = expert not resident on this GPU (expert parallel) */
-    const mk_weight *shared[3];      /* shared expert w1, w2, w3; all NULL = none here */
+    const mk_weight *shared[3];      /* MXFP4 shared expert w1, w2, w3; all NULL = none here */
+    int32_t router;                  /* MK_ROUTER_* */
+    float   route_scale;             /* MK_ROUTER_SQRT_SOFTPLUS only; 0 is read as 1 */
+    int32_t latent;                  /* MK_MOE_SITU: routed_hidden, the width the experts work on; 0 = d */
+    float   rms_eps;
+    const mk_weight *routed_down;    /* f32 [latent, d]   (mk_weight_f32) */
+    const mk_weight *routed_up;      /* f32 [d, latent] */
+    const float *routed_norm;        /* HOST f32 [latent] */
+    const mk_weight *shared_f32[3];  /* f32 shared expert: gate [si, d], down [d, si], up [si, d]; all NULL = none */
 } mk_moe_desc;
 int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out);
 int32_t mk_moe_free(mk_ctx *ctx, mk_moe *moe);

@@ -17,10 +17,22 @@
 using namespace mkq;
 
 struct mk_moe {
-    int n_experts, top_k, d, inter, activation;
+    int n_experts, top_k, d, inter, activation;   // d: width the experts work on (the latent width when there is one)
+    int dx;                        // model width: router rows, layer input and output
+    int router_kind;               // MK_ROUTER_*
+    float route_scale;
     float limit;
     bool has_router, has_shared;
     float *gate_w, *gate_b;        // device
+    // K3 latent MoE (src/model.rs:2202-2380); the f32 matrices belong to the caller's handles
+    int latent;                    // routed_hidden, 0 = none
+    const float *routed_down, *routed_up; // device f32 [latent, dx], [dx, latent]
+    float *routed_norm;            // device f32 [latent] (owned)
+    float rms_eps;
+    const float *sh_gate, *sh_down, *sh_up; // f32 shared expert [si, dx], [dx, si], [si, dx]; nullptr = none
+    int shared_inter;
+    float *lat_h, *lat_y, *lat_yn; // [cap_rows][latent]: routed_down x, weighted expert sum, its rmsnorm
+    float *sh_a, *sh_u;            // [cap_rows][shared_inter]
     const void **wv, **wsc;        // device tables [(n_experts+1)*3] of tiled values / scales (nullptr = not resident)
     int64_t nbp_d, nbp_i;          // padded block counts of d and inter
     // workspace, sized for cap_rows activation rows and cap_pairs pairs
@@ -45,13 +57,20 @@ namespace {
 // logits[t][e] = dot(gate_w[e], x[t]) in the engine's order (src/model.rs:63-82):
 // 8 accumulators, element j of each 8-chunk into accumulator j with a separate
 // multiply and add, then ((a0+a1)+(a2+a3))+(a4+a5))+(a6+a7), tail sequential.
-// Every logits kernel also stores score = 1/(1+exp(-l)) and key = score + bias
-// (src/model.rs:2152-2156); exp() runs in double and is rounded once, which agrees
-// with a correctly rounded expf.
+// Every logits kernel also stores the score - MK_ROUTER_SIGMOID: 1/(1+exp(-l))
+// (src/model.rs:2152-2156); MK_ROUTER_SQRT_SOFTPLUS: sqrt(softplus(l)), softplus = l above 20,
+// else ln(1 + exp(l)) (src/deepseek.rs:29-32, 60-68) - and key = score + bias.  exp() and
+// log() run in double and are rounded once, which agrees with a correctly rounded libm.
 __device__ __forceinline__ void router_store(float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key,
-                                             const float *__restrict__ gate_b, int64_t at, int e, float l) {
-    const float ex = (float)exp((double)(-l));
-    const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
+                                             const float *__restrict__ gate_b, int64_t at, int e, float l, int kind) {
+    float sg;
+    if (kind == MK_ROUTER_SQRT_SOFTPLUS) {
+        const float sp = l > 20.0f ? l : (float)log((double)__fadd_rn(1.0f, (float)exp((double)l)));
+        sg = __fsqrt_rn(sp);
+    } else {
+        const float ex = (float)exp((double)(-l));
+        sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
+    }
     logits[at] = l;
     score[at] = sg;
     key[at] = __fadd_rn(sg, gate_b ? gate_b[e] : 0.0f);
@@ -62,7 +81,7 @@ template <int T>
 __global__ void __launch_bounds__(256)
 moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
                          float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key, int n_experts, int d,
-                         int n_tokens) {
+                         int n_tokens, int kind) {
     const int warp_g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
     const int ewarps = (n_experts + 3) / 4;
@@ -75,7 +94,7 @@ moe_router_logits_kernel(const float *__restrict__ gate_w, const float *__restri
     mkf::rows_dot<T>(gate_w + (size_t)(ev ? e : 0) * d, x, d, n_tokens, tok0, ev, lane, out);
 #pragma unroll
     for (int t = 0; t < T; ++t)
-        if (j == 0 && ev && tok0 + t < n_tokens) router_store(logits, score, key, gate_b, (int64_t)(tok0 + t) * n_experts + e, e, out[t]);
+        if (j == 0 && ev && tok0 + t < n_tokens) router_store(logits, score, key, gate_b, (int64_t)(tok0 + t) * n_experts + e, e, out[t], kind);
 }
 
 // Tiled form (mkf::tile_dot; d a multiple of 4, rows 16-byte aligned).  Two shapes: RtBig
@@ -88,18 +107,19 @@ template <class S>
 __global__ void __launch_bounds__(256)
 moe_router_tile_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
                        float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key, int n_experts, int d,
-                       int n_tokens) {
+                       int n_tokens, int kind) {
     extern __shared__ __align__(16) float rsm[];
     int e, tok;
     bool valid;
     const float l = mkf::tile_dot<S>(gate_w, x, n_experts, d, n_tokens, blockIdx.x * S::NE, blockIdx.y * S::NT, rsm, &e, &tok, &valid);
-    if (valid) router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, l);
+    if (valid) router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, l, kind);
 }
 
 // ------------------------------------------------------------------ top-k
 // One warp per token.  The top_k by (key descending, index ascending) in that order is
 // what the engine's running selection ends with (src/model.rs:2157-2171); weights =
-// score / (sum + 1e-20) with the sum taken in slot order (src/model.rs:2172-2173).
+// score / (sum + 1e-20) with the sum taken in slot order (src/model.rs:2172-2173), or for
+// MK_ROUTER_SQRT_SOFTPLUS score / sum * route_scale (src/deepseek.rs:51-56).
 // kb: n_experts floats of shared memory owned by this warp.
 __device__ __forceinline__ uint32_t float_order(float f) {
     const uint32_t b = __float_as_uint(f);
@@ -107,7 +127,8 @@ __device__ __forceinline__ uint32_t float_order(float f) {
 }
 __device__ __forceinline__ void topk_token(const float *score, const float *key, int n_experts, int top_k, int tok, int lane, float *kb,
                                            int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
-                                           int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot) {
+                                           int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot,
+                                           int kind, float route_scale) {
     for (int e = lane; e < n_experts; e += 32) kb[e] = __fadd_rn(__ldcg(key + (size_t)tok * n_experts + e), 0.0f); // -0 -> +0
     __syncwarp();
     int my_id = 0;
@@ -129,10 +150,11 @@ __device__ __forceinline__ void topk_token(const float *score, const float *key,
     const float my_sc = lane < top_k ? __ldcg(score + (size_t)tok * n_experts + my_id) : 0.0f;
     float sumw = 0.0f;
     for (int r = 0; r < top_k; ++r) sumw = __fadd_rn(sumw, __shfl_sync(0xFFFFFFFFu, my_sc, r));
-    sumw = __fadd_rn(sumw, 1e-20f);
+    if (kind != MK_ROUTER_SQRT_SOFTPLUS) sumw = __fadd_rn(sumw, 1e-20f);
     const int slots = top_k + (shared_slot ? 1 : 0);
     if (lane < top_k) {
-        const float w = __fdiv_rn(my_sc, sumw);
+        float w = __fdiv_rn(my_sc, sumw);
+        if (kind == MK_ROUTER_SQRT_SOFTPLUS) w = __fmul_rn(w, route_scale);
         ids[(size_t)tok * top_k + lane] = my_id;
         wts[(size_t)tok * top_k + lane] = w;
         if (pair_row) {
@@ -153,13 +175,14 @@ __device__ __forceinline__ void topk_token(const float *score, const float *key,
 __global__ void __launch_bounds__(128)
 moe_topk_kernel(const float *__restrict__ score, const float *__restrict__ key, int n_experts, int top_k, int n_tokens,
                 int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
-                int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot) {
+                int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot, int kind,
+                float route_scale) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (blockDim.x >> 5) + warp;
     if (tok >= n_tokens) return;
     topk_token(score, key, n_experts, top_k, tok, lane, sm + (size_t)warp * n_experts, ids, wts, pair_row, pair_expert, pair_weight,
-               shared_slot);
+               shared_slot, kind, route_scale);
 }
 
 // Grouping of a SMALL pair list by one CTA without per-expert arrays: the place of a pair
@@ -222,7 +245,8 @@ __device__ __forceinline__ void plan_small(const int32_t *pair_expert, int n_pai
 struct RouterFusedArgs {
     const float *gate_w, *gate_b, *x;
     float *logits, *score, *key;
-    int n_experts, d, n_tokens, top_k, shared_slot;
+    int n_experts, d, n_tokens, top_k, shared_slot, router_kind;
+    float route_scale;
     int32_t *ids; float *wts;
     int32_t *pair_row, *pair_expert; float *pair_weight;
     const void *const *wv;
@@ -260,7 +284,7 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
         int e, tok;
         bool valid;
         const float l = mkf::tile_dot<S>(a.gate_w, a.x, n_experts, d, n_tokens, blockIdx.x * S::NE, 0, rsm, &e, &tok, &valid);
-        if (valid) router_store(a.logits, a.score, a.key, a.gate_b, (int64_t)tok * n_experts + e, e, l);
+        if (valid) router_store(a.logits, a.score, a.key, a.gate_b, (int64_t)tok * n_experts + e, e, l, a.router_kind);
     }
     // ---- the last logits CTA to get here does the rest
     __shared__ int s_last;
@@ -278,7 +302,7 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
         for (int tok = warp; tok < n_tokens; tok += nw)
             topk_token(a.score, a.key, n_experts, a.top_k, tok, lane, rsm + (size_t)warp * n_experts, a.ids, a.wts, a.pair_row,
-                       a.pair_expert, a.pair_weight, a.shared_slot);
+                       a.pair_expert, a.pair_weight, a.shared_slot, a.router_kind, a.route_scale);
     }
     __threadfence_block();
     __syncthreads();
@@ -353,6 +377,7 @@ struct MoeArgs {
     float *outs;                 // [pairs][d]
     int64_t nbp_d, nbp_i;
     int d, inter;
+    int activation;              // MK_MOE_*
     float limit;
     Consts k;
 };
@@ -453,11 +478,16 @@ __global__ void __launch_bounds__(MK_G1_KS * 128, MODE == MOE_BIG_ITEMS ? MK_MOE
         float gate = part[jg][r16][c], up = part[ju][r16][c];
 #pragma unroll
         for (int q = 1; q < MK_G1_KS; ++q) { gate += part[jg + q][r16][c]; up += part[ju + q][r16][c]; }
-        const float gl = fminf(gate, a.limit);
-        const float ul = fminf(fmaxf(up, -a.limit), a.limit);
-        const float ex = (float)exp((double)(-gl));
-        const float silu = __fdiv_rn(gl, __fadd_rn(1.0f, ex));
-        const float act = __fmul_rn(__fmul_rn(wgt_s[c], silu), ul);
+        float act;
+        if (a.activation == MK_MOE_SITU) {
+            act = mk_situ(gate, up); // the routing weight is applied after w2 (src/model.rs:2346-2351)
+        } else {
+            const float gl = fminf(gate, a.limit);
+            const float ul = fminf(fmaxf(up, -a.limit), a.limit);
+            const float ex = (float)exp((double)(-gl));
+            const float silu = __fdiv_rn(gl, __fadd_rn(1.0f, ex));
+            act = __fmul_rn(__fmul_rn(wgt_s[c], silu), ul);
+        }
         float mx = fabsf(act);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
@@ -506,7 +536,10 @@ __global__ void __launch_bounds__(256, MODE == MOE_BIG_ITEMS ? MK_MOE_BIG_CTAS :
     const int tl = threadIdx.x >> 7, r16 = (threadIdx.x >> 3) & 15, c = threadIdx.x & 7;
     const int64_t row = ((int64_t)blockIdx.x * 2 + tl) * 16 + r16;
     if (c < n && row < a.d) {
-        const float v = ((part[tl * 4 + 0][r16][c] + part[tl * 4 + 1][r16][c]) + part[tl * 4 + 2][r16][c]) + part[tl * 4 + 3][r16][c];
+        float v = ((part[tl * 4 + 0][r16][c] + part[tl * 4 + 1][r16][c]) + part[tl * 4 + 2][r16][c]) + part[tl * 4 + 3][r16][c];
+        // K3 body: the routing weight multiplies the expert output, y += w_i * o_i (src/model.rs:2346-2351);
+        // the product is formed here and the combine step adds the terms in slot order
+        if (a.activation == MK_MOE_SITU) v = __fmul_rn(a.pair_weight[pair_s[c]], v);
         a.outs[(int64_t)pair_s[c] * a.d + row] = v;
     }
 }
@@ -530,8 +563,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
 
 static void moe_free_ws(mk_moe *m) {
     void *ptrs[] = {m->logits, m->ids, m->wts, m->xq, m->xs, m->pair_row, m->pair_expert, m->pair_weight,
-                    m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs};
+                    m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs, m->lat_h, m->lat_y, m->lat_yn, m->sh_a, m->sh_u};
     for (void *p : ptrs) if (p) cudaFree(p);
+    m->lat_h = m->lat_y = m->lat_yn = m->sh_a = m->sh_u = nullptr;
     m->logits = nullptr; m->ids = nullptr; m->wts = nullptr; m->xq = nullptr; m->xs = nullptr;
     m->pair_row = m->pair_expert = nullptr; m->pair_weight = nullptr; m->sorted = m->items = m->n_items = nullptr;
     m->actq = nullptr; m->acts = nullptr; m->outs = nullptr;
@@ -564,6 +598,15 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     MK_CUDA(cudaMalloc(&m->actq, (size_t)np * ldq_i));
     MK_CUDA(cudaMalloc(&m->acts, (size_t)np * m->nbp_i * 4));
     MK_CUDA(cudaMalloc(&m->outs, (size_t)np * m->d * 4));
+    if (m->latent > 0) {
+        MK_CUDA(cudaMalloc(&m->lat_h, (size_t)nr * m->latent * 4));
+        MK_CUDA(cudaMalloc(&m->lat_y, (size_t)nr * m->latent * 4));
+        MK_CUDA(cudaMalloc(&m->lat_yn, (size_t)nr * m->latent * 4));
+    }
+    if (m->sh_gate) {
+        MK_CUDA(cudaMalloc(&m->sh_a, (size_t)nr * m->shared_inter * 4));
+        MK_CUDA(cudaMalloc(&m->sh_u, (size_t)nr * m->shared_inter * 4));
+    }
     // padded tails of the q8 rows must read as zero
     MK_CUDA(cudaMemsetAsync(m->actq, 0, (size_t)np * ldq_i, ctx->stream));
     MK_CUDA(cudaMemsetAsync(m->acts, 0, (size_t)np * m->nbp_i * 4, ctx->stream));
@@ -575,11 +618,31 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
 extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out) {
     MK_CHECK_ARG(ctx != nullptr && desc != nullptr && out != nullptr, "NULL argument");
     *out = nullptr;
-    const int E = desc->n_experts, k = desc->top_k, d = desc->d, I = desc->inter;
+    const int E = desc->n_experts, k = desc->top_k, dx = desc->d, I = desc->inter, latent = desc->latent;
+    const int d = latent > 0 ? latent : dx; // the width the experts work on
     MK_CHECK_ARG(E >= 1 && E <= 4095 && k >= 1 && k <= 31 && k <= E, "need 1 <= top_k <= min(31, n_experts) and n_experts <= 4095");
-    MK_CHECK_ARG(d > 0 && d % 32 == 0 && I > 0 && I % 32 == 0, "d and inter must be positive multiples of 32");
-    MK_CHECK_ARG(desc->activation == MK_MOE_SWIGLU_CLAMP, "unknown activation");
+    MK_CHECK_ARG(dx > 0 && dx % 32 == 0 && I > 0 && I % 32 == 0, "d and inter must be positive multiples of 32");
+    MK_CHECK_ARG(desc->activation == MK_MOE_SWIGLU_CLAMP || desc->activation == MK_MOE_SITU, "unknown activation");
+    MK_CHECK_ARG(desc->router == MK_ROUTER_SIGMOID || desc->router == MK_ROUTER_SQRT_SOFTPLUS, "unknown router kind");
     MK_CHECK_ARG(desc->experts != nullptr, "experts table is NULL");
+    const bool situ = desc->activation == MK_MOE_SITU;
+    auto f32ok = [](const mk_weight *w, int rows, int cols) { return w && w->fmt == MK_FMT_F32 && w->rows == rows && w->cols == cols; };
+    if (latent != 0) {
+        MK_CHECK_ARG(situ, "a latent width needs MK_MOE_SITU (the K3 body)");
+        MK_CHECK_ARG(latent > 0 && latent % 32 == 0, "latent must be a positive multiple of 32");
+        MK_CHECK_ARG(f32ok(desc->routed_down, latent, dx) && f32ok(desc->routed_up, dx, latent) && desc->routed_norm != nullptr,
+                     "latent MoE needs f32 routed_down [latent, d], routed_up [d, latent] and routed_norm [latent]");
+    }
+    const bool sh32 = desc->shared_f32[0] || desc->shared_f32[1] || desc->shared_f32[2];
+    int si = 0;
+    if (sh32) {
+        MK_CHECK_ARG(situ, "the f32 shared expert belongs to MK_MOE_SITU (the K3 body)");
+        MK_CHECK_ARG(desc->shared_f32[0] && desc->shared_f32[0]->fmt == MK_FMT_F32, "shared_f32[0] must be an f32 weight");
+        si = (int)desc->shared_f32[0]->rows;
+        MK_CHECK_ARG(f32ok(desc->shared_f32[0], si, dx) && f32ok(desc->shared_f32[1], dx, si) && f32ok(desc->shared_f32[2], si, dx),
+                     "f32 shared expert needs gate [si, d], down [d, si], up [si, d]");
+    }
+    if (situ) MK_CHECK_ARG(!desc->shared[0] && !desc->shared[1] && !desc->shared[2], "MK_MOE_SITU takes its shared expert in shared_f32");
     MK_CUDA(cudaSetDevice(ctx->device));
     std::vector<const void *> hv((size_t)(E + 1) * 3, nullptr), hs((size_t)(E + 1) * 3, nullptr);
     auto check = [&](const mk_weight *w, int rows, int cols) {
@@ -601,8 +664,19 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     mk_moe *m = new (std::nothrow) mk_moe();
     if (!m) return MK_ERR_OOM;
     memset(m, 0, sizeof(*m));
-    m->n_experts = E; m->top_k = k; m->d = d; m->inter = I; m->activation = desc->activation;
+    m->n_experts = E; m->top_k = k; m->d = d; m->dx = dx; m->inter = I; m->activation = desc->activation;
+    m->router_kind = desc->router;
+    m->route_scale = desc->route_scale == 0.0f ? 1.0f : desc->route_scale;
     m->limit = desc->swiglu_limit;
+    m->latent = latent > 0 ? latent : 0;
+    m->rms_eps = desc->rms_eps;
+    if (latent > 0) { m->routed_down = (const float *)desc->routed_down->values; m->routed_up = (const float *)desc->routed_up->values; }
+    if (sh32) {
+        m->sh_gate = (const float *)desc->shared_f32[0]->values;
+        m->sh_down = (const float *)desc->shared_f32[1]->values;
+        m->sh_up = (const float *)desc->shared_f32[2]->values;
+        m->shared_inter = si;
+    }
     m->has_router = desc->gate_w != nullptr;
     m->has_shared = hv[(size_t)E * 3] != nullptr;
     m->nbp_d = mk_ceil_div(d / 32, 4) * 4;
@@ -614,13 +688,17 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     if (e_ == cudaSuccess) e_ = cudaMemcpyAsync((void *)m->wv, hv.data(), tb, cudaMemcpyHostToDevice, ctx->stream);
     if (e_ == cudaSuccess) e_ = cudaMemcpyAsync((void *)m->wsc, hs.data(), tb, cudaMemcpyHostToDevice, ctx->stream);
     if (e_ == cudaSuccess && m->has_router) {
-        e_ = cudaMalloc(&m->gate_w, (size_t)E * d * 4);
+        e_ = cudaMalloc(&m->gate_w, (size_t)E * dx * 4);
         if (e_ == cudaSuccess) e_ = cudaMalloc(&m->gate_b, (size_t)E * 4);
-        if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->gate_w, desc->gate_w, (size_t)E * d * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->gate_w, desc->gate_w, (size_t)E * dx * 4, cudaMemcpyHostToDevice, ctx->stream);
         if (e_ == cudaSuccess) {
             if (desc->gate_b) e_ = cudaMemcpyAsync(m->gate_b, desc->gate_b, (size_t)E * 4, cudaMemcpyHostToDevice, ctx->stream);
             else e_ = cudaMemsetAsync(m->gate_b, 0, (size_t)E * 4, ctx->stream);
         }
+    }
+    if (e_ == cudaSuccess && latent > 0) {
+        e_ = cudaMalloc(&m->routed_norm, (size_t)latent * 4);
+        if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->routed_norm, desc->routed_norm, (size_t)latent * 4, cudaMemcpyHostToDevice, ctx->stream);
     }
     if (e_ == cudaSuccess) e_ = cudaMalloc(&m->counter, 4);
     if (e_ == cudaSuccess) e_ = cudaMemsetAsync(m->counter, 0, 4, ctx->stream);
@@ -644,6 +722,7 @@ extern "C" int32_t mk_moe_free(mk_ctx *ctx, mk_moe *m) {
     if (m->gate_w) cudaFree(m->gate_w);
     if (m->gate_b) cudaFree(m->gate_b);
     if (m->counter) cudaFree(m->counter);
+    if (m->routed_norm) cudaFree(m->routed_norm);
     delete m;
     return MK_OK;
 }
@@ -656,7 +735,7 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
     {
         mk_prof_scope prof(ctx, MK_PROF_ROUTER);
         const int ewarps = (E + 3) / 4;
-        if (m->d % 4 == 0 && ((uintptr_t)x & 15) == 0) {
+        if (m->dx % 4 == 0 && ((uintptr_t)x & 15) == 0) {
             static bool attr = false;
             if (!attr) {
                 cudaFuncSetAttribute(moe_router_tile_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtBig::SMEM);
@@ -665,23 +744,23 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
             }
             if (n <= RtSmall::NT)
                 moe_router_tile_kernel<RtSmall><<<dim3((unsigned)mk_ceil_div(E, RtSmall::NE), 1), 256, RtSmall::SMEM, ctx->stream>>>(
-                    m->gate_w, m->gate_b, x, m->logits, score, key, E, m->d, n);
+                    m->gate_w, m->gate_b, x, m->logits, score, key, E, m->dx, n, m->router_kind);
             else
                 moe_router_tile_kernel<RtBig><<<dim3((unsigned)mk_ceil_div(E, RtBig::NE), (unsigned)mk_ceil_div(n, RtBig::NT)), 256,
-                                                RtBig::SMEM, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits, score, key, E, m->d, n);
+                                                RtBig::SMEM, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits, score, key, E, m->dx, n, m->router_kind);
         } else if (n >= 4) {
             const int64_t warps = (int64_t)ewarps * mk_ceil_div(n, 4);
             moe_router_logits_kernel<4><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits,
-                                                                                                       score, key, E, m->d, n);
+                                                                                                       score, key, E, m->dx, n, m->router_kind);
         } else {
             const int64_t warps = (int64_t)ewarps * n;
             moe_router_logits_kernel<1><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits,
-                                                                                                       score, key, E, m->d, n);
+                                                                                                       score, key, E, m->dx, n, m->router_kind);
         }
         const size_t smem = (size_t)4 * E * sizeof(float);
         moe_topk_kernel<<<(unsigned)mk_ceil_div(n, 4), 128, smem, ctx->stream>>>(
             score, key, E, m->top_k, n, m->ids, m->wts, with_pairs ? m->pair_row : nullptr, m->pair_expert, m->pair_weight,
-            m->has_shared ? 1 : 0);
+            m->has_shared ? 1 : 0, m->router_kind, m->route_scale);
         ctx->launches += 2;
     }
     MK_CUDA(cudaGetLastError());
@@ -691,9 +770,9 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
 // grouped experts over an explicit pair list (device arrays); x rows already on device
 static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_rows, const int32_t *pair_row,
                                   const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs,
-                                  bool prepared = false) {
-    // prepared: the fused router kernel has already quantized x and grouped the pairs
-    if (!prepared) {
+                                  bool prepared = false, bool quantized = false) {
+    // prepared: the fused router kernel has already grouped the pairs; quantized: and quantized x
+    if (!quantized) {
         int32_t rc = mk_launch_quantize_act(ctx, x, n_rows, m->d, m->d, m->nbp_d, 0, m->xq, m->xs);
         if (rc != MK_OK) return rc;
     }
@@ -707,7 +786,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     MoeArgs a;
     a.wv = m->wv; a.wsc = m->wsc; a.items = m->items; a.n_items = m->n_items; a.sorted = m->sorted;
     a.pair_row = pair_row; a.pair_weight = pair_weight; a.xq = m->xq; a.xs = m->xs; a.actq = m->actq; a.acts = m->acts;
-    a.outs = outs; a.nbp_d = m->nbp_d; a.nbp_i = m->nbp_i; a.d = m->d; a.inter = m->inter; a.limit = m->limit;
+    a.outs = outs; a.nbp_d = m->nbp_d; a.nbp_i = m->nbp_i; a.d = m->d; a.inter = m->inter; a.activation = m->activation; a.limit = m->limit;
     a.k = Consts{65536u, 0xFFFFFFFFu, ctx->zeros_dev};
     // an upper bound on the work items of this call (the kernels exit early past *n_items)
     int items_ub = n_pairs / 8 + (n_pairs < slots ? n_pairs : slots);
@@ -776,21 +855,30 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
     const int slots = m->top_k + (m->has_shared ? 1 : 0);
     int32_t rc = moe_reserve(ctx, m, n, n * slots);
     if (rc != MK_OK) return rc;
+    // K3 latent MoE: the experts work on h = routed_down x (src/model.rs:2202-2204)
+    const float *xe = x;
+    if (m->latent > 0) {
+        rc = mk_launch_f32_gemv(ctx, m->routed_down, m->latent, m->dx, x, n, m->lat_h, m->latent, 0);
+        if (rc != MK_OK) return rc;
+        xe = m->lat_h;
+    }
     // small batches: router logits, activation quantization, top-k and pair grouping in ONE launch
     const bool small = n <= RtSmall::NT;
     size_t smem_f = small ? RtSmall::SMEM : RtBig::SMEM;
     if ((size_t)8 * m->n_experts * 4 > smem_f) smem_f = (size_t)8 * m->n_experts * 4;
     if ((size_t)3 * n * slots * 4 > smem_f) smem_f = (size_t)3 * n * slots * 4;
-    const bool fused = n <= 16 && m->d % 4 == 0 && ((uintptr_t)x & 15) == 0 && smem_f <= 200 * 1024 && !ctx->moe_no_fuse;
+    const bool fused = n <= 16 && m->dx % 4 == 0 && ((uintptr_t)x & 15) == 0 && smem_f <= 200 * 1024 && !ctx->moe_no_fuse;
+    const bool fused_q = fused && m->latent == 0; // the router's rows are the experts' rows: quantize them in the same launch
     if (fused) {
         RouterFusedArgs ra;
         ra.gate_w = m->gate_w; ra.gate_b = m->gate_b; ra.x = x; ra.logits = m->logits;
         ra.score = m->logits + (size_t)m->cap_rows * m->n_experts; ra.key = ra.score + (size_t)m->cap_rows * m->n_experts;
-        ra.n_experts = m->n_experts; ra.d = m->d; ra.n_tokens = n; ra.top_k = m->top_k; ra.shared_slot = m->has_shared ? 1 : 0;
+        ra.n_experts = m->n_experts; ra.d = m->dx; ra.n_tokens = n; ra.top_k = m->top_k; ra.shared_slot = m->has_shared ? 1 : 0;
+        ra.router_kind = m->router_kind; ra.route_scale = m->route_scale;
         ra.ids = m->ids; ra.wts = m->wts; ra.pair_row = m->pair_row; ra.pair_expert = m->pair_expert; ra.pair_weight = m->pair_weight;
         ra.wv = m->wv; ra.sorted = m->sorted; ra.items = m->items; ra.n_items = m->n_items; ra.max_items = m->max_items;
         ra.status = ctx->status_dev; ra.counter = m->counter; ra.xq = m->xq; ra.xs = m->xs; ra.nbp = m->nbp_d;
-        const unsigned qctas = (unsigned)mk_ceil_div((int64_t)n * m->nbp_d, 8);
+        const unsigned qctas = fused_q ? (unsigned)mk_ceil_div((int64_t)n * m->nbp_d, 8) : 0u;
         {
             mk_prof_scope prof(ctx, MK_PROF_ROUTER);
             static bool attr = false;
@@ -810,10 +898,27 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
         rc = moe_route_launch(ctx, m, x, n, true);
         if (rc != MK_OK) return rc;
     }
-    rc = moe_experts_launch(ctx, m, x, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, m->outs, fused);
+    rc = moe_experts_launch(ctx, m, xe, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, m->outs, fused, fused_q);
     if (rc != MK_OK) return rc;
-    rc = mk_moe_combine_dev(ctx, m->outs, n, slots, m->d, out);
+    // slot-order sum (for MK_MOE_SITU the terms already carry their routing weights)
+    rc = mk_moe_combine_dev(ctx, m->outs, n, slots, m->d, m->latent > 0 ? m->lat_y : out);
     if (rc != MK_OK) return rc;
+    if (m->latent > 0) {
+        // norm BEFORE the up projection (src/model.rs:2352-2356)
+        rc = mk_launch_rmsnorm(ctx, m->lat_y, m->routed_norm, n, m->latent, m->rms_eps, m->lat_yn);
+        if (rc != MK_OK) return rc;
+        rc = mk_launch_f32_gemv(ctx, m->routed_up, m->dx, m->latent, m->lat_yn, n, out, m->dx, 0);
+        if (rc != MK_OK) return rc;
+    }
+    if (m->sh_gate) {
+        // f32 shared expert on the layer input, added to the routed output (src/model.rs:2357-2378)
+        const int si = m->shared_inter;
+        rc = mk_launch_f32_gemv(ctx, m->sh_gate, si, m->dx, x, n, m->sh_a, si, 0);
+        if (rc == MK_OK) rc = mk_launch_f32_gemv(ctx, m->sh_up, si, m->dx, x, n, m->sh_u, si, 0);
+        if (rc == MK_OK) rc = mk_launch_situ(ctx, m->sh_a, m->sh_u, (int64_t)n * si, m->sh_a);
+        if (rc == MK_OK) rc = mk_launch_f32_gemv(ctx, m->sh_down, m->dx, si, m->sh_a, n, out, m->dx, 1);
+        if (rc != MK_OK) return rc;
+    }
     if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     return MK_OK;
@@ -823,7 +928,7 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
 extern "C" int32_t mk_moe_route(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, int32_t *ids, float *weights, float *logits) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && n > 0, "bad argument");
     MK_CUDA(cudaSetDevice(ctx->device));
-    const size_t xb = (size_t)n * m->d * 4;
+    const size_t xb = (size_t)n * m->dx * 4;
     int32_t rc = mk_io_reserve(ctx, mk_align_up(xb, 256));
     if (rc != MK_OK) return rc;
     MK_CUDA(cudaMemcpyAsync(ctx->io_dev, x, xb, cudaMemcpyHostToDevice, ctx->stream));
@@ -839,14 +944,14 @@ extern "C" int32_t mk_moe_route(mk_ctx *ctx, mk_moe *m, const float *x, int32_t 
 extern "C" int32_t mk_moe_forward(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && out != nullptr && n > 0, "bad argument");
     MK_CUDA(cudaSetDevice(ctx->device));
-    const size_t xb = mk_align_up((size_t)n * m->d * 4, 256);
+    const size_t xb = mk_align_up((size_t)n * m->dx * 4, 256);
     int32_t rc = mk_io_reserve(ctx, 2 * xb);
     if (rc != MK_OK) return rc;
     float *dx = (float *)ctx->io_dev, *dout = (float *)((char *)ctx->io_dev + xb);
-    MK_CUDA(cudaMemcpyAsync(dx, x, (size_t)n * m->d * 4, cudaMemcpyHostToDevice, ctx->stream));
+    MK_CUDA(cudaMemcpyAsync(dx, x, (size_t)n * m->dx * 4, cudaMemcpyHostToDevice, ctx->stream));
     rc = mk_moe_forward_dev(ctx, m, dx, n, dout, nullptr, nullptr);
     if (rc != MK_OK) return rc;
-    MK_CUDA(cudaMemcpyAsync(out, dout, (size_t)n * m->d * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaMemcpyAsync(out, dout, (size_t)n * m->dx * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
     MK_CUDA(cudaStreamSynchronize(ctx->stream));

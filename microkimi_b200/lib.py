@@ -14,6 +14,10 @@ MK_ACT_Q8X2 = 1
 MK_ACT_STRICT = 0x100
 MK_SCALE_F32 = 0
 MK_SCALE_F16 = 1
+MK_MOE_SWIGLU_CLAMP = 0
+MK_MOE_SITU = 1
+MK_ROUTER_SIGMOID = 0
+MK_ROUTER_SQRT_SOFTPLUS = 1
 PROF_CATEGORIES = {"matvec_mxfp4": 0, "lm_head": 1, "router": 2, "experts": 3, "mla": 4, "other": 5}
 
 
@@ -33,7 +37,9 @@ class MoeDesc(C.Structure):
     """mk_moe_desc"""
     _fields_ = [("n_experts", _i32), ("top_k", _i32), ("d", _i32), ("inter", _i32),
                 ("swiglu_limit", C.c_float), ("activation", _i32),
-                ("gate_w", _vp), ("gate_b", _vp), ("experts", C.POINTER(_vp)), ("shared", _vp * 3)]
+                ("gate_w", _vp), ("gate_b", _vp), ("experts", C.POINTER(_vp)), ("shared", _vp * 3),
+                ("router", _i32), ("route_scale", C.c_float), ("latent", _i32), ("rms_eps", C.c_float),
+                ("routed_down", _vp), ("routed_up", _vp), ("routed_norm", _vp), ("shared_f32", _vp * 3)]
 
 
 class MlaDesc(C.Structure):

@@ -306,33 +306,54 @@ class Q8Head(_Weight):
 
 
 class MoeLayer:
-    """One MoE layer resident on the GPU: the noaux_tc router of moe_forward
-    (src/model.rs:2153-2173) feeding MXFP4 experts with the SwiGLU-clamp body of ds_moe
-    (src/deepseek.rs:1038-1108), plus one unweighted shared expert.
+    """One MoE layer resident on the GPU.
+
+    Default: the noaux_tc router of moe_forward (src/model.rs:2153-2173) feeding MXFP4
+    experts with the SwiGLU-clamp body of ds_moe (src/deepseek.rs:1038-1108), plus one
+    unweighted MXFP4 shared expert.
+    router="sqrt_softplus": DeepSeek's gate_forward (src/deepseek.rs:16-58) with route_scale.
+    activation="situ": the K3 body (src/model.rs:2202-2380) - SiTU, routing weight applied
+    to the expert outputs; with routed_down / routed_up (F32Weight) and routed_norm the
+    experts work on the latent h = routed_down x and the layer returns
+    routed_up rmsnorm(y); shared_f32 = (gate, down, up) F32Weights is the f32 shared expert.
 
     experts: list over expert ids of (w1, w2, w3) MxFp4Weight triples, or None for an
     expert that lives on another GPU (expert parallel); shared: one triple or None.
+    `dx` is the layer's input/output width, `d` the width the experts work on.
     """
 
-    def __init__(self, gate_w, gate_b, experts, shared, top_k, swiglu_limit=10.0, ctx=None):
+    def __init__(self, gate_w, gate_b, experts, shared, top_k, swiglu_limit=10.0, ctx=None, router="sigmoid",
+                 route_scale=1.0, activation="swiglu_clamp", routed_down=None, routed_up=None, routed_norm=None,
+                 rms_eps=1e-6, shared_f32=None):
         ctx = ctx or Context.default()
         self.ctx = ctx
         self.n_experts = len(experts)
         self.top_k = int(top_k)
         first = next(t for t in list(experts) + [shared] if t is not None)
         self.inter, self.d = first[0].rows, first[0].cols
+        self.dx = routed_down.cols if routed_down is not None else self.d
         self.has_shared = shared is not None
-        self._keep = (experts, shared)
+        self._keep = (experts, shared, routed_down, routed_up, shared_f32)
         tbl = (C.c_void_p * (3 * self.n_experts))()
         for e, tri in enumerate(experts):
             for j in range(3):
                 tbl[3 * e + j] = tri[j]._h if tri is not None else None
         desc = _l.MoeDesc()
-        desc.n_experts, desc.top_k, desc.d, desc.inter = self.n_experts, self.top_k, self.d, self.inter
-        desc.swiglu_limit, desc.activation = float(swiglu_limit), 0
+        desc.n_experts, desc.top_k, desc.d, desc.inter = self.n_experts, self.top_k, self.dx, self.inter
+        desc.swiglu_limit = float(swiglu_limit)
+        desc.activation = {"swiglu_clamp": _l.MK_MOE_SWIGLU_CLAMP, "situ": _l.MK_MOE_SITU}[activation]
+        desc.router = {"sigmoid": _l.MK_ROUTER_SIGMOID, "sqrt_softplus": _l.MK_ROUTER_SQRT_SOFTPLUS}[router]
+        desc.route_scale, desc.rms_eps = float(route_scale), float(rms_eps)
+        if routed_down is not None:
+            rn = np.ascontiguousarray(routed_norm, dtype=np.float32)
+            assert rn.size == self.d, "routed_norm must hold one weight per latent column"
+            desc.latent = self.d
+            desc.routed_down, desc.routed_up, desc.routed_norm = routed_down._h, routed_up._h, _np_ptr(rn)
+        for j in range(3):
+            desc.shared_f32[j] = shared_f32[j]._h if shared_f32 is not None else None
         if gate_w is not None:
             gw = np.ascontiguousarray(gate_w, dtype=np.float32)
-            assert gw.shape == (self.n_experts, self.d)
+            assert gw.shape == (self.n_experts, self.dx)
             gb = np.ascontiguousarray(gate_b if gate_b is not None else np.zeros(self.n_experts), dtype=np.float32)
             desc.gate_w, desc.gate_b = _np_ptr(gw), _np_ptr(gb)
         desc.experts = C.cast(tbl, C.POINTER(C.c_void_p))
@@ -357,7 +378,7 @@ class MoeLayer:
         """Router only: (ids [n, top_k] int32, weights [n, top_k] f32[, logits [n, E]])."""
         if _is_torch_cuda(x):
             import torch
-            xs = x.reshape(-1, self.d)
+            xs = x.reshape(-1, self.dx)
             n = xs.shape[0]
             ids = torch.empty((n, self.top_k), dtype=torch.int32, device=x.device)
             w = torch.empty((n, self.top_k), dtype=torch.float32, device=x.device)
@@ -365,7 +386,7 @@ class MoeLayer:
             _l.check(self.ctx._L.mk_moe_route_dev(self.ctx._h, self._h, C.c_void_p(xs.data_ptr()), n, C.c_void_p(ids.data_ptr()),
                                                   C.c_void_p(w.data_ptr()), C.c_void_p(lg.data_ptr()) if want_logits else None))
             return (ids, w, lg) if want_logits else (ids, w)
-        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.d)
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.dx)
         n = x.shape[0]
         ids = np.empty((n, self.top_k), np.int32)
         w = np.empty((n, self.top_k), np.float32)
@@ -379,7 +400,7 @@ class MoeLayer:
         L = self.ctx._L
         if _is_torch_cuda(x):
             import torch
-            xs = x.reshape(-1, self.d)
+            xs = x.reshape(-1, self.dx)
             assert xs.dtype == torch.float32 and xs.is_contiguous()
             n = xs.shape[0]
             out = torch.empty_like(xs)
@@ -391,7 +412,7 @@ class MoeLayer:
             out = out.reshape(x.shape)
         else:
             xa = np.ascontiguousarray(x, dtype=np.float32)
-            xs = xa.reshape(-1, self.d)
+            xs = xa.reshape(-1, self.dx)
             n = xs.shape[0]
             out = np.empty_like(xs)
             ids = np.empty((n, self.top_k), np.int32) if want_routing else None

@@ -589,6 +589,44 @@ void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
     free(ids); free(wts); free(outs);
 }
 
+/* model.rs:2150-2380 : K3 latent MoE layer, one token */
+void or_moe_k3_forward(const or_moe_k3_desc *m, const float *x, float *out, int32_t *ids_out, float *w_out) {
+    size_t k = m->top_k, d = m->d, rh = m->rh, I = m->inter;
+    int32_t *ids = (int32_t *)malloc(sizeof(int32_t) * k);
+    float *wts = (float *)malloc(sizeof(float) * k);
+    float *h = (float *)malloc(sizeof(float) * rh);
+    float *outs = (float *)malloc(sizeof(float) * k * rh);
+    float *a = (float *)malloc(sizeof(float) * I), *u = (float *)malloc(sizeof(float) * I), *act = (float *)malloc(sizeof(float) * I);
+    float *y = (float *)calloc(rh, sizeof(float)), *yn = (float *)malloc(sizeof(float) * rh);
+    or_router_k3(m->gate_w, m->gate_b, m->n_experts, d, k, x, ids, wts, NULL);   /* :2152-2173 */
+    or_matvec_f32(m->routed_down, rh, d, x, h, 1);                               /* :2202-2203 */
+    for (size_t ei = 0; ei < k; ++ei) {                                          /* :2227-2260 */
+        const uint8_t *const *p = m->packed + (size_t)ids[ei] * 3, *const *s = m->scales + (size_t)ids[ei] * 3;
+        or_mxfp4_matvec(p[0], s[0], I, rh, h, a, 1, m->use_q8);
+        or_mxfp4_matvec(p[2], s[2], I, rh, h, u, 1, m->use_q8);
+        for (size_t j = 0; j < I; ++j) act[j] = or_situ(a[j], u[j]);
+        or_mxfp4_matvec(p[1], s[1], rh, I, act, outs + ei * rh, 1, m->use_q8);
+    }
+    for (size_t ei = 0; ei < k; ++ei)                                            /* :2346-2351 */
+        for (size_t j = 0; j < rh; ++j) y[j] += wts[ei] * outs[ei * rh + j];
+    or_rmsnorm(y, m->routed_norm, rh, m->rms_eps, yn);                           /* :2352-2354 */
+    or_matvec_f32(m->routed_up, d, rh, yn, out, 1);                              /* :2355-2356 */
+    if (m->shared_gate) {                                                        /* :2357-2378 */
+        size_t si = m->shared_inter;
+        float *sa = (float *)malloc(sizeof(float) * si), *su = (float *)malloc(sizeof(float) * si);
+        float *sout = (float *)malloc(sizeof(float) * d);
+        or_matvec_f32(m->shared_gate, si, d, x, sa, 1);
+        or_matvec_f32(m->shared_up, si, d, x, su, 1);
+        for (size_t j = 0; j < si; ++j) sa[j] = or_situ(sa[j], su[j]);
+        or_matvec_f32(m->shared_down, d, si, sa, sout, 1);
+        for (size_t j = 0; j < d; ++j) out[j] += sout[j];
+        free(sa); free(su); free(sout);
+    }
+    if (ids_out) memcpy(ids_out, ids, sizeof(int32_t) * k);
+    if (w_out) memcpy(w_out, wts, sizeof(float) * k);
+    free(ids); free(wts); free(h); free(outs); free(a); free(u); free(act); free(y); free(yn);
+}
+
 /* ------------------------------------------------------------------ MLA, per-head layout */
 or_mla_cache *or_mla_new(size_t nh, size_t nope, size_t rope, size_t vd, size_t cap) {
     or_mla_cache *c = (or_mla_cache *)calloc(1, sizeof(*c));

@@ -100,6 +100,28 @@ typedef struct {
 void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
                        int32_t *ids_out /* [top_k], nullable */, float *w_out /* nullable */, int n_threads);
 
+/* K3 latent MoE layer (model.rs:2150-2380), one token: router on x [d]; h = routed_down x;
+ * per selected expert a = w1 h, u = w3 h, act = situ(a, u), o = w2 act (MXFP4 experts over
+ * the latent width rh); y = sum of w_i * o_i in slot order; out = routed_up rmsnorm(y) plus
+ * the f32 shared expert (SiTU MLP on x). */
+typedef struct {
+    size_t d, rh, inter, n_experts, top_k, shared_inter;
+    float rms_eps;
+    int use_q8;
+    const float *gate_w;       /* [n_experts][d] */
+    const float *gate_b;       /* [n_experts] */
+    const float *routed_down;  /* [rh][d] */
+    const float *routed_norm;  /* [rh] */
+    const float *routed_up;    /* [d][rh] */
+    const float *shared_gate;  /* [shared_inter][d], NULL = no shared expert */
+    const float *shared_up;    /* [shared_inter][d] */
+    const float *shared_down;  /* [d][shared_inter] */
+    const uint8_t *const *packed; /* [n_experts*3] w1 [inter x rh], w2 [rh x inter], w3 [inter x rh] */
+    const uint8_t *const *scales;
+} or_moe_k3_desc;
+void or_moe_k3_forward(const or_moe_k3_desc *m, const float *x, float *out,
+                       int32_t *ids_out /* [top_k], nullable */, float *w_out /* nullable */);
+
 /* ---- MLA q8_0 cache, reference per-head layout (model.rs:765-781) ---- */
 typedef struct {
     size_t nh, nope, rope, vd;

@@ -55,6 +55,14 @@ class _MoeDesc(C.Structure):
                 ("sh_packed", _u8p * 3), ("sh_scales", _u8p * 3)]
 
 
+class _MoeK3Desc(C.Structure):
+    _fields_ = [("d", _sz), ("rh", _sz), ("inter", _sz), ("n_experts", _sz), ("top_k", _sz), ("shared_inter", _sz),
+                ("rms_eps", C.c_float), ("use_q8", C.c_int),
+                ("gate_w", _f32p), ("gate_b", _f32p), ("routed_down", _f32p), ("routed_norm", _f32p), ("routed_up", _f32p),
+                ("shared_gate", _f32p), ("shared_up", _f32p), ("shared_down", _f32p),
+                ("packed", C.POINTER(_u8p)), ("scales", C.POINTER(_u8p))]
+
+
 def _declare(L):
     def sig(name, res, *args):
         f = getattr(L, name)
@@ -88,6 +96,7 @@ def _declare(L):
     sig("or_gate_ds", None, _f32p, _f32p, _sz, _sz, _sz, C.c_float, _f32p, _i32p, _f32p)
     sig("or_expert_ds_f32", None, _f32p, _f32p, _f32p, _f32p, _sz, _sz, C.c_float, _f32p)
     sig("or_moe_ds_forward", None, C.POINTER(_MoeDesc), _f32p, _f32p, _i32p, _f32p, C.c_int)
+    sig("or_moe_k3_forward", None, C.POINTER(_MoeK3Desc), _f32p, _f32p, _i32p, _f32p)
     sig("or_mla_new", C.c_void_p, _sz, _sz, _sz, _sz, _sz)
     sig("or_mla_free", None, C.c_void_p)
     sig("or_mla_push", None, C.c_void_p, _f32p, _f32p)
@@ -321,6 +330,53 @@ class MoeDs:
         ids = np.empty(self.top_k, np.int32)
         w = np.empty(self.top_k, np.float32)
         lib().or_moe_ds_forward(C.byref(d), _p(x, _f32p), _p(out, _f32p), _p(ids, _i32p), _p(w, _f32p), n_threads)
+        return out, ids, w
+
+
+class MoeK3:
+    """K3 latent MoE layer (model.rs:2150-2380), one token at a time.
+
+    experts: list of (w1, w2, w3), each = (packed, scales) uint8 arrays over the latent width;
+    shared: (gate [si, d], up [si, d], down [d, si]) f32 arrays or None.
+    """
+
+    def __init__(self, gate_w, gate_b, routed_down, routed_norm, routed_up, experts, shared, top_k, rms_eps=1e-6):
+        self.gate_w, self.gate_b = _c(gate_w, np.float32), _c(gate_b, np.float32)
+        self.routed_down, self.routed_norm, self.routed_up = (_c(routed_down, np.float32), _c(routed_norm, np.float32),
+                                                            _c(routed_up, np.float32))
+        self.n_experts, self.d = self.gate_w.shape
+        self.rh = self.routed_down.shape[0]
+        self.top_k, self.rms_eps = top_k, float(rms_eps)
+        self.shared = None if shared is None else tuple(_c(a, np.float32) for a in shared)
+        self._keep = []
+        n = self.n_experts
+        self._pp = (_u8p * (3 * n))()
+        self._sp = (_u8p * (3 * n))()
+        for e, tri in enumerate(experts):
+            for j, (p, s) in enumerate(tri):
+                p, s = _c(p, np.uint8), _c(s, np.uint8)
+                self._keep += [p, s]
+                self._pp[3 * e + j] = _p(p, _u8p)
+                self._sp[3 * e + j] = _p(s, _u8p)
+        self.inter = experts[0][0][0].shape[0]
+
+    def forward(self, x, use_q8=True):
+        x = _c(x, np.float32)
+        d = _MoeK3Desc()
+        d.d, d.rh, d.inter, d.n_experts, d.top_k = self.d, self.rh, self.inter, self.n_experts, self.top_k
+        d.rms_eps, d.use_q8 = self.rms_eps, int(use_q8)
+        d.gate_w, d.gate_b = _p(self.gate_w, _f32p), _p(self.gate_b, _f32p)
+        d.routed_down, d.routed_norm, d.routed_up = (_p(self.routed_down, _f32p), _p(self.routed_norm, _f32p),
+                                                     _p(self.routed_up, _f32p))
+        if self.shared is not None:
+            d.shared_inter = self.shared[0].shape[0]
+            d.shared_gate, d.shared_up, d.shared_down = (_p(a, _f32p) for a in self.shared)
+        d.packed = C.cast(self._pp, C.POINTER(_u8p))
+        d.scales = C.cast(self._sp, C.POINTER(_u8p))
+        out = np.empty(self.d, np.float32)
+        ids = np.empty(self.top_k, np.int32)
+        w = np.empty(self.top_k, np.float32)
+        lib().or_moe_k3_forward(C.byref(d), _p(x, _f32p), _p(out, _f32p), _p(ids, _i32p), _p(w, _f32p))
         return out, ids, w
 
 

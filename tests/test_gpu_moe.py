@@ -127,3 +127,128 @@ def test_explicit_pairs_and_missing_experts(mk):
                      torch.from_numpy(pe2).cuda(), torch.tensor([1.0, 1.0]).cuda())
     torch.cuda.synchronize()
     assert ctx.status_word() == -1
+
+
+# ------------------------------------------------------------------ DeepSeek router (sqrt-softplus)
+def _dummy_experts(mk, n_experts, d, inter):
+    z = lambda r, c: mk.MxFp4Weight(np.zeros((r, c // 2), np.uint8), np.zeros((r, c // 32), np.uint8), r, c)
+    return [(z(inter, d), z(d, inter), z(inter, d)) for _ in range(n_experts)]
+
+
+def test_ds_router_matches_golden_gate(mk):
+    """gate_forward (src/deepseek.rs:16-58) on the reference's own vector: the 'gate' section of
+    ref/ds_golden2.json (3 tokens x 32 experts, top-6, route_scale 1.5), which the reference checks
+    in src/selftest.rs:259-311 with sorted ids and a 1e-3 weight tolerance."""
+    import os
+    from conftest import GOLDEN
+    g = np.load(os.path.join(GOLDEN, "ds_gate_expert.npz"))
+    gw, gb, x = g["gate_w"], g["gate_bias"], g["gate_x"]
+    d = gw.shape[1]
+    # the router works on rows of any multiple of 32; the golden d is 16, so pad rows with zeros
+    # (zero columns add exact zeros to every accumulator: same logits)
+    dp = 32
+    gwp = np.zeros((32, dp), np.float32); gwp[:, :d] = gw
+    xp = np.zeros((3, dp), np.float32); xp[:, :d] = x
+    layer = mk.MoeLayer(gwp, gb, _dummy_experts(mk, 32, dp, 32), None, 6, router="sqrt_softplus", route_scale=1.5)
+    ids, w = layer.route(xp)
+    scale = np.abs(g["gate_weights"]).max()
+    for t in range(3):
+        assert sorted(ids[t].tolist()) == sorted(g["gate_indices"][t].tolist())
+        want = dict(zip(g["gate_indices"][t].tolist(), g["gate_weights"][t].tolist()))
+        for i, wi in zip(ids[t].tolist(), w[t].tolist()):
+            assert abs(wi - want[i]) <= 1e-5 + 1e-3 * scale
+        ids_o, w_o = O.gate_ds(gw, gb, x[t], 6, 1.5)
+        assert np.array_equal(ids[t], ids_o), "slot order must match the CPU's"
+        assert np.abs(w[t] - w_o).max() <= 1e-6 * np.abs(w_o).max()
+
+
+@pytest.mark.parametrize("n_experts,top_k,d,batch", [(64, 6, 256, 5), (896, 16, 512, 19)])
+def test_ds_router_against_oracle(mk, n_experts, top_k, d, batch):
+    rng = np.random.default_rng(n_experts + d)
+    gw = (rng.standard_normal((n_experts, d)) * 0.3).astype(np.float32)   # logits on both sides of the softplus knee
+    gb = (rng.standard_normal(n_experts) * 0.1).astype(np.float32)
+    x = rng.standard_normal((batch, d)).astype(np.float32)
+    x[0] *= 8.0                                                             # some logits above the threshold of 20
+    layer = mk.MoeLayer(gw, gb, _dummy_experts(mk, n_experts, d, 32), None, top_k, router="sqrt_softplus", route_scale=2.5)
+    ids, w = layer.route(x)
+    for t in range(batch):
+        ids_o, w_o = O.gate_ds(gw, gb, x[t], top_k, 2.5)
+        assert np.array_equal(ids[t], ids_o)
+        assert np.abs(w[t] - w_o).max() <= 2e-6 * np.abs(w_o).max()
+
+
+# ------------------------------------------------------------------ K3 latent MoE (SiTU)
+def make_k3_layer(mk, n_experts, top_k, d, rh, inter, si, seed):
+    rng = np.random.default_rng(seed)
+    g = lambda *shape, s=0.02: (rng.standard_normal(shape) * s).astype(np.float32)
+    gate_w, gate_b = g(n_experts, d), g(n_experts, s=0.05)
+    routed_down, routed_up = g(rh, d, s=0.05), g(d, rh, s=0.05)
+    routed_norm = (1.0 + 0.1 * rng.standard_normal(rh)).astype(np.float32)
+    shared = (g(si, d, s=0.05), g(si, d, s=0.05), g(d, si, s=0.05))     # gate, up, down
+    host, dev = [], []
+    for e in range(n_experts):
+        tri_h, tri_d = [], []
+        for rows, cols in ((inter, rh), (rh, inter), (inter, rh)):
+            p, s = O.mxfp4_quantize(g(rows, cols, s=0.2))
+            tri_h.append((p, s))
+            tri_d.append(mk.MxFp4Weight(p, s, rows, cols))
+        host.append(tri_h)
+        dev.append(tuple(tri_d))
+    ref = O.MoeK3(gate_w, gate_b, routed_down, routed_norm, routed_up, host, shared, top_k, rms_eps=1e-6)
+    layer = mk.MoeLayer(gate_w, gate_b, dev, None, top_k, activation="situ",
+                        routed_down=mk.F32Weight(routed_down, rh, d), routed_up=mk.F32Weight(routed_up, d, rh),
+                        routed_norm=routed_norm, rms_eps=1e-6,
+                        shared_f32=(mk.F32Weight(shared[0], si, d), mk.F32Weight(shared[2], d, si), mk.F32Weight(shared[1], si, d)))
+    return layer, ref, rng
+
+
+@pytest.mark.parametrize("n_experts,top_k,d,rh,inter,si,batches", [
+    (896, 16, 512, 128, 64, 128, (1, 2, 5, 20)),     # the engine's micro configuration (src/config.rs:47-79)
+    (24, 4, 256, 64, 32, 96, (1, 3)),
+])
+def test_k3_latent_moe_against_oracle(mk, n_experts, top_k, d, rh, inter, si, batches):
+    """moe_forward of the K3 engine (src/model.rs:2150-2380): ids exact, output within 1e-3 * max
+    of the CPU q8 path (the f32 projections are bit-exact; the MXFP4 expert sums differ from the
+    CPU in summation order only, and SiTU's tanh/exp are correctly rounded here)."""
+    layer, ref, rng = make_k3_layer(mk, n_experts, top_k, d, rh, inter, si, seed=n_experts + d)
+    for b in batches:
+        x = rng.standard_normal((b, d)).astype(np.float32)
+        out, ids, w = layer.moe_forward(x, want_routing=True)
+        for t in range(b):
+            o_ref, ids_ref, w_ref = ref.forward(x[t], use_q8=True)
+            assert np.array_equal(ids[t], ids_ref)
+            assert np.abs(w[t] - w_ref).max() <= 1e-6 * np.abs(w_ref).max()
+            assert rel(out[t], o_ref) <= 1e-3
+        single = np.stack([layer.moe_forward(x[t]) for t in range(b)])
+        assert np.array_equal(bits(single), bits(out))
+
+
+def test_situ_without_latent_and_bad_descriptors(mk):
+    """MK_MOE_SITU on the model width (no latent projections): weights multiply the expert outputs."""
+    from microkimi_b200 import lib as L
+    rng = np.random.default_rng(3)
+    E, k, d, inter = 8, 2, 128, 64
+    gate_w = (rng.standard_normal((E, d)) * 0.02).astype(np.float32)
+    host, dev = [], []
+    for e in range(E):
+        tri_h, tri_d = [], []
+        for rows, cols in ((inter, d), (d, inter), (inter, d)):
+            p, s = O.mxfp4_quantize((rng.standard_normal((rows, cols)) * 0.2).astype(np.float32))
+            tri_h.append((p, s)); tri_d.append(mk.MxFp4Weight(p, s, rows, cols))
+        host.append(tri_h); dev.append(tuple(tri_d))
+    layer = mk.MoeLayer(gate_w, None, dev, None, k, activation="situ")
+    x = rng.standard_normal((3, d)).astype(np.float32)
+    out, ids, w = layer.moe_forward(x, want_routing=True)
+    for t in range(3):
+        y = np.zeros(d, np.float32)
+        for slot in range(k):
+            tri = host[ids[t, slot]]
+            a = O.mxfp4_matvec(tri[0][0], tri[0][1], x[t], use_q8=True)
+            u = O.mxfp4_matvec(tri[2][0], tri[2][1], x[t], use_q8=True)
+            act = np.array([O.lib().or_situ(float(a[j]), float(u[j])) for j in range(inter)], np.float32)
+            o = O.mxfp4_matvec(tri[1][0], tri[1][1], act, use_q8=True)
+            y = (y + (w[t, slot] * o).astype(np.float32)).astype(np.float32)
+        assert rel(out[t], y) <= 1e-3
+    # the K3 body takes its shared expert as f32 matrices: an MXFP4 shared triple is refused
+    with pytest.raises(L.MkError):
+        mk.MoeLayer(gate_w, None, dev, dev[0], k, activation="situ")
