@@ -80,7 +80,8 @@ struct mk_ctx {
     size_t io_pinned_bytes;
     int force_ks;           // 0 = choose per shape
     int moe_no_fuse;        // 1 = separate router / top-k / plan / quantize launches also for small batches (study knob)
-    int mla_no_tc;          // 1 = absorbed-layout attention on the CUDA-core kernel (study knob)
+    int mla_no_tc;
+    int mla_no_t5;          // 1 = absorbed MLA on the mma.sync kernel instead of the tcgen05 one (study knob)          // 1 = absorbed-layout attention on the CUDA-core kernel (study knob)
     // optional per-category event timing (mk_prof_*)
     int prof_on;
     struct mk_prof_pair *prof_pairs; // pool of event pairs

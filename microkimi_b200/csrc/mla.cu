@@ -23,6 +23,7 @@
 // (lane = columns).  Splits are merged by a second kernel with a log-sum-exp.
 #include "mk_common.cuh"
 #include "mla_tc.cuh"
+#include "mla_t5.cuh"
 
 struct mk_mla {
     int layout, H, nope, rope, vd, cap, nseq;
@@ -532,25 +533,45 @@ mla_attend_ph128_kernel(const MlaDev c, const int8_t *__restrict__ qq, const flo
     }
 }
 
-// log-sum-exp merge of the split partials: grid (H, nseq), one thread per column
-__global__ void mla_merge_kernel(int H, int vd, int nsplit, const float *__restrict__ part_m, const float *__restrict__ part_l,
-                                 const float *__restrict__ part_o, float *__restrict__ out) {
+// log-sum-exp merge of the split partials: grid (H, nseq, column chunks of 128), one thread per column;
+// the split weights exp(m_s - M) / L are formed once per CTA in shared memory (nsplit <= 1024)
+__global__ void __launch_bounds__(128) mla_merge_kernel(int H, int vd, int nsplit, const float *__restrict__ part_m,
+                                                        const float *__restrict__ part_l, const float *__restrict__ part_o,
+                                                        float *__restrict__ out) {
+    __shared__ float wgt[1024];
+    __shared__ float red[4];
     const int64_t bh = (int64_t)blockIdx.y * H + blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_m[bh * nsplit + s]);
+    for (int s = tid; s < nsplit; s += 128) M = fmaxf(M, part_m[bh * nsplit + s]);
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
     float L = 0.0f;
-    for (int s = 0; s < nsplit; ++s) {
+    for (int s = tid; s < nsplit; s += 128) {
         const float ms = part_m[bh * nsplit + s];
-        if (ms != -INFINITY) L += part_l[bh * nsplit + s] * expf(ms - M);
+        const float w = ms != -INFINITY ? expf(ms - M) : 0.0f;
+        wgt[s] = w;
+        L += part_l[bh * nsplit + s] * w;
     }
-    for (int col = threadIdx.x; col < vd; col += blockDim.x) {
-        float acc = 0.0f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float ms = part_m[bh * nsplit + s];
-            if (ms != -INFINITY) acc += part_o[(bh * nsplit + s) * vd + col] * expf(ms - M);
-        }
-        out[bh * vd + col] = acc / L;
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xFFFFFFFFu, L, o);
+    if (lane == 0) red[warp] = L;
+    __syncthreads();
+    L = (red[0] + red[1]) + (red[2] + red[3]);
+    const int col = blockIdx.z * 128 + tid;
+    if (col >= vd) return;
+    float acc0 = 0.0f, acc1 = 0.0f;
+    const float *po = part_o + bh * nsplit * vd + col;
+    int s = 0;
+    for (; s + 1 < nsplit; s += 2) {
+        const float w0 = wgt[s], w1 = wgt[s + 1];
+        if (w0 != 0.0f) acc0 += po[(int64_t)s * vd] * w0;       // an empty split's partial is never read
+        if (w1 != 0.0f) acc1 += po[(int64_t)(s + 1) * vd] * w1;
     }
+    if (s < nsplit && wgt[s] != 0.0f) acc0 += po[(int64_t)s * vd] * wgt[s];
+    out[bh * vd + col] = (acc0 + acc1) / L;
 }
 
 } // namespace
@@ -701,8 +722,32 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     int32_t rc = mk_launch_quantize_act(ctx, q, nq * m->H, m->nope, qdim, m->q_nbp, 0, m->qq, m->qs);
     if (rc != MK_OK) return rc;
     mk_prof_scope prof(ctx, MK_PROF_MLA);
+    if (m->layout == MK_MLA_ABSORBED && m->H == mla_t5::H && m->nope == mla_t5::LAT && m->vd == mla_t5::VD && !ctx->mla_no_tc &&
+        !ctx->mla_no_t5) {
+        // tcgen05 kernel: one CTA per (sequence, KV split), 128 positions per tile, accumulators in tensor memory
+        static bool attr5 = false;
+        if (!attr5) {
+            MK_CUDA(cudaFuncSetAttribute(mla_t5::mla_absorbed_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla_t5::SM_TOTAL));
+            attr5 = true;
+        }
+        const int nt128 = (max_n + mla_t5::TJ - 1) / mla_t5::TJ;
+        int ns = ctx->sm_count / nq;
+        if (ns > nt128) ns = nt128;
+        if (ns > m->max_split) ns = m->max_split;
+        if (ns < 1) ns = 1;
+        mla_t5::mla_absorbed_t5_kernel<<<dim3((unsigned)ns, (unsigned)nq), mla_t5::THREADS, mla_t5::SM_TOTAL, ctx->stream>>>(
+            m->vq, m->vs, m->cap, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0,
+            scale, ns, m->part_m, m->part_l, m->part_o, out, ctx->status_dev);
+        ctx->launches++;
+        if (ns > 1) {
+            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq, (unsigned)mk_ceil_div(m->vd, 128)), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
+            ctx->launches++;
+        }
+        MK_CUDA(cudaGetLastError());
+        return MK_OK;
+    }
     if (m->layout == MK_MLA_ABSORBED && m->H == mla_tc::H && m->nope == mla_tc::LAT && m->vd == mla_tc::VD && !ctx->mla_no_tc) {
-        // tensor-core kernel: one CTA per (sequence, KV split), 64 positions per tile
+        // mma.sync tensor-core kernel: one CTA per (sequence, KV split), 64 positions per tile
         static bool attr = false;
         if (!attr) {
             MK_CUDA(cudaFuncSetAttribute(mla_tc::mla_absorbed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla_tc::SM_TOTAL));
@@ -718,7 +763,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
             scale, ns, m->part_m, m->part_l, m->part_o, out);
         ctx->launches++;
         if (ns > 1) {
-            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
+            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq, (unsigned)mk_ceil_div(m->vd, 128)), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
             ctx->launches++;
         }
         MK_CUDA(cudaGetLastError());
@@ -751,7 +796,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
             m->part_m, m->part_l, m->part_o, out, ctx->status_dev);
         ctx->launches++;
         if (ns > 1) {
-            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
+            mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq, (unsigned)mk_ceil_div(m->vd, 128)), 128, 0, ctx->stream>>>(m->H, m->vd, ns, m->part_m, m->part_l, m->part_o, out);
             ctx->launches++;
         }
         MK_CUDA(cudaGetLastError());
@@ -778,7 +823,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
 #undef MLA_LAUNCH
     ctx->launches++;
     if (nsplit > 1) {
-        mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 128, 0, ctx->stream>>>(m->H, m->vd, nsplit, m->part_m, m->part_l, m->part_o, out);
+        mla_merge_kernel<<<dim3((unsigned)m->H, (unsigned)nq, (unsigned)mk_ceil_div(m->vd, 128)), 128, 0, ctx->stream>>>(m->H, m->vd, nsplit, m->part_m, m->part_l, m->part_o, out);
         ctx->launches++;
     }
     MK_CUDA(cudaGetLastError());
@@ -843,3 +888,4 @@ extern "C" int32_t mk_mla_export(mk_ctx *ctx, const mk_mla *m, int32_t seq, int8
     if (e != cudaSuccess) { mk_set_error("mk_mla_export: %s", cudaGetErrorString(e)); return MK_ERR_CUDA; }
     return MK_OK;
 }
+
