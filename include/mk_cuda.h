@@ -85,6 +85,8 @@ int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
  *   "force_ks" : K split of the matvec kernels, one of 0 (auto), 1, 2, 4, 8.
  *   "moe_no_fuse": 1 = small-batch MoE calls use the separate router / top-k / plan /
  *                quantize launches of large batches instead of the fused router kernel.
+ *   "mla_max_split": upper bound on the KV splits of an attention call, 0 = automatic
+ *                (fewer splits = more tiles per CTA; used by the tests).
  *   "mla_no_t5": 1 = absorbed-layout attention on the mma.sync kernel instead of the
  *                tcgen05 (tensor-memory) kernel.
  *   "mla_no_tc": 1 = run attention on the generic one-warp-per-head CUDA-core kernel

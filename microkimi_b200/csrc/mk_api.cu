@@ -114,6 +114,11 @@ extern "C" int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value) {
         ctx->moe_no_fuse = value != 0;
         return MK_OK;
     }
+    if (strcmp(name, "mla_max_split") == 0) {
+        MK_CHECK_ARG(value >= 0 && value <= 256, "mla_max_split must be in [0, 256]");
+        ctx->mla_max_split = (int)value;
+        return MK_OK;
+    }
     if (strcmp(name, "mla_no_t5") == 0) {
         ctx->mla_no_t5 = value != 0;
         return MK_OK;

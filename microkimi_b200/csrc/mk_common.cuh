@@ -79,6 +79,7 @@ struct mk_ctx {
     void *io_pinned;
     size_t io_pinned_bytes;
     int force_ks;           // 0 = choose per shape
+    int mla_max_split;      // > 0: upper bound on the KV splits of an attention call (study / test knob)
     int moe_no_fuse;        // 1 = separate router / top-k / plan / quantize launches also for small batches (study knob)
     int mla_no_tc;
     int mla_no_t5;          // 1 = absorbed MLA on the mma.sync kernel instead of the tcgen05 one (study knob)          // 1 = absorbed-layout attention on the CUDA-core kernel (study knob)

@@ -734,6 +734,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
         int ns = ctx->sm_count / nq;
         if (ns > nt128) ns = nt128;
         if (ns > m->max_split) ns = m->max_split;
+        if (ctx->mla_max_split > 0 && ns > ctx->mla_max_split) ns = ctx->mla_max_split;
         if (ns < 1) ns = 1;
         mla_t5::mla_absorbed_t5_kernel<<<dim3((unsigned)ns, (unsigned)nq), mla_t5::THREADS, mla_t5::SM_TOTAL, ctx->stream>>>(
             m->vq, m->vs, m->cap, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0,
@@ -757,6 +758,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
         int ns = ctx->sm_count / nq;
         if (ns > nt64) ns = nt64;
         if (ns > m->max_split) ns = m->max_split;
+        if (ctx->mla_max_split > 0 && ns > ctx->mla_max_split) ns = ctx->mla_max_split;
         if (ns < 1) ns = 1;
         mla_tc::mla_absorbed_tc_kernel<<<dim3((unsigned)ns, (unsigned)nq), mla_tc::THREADS, mla_tc::SM_TOTAL, ctx->stream>>>(
             m->vq, m->vs, m->cap, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0,
@@ -776,6 +778,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
         int ns = (int)mk_ceil_div((int64_t)ctx->sm_count * 10, (int64_t)nq * hgroups);
         if (ns > ntiles_p) ns = ntiles_p;
         if (ns > m->max_split) ns = m->max_split;
+        if (ctx->mla_max_split > 0 && ns > ctx->mla_max_split) ns = ctx->mla_max_split;
         if (ns < 1) ns = 1;
         const MlaDev cph = mla_dev(m);
         const size_t qw = (size_t)m->nope + mk_align_up((size_t)m->nb * 4, 16);
@@ -806,6 +809,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     int nsplit = (int)mk_ceil_div((int64_t)ctx->sm_count * 32, (int64_t)nq * m->H);
     if (nsplit > ntiles) nsplit = ntiles;
     if (nsplit > m->max_split) nsplit = m->max_split;
+    if (ctx->mla_max_split > 0 && nsplit > ctx->mla_max_split) nsplit = ctx->mla_max_split;
     if (nsplit < 1) nsplit = 1;
     const MlaDev c = mla_dev(m);
     const dim3 grid((unsigned)mk_ceil_div(nsplit, MLA_WARPS), (unsigned)m->H, (unsigned)nq);

@@ -147,6 +147,45 @@ def test_absorbed_layout(mk, nh, n):
                 ctx.set_option("mla_no_tc", 0)
 
 
+def test_absorbed_tensor_core_kernels_moving_maximum(mk):
+    """The tcgen05 kernel keeps a lazily updated softmax maximum: O and l are rescaled only when a
+    tile's maximum exceeds the maximum in use by more than 2^11.  Rows whose magnitude grows along
+    the sequence make the scores climb by far more than that several times, so the rescale path runs
+    on many tiles; positions at and around the 128-position tile edges check the masking.  The same
+    cache is read by the mma.sync kernel and the CUDA-core kernel."""
+    rng = np.random.default_rng(77)
+    nh, lat, vd, n = 64, 576, 512, 1100
+    rows = rng.standard_normal((n, lat)).astype(np.float32)
+    # a positive score ramp: every row gets a component along q's direction that grows with the position
+    q = rng.standard_normal((nh, lat)).astype(np.float32)
+    qdir = q.mean(axis=0)
+    qdir /= np.linalg.norm(qdir)
+    ramp = (np.arange(n, dtype=np.float32) / 128.0).astype(np.float32) ** 2      # 0 .. ~74
+    rows = rows + ramp[:, None] * qdir[None, :] * 6.0
+    ref = O.MlaAbsCache(lat, vd, n)
+    ref.push_many(rows)
+    dev = mk.MlaCache(nh, lat, 0, vd, n, layout="absorbed")
+    dev.push(rows)
+    scale = np.float32(1.0 / np.sqrt(192.0))
+    ctx = mk.Context.default()
+    try:
+        for splits in (1, 2, 0):      # 1 and 2: every CTA walks many tiles, so the maximum moves inside a CTA
+            ctx.set_option("mla_max_split", splits)
+            for pos in (0, 126, 127, 128, 129, 255, 256, 383, 700, n - 1):
+                want = ref.attn(q, pos, scale)
+                got = dev.mla_attn_flash_q8_mqa(q, pos, scale)
+                assert np.isfinite(got).all()
+                assert rel(got, want) <= 1e-3, f"tcgen05 kernel, pos {pos}, splits {splits}"
+                ctx.set_option("mla_no_t5", 1)
+                try:
+                    assert rel(dev.mla_attn_flash_q8_mqa(q, pos, scale), want) <= 1e-3, f"mma.sync kernel, pos {pos}"
+                finally:
+                    ctx.set_option("mla_no_t5", 0)
+    finally:
+        ctx.set_option("mla_max_split", 0)
+    assert ctx.status_word() == 0
+
+
 @pytest.mark.parametrize("nh,tol", [(16, 2e-4), (64, 1e-3)])
 def test_batch_of_sequences_with_different_lengths(mk, nh, tol):
     import torch
