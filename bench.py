@@ -178,11 +178,19 @@ def run_gpu(args):
     gen.manual_seed(7)
     x = torch.randn((batch, HIDDEN), dtype=torch.float32, device=dev, generator=gen)
     logits = torch.empty((batch, VOCAB), dtype=torch.float32, device=dev) if world > 1 else None
+    # N > 1: the matvec kernel stores its rows straight into every rank's gather buffer (peer memory);
+    # --collective nccl runs the library all-gather instead, for comparison
+    fused = None
+    if world > 1 and batch <= 2 and args.collective == "peer":
+        from microkimi_b200 import dist as mkd
+        fused = mkd.FusedVocabHead(heads[0], VOCAB, max_batch=batch)
 
     def step(i):
         if world == 1:
             y, _ = heads[i % copies].matvec(x, want_argmax=True)
             return y
+        if fused is not None:
+            return fused.matvec(x, want_argmax=True, head=heads[i % copies])
         y = heads[i % copies].matvec(x)
         if world > 1:
             # vocab-sharded logits -> full logits on every rank
@@ -191,7 +199,7 @@ def run_gpu(args):
             else:
                 parts = [logits[:, r * rows:(r + 1) * rows] for r in range(world)]
                 dist.all_gather(parts, y)  # strided destination views
-            return logits
+            return logits, logits.argmax(dim=1)   # the step ends with the token id, as on the other paths
         return y
 
     def barrier():
@@ -229,13 +237,35 @@ def run_gpu(args):
     xh.copy_(x.cpu())
     xn = xh.numpy()
     e2e_steps = max(10, min(args.steps, 100))
-    heads[0].matvec(xn, want_argmax=True)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        yh, amh = heads[i % copies].matvec(xn, want_argmax=True)
-    torch.cuda.synchronize()
-    e2e_dt = (time.perf_counter() - t0) / e2e_steps
+    if fused is None:
+        heads[0].matvec(xn, want_argmax=True)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            yh, amh = heads[i % copies].matvec(xn, want_argmax=True)
+        torch.cuda.synchronize()
+        e2e_dt = (time.perf_counter() - t0) / e2e_steps
+    else:
+        # every rank: x from pinned host memory, the fused matvec + gather, then this rank's rows of the
+        # complete logits and the token id back to pinned host memory (the ranks together return the logits once)
+        xd = torch.empty_like(x)
+        yh = torch.empty((batch, rows), dtype=torch.float32).pin_memory()
+        amh = torch.empty((batch,), dtype=torch.int32).pin_memory()
+        lo = rank * rows
+
+        def e2e_step(i):
+            xd.copy_(xh, non_blocking=True)
+            ptr, am = fused.matvec(xd, want_argmax=True, head=heads[i % copies])
+            full = fused.logits_tensor(ptr, batch)
+            yh.copy_(full[:, lo:lo + rows], non_blocking=True)
+            amh.copy_(am, non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_step(0)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e2e_dt = (time.perf_counter() - t0) / e2e_steps
     te = torch.tensor([e2e_dt], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
@@ -257,7 +287,9 @@ def run_gpu(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": f"q8_0 lm_head GEMV {VOCAB}x{HIDDEN} (f32 block scales), batch {batch}, "
-                                   f"vocab-sharded {world} way(s) + f32 logits all-gather",
+                                   f"vocab-sharded {world} way(s)" + ("" if world == 1 else (
+                                       ", logits stored into every rank's buffer by the matvec kernel (peer memory)"
+                                       if fused is not None else " + f32 logits all-gather (NCCL)")),
                        "batch": batch, "rows_per_gpu": rows,
                        "l2": f"inputs larger than L2: {shard_bytes * copies / 1e6:.0f} MB of weights per GPU"
                              + (f" ({copies} rotating copies of the shard)" if copies > 1 else ""),
@@ -270,7 +302,8 @@ def run_gpu(args):
             "cpu_baseline": cb,
             "e2e": {"value": alg_step / e2e_dt / 1e9, "unit": "GB/s", "ms_per_step": e2e_dt * 1e3,
                     "h2d_bytes_per_step": batch * HIDDEN * 4, "d2h_bytes_per_step": batch * rows * 4 + batch * 4,
-                    "api": "mk_matvec_q8 (host pointers, pinned)"},
+                    "api": "mk_matvec_q8 (host pointers, pinned)" if fused is None else
+                           "pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank"},
             "gpu_launches": launches,
             "clocks": clocks,
         }
@@ -446,6 +479,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: logits by peer-memory stores from the matvec kernel (default) or by an NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

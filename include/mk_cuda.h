@@ -74,6 +74,9 @@ const char *mk_last_error(void);
  * non-blocking stream of its own. */
 int32_t mk_set_stream(mk_ctx *ctx, void *cuda_stream);
 int32_t mk_sync(mk_ctx *ctx);
+/* Device-to-device copy on the context's stream (for results the library hands out as device
+ * pointers, e.g. the gathered logits). */
+int32_t mk_memcpy_dev(mk_ctx *ctx, void *dst, const void *src, uint64_t bytes);
 /* Number of kernels this context has launched since mk_init. */
 int64_t mk_launch_count(mk_ctx *ctx);
 int32_t mk_device_info(mk_ctx *ctx, int32_t *sm_count, int32_t *cc_major, int32_t *cc_minor, uint64_t *mem_bytes);
@@ -175,6 +178,31 @@ int32_t mk_matvec_f32_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float
 /* rmsnorm (src/model.rs:599-605) on DEVICE rows: out[i] = (x[i] * inv) * w[i] with
  * inv = 1 / sqrt(dot(x, x) / len + eps); x, out f32 [n, len], w f32 [len].  Bit-identical. */
 int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, int32_t n, int32_t len, float eps, float *out);
+
+/* ---- vocabulary-sharded lm_head over the GPUs of one node ---------------
+ * No counterpart in the reference (a single-process engine).  Rank r registers rows
+ * [row0, row0 + rows) of the lm_head (mk_weight_q8_from_f32 on its slice); one call then
+ * computes the shard's logits into this rank's gather buffer and one exchange kernel
+ * pushes them into the gather buffers of all other ranks over NVLink (peer memory, plain
+ * stores; no collective library call on the path), sends this rank's (maximum, index)
+ * pair along, waits - bounded, MK_ERR_TIMEOUT in the status word if a rank never arrives -
+ * until every rank has delivered, and picks the token: the complete f32 logits
+ * [batch, vocab] are then in this rank's buffer.
+ * The result is bit-identical to one GPU computing the whole matrix.
+ *   mk_gather_create : allocates this rank's buffer, returns a 64-byte handle for it
+ *   mk_gather_connect: opens the other ranks' buffers from their handles ([world][64] by
+ *                      rank; exchange them with any host-side means)
+ * world <= 8, max_batch <= 2 (decode).  Every rank must make the same sequence of calls. */
+typedef struct mk_gather mk_gather;
+int32_t mk_gather_create(mk_ctx *ctx, int32_t rank, int32_t world, int64_t vocab, int32_t max_batch, mk_gather **out,
+                         uint8_t *handle);
+int32_t mk_gather_connect(mk_ctx *ctx, mk_gather *g, const uint8_t *handles);
+int32_t mk_gather_free(mk_ctx *ctx, mk_gather *g);
+/* x f32 [batch, cols] on the DEVICE (the same on every rank); *logits receives a DEVICE pointer to the
+ * complete [batch, vocab] logits (valid until the call after next); argmax (optional, DEVICE int32
+ * [batch]) = first index of the maximum over the whole vocabulary. */
+int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
+                                const float **logits, int32_t *argmax);
 
 /* ---- MoE layer ---------------------------------------------------------
  * One call per layer instead of 3 matvecs per selected expert: replaces

@@ -1,0 +1,224 @@
+// Vocabulary-sharded lm_head across the GPUs of one node without a collective library
+// call on the decode path.  The matvec kernel of rank r writes its logits rows into rank
+// r's own gather buffer; ONE exchange kernel (one CTA) then pushes that slice into the
+// gather buffers of all other ranks (peer memory over NVLink, 16-byte stores), fences,
+// publishes this rank's step number in every rank's flag word (st.release.sys) and waits,
+// bounded, until all ranks have published the current step (ld.acquire.sys).
+// Measured alternative, rejected: storing the rows to the peers from the matvec kernel's own
+// epilogue (4-byte peer stores from every CTA) made the matvec 12 % slower at 2 GPUs (105 vs
+// 94 us) - with or without a system-wide fence per CTA - which costs more than this push.
+//
+// The reference engine is single-process (no rank concept), so there is no reference code
+// for this file; what it preserves is the single-GPU result: the gathered logits are the
+// bits one GPU computes for the whole matrix (rows are independent), and the greedy pick is
+// the first index of the maximum (src/model.rs:3277-3290).
+//
+// Buffers: one cudaMalloc blob per rank, exported with cudaIpcGetMemHandle and opened by the
+// other ranks: [flags: 2 parities x 8 ranks u32][pad to 256 B][(maximum, index) pairs: 2 parities x 8 ranks x 2 tokens x 16 B]
+// [logits: 2 x max_batch x vocab f32].
+// Two parities: a rank may run one step ahead of a peer that still reads the previous logits.
+// A rank cannot get two steps ahead: its wait for step s+1 needs the peer's flag of s+1, which
+// the peer publishes after (stream order) it has consumed step s.
+#include "mk_common.cuh"
+
+#include <new>
+
+struct mk_gather {
+    int rank, world, max_batch;
+    int64_t vocab;
+    size_t logits_off, blob_bytes;
+    void *blob;        // local
+    void *peer[8];     // blobs of all ranks (peer[rank] == blob)
+    bool connected;
+    uint32_t step;
+};
+
+namespace {
+constexpr uint32_t GATHER_WAIT_LIMIT = 1u << 22; // polls of >= 100 ns each: about half a second
+
+struct Best { float v; int64_t i; };
+// first index of the maximum (src/model.rs:3277-3290): a larger value wins, an equal value only with a lower index
+__device__ __forceinline__ Best better(Best a, Best b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
+
+// One CTA.  Reads this rank's slice [batch][n] (row stride ld) once: every 16 bytes go to the same place in
+// every other rank's buffer and into this rank's running (maximum, index).  Then the (maximum, index) pairs go
+// to every rank, everything is fenced system-wide, lane r publishes this rank's step in rank r's flag word and
+// waits for rank r's flag here to reach `step`; finally thread b picks token b's winner among the ranks' pairs.
+struct GatherPeers { float *dst[8]; uint32_t *flag[8]; Best *pairs[8]; };
+__global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers pe, const float *__restrict__ src, int batch, int64_t n,
+                                                              int64_t ld, int64_t row0, int rank, int world,
+                                                              const uint32_t *__restrict__ flags, const Best *__restrict__ my_pairs,
+                                                              uint32_t step, int32_t *__restrict__ argmax, int32_t *__restrict__ status) {
+    __shared__ Best red[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool vec = (n % 4 == 0) && (ld % 4 == 0) && (row0 % 4 == 0) && (((uintptr_t)src & 15) == 0);
+    for (int b = 0; b < batch; ++b) {
+        const float *s = src + (int64_t)b * ld;
+        Best best = {-INFINITY, INT64_MAX};
+        if (vec) {
+            for (int64_t i = tid; i < n / 4; i += blockDim.x) {
+                const float4 v = ((const float4 *)s)[i];
+                for (int p = 0; p < world; ++p)
+                    if (p != rank) ((float4 *)(pe.dst[p] + (int64_t)b * ld))[i] = v;
+                best = better(best, Best{v.x, 4 * i});
+                best = better(best, Best{v.y, 4 * i + 1});
+                best = better(best, Best{v.z, 4 * i + 2});
+                best = better(best, Best{v.w, 4 * i + 3});
+            }
+        } else {
+            for (int64_t i = tid; i < n; i += blockDim.x) {
+                const float v = s[i];
+                for (int p = 0; p < world; ++p)
+                    if (p != rank) pe.dst[p][(int64_t)b * ld + i] = v;
+                best = better(best, Best{v, i});
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+            best = better(best, other);
+        }
+        if (lane == 0) red[warp] = best;
+        __syncthreads();
+        if (warp == 0) {
+            best = lane < (int)(blockDim.x >> 5) ? red[lane] : Best{-INFINITY, INT64_MAX};
+            for (int o = 16; o > 0; o >>= 1) {
+                Best other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+                best = better(best, other);
+            }
+            if (lane < world) pe.pairs[lane][b] = Best{best.v, best.i == INT64_MAX ? row0 : row0 + best.i}; // this rank's pair, to rank `lane`
+        }
+        __syncthreads();
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < world) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pe.flag[tid]), "r"(step) : "memory");
+        bool ok = false;
+        for (uint32_t it = 0; it < GATHER_WAIT_LIMIT; ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
+            if ((int32_t)(v - step) >= 0) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (argmax != nullptr && tid < batch) {
+        Best best = {-INFINITY, INT64_MAX};
+        for (int r = 0; r < world; ++r) {
+            Best q;
+            q.v = __ldcv(&my_pairs[(int64_t)r * 2 + tid].v);
+            q.i = __ldcv(&my_pairs[(int64_t)r * 2 + tid].i);
+            best = better(best, q);
+        }
+        argmax[tid] = (int32_t)best.i;
+    }
+}
+} // namespace
+
+extern "C" int32_t mk_gather_create(mk_ctx *ctx, int32_t rank, int32_t world, int64_t vocab, int32_t max_batch, mk_gather **out,
+                                    uint8_t *handle /* 64 bytes */) {
+    MK_CHECK_ARG(ctx != nullptr && out != nullptr && handle != nullptr, "NULL argument");
+    MK_CHECK_ARG(world >= 1 && world <= 8 && rank >= 0 && rank < world, "need 0 <= rank < world <= 8");
+    MK_CHECK_ARG(vocab > 0 && max_batch >= 1 && max_batch <= 2, "vocab > 0 and max_batch in [1, 2] required");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    *out = nullptr;
+    MK_CUDA(cudaSetDevice(ctx->device));
+    mk_gather *g = new (std::nothrow) mk_gather();
+    if (!g) return MK_ERR_OOM;
+    memset(g, 0, sizeof(*g));
+    g->rank = rank; g->world = world; g->max_batch = max_batch; g->vocab = vocab;
+    g->logits_off = 256 + 2 * 8 * 2 * sizeof(Best); // flags, pairs, then the logits (768 B in: 16-byte aligned)
+    g->blob_bytes = g->logits_off + (size_t)2 * max_batch * vocab * 4;
+    cudaError_t e = cudaMalloc(&g->blob, g->blob_bytes);
+    if (e == cudaSuccess) e = cudaMemset(g->blob, 0, g->blob_bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, g->blob);
+    if (e != cudaSuccess) {
+        mk_set_error("mk_gather_create: %s", cudaGetErrorString(e));
+        if (g->blob) cudaFree(g->blob);
+        delete g;
+        return e == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA;
+    }
+    memcpy(handle, &h, 64);
+    g->peer[rank] = g->blob;
+    *out = g;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_gather_connect(mk_ctx *ctx, mk_gather *g, const uint8_t *handles /* [world][64], by rank */) {
+    MK_CHECK_ARG(ctx != nullptr && g != nullptr && handles != nullptr, "NULL argument");
+    MK_CHECK_ARG(!g->connected, "already connected");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    for (int r = 0; r < g->world; ++r) {
+        if (r == g->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        cudaError_t e = cudaIpcOpenMemHandle(&g->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            mk_set_error("mk_gather_connect: rank %d cannot open rank %d's buffer: %s", g->rank, r, cudaGetErrorString(e));
+            for (int q = 0; q < r; ++q)
+                if (q != g->rank && g->peer[q]) { cudaIpcCloseMemHandle(g->peer[q]); g->peer[q] = nullptr; }
+            return MK_ERR_CUDA;
+        }
+    }
+    g->connected = true;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_gather_free(mk_ctx *ctx, mk_gather *g) {
+    MK_CHECK_ARG(ctx != nullptr && g != nullptr, "NULL argument");
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int r = 0; r < g->world; ++r)
+        if (r != g->rank && g->peer[r]) cudaIpcCloseMemHandle(g->peer[r]);
+    if (g->blob) cudaFree(g->blob);
+    delete g;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
+                                           const float **logits /* out: device pointer to [batch][vocab] */, int32_t *argmax) {
+    MK_CHECK_ARG(ctx != nullptr && w != nullptr && g != nullptr && x != nullptr, "NULL argument");
+    MK_CHECK_ARG(w->fmt == MK_FMT_Q8, "weight handle has the wrong format for this call");
+    MK_CHECK_ARG(g->connected || g->world == 1, "mk_gather_connect has not run");
+    MK_CHECK_ARG(batch >= 1 && batch <= g->max_batch, "batch exceeds the gather buffers");
+    MK_CHECK_ARG(row0 >= 0 && row0 + w->rows <= g->vocab, "shard rows outside the vocabulary");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const int64_t ldq = w->nbp * 32;
+    const size_t xq_bytes = mk_align_up((size_t)batch * ldq, 256), xs_bytes = mk_align_up((size_t)batch * w->nbp * 4, 256);
+    int32_t rc = mk_ws_reserve(ctx, xq_bytes + xs_bytes);
+    if (rc != MK_OK) return rc;
+    int8_t *xq = (int8_t *)ctx->ws;
+    float *xs = (float *)((char *)ctx->ws + xq_bytes);
+    rc = mk_launch_quantize_act(ctx, x, batch, w->cols, w->cols, w->nbp, 0, xq, xs);
+    if (rc != MK_OK) return rc;
+
+    g->step++;
+    const uint32_t par = g->step & 1u;
+    const size_t step_off = g->logits_off + (size_t)par * g->max_batch * g->vocab * 4;
+    // this rank's rows go straight into its own gather buffer ...
+    float *full = (float *)((char *)g->blob + step_off);
+    rc = mk_launch_qgemv(ctx, w, xq, xs, batch, 0, 0, full + row0, g->vocab);
+    if (rc != MK_OK) return rc;
+    // ... and one kernel pushes them to the other ranks, signals and waits
+    GatherPeers pe;
+    memset(&pe, 0, sizeof(pe));
+    const size_t pairs_off = 256 + (size_t)par * 8 * 2 * sizeof(Best);
+    for (int r = 0; r < g->world; ++r) {
+        pe.dst[r] = (float *)((char *)g->peer[r] + step_off) + row0;
+        pe.flag[r] = (uint32_t *)g->peer[r] + par * 8 + g->rank;
+        pe.pairs[r] = (Best *)((char *)g->peer[r] + pairs_off) + (size_t)g->rank * 2;
+    }
+    {
+        mk_prof_scope prof(ctx, MK_PROF_OTHER);
+        gather_exchange_kernel<<<1, 1024, 0, ctx->stream>>>(pe, full + row0, batch, w->rows, g->vocab, row0, g->rank, g->world,
+                                                           (const uint32_t *)g->blob + par * 8, (const Best *)((char *)g->blob + pairs_off),
+                                                           g->step, argmax, ctx->status_dev);
+        ctx->launches++;
+    }
+    MK_CUDA(cudaGetLastError());
+    if (logits) *logits = full;
+    return MK_OK;
+}

@@ -81,6 +81,12 @@ extern "C" int32_t mk_set_stream(mk_ctx *ctx, void *cuda_stream) {
     ctx->stream = (cudaStream_t)cuda_stream;
     return MK_OK;
 }
+extern "C" int32_t mk_memcpy_dev(mk_ctx *ctx, void *dst, const void *src, uint64_t bytes) {
+    MK_CHECK_ARG(ctx != nullptr && dst != nullptr && src != nullptr, "NULL argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    MK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return MK_OK;
+}
 extern "C" int32_t mk_sync(mk_ctx *ctx) {
     MK_CHECK_ARG(ctx != nullptr, "ctx is NULL");
     MK_CUDA(cudaStreamSynchronize(ctx->stream));

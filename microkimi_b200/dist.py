@@ -54,6 +54,67 @@ def greedy_token(full_logits):
     return torch.where(full_logits == mx, idx, big).min(dim=1).values.to(torch.int32)
 
 
+class FusedVocabHead:
+    """Vocabulary-sharded q8_0 lm_head whose logits reach every rank by peer-memory stores over NVLink
+    (one exchange kernel per token after the matvec: push, signal, bounded wait, token pick) - no
+    collective library call per token.
+
+    `head` is this rank's ops.Q8Head over rows vocab_shard(vocab, world, rank).  Construction
+    exchanges the buffer handles once (all_gather over the process group)."""
+
+    def __init__(self, head, vocab, group=None, max_batch=1):
+        import ctypes as C
+        from . import lib as _l
+        self.head, self.vocab, self.ctx = head, int(vocab), head.ctx
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.row0, hi = vocab_shard(vocab, self.world, self.rank)
+        assert hi - self.row0 == head.rows, "the head must hold exactly this rank's vocabulary rows"
+        self.max_batch = int(max_batch)
+        L = self.ctx._L
+        h = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        _l.check(L.mk_gather_create(self.ctx._h, self.rank, self.world, self.vocab, self.max_batch, C.byref(h), handle))
+        self._h = h
+        dev = torch.device("cuda", self.ctx.device)
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
+        allh = torch.empty((self.world, 64), dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(allh.view(-1), mine, group=group)
+        buf = (C.c_uint8 * (64 * self.world)).from_buffer_copy(bytes(allh.cpu().numpy().tobytes()))
+        _l.check(L.mk_gather_connect(self.ctx._h, self._h, buf))
+        dist.barrier(group=group)
+        self._am = torch.empty((self.max_batch,), dtype=torch.int32, device=dev)
+
+    def matvec(self, x, want_argmax=True, head=None):
+        """x [batch, cols] (torch CUDA, identical on every rank) -> (device address of the complete logits
+        [batch, vocab] in this rank's gather buffer, valid until the call after next; argmax int32 [batch]).
+        `head`: another Q8Head over the same rows (every rank must pass its counterpart)."""
+        import ctypes as C
+        from . import lib as _l
+        head = head or self.head
+        assert head.rows == self.head.rows and head.cols == self.head.cols
+        xs = x.reshape(-1, self.head.cols)
+        assert xs.dtype == torch.float32 and xs.is_contiguous() and xs.shape[0] <= self.max_batch
+        batch = xs.shape[0]
+        ptr = C.c_void_p()
+        _l.check(self.ctx._L.mk_matvec_q8_gather_dev(self.ctx._h, head._h, self._h, C.c_void_p(xs.data_ptr()), batch, self.row0,
+                                                    C.byref(ptr), C.c_void_p(self._am.data_ptr()) if want_argmax else None))
+        self._last_ptr = ptr.value
+        return ptr.value, (self._am[:batch] if want_argmax else None)
+
+    def logits_tensor(self, ptr, batch):
+        """Copies the complete logits behind `ptr` into a fresh torch tensor [batch, vocab]."""
+        import ctypes as C
+        from . import lib as _l
+        out = torch.empty((batch, self.vocab), dtype=torch.float32, device=torch.device("cuda", self.ctx.device))
+        _l.check(self.ctx._L.mk_memcpy_dev(self.ctx._h, C.c_void_p(out.data_ptr()), C.c_void_p(ptr), batch * self.vocab * 4))
+        return out
+
+    def free(self):
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._L.mk_gather_free(self.ctx._h, self._h)
+        self._h = None
+
+
 # ---------------------------------------------------------------- expert-parallel MoE
 def expert_owner(expert, n_experts, world):
     """Block partition of the routed experts: expert e lives on rank e // (n_experts / world)."""

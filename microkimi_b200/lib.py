@@ -55,6 +55,7 @@ SIGNATURES = {
     "mk_last_error": (C.c_char_p, []),
     "mk_set_stream": (_i32, [_vp, _vp]),
     "mk_sync": (_i32, [_vp]),
+    "mk_memcpy_dev": (_i32, [_vp, _vp, _vp, C.c_uint64]),
     "mk_launch_count": (_i64, [_vp]),
     "mk_device_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32), C.POINTER(C.c_uint64)]),
     "mk_status_word": (_i32, [_vp, C.POINTER(_i32)]),
@@ -71,6 +72,10 @@ SIGNATURES = {
     "mk_quantize_q8": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "mk_matvec_mxfp4": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_mxfp4_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "mk_gather_create": (_i32, [_vp, _i32, _i32, _i64, _i32, C.POINTER(_vp), _vp]),
+    "mk_gather_connect": (_i32, [_vp, _vp, _vp]),
+    "mk_gather_free": (_i32, [_vp, _vp]),
+    "mk_matvec_q8_gather_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, C.POINTER(_vp), _vp]),
     "mk_weight_f32": (_i32, [_vp, _vp, _i64, _i64, _i32, C.POINTER(_vp)]),
     "mk_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _i32]),
     "mk_matvec_f32_dev": (_i32, [_vp, _vp, _vp, _vp, _i32]),

@@ -43,6 +43,21 @@ def _worker(rank, world, port, ret):
         single = mk.Q8Head.from_f32(wf, vocab, d, ctx=ctx).matvec(x.to(dev))
         torch.cuda.synchronize()
         ok_head = torch.equal(full, single) and torch.equal(mkd.greedy_token(full).cpu().long(), single.argmax(1).cpu())
+        # ---- the same head with the logits stored straight into every rank's gather buffer (peer memory),
+        # several steps in a row (the buffers alternate by step parity), batch 1 and 2
+        fused = mkd.FusedVocabHead(head, vocab, max_batch=2)
+        xd = x.to(dev)
+        for step in range(5):
+            nb = 1 + step % 2
+            xin = (xd[:nb] * float(step + 1)).contiguous()
+            ptr, am = fused.matvec(xin)
+            got = fused.logits_tensor(ptr, nb)
+            want = mk.Q8Head.from_f32(wf, vocab, d, ctx=ctx).matvec(xin)
+            torch.cuda.synchronize()
+            ok_head = ok_head and torch.equal(got, want) and torch.equal(am.cpu().long(), want.argmax(1).cpu())
+        ok_head = ok_head and ctx.status_word() == 0
+        dist.barrier()
+        fused.free()
         # ---- MoE, expert-parallel, tokens sharded
         E, k, dm, inter, n_tok = 16, 4, 256, 128, 11
         gw = (torch.randn((E, dm), generator=g) * 0.02).numpy()
