@@ -129,6 +129,10 @@ int32_t mk_weight_q8(mk_ctx *ctx, const int8_t *q, const void *scales, int64_t r
 /* A dense f32 matrix [rows, cols] (row-major), as the engine's matvec consumes it
  * (src/model.rs:199; the Metal seam uploads the same bytes, src/metal.rs:750). */
 int32_t mk_weight_f32(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, int32_t src_on_device, mk_weight **out);
+/* A VQ1 matrix (src/quant.rs:17-18, 313-346): codebook f32 [256, 16] and one index byte per 16
+ * weights, indices u8 [rows, cols/16]; W[r, 16 v + j] = codebook[indices[r, v]][j]. */
+int32_t mk_weight_vq1(mk_ctx *ctx, const float *codebook, const uint8_t *indices, int64_t rows, int64_t cols,
+                      int32_t src_on_device, mk_weight **out);
 int32_t mk_weight_free(mk_ctx *ctx, mk_weight *w);
 /* Bytes held on the device for this weight (values + scales). */
 int64_t mk_weight_bytes(const mk_weight *w);
@@ -175,6 +179,11 @@ int32_t mk_matvec_q8_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float 
  * x f32 [batch, cols], y f32 [batch, rows]. */
 int32_t mk_matvec_f32(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch);
 int32_t mk_matvec_f32_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch);
+/* quant::matvec_vq / lutgemv::matvec_vq_lut (src/quant.rs:340-346, src/lutgemv.rs:208-238): the VQ1
+ * matvec by lookup table, bit-identical to both of the engine's paths (table entries and rows
+ * accumulate in the engine's ascending order). x f32 [batch, cols], y f32 [batch, rows]. */
+int32_t mk_matvec_vq1(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch);
+int32_t mk_matvec_vq1_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float *y, int32_t batch);
 /* rmsnorm (src/model.rs:599-605) on DEVICE rows: out[i] = (x[i] * inv) * w[i] with
  * inv = 1 / sqrt(dot(x, x) / len + eps); x, out f32 [n, len], w f32 [len].  Bit-identical. */
 int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, int32_t n, int32_t len, float eps, float *out);

@@ -33,7 +33,7 @@ void mk_set_error(const char *fmt, ...);
     } while (0)
 
 // ---------------------------------------------------------------- records
-enum { MK_FMT_MXFP4 = 0, MK_FMT_Q8 = 1, MK_FMT_F32 = 2 };
+enum { MK_FMT_MXFP4 = 0, MK_FMT_Q8 = 1, MK_FMT_F32 = 2, MK_FMT_VQ1 = 3 };
 
 // A registered weight matrix in the fragment-major ("tiled") device layout.
 //

@@ -212,6 +212,27 @@ class F32Weight(_Weight):
         return y[0] if (x.ndim if hasattr(x, "ndim") else x.dim()) == 1 else y
 
 
+class Vq1Weight(_Weight):
+    """A VQ1 matrix resident on the GPU: codebook f32 [256, 16] + index bytes u8 [rows, cols/16]
+    (src/quant.rs:313-346)."""
+
+    def __init__(self, codebook, indices, rows, cols, ctx=None):
+        ctx = ctx or Context.default()
+        cb = np.ascontiguousarray(codebook, dtype=np.float32)
+        idx = np.ascontiguousarray(indices, dtype=np.uint8)
+        assert cb.size == 256 * 16 and idx.size == rows * cols // 16
+        h = C.c_void_p()
+        _l.check(ctx._L.mk_weight_vq1(ctx._h, _np_ptr(cb), _np_ptr(idx), rows, cols, 0, C.byref(h)))
+        super().__init__(ctx, h, rows, cols)
+
+    def matvec(self, x):
+        """quant::matvec_vq: out[r] = sum_c W[r, c] x[c], bit-identical to the engine. x: [cols] or [batch, cols]."""
+        L = self.ctx._L
+        batch, y, fn, args = self._run(L.mk_matvec_vq1, L.mk_matvec_vq1_dev, x, "q8", False)
+        _l.check(fn(self.ctx._h, self._h, *args[:3]))
+        return y[0] if (x.ndim if hasattr(x, "ndim") else x.dim()) == 1 else y
+
+
 def matvec(w, rows, cols, x, ctx=None):
     """Drop-in for model::matvec / metal::gpu_matvec with borrowed host slices."""
     h = F32Weight(w, rows, cols, ctx)

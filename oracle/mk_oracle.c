@@ -589,6 +589,41 @@ void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
     free(ids); free(wts); free(outs);
 }
 
+/* ------------------------------------------------------------------ VQ1 codebook matvec */
+void or_matvec_vq_gather(const float *codebook, const uint8_t *indices, size_t rows, size_t cols, const float *x, float *out) {
+    size_t vpr = cols / 16; /* quant.rs:317-335 */
+    for (size_t r = 0; r < rows; ++r) {
+        float sum = 0.0f;
+        for (size_t v = 0; v < vpr; ++v) {
+            const float *cb = codebook + (size_t)indices[r * vpr + v] * 16, *xs = x + v * 16;
+            float s = 0.0f;
+            for (size_t j = 0; j < 16; ++j) s += cb[j] * xs[j];
+            sum += s;
+        }
+        out[r] = sum;
+    }
+}
+void or_matvec_vq_lut(const float *codebook, const uint8_t *indices, size_t rows, size_t cols, const float *x, float *out) {
+    size_t vpr = cols / 16; /* lutgemv.rs:208-238, tiles of 16 groups */
+    float *lut = (float *)malloc(sizeof(float) * 16 * 256);
+    for (size_t r = 0; r < rows; ++r) out[r] = 0.0f;
+    for (size_t g0 = 0; g0 < vpr; g0 += 16) {
+        size_t groups = vpr - g0 < 16 ? vpr - g0 : 16;
+        for (size_t g = 0; g < groups; ++g)
+            for (size_t k = 0; k < 256; ++k) { /* lutgemv.rs:116-125 */
+                float s = 0.0f;
+                for (size_t j = 0; j < 16; ++j) s += codebook[k * 16 + j] * x[(g0 + g) * 16 + j];
+                lut[g * 256 + k] = s;
+            }
+        for (size_t r = 0; r < rows; ++r) { /* lutgemv.rs:67-92 */
+            float a = out[r];
+            for (size_t g = 0; g < groups; ++g) a += lut[g * 256 + indices[r * vpr + g0 + g]];
+            out[r] = a;
+        }
+    }
+    free(lut);
+}
+
 /* model.rs:2150-2380 : K3 latent MoE layer, one token */
 void or_moe_k3_forward(const or_moe_k3_desc *m, const float *x, float *out, int32_t *ids_out, float *w_out) {
     size_t k = m->top_k, d = m->d, rh = m->rh, I = m->inter;

@@ -100,6 +100,14 @@ typedef struct {
 void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
                        int32_t *ids_out /* [top_k], nullable */, float *w_out /* nullable */, int n_threads);
 
+/* ---- VQ1 codebook matvec (quant.rs:313-346, lutgemv.rs:208-238) ----
+ * codebook f32 [256][16]; indices u8 [rows][cols/16]: W[r, 16v + j] = codebook[idx[r][v]][j].
+ * gather: out[r] = sum over v (ascending) of s_v, s_v = sum over j (ascending) of cb[idx][j] * x[16v + j],
+ * every sum starting from 0 with a separate multiply and add.  lut: one table of 256 such dots per group,
+ * then additions only; bit-identical to gather (lutgemv.rs:22-27). */
+void or_matvec_vq_gather(const float *codebook, const uint8_t *indices, size_t rows, size_t cols, const float *x, float *out);
+void or_matvec_vq_lut(const float *codebook, const uint8_t *indices, size_t rows, size_t cols, const float *x, float *out);
+
 /* K3 latent MoE layer (model.rs:2150-2380), one token: router on x [d]; h = routed_down x;
  * per selected expert a = w1 h, u = w3 h, act = situ(a, u), o = w2 act (MXFP4 experts over
  * the latent width rh); y = sum of w_i * o_i in slot order; out = routed_up rmsnorm(y) plus

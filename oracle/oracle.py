@@ -96,6 +96,8 @@ def _declare(L):
     sig("or_gate_ds", None, _f32p, _f32p, _sz, _sz, _sz, C.c_float, _f32p, _i32p, _f32p)
     sig("or_expert_ds_f32", None, _f32p, _f32p, _f32p, _f32p, _sz, _sz, C.c_float, _f32p)
     sig("or_moe_ds_forward", None, C.POINTER(_MoeDesc), _f32p, _f32p, _i32p, _f32p, C.c_int)
+    sig("or_matvec_vq_gather", None, _f32p, _u8p, _sz, _sz, _f32p, _f32p)
+    sig("or_matvec_vq_lut", None, _f32p, _u8p, _sz, _sz, _f32p, _f32p)
     sig("or_moe_k3_forward", None, C.POINTER(_MoeK3Desc), _f32p, _f32p, _i32p, _f32p)
     sig("or_mla_new", C.c_void_p, _sz, _sz, _sz, _sz, _sz)
     sig("or_mla_free", None, C.c_void_p)
@@ -207,6 +209,16 @@ def matvec_f32(w, x, n_threads=1):
     w, x = _c(w, np.float32), _c(x, np.float32)
     out = np.empty(w.shape[0], np.float32)
     lib().or_matvec_f32(_p(w, _f32p), w.shape[0], w.shape[1], _p(x, _f32p), _p(out, _f32p), n_threads)
+    return out
+
+
+def matvec_vq(codebook, indices, x, lut=True):
+    """VQ1 matvec (quant.rs:340-346): codebook f32 [256, 16], indices u8 [rows, cols/16]."""
+    cb, idx, x = _c(codebook, np.float32), _c(indices, np.uint8), _c(x, np.float32)
+    rows, vpr = idx.shape
+    out = np.empty(rows, np.float32)
+    fn = lib().or_matvec_vq_lut if lut else lib().or_matvec_vq_gather
+    fn(_p(cb, _f32p), _p(idx, _u8p), rows, vpr * 16, _p(x, _f32p), _p(out, _f32p))
     return out
 
 

@@ -97,3 +97,21 @@ def test_f32_matvec_argument_errors(mk):
         L.check(h.ctx._L.mk_matvec_f32(h.ctx._h, fp4._h, None, None, 1))
     h.free()
     fp4.free()
+
+
+# ------------------------------------------------------------------ VQ1 codebook matvec by lookup table
+@pytest.mark.parametrize("rows,cols", [(7, 16), (130, 272), (7168, 2048), (300, 7168)])
+@pytest.mark.parametrize("batch", [1, 3, 9])
+def test_vq1_matvec_bit_exact(mk, rows, cols, batch):
+    """quant::matvec_vq (src/quant.rs:340-346; lutgemv.rs:208-238): bit-identical to the CPU, as the
+    reference's own LUT kernel is to its gather kernel."""
+    rng = np.random.default_rng(rows + cols + batch)
+    cb = (rng.standard_normal((256, 16)) * 0.05).astype(np.float32)
+    idx = rng.integers(0, 256, (rows, cols // 16), dtype=np.uint8)
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    w = mk.Vq1Weight(cb, idx, rows, cols)
+    y = w.matvec(x)
+    ref = np.stack([O.matvec_vq(cb, idx, x[b]) for b in range(batch)])
+    assert np.array_equal(bits(y), bits(ref))
+    assert np.array_equal(bits(w.matvec(x[0])), bits(ref[0]))
+    w.free()

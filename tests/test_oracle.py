@@ -419,3 +419,23 @@ def test_k3_latent_moe_restatement_against_dense_f64():
     yn = y / np.sqrt((y * y).mean() + 1e-6) * rn
     want = ru.astype(np.float64) @ yn + sd.astype(np.float64) @ situ(sg.astype(np.float64) @ x64, su.astype(np.float64) @ x64)
     assert np.abs(out - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
+def test_vq1_lut_gemv_bit_identical_to_gather():
+    """lutgemv.rs:22-27 and its unit tests: the table form equals the gather form bit for bit
+    (same ascending j and ascending group order), and both equal a plain sequential f32 loop."""
+    rng = np.random.default_rng(31)
+    for rows, cols in ((7, 16), (33, 272), (64, 2048)):
+        cb = (rng.standard_normal((256, 16)) * 0.05).astype(np.float32)
+        idx = rng.integers(0, 256, (rows, cols // 16), dtype=np.uint8)
+        x = rng.standard_normal(cols).astype(np.float32)
+        a, b = O.matvec_vq(cb, idx, x, lut=True), O.matvec_vq(cb, idx, x, lut=False)
+        assert np.array_equal(bits(a), bits(b))
+        r = rows // 2
+        s = np.float32(0.0)
+        for v in range(cols // 16):
+            g = np.float32(0.0)
+            for j in range(16):
+                g = np.float32(g + np.float32(cb[idx[r, v], j] * x[16 * v + j]))
+            s = np.float32(s + g)
+        assert bits(np.array([s]))[0] == bits(a[r:r + 1])[0]
