@@ -142,6 +142,11 @@ int32_t mk_weight_export(mk_ctx *ctx, const mk_weight *w, void *values, void *sc
 /* mxfp4::dequant (src/mxfp4.rs:19-31) on the GPU: f32 [rows, cols] to HOST. */
 int32_t mk_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out);
 
+/* dequant::dequant_fp8 (src/dequant.rs:12-41) on the GPU: e4m3fn bytes w [rows, cols] with one ue8m0
+ * scale byte per 128 x 128 block (scales [ceil(rows/128), ceil(cols/128)]) -> f32 [rows, cols].
+ * HOST in / HOST out; bit-identical (DeepSeek spine weights; no BASELINE config runs them). */
+int32_t mk_dequant_fp8(mk_ctx *ctx, const uint8_t *w, const uint8_t *scales, int64_t rows, int64_t cols, float *out);
+
 /* ---- activations ------------------------------------------------------ */
 /* q8::quantize_q8_into (src/q8.rs:49-69) on the GPU, HOST in / HOST out:
  * x f32 [n] (n % 32 == 0) -> q i8 [n], scales f32 [n/32].  Bit-identical. */

@@ -144,6 +144,22 @@ __global__ void retile_q8_kernel(const int8_t *__restrict__ q, const ST *__restr
     }
 }
 
+// one thread per element: W[r,c] = e4m3fn(w[r,c]) * 2^(scale[r/128, c/128] - 127), bit-exact (src/dequant.rs:12-41)
+__global__ void dequant_fp8_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ scales, float *__restrict__ out,
+                                   int64_t rows, int64_t cols) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * cols) return;
+    const int64_t r = idx / cols, c = idx % cols;
+    const uint32_t b = w[idx];
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    float v;
+    if (e == 15u && m == 7u) v = __uint_as_float(0x7FC00000u);                 // the format's NaN
+    else if (e == 0u) v = (float)m * 0.001953125f;                             // m / 8 * 2^-6 = m * 2^-9, exact
+    else v = __uint_as_float(((e + 120u) << 23) | (m << 20));                  // 2^(e-7) * (1 + m/8)
+    if (b & 0x80u) v = -v;
+    out[idx] = v * mk_e8m0(scales[(r >> 7) * ((cols + 127) >> 7) + (c >> 7)]);
+}
+
 } // namespace
 
 static unsigned grid_for(int64_t n, int block) { return (unsigned)mk_ceil_div(n > 0 ? n : 1, block); }
@@ -209,5 +225,25 @@ int32_t mk_launch_untile_q8(mk_ctx *ctx, const mk_weight *w, int8_t *q, void *sc
                                                                         true, q, (float *)scales);
     ctx->launches++;
     MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+// e4m3fn weights + ue8m0 scales per 128 x 128 block -> f32, HOST in / HOST out (a check kernel like mk_dequant_mxfp4)
+extern "C" int32_t mk_dequant_fp8(mk_ctx *ctx, const uint8_t *w, const uint8_t *scales, int64_t rows, int64_t cols, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && w != nullptr && scales != nullptr && out != nullptr, "NULL argument");
+    MK_CHECK_ARG(rows > 0 && cols > 0, "rows and cols must be positive");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const size_t wb = (size_t)rows * cols, sb = (size_t)mk_ceil_div(rows, 128) * mk_ceil_div(cols, 128), ob = wb * 4;
+    int32_t rc = mk_io_reserve(ctx, mk_align_up(wb, 256) + mk_align_up(sb, 256) + mk_align_up(ob, 256));
+    if (rc != MK_OK) return rc;
+    uint8_t *dw = (uint8_t *)ctx->io_dev, *ds = dw + mk_align_up(wb, 256);
+    float *dout = (float *)(ds + mk_align_up(sb, 256));
+    MK_CUDA(cudaMemcpyAsync(dw, w, wb, cudaMemcpyHostToDevice, ctx->stream));
+    MK_CUDA(cudaMemcpyAsync(ds, scales, sb, cudaMemcpyHostToDevice, ctx->stream));
+    dequant_fp8_kernel<<<grid_for((int64_t)wb, 256), 256, 0, ctx->stream>>>(dw, ds, dout, rows, cols);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    MK_CUDA(cudaMemcpyAsync(out, dout, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
     return MK_OK;
 }

@@ -233,6 +233,17 @@ class Vq1Weight(_Weight):
         return y[0] if (x.ndim if hasattr(x, "ndim") else x.dim()) == 1 else y
 
 
+def dequant_fp8(w, scales, rows, cols, ctx=None):
+    """dequant::dequant_fp8 (src/dequant.rs:27-41) on the GPU: numpy u8 in, f32 [rows, cols] out."""
+    ctx = ctx or Context.default()
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    assert w.size == rows * cols and scales.size == -(-rows // 128) * -(-cols // 128)
+    out = np.empty((rows, cols), np.float32)
+    _l.check(ctx._L.mk_dequant_fp8(ctx._h, _np_ptr(w), _np_ptr(scales), rows, cols, _np_ptr(out)))
+    return out
+
+
 def matvec(w, rows, cols, x, ctx=None):
     """Drop-in for model::matvec / metal::gpu_matvec with borrowed host slices."""
     h = F32Weight(w, rows, cols, ctx)

@@ -589,6 +589,24 @@ void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
     free(ids); free(wts); free(outs);
 }
 
+/* ------------------------------------------------------------------ FP8 e4m3fn dequant */
+float or_e4m3_to_f32(uint8_t b) { /* dequant.rs:12-23 */
+    float sign = (b & 0x80) ? -1.0f : 1.0f;
+    int e = (b >> 3) & 0x0F;
+    float m = (float)(b & 0x07);
+    if (e == 15 && (b & 0x07) == 7) return NAN;
+    if (e == 0) return sign * (m / 8.0f) * 0.015625f; /* 2^-6 */
+    return sign * (1.0f + m / 8.0f) * or_exp2_i(e - 7);
+}
+void or_dequant_fp8(const uint8_t *w, const uint8_t *scales, size_t rows, size_t cols, float *out) { /* dequant.rs:27-41 */
+    size_t scols = (cols + 127) / 128;
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t c = 0; c < cols; ++c) {
+            float s = or_exp2_i((int)scales[(r / 128) * scols + c / 128] - 127);
+            out[r * cols + c] = or_e4m3_to_f32(w[r * cols + c]) * s;
+        }
+}
+
 /* ------------------------------------------------------------------ VQ1 codebook matvec */
 void or_matvec_vq_gather(const float *codebook, const uint8_t *indices, size_t rows, size_t cols, const float *x, float *out) {
     size_t vpr = cols / 16; /* quant.rs:317-335 */

@@ -100,6 +100,10 @@ typedef struct {
 void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
                        int32_t *ids_out /* [top_k], nullable */, float *w_out /* nullable */, int n_threads);
 
+/* ---- FP8 e4m3fn + ue8m0 (128 x 128 blocks) dequant (dequant.rs:10-41) ---- */
+float or_e4m3_to_f32(uint8_t b);
+void or_dequant_fp8(const uint8_t *w, const uint8_t *scales, size_t rows, size_t cols, float *out);
+
 /* ---- VQ1 codebook matvec (quant.rs:313-346, lutgemv.rs:208-238) ----
  * codebook f32 [256][16]; indices u8 [rows][cols/16]: W[r, 16v + j] = codebook[idx[r][v]][j].
  * gather: out[r] = sum over v (ascending) of s_v, s_v = sum over j (ascending) of cb[idx][j] * x[16v + j],

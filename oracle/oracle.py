@@ -96,6 +96,7 @@ def _declare(L):
     sig("or_gate_ds", None, _f32p, _f32p, _sz, _sz, _sz, C.c_float, _f32p, _i32p, _f32p)
     sig("or_expert_ds_f32", None, _f32p, _f32p, _f32p, _f32p, _sz, _sz, C.c_float, _f32p)
     sig("or_moe_ds_forward", None, C.POINTER(_MoeDesc), _f32p, _f32p, _i32p, _f32p, C.c_int)
+    sig("or_dequant_fp8", None, _u8p, _u8p, _sz, _sz, _f32p)
     sig("or_matvec_vq_gather", None, _f32p, _u8p, _sz, _sz, _f32p, _f32p)
     sig("or_matvec_vq_lut", None, _f32p, _u8p, _sz, _sz, _f32p, _f32p)
     sig("or_moe_k3_forward", None, C.POINTER(_MoeK3Desc), _f32p, _f32p, _i32p, _f32p)
@@ -209,6 +210,14 @@ def matvec_f32(w, x, n_threads=1):
     w, x = _c(w, np.float32), _c(x, np.float32)
     out = np.empty(w.shape[0], np.float32)
     lib().or_matvec_f32(_p(w, _f32p), w.shape[0], w.shape[1], _p(x, _f32p), _p(out, _f32p), n_threads)
+    return out
+
+
+def dequant_fp8(w, scales, rows, cols):
+    """dequant::dequant_fp8 (dequant.rs:27-41): e4m3fn bytes [rows, cols] + ue8m0 scale per 128 x 128 block."""
+    w, scales = _c(w, np.uint8), _c(scales, np.uint8)
+    out = np.empty((rows, cols), np.float32)
+    lib().or_dequant_fp8(_p(w, _u8p), _p(scales, _u8p), rows, cols, _p(out, _f32p))
     return out
 
 

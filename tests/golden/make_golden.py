@@ -5,7 +5,7 @@ Run once where the reference project is mounted (default /root/reference):
     python tests/golden/make_golden.py [/path/to/reference]
 
 It (1) extracts the vectors the reference's own `selftest` consumes for this
-path from ref/ds_golden.json (fp4 block, src/selftest.rs:226-234) and
+path from ref/ds_golden.json (fp4 block and fp8 block, src/selftest.rs:205-234) and
 ref/ds_golden2.json (gate + expert, src/selftest.rs:259-323), and (2) imports
 the two reference Python helpers that touch this path - ref/mxfp4_numpy.py
 (dequant) and nano/export.py::quantize_mxfp4 (naive-scale quantizer) - and
@@ -37,6 +37,13 @@ def main():
              rows=np.int64(g["rows"]), cols=np.int64(g["cols"]),
              packed=np.array(g["packed"], np.uint8), scales=np.array(g["scales"], np.uint8),
              dequant=np.array(g["dequant"], np.float32))
+
+    # 1b. torch-generated fp8 e4m3 + ue8m0 (128 x 128 blocks) matrix of the same file (src/selftest.rs:205-224)
+    g8 = json.load(open(os.path.join(REF, "ref/ds_golden.json")))["fp8"]
+    np.savez_compressed(os.path.join(OUT, "ds_fp8.npz"),
+                        rows=np.int64(g8["rows"]), cols=np.int64(g8["cols"]),
+                        w_packed=np.array(g8["w_packed"], np.uint8), scales=np.array(g8["scales"], np.uint8),
+                        dequant=np.array(g8["dequant"], np.float32))
 
     # 2. DeepSeek gate (3 tokens x 32 experts, top-6, route_scale 1.5) and SwiGLU-clamp expert
     g2 = json.load(open(os.path.join(REF, "ref/ds_golden2.json")))

@@ -288,3 +288,21 @@ def test_argument_errors_are_statuses_not_crashes(mk):
     rc = L.mk_matvec_q8(ctx._h, w._h, x.ctypes.data_as(C.c_void_p), x.ctypes.data_as(C.c_void_p), 1, 0, None)
     assert rc == -1 and b"format" in L.mk_last_error()
     assert ctx.status_word() == 0
+
+
+def test_fp8_dequant_bit_exact(mk):
+    """dequant::dequant_fp8 against the torch-generated block of ref/ds_golden.json and, for every byte
+    value and extreme scale bytes, against the oracle (NaN encodings, -0.0, subnormal scales)."""
+    g = np.load(os.path.join(GOLDEN, "ds_fp8.npz"))
+    rows, cols = int(g["rows"]), int(g["cols"])
+    out = mk.dequant_fp8(g["w_packed"], g["scales"], rows, cols)
+    assert np.array_equal(bits(out), bits(g["dequant"].reshape(rows, cols)))
+    rng = np.random.default_rng(8)
+    w = rng.integers(0, 256, (200, 300), dtype=np.uint8)
+    w[0, :256] = np.arange(256)
+    s = rng.integers(0, 255, (2, 3), dtype=np.uint8)
+    s[0, 0], s[1, 2] = 0, 254
+    got, ref = mk.dequant_fp8(w, s, 200, 300), O.dequant_fp8(w, s, 200, 300)
+    nan = np.isnan(ref)
+    assert np.array_equal(nan, np.isnan(got))
+    assert np.array_equal(bits(got)[~nan], bits(ref)[~nan])

@@ -439,3 +439,17 @@ def test_vq1_lut_gemv_bit_identical_to_gather():
                 g = np.float32(g + np.float32(cb[idx[r, v], j] * x[16 * v + j]))
             s = np.float32(s + g)
         assert bits(np.array([s]))[0] == bits(a[r:r + 1])[0]
+
+
+def test_fp8_dequant_matches_torch_golden():
+    """ref/ds_golden.json 'fp8' (src/selftest.rs:205-211): 256 x 256 e4m3fn + ue8m0 per 128 x 128, exact."""
+    g = np.load(os.path.join(GOLDEN, "ds_fp8.npz"))
+    rows, cols = int(g["rows"]), int(g["cols"])
+    out = O.dequant_fp8(g["w_packed"], g["scales"], rows, cols)
+    assert np.array_equal(bits(out), bits(g["dequant"].reshape(rows, cols)))
+    # every byte value, scale bytes at the ends of the range
+    allb = np.arange(256, dtype=np.uint8).reshape(1, 256)
+    for sb in (0, 1, 127, 140, 254):
+        o = O.dequant_fp8(allb, np.array([sb, sb], np.uint8), 1, 256)[0]
+        assert np.isnan(o[0x7F]) and np.isnan(o[0xFF])
+        assert o[0] == 0.0 and np.signbit(o[0x80]) and o[0x80] == 0.0
