@@ -56,14 +56,26 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
         const float *s = src + (int64_t)b * ld;
         Best best = {-INFINITY, INT64_MAX};
         if (vec) {
-            for (int64_t i = tid; i < n / 4; i += blockDim.x) {
-                const float4 v = ((const float4 *)s)[i];
-                for (int p = 0; p < world; ++p)
-                    if (p != rank) ((float4 *)(pe.dst[p] + (int64_t)b * ld))[i] = v;
-                best = better(best, Best{v.x, 4 * i});
-                best = better(best, Best{v.y, 4 * i + 1});
-                best = better(best, Best{v.z, 4 * i + 2});
-                best = better(best, Best{v.w, 4 * i + 3});
+            // 4 independent 16-byte loads in flight per thread: one CTA has to keep a third of a megabyte moving
+            const int64_t n4 = n / 4, stride = blockDim.x;
+            for (int64_t i0 = tid; i0 < n4; i0 += 4 * stride) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t i = i0 + u * stride;
+                    v[u] = i < n4 ? __ldcg((const float4 *)s + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t i = i0 + u * stride;
+                    if (i >= n4) continue;
+                    for (int p = 0; p < world; ++p)
+                        if (p != rank) ((float4 *)(pe.dst[p] + (int64_t)b * ld))[i] = v[u];
+                    best = better(best, Best{v[u].x, 4 * i});
+                    best = better(best, Best{v[u].y, 4 * i + 1});
+                    best = better(best, Best{v[u].z, 4 * i + 2});
+                    best = better(best, Best{v[u].w, 4 * i + 3});
+                }
             }
         } else {
             for (int64_t i = tid; i < n; i += blockDim.x) {
