@@ -326,6 +326,48 @@ mla_rope_scores_kernel(const MlaDev c, const float *__restrict__ q_f32, const in
     }
 }
 
+// The same with the position's rope row held in registers (RC float4 per lane) and only the queries in
+// shared memory: the kernel above reads 4 shared-memory vectors per 8 multiply-adds and is bound by
+// shared-memory bandwidth; here a head costs RC broadcast reads against 8 RC multiply-adds.  The 8
+// accumulators and their reduction keep the engine's shape, but each term is a fused multiply-add
+// (one rounding less than the engine's separate multiply and add): the attention output is held to the
+// oracle by tolerance, not bit for bit, and this pre-pass is FP32-issue-bound (64 terms per position
+// and head against 4 per instruction in the int8 part).
+template <int RC>
+__global__ void __launch_bounds__(256)
+mla_rope_scores_reg_kernel(const MlaDev c, const float *__restrict__ q_f32, const int *__restrict__ npos_arr, int npos_fixed,
+                           int seq0, float *__restrict__ rs) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tile = blockIdx.x, bi = blockIdx.y, seq = seq0 + bi;
+    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    if (tile * 32 >= n) return;
+    float4 *q_s = (float4 *)smem;                        // [H][RC]
+    const int hd = c.nope + c.rope;
+    const int p = threadIdx.x & 31;
+    const float4 *src = (const float4 *)c.krt + ((int64_t)seq * c.T + tile) * RC * 32;
+    float4 k[RC];
+    // the rope row first: its (cold) loads travel while the queries are staged
+#pragma unroll
+    for (int c4 = 0; c4 < RC; ++c4) k[c4] = __ldg(src + c4 * 32 + p);
+    for (int i = threadIdx.x; i < c.H * RC; i += blockDim.x)
+        q_s[i] = __ldg((const float4 *)(q_f32 + ((int64_t)bi * c.H + i / RC) * hd + c.nope + (i % RC) * 4));
+    __syncthreads();
+    for (int h = threadIdx.x >> 5; h < c.H; h += blockDim.x >> 5) {
+        float a8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int c4 = 0; c4 < RC; c4 += 2) {
+            const float4 q0 = q_s[h * RC + c4], q1 = q_s[h * RC + c4 + 1];
+            a8[0] = fmaf(q0.x, k[c4].x, a8[0]); a8[1] = fmaf(q0.y, k[c4].y, a8[1]);
+            a8[2] = fmaf(q0.z, k[c4].z, a8[2]); a8[3] = fmaf(q0.w, k[c4].w, a8[3]);
+            a8[4] = fmaf(q1.x, k[c4 + 1].x, a8[4]); a8[5] = fmaf(q1.y, k[c4 + 1].y, a8[5]);
+            a8[6] = fmaf(q1.z, k[c4 + 1].z, a8[6]); a8[7] = fmaf(q1.w, k[c4 + 1].w, a8[7]);
+        }
+        rs[((int64_t)bi * c.H + h) * c.T * 32 + tile * 32 + p] =
+            __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(a8[0], a8[1]), __fadd_rn(a8[2], a8[3])), __fadd_rn(a8[4], a8[5])),
+                      __fadd_rn(a8[6], a8[7]));
+    }
+}
+
 // ------------------------------------------------------------------ per-head layout, vd == 128
 // One warp per (sequence, head, KV split), 8 warps (8 consecutive heads, same split) per CTA.
 // The record of a (position tile, head) - 9216 contiguous bytes at the micro head dims -
@@ -784,12 +826,18 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
         const size_t qw = (size_t)m->nope + mk_align_up((size_t)m->nb * 4, 16);
         const size_t smem_ph = (size_t)PH_WARPS * m->rec_bytes + PH_WARPS * qw + PH_WARPS * 2 * 8 + 128;
         {
-            const size_t smem_rs = ((size_t)m->RC * 32 + (size_t)m->H * m->RC) * 16;
-            static bool attr_rs = false;
-            if (!attr_rs) { MK_CUDA(cudaFuncSetAttribute(mla_rope_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_rs = true; }
-            MK_CHECK_ARG(smem_rs <= 200 * 1024, "rope dims too large");
-            mla_rope_scores_kernel<<<dim3((unsigned)ntiles_p, (unsigned)nq), 256, smem_rs, ctx->stream>>>(
-                cph, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, m->rope_scores);
+            if (m->RC == 16 && (size_t)m->H * 256 <= 48 * 1024) {
+                // rope 64: the position's rope row lives in registers
+                mla_rope_scores_reg_kernel<16><<<dim3((unsigned)ntiles_p, (unsigned)nq), 256, (size_t)m->H * 16 * 16, ctx->stream>>>(
+                    cph, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, m->rope_scores);
+            } else {
+                const size_t smem_rs = ((size_t)m->RC * 32 + (size_t)m->H * m->RC) * 16;
+                static bool attr_rs = false;
+                if (!attr_rs) { MK_CUDA(cudaFuncSetAttribute(mla_rope_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_rs = true; }
+                MK_CHECK_ARG(smem_rs <= 200 * 1024, "rope dims too large");
+                mla_rope_scores_kernel<<<dim3((unsigned)ntiles_p, (unsigned)nq), 256, smem_rs, ctx->stream>>>(
+                    cph, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, m->rope_scores);
+            }
             ctx->launches++;
         }
         static bool attr_ph = false;
