@@ -181,9 +181,19 @@ def run_gpu(args):
     # N > 1: the matvec kernel stores its rows straight into every rank's gather buffer (peer memory);
     # --collective nccl runs the library all-gather instead, for comparison
     fused = None
+    fused_note = None
     if world > 1 and batch <= 2 and args.collective == "peer":
         from microkimi_b200 import dist as mkd
-        fused = mkd.FusedVocabHead(heads[0], VOCAB, max_batch=batch)
+        ok = torch.ones(1, dtype=torch.int32, device=dev)
+        try:
+            fused = mkd.FusedVocabHead(heads[0], VOCAB, max_batch=batch)
+        except Exception as exc:   # e.g. no peer access between two GPUs of this box
+            fused_note = f"peer buffers unavailable ({type(exc).__name__}: {exc}); NCCL all-gather used"
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # all ranks take the same path
+        if int(ok.item()) == 0:
+            fused = None
+            fused_note = fused_note or "peer buffers unavailable on another rank; NCCL all-gather used"
 
     def step(i):
         if world == 1:
@@ -293,7 +303,7 @@ def run_gpu(args):
                        "batch": batch, "rows_per_gpu": rows,
                        "l2": f"inputs larger than L2: {shard_bytes * copies / 1e6:.0f} MB of weights per GPU"
                              + (f" ({copies} rotating copies of the shard)" if copies > 1 else ""),
-                       "algorithmic_bytes_per_step": alg_step},
+                       "algorithmic_bytes_per_step": alg_step, **({"note": fused_note} if fused_note else {})},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": (achieved / peak) if achieved else None,
                          "traffic": NCU_TRAFFIC_PER_LAUNCH_N1 / world if batch == 1 else None,

@@ -80,8 +80,18 @@ class FusedVocabHead:
         allh = torch.empty((self.world, 64), dtype=torch.uint8, device=dev)
         dist.all_gather_into_tensor(allh.view(-1), mine, group=group)
         buf = (C.c_uint8 * (64 * self.world)).from_buffer_copy(bytes(allh.cpu().numpy().tobytes()))
-        _l.check(L.mk_gather_connect(self.ctx._h, self._h, buf))
-        dist.barrier(group=group)
+        # every rank learns whether all ranks could open all buffers, so that all of them raise or none does
+        ok = torch.ones(1, dtype=torch.int32, device=dev)
+        err = None
+        try:
+            _l.check(L.mk_gather_connect(self.ctx._h, self._h, buf))
+        except Exception as exc:
+            err = exc
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            self.free()
+            raise RuntimeError(f"peer gather buffers could not be connected on every rank ({err})")
         self._am = torch.empty((self.max_batch,), dtype=torch.int32, device=dev)
 
     def matvec(self, x, want_argmax=True, head=None):
