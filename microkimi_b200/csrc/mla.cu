@@ -330,8 +330,8 @@ mla_rope_scores_kernel(const MlaDev c, const float *__restrict__ q_f32, const in
 // shared memory: the kernel above reads 4 shared-memory vectors per 8 multiply-adds and is bound by
 // shared-memory bandwidth; here a head costs RC broadcast reads against 8 RC multiply-adds.  The 8
 // accumulators and their reduction keep the engine's shape, but each term is a fused multiply-add
-// (one rounding less than the engine's separate multiply and add): the attention output is held to the
-// oracle by tolerance, not bit for bit, and this pre-pass is FP32-issue-bound (64 terms per position
+// (one rounding less than the engine's separate multiply and add): the attention output is compared with the
+// CPU recipe by tolerance, not bit for bit, and this pre-pass is FP32-issue-bound (64 terms per position
 // and head against 4 per instruction in the int8 part).
 template <int RC>
 __global__ void __launch_bounds__(256)
