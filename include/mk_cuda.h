@@ -278,6 +278,25 @@ int32_t mk_moe_experts_dev(mk_ctx *ctx, mk_moe *moe, const float *x, int32_t n_r
  * combination after the expert jobs (src/deepseek.rs:1095-1106).  DEVICE pointers. */
 int32_t mk_moe_combine_dev(mk_ctx *ctx, const float *outs, int32_t n_tokens, int32_t slots, int32_t d, float *out);
 
+/* ---- expert-parallel MoE over the GPUs of one node (decode) ----------------
+ * No counterpart in the reference (a single-process engine).  Token rows are replicated on
+ * every rank (<= 16 rows); the layer object of a rank holds only that rank's routed experts
+ * (NULL entries for the others) plus the shared expert.  One call routes all rows on every
+ * rank (identical ids), runs the (row, expert) pairs whose expert is resident - the shared
+ * expert of row t on rank t % world -, pushes their output rows into the (row, slot) table
+ * of every other rank over NVLink (peer memory, no collective library call), waits -
+ * bounded, MK_ERR_TIMEOUT in the status word otherwise - for the other ranks' rows and sums
+ * the table in slot order: the result is bit-identical to one GPU holding all experts.
+ * Create / connect work like mk_gather_create / mk_gather_connect (64-byte handles). */
+typedef struct mk_moe_ep mk_moe_ep;
+int32_t mk_moe_ep_create(mk_ctx *ctx, const mk_moe *moe, int32_t rank, int32_t world, int32_t max_tokens, mk_moe_ep **out,
+                         uint8_t *handle);
+int32_t mk_moe_ep_connect(mk_ctx *ctx, mk_moe_ep *ep, const uint8_t *handles);
+int32_t mk_moe_ep_free(mk_ctx *ctx, mk_moe_ep *ep);
+/* Arguments as mk_moe_forward_dev; every rank passes the same x and must make the same sequence of calls. */
+int32_t mk_moe_forward_ep_dev(mk_ctx *ctx, mk_moe *moe, mk_moe_ep *ep, const float *x, int32_t n_tokens, float *out, int32_t *ids,
+                              float *weights);
+
 /* ---- q8_0 MLA KV cache and decode attention ------------------------------
  * Replaces MlaCache::push and mla_attn_flash_q8_mqa (src/model.rs:1583-1618,
  * 1804-1908).  One object holds n_seqs independent caches of max_positions each.

@@ -51,6 +51,22 @@ struct mk_moe {
     int max_items;
 };
 
+// Expert parallelism over the GPUs of one node for decode (token rows replicated on every rank, <= 16 rows):
+// every rank routes all rows (bit-identical ids), runs the pairs whose expert it holds, pushes their
+// output rows into the (token, slot) table of every other rank (peer memory), and combines the full table.
+// Buffer per rank (cudaMalloc, shared by CUDA IPC): [flags: 2 parities x 8 ranks u32, 256 B]
+// [outs: 2 parities x max_tokens * slots x d f32].
+struct mk_moe_ep {
+    int rank, world, max_tokens, slots, d;
+    size_t par_bytes, blob_bytes;
+    void *blob;
+    void *peer[8];
+    bool connected;
+    uint32_t step;
+    int32_t *n_local;   // device: pairs computed by this rank in the current call
+    uint32_t *counter;  // device: exchange kernel's finished CTAs, 0 between calls
+};
+
 namespace {
 
 // ------------------------------------------------------------------ router logits
@@ -188,14 +204,22 @@ moe_topk_kernel(const float *__restrict__ score, const float *__restrict__ key, 
 // Grouping of a SMALL pair list by one CTA without per-expert arrays: the place of a pair
 // in the expert-sorted list is the number of pairs that come before it in (expert, pair id)
 // order; one work item starts at every 8th pair of an expert.  sh: 3 * n_pairs ints.
+// ep_world > 0 (expert parallel over replicated tokens): pairs of experts that live on another rank are
+// left to that rank without complaint, and the shared expert (resident everywhere) of token t is taken
+// by rank t % ep_world; n_local receives the number of pairs this rank computes (= entries of `sorted`).
 __device__ __forceinline__ void plan_small(const int32_t *pair_expert, int n_pairs, int n_slots, const void *const *__restrict__ wv,
                                            int32_t *__restrict__ sorted, int32_t *__restrict__ items, int32_t *__restrict__ n_items,
-                                           int max_items, int32_t *__restrict__ status, int *sh) {
+                                           int max_items, int32_t *__restrict__ status, int *sh, int pairs_per_tok, int ep_rank,
+                                           int ep_world, int32_t *__restrict__ n_local) {
     int *sh_e = sh, *sh_rank = sh + n_pairs, *sh_start = sh + 2 * n_pairs;
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int e = pair_expert[p];
-        const bool ok = e >= 0 && e < n_slots && wv[e * 3] != nullptr;
-        if (!ok) atomicCAS(status, 0, MK_ERR_ARG);
+        bool ok = e >= 0 && e < n_slots && wv[e * 3] != nullptr;
+        if (ep_world > 0) {
+            if (ok && e == n_slots - 1 && (p / pairs_per_tok) % ep_world != ep_rank) ok = false;
+        } else if (!ok) {
+            atomicCAS(status, 0, MK_ERR_ARG);
+        }
         sh_e[p] = ok ? e : -1; // pairs naming an expert that is not resident are dropped
     }
     __syncthreads();
@@ -230,8 +254,9 @@ __device__ __forceinline__ void plan_small(const int32_t *pair_expert, int n_pai
         }
     }
     if (threadIdx.x == 0) {
-        int total = 0;
-        for (int q = 0; q < n_pairs; ++q) total += sh_start[q];
+        int total = 0, mine = 0;
+        for (int q = 0; q < n_pairs; ++q) { total += sh_start[q]; mine += sh_e[q] >= 0 ? 1 : 0; }
+        if (n_local) *n_local = mine;
         *n_items = total < max_items ? total : max_items;
         if (total > max_items) atomicCAS(status, 0, MK_ERR_STATE);
     }
@@ -253,6 +278,7 @@ struct RouterFusedArgs {
     int32_t *sorted, *items, *n_items; int max_items;
     int32_t *status, *counter;
     int8_t *xq; float *xs; int64_t nbp;
+    int ep_rank, ep_world; int32_t *n_local;   // expert parallel over replicated tokens (ep_world 0 = off)
 };
 template <class S>
 __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFusedArgs a) {
@@ -307,7 +333,8 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
     __threadfence_block();
     __syncthreads();
     const int slots = a.top_k + (a.shared_slot ? 1 : 0);
-    plan_small(a.pair_expert, n_tokens * slots, n_experts + 1, a.wv, a.sorted, a.items, a.n_items, a.max_items, a.status, (int *)rsm);
+    plan_small(a.pair_expert, n_tokens * slots, n_experts + 1, a.wv, a.sorted, a.items, a.n_items, a.max_items, a.status, (int *)rsm, slots,
+               a.ep_rank, a.ep_world, a.n_local);
 }
 
 // ------------------------------------------------------------------ plan
@@ -553,6 +580,50 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
     float v = 0.0f;
     for (int s = 0; s < slots; ++s) v = __fadd_rn(v, outs[(t * slots + s) * d + j]);
     out[idx] = v;
+}
+
+// ------------------------------------------------------------------ expert-parallel exchange
+// CTA c copies the output row of the c-th pair this rank computed into the same table slot of every other
+// rank (16-byte peer stores).  The last CTA to finish publishes this rank's step number in every rank's flag
+// word and waits - bounded - for all ranks' flags: when the kernel ends, the local table is complete.
+constexpr uint32_t EP_WAIT_LIMIT = 1u << 22; // polls of >= 100 ns: about half a second
+struct EpPeers { float *outs[8]; uint32_t *flag[8]; };
+__global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, const float *__restrict__ local_outs,
+                                                             const int32_t *__restrict__ sorted, const int32_t *__restrict__ n_local, int d,
+                                                             int rank, int world, const uint32_t *__restrict__ flags, uint32_t step,
+                                                             uint32_t *__restrict__ counter, int32_t *__restrict__ status) {
+    __shared__ int s_last;
+    if ((int)blockIdx.x < *n_local) {
+        const int64_t p = sorted[blockIdx.x];
+        const float4 *src = (const float4 *)(local_outs + p * d);
+        for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+            const float4 v = __ldcg(src + i);
+            for (int q = 0; q < world; ++q)
+                if (q != rank) ((float4 *)(pe.outs[q] + p * d))[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(counter, 1u);
+        s_last = prev == gridDim.x - 1 ? 1 : 0;
+        if (s_last) *counter = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    if ((int)threadIdx.x < world) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pe.flag[threadIdx.x]), "r"(step) : "memory");
+        bool ok = false;
+        for (uint32_t it = 0; it < EP_WAIT_LIMIT; ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+            if ((int32_t)(v - step) >= 0) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
+    }
+    __threadfence_system();
 }
 
 } // namespace
@@ -848,7 +919,7 @@ extern "C" int32_t mk_moe_experts_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
     return moe_experts_launch(ctx, m, x, n_rows, pair_row, pair_expert, pair_weight, n_pairs, outs);
 }
 
-extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
+static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && out != nullptr && n > 0, "bad argument");
     MK_CHECK_ARG(m->has_router, "this MoE object was created without a router");
     MK_CUDA(cudaSetDevice(ctx->device));
@@ -867,7 +938,9 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
     size_t smem_f = small ? RtSmall::SMEM : RtBig::SMEM;
     if ((size_t)8 * m->n_experts * 4 > smem_f) smem_f = (size_t)8 * m->n_experts * 4;
     if ((size_t)3 * n * slots * 4 > smem_f) smem_f = (size_t)3 * n * slots * 4;
-    const bool fused = n <= 16 && m->dx % 4 == 0 && ((uintptr_t)x & 15) == 0 && smem_f <= 200 * 1024 && !ctx->moe_no_fuse;
+    const bool fused = n <= 16 && m->dx % 4 == 0 && ((uintptr_t)x & 15) == 0 && smem_f <= 200 * 1024 && (!ctx->moe_no_fuse || ep);
+    MK_CHECK_ARG(ep == nullptr || (fused && n <= ep->max_tokens && slots == ep->slots && m->d == ep->d && (ep->connected || ep->world == 1)),
+                 "expert-parallel call: needs <= max_tokens (<= 16) aligned rows and a connected exchange object made for this layer");
     const bool fused_q = fused && m->latent == 0; // the router's rows are the experts' rows: quantize them in the same launch
     if (fused) {
         RouterFusedArgs ra;
@@ -878,6 +951,7 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
         ra.ids = m->ids; ra.wts = m->wts; ra.pair_row = m->pair_row; ra.pair_expert = m->pair_expert; ra.pair_weight = m->pair_weight;
         ra.wv = m->wv; ra.sorted = m->sorted; ra.items = m->items; ra.n_items = m->n_items; ra.max_items = m->max_items;
         ra.status = ctx->status_dev; ra.counter = m->counter; ra.xq = m->xq; ra.xs = m->xs; ra.nbp = m->nbp_d;
+        ra.ep_rank = ep ? ep->rank : 0; ra.ep_world = ep ? ep->world : 0; ra.n_local = ep ? ep->n_local : nullptr;
         const unsigned qctas = fused_q ? (unsigned)mk_ceil_div((int64_t)n * m->nbp_d, 8) : 0u;
         {
             mk_prof_scope prof(ctx, MK_PROF_ROUTER);
@@ -898,10 +972,33 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
         rc = moe_route_launch(ctx, m, x, n, true);
         if (rc != MK_OK) return rc;
     }
-    rc = moe_experts_launch(ctx, m, xe, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, m->outs, fused, fused_q);
-    if (rc != MK_OK) return rc;
+    float *outs = m->outs;
+    if (ep) {
+        // the (token, slot) table of this step lives in the exchange buffer: local pairs are written by the
+        // expert kernels, the others arrive from their ranks
+        ep->step++;
+        const uint32_t par = ep->step & 1u;
+        outs = (float *)((char *)ep->blob + 256 + (size_t)par * ep->par_bytes);
+        rc = moe_experts_launch(ctx, m, xe, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, outs, true, fused_q);
+        if (rc != MK_OK) return rc;
+        EpPeers pe;
+        memset(&pe, 0, sizeof(pe));
+        for (int r = 0; r < ep->world; ++r) {
+            pe.outs[r] = (float *)((char *)ep->peer[r] + 256 + (size_t)par * ep->par_bytes);
+            pe.flag[r] = (uint32_t *)ep->peer[r] + par * 8 + ep->rank;
+        }
+        mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
+        moe_ep_exchange_kernel<<<(unsigned)(n * slots), 256, 0, ctx->stream>>>(pe, outs, m->sorted, ep->n_local, m->d, ep->rank, ep->world,
+                                                                             (const uint32_t *)ep->blob + par * 8, ep->step, ep->counter,
+                                                                             ctx->status_dev);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+    } else {
+        rc = moe_experts_launch(ctx, m, xe, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, outs, fused, fused_q);
+        if (rc != MK_OK) return rc;
+    }
     // slot-order sum (for MK_MOE_SITU the terms already carry their routing weights)
-    rc = mk_moe_combine_dev(ctx, m->outs, n, slots, m->d, m->latent > 0 ? m->lat_y : out);
+    rc = mk_moe_combine_dev(ctx, outs, n, slots, m->d, m->latent > 0 ? m->lat_y : out);
     if (rc != MK_OK) return rc;
     if (m->latent > 0) {
         // norm BEFORE the up projection (src/model.rs:2352-2356)
@@ -921,6 +1018,87 @@ extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
     }
     if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)n * m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_forward_dev(mk_ctx *ctx, mk_moe *m, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
+    return moe_forward_impl(ctx, m, nullptr, x, n, out, ids, weights);
+}
+
+extern "C" int32_t mk_moe_forward_ep_dev(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const float *x, int32_t n, float *out, int32_t *ids,
+                                         float *weights) {
+    MK_CHECK_ARG(ep != nullptr, "NULL exchange object");
+    return moe_forward_impl(ctx, m, ep, x, n, out, ids, weights);
+}
+
+extern "C" int32_t mk_moe_ep_create(mk_ctx *ctx, const mk_moe *m, int32_t rank, int32_t world, int32_t max_tokens, mk_moe_ep **out,
+                                    uint8_t *handle /* 64 bytes */) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && out != nullptr && handle != nullptr, "NULL argument");
+    MK_CHECK_ARG(world >= 1 && world <= 8 && rank >= 0 && rank < world, "need 0 <= rank < world <= 8");
+    MK_CHECK_ARG(max_tokens >= 1 && max_tokens <= 16, "max_tokens must be in [1, 16]");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    *out = nullptr;
+    MK_CUDA(cudaSetDevice(ctx->device));
+    mk_moe_ep *ep = new (std::nothrow) mk_moe_ep();
+    if (!ep) return MK_ERR_OOM;
+    memset(ep, 0, sizeof(*ep));
+    ep->rank = rank; ep->world = world; ep->max_tokens = max_tokens;
+    ep->slots = m->top_k + (m->has_shared ? 1 : 0);
+    ep->d = m->d;
+    ep->par_bytes = (size_t)max_tokens * ep->slots * ep->d * 4;
+    ep->blob_bytes = 256 + 2 * ep->par_bytes;
+    cudaError_t e = cudaMalloc(&ep->blob, ep->blob_bytes);
+    if (e == cudaSuccess) e = cudaMemset(ep->blob, 0, ep->blob_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ep->n_local, 4);
+    if (e == cudaSuccess) e = cudaMalloc(&ep->counter, 4);
+    if (e == cudaSuccess) e = cudaMemset(ep->n_local, 0, 4);
+    if (e == cudaSuccess) e = cudaMemset(ep->counter, 0, 4);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ep->blob);
+    if (e != cudaSuccess) {
+        mk_set_error("mk_moe_ep_create: %s", cudaGetErrorString(e));
+        if (ep->blob) cudaFree(ep->blob);
+        if (ep->n_local) cudaFree(ep->n_local);
+        if (ep->counter) cudaFree(ep->counter);
+        delete ep;
+        return e == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA;
+    }
+    memcpy(handle, &h, 64);
+    ep->peer[rank] = ep->blob;
+    *out = ep;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_ep_connect(mk_ctx *ctx, mk_moe_ep *ep, const uint8_t *handles /* [world][64], by rank */) {
+    MK_CHECK_ARG(ctx != nullptr && ep != nullptr && handles != nullptr, "NULL argument");
+    MK_CHECK_ARG(!ep->connected, "already connected");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    for (int r = 0; r < ep->world; ++r) {
+        if (r == ep->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        cudaError_t e = cudaIpcOpenMemHandle(&ep->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            mk_set_error("mk_moe_ep_connect: rank %d cannot open rank %d's buffer: %s", ep->rank, r, cudaGetErrorString(e));
+            for (int q = 0; q < r; ++q)
+                if (q != ep->rank && ep->peer[q]) { cudaIpcCloseMemHandle(ep->peer[q]); ep->peer[q] = nullptr; }
+            return MK_ERR_CUDA;
+        }
+    }
+    ep->connected = true;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_moe_ep_free(mk_ctx *ctx, mk_moe_ep *ep) {
+    MK_CHECK_ARG(ctx != nullptr && ep != nullptr, "NULL argument");
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int r = 0; r < ep->world; ++r)
+        if (r != ep->rank && ep->peer[r]) cudaIpcCloseMemHandle(ep->peer[r]);
+    if (ep->blob) cudaFree(ep->blob);
+    if (ep->n_local) cudaFree(ep->n_local);
+    if (ep->counter) cudaFree(ep->counter);
+    delete ep;
     return MK_OK;
 }
 

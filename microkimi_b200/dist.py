@@ -125,6 +125,57 @@ class FusedVocabHead:
         self._h = None
 
 
+class PeerEpMoeLayer:
+    """Expert-parallel MoE for decode without a collective library call per layer: token rows are
+    replicated on every rank (<= 16), each rank runs the pairs of its resident experts and the
+    output rows travel by peer-memory stores (mk_moe_forward_ep_dev).  `layer` is an ops.MoeLayer
+    built with None for the routed experts that live on other ranks (local_expert_range) and with
+    the shared expert on every rank."""
+
+    def __init__(self, layer, group=None, max_tokens=16):
+        import ctypes as C
+        from . import lib as _l
+        self.layer, self.ctx = layer, layer.ctx
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        L = self.ctx._L
+        h = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        _l.check(L.mk_moe_ep_create(self.ctx._h, layer._h, self.rank, self.world, int(max_tokens), C.byref(h), handle))
+        self._h = h
+        dev = torch.device("cuda", self.ctx.device)
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
+        allh = torch.empty((self.world, 64), dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(allh.view(-1), mine, group=group)
+        buf = (C.c_uint8 * (64 * self.world)).from_buffer_copy(bytes(allh.cpu().numpy().tobytes()))
+        ok = torch.ones(1, dtype=torch.int32, device=dev)
+        err = None
+        try:
+            _l.check(L.mk_moe_ep_connect(self.ctx._h, self._h, buf))
+        except Exception as exc:
+            err = exc
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            self.free()
+            raise RuntimeError(f"peer exchange buffers could not be connected on every rank ({err})")
+
+    def forward(self, x):
+        """x [n, d] (torch CUDA, n <= max_tokens, the same rows on every rank) -> [n, d], the same on every rank."""
+        import ctypes as C
+        from . import lib as _l
+        xs = x.reshape(-1, self.layer.dx)
+        assert xs.dtype == torch.float32 and xs.is_contiguous()
+        out = torch.empty_like(xs)
+        _l.check(self.ctx._L.mk_moe_forward_ep_dev(self.ctx._h, self.layer._h, self._h, C.c_void_p(xs.data_ptr()), xs.shape[0],
+                                                  C.c_void_p(out.data_ptr()), None, None))
+        return out.reshape(x.shape)
+
+    def free(self):
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._L.mk_moe_ep_free(self.ctx._h, self._h)
+        self._h = None
+
+
 # ---------------------------------------------------------------- expert-parallel MoE
 def expert_owner(expert, n_experts, world):
     """Block partition of the routed experts: expert e lives on rank e // (n_experts / world)."""

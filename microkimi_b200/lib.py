@@ -93,6 +93,10 @@ SIGNATURES = {
     "mk_moe_route_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "mk_moe_forward": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "mk_moe_forward_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "mk_moe_ep_create": (_i32, [_vp, _vp, _i32, _i32, _i32, C.POINTER(_vp), _vp]),
+    "mk_moe_ep_connect": (_i32, [_vp, _vp, _vp]),
+    "mk_moe_ep_free": (_i32, [_vp, _vp]),
+    "mk_moe_forward_ep_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "mk_moe_experts_dev": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp]),
     "mk_moe_combine_dev": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "mk_mla_create": (_i32, [_vp, C.POINTER(MlaDesc), C.POINTER(_vp)]),

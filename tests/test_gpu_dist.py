@@ -77,6 +77,18 @@ def _worker(rank, world, port, ret):
         out = ep.forward(xt[tlo:thi].contiguous())
         torch.cuda.synchronize()
         ok_moe = torch.equal(out, ref[tlo:thi]) and ctx.status_word() == 0
+        # ---- the decode form: rows replicated, outputs exchanged by peer-memory stores; several calls in a
+        # row (the table alternates by step parity) and several row counts
+        pep = mkd.PeerEpMoeLayer(mk.MoeLayer(gw, None, mine, experts[-1], k, ctx=ctx), max_tokens=16)
+        for step, nrows in enumerate((1, 2, 5, 11, 1, 3)):
+            xin = (xt[:nrows] * float(1 + step % 3)).contiguous()
+            got = pep.forward(xin)
+            want = whole.moe_forward(xin)
+            torch.cuda.synchronize()
+            ok_moe = ok_moe and torch.equal(got, want)
+        ok_moe = ok_moe and ctx.status_word() == 0
+        dist.barrier()
+        pep.free()
         ret[rank] = (bool(ok_head), bool(ok_moe))
     finally:
         dist.destroy_process_group()

@@ -252,3 +252,30 @@ def test_situ_without_latent_and_bad_descriptors(mk):
     # the K3 body takes its shared expert as f32 matrices: an MXFP4 shared triple is refused
     with pytest.raises(L.MkError):
         mk.MoeLayer(gate_w, None, dev, dev[0], k, activation="situ")
+
+
+def test_expert_parallel_entry_point_with_one_rank(mk):
+    """mk_moe_forward_ep_dev with world = 1: the same grouping rule, exchange kernel (no peer to push to,
+    its own flag to wait for) and table combine as on several GPUs; results equal mk_moe_forward_dev bit for bit."""
+    import ctypes as C
+    import torch
+    from microkimi_b200 import lib as L
+    layer, ref, rng = make_layer(mk, 16, 4, 256, 128, seed=123)
+    ctx = mk.Context.default()
+    ctx.use_torch_stream()
+    ep, handle = C.c_void_p(), (C.c_uint8 * 64)()
+    L.check(ctx._L.mk_moe_ep_create(ctx._h, layer._h, 0, 1, 16, C.byref(ep), handle))
+    try:
+        for n in (1, 2, 7, 16, 3):
+            x = torch.from_numpy(rng.standard_normal((n, 256)).astype(np.float32)).cuda()
+            want = layer.moe_forward(x)
+            got = torch.empty_like(x)
+            L.check(ctx._L.mk_moe_forward_ep_dev(ctx._h, layer._h, ep, C.c_void_p(x.data_ptr()), n, C.c_void_p(got.data_ptr()), None, None))
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)
+        with pytest.raises(L.MkError):   # more rows than the exchange table holds
+            x = torch.zeros((17, 256), device="cuda")
+            L.check(ctx._L.mk_moe_forward_ep_dev(ctx._h, layer._h, ep, C.c_void_p(x.data_ptr()), 17, C.c_void_p(x.data_ptr()), None, None))
+        assert ctx.status_word() == 0
+    finally:
+        L.check(ctx._L.mk_moe_ep_free(ctx._h, ep))
