@@ -434,6 +434,75 @@ def run_case_moe(args):
                                    "peak_kind": kind, "note": "whole layer call, not one kernel"}}), flush=True)
 
 
+def run_case_moe_ep(args):
+    """Side workload under torchrun: the MoE layer of --case moe with its routed experts block-partitioned
+    over the ranks (expert parallelism) and the same `batch` token rows on every rank (decode).  Times the
+    peer-memory path (one call per layer, no collective library call) and, with --collective nccl, the
+    all-to-all path on the same weights (there every rank owns batch / world of the rows).  Time = max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    import microkimi_b200 as mk
+    from microkimi_b200 import dist as mkd
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
+    dev = torch.device("cuda", local)
+    ctx = mk.Context(local)
+    mk.Context._default = ctx
+    ctx.use_torch_stream()
+    E, k, d, inter, B = args.experts, 8, 7168, 2048, args.batch
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)  # the same router and token rows on every rank
+
+    def rand_w(rows, cols):
+        p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
+        s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
+        return mk.MxFp4Weight(p, s, rows, cols, ctx=ctx)
+
+    gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
+    x = torch.randn((B, d), dtype=torch.float32, device=dev, generator=gen)
+    lo, hi = mkd.local_expert_range(E, world, rank)
+    layers = []
+    for _ in range(args.copies):
+        mine = [None] * E
+        for e in range(lo, hi):
+            mine[e] = (rand_w(inter, d), rand_w(d, inter), rand_w(inter, d))
+        shared = (rand_w(inter, d), rand_w(d, inter), rand_w(inter, d))
+        layers.append(mk.MoeLayer(gw, None, mine, shared, k, ctx=ctx))
+    if args.collective == "peer":
+        eps = [mkd.PeerEpMoeLayer(l, max_tokens=16) for l in layers]
+        fn = lambda i: eps[i % args.copies].forward(x)
+    else:
+        eps = [mkd.EpMoeLayer(l) for l in layers]
+        per = (B + world - 1) // world
+        xl = x[rank * per:(rank + 1) * per].contiguous()
+        fn = lambda i: eps[i % args.copies].forward(xl)
+
+    for i in range(args.warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    st = ctx.status_word()
+    if rank == 0:
+        print(json.dumps({"case": "moe_ep", "collective": args.collective, "n_gpus": world, "experts": E, "top_k": k, "batch": B,
+                          "copies": args.copies, "ms_per_layer": float(t.item()), "tokens_per_s": B / (float(t.item()) * 1e-3),
+                          "status_word": st}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_case_mla(args):
     """Side workload: q8_0 MLA decode attention, 64 heads.  --layout absorbed: one shared
     512+64 latent row per position (648 B with f32 scales); --layout per_head: the engine's
@@ -474,7 +543,7 @@ def run_case_mla(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "mla"],
+    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "moe_ep", "mla"],
                     help="lm_head is the benchmark proper; the others are side workloads for kernel studies")
     ap.add_argument("--rows", type=int, default=7168)
     ap.add_argument("--cols", type=int, default=2048)
@@ -499,6 +568,8 @@ def main():
         run_case_mxfp4(args)
     elif args.case == "moe":
         run_case_moe(args)
+    elif args.case == "moe_ep":
+        run_case_moe_ep(args)
     elif args.case == "mla":
         run_case_mla(args)
     else:

@@ -193,6 +193,42 @@ int32_t mk_matvec_vq1_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float
  * inv = 1 / sqrt(dot(x, x) / len + eps); x, out f32 [n, len], w f32 [len].  Bit-identical. */
 int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, int32_t n, int32_t len, float eps, float *out);
 
+/* ---- KDA decode step (src/model.rs:1066-1228) ----------------------------
+ * The part of kda_forward between its projections and o_proj, one token per call, with the
+ * layer's state resident on the device: the conv windows of q, k, v (kconv - 1 previous raw
+ * inputs each, src/model.rs:1070-1085) and the matrix S [heads][dim][dim] (:1114-1156).
+ * mk_kda_create copies the HOST parameter arrays and zeroes the state (a new sequence). */
+typedef struct mk_kda mk_kda;
+typedef struct {
+    int32_t heads, dim, kconv;                /* cfg.kda_heads, kda_dim (<= 1024), kda_conv (4; 2..16) */
+    float gate_lb, rms_eps;                   /* cfg.gate_lb (-5), cfg.rms_eps */
+    const float *q_conv, *k_conv, *v_conv;    /* [heads * dim][kconv], weight kconv - 1 on the current input */
+    const float *a_log, *dt_bias, *o_norm;    /* [dim], [heads * dim], [dim] */
+} mk_kda_desc;
+int32_t mk_kda_create(mk_ctx *ctx, const mk_kda_desc *desc, mk_kda **out);
+void    mk_kda_free(mk_ctx *ctx, mk_kda *kda);
+int32_t mk_kda_reset(mk_ctx *ctx, mk_kda *kda);   /* zero state: KdaCache::new */
+/* DEVICE f32 inputs: the raw projections q, k, v [heads * dim], g_low = f_b(f_a(x)) [heads * dim],
+ * beta_raw = b_proj(x) [heads] (before the sigmoid), g2 = g_proj(x) [heads * dim].  Does, in the
+ * engine's order: conv + SiLU of q, k, v and the window shift; per-head L2 norm of q (times
+ * dim^-0.5) and k; gate = gate_lb * sigmoid(exp(A_log) * (g_low + dt_bias)); the recurrence
+ * (decay, delta = v - k^T S, S += (beta k) (x) delta, o = q^T S); the gated per-head RMS norm.
+ * o f32 [heads * dim] is the input of o_proj.  Sums keep the engine's order; exp is rounded once
+ * from double precision, so results equal the CPU's except where two correctly-rounded-in-
+ * practice expf differ (tests hold it to 1e-6 relative). */
+int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *kda, const float *q_raw, const float *k_raw, const float *v_raw,
+                        const float *g_low, const float *beta_raw, const float *g2, float *o);
+/* State to / from HOST memory (cache snapshots for speculative rollback, src/spec.rs:214, 294-299;
+ * .mkmem files): s [heads][dim][dim]; conv [3 (q, k, v)][kconv - 1][heads * dim], oldest input first
+ * (the layout of KdaCache::conv_q / conv_k / conv_v). */
+int32_t mk_kda_export(mk_ctx *ctx, mk_kda *kda, float *s, float *conv);
+int32_t mk_kda_import(mk_ctx *ctx, mk_kda *kda, const float *s, const float *conv);
+/* attn_res (src/model.rs:625-669) on DEVICE rows: softmax over the RMS-normed scores of b block
+ * rows (blocks + i * ld, i < b) and the prefix row, output = the probability-weighted sum of the
+ * RAW rows; w = norm.weight * proj.weight; all f32 [d].  Same sum orders as the engine. */
+int32_t mk_attn_res_dev(mk_ctx *ctx, const float *prefix, const float *blocks, int64_t ld, int32_t b, const float *w,
+                        int32_t d, float eps, float *out);
+
 /* ---- vocabulary-sharded lm_head over the GPUs of one node ---------------
  * No counterpart in the reference (a single-process engine).  Rank r registers rows
  * [row0, row0 + rows) of the lm_head (mk_weight_q8_from_f32 on its slice); one call then

@@ -1,0 +1,305 @@
+// KDA decode step and AttnRes on the device (sm_100a).
+//
+// Reference: kda_conv_step, kda_norm_head, kda_gate, kda_recur_step, kda_gated_onorm and the
+// part of kda_forward that strings them together (src/model.rs:1066-1228); attn_res_refs
+// (src/model.rs:632-669).  One token per call; the layer's state (the conv windows of q, k, v
+// and the matrix S [heads][dim][dim]) stays in device memory between calls.
+//
+// Arithmetic: every sum runs in the engine's order with a separate multiply and add, dot()
+// with its 8 accumulators; exp is taken in double precision and rounded once, which gives
+// the bits of a correctly rounded expf in all but about one case in 10^9.
+//
+// kda_step_kernel: one CTA per head, one thread per channel.  The columns of S are
+// independent of one another (decay scales rows, delta[j] and o[j] are sums down column j),
+// so thread j owns column j, reads it once into registers (dim <= 128), walks it in row
+// order for delta, then again for the update and o, and writes it once: 2 * dim^2 * 4 bytes
+// of traffic per head and token, coalesced across the threads of a row.
+#include "f32gemv.cuh"
+#include "mk_common.cuh"
+
+#include <cmath>
+#include <new>
+
+struct mk_kda {
+    int heads, dim, kconv;
+    float gate_lb, rms_eps, q_scale;
+    float *conv_w;   // [3][proj][kconv]  q, k, v
+    float *a_log;    // [dim]
+    float *dt_bias;  // [proj]
+    float *o_norm;   // [dim]
+    float *conv;     // [3][kconv - 1][proj]  previous raw inputs, oldest first
+    float *s;        // [heads][dim][dim]
+};
+
+namespace {
+__device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x); }
+__device__ __forceinline__ float sigmoid_cr(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_cr(-x))); }
+
+// dot(a, a) over n values in shared memory, by one whole warp, in the engine's order; the result in every lane
+__device__ __forceinline__ float warp_sumsq(const float *a, int n, int lane) {
+    const int j = lane & 7, full = n & ~7;
+    float acc = 0.0f;
+    for (int c = 0; c < full; c += 8) acc = __fadd_rn(acc, __fmul_rn(a[c + j], a[c + j]));
+    float ss = mkf::reduce8(acc, lane);
+    for (int c = full; c < n; ++c) ss = __fadd_rn(ss, __fmul_rn(a[c], a[c]));
+    return ss;
+}
+
+struct KdaArgs {
+    const float *q_raw, *k_raw, *v_raw, *g_low, *beta_raw, *g2;
+    const float *conv_w, *a_log, *dt_bias, *o_norm;
+    float *conv, *s, *o;
+    int heads, dim, kconv;
+    float gate_lb, rms_eps, q_scale;
+};
+
+// depthwise causal conv + SiLU of channel i; shifts the channel's window (no other thread touches it)
+__device__ __forceinline__ float conv_channel(const float *w, float *win, int64_t proj, int64_t i, int kconv, float raw) {
+    float acc = 0.0f;
+    for (int j = 0; j < kconv - 1; ++j) {
+        const float old = win[(int64_t)j * proj + i];
+        acc = __fadd_rn(acc, __fmul_rn(w[i * kconv + j], old));
+        if (j > 0) win[(int64_t)(j - 1) * proj + i] = old;
+    }
+    win[(int64_t)(kconv - 2) * proj + i] = raw;
+    acc = __fadd_rn(acc, __fmul_rn(w[i * kconv + kconv - 1], raw));
+    return __fmul_rn(acc, sigmoid_cr(acc));
+}
+
+// DIM > 0: the column lives in registers; DIM == 0: any dim, the decayed column is parked in S between the passes
+template <int DIM>
+__global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs a) {
+    extern __shared__ float sm[];
+    const int dim = DIM > 0 ? DIM : a.dim;
+    float *qs = sm, *ks = sm + dim, *ds = sm + 2 * dim, *red = sm + 3 * dim;
+    const int h = blockIdx.x, c = threadIdx.x, lane = c & 31, warp = c >> 5, nwarps = blockDim.x >> 5;
+    const bool active = c < dim;
+    const int64_t proj = (int64_t)a.heads * dim, i = (int64_t)h * dim + c;
+    float vv = 0.0f;
+    if (active) {
+        qs[c] = conv_channel(a.conv_w, a.conv, proj, i, a.kconv, a.q_raw[i]);
+        ks[c] = conv_channel(a.conv_w + proj * a.kconv, a.conv + (int64_t)(a.kconv - 1) * proj, proj, i, a.kconv, a.k_raw[i]);
+        vv = conv_channel(a.conv_w + 2 * proj * a.kconv, a.conv + 2 * (int64_t)(a.kconv - 1) * proj, proj, i, a.kconv, a.v_raw[i]);
+        const float g = __fmul_rn(a.gate_lb, sigmoid_cr(__fmul_rn(exp_cr(a.a_log[c]), __fadd_rn(a.g_low[i], a.dt_bias[i]))));
+        ds[c] = exp_cr(g);
+    }
+    __syncthreads();
+    // per-head L2 norms: q by warp 0, k by the last warp (the same warp when there is one)
+    if (warp == 0) {
+        const float n2 = warp_sumsq(qs, dim, lane);
+        if (lane == 0) red[0] = __fdiv_rn(a.q_scale, fmaxf(__fsqrt_rn(n2), 1e-12f));
+    }
+    if (warp == nwarps - 1) {
+        const float n2 = warp_sumsq(ks, dim, lane);
+        if (lane == 0) red[1] = __fdiv_rn(1.0f, fmaxf(__fsqrt_rn(n2), 1e-12f));
+    }
+    __syncthreads();
+    if (active) {
+        qs[c] = __fmul_rn(qs[c], red[0]);
+        ks[c] = __fmul_rn(ks[c], red[1]);
+    }
+    __syncthreads();
+    float o = 0.0f;
+    if (active) {
+        const float bh = sigmoid_cr(a.beta_raw[h]);
+        float *col = a.s + (int64_t)h * dim * dim + c;
+        float delta = vv;
+        if constexpr (DIM > 0) {
+            float x[DIM];
+#pragma unroll
+            for (int r = 0; r < DIM; ++r) x[r] = col[(int64_t)r * DIM];
+#pragma unroll
+            for (int r = 0; r < DIM; ++r) {
+                x[r] = __fmul_rn(x[r], ds[r]);
+                delta = __fsub_rn(delta, __fmul_rn(ks[r], x[r]));
+            }
+#pragma unroll
+            for (int r = 0; r < DIM; ++r) {
+                x[r] = __fadd_rn(x[r], __fmul_rn(__fmul_rn(bh, ks[r]), delta));
+                o = __fadd_rn(o, __fmul_rn(qs[r], x[r]));
+                col[(int64_t)r * DIM] = x[r];
+            }
+        } else {
+            for (int r = 0; r < dim; ++r) {
+                const float x = __fmul_rn(col[(int64_t)r * dim], ds[r]);
+                col[(int64_t)r * dim] = x;
+                delta = __fsub_rn(delta, __fmul_rn(ks[r], x));
+            }
+            for (int r = 0; r < dim; ++r) {
+                const float x = __fadd_rn(col[(int64_t)r * dim], __fmul_rn(__fmul_rn(bh, ks[r]), delta));
+                o = __fadd_rn(o, __fmul_rn(qs[r], x));
+                col[(int64_t)r * dim] = x;
+            }
+        }
+    }
+    __syncthreads();            // qs is free: it now holds o for the head's RMS
+    if (active) qs[c] = o;
+    __syncthreads();
+    if (warp == 0) {
+        const float ss = __fdiv_rn(warp_sumsq(qs, dim, lane), (float)dim);
+        if (lane == 0) red[2] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ss, a.rms_eps)));
+    }
+    __syncthreads();
+    if (active) a.o[i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), a.o_norm[c]), sigmoid_cr(a.g2[i]));
+}
+
+// ---- AttnRes: scores (one warp per row: blocks 0..b-1, then the prefix), then softmax + mix
+__global__ void __launch_bounds__(32) attn_res_score_kernel(const float *__restrict__ prefix, const float *__restrict__ blocks,
+                                                           int64_t ld, int b, const float *__restrict__ w, int d, float eps,
+                                                           float *__restrict__ scores) {
+    const int row = blockIdx.x, lane = threadIdx.x, j = lane & 7, full = d & ~7;
+    const float *v = row < b ? blocks + (int64_t)row * ld : prefix;
+    float acc = 0.0f;
+    for (int c = 0; c < full; c += 8) acc = __fadd_rn(acc, __fmul_rn(v[c + j], v[c + j]));
+    float ss = mkf::reduce8(acc, lane);
+    for (int c = full; c < d; ++c) ss = __fadd_rn(ss, __fmul_rn(v[c], v[c]));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)d), eps)));
+    acc = 0.0f;
+    for (int c = 0; c < full; c += 8) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(v[c + j], inv), w[c + j]));
+    float sc = mkf::reduce8(acc, lane);
+    for (int c = full; c < d; ++c) sc = __fadd_rn(sc, __fmul_rn(__fmul_rn(v[c], inv), w[c]));
+    if (lane == 0) scores[row] = sc;
+}
+__global__ void __launch_bounds__(256) attn_res_mix_kernel(const float *__restrict__ prefix, const float *__restrict__ blocks, int64_t ld,
+                                                          int b, int d, const float *__restrict__ scores, float *__restrict__ out) {
+    extern __shared__ float p[]; // b + 1 probabilities
+    if (threadIdx.x == 0) {      // the engine's sequential softmax (b + 1 is a handful of values)
+        float m = -INFINITY;
+        for (int i = 0; i <= b; ++i) m = fmaxf(m, scores[i]);
+        float z = 0.0f;
+        for (int i = 0; i <= b; ++i) {
+            p[i] = exp_cr(__fsub_rn(scores[i], m));
+            z = __fadd_rn(z, p[i]);
+        }
+        for (int i = 0; i <= b; ++i) p[i] = __fdiv_rn(p[i], z);
+    }
+    __syncthreads();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= d) return;
+    float o = 0.0f;
+    for (int i = 0; i < b; ++i) o = __fadd_rn(o, __fmul_rn(p[i], blocks[(int64_t)i * ld + j]));
+    out[j] = __fadd_rn(o, __fmul_rn(p[b], prefix[j]));
+}
+} // namespace
+
+// ====================================================================== C ABI
+extern "C" int32_t mk_kda_create(mk_ctx *ctx, const mk_kda_desc *d, mk_kda **out) {
+    MK_CHECK_ARG(ctx != nullptr && d != nullptr && out != nullptr, "NULL argument");
+    *out = nullptr;
+    MK_CHECK_ARG(d->heads >= 1 && d->dim >= 1 && d->dim <= 1024 && d->kconv >= 2 && d->kconv <= 16,
+                 "heads >= 1, dim in [1, 1024] and kconv in [2, 16] required");
+    MK_CHECK_ARG(d->q_conv && d->k_conv && d->v_conv && d->a_log && d->dt_bias && d->o_norm, "NULL parameter array");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    mk_kda *k = new (std::nothrow) mk_kda();
+    if (!k) return MK_ERR_OOM;
+    memset(k, 0, sizeof(*k));
+    k->heads = d->heads;
+    k->dim = d->dim;
+    k->kconv = d->kconv;
+    k->gate_lb = d->gate_lb;
+    k->rms_eps = d->rms_eps;
+    k->q_scale = powf((float)d->dim, -0.5f); // (kda_dim as f32).powf(-0.5), src/model.rs:1216
+    const size_t proj = (size_t)d->heads * d->dim, cw = proj * d->kconv * 4;
+    const size_t win = (size_t)(d->kconv - 1) * proj * 4, sb = (size_t)d->heads * d->dim * d->dim * 4;
+    cudaError_t e = cudaMalloc(&k->conv_w, 3 * cw);
+    if (e == cudaSuccess) e = cudaMalloc(&k->a_log, (size_t)d->dim * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&k->dt_bias, proj * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&k->o_norm, (size_t)d->dim * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&k->conv, 3 * win + 16);
+    if (e == cudaSuccess) e = cudaMalloc(&k->s, sb);
+    const float *cws[3] = {d->q_conv, d->k_conv, d->v_conv};
+    for (int t = 0; t < 3 && e == cudaSuccess; ++t)
+        e = cudaMemcpyAsync((char *)k->conv_w + t * cw, cws[t], cw, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(k->a_log, d->a_log, (size_t)d->dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(k->dt_bias, d->dt_bias, proj * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(k->o_norm, d->o_norm, (size_t)d->dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(k->conv, 0, 3 * win + 16, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(k->s, 0, sb, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        mk_set_error("mk_kda_create: %s", cudaGetErrorString(e));
+        mk_kda_free(ctx, k);
+        return e == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA;
+    }
+    *out = k;
+    return MK_OK;
+}
+
+extern "C" void mk_kda_free(mk_ctx *ctx, mk_kda *k) {
+    if (!k) return;
+    if (ctx) cudaSetDevice(ctx->device);
+    float *bufs[6] = {k->conv_w, k->a_log, k->dt_bias, k->o_norm, k->conv, k->s};
+    for (float *b : bufs)
+        if (b) cudaFree(b);
+    delete k;
+}
+
+extern "C" int32_t mk_kda_reset(mk_ctx *ctx, mk_kda *k) {
+    MK_CHECK_ARG(ctx != nullptr && k != nullptr, "NULL argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const size_t proj = (size_t)k->heads * k->dim;
+    MK_CUDA(cudaMemsetAsync(k->conv, 0, 3 * (size_t)(k->kconv - 1) * proj * 4 + 16, ctx->stream));
+    MK_CUDA(cudaMemsetAsync(k->s, 0, (size_t)k->heads * k->dim * k->dim * 4, ctx->stream));
+    return MK_OK;
+}
+
+// direction 0: device -> host (export), 1: host -> device (import)
+static int32_t kda_state_copy(mk_ctx *ctx, mk_kda *k, float *s, float *conv, int to_device) {
+    MK_CHECK_ARG(ctx != nullptr && k != nullptr && s != nullptr && conv != nullptr, "NULL argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const size_t proj = (size_t)k->heads * k->dim, win = 3 * (size_t)(k->kconv - 1) * proj * 4;
+    const size_t sb = (size_t)k->heads * k->dim * k->dim * 4;
+    if (to_device) {
+        MK_CUDA(cudaMemcpyAsync(k->s, s, sb, cudaMemcpyHostToDevice, ctx->stream));
+        if (win) MK_CUDA(cudaMemcpyAsync(k->conv, conv, win, cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+        MK_CUDA(cudaMemcpyAsync(s, k->s, sb, cudaMemcpyDeviceToHost, ctx->stream));
+        if (win) MK_CUDA(cudaMemcpyAsync(conv, k->conv, win, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+extern "C" int32_t mk_kda_export(mk_ctx *ctx, mk_kda *k, float *s, float *conv) { return kda_state_copy(ctx, k, s, conv, 0); }
+extern "C" int32_t mk_kda_import(mk_ctx *ctx, mk_kda *k, const float *s, const float *conv) {
+    return kda_state_copy(ctx, k, const_cast<float *>(s), const_cast<float *>(conv), 1);
+}
+
+extern "C" int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *k, const float *q_raw, const float *k_raw, const float *v_raw,
+                                   const float *g_low, const float *beta_raw, const float *g2, float *o) {
+    MK_CHECK_ARG(ctx != nullptr && k != nullptr, "NULL argument");
+    MK_CHECK_ARG(q_raw && k_raw && v_raw && g_low && beta_raw && g2 && o, "NULL device pointer");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    KdaArgs a;
+    a.q_raw = q_raw; a.k_raw = k_raw; a.v_raw = v_raw; a.g_low = g_low; a.beta_raw = beta_raw; a.g2 = g2;
+    a.conv_w = k->conv_w; a.a_log = k->a_log; a.dt_bias = k->dt_bias; a.o_norm = k->o_norm;
+    a.conv = k->conv; a.s = k->s; a.o = o;
+    a.heads = k->heads; a.dim = k->dim; a.kconv = k->kconv;
+    a.gate_lb = k->gate_lb; a.rms_eps = k->rms_eps; a.q_scale = k->q_scale;
+    const size_t smem = (size_t)(3 * k->dim + 4) * sizeof(float);
+    mk_prof_scope prof(ctx, MK_PROF_OTHER);
+    if (k->dim == 128)
+        kda_step_kernel<128><<<k->heads, 128, smem, ctx->stream>>>(a);
+    else if (k->dim == 64)
+        kda_step_kernel<64><<<k->heads, 64, smem, ctx->stream>>>(a);
+    else
+        kda_step_kernel<0><<<k->heads, (unsigned)mk_align_up(k->dim, 32), smem, ctx->stream>>>(a);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+extern "C" int32_t mk_attn_res_dev(mk_ctx *ctx, const float *prefix, const float *blocks, int64_t ld, int32_t b, const float *w,
+                                   int32_t d, float eps, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && prefix != nullptr && w != nullptr && out != nullptr, "NULL argument");
+    MK_CHECK_ARG(b >= 0 && b <= 4095 && d >= 1 && (b == 0 || (blocks != nullptr && ld >= d)), "0 <= b <= 4095, d >= 1, ld >= d required");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = mk_ws_reserve(ctx, (size_t)(b + 1) * 4);
+    if (rc != MK_OK) return rc;
+    float *scores = (float *)ctx->ws;
+    mk_prof_scope prof(ctx, MK_PROF_OTHER);
+    attn_res_score_kernel<<<b + 1, 32, 0, ctx->stream>>>(prefix, blocks, ld, b, w, d, eps, scores);
+    attn_res_mix_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, (size_t)(b + 1) * 4, ctx->stream>>>(prefix, blocks, ld, b, d, scores, out);
+    ctx->launches += 2;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}

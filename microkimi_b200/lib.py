@@ -33,6 +33,12 @@ _vp = C.c_void_p
 _i32 = C.c_int32
 _i64 = C.c_int64
 
+class KdaDesc(C.Structure):
+    """mk_kda_desc"""
+    _fields_ = [("heads", _i32), ("dim", _i32), ("kconv", _i32), ("gate_lb", C.c_float), ("rms_eps", C.c_float),
+                ("q_conv", _vp), ("k_conv", _vp), ("v_conv", _vp), ("a_log", _vp), ("dt_bias", _vp), ("o_norm", _vp)]
+
+
 class MoeDesc(C.Structure):
     """mk_moe_desc"""
     _fields_ = [("n_experts", _i32), ("top_k", _i32), ("d", _i32), ("inter", _i32),
@@ -84,6 +90,13 @@ SIGNATURES = {
     "mk_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _i32]),
     "mk_matvec_f32_dev": (_i32, [_vp, _vp, _vp, _vp, _i32]),
     "mk_rmsnorm_dev": (_i32, [_vp, _vp, _vp, _i32, _i32, C.c_float, _vp]),
+    "mk_kda_create": (_i32, [_vp, C.POINTER(KdaDesc), C.POINTER(_vp)]),
+    "mk_kda_free": (None, [_vp, _vp]),
+    "mk_kda_reset": (_i32, [_vp, _vp]),
+    "mk_kda_step_dev": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mk_kda_export": (_i32, [_vp, _vp, _vp, _vp]),
+    "mk_kda_import": (_i32, [_vp, _vp, _vp, _vp]),
+    "mk_attn_res_dev": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _i32, C.c_float, _vp]),
     "mk_matvec_mxfp4_noalloc_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_q8": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_matvec_q8_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),

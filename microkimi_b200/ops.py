@@ -266,6 +266,77 @@ def rmsnorm(x, w, eps, ctx=None):
     return out
 
 
+def attn_res(prefix, blocks, w, eps, ctx=None):
+    """attn_res (src/model.rs:625-669) on torch CUDA rows: prefix [d], blocks [b, d] (b may be 0), w [d] -> [d]."""
+    import torch
+    ctx = ctx or Context.default()
+    assert all(_is_torch_cuda(t) and t.dtype == torch.float32 and t.is_contiguous() for t in (prefix, blocks, w))
+    d = prefix.numel()
+    b = blocks.shape[0] if blocks.numel() else 0
+    assert w.numel() == d and (b == 0 or blocks.shape[1] == d)
+    out = torch.empty_like(prefix)
+    _l.check(ctx._L.mk_attn_res_dev(ctx._h, C.c_void_p(prefix.data_ptr()), C.c_void_p(blocks.data_ptr()) if b else None, d, b,
+                                    C.c_void_p(w.data_ptr()), d, float(eps), C.c_void_p(out.data_ptr())))
+    return out
+
+
+class KdaLayer:
+    """The device-resident state of one KDA layer (KdaCache, src/model.rs) and the decode step between the
+    projections and o_proj (kda_forward, src/model.rs:1203-1228).  Parameter arrays are host float32."""
+
+    def __init__(self, heads, dim, q_conv, k_conv, v_conv, a_log, dt_bias, o_norm, kconv=4, gate_lb=-5.0, rms_eps=1e-6, ctx=None):
+        self.ctx = ctx or Context.default()
+        self.heads, self.dim, self.kconv = int(heads), int(dim), int(kconv)
+        keep = [np.ascontiguousarray(a, dtype=np.float32) for a in (q_conv, k_conv, v_conv, a_log, dt_bias, o_norm)]
+        proj = self.heads * self.dim
+        assert all(a.size == proj * self.kconv for a in keep[:3]) and keep[3].size == self.dim
+        assert keep[4].size == proj and keep[5].size == self.dim
+        d = _l.KdaDesc()
+        d.heads, d.dim, d.kconv, d.gate_lb, d.rms_eps = self.heads, self.dim, self.kconv, float(gate_lb), float(rms_eps)
+        d.q_conv, d.k_conv, d.v_conv, d.a_log, d.dt_bias, d.o_norm = (a.ctypes.data for a in keep)
+        h = C.c_void_p()
+        _l.check(self.ctx._L.mk_kda_create(self.ctx._h, C.byref(d), C.byref(h)))
+        self._h = h
+
+    def step(self, q_raw, k_raw, v_raw, g_low, beta_raw, g2):
+        """torch CUDA float32 vectors (q, k, v, g_low, g2 [heads * dim]; beta_raw [heads]) -> o [heads * dim]."""
+        import torch
+        ins = (q_raw, k_raw, v_raw, g_low, beta_raw, g2)
+        assert all(_is_torch_cuda(t) and t.dtype == torch.float32 and t.is_contiguous() for t in ins)
+        proj = self.heads * self.dim
+        assert all(t.numel() == proj for t in (q_raw, k_raw, v_raw, g_low, g2)) and beta_raw.numel() == self.heads
+        o = torch.empty(proj, dtype=torch.float32, device=q_raw.device)
+        _l.check(self.ctx._L.mk_kda_step_dev(self.ctx._h, self._h, *(C.c_void_p(t.data_ptr()) for t in ins), C.c_void_p(o.data_ptr())))
+        return o
+
+    def reset(self):
+        _l.check(self.ctx._L.mk_kda_reset(self.ctx._h, self._h))
+
+    def export_state(self):
+        """(S [heads, dim, dim], conv [3, kconv - 1, heads * dim]) as host arrays."""
+        s = np.empty((self.heads, self.dim, self.dim), np.float32)
+        conv = np.empty((3, max(self.kconv - 1, 0), self.heads * self.dim), np.float32)
+        _l.check(self.ctx._L.mk_kda_export(self.ctx._h, self._h, _np_ptr(s), C.c_void_p(conv.ctypes.data)))
+        return s, conv
+
+    def import_state(self, s, conv):
+        s = np.ascontiguousarray(s, dtype=np.float32)
+        conv = np.ascontiguousarray(conv, dtype=np.float32)
+        assert s.size == self.heads * self.dim * self.dim and conv.size == 3 * (self.kconv - 1) * self.heads * self.dim
+        _l.check(self.ctx._L.mk_kda_import(self.ctx._h, self._h, _np_ptr(s), C.c_void_p(conv.ctypes.data)))
+
+    def free(self):
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._L.mk_kda_free(self.ctx._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 def matvec_packed(packed, scales, rows, cols, x, act="q8", strict=False, ctx=None):
     """Drop-in for mxfp4::matvec_packed / metal::gpu_matvec_fp4 with borrowed host
     slices: registers the matrix, multiplies, frees.  Callers that reuse a matrix

@@ -388,6 +388,155 @@ void or_q8head_matvec(const int8_t *q, const float *scales, size_t rows, size_t 
     free(xs);
 }
 
+/* ------------------------------------------------------------------ KDA decode step, AttnRes */
+static float or_silu(float x) { return x * or_sigmoid(x); } /* model.rs:612-615 */
+
+void or_kda_conv_step(size_t proj, size_t kconv, const float *w_conv, float *vec, float *cache_raw) { /* model.rs:1070-1085 */
+    float *out = (float *)malloc(sizeof(float) * proj);
+    size_t prev = kconv - 1;
+    for (size_t c = 0; c < proj; ++c) {
+        float acc = 0.0f;
+        for (size_t j = 0; j < prev; ++j) acc += w_conv[c * kconv + j] * cache_raw[j * proj + c];
+        acc += w_conv[c * kconv + prev] * vec[c];
+        out[c] = or_silu(acc);
+    }
+    memmove(cache_raw, cache_raw + proj, sizeof(float) * (prev - 1) * proj);
+    memcpy(cache_raw + (prev - 1) * proj, vec, sizeof(float) * proj);
+    memcpy(vec, out, sizeof(float) * proj);
+    free(out);
+}
+void or_kda_norm_head(size_t heads, size_t dim, float *vec, float scale) { /* model.rs:1088-1097 */
+    for (size_t h = 0; h < heads; ++h) {
+        float *head = vec + h * dim;
+        float n2 = or_dot(head, head, dim);
+        float inv = scale / fmaxf(sqrtf(n2), 1e-12f);
+        for (size_t i = 0; i < dim; ++i) head[i] *= inv;
+    }
+}
+void or_kda_gate(size_t heads, size_t dim, float gate_lb, const float *a_log, const float *dt_bias, const float *g_low, float *g) {
+    for (size_t h = 0; h < heads; ++h) /* model.rs:1100-1109 */
+        for (size_t c = 0; c < dim; ++c) {
+            size_t i = h * dim + c;
+            g[i] = gate_lb * or_sigmoid(expf(a_log[c]) * (g_low[i] + dt_bias[i]));
+        }
+}
+void or_kda_recur_step(size_t heads, size_t dim, float *s, const float *q, const float *k, const float *v, const float *g,
+                       const float *beta, float *o) { /* model.rs:1114-1156 */
+    float *delta = (float *)malloc(sizeof(float) * dim);
+    for (size_t h = 0; h < heads; ++h) {
+        float *sh = s + h * dim * dim;
+        const float *gh = g + h * dim, *kh = k + h * dim, *vh = v + h * dim, *qh = q + h * dim;
+        for (size_t i = 0; i < dim; ++i) {
+            float decay = expf(gh[i]);
+            for (size_t j = 0; j < dim; ++j) sh[i * dim + j] *= decay;
+        }
+        memcpy(delta, vh, sizeof(float) * dim);
+        for (size_t i = 0; i < dim; ++i)
+            for (size_t j = 0; j < dim; ++j) delta[j] -= kh[i] * sh[i * dim + j];
+        float bh = beta[h];
+        float *oh = o + h * dim;
+        for (size_t j = 0; j < dim; ++j) oh[j] = 0.0f;
+        for (size_t i = 0; i < dim; ++i) {
+            float bk = bh * kh[i], qi = qh[i];
+            for (size_t j = 0; j < dim; ++j) sh[i * dim + j] += bk * delta[j];
+            for (size_t j = 0; j < dim; ++j) oh[j] += qi * sh[i * dim + j];
+        }
+    }
+    free(delta);
+}
+void or_kda_gated_onorm(size_t heads, size_t dim, float eps, float *o, const float *o_norm, const float *g2) { /* model.rs:1167-1176 */
+    for (size_t h = 0; h < heads; ++h) {
+        float *oh = o + h * dim;
+        float ss = or_dot(oh, oh, dim) / (float)dim;
+        float inv = 1.0f / sqrtf(ss + eps);
+        for (size_t c = 0; c < dim; ++c) oh[c] = oh[c] * inv * o_norm[c] * or_sigmoid(g2[h * dim + c]);
+    }
+}
+void or_kda_step(const or_kda_desc *d, float *conv_q, float *conv_k, float *conv_v, float *s, const float *q_raw,
+                 const float *k_raw, const float *v_raw, const float *g_low, const float *beta_raw, const float *g2, float *o) {
+    size_t proj = d->heads * d->dim; /* model.rs:1203-1228 */
+    float *q = (float *)malloc(sizeof(float) * proj), *k = (float *)malloc(sizeof(float) * proj);
+    float *v = (float *)malloc(sizeof(float) * proj), *g = (float *)malloc(sizeof(float) * proj);
+    float *beta = (float *)malloc(sizeof(float) * d->heads);
+    memcpy(q, q_raw, sizeof(float) * proj);
+    memcpy(k, k_raw, sizeof(float) * proj);
+    memcpy(v, v_raw, sizeof(float) * proj);
+    for (size_t h = 0; h < d->heads; ++h) beta[h] = or_sigmoid(beta_raw[h]);
+    or_kda_conv_step(proj, d->kconv, d->q_conv, q, conv_q);
+    or_kda_conv_step(proj, d->kconv, d->k_conv, k, conv_k);
+    or_kda_conv_step(proj, d->kconv, d->v_conv, v, conv_v);
+    or_kda_norm_head(d->heads, d->dim, q, powf((float)d->dim, -0.5f));
+    or_kda_norm_head(d->heads, d->dim, k, 1.0f);
+    or_kda_gate(d->heads, d->dim, d->gate_lb, d->a_log, d->dt_bias, g_low, g);
+    or_kda_recur_step(d->heads, d->dim, s, q, k, v, g, beta, o);
+    or_kda_gated_onorm(d->heads, d->dim, d->rms_eps, o, d->o_norm, g2);
+    free(q); free(k); free(v); free(g); free(beta);
+}
+void or_kda_core(const float *q, const float *k, const float *v, const float *g, const float *beta, const float *a_log,
+                 const float *dt_bias, size_t t_steps, size_t heads, size_t dim, float *o, float *s) { /* selftest.rs:48-113 */
+    float scale = powf((float)dim, -0.5f);
+    float *qn = (float *)malloc(sizeof(float) * dim), *kn = (float *)malloc(sizeof(float) * dim);
+    float *gg = (float *)malloc(sizeof(float) * dim), *delta = (float *)malloc(sizeof(float) * dim);
+    memset(s, 0, sizeof(float) * heads * dim * dim);
+    for (size_t t = 0; t < t_steps; ++t)
+        for (size_t h = 0; h < heads; ++h) {
+            size_t base = (t * heads + h) * dim;
+            const float *qh = q + base, *kh = k + base, *vh = v + base, *gh = g + base;
+            float bh = 1.0f / (1.0f + expf(-beta[t * heads + h]));
+            float nq = 0.0f, nk = 0.0f;
+            for (size_t i = 0; i < dim; ++i) nq += qh[i] * qh[i];
+            for (size_t i = 0; i < dim; ++i) nk += kh[i] * kh[i];
+            nq = fmaxf(sqrtf(nq), 1e-12f);
+            nk = fmaxf(sqrtf(nk), 1e-12f);
+            for (size_t i = 0; i < dim; ++i) qn[i] = qh[i] / nq * scale;
+            for (size_t i = 0; i < dim; ++i) kn[i] = kh[i] / nk;
+            for (size_t c = 0; c < dim; ++c) {
+                float a = expf(a_log[c]), x = gh[c] + dt_bias[h * dim + c];
+                gg[c] = -5.0f / (1.0f + expf(-a * x));
+            }
+            float *sh = s + h * dim * dim;
+            for (size_t i = 0; i < dim; ++i) {
+                float decay = expf(gg[i]);
+                for (size_t j = 0; j < dim; ++j) sh[i * dim + j] *= decay;
+            }
+            memcpy(delta, vh, sizeof(float) * dim);
+            for (size_t i = 0; i < dim; ++i)
+                for (size_t j = 0; j < dim; ++j) delta[j] -= kn[i] * sh[i * dim + j];
+            float *oh = o + base;
+            for (size_t j = 0; j < dim; ++j) oh[j] = 0.0f;
+            for (size_t i = 0; i < dim; ++i) {
+                float bk = bh * kn[i];
+                for (size_t j = 0; j < dim; ++j) sh[i * dim + j] += bk * delta[j];
+                for (size_t j = 0; j < dim; ++j) oh[j] += qn[i] * sh[i * dim + j];
+            }
+        }
+    free(qn); free(kn); free(gg); free(delta);
+}
+void or_attn_res(size_t d, float eps, const float *prefix, const float *blocks, size_t b, const float *w, float *out) {
+    float *scores = (float *)malloc(sizeof(float) * (b + 1)); /* model.rs:632-669 */
+    float *kbuf = (float *)malloc(sizeof(float) * d);
+    for (size_t i = 0; i <= b; ++i) {
+        const float *v = i < b ? blocks + i * d : prefix;
+        float ss = or_dot(v, v, d) / (float)d;
+        float inv = 1.0f / sqrtf(ss + eps);
+        for (size_t j = 0; j < d; ++j) kbuf[j] = v[j] * inv;
+        scores[i] = or_dot(kbuf, w, d);
+    }
+    float m = -INFINITY;
+    for (size_t i = 0; i <= b; ++i) m = fmaxf(m, scores[i]);
+    float z = 0.0f;
+    for (size_t i = 0; i <= b; ++i) {
+        scores[i] = expf(scores[i] - m);
+        z += scores[i];
+    }
+    for (size_t i = 0; i <= b; ++i) scores[i] /= z;
+    for (size_t j = 0; j < d; ++j) out[j] = 0.0f;
+    for (size_t i = 0; i < b; ++i)
+        for (size_t j = 0; j < d; ++j) out[j] += scores[i] * blocks[i * d + j];
+    for (size_t j = 0; j < d; ++j) out[j] += scores[b] * prefix[j];
+    free(scores); free(kbuf);
+}
+
 uint16_t or_f32_to_f16(float f) {
     uint32_t x = f32_bits(f);
     uint32_t sign = (x >> 16) & 0x8000u;

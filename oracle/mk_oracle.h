@@ -177,6 +177,29 @@ void or_mla_abs_attn_f64(const or_mla_abs_cache *c, const float *q, size_t nh,
                          size_t pos, float scale, double *out);
 
 /* IEEE half helpers (round-to-nearest-even), used only by the f16-scale variant */
+/* ---- KDA decode step and AttnRes (src/model.rs:1066-1177, 625-669; src/selftest.rs:48-113) ---- */
+/* conv window: kconv - 1 previous raw inputs [j][proj] (oldest first); vec is replaced by silu(conv) */
+void or_kda_conv_step(size_t proj, size_t kconv, const float *w_conv /* [proj][kconv] */, float *vec, float *cache_raw); /* :1070-1085 */
+void or_kda_norm_head(size_t heads, size_t dim, float *vec, float scale);                                             /* :1088-1097 */
+void or_kda_gate(size_t heads, size_t dim, float gate_lb, const float *a_log, const float *dt_bias, const float *g_low, float *g); /* :1100-1109 */
+void or_kda_recur_step(size_t heads, size_t dim, float *s, const float *q, const float *k, const float *v, const float *g,
+                       const float *beta, float *o);                                                                  /* :1114-1156 */
+void or_kda_gated_onorm(size_t heads, size_t dim, float eps, float *o, const float *o_norm, const float *g2);         /* :1167-1176 */
+/* kda_forward between its projections and o_proj (:1203-1228): raw q, k, v, g_low, beta, g2 in; o [heads*dim] out */
+typedef struct {
+    size_t heads, dim, kconv;
+    float gate_lb, rms_eps;
+    const float *q_conv, *k_conv, *v_conv; /* [heads*dim][kconv] */
+    const float *a_log, *dt_bias, *o_norm; /* [dim], [heads*dim], [dim] */
+} or_kda_desc;
+void or_kda_step(const or_kda_desc *d, float *conv_q, float *conv_k, float *conv_v /* [(kconv-1)][proj] each */, float *s,
+                 const float *q_raw, const float *k_raw, const float *v_raw, const float *g_low, const float *beta_raw,
+                 const float *g2, float *o);
+/* the selftest's standalone recurrence on raw inputs (selftest.rs:48-113): o [T][H][dim], s [H][dim][dim] (zeroed here) */
+void or_kda_core(const float *q, const float *k, const float *v, const float *g, const float *beta, const float *a_log,
+                 const float *dt_bias, size_t t_steps, size_t heads, size_t dim, float *o, float *s);
+void or_attn_res(size_t d, float eps, const float *prefix, const float *blocks /* [b][d] */, size_t b, const float *w, float *out); /* :632-669 */
+
 uint16_t or_f32_to_f16(float f);
 float    or_f16_to_f32(uint16_t h);
 

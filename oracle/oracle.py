@@ -55,6 +55,11 @@ class _MoeDesc(C.Structure):
                 ("sh_packed", _u8p * 3), ("sh_scales", _u8p * 3)]
 
 
+class _KdaDesc(C.Structure):
+    _fields_ = [("heads", _sz), ("dim", _sz), ("kconv", _sz), ("gate_lb", C.c_float), ("rms_eps", C.c_float),
+                ("q_conv", _f32p), ("k_conv", _f32p), ("v_conv", _f32p), ("a_log", _f32p), ("dt_bias", _f32p), ("o_norm", _f32p)]
+
+
 class _MoeK3Desc(C.Structure):
     _fields_ = [("d", _sz), ("rh", _sz), ("inter", _sz), ("n_experts", _sz), ("top_k", _sz), ("shared_inter", _sz),
                 ("rms_eps", C.c_float), ("use_q8", C.c_int),
@@ -100,6 +105,12 @@ def _declare(L):
     sig("or_matvec_vq_gather", None, _f32p, _u8p, _sz, _sz, _f32p, _f32p)
     sig("or_matvec_vq_lut", None, _f32p, _u8p, _sz, _sz, _f32p, _f32p)
     sig("or_moe_k3_forward", None, C.POINTER(_MoeK3Desc), _f32p, _f32p, _i32p, _f32p)
+    sig("or_kda_step", None, C.POINTER(_KdaDesc), _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p)
+    sig("or_kda_core", None, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _f32p, _f32p)
+    sig("or_kda_recur_step", None, _sz, _sz, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p)
+    sig("or_kda_norm_head", None, _sz, _sz, _f32p, C.c_float)
+    sig("or_kda_gate", None, _sz, _sz, C.c_float, _f32p, _f32p, _f32p, _f32p)
+    sig("or_attn_res", None, _sz, C.c_float, _f32p, _f32p, _sz, _f32p, _f32p)
     sig("or_mla_new", C.c_void_p, _sz, _sz, _sz, _sz, _sz)
     sig("or_mla_free", None, C.c_void_p)
     sig("or_mla_push", None, C.c_void_p, _f32p, _f32p)
@@ -352,6 +363,67 @@ class MoeDs:
         w = np.empty(self.top_k, np.float32)
         lib().or_moe_ds_forward(C.byref(d), _p(x, _f32p), _p(out, _f32p), _p(ids, _i32p), _p(w, _f32p), n_threads)
         return out, ids, w
+
+
+class KdaLayer:
+    """The KDA decode step between the projections and o_proj (model.rs:1203-1228): holds the conv windows
+    (kconv - 1 previous raw inputs of q, k, v) and the recurrent state S [heads, dim, dim]."""
+
+    def __init__(self, heads, dim, q_conv, k_conv, v_conv, a_log, dt_bias, o_norm, kconv=4, gate_lb=-5.0, rms_eps=1e-6):
+        self.heads, self.dim, self.kconv, self.gate_lb, self.rms_eps = heads, dim, kconv, float(gate_lb), float(rms_eps)
+        self.w = [_c(a, np.float32) for a in (q_conv, k_conv, v_conv, a_log, dt_bias, o_norm)]
+        proj = heads * dim
+        self.conv = [np.zeros((kconv - 1, proj), np.float32) for _ in range(3)]
+        self.s = np.zeros((heads, dim, dim), np.float32)
+
+    def step(self, q_raw, k_raw, v_raw, g_low, beta_raw, g2):
+        d = _KdaDesc()
+        d.heads, d.dim, d.kconv, d.gate_lb, d.rms_eps = self.heads, self.dim, self.kconv, self.gate_lb, self.rms_eps
+        d.q_conv, d.k_conv, d.v_conv, d.a_log, d.dt_bias, d.o_norm = (_p(a, _f32p) for a in self.w)
+        ins = [_c(a, np.float32) for a in (q_raw, k_raw, v_raw, g_low, beta_raw, g2)]
+        o = np.empty(self.heads * self.dim, np.float32)
+        lib().or_kda_step(C.byref(d), *(_p(c, _f32p) for c in self.conv), _p(self.s, _f32p), *(_p(a, _f32p) for a in ins),
+                          _p(o, _f32p))
+        return o
+
+
+def kda_core(q, k, v, g, beta, a_log, dt_bias, t_steps, heads, dim):
+    """The selftest's standalone recurrence (selftest.rs:48-113): (o [T*H*dim], S [H*dim*dim])."""
+    a = [_c(x, np.float32) for x in (q, k, v, g, beta, a_log, dt_bias)]
+    o = np.empty(t_steps * heads * dim, np.float32)
+    s = np.empty(heads * dim * dim, np.float32)
+    lib().or_kda_core(*(_p(x, _f32p) for x in a), t_steps, heads, dim, _p(o, _f32p), _p(s, _f32p))
+    return o, s
+
+
+def kda_model_recurrence(q, k, v, g, beta, a_log, dt_bias, t_steps, heads, dim, gate_lb=-5.0):
+    """The same raw inputs through the engine's own pieces: kda_norm_head, kda_gate, sigmoid(beta) and
+    kda_recur_step (model.rs:1088-1156)."""
+    L = lib()
+    proj = heads * dim
+    s = np.zeros(heads * dim * dim, np.float32)
+    o = np.empty((t_steps, proj), np.float32)
+    a_log, dt_bias = _c(a_log, np.float32), _c(dt_bias, np.float32)
+    for t in range(t_steps):
+        qt = _c(np.asarray(q, np.float32).reshape(t_steps, proj)[t].copy(), np.float32)
+        kt = _c(np.asarray(k, np.float32).reshape(t_steps, proj)[t].copy(), np.float32)
+        vt = _c(np.asarray(v, np.float32).reshape(t_steps, proj)[t], np.float32)
+        gl = _c(np.asarray(g, np.float32).reshape(t_steps, proj)[t], np.float32)
+        bt = np.array([L.or_sigmoid(float(b)) for b in np.asarray(beta, np.float32).reshape(t_steps, heads)[t]], np.float32)
+        L.or_kda_norm_head(heads, dim, _p(qt, _f32p), float(np.float32(dim) ** np.float32(-0.5)))
+        L.or_kda_norm_head(heads, dim, _p(kt, _f32p), 1.0)
+        gg = np.empty(proj, np.float32)
+        L.or_kda_gate(heads, dim, float(gate_lb), _p(a_log, _f32p), _p(dt_bias, _f32p), _p(gl, _f32p), _p(gg, _f32p))
+        L.or_kda_recur_step(heads, dim, _p(s, _f32p), _p(qt, _f32p), _p(kt, _f32p), _p(vt, _f32p), _p(gg, _f32p), _p(bt, _f32p),
+                            _p(o[t], _f32p))
+    return o.reshape(-1), s
+
+
+def attn_res(prefix, blocks, w, eps):
+    prefix, blocks, w = _c(prefix, np.float32), _c(blocks, np.float32), _c(w, np.float32)
+    out = np.empty_like(prefix)
+    lib().or_attn_res(prefix.size, float(eps), _p(prefix, _f32p), _p(blocks, _f32p), blocks.shape[0], _p(w, _f32p), _p(out, _f32p))
+    return out
 
 
 class MoeK3:

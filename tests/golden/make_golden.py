@@ -82,6 +82,41 @@ def main():
     w[5, 0] = -0.0
     p, s = ex_mod.quantize_mxfp4(w)
     np.savez(os.path.join(OUT, "export_quantize_naive.npz"), w=w, packed=p.astype(np.uint8), scales=s.astype(np.uint8))
+    # 5. the KDA recurrence and AttnRes vectors of the reference's `selftest` (src/selftest.rs:131-180): the
+    #    inputs and calls of ref/make_golden.py (seed 42, chunk_kda of the vendored fla shim, the AttnRes formula)
+    import torch
+    sys.path.insert(0, os.path.join(REF, "nano", "vendor"))
+    from fla.ops.kda import chunk_kda
+    tg = torch.Generator().manual_seed(42)
+    T, H, K, V = 3, 4, 128, 128
+    q = torch.randn(1, T, H, K, generator=tg)
+    k = torch.randn(1, T, H, K, generator=tg)
+    v = torch.randn(1, T, H, V, generator=tg)
+    graw = torch.randn(1, T, H, K, generator=tg)
+    beta = torch.randn(1, T, H, generator=tg)
+    a_log = torch.randn(K, generator=tg)
+    dt_bias = torch.randn(H * K, generator=tg)
+    o, S = chunk_kda(q, k, v, graw, beta, A_log=a_log, dt_bias=dt_bias, scale=None, initial_state=None,
+                     output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                     use_beta_sigmoid_in_kernel=True, safe_gate=True, lower_bound=-5.0)
+    f = lambda t: t.flatten().numpy().astype(np.float32)
+    np.savez_compressed(os.path.join(OUT, "kda_recurrence.npz"), T=np.int64(T), H=np.int64(H), K=np.int64(K),
+                        q=f(q), k=f(k), v=f(v), g=f(graw), beta=f(beta), A_log=f(a_log), dt_bias=f(dt_bias), o=f(o), S=f(S))
+    # the same generator goes on: 2 x 16 SiTU inputs, then the AttnRes inputs (D = 512, 3 blocks + prefix, eps 1e-5)
+    gs = torch.randn(16, generator=tg) * 6.0
+    us = torch.randn(16, generator=tg) * 30.0
+    situ = 4.0 * torch.tanh(gs / 4.0) * torch.sigmoid(gs) * (25.0 * torch.tanh(us / 25.0))
+    D, B = 512, 3
+    blocks = torch.randn(B, D, generator=tg)
+    prefix = torch.randn(D, generator=tg)
+    norm_w = torch.randn(D, generator=tg)
+    proj_w = torch.randn(D, generator=tg)
+    vv = torch.cat([blocks, prefix.unsqueeze(0)], dim=0)
+    kk = vv * torch.rsqrt(vv.pow(2).mean(-1, keepdim=True) + 1e-5)
+    probs = (kk * (norm_w * proj_w)).sum(-1).softmax(-1)
+    out = (probs.unsqueeze(-1) * vv).sum(0)
+    np.savez_compressed(os.path.join(OUT, "situ_attn_res.npz"), situ_g=f(gs), situ_u=f(us), situ_out=f(situ),
+                        blocks=blocks.numpy().astype(np.float32), prefix=f(prefix), norm_w=f(norm_w), proj_w=f(proj_w), out=f(out))
     print("wrote fixtures to", OUT)
 
 

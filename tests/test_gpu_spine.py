@@ -115,3 +115,88 @@ def test_vq1_matvec_bit_exact(mk, rows, cols, batch):
     assert np.array_equal(bits(y), bits(ref))
     assert np.array_equal(bits(w.matvec(x[0])), bits(ref[0]))
     w.free()
+
+
+# ------------------------------------------------------------------ KDA decode step, AttnRes
+def _kda_params(rng, heads, dim, kconv):
+    proj = heads * dim
+    cw = [(rng.standard_normal((proj, kconv)) * 0.5).astype(np.float32) for _ in range(3)]
+    a_log = np.log(rng.uniform(1.0, 16.0, dim)).astype(np.float32)      # the builder's A_log = ln(U(1, 16))
+    dt_bias = (rng.standard_normal(proj) * 0.3).astype(np.float32)
+    o_norm = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    return cw, a_log, dt_bias, o_norm
+
+
+# (4, 128): the engine's heads and kda_dim; (2, 64): the other register-resident size; (3, 40): the generic kernel
+# with a partly filled last warp; kconv 2: a one-row window
+@pytest.mark.parametrize("heads,dim,kconv", [(4, 128, 4), (2, 64, 4), (3, 40, 4), (2, 128, 2), (1, 8, 3)])
+def test_kda_step_against_oracle(mk, heads, dim, kconv):
+    """kda_forward between its projections and o_proj (src/model.rs:1203-1228), 8 tokens in a row.  Every sum keeps
+    the engine's order, exp comes from double precision rounded once: tolerance 1e-6 relative to the largest value
+    (a differing last bit of one exp), and the run normally is bit-identical, which the test reports."""
+    import torch
+    rng = np.random.default_rng(heads * 1000 + dim + kconv)
+    cw, a_log, dt_bias, o_norm = _kda_params(rng, heads, dim, kconv)
+    proj = heads * dim
+    ref = O.KdaLayer(heads, dim, *cw, a_log, dt_bias, o_norm, kconv=kconv, gate_lb=-5.0, rms_eps=1e-6)
+    dev = mk.KdaLayer(heads, dim, *cw, a_log, dt_bias, o_norm, kconv=kconv, gate_lb=-5.0, rms_eps=1e-6)
+    exact = True
+    for t in range(8):
+        ins = [rng.standard_normal(proj).astype(np.float32) for _ in range(3)]
+        ins += [rng.standard_normal(proj).astype(np.float32), rng.standard_normal(heads).astype(np.float32),
+                rng.standard_normal(proj).astype(np.float32)]
+        want = ref.step(*ins)
+        got = dev.step(*[torch.from_numpy(a).cuda() for a in ins]).cpu().numpy()
+        assert np.abs(got - want).max() <= 1e-6 * max(1.0, np.abs(want).max())
+        exact &= np.array_equal(bits(got), bits(want))
+    s, conv = dev.export_state()
+    assert np.abs(s - ref.s).max() <= 1e-6 * max(1.0, np.abs(ref.s).max())
+    for i in range(3):
+        assert np.array_equal(bits(conv[i]), bits(ref.conv[i]))       # raw inputs, moved only
+    print(f"kda {heads}x{dim}: bit-identical over 8 tokens: {exact}")
+    dev.free()
+
+
+def test_kda_state_snapshot_restore_and_reset(mk):
+    """Cache snapshot / restore (the engine clones the layer caches before a draft batch and restores them on a
+    partial accept, src/spec.rs:214, 294-299): a restored state replays the same bits; reset = a new sequence."""
+    import torch
+    rng = np.random.default_rng(3)
+    heads, dim = 4, 128
+    cw, a_log, dt_bias, o_norm = _kda_params(rng, heads, dim, 4)
+    dev = mk.KdaLayer(heads, dim, *cw, a_log, dt_bias, o_norm)
+    proj = heads * dim
+    toks = [[torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda() for n in (proj, proj, proj, proj, heads, proj)]
+            for _ in range(5)]
+    first = [dev.step(*toks[t]).clone() for t in range(2)]
+    snap = dev.export_state()
+    tail = [dev.step(*toks[t]).clone() for t in range(2, 5)]
+    dev.import_state(*snap)
+    again = [dev.step(*toks[t]) for t in range(2, 5)]
+    assert all(torch.equal(a, b) for a, b in zip(tail, again))
+    dev.reset()
+    fresh = [dev.step(*toks[t]) for t in range(2)]
+    assert all(torch.equal(a, b) for a, b in zip(first, fresh))
+    dev.free()
+
+
+@pytest.mark.parametrize("d,b", [(512, 3), (7168, 8), (100, 1), (64, 0)])
+def test_attn_res_against_oracle(mk, d, b):
+    """attn_res (src/model.rs:625-669): same tolerance rule as the KDA step (one exp per row)."""
+    import torch
+    rng = np.random.default_rng(d + b)
+    prefix = rng.standard_normal(d).astype(np.float32)
+    blocks = rng.standard_normal((b, d)).astype(np.float32)
+    w = (rng.standard_normal(d) * 0.1).astype(np.float32)
+    want = O.attn_res(prefix, blocks, w, 1e-5)
+    got = mk.attn_res(torch.from_numpy(prefix).cuda(), torch.from_numpy(blocks).cuda(), torch.from_numpy(w).cuda(), 1e-5).cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-6 * max(1.0, np.abs(want).max())
+
+
+def test_attn_res_golden(mk):
+    """The AttnRes vector of the reference's selftest (src/selftest.rs:165-180), its tolerance (1e-4 relative + 1e-6)."""
+    import torch
+    g = np.load(os.path.join(GOLDEN, "situ_attn_res.npz"))
+    w = g["norm_w"] * g["proj_w"]
+    got = mk.attn_res(torch.from_numpy(g["prefix"]).cuda(), torch.from_numpy(g["blocks"]).cuda(), torch.from_numpy(w).cuda(), 1e-5)
+    assert (np.abs(got.cpu().numpy() - g["out"]) <= 1e-6 + 1e-4 * np.abs(g["out"])).all()

@@ -453,3 +453,67 @@ def test_fp8_dequant_matches_torch_golden():
         o = O.dequant_fp8(allb, np.array([sb, sb], np.uint8), 1, 256)[0]
         assert np.isnan(o[0x7F]) and np.isnan(o[0xFF])
         assert o[0] == 0.0 and np.signbit(o[0x80]) and o[0x80] == 0.0
+
+
+# ------------------------------------------------------------------ KDA recurrence, SiTU, AttnRes (selftest.rs:131-180)
+def _selftest_ok(got, want):
+    """The reference selftest's acceptance rule (selftest.rs:7-8, 19-34): |d| <= 1e-6 + 1e-4 |want|."""
+    d = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64))
+    return bool((d <= 1e-6 + 1e-4 * np.abs(want)).all())
+
+
+def test_kda_recurrence_matches_fla_golden():
+    g = np.load(os.path.join(GOLDEN, "kda_recurrence.npz"))
+    T, H, K = int(g["T"]), int(g["H"]), int(g["K"])
+    args = (g["q"], g["k"], g["v"], g["g"], g["beta"], g["A_log"], g["dt_bias"], T, H, K)
+    o, s = O.kda_core(*args)                      # the selftest's standalone form
+    assert _selftest_ok(o, g["o"]) and _selftest_ok(s, g["S"])
+    o2, s2 = O.kda_model_recurrence(*args)         # the engine's own pieces on the same inputs
+    assert _selftest_ok(o2, g["o"]) and _selftest_ok(s2, g["S"])
+
+
+def test_situ_and_attn_res_match_golden():
+    g = np.load(os.path.join(GOLDEN, "situ_attn_res.npz"))
+    situ = np.array([O.lib().or_situ(float(a), float(b)) for a, b in zip(g["situ_g"], g["situ_u"])], np.float32)
+    assert _selftest_ok(situ, g["situ_out"])
+    out = O.attn_res(g["prefix"], g["blocks"], g["norm_w"] * g["proj_w"], 1e-5)
+    assert _selftest_ok(out, g["out"])
+
+
+def test_kda_step_is_conv_norm_gate_recurrence_onorm():
+    """or_kda_step against a float64 numpy statement of kda_forward's middle part over several tokens."""
+    rng = np.random.default_rng(11)
+    H, D, KC = 2, 16, 4
+    proj = H * D
+    cw = [(rng.standard_normal((proj, KC)) * 0.5).astype(np.float32) for _ in range(3)]
+    a_log = rng.standard_normal(D).astype(np.float32) * 0.3
+    dt_bias = rng.standard_normal(proj).astype(np.float32) * 0.3
+    o_norm = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    layer = O.KdaLayer(H, D, *cw, a_log, dt_bias, o_norm, kconv=KC, gate_lb=-5.0, rms_eps=1e-6)
+    win = [np.zeros((KC - 1, proj)) for _ in range(3)]
+    S = np.zeros((H, D, D))
+    sig = lambda x: 1.0 / (1.0 + np.exp(-x))
+    for t in range(6):
+        raw = [rng.standard_normal(proj).astype(np.float32) for _ in range(3)]
+        g_low, g2 = rng.standard_normal(proj).astype(np.float32), rng.standard_normal(proj).astype(np.float32)
+        beta = rng.standard_normal(H).astype(np.float32)
+        got = layer.step(*raw, g_low, beta, g2)
+        qkv = []
+        for i in range(3):
+            acc = (cw[i][:, :3].astype(np.float64) * win[i].T).sum(1) + cw[i][:, 3] * raw[i].astype(np.float64)
+            qkv.append(acc * sig(acc))
+            win[i] = np.vstack([win[i][1:], raw[i][None].astype(np.float64)])
+        q, k, v = (a.reshape(H, D) for a in qkv)
+        q = q / np.maximum(np.linalg.norm(q, axis=1, keepdims=True), 1e-12) * D ** -0.5
+        k = k / np.maximum(np.linalg.norm(k, axis=1, keepdims=True), 1e-12)
+        gate = -5.0 * sig(np.exp(a_log.astype(np.float64))[None] * (g_low.reshape(H, D) + dt_bias.reshape(H, D)))
+        want = np.empty((H, D))
+        for h in range(H):
+            S[h] *= np.exp(gate[h])[:, None]
+            delta = v[h] - k[h] @ S[h]
+            S[h] += np.outer(sig(beta[h]) * k[h], delta)
+            o = q[h] @ S[h]
+            want[h] = o / np.sqrt((o * o).mean() + 1e-6) * o_norm * sig(g2.reshape(H, D)[h])
+        assert np.abs(got - want.reshape(-1)).max() <= 2e-5 * max(1.0, np.abs(want).max())
+        assert np.abs(layer.s - S).max() <= 2e-5 * max(1.0, np.abs(S).max())
+        assert np.array_equal(layer.conv[0], win[0].astype(np.float32))
