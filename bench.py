@@ -503,6 +503,38 @@ def run_case_moe_ep(args):
     dist.destroy_process_group()
 
 
+def run_case_kda(args):
+    """Side workload: the KDA decode step (conv + SiLU, head norms, gate, recurrence, gated RMS) of `--heads`
+    heads of width 128, `copies` layers in rotation (each layer's state S is heads x 64 KB); one launch per step."""
+    torch, mk, ctx, dev = _side_ctx()
+    H, D = args.heads, 128
+    proj = H * D
+    rng = np.random.default_rng(5)
+    layers = []
+    for _ in range(args.copies):
+        cw = [(rng.standard_normal((proj, 4)) * 0.5).astype(np.float32) for _ in range(3)]
+        layers.append(mk.KdaLayer(H, D, *cw, np.log(rng.uniform(1, 16, D)).astype(np.float32),
+                                  (rng.standard_normal(proj) * 0.3).astype(np.float32), np.ones(D, np.float32), ctx=ctx))
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9)
+    ins = [torch.randn(n, dtype=torch.float32, device=dev, generator=gen) for n in (proj, proj, proj, proj, H, proj)]
+    ms_call = _timed(torch, lambda i: layers[i % args.copies].step(*ins), args.steps, args.warmup)
+    # one launch per call: the loop above is bound by the host's call overhead, so the kernel itself is timed
+    # by the library's event pairs around each launch
+    ctx.prof_enable(True)
+    _timed(torch, lambda i: layers[i % args.copies].step(*ins), args.steps, 0)
+    n_k, ms_k = ctx.prof_read("other")
+    ctx.prof_enable(False)
+    ms = ms_k / max(n_k, 1)
+    alg = H * D * D * 8 + 10 * proj * 4
+    peak, kind = measured_peaks()
+    ach = alg / (ms * 1e-3) / 1e9
+    print(json.dumps({"case": "kda_step", "heads": H, "dim": D, "copies": args.copies, "kernel_us": ms * 1e3,
+                      "call_us_host_loop": ms_call * 1e3, "algorithmic_bytes": alg, "status_word": ctx.status_word(),
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                                   "peak_kind": kind, "note": "latency-bound: one CTA per head"}}), flush=True)
+
+
 def run_case_mla(args):
     """Side workload: q8_0 MLA decode attention, 64 heads.  --layout absorbed: one shared
     512+64 latent row per position (648 B with f32 scales); --layout per_head: the engine's
@@ -543,7 +575,7 @@ def run_case_mla(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "moe_ep", "mla"],
+    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "moe_ep", "mla", "kda"],
                     help="lm_head is the benchmark proper; the others are side workloads for kernel studies")
     ap.add_argument("--rows", type=int, default=7168)
     ap.add_argument("--cols", type=int, default=2048)
@@ -551,6 +583,7 @@ def main():
     ap.add_argument("--act", default="q8", choices=["q8", "q8x2"])
     ap.add_argument("--experts", type=int, default=384)
     ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=4, help="--case kda: KDA heads of width 128")
     ap.add_argument("--layout", default="absorbed", choices=["absorbed", "per_head"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
@@ -572,6 +605,8 @@ def main():
         run_case_moe_ep(args)
     elif args.case == "mla":
         run_case_mla(args)
+    elif args.case == "kda":
+        run_case_kda(args)
     else:
         run_gpu(args)
 

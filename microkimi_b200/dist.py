@@ -104,6 +104,7 @@ class FusedVocabHead:
         assert head.rows == self.head.rows and head.cols == self.head.cols
         xs = x.reshape(-1, self.head.cols)
         assert xs.dtype == torch.float32 and xs.is_contiguous() and xs.shape[0] <= self.max_batch
+        self.ctx._follow_torch()
         batch = xs.shape[0]
         ptr = C.c_void_p()
         _l.check(self.ctx._L.mk_matvec_q8_gather_dev(self.ctx._h, head._h, self._h, C.c_void_p(xs.data_ptr()), batch, self.row0,
@@ -165,6 +166,7 @@ class PeerEpMoeLayer:
         from . import lib as _l
         xs = x.reshape(-1, self.layer.dx)
         assert xs.dtype == torch.float32 and xs.is_contiguous()
+        self.ctx._follow_torch()
         out = torch.empty_like(xs)
         _l.check(self.ctx._L.mk_moe_forward_ep_dev(self.ctx._h, self.layer._h, self._h, C.c_void_p(xs.data_ptr()), xs.shape[0],
                                                   C.c_void_p(out.data_ptr()), None, None))

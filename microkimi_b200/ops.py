@@ -61,6 +61,14 @@ class Context:
         import torch
         s = torch.cuda.current_stream(self.device).cuda_stream
         _l.check(self._L.mk_set_stream(self._h, C.c_void_p(s)))
+        self._stream = s
+
+    def _follow_torch(self):
+        """Every call that takes torch CUDA tensors runs on torch's current stream, so that it is ordered
+        after the work that produced its inputs and before the work that reads its outputs."""
+        import torch
+        if torch.cuda.current_stream(self.device).cuda_stream != getattr(self, "_stream", None):
+            self.use_torch_stream()
 
     def sync(self):
         _l.check(self._L.mk_sync(self._h))
@@ -121,6 +129,7 @@ class _Weight:
         mode = _act_mode(act, strict)
         if import_torch:
             import torch
+            self.ctx._follow_torch()
             assert x.dtype == torch.float32 and x.is_contiguous()
             batch = 1 if x.dim() == 1 else x.shape[0]
             assert x.shape[-1] == self.cols, "x length must equal cols"
@@ -141,6 +150,7 @@ class MxFp4Weight(_Weight):
         ctx = ctx or Context.default()
         h = C.c_void_p()
         if _is_torch_cuda(packed):
+            ctx._follow_torch()
             assert packed.numel() == rows * cols // 2 and scales.numel() == rows * cols // 32
             _l.check(ctx._L.mk_weight_mxfp4(ctx._h, C.c_void_p(packed.data_ptr()), C.c_void_p(scales.data_ptr()),
                                             rows, cols, 1, C.byref(h)))
@@ -167,6 +177,7 @@ class MxFp4Weight(_Weight):
         that array, so keep them on one stream."""
         import torch
         assert _is_torch_cuda(x) and x.dtype == torch.float32 and x.is_contiguous()
+        self.ctx._follow_torch()
         batch = 1 if x.dim() == 1 else x.shape[0]
         assert x.shape[-1] == self.cols, "x length must equal cols"
         y = torch.empty((batch, self.rows), dtype=torch.float32, device=x.device)
@@ -196,6 +207,7 @@ class F32Weight(_Weight):
         h = C.c_void_p()
         if _is_torch_cuda(w):
             import torch
+            ctx._follow_torch()
             assert w.dtype == torch.float32 and w.is_contiguous() and w.numel() == rows * cols
             _l.check(ctx._L.mk_weight_f32(ctx._h, C.c_void_p(w.data_ptr()), rows, cols, 1, C.byref(h)))
         else:
@@ -259,6 +271,7 @@ def rmsnorm(x, w, eps, ctx=None):
     ctx = ctx or Context.default()
     assert _is_torch_cuda(x) and _is_torch_cuda(w) and x.dtype == torch.float32 and w.dtype == torch.float32
     assert x.is_contiguous() and w.is_contiguous() and x.shape[-1] == w.numel()
+    ctx._follow_torch()
     n = 1 if x.dim() == 1 else x.shape[0]
     out = torch.empty_like(x)
     _l.check(ctx._L.mk_rmsnorm_dev(ctx._h, C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), n, x.shape[-1], float(eps),
@@ -271,6 +284,7 @@ def attn_res(prefix, blocks, w, eps, ctx=None):
     import torch
     ctx = ctx or Context.default()
     assert all(_is_torch_cuda(t) and t.dtype == torch.float32 and t.is_contiguous() for t in (prefix, blocks, w))
+    ctx._follow_torch()
     d = prefix.numel()
     b = blocks.shape[0] if blocks.numel() else 0
     assert w.numel() == d and (b == 0 or blocks.shape[1] == d)
@@ -303,6 +317,7 @@ class KdaLayer:
         import torch
         ins = (q_raw, k_raw, v_raw, g_low, beta_raw, g2)
         assert all(_is_torch_cuda(t) and t.dtype == torch.float32 and t.is_contiguous() for t in ins)
+        self.ctx._follow_torch()
         proj = self.heads * self.dim
         assert all(t.numel() == proj for t in (q_raw, k_raw, v_raw, g_low, g2)) and beta_raw.numel() == self.heads
         o = torch.empty(proj, dtype=torch.float32, device=q_raw.device)
@@ -362,6 +377,7 @@ class Q8Head(_Weight):
         st = {"f32": _l.MK_SCALE_F32, "f16": _l.MK_SCALE_F16}[scale]
         h = C.c_void_p()
         if _is_torch_cuda(w):
+            ctx._follow_torch()
             assert w.numel() == rows * cols and w.is_contiguous()
             _l.check(ctx._L.mk_weight_q8_from_f32(ctx._h, C.c_void_p(w.data_ptr()), rows, cols, st, 1, C.byref(h)))
         else:
@@ -389,6 +405,7 @@ class Q8Head(_Weight):
         if want_argmax:
             if _is_torch_cuda(x):
                 import torch
+                self.ctx._follow_torch()
                 am = torch.empty(batch, dtype=torch.int32, device=x.device)
                 amp = C.c_void_p(am.data_ptr())
             else:
@@ -481,6 +498,7 @@ class MoeLayer:
         """Router only: (ids [n, top_k] int32, weights [n, top_k] f32[, logits [n, E]])."""
         if _is_torch_cuda(x):
             import torch
+            self.ctx._follow_torch()
             xs = x.reshape(-1, self.dx)
             n = xs.shape[0]
             ids = torch.empty((n, self.top_k), dtype=torch.int32, device=x.device)
@@ -503,6 +521,7 @@ class MoeLayer:
         L = self.ctx._L
         if _is_torch_cuda(x):
             import torch
+            self.ctx._follow_torch()
             xs = x.reshape(-1, self.dx)
             assert xs.dtype == torch.float32 and xs.is_contiguous()
             n = xs.shape[0]
@@ -528,6 +547,7 @@ class MoeLayer:
     def experts_dev(self, x, pair_row, pair_expert, pair_weight):
         """Grouped experts on explicit pairs (torch CUDA tensors): outs [n_pairs, d]."""
         import torch
+        self.ctx._follow_torch()
         n_pairs = pair_row.numel()
         outs = torch.empty((n_pairs, self.d), dtype=torch.float32, device=x.device)
         _l.check(self.ctx._L.mk_moe_experts_dev(self.ctx._h, self._h, C.c_void_p(x.data_ptr()), x.shape[0],
@@ -537,6 +557,7 @@ class MoeLayer:
 
     def combine_dev(self, outs, n_tokens, slots):
         import torch
+        self.ctx._follow_torch()
         out = torch.empty((n_tokens, self.d), dtype=torch.float32, device=outs.device)
         _l.check(self.ctx._L.mk_moe_combine_dev(self.ctx._h, C.c_void_p(outs.data_ptr()), n_tokens, slots, self.d,
                                                 C.c_void_p(out.data_ptr())))
@@ -588,6 +609,7 @@ class MlaCache:
         L = self.ctx._L
         kdim = self.nope if self.layout == "absorbed" else self.H * (self.nope + self.rope)
         if _is_torch_cuda(k_row):
+            self.ctx._follow_torch()
             n = k_row.numel() // kdim
             vp = C.c_void_p(v_row.data_ptr()) if v_row is not None else None
             _l.check(L.mk_mla_append_dev(self.ctx._h, self._h, seq, C.c_void_p(k_row.data_ptr()), vp, n))
@@ -612,6 +634,7 @@ class MlaCache:
     def attend_batch(self, q, scale):
         """All sequences at once (torch CUDA q [n_seqs, H, qdim]) over all positions each holds."""
         import torch
+        self.ctx._follow_torch()
         assert q.is_contiguous() and q.dtype == torch.float32 and q.numel() == self.n_seqs * self.H * (self.nope + self.rope)
         out = torch.empty((self.n_seqs, self.H, self.vd), dtype=torch.float32, device=q.device)
         _l.check(self.ctx._L.mk_mla_attend_batch_dev(self.ctx._h, self._h, C.c_void_p(q.data_ptr()), float(scale),
