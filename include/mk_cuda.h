@@ -192,6 +192,8 @@ int32_t mk_matvec_vq1_dev(mk_ctx *ctx, const mk_weight *w, const float *x, float
 /* rmsnorm (src/model.rs:599-605) on DEVICE rows: out[i] = (x[i] * inv) * w[i] with
  * inv = 1 / sqrt(dot(x, x) / len + eps); x, out f32 [n, len], w f32 [len].  Bit-identical. */
 int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, int32_t n, int32_t len, float eps, float *out);
+/* a[i] *= sigmoid(g[i]) on DEVICE vectors: the output gate of mla_forward (src/model.rs:2015-2019). */
+int32_t mk_sigmoid_gate_dev(mk_ctx *ctx, float *a, const float *g, int64_t count);
 
 /* ---- KDA decode step (src/model.rs:1066-1228) ----------------------------
  * The part of kda_forward between its projections and o_proj, one token per call, with the

@@ -70,6 +70,12 @@ __global__ void __launch_bounds__(256) situ_kernel(const float *__restrict__ a, 
     if (i < count) out[i] = mk_situ(a[i], u[i]);
 }
 
+// a[i] *= sigmoid(g[i]) (the output gate of mla_forward, src/model.rs:2017-2019); exp in double precision, rounded once
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(float *__restrict__ a, const float *__restrict__ g, int64_t count) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) a[i] = __fmul_rn(a[i], __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-g[i])))));
+}
+
 using GemvB1 = mkf::TileShape<32, 1, 128, 4>;
 using GemvB2 = mkf::TileShape<16, 2, 128, 4>;
 using GemvB4 = mkf::TileShape<8, 4, 256, 3>;
@@ -187,4 +193,14 @@ extern "C" int32_t mk_rmsnorm_dev(mk_ctx *ctx, const float *x, const float *w, i
     MK_CHECK_ARG(ctx != nullptr && x != nullptr && w != nullptr && out != nullptr && n > 0 && len > 0, "bad argument");
     MK_CUDA(cudaSetDevice(ctx->device));
     return mk_launch_rmsnorm(ctx, x, w, n, len, eps, out);
+}
+
+extern "C" int32_t mk_sigmoid_gate_dev(mk_ctx *ctx, float *a, const float *g, int64_t count) {
+    MK_CHECK_ARG(ctx != nullptr && a != nullptr && g != nullptr && count > 0, "bad argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    mk_prof_scope prof(ctx, MK_PROF_OTHER);
+    sigmoid_gate_kernel<<<(unsigned)mk_ceil_div(count, 256), 256, 0, ctx->stream>>>(a, g, count);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
 }

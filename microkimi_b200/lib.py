@@ -90,6 +90,7 @@ SIGNATURES = {
     "mk_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _i32]),
     "mk_matvec_f32_dev": (_i32, [_vp, _vp, _vp, _vp, _i32]),
     "mk_rmsnorm_dev": (_i32, [_vp, _vp, _vp, _i32, _i32, C.c_float, _vp]),
+    "mk_sigmoid_gate_dev": (_i32, [_vp, _vp, _vp, _i64]),
     "mk_kda_create": (_i32, [_vp, C.POINTER(KdaDesc), C.POINTER(_vp)]),
     "mk_kda_free": (None, [_vp, _vp]),
     "mk_kda_reset": (_i32, [_vp, _vp]),
