@@ -53,7 +53,37 @@ struct KdaArgs {
     float gate_lb, rms_eps, q_scale;
 };
 
-// depthwise causal conv + SiLU of channel i; shifts the channel's window (no other thread touches it)
+// One channel's conv inputs, loaded before any arithmetic so that all global loads of a thread are in flight
+// together: KC weights (weight KC - 1 on the current input) and the KC - 1 previous raw inputs, oldest first.
+template <int KC>
+struct ConvIn {
+    float w[KC > 0 ? KC : 1], old[KC > 1 ? KC - 1 : 1], raw;
+    __device__ __forceinline__ void load(const float *__restrict__ cw, const float *__restrict__ win, int64_t proj, int64_t i,
+                                         const float *__restrict__ src) {
+        if constexpr (KC == 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(cw + i * 4);
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < KC; ++j) w[j] = cw[i * KC + j];
+        }
+#pragma unroll
+        for (int j = 0; j < KC - 1; ++j) old[j] = win[(int64_t)j * proj + i];
+        raw = src[i];
+    }
+    // conv + SiLU in the engine's order; shifts the channel's window (no other thread touches it)
+    __device__ __forceinline__ float apply(float *__restrict__ win, int64_t proj, int64_t i) const {
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < KC - 1; ++j) {
+            acc = __fadd_rn(acc, __fmul_rn(w[j], old[j]));
+            win[(int64_t)j * proj + i] = j + 1 < KC - 1 ? old[j + 1] : raw;
+        }
+        acc = __fadd_rn(acc, __fmul_rn(w[KC - 1], raw));
+        return __fmul_rn(acc, sigmoid_cr(acc));
+    }
+};
+// any kconv: the same, with the loads inside the loop
 __device__ __forceinline__ float conv_channel(const float *w, float *win, int64_t proj, int64_t i, int kconv, float raw) {
     float acc = 0.0f;
     for (int j = 0; j < kconv - 1; ++j) {
@@ -66,8 +96,10 @@ __device__ __forceinline__ float conv_channel(const float *w, float *win, int64_
     return __fmul_rn(acc, sigmoid_cr(acc));
 }
 
-// DIM > 0: the column lives in registers; DIM == 0: any dim, the decayed column is parked in S between the passes
-template <int DIM>
+// DIM > 0: the column lives in registers and is fetched at kernel start, together with every other input of the
+// thread; DIM == 0: any dim, the decayed column is parked in S between the passes.  KC == 4: the engine's conv
+// width with its loads hoisted; KC == 0: any width.
+template <int DIM, int KC>
 __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs a) {
     extern __shared__ float sm[];
     const int dim = DIM > 0 ? DIM : a.dim;
@@ -75,13 +107,38 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
     const int h = blockIdx.x, c = threadIdx.x, lane = c & 31, warp = c >> 5, nwarps = blockDim.x >> 5;
     const bool active = c < dim;
     const int64_t proj = (int64_t)a.heads * dim, i = (int64_t)h * dim + c;
-    float vv = 0.0f;
+    const int64_t wq = 0, wk = proj * a.kconv, wv = 2 * proj * a.kconv;                       // conv weights of q, k, v
+    const int64_t cq = 0, ck = (int64_t)(a.kconv - 1) * proj, cv = 2 * (int64_t)(a.kconv - 1) * proj; // their windows
+    float *col = a.s + (int64_t)h * dim * dim + c;
+    float x[DIM > 0 ? DIM : 1];
+    float vv = 0.0f, g2v = 0.0f, onv = 0.0f, bh = 0.0f;
     if (active) {
-        qs[c] = conv_channel(a.conv_w, a.conv, proj, i, a.kconv, a.q_raw[i]);
-        ks[c] = conv_channel(a.conv_w + proj * a.kconv, a.conv + (int64_t)(a.kconv - 1) * proj, proj, i, a.kconv, a.k_raw[i]);
-        vv = conv_channel(a.conv_w + 2 * proj * a.kconv, a.conv + 2 * (int64_t)(a.kconv - 1) * proj, proj, i, a.kconv, a.v_raw[i]);
-        const float g = __fmul_rn(a.gate_lb, sigmoid_cr(__fmul_rn(exp_cr(a.a_log[c]), __fadd_rn(a.g_low[i], a.dt_bias[i]))));
+        float glow, dtb, alog;
+        ConvIn<KC> iq, ik, iv;
+        if constexpr (KC > 0) {
+            iq.load(a.conv_w + wq, a.conv + cq, proj, i, a.q_raw);
+            ik.load(a.conv_w + wk, a.conv + ck, proj, i, a.k_raw);
+            iv.load(a.conv_w + wv, a.conv + cv, proj, i, a.v_raw);
+        }
+        glow = a.g_low[i]; dtb = a.dt_bias[i]; alog = a.a_log[c];
+        g2v = a.g2[i]; onv = a.o_norm[c]; bh = a.beta_raw[h];
+        if constexpr (DIM > 0) {
+#pragma unroll
+            for (int r = 0; r < DIM; ++r) x[r] = col[(int64_t)r * DIM];
+        }
+        if constexpr (KC > 0) {
+            qs[c] = iq.apply(a.conv + cq, proj, i);
+            ks[c] = ik.apply(a.conv + ck, proj, i);
+            vv = iv.apply(a.conv + cv, proj, i);
+        } else {
+            qs[c] = conv_channel(a.conv_w + wq, a.conv + cq, proj, i, a.kconv, a.q_raw[i]);
+            ks[c] = conv_channel(a.conv_w + wk, a.conv + ck, proj, i, a.kconv, a.k_raw[i]);
+            vv = conv_channel(a.conv_w + wv, a.conv + cv, proj, i, a.kconv, a.v_raw[i]);
+        }
+        const float g = __fmul_rn(a.gate_lb, sigmoid_cr(__fmul_rn(exp_cr(alog), __fadd_rn(glow, dtb))));
         ds[c] = exp_cr(g);
+        bh = sigmoid_cr(bh);
+        g2v = sigmoid_cr(g2v);
     }
     __syncthreads();
     // per-head L2 norms: q by warp 0, k by the last warp (the same warp when there is one)
@@ -101,13 +158,8 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
     __syncthreads();
     float o = 0.0f;
     if (active) {
-        const float bh = sigmoid_cr(a.beta_raw[h]);
-        float *col = a.s + (int64_t)h * dim * dim + c;
         float delta = vv;
         if constexpr (DIM > 0) {
-            float x[DIM];
-#pragma unroll
-            for (int r = 0; r < DIM; ++r) x[r] = col[(int64_t)r * DIM];
 #pragma unroll
             for (int r = 0; r < DIM; ++r) {
                 x[r] = __fmul_rn(x[r], ds[r]);
@@ -121,14 +173,14 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
             }
         } else {
             for (int r = 0; r < dim; ++r) {
-                const float x = __fmul_rn(col[(int64_t)r * dim], ds[r]);
-                col[(int64_t)r * dim] = x;
-                delta = __fsub_rn(delta, __fmul_rn(ks[r], x));
+                const float xr = __fmul_rn(col[(int64_t)r * dim], ds[r]);
+                col[(int64_t)r * dim] = xr;
+                delta = __fsub_rn(delta, __fmul_rn(ks[r], xr));
             }
             for (int r = 0; r < dim; ++r) {
-                const float x = __fadd_rn(col[(int64_t)r * dim], __fmul_rn(__fmul_rn(bh, ks[r]), delta));
-                o = __fadd_rn(o, __fmul_rn(qs[r], x));
-                col[(int64_t)r * dim] = x;
+                const float xr = __fadd_rn(col[(int64_t)r * dim], __fmul_rn(__fmul_rn(bh, ks[r]), delta));
+                o = __fadd_rn(o, __fmul_rn(qs[r], xr));
+                col[(int64_t)r * dim] = xr;
             }
         }
     }
@@ -140,7 +192,7 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
         if (lane == 0) red[2] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ss, a.rms_eps)));
     }
     __syncthreads();
-    if (active) a.o[i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), a.o_norm[c]), sigmoid_cr(a.g2[i]));
+    if (active) a.o[i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), onv), g2v);
 }
 
 // ---- AttnRes: scores (one warp per row: blocks 0..b-1, then the prefix), then softmax + mix
@@ -277,12 +329,19 @@ extern "C" int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *k, const float *q_raw, c
     a.gate_lb = k->gate_lb; a.rms_eps = k->rms_eps; a.q_scale = k->q_scale;
     const size_t smem = (size_t)(3 * k->dim + 4) * sizeof(float);
     mk_prof_scope prof(ctx, MK_PROF_OTHER);
-    if (k->dim == 128)
-        kda_step_kernel<128><<<k->heads, 128, smem, ctx->stream>>>(a);
+    const bool kc4 = k->kconv == 4;
+    if (k->dim == 128 && kc4)
+        kda_step_kernel<128, 4><<<k->heads, 128, smem, ctx->stream>>>(a);
+    else if (k->dim == 128)
+        kda_step_kernel<128, 0><<<k->heads, 128, smem, ctx->stream>>>(a);
+    else if (k->dim == 64 && kc4)
+        kda_step_kernel<64, 4><<<k->heads, 64, smem, ctx->stream>>>(a);
     else if (k->dim == 64)
-        kda_step_kernel<64><<<k->heads, 64, smem, ctx->stream>>>(a);
+        kda_step_kernel<64, 0><<<k->heads, 64, smem, ctx->stream>>>(a);
+    else if (kc4)
+        kda_step_kernel<0, 4><<<k->heads, (unsigned)mk_align_up(k->dim, 32), smem, ctx->stream>>>(a);
     else
-        kda_step_kernel<0><<<k->heads, (unsigned)mk_align_up(k->dim, 32), smem, ctx->stream>>>(a);
+        kda_step_kernel<0, 0><<<k->heads, (unsigned)mk_align_up(k->dim, 32), smem, ctx->stream>>>(a);
     ctx->launches++;
     MK_CUDA(cudaGetLastError());
     return MK_OK;
