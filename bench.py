@@ -223,6 +223,24 @@ def run_gpu(args):
     for i in range(args.warmup):
         step(i)
     barrier()
+    if fused is not None:
+        # self-check of the peer path before it is timed: the complete logits and the token id of one step must equal
+        # the library all-gather of the same shard results bit for bit, and no bounded wait may have run out
+        ptr, am = fused.matvec(x, want_argmax=True, head=heads[0])
+        got = fused.logits_tensor(ptr, batch)
+        y = heads[0].matvec(x)
+        want = torch.empty((world, batch, rows), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(want.view(-1), y.contiguous().view(-1))
+        want = want.permute(1, 0, 2).reshape(batch, VOCAB)
+        bad = torch.tensor([int(ctx.status_word() != 0 or not torch.equal(got, want)
+                                or not torch.equal(am.view(-1).long(), want.argmax(dim=1)))], dtype=torch.int32, device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            fused = None
+            fused_note = "peer-memory gather failed its self-check against the NCCL all-gather; NCCL all-gather used"
+            for i in range(args.warmup):
+                step(i)
+            barrier()
     launches0 = ctx.launches
     ctx.prof_enable(True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -236,6 +254,10 @@ def run_gpu(args):
     kn, kms = ctx.prof_read("lm_head")
     ctx.prof_enable(False)
     launches = ctx.launches - launches0
+    st = torch.tensor([ctx.status_word()], dtype=torch.int32, device=dev)   # a bounded device-side wait that ran out sets it
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    status_all = int(st.item())
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -315,6 +337,7 @@ def run_gpu(args):
                     "api": "mk_matvec_q8 (host pointers, pinned)" if fused is None else
                            "pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank"},
             "gpu_launches": launches,
+            "status_word": status_all,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
