@@ -243,7 +243,11 @@ int32_t mk_attn_res_dev(mk_ctx *ctx, const float *prefix, const float *blocks, i
  * The result is bit-identical to one GPU computing the whole matrix.
  *   mk_gather_create : allocates this rank's buffer, returns a 64-byte handle for it
  *   mk_gather_connect: opens the other ranks' buffers from their handles ([world][64] by
- *                      rank; exchange them with any host-side means)
+ *                      rank; exchange them with any host-side means).  An all-zero handle
+ *                      stands for a rank that never joined: its share is written to a local
+ *                      stand-in buffer, its flag never arrives, and every call reports
+ *                      MK_ERR_TIMEOUT in the status word after the bounded wait (about half
+ *                      a second) instead of hanging
  * world <= 8, max_batch <= 2 (decode).  Every rank must make the same sequence of calls. */
 typedef struct mk_gather mk_gather;
 int32_t mk_gather_create(mk_ctx *ctx, int32_t rank, int32_t world, int64_t vocab, int32_t max_batch, mk_gather **out,

@@ -29,6 +29,8 @@ struct mk_gather {
     size_t logits_off, blob_bytes;
     void *blob;        // local
     void *peer[8];     // blobs of all ranks (peer[rank] == blob)
+    void *absent;      // stand-in target for ranks that have not joined (all-zero handle): local scratch
+    bool is_absent[8];
     bool connected;
     uint32_t step;
 };
@@ -106,10 +108,14 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
     if (tid < world) {
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pe.flag[tid]), "r"(step) : "memory");
         bool ok = false;
-        for (uint32_t it = 0; it < GATHER_WAIT_LIMIT; ++it) {
+        uint64_t t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (uint32_t it = 0; it < GATHER_WAIT_LIMIT; ++it) {   // bounded twice: by polls and by one second of wall time
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
             if ((int32_t)(v - step) >= 0) { ok = true; break; }
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 1000000000ull) break;
             __nanosleep(100);
         }
         if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
@@ -167,11 +173,21 @@ extern "C" int32_t mk_gather_connect(mk_ctx *ctx, mk_gather *g, const uint8_t *h
         if (r == g->rank) continue;
         cudaIpcMemHandle_t h;
         memcpy(&h, handles + (size_t)r * 64, 64);
-        cudaError_t e = cudaIpcOpenMemHandle(&g->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+        bool zero = true;
+        for (int b = 0; b < 64; ++b) zero = zero && handles[(size_t)r * 64 + b] == 0;
+        cudaError_t e = cudaSuccess;
+        if (zero) { // the rank never joined: its rows go to local scratch, its flag never arrives, the wait runs out
+            if (!g->absent) e = cudaMalloc(&g->absent, g->blob_bytes);
+            if (e == cudaSuccess) e = cudaMemset(g->absent, 0, g->blob_bytes);
+            g->peer[r] = g->absent;
+            g->is_absent[r] = true;
+        } else {
+            e = cudaIpcOpenMemHandle(&g->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+        }
         if (e != cudaSuccess) {
             mk_set_error("mk_gather_connect: rank %d cannot open rank %d's buffer: %s", g->rank, r, cudaGetErrorString(e));
             for (int q = 0; q < r; ++q)
-                if (q != g->rank && g->peer[q]) { cudaIpcCloseMemHandle(g->peer[q]); g->peer[q] = nullptr; }
+                if (q != g->rank && g->peer[q] && !g->is_absent[q]) { cudaIpcCloseMemHandle(g->peer[q]); g->peer[q] = nullptr; }
             return MK_ERR_CUDA;
         }
     }
@@ -184,7 +200,8 @@ extern "C" int32_t mk_gather_free(mk_ctx *ctx, mk_gather *g) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     for (int r = 0; r < g->world; ++r)
-        if (r != g->rank && g->peer[r]) cudaIpcCloseMemHandle(g->peer[r]);
+        if (r != g->rank && g->peer[r] && !g->is_absent[r]) cudaIpcCloseMemHandle(g->peer[r]);
+    if (g->absent) cudaFree(g->absent);
     if (g->blob) cudaFree(g->blob);
     delete g;
     return MK_OK;

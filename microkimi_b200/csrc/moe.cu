@@ -61,6 +61,8 @@ struct mk_moe_ep {
     size_t par_bytes, blob_bytes;
     void *blob;
     void *peer[8];
+    void *absent;       // stand-in target for ranks that have not joined (all-zero handle): local scratch
+    bool is_absent[8];
     bool connected;
     uint32_t step;
     int32_t *n_local;   // device: pairs computed by this rank in the current call
@@ -615,10 +617,14 @@ __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, 
     if ((int)threadIdx.x < world) {
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pe.flag[threadIdx.x]), "r"(step) : "memory");
         bool ok = false;
-        for (uint32_t it = 0; it < EP_WAIT_LIMIT; ++it) {
+        uint64_t t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (uint32_t it = 0; it < EP_WAIT_LIMIT; ++it) {   // bounded twice: by polls and by one second of wall time
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
             if ((int32_t)(v - step) >= 0) { ok = true; break; }
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 1000000000ull) break;
             __nanosleep(100);
         }
         if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
@@ -1077,11 +1083,21 @@ extern "C" int32_t mk_moe_ep_connect(mk_ctx *ctx, mk_moe_ep *ep, const uint8_t *
         if (r == ep->rank) continue;
         cudaIpcMemHandle_t h;
         memcpy(&h, handles + (size_t)r * 64, 64);
-        cudaError_t e = cudaIpcOpenMemHandle(&ep->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+        bool zero = true;
+        for (int b = 0; b < 64; ++b) zero = zero && handles[(size_t)r * 64 + b] == 0;
+        cudaError_t e = cudaSuccess;
+        if (zero) { // the rank never joined: its table rows go to local scratch, its flag never arrives, the wait runs out
+            if (!ep->absent) e = cudaMalloc(&ep->absent, ep->blob_bytes);
+            if (e == cudaSuccess) e = cudaMemset(ep->absent, 0, ep->blob_bytes);
+            ep->peer[r] = ep->absent;
+            ep->is_absent[r] = true;
+        } else {
+            e = cudaIpcOpenMemHandle(&ep->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+        }
         if (e != cudaSuccess) {
             mk_set_error("mk_moe_ep_connect: rank %d cannot open rank %d's buffer: %s", ep->rank, r, cudaGetErrorString(e));
             for (int q = 0; q < r; ++q)
-                if (q != ep->rank && ep->peer[q]) { cudaIpcCloseMemHandle(ep->peer[q]); ep->peer[q] = nullptr; }
+                if (q != ep->rank && ep->peer[q] && !ep->is_absent[q]) { cudaIpcCloseMemHandle(ep->peer[q]); ep->peer[q] = nullptr; }
             return MK_ERR_CUDA;
         }
     }
@@ -1094,7 +1110,8 @@ extern "C" int32_t mk_moe_ep_free(mk_ctx *ctx, mk_moe_ep *ep) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     for (int r = 0; r < ep->world; ++r)
-        if (r != ep->rank && ep->peer[r]) cudaIpcCloseMemHandle(ep->peer[r]);
+        if (r != ep->rank && ep->peer[r] && !ep->is_absent[r]) cudaIpcCloseMemHandle(ep->peer[r]);
+    if (ep->absent) cudaFree(ep->absent);
     if (ep->blob) cudaFree(ep->blob);
     if (ep->n_local) cudaFree(ep->n_local);
     if (ep->counter) cudaFree(ep->counter);

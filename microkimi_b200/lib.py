@@ -9,6 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SO_PATH = os.path.join(_HERE, "libmk_b200.so")
 
 MK_OK = 0
+MK_ERR_ARG, MK_ERR_CUDA, MK_ERR_OOM, MK_ERR_STATE, MK_ERR_TIMEOUT, MK_ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
 MK_ACT_Q8 = 0
 MK_ACT_Q8X2 = 1
 MK_ACT_STRICT = 0x100
