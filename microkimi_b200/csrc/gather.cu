@@ -29,6 +29,7 @@ struct mk_gather {
     size_t logits_off, blob_bytes;
     void *blob;        // local
     void *peer[8];     // blobs of all ranks (peer[rank] == blob)
+    void *scratch;     // device: per-CTA (maximum, index) partials [32][2], then the CTA counter
     void *absent;      // stand-in target for ranks that have not joined (all-zero handle): local scratch
     bool is_absent[8];
     bool connected;
@@ -42,35 +43,40 @@ struct Best { float v; int64_t i; };
 // first index of the maximum (src/model.rs:3277-3290): a larger value wins, an equal value only with a lower index
 __device__ __forceinline__ Best better(Best a, Best b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
 
-// One CTA.  Reads this rank's slice [batch][n] (row stride ld) once: every 16 bytes go to the same place in
-// every other rank's buffer and into this rank's running (maximum, index).  Then the (maximum, index) pairs go
-// to every rank, everything is fenced system-wide, lane r publishes this rank's step in rank r's flag word and
-// waits for rank r's flag here to reach `step`; finally thread b picks token b's winner among the ranks' pairs.
+// gridDim.x CTAs share this rank's slice [batch][n] (row stride ld), each a contiguous range of 16-byte pieces, read
+// once: every piece goes to the same place in every other rank's buffer and into the CTA's running (maximum,
+// index), which lands in `partials`.  Every CTA fences system-wide and counts itself in; the last one to arrive
+// folds the partials, sends this rank's (maximum, index) pairs to every rank, fences, lane r publishes this rank's
+// step in rank r's flag word and waits for rank r's flag here to reach `step`; finally thread b picks token b's
+// winner among the ranks' pairs.  Without 16-byte alignment the host launches one CTA and it copies by floats.
+constexpr int GATHER_MAX_CTAS = 32, GATHER_PIECES_PER_CTA = 2048;
 struct GatherPeers { float *dst[8]; uint32_t *flag[8]; Best *pairs[8]; };
 __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers pe, const float *__restrict__ src, int batch, int64_t n,
                                                               int64_t ld, int64_t row0, int rank, int world,
                                                               const uint32_t *__restrict__ flags, const Best *__restrict__ my_pairs,
-                                                              uint32_t step, int32_t *__restrict__ argmax, int32_t *__restrict__ status) {
+                                                              uint32_t step, int32_t *__restrict__ argmax, int32_t *__restrict__ status,
+                                                              Best *__restrict__ partials, unsigned *__restrict__ counter) {
     __shared__ Best red[32];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, ncta = gridDim.x, cta = blockIdx.x;
     const bool vec = (n % 4 == 0) && (ld % 4 == 0) && (row0 % 4 == 0) && (((uintptr_t)src & 15) == 0);
     for (int b = 0; b < batch; ++b) {
         const float *s = src + (int64_t)b * ld;
         Best best = {-INFINITY, INT64_MAX};
         if (vec) {
-            // 4 independent 16-byte loads in flight per thread: one CTA has to keep a third of a megabyte moving
-            const int64_t n4 = n / 4, stride = blockDim.x;
-            for (int64_t i0 = tid; i0 < n4; i0 += 4 * stride) {
+            // up to 4 independent 16-byte loads in flight per thread
+            const int64_t n4 = n / 4, per = (n4 + ncta - 1) / ncta, lo = cta * per, hi = min(n4, lo + per), stride = blockDim.x;
+            for (int64_t i0 = lo + tid; i0 < hi; i0 += 4 * stride) {
                 float4 v[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int64_t i = i0 + u * stride;
-                    v[u] = i < n4 ? __ldcg((const float4 *)s + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                    v[u] = i < hi ? __ldcg((const float4 *)s + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int64_t i = i0 + u * stride;
-                    if (i >= n4) continue;
+                    if (i >= hi) continue;
                     for (int p = 0; p < world; ++p)
                         if (p != rank) ((float4 *)(pe.dst[p] + (int64_t)b * ld))[i] = v[u];
                     best = better(best, Best{v[u].x, 4 * i});
@@ -79,7 +85,7 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
                     best = better(best, Best{v[u].w, 4 * i + 3});
                 }
             }
-        } else {
+        } else if (cta == 0) {
             for (int64_t i = tid; i < n; i += blockDim.x) {
                 const float v = s[i];
                 for (int p = 0; p < world; ++p)
@@ -99,9 +105,33 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
                 Best other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
                 best = better(best, other);
             }
-            if (lane < world) pe.pairs[lane][b] = Best{best.v, best.i == INT64_MAX ? row0 : row0 + best.i}; // this rank's pair, to rank `lane`
+            if (lane == 0) partials[cta * 2 + b] = best;
         }
         __syncthreads();
+    }
+    __threadfence_system();     // this CTA's peer stores and its partials, before it counts itself in
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(counter, 1u);
+        s_last = prev == (unsigned)ncta - 1 ? 1 : 0;
+        if (s_last) *counter = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    if (warp == 0) {
+        for (int b = 0; b < batch; ++b) {
+            Best best = {-INFINITY, INT64_MAX};
+            if (lane < ncta) {
+                best.v = __ldcg(&partials[lane * 2 + b].v);
+                best.i = __ldcg(&partials[lane * 2 + b].i);
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                Best other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+                best = better(best, other);
+            }
+            if (lane < world) pe.pairs[lane][b] = Best{best.v, best.i == INT64_MAX ? row0 : row0 + best.i}; // this rank's pair, to rank `lane`
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -151,11 +181,15 @@ extern "C" int32_t mk_gather_create(mk_ctx *ctx, int32_t rank, int32_t world, in
     g->blob_bytes = g->logits_off + (size_t)2 * max_batch * vocab * 4;
     cudaError_t e = cudaMalloc(&g->blob, g->blob_bytes);
     if (e == cudaSuccess) e = cudaMemset(g->blob, 0, g->blob_bytes);
+    const size_t scratch_bytes = (size_t)GATHER_MAX_CTAS * 2 * sizeof(Best) + 256;
+    if (e == cudaSuccess) e = cudaMalloc(&g->scratch, scratch_bytes);
+    if (e == cudaSuccess) e = cudaMemset(g->scratch, 0, scratch_bytes);
     cudaIpcMemHandle_t h;
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, g->blob);
     if (e != cudaSuccess) {
         mk_set_error("mk_gather_create: %s", cudaGetErrorString(e));
         if (g->blob) cudaFree(g->blob);
+        if (g->scratch) cudaFree(g->scratch);
         delete g;
         return e == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA;
     }
@@ -202,6 +236,7 @@ extern "C" int32_t mk_gather_free(mk_ctx *ctx, mk_gather *g) {
     for (int r = 0; r < g->world; ++r)
         if (r != g->rank && g->peer[r] && !g->is_absent[r]) cudaIpcCloseMemHandle(g->peer[r]);
     if (g->absent) cudaFree(g->absent);
+    if (g->scratch) cudaFree(g->scratch);
     if (g->blob) cudaFree(g->blob);
     delete g;
     return MK_OK;
@@ -242,9 +277,17 @@ extern "C" int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_g
     }
     {
         mk_prof_scope prof(ctx, MK_PROF_OTHER);
-        gather_exchange_kernel<<<1, 1024, 0, ctx->stream>>>(pe, full + row0, batch, w->rows, g->vocab, row0, g->rank, g->world,
-                                                           (const uint32_t *)g->blob + par * 8, (const Best *)((char *)g->blob + pairs_off),
-                                                           g->step, argmax, ctx->status_dev);
+        // several CTAs when the slice can move in 16-byte pieces (the kernel's own test, repeated here)
+        const bool vec = w->rows % 4 == 0 && g->vocab % 4 == 0 && row0 % 4 == 0 && (((uintptr_t)(full + row0)) & 15) == 0;
+        int64_t ncta = vec ? mk_ceil_div(w->rows / 4, GATHER_PIECES_PER_CTA) : 1;
+        if (ncta > GATHER_MAX_CTAS) ncta = GATHER_MAX_CTAS;
+        if (ncta < 1) ncta = 1;
+        Best *partials = (Best *)g->scratch;
+        unsigned *counter = (unsigned *)((char *)g->scratch + (size_t)GATHER_MAX_CTAS * 2 * sizeof(Best));
+        gather_exchange_kernel<<<(unsigned)ncta, 1024, 0, ctx->stream>>>(pe, full + row0, batch, w->rows, g->vocab, row0, g->rank, g->world,
+                                                                        (const uint32_t *)g->blob + par * 8,
+                                                                        (const Best *)((char *)g->blob + pairs_off), g->step, argmax,
+                                                                        ctx->status_dev, partials, counter);
         ctx->launches++;
     }
     MK_CUDA(cudaGetLastError());
