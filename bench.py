@@ -73,9 +73,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([time.time()] + [c.strip() for c in line.split(",")])
 
-    def stop(self):
+    def stop(self, window=None):
+        """Median SM clock and the throttle reasons seen; `window` = (t0, t1) wall-clock seconds keeps only the
+        samples taken while the load ran (all samples if none fell inside)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -85,7 +87,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        rows = self.rows
+        inside = [r for r in rows if window and window[0] <= r[0] <= window[1]]
+        where = "under load" if inside else "whole run"
+        for r in (inside or rows):
+            r = r[1:]
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -95,7 +101,7 @@ class ClockSampler:
             except (ValueError, IndexError):
                 continue
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": where}
 
 
 # ---------------------------------------------------------------- CPU legs (the oracle is the thing timed here)
@@ -161,6 +167,9 @@ def run_gpu(args):
     mk.Context._default = ctx
     ctx.use_torch_stream()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()          # nvidia-smi needs a second to start: begin before the weights are made
     batch = args.batch
     rows = VOCAB // world
     shard_bytes = rows * HIDDEN + rows * (HIDDEN // 32) * 4
@@ -217,9 +226,6 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()          # nvidia-smi needs a moment to start: begin before the warm-up
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -245,6 +251,7 @@ def run_gpu(args):
     ctx.prof_enable(True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_load0 = time.time()
     e0.record()
     for i in range(args.steps):
         step(i)
@@ -263,6 +270,12 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
+    # the timed region may be shorter than nvidia-smi's sampling period: the same steps go on, untimed, for about
+    # a second, and the clocks reported are the samples taken between the start of the timed region and here
+    for i in range(int(min(20000, max(1, 1.0 / (ms_step * 1e-3))))):
+        step(i)
+    barrier()
+    t_load1 = time.time()
 
     # ---- end to end through the host-pointer entry point (pinned host buffers)
     xh = torch.empty((batch, HIDDEN), dtype=torch.float32).pin_memory()
@@ -302,7 +315,7 @@ def run_gpu(args):
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_dt = float(te.item())
-    clocks = sampler.stop() if rank == 0 else None   # covers warm-up, the timed region and the end-to-end loop
+    clocks = sampler.stop((t_load0, t_load1)) if rank == 0 else None
 
     alg_step = algorithmic_bytes(rows, HIDDEN, batch) * world
     value = alg_step / (ms_step * 1e-3) / 1e9
