@@ -1,8 +1,8 @@
 """Generates the committed golden fixtures from the reference checkout.
 
-Run once where the reference project is mounted (default /root/reference):
+Run once where the reference project's checkout is at hand:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It (1) extracts the vectors the reference's own `selftest` consumes for this
 path from ref/ds_golden.json (fp4 block and fp8 block, src/selftest.rs:205-234) and
@@ -19,7 +19,9 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+REF = sys.argv[1]
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
