@@ -283,11 +283,15 @@ def run_gpu(args):
     xn = xh.numpy()
     e2e_steps = max(10, min(args.steps, 100))
     if fused is None:
-        heads[0].matvec(xn, want_argmax=True)
+        # caller-owned pinned result buffers, as the engine passes `out: &mut [f32]`
+        yp = torch.empty((batch, rows), dtype=torch.float32).pin_memory()
+        ap = torch.empty((batch,), dtype=torch.int32).pin_memory()
+        yn, an = yp.numpy(), ap.numpy()
+        heads[0].matvec(xn, want_argmax=True, out=yn, argmax_out=an)
         barrier()
         t0 = time.perf_counter()
         for i in range(e2e_steps):
-            yh, amh = heads[i % copies].matvec(xn, want_argmax=True)
+            yh, amh = heads[i % copies].matvec(xn, want_argmax=True, out=yn, argmax_out=an)
         torch.cuda.synchronize()
         e2e_dt = (time.perf_counter() - t0) / e2e_steps
     else:
@@ -347,7 +351,7 @@ def run_gpu(args):
             "cpu_baseline": cb,
             "e2e": {"value": alg_step / e2e_dt / 1e9, "unit": "GB/s", "ms_per_step": e2e_dt * 1e3,
                     "h2d_bytes_per_step": batch * HIDDEN * 4, "d2h_bytes_per_step": batch * rows * 4 + batch * 4,
-                    "api": "mk_matvec_q8 (host pointers, pinned)" if fused is None else
+                    "api": "mk_matvec_q8 (host pointers: pinned x, pinned logits and token id)" if fused is None else
                            "pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank"},
             "gpu_launches": launches,
             "status_word": status_all,

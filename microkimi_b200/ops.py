@@ -397,10 +397,16 @@ class Q8Head(_Weight):
         _l.check(ctx._L.mk_weight_q8(ctx._h, _np_ptr(q), _np_ptr(scales), rows, cols, st, 0, C.byref(h)))
         return cls(ctx, h, rows, cols, st)
 
-    def matvec(self, x, act="q8", strict=False, want_argmax=False):
-        """Q8Head::matvec: logits [rows] (or [batch, rows]); optionally the greedy pick."""
+    def matvec(self, x, act="q8", strict=False, want_argmax=False, out=None, argmax_out=None):
+        """Q8Head::matvec: logits [rows] (or [batch, rows]); optionally the greedy pick.  Host arrays only: `out`
+        (float32 [batch, rows]) and `argmax_out` (int32 [batch]) are caller-owned result buffers, as the engine's
+        `out: &mut [f32]` is; views of pinned memory spare the staging copy of a pageable destination."""
         L = self.ctx._L
         batch, y, fn, args = self._run(L.mk_matvec_q8, L.mk_matvec_q8_dev, x, act, strict)
+        if out is not None:
+            assert not _is_torch_cuda(x) and out.dtype == np.float32 and out.flags.c_contiguous and out.size == batch * self.rows
+            y = out.reshape(batch, self.rows)
+            args = (args[0], _np_ptr(y)) + tuple(args[2:])
         am = None
         if want_argmax:
             if _is_torch_cuda(x):
@@ -409,7 +415,8 @@ class Q8Head(_Weight):
                 am = torch.empty(batch, dtype=torch.int32, device=x.device)
                 amp = C.c_void_p(am.data_ptr())
             else:
-                am = np.empty(batch, np.int32)
+                am = np.empty(batch, np.int32) if argmax_out is None else argmax_out
+                assert am.dtype == np.int32 and am.size == batch
                 amp = _np_ptr(am)
         else:
             amp = C.c_void_p(0)

@@ -234,6 +234,12 @@ def test_q8_head_batched(mk, batch):
         assert np.array_equal(bits(ys[t]), bits(ref))
         assert int(am[t]) == O.argmax(ref)
         assert rel(yd[t], ref) <= 1e-5
+    # caller-owned result buffers (the engine's `out: &mut [f32]`), here views of pinned memory
+    import torch
+    yp, ap = torch.empty((batch, rows), dtype=torch.float32).pin_memory(), torch.empty(batch, dtype=torch.int32).pin_memory()
+    y2, am2 = head.matvec(xs, strict=True, want_argmax=True, out=yp.numpy(), argmax_out=ap.numpy())
+    assert np.array_equal(bits(yp.numpy()), bits(ys)) and np.array_equal(ap.numpy(), am)
+    assert np.shares_memory(y2, yp.numpy())
 
 
 def test_q8_head_prequantized_rows_and_argmax_ties(mk):
