@@ -394,12 +394,33 @@ def run_case_mxfp4(args):
     torch.cuda.synchronize()
     n, kms = ctx.prof_read("matvec_mxfp4")
     ctx.prof_enable(False)
+    # the same ring of calls as ONE CUDA graph (activation quantization + GEMV per matrix): what a decode loop that
+    # replays its token pays per call, without the host's launch cost
+    graph_us = None
+    if args.graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(args.copies):
+                ws[i].matvec(x, act=args.act)
+        ctx.use_torch_stream()
+        reps = max(3, args.steps // args.copies)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(reps):
+            g.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        graph_us = g0.elapsed_time(g1) / (reps * args.copies) * 1e3
     alg = rows * cols // 2 + rows * cols // 32 + batch * (cols + rows) * 4
     peak, kind = measured_peaks()
     ach = alg / (kms / n * 1e-3) / 1e9
     print(json.dumps({"case": "mxfp4_gemv", "rows": rows, "cols": cols, "batch": batch, "copies": args.copies,
                       "act": args.act, "ms_per_step": e0.elapsed_time(e1) / args.steps, "kernel_us": kms / n * 1e3,
-                      "algorithmic_bytes": alg,
+                      "graph_us_per_call": graph_us, "graph_gbs": (alg / (graph_us * 1e-6) / 1e9) if graph_us else None,
+                      "algorithmic_bytes": alg, "status_word": ctx.status_word(),
                       "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                                    "peak_kind": kind}}), flush=True)
 
@@ -464,9 +485,27 @@ def run_case_moe(args):
     n_e, ms_e = ctx.prof_read("experts")
     n_r, ms_r = ctx.prof_read("router")
     ctx.prof_enable(False)
+    graph_ms = None
+    if args.graph:   # `copies` layer calls as one CUDA graph: the layer without the host's launch cost
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for l in layers:
+                l.moe_forward(x)
+        ctx.use_torch_stream()
+        reps = max(3, args.steps // args.copies)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(reps):
+            g.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        graph_ms = g0.elapsed_time(g1) / (reps * args.copies)
     peak, kind = measured_peaks()
     ach = alg / (ms * 1e-3) / 1e9
-    print(json.dumps({"case": "moe", "experts": E, "top_k": k, "batch": B, "copies": args.copies,
+    print(json.dumps({"case": "moe", "graph_ms_per_layer": graph_ms, "status_word": ctx.status_word(), "experts": E, "top_k": k, "batch": B, "copies": args.copies,
                       "distinct_experts_routed": distinct, "ms_per_layer": ms, "tokens_per_s": B / (ms * 1e-3),
                       "experts_ms": ms_e / args.steps if n_e else None, "router_ms": ms_r / args.steps if n_r else None,
                       "launches_per_call": launches, "algorithmic_bytes": alg,
@@ -631,6 +670,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--graph", action="store_true", help="--case mxfp4_gemv / moe: also time the ring of calls as one CUDA graph")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: logits by peer-memory stores from the matvec kernel (default) or by an NCCL all-gather")
     args = ap.parse_args()

@@ -312,3 +312,35 @@ def test_fp8_dequant_bit_exact(mk):
     nan = np.isnan(ref)
     assert np.array_equal(nan, np.isnan(got))
     assert np.array_equal(bits(got)[~nan], bits(ref)[~nan])
+
+
+def test_device_calls_replay_from_a_cuda_graph(mk):
+    """Device-pointer calls launch on the caller's stream and neither allocate nor synchronize once warm, so a
+    decode loop can capture them in a CUDA graph: the replay on new inputs gives the bits of the direct call."""
+    import torch
+    rng = np.random.default_rng(31)
+    rows, cols = 768, 1024
+    wf = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    p, s = O.mxfp4_quantize(wf)
+    ctx = mk.Context.default()
+    w = mk.MxFp4Weight(p, s, rows, cols)
+    head = mk.Q8Head.from_f32(wf, rows, cols)
+    f32w = mk.F32Weight(wf, rows, cols)
+    x = torch.from_numpy(rng.standard_normal((1, cols)).astype(np.float32)).cuda()
+    for _ in range(2):                      # warm: workspaces grow here, not under capture
+        w.matvec(x), head.matvec(x, want_argmax=True), f32w.matvec(x)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y1 = w.matvec(x)
+        y2, am = head.matvec(x, want_argmax=True)
+        y3 = f32w.matvec(x)
+    x2 = torch.from_numpy(rng.standard_normal((1, cols)).astype(np.float32)).cuda()
+    x.copy_(x2)
+    g.replay()
+    torch.cuda.synchronize()
+    got = [t.clone() for t in (y1, y2, am, y3)]
+    want = [w.matvec(x2), *head.matvec(x2, want_argmax=True), f32w.matvec(x2)]
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(got, want))
+    assert ctx.status_word() == 0
