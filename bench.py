@@ -606,9 +606,44 @@ def run_case_kda(args):
     ctx.prof_enable(False)
     ms = ms_k / max(n_k, 1)
     alg = H * D * D * 8 + 10 * proj * 4
+    block = None
+    if args.graph:
+        # the whole kda_forward of one layer (model width --rows, f_a rank 128): stacked projections, f_b, the step,
+        # o_proj = 4 launches; `copies` layers in rotation, from a host loop and as one CUDA graph
+        from microkimi_b200.blocks import KdaBlock
+        d, fa = args.rows, 128
+        g32 = lambda *shape: (rng.standard_normal(shape) * 0.05).astype(np.float32)
+        blocks = []
+        for _ in range(args.copies):
+            w = {"q_proj": g32(proj, d), "k_proj": g32(proj, d), "v_proj": g32(proj, d), "g_proj": g32(proj, d), "f_a": g32(fa, d),
+                 "f_b": g32(proj, fa), "b_proj": g32(H, d), "o_proj": g32(d, proj), "q_conv": g32(proj, 4), "k_conv": g32(proj, 4),
+                 "v_conv": g32(proj, 4), "a_log": np.log(rng.uniform(1, 16, D)).astype(np.float32), "dt_bias": g32(proj),
+                 "o_norm": np.ones(D, np.float32)}
+            blocks.append(KdaBlock(H, D, w, ctx=ctx))
+        xb = torch.randn(d, dtype=torch.float32, device=dev, generator=gen)
+        host_ms = _timed(torch, lambda i: blocks[i % args.copies].forward(xb), args.steps, args.warmup)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for b in blocks:
+                b.forward(xb)
+        ctx.use_torch_stream()
+        reps = max(3, args.steps // args.copies)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(reps):
+            g.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        wbytes = 4 * ((4 * proj + fa + H) * d + proj * fa + d * proj)
+        gus = g0.elapsed_time(g1) / (reps * args.copies) * 1e3
+        block = {"d": d, "launches": 4, "host_loop_us": host_ms * 1e3, "graph_us": gus, "weight_bytes": wbytes,
+                 "graph_gbs": (wbytes + alg) / (gus * 1e-6) / 1e9}
     peak, kind = measured_peaks()
     ach = alg / (ms * 1e-3) / 1e9
-    print(json.dumps({"case": "kda_step", "heads": H, "dim": D, "copies": args.copies, "kernel_us": ms * 1e3,
+    print(json.dumps({"case": "kda_step", "block": block, "heads": H, "dim": D, "copies": args.copies, "kernel_us": ms * 1e3,
                       "call_us_host_loop": ms_call * 1e3, "algorithmic_bytes": alg, "status_word": ctx.status_word(),
                       "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                                    "peak_kind": kind, "note": "latency-bound: one CTA per head"}}), flush=True)
