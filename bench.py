@@ -586,6 +586,8 @@ def run_case_kda(args):
     """Side workload: the KDA decode step (conv + SiLU, head norms, gate, recurrence, gated RMS) of `--heads`
     heads of width 128, `copies` layers in rotation (each layer's state S is heads x 64 KB); one launch per step."""
     torch, mk, ctx, dev = _side_ctx()
+    if args.kda_smem:
+        ctx.set_option("kda_smem", 1)
     H, D = args.heads, 128
     proj = H * D
     rng = np.random.default_rng(5)
@@ -643,7 +645,7 @@ def run_case_kda(args):
                  "graph_gbs": (wbytes + alg) / (gus * 1e-6) / 1e9}
     peak, kind = measured_peaks()
     ach = alg / (ms * 1e-3) / 1e9
-    print(json.dumps({"case": "kda_step", "block": block, "heads": H, "dim": D, "copies": args.copies, "kernel_us": ms * 1e3,
+    print(json.dumps({"case": "kda_step", "form": "shared memory" if args.kda_smem else "registers", "block": block, "heads": H, "dim": D, "copies": args.copies, "kernel_us": ms * 1e3,
                       "call_us_host_loop": ms_call * 1e3, "algorithmic_bytes": alg, "status_word": ctx.status_word(),
                       "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                                    "peak_kind": kind, "note": "latency-bound: one CTA per head"}}), flush=True)
@@ -698,6 +700,7 @@ def main():
     ap.add_argument("--experts", type=int, default=384)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=4, help="--case kda: KDA heads of width 128")
+    ap.add_argument("--kda-smem", action="store_true", help="--case kda: the shared-memory form of the step kernel (default at width 128: registers)")
     ap.add_argument("--layout", default="absorbed", choices=["absorbed", "per_head"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)

@@ -90,6 +90,8 @@ int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
  *                quantize launches of large batches instead of the fused router kernel.
  *   "mla_max_split": upper bound on the KV splits of an attention call, 0 = automatic
  *                (fewer splits = more tiles per CTA; used by the tests).
+ *   "kda_smem": 1 = the KDA step stages S in shared memory (short loops) also for kda_dim 64 and 128,
+ *                where the default keeps each column in registers (fully unrolled); same bits.
  *   "mla_no_t5": 1 = absorbed-layout attention on the mma.sync kernel instead of the
  *                tcgen05 (tensor-memory) kernel.
  *   "mla_no_tc": 1 = run attention on the generic one-warp-per-head CUDA-core kernel

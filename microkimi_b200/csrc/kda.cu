@@ -195,6 +195,108 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
     if (active) a.o[i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), onv), g2v);
 }
 
+// The same step with the head's S [dim][dim] staged in shared memory by cp.async at kernel start (dim % 4 == 0,
+// dim <= 224): both passes become short loops that stay in the instruction cache, the column is read from shared
+// memory twice (conflict-free: consecutive threads, consecutive words) and written to global memory once.  The
+// decayed value x * decay is formed twice with the same operands, so the bits equal the register form's.
+template <int KC>
+__global__ void __launch_bounds__(256) kda_step_smem_kernel(KdaArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int dim = a.dim;
+    float *xs = sm, *qs = xs + (size_t)dim * dim, *ks = qs + dim, *ds = ks + dim, *bks = ds + dim, *red = bks + dim;
+    const int h = blockIdx.x, c = threadIdx.x, lane = c & 31, warp = c >> 5, nwarps = blockDim.x >> 5;
+    const bool active = c < dim;
+    const int64_t proj = (int64_t)a.heads * dim, i = (int64_t)h * dim + c;
+    const int64_t wq = 0, wk = proj * a.kconv, wv = 2 * proj * a.kconv;
+    const int64_t cq = 0, ck = (int64_t)(a.kconv - 1) * proj, cv = 2 * (int64_t)(a.kconv - 1) * proj;
+    float *S = a.s + (int64_t)h * dim * dim;
+    for (int idx = c; idx < dim * dim / 4; idx += blockDim.x) mkf::cp16(xs + idx * 4, S + idx * 4);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    float vv = 0.0f, g2v = 0.0f, onv = 0.0f, bh = 0.0f;
+    if (active) {
+        float glow, dtb, alog;
+        ConvIn<KC> iq, ik, iv;
+        if constexpr (KC > 0) {
+            iq.load(a.conv_w + wq, a.conv + cq, proj, i, a.q_raw);
+            ik.load(a.conv_w + wk, a.conv + ck, proj, i, a.k_raw);
+            iv.load(a.conv_w + wv, a.conv + cv, proj, i, a.v_raw);
+        }
+        glow = a.g_low[i]; dtb = a.dt_bias[i]; alog = a.a_log[c];
+        g2v = a.g2[i]; onv = a.o_norm[c]; bh = a.beta_raw[h];
+        if constexpr (KC > 0) {
+            qs[c] = iq.apply(a.conv + cq, proj, i);
+            ks[c] = ik.apply(a.conv + ck, proj, i);
+            vv = iv.apply(a.conv + cv, proj, i);
+        } else {
+            qs[c] = conv_channel(a.conv_w + wq, a.conv + cq, proj, i, a.kconv, a.q_raw[i]);
+            ks[c] = conv_channel(a.conv_w + wk, a.conv + ck, proj, i, a.kconv, a.k_raw[i]);
+            vv = conv_channel(a.conv_w + wv, a.conv + cv, proj, i, a.kconv, a.v_raw[i]);
+        }
+        const float g = __fmul_rn(a.gate_lb, sigmoid_cr(__fmul_rn(exp_cr(alog), __fadd_rn(glow, dtb))));
+        ds[c] = exp_cr(g);
+        bh = sigmoid_cr(bh);
+        g2v = sigmoid_cr(g2v);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float n2 = warp_sumsq(qs, dim, lane);
+        if (lane == 0) red[0] = __fdiv_rn(a.q_scale, fmaxf(__fsqrt_rn(n2), 1e-12f));
+    }
+    if (warp == nwarps - 1) {
+        const float n2 = warp_sumsq(ks, dim, lane);
+        if (lane == 0) red[1] = __fdiv_rn(1.0f, fmaxf(__fsqrt_rn(n2), 1e-12f));
+    }
+    __syncthreads();
+    if (active) {
+        qs[c] = __fmul_rn(qs[c], red[0]);
+        const float kn = __fmul_rn(ks[c], red[1]);
+        ks[c] = kn;
+        bks[c] = __fmul_rn(bh, kn);     // beta * k[r], the same for every column
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    float o = 0.0f;
+    if (active) {
+        float delta = vv;
+        const float *xc = xs + c;
+#pragma unroll 4
+        for (int r = 0; r < dim; r += 4) {
+            const float4 d4 = *reinterpret_cast<const float4 *>(ds + r), k4 = *reinterpret_cast<const float4 *>(ks + r);
+            delta = __fsub_rn(delta, __fmul_rn(k4.x, __fmul_rn(xc[(r + 0) * dim], d4.x)));
+            delta = __fsub_rn(delta, __fmul_rn(k4.y, __fmul_rn(xc[(r + 1) * dim], d4.y)));
+            delta = __fsub_rn(delta, __fmul_rn(k4.z, __fmul_rn(xc[(r + 2) * dim], d4.z)));
+            delta = __fsub_rn(delta, __fmul_rn(k4.w, __fmul_rn(xc[(r + 3) * dim], d4.w)));
+        }
+        float *col = S + c;
+#pragma unroll 2
+        for (int r = 0; r < dim; r += 4) {
+            const float4 d4 = *reinterpret_cast<const float4 *>(ds + r), b4 = *reinterpret_cast<const float4 *>(bks + r);
+            const float4 q4 = *reinterpret_cast<const float4 *>(qs + r);
+            const float x0 = __fadd_rn(__fmul_rn(xc[(r + 0) * dim], d4.x), __fmul_rn(b4.x, delta));
+            const float x1 = __fadd_rn(__fmul_rn(xc[(r + 1) * dim], d4.y), __fmul_rn(b4.y, delta));
+            const float x2 = __fadd_rn(__fmul_rn(xc[(r + 2) * dim], d4.z), __fmul_rn(b4.z, delta));
+            const float x3 = __fadd_rn(__fmul_rn(xc[(r + 3) * dim], d4.w), __fmul_rn(b4.w, delta));
+            o = __fadd_rn(o, __fmul_rn(q4.x, x0));
+            o = __fadd_rn(o, __fmul_rn(q4.y, x1));
+            o = __fadd_rn(o, __fmul_rn(q4.z, x2));
+            o = __fadd_rn(o, __fmul_rn(q4.w, x3));
+            col[(int64_t)(r + 0) * dim] = x0;
+            col[(int64_t)(r + 1) * dim] = x1;
+            col[(int64_t)(r + 2) * dim] = x2;
+            col[(int64_t)(r + 3) * dim] = x3;
+        }
+    }
+    __syncthreads();
+    if (active) qs[c] = o;
+    __syncthreads();
+    if (warp == 0) {
+        const float ss = __fdiv_rn(warp_sumsq(qs, dim, lane), (float)dim);
+        if (lane == 0) red[2] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ss, a.rms_eps)));
+    }
+    __syncthreads();
+    if (active) a.o[i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), onv), g2v);
+}
+
 // ---- AttnRes: scores (one warp per row: blocks 0..b-1, then the prefix), then softmax + mix
 __global__ void __launch_bounds__(32) attn_res_score_kernel(const float *__restrict__ prefix, const float *__restrict__ blocks,
                                                            int64_t ld, int b, const float *__restrict__ w, int d, float eps,
@@ -330,7 +432,19 @@ extern "C" int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *k, const float *q_raw, c
     const size_t smem = (size_t)(3 * k->dim + 4) * sizeof(float);
     mk_prof_scope prof(ctx, MK_PROF_OTHER);
     const bool kc4 = k->kconv == 4;
-    if (k->dim == 128 && kc4)
+    const size_t smem_s = ((size_t)k->dim * k->dim + 4 * (size_t)k->dim + 4) * sizeof(float);
+    const bool reg_dim = k->dim == 64 || k->dim == 128;
+    if ((ctx->kda_smem || !reg_dim) && k->dim % 4 == 0 && k->dim >= 32 && k->dim <= 224) {
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(kda_step_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(kda_step_smem_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            attr = true;
+        }
+        const unsigned threads = (unsigned)mk_align_up(k->dim, 32);
+        if (kc4) kda_step_smem_kernel<4><<<k->heads, threads, smem_s, ctx->stream>>>(a);
+        else kda_step_smem_kernel<0><<<k->heads, threads, smem_s, ctx->stream>>>(a);
+    } else if (k->dim == 128 && kc4)
         kda_step_kernel<128, 4><<<k->heads, 128, smem, ctx->stream>>>(a);
     else if (k->dim == 128)
         kda_step_kernel<128, 0><<<k->heads, 128, smem, ctx->stream>>>(a);

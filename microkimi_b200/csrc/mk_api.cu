@@ -125,6 +125,10 @@ extern "C" int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value) {
         ctx->mla_max_split = (int)value;
         return MK_OK;
     }
+    if (strcmp(name, "kda_smem") == 0) {
+        ctx->kda_smem = value != 0;
+        return MK_OK;
+    }
     if (strcmp(name, "mla_no_t5") == 0) {
         ctx->mla_no_t5 = value != 0;
         return MK_OK;

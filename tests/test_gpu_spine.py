@@ -200,3 +200,28 @@ def test_attn_res_golden(mk):
     w = g["norm_w"] * g["proj_w"]
     got = mk.attn_res(torch.from_numpy(g["prefix"]).cuda(), torch.from_numpy(g["blocks"]).cuda(), torch.from_numpy(w).cuda(), 1e-5)
     assert (np.abs(got.cpu().numpy() - g["out"]) <= 1e-6 + 1e-4 * np.abs(g["out"])).all()
+
+
+def test_kda_step_shared_memory_form_equals_register_form(mk):
+    """kda_dim 64 / 128 run with each column of S in registers by default; the option "kda_smem" stages S in shared
+    memory instead (the form every other width divisible by 4 takes).  Same operations in the same order: same bits."""
+    import torch
+    rng = np.random.default_rng(77)
+    ctx = mk.Context.default()
+    for heads, dim in ((4, 128), (2, 64)):
+        cw, a_log, dt_bias, o_norm = _kda_params(rng, heads, dim, 4)
+        a, b = (mk.KdaLayer(heads, dim, *cw, a_log, dt_bias, o_norm) for _ in range(2))
+        proj = heads * dim
+        for t in range(4):
+            ins = [torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda() for n in (proj, proj, proj, proj, heads, proj)]
+            ya = a.step(*ins)
+            ctx.set_option("kda_smem", 1)
+            try:
+                yb = b.step(*ins)
+            finally:
+                ctx.set_option("kda_smem", 0)
+            assert torch.equal(ya, yb)
+        sa, ca = a.export_state()
+        sb, cb = b.export_state()
+        assert np.array_equal(bits(sa), bits(sb)) and np.array_equal(bits(ca), bits(cb))
+        a.free(), b.free()
