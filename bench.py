@@ -89,7 +89,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         rows = self.rows
         inside = [r for r in rows if window and window[0] <= r[0] <= window[1]]
-        where = "under load" if inside else "whole run"
+        where = "timed region + about 1 s of the same steps" if inside else "whole run"
         for r in (inside or rows):
             r = r[1:]
             try:
