@@ -259,6 +259,7 @@ def run_gpu(args):
     barrier()
     ms_total = e0.elapsed_time(e1)
     kn, kms = ctx.prof_read("lm_head")
+    xn_, xms_ = ctx.prof_read("other")     # N > 1, peer path: the exchange kernel (push, flags, wait, token pick)
     ctx.prof_enable(False)
     launches = ctx.launches - launches0
     st = torch.tensor([ctx.status_word()], dtype=torch.int32, device=dev)   # a bounded device-side wait that ran out sets it
@@ -354,6 +355,7 @@ def run_gpu(args):
                     "api": "mk_matvec_q8 (host pointers: pinned x, pinned logits and token id)" if fused is None else
                            "pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank"},
             "gpu_launches": launches,
+            **({"exchange_kernel_ms": xms_ / xn_} if (fused is not None and xn_) else {}),
             "status_word": status_all,
             "clocks": clocks,
         }
