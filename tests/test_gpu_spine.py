@@ -225,3 +225,28 @@ def test_kda_step_shared_memory_form_equals_register_form(mk):
         sb, cb = b.export_state()
         assert np.array_equal(bits(sa), bits(sb)) and np.array_equal(bits(ca), bits(cb))
         a.free(), b.free()
+
+
+def test_kda_and_attn_res_argument_errors(mk):
+    """Bad descriptors and pointers are refused with a status, nothing is launched."""
+    import ctypes as C
+    import torch
+    from microkimi_b200 import lib as L
+    rng = np.random.default_rng(5)
+    cw, a_log, dt_bias, o_norm = _kda_params(rng, 2, 64, 4)
+    big = _kda_params(rng, 1, 2048, 4)
+    with pytest.raises(L.MkError):
+        mk.KdaLayer(1, 2048, *big[0], *big[1:])                         # kda_dim above 1024
+    one = [c[:, :1].copy() for c in cw]
+    with pytest.raises(L.MkError):
+        mk.KdaLayer(2, 64, *one, a_log, dt_bias, o_norm, kconv=1)       # a conv of width 1 has no window
+    layer = mk.KdaLayer(2, 64, *cw, a_log, dt_bias, o_norm)
+    ctx = layer.ctx
+    v = torch.zeros(128, device="cuda")
+    with pytest.raises(L.MkError):
+        L.check(ctx._L.mk_kda_step_dev(ctx._h, layer._h, C.c_void_p(v.data_ptr()), None, None, None, None, None, C.c_void_p(v.data_ptr())))
+    with pytest.raises(L.MkError):
+        L.check(ctx._L.mk_attn_res_dev(ctx._h, C.c_void_p(v.data_ptr()), None, 128, 3, C.c_void_p(v.data_ptr()), 128, 1e-5,
+                                       C.c_void_p(v.data_ptr())))      # 3 blocks announced, no block rows given
+    assert ctx.status_word() == 0
+    layer.free()
