@@ -109,16 +109,21 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
         }
         __syncthreads();
     }
-    __threadfence_system();     // this CTA's peer stores and its partials, before it counts itself in
+    // Release by one thread for the CTA: the barrier orders every thread's peer stores and the partials before
+    // thread 0's system-wide fence (fences are cumulative), the fence before the count; the last CTA's thread 0
+    // fences again after it saw the full count (acquire side) and the second barrier hands that to its flag writers.
     __syncthreads();
     if (tid == 0) {
+        __threadfence_system();
         const unsigned prev = atomicAdd(counter, 1u);
         s_last = prev == (unsigned)ncta - 1 ? 1 : 0;
-        if (s_last) *counter = 0u;
+        if (s_last) {
+            *counter = 0u;
+            __threadfence_system();
+        }
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence_system();
     if (warp == 0) {
         for (int b = 0; b < batch; ++b) {
             Best best = {-INFINITY, INT64_MAX};
@@ -133,8 +138,8 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
             if (lane < world) pe.pairs[lane][b] = Best{best.v, best.i == INT64_MAX ? row0 : row0 + best.i}; // this rank's pair, to rank `lane`
         }
     }
-    __threadfence_system();
-    __syncthreads();
+    // thread r (a lane of warp 0) wrote rank r's pairs itself: its release store below orders them, and everything
+    // the barriers above made visible to it, before the flag
     if (tid < world) {
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pe.flag[tid]), "r"(step) : "memory");
         bool ok = false;

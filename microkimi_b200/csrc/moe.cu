@@ -604,16 +604,21 @@ __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, 
                 if (q != rank) ((float4 *)(pe.outs[q] + p * d))[i] = v;
         }
     }
-    __threadfence_system();
+    // Release by one thread for the CTA: the barrier orders every thread's peer stores before thread 0's system-wide
+    // fence (fences are cumulative), the fence before the count; the last CTA's thread 0 fences again after it saw the
+    // full count and the second barrier hands that to the flag writers, whose release stores carry it to the peers.
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const unsigned prev = atomicAdd(counter, 1u);
         s_last = prev == gridDim.x - 1 ? 1 : 0;
-        if (s_last) *counter = 0u;
+        if (s_last) {
+            *counter = 0u;
+            __threadfence_system();
+        }
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence_system();
     if ((int)threadIdx.x < world) {
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pe.flag[threadIdx.x]), "r"(step) : "memory");
         bool ok = false;
