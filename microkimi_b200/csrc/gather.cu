@@ -1,7 +1,8 @@
 // Vocabulary-sharded lm_head across the GPUs of one node without a collective library
 // call on the decode path.  The matvec kernel of rank r writes its logits rows into rank
-// r's own gather buffer; ONE exchange kernel (one CTA) then pushes that slice into the
-// gather buffers of all other ranks (peer memory over NVLink, 16-byte stores), fences,
+// r's own gather buffer; ONE exchange kernel (a few CTAs) then pushes that slice into the
+// gather buffers of all other ranks (peer memory over NVLink, 16-byte stores); each CTA ends
+// with a barrier and one system-wide fence and counts itself in, the last one to arrive
 // publishes this rank's step number in every rank's flag word (st.release.sys) and waits,
 // bounded, until all ranks have published the current step (ld.acquire.sys).
 // Measured alternative, rejected: storing the rows to the peers from the matvec kernel's own
