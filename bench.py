@@ -4,16 +4,20 @@
     python bench.py --gpus N --steps K --warmup W            (this library)
     python bench.py --impl reference --gpus N --steps K ...  (CPU restatement of the reference path)
 
-Workload: the q8_0 lm_head GEMV - W is vocab 163840 x hidden 7168 drawn from
+Headline workload: the q8_0 lm_head GEMV - W is vocab 163840 x hidden 7168 drawn from
 N(0, 0.02) and quantized row-wise to q8_0 (32-wide blocks, int8 values + one f32
 scale per block, the engine's layout); x is f32[7168] from N(0, 1); batch 1.  A
 step is one logits projection (activation quantization + GEMV + greedy argmax).
-With N > 1 GPUs the vocabulary is sharded V/N rows per rank and the f32 logits
-are all-gathered (NCCL); total work is fixed, so scaling is "strong".
+With N > 1 GPUs the vocabulary is sharded V/N rows per rank and the complete f32 logits
+reach every rank (peer-memory exchange kernel, or the NCCL all-gather with --collective nccl);
+total work is fixed, so scaling is "strong".
 
 metric = quantized GB/s: algorithmic bytes of one step (int8 values + block
 scales + x + logits) divided by the step time, summed over all ranks.
-Prints ONE JSON line on rank 0.
+Prints ONE JSON line on rank 0.  After the headline measurement the same line carries, under
+"extra", bounded runs of the other workloads of the path (single-expert MXFP4 GEMV, the MoE
+layer, absorbed MLA decode attention, the lm_head at batch 8; expert-parallel MoE at N > 1);
+--no-extra skips them.
 """
 import argparse
 import json
@@ -32,15 +36,27 @@ if ROOT not in sys.path:
 VOCAB, HIDDEN = 163840, 7168
 SIGMA_W = 0.02
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the lm_head kernel at N=1, from the
-# ncu capture summarised in profiles/lm_head_q8_gemv_163840x7168.md (1.321224 GB + 4.7 MB)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the lm_head kernel on one GPU holding the whole
+# matrix, from an ncu capture of this command (1.321224 GB read + 4.7 MB written); a constant, not re-measured per run
 NCU_TRAFFIC_PER_LAUNCH_N1 = 1.3259e9
 CPU_SAMPLE_ROWS = 32768  # bounded sample of the workload for the CPU legs (235 MB of int8, > any LLC)
+METRIC = "quantized GB/s, q8_0 lm_head GEMV"
+ACT_MODE = "q8 (the engine's default integer path: q8_0 activation, exact int32 block dots, f32 rescale)"
 
 
 def algorithmic_bytes(rows, cols, batch, scale_bytes=4):
     """int8 values + block scales + x (f32) + logits (f32), per step."""
     return rows * cols + rows * (cols // 32) * scale_bytes + batch * cols * 4 + batch * rows * 4
+
+
+def workload_config(world, batch):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": f"q8_0 lm_head GEMV {VOCAB}x{HIDDEN} (f32 block scales), batch {batch}, vocab-sharded {world} way(s)"
+                        + ("" if world == 1 else ", complete f32 logits on every rank"),
+            "batch": batch, "rows_per_gpu": VOCAB // world, "act_mode": ACT_MODE,
+            "l2": "inputs larger than L2: every timed pass streams a weight shard that is not resident "
+                  "(shards below 4 x L2 rotate over copies until they exceed it)",
+            "algorithmic_bytes_per_step": algorithmic_bytes(VOCAB // world, HIDDEN, batch) * world}
 
 
 def measured_peaks():
@@ -51,6 +67,16 @@ def measured_peaks():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def measured_tflops():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -89,7 +115,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         rows = self.rows
         inside = [r for r in rows if window and window[0] <= r[0] <= window[1]]
-        where = "timed region + about 1 s of the same steps" if inside else "whole run"
+        where = "timed regions + about 1 s of the same steps" if inside else "whole run"
         for r in (inside or rows):
             r = r[1:]
             try:
@@ -106,10 +132,12 @@ class ClockSampler:
 
 # ---------------------------------------------------------------- CPU legs (the oracle is the thing timed here)
 def cpu_leg(steps, warmup, rows=CPU_SAMPLE_ROWS):
-    """Times the CPU restatement of Q8Head::matvec (all host threads) on a bounded
-    sample of the workload: the first `rows` vocabulary rows."""
+    """Times the CPU restatement of Q8Head::matvec on a bounded sample of the workload: the first `rows`
+    vocabulary rows.  All host cores this process may use, counted from its affinity mask - not from
+    OMP_NUM_THREADS, which torchrun sets to 1 for its children."""
     from oracle import oracle as O
-    threads = O.num_threads()
+    threads = O.host_threads()
+    O.set_num_threads(threads)
     rng = np.random.default_rng(1234)
     w = rng.standard_normal((rows, HIDDEN), dtype=np.float32) * np.float32(SIGMA_W)
     q, s = O.q8head_from_f32(w)
@@ -123,27 +151,295 @@ def cpu_leg(steps, warmup, rows=CPU_SAMPLE_ROWS):
     dt = (time.perf_counter() - t0) / steps
     gbs = algorithmic_bytes(rows, HIDDEN, 1) / dt / 1e9
     return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"first {rows} of {VOCAB} vocabulary rows x {HIDDEN}, batch 1, {steps} steps, "
-                      f"C restatement of Q8Head::matvec with {threads} OpenMP threads"}, dt
+            "sample": f"first {rows} of {VOCAB} vocabulary rows x {HIDDEN}, batch 1, {steps} steps after {max(1, warmup)} "
+                      f"warm-up, C restatement of Q8Head::matvec (src/model.rs:290-335) with {threads} OpenMP threads"}, dt
 
 
 def run_reference(args):
+    """The reference arm: the engine's own CPU implementation of the path.  The engine is Rust and no Rust
+    toolchain exists on this machine, so the arm times the line-by-line C restatement of Q8Head::matvec
+    (the oracle) with all host threads.  Under torchrun rank 0 alone runs; the others leave at once."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = min(args.steps, 40)
-    cb, dt = cpu_leg(steps, min(args.warmup, 3))
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    cb, dt = cpu_leg(args.steps, args.warmup)
     line = {
-        "impl": "reference", "metric": "quantized GB/s, q8_0 lm_head GEMV", "value": cb["value"], "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3,
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "q8_0 lm_head GEMV 163840x7168 batch 1 (CPU: bounded sample of the rows)",
-                   "rows_sampled": CPU_SAMPLE_ROWS},
+        "config": workload_config(world, args.batch),
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- helpers shared by the workloads
+def _timed(torch, fn, steps, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _graph_time(torch, ctx, body, calls, reps):
+    """`body()` enqueues `calls` library calls; they are captured as ONE CUDA graph and replayed: what a decode
+    loop that replays its token pays per call, without the host's launch cost.  Returns ms per call."""
+    body()                                   # first-use set-up (workspace growth, attributes) stays outside the capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    ctx.use_torch_stream()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(reps):
+        g.replay()
+    g1.record()
+    torch.cuda.synchronize()
+    return g0.elapsed_time(g1) / (reps * calls)
+
+
+def _rand_mxfp4(torch, mk, ctx, gen, dev, rows, cols):
+    """Synthetic MXFP4 matrix: uniform codes, scale bytes 118..123 (the kernels' speed does not depend on values)."""
+    p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
+    s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
+    return mk.MxFp4Weight(p, s, rows, cols, ctx=ctx)
+
+
+def _roof(alg_bytes, ms, note=None):
+    peak, kind = measured_peaks()
+    ach = alg_bytes / (ms * 1e-3) / 1e9
+    r = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind}
+    if note:
+        r["note"] = note
+    return r
+
+
+# ---------------------------------------------------------------- workloads beside the headline
+def measure_mxfp4_gemv(torch, mk, ctx, dev, rows=7168, cols=2048, batch=1, copies=128, steps=256, warmup=20, act="q8",
+                       graph=True):
+    """One MXFP4 matvec (the down-projection of one expert, 7168 x 2048 by default) over `copies` rotating matrices,
+    so that every call reads a matrix that is not in L2."""
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    ws = [_rand_mxfp4(torch, mk, ctx, gen, dev, rows, cols) for _ in range(copies)]
+    x = torch.randn((batch, cols), dtype=torch.float32, device=dev, generator=gen)
+    ms_call = _timed(torch, lambda i: ws[i % copies].matvec(x, act=act), steps, warmup)
+    ctx.prof_enable(True)
+    _timed(torch, lambda i: ws[i % copies].matvec(x, act=act), steps, 0)
+    n, kms = ctx.prof_read("matvec_mxfp4")
+    ctx.prof_enable(False)
+    graph_us = None
+    if graph:
+        def body():
+            for w in ws:
+                w.matvec(x, act=act)
+        graph_us = _graph_time(torch, ctx, body, copies, max(3, steps // copies)) * 1e3
+    alg = rows * cols // 2 + rows * cols // 32 + batch * (cols + rows) * 4
+    out = {"workload": f"MXFP4 GEMV {rows}x{cols}, batch {batch}, ring of {copies} cold matrices", "act": act,
+           "us_per_call_host_loop": ms_call * 1e3, "kernel_us": kms / max(n, 1) * 1e3, "graph_us_per_call": graph_us,
+           "algorithmic_bytes": alg, "status_word": ctx.status_word(),
+           "roofline": _roof(alg, (graph_us * 1e-3) if graph_us else ms_call,
+                             "whole call (activation quantization + GEMV) " + ("inside a CUDA graph" if graph_us else "from a host loop"))}
+    for w in ws:
+        w.free()
+    return out
+
+
+def build_moe_layers(torch, mk, ctx, dev, experts, copies, seed=3):
+    E, k, d, inter = experts, 8, 7168, 2048
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    layers = []
+    for _ in range(copies):
+        ex = [tuple(_rand_mxfp4(torch, mk, ctx, gen, dev, r, c) for r, c in ((inter, d), (d, inter), (inter, d)))
+              for _ in range(E + 1)]
+        gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
+        layers.append(mk.MoeLayer(gw, None, ex[:-1], ex[-1], k, ctx=ctx))
+    return layers, gen
+
+
+def free_moe_layers(layers):
+    for l in layers:
+        ex, sh = l._keep[0], l._keep[1]
+        l.free()
+        for tri in list(ex) + [sh]:
+            if tri is not None:
+                for w in tri:
+                    w.free()
+
+
+def measure_moe(torch, mk, ctx, dev, layers, gen, batch, steps, warmup, graph=False):
+    """One MoE FFN layer: 384 routed MXFP4 experts + 1 shared, top-8, hidden 7168, intermediate 2048, sigmoid router;
+    tokens N(0,1).  `layers` rotate so that the timed passes stay cold in L2."""
+    E, k, d, inter, copies = layers[0].n_experts, 8, 7168, 2048, len(layers)
+    x = torch.randn((batch, d), dtype=torch.float32, device=dev, generator=gen)
+    _, ids, _ = layers[0].moe_forward(x, want_routing=True)
+    distinct = int(torch.unique(ids).numel())
+    per_expert = 3 * (inter * d // 2 + inter * d // 32)
+    alg = E * d * 4 + (distinct + 1) * per_expert + 2 * batch * d * 4
+    ms = _timed(torch, lambda i: layers[i % copies].moe_forward(x), steps, warmup)
+    l0 = ctx.launches
+    layers[0].moe_forward(x)
+    launches = ctx.launches - l0
+    ctx.prof_enable(True)
+    _timed(torch, lambda i: layers[i % copies].moe_forward(x), steps, 0)
+    n_e, ms_e = ctx.prof_read("experts")
+    n_r, ms_r = ctx.prof_read("router")
+    ctx.prof_enable(False)
+    graph_ms = None
+    if graph:
+        def body():
+            for l in layers:
+                l.moe_forward(x)
+        graph_ms = _graph_time(torch, ctx, body, copies, max(3, steps // copies))
+    return {"workload": f"MoE layer {E}+1 MXFP4 experts, top-{k}, {d}x{inter}, batch {batch}, {copies} rotating layers",
+            "batch": batch, "distinct_experts_routed": distinct, "ms_per_layer": ms, "graph_ms_per_layer": graph_ms,
+            "tokens_per_s": batch / (ms * 1e-3), "experts_ms": ms_e / steps if n_e else None,
+            "router_ms": ms_r / steps if n_r else None, "launches_per_call": launches, "algorithmic_bytes": alg,
+            "status_word": ctx.status_word(), "roofline": _roof(alg, ms, "whole layer call, not one kernel")}
+
+
+def measure_mla(torch, mk, ctx, dev, layout, ctx_len, batch, steps, warmup):
+    """q8_0 MLA decode attention, 64 heads.  absorbed: one shared 512+64 latent row per position (648 B with f32
+    scales); per_head: the engine's layout at nope 128 / rope 64 / v 128 (18,688 B per position).  Cache rows N(0,1),
+    `batch` independent sequences of `ctx_len` positions, softmax scale 1/sqrt(192)."""
+    H, B, n = 64, batch, ctx_len
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4)
+    if layout == "absorbed":
+        cache = mk.MlaCache(H, 576, 0, 512, n, n_seqs=B, layout="absorbed", ctx=ctx)
+        qdim, per_pos = 576, 576 + 18 * 4
+        for s_ in range(B):
+            for lo in range(0, n, 8192):
+                m = min(8192, n - lo)
+                cache.push(torch.randn((m, 576), dtype=torch.float32, device=dev, generator=gen), seq=s_)
+    else:
+        cache = mk.MlaCache(H, 128, 64, 128, n, n_seqs=B, ctx=ctx)
+        qdim, per_pos = 192, H * 128 + H * 4 * 4 + 64 * 4 + H * 128 + H * 4 * 4
+        for s_ in range(B):
+            for lo in range(0, n, 1024):
+                m = min(1024, n - lo)
+                kk = torch.randn((m, H, 192), dtype=torch.float32, device=dev, generator=gen)
+                vv = torch.randn((m, H, 128), dtype=torch.float32, device=dev, generator=gen)
+                cache.push(kk, vv, seq=s_)
+    q = torch.randn((B, H, qdim), dtype=torch.float32, device=dev, generator=gen)
+    scale = 1.0 / np.sqrt(192.0)
+    ms = _timed(torch, lambda i: cache.attend_batch(q, scale), steps, warmup)
+    alg = B * n * per_pos + B * H * (qdim + cache.vd) * 4
+    flops = B * n * 2 * H * (qdim + cache.vd) if layout == "absorbed" else B * n * 2 * H * (192 + 128)
+    tf = flops / (ms * 1e-3) / 1e12
+    tpeak, tkind = measured_tflops()
+    out = {"workload": f"q8_0 MLA decode attention, {layout} layout, 64 heads, ctx {n}, batch {B}", "ms_per_call": ms,
+           "algorithmic_bytes": alg, "tflops": tf, "frac_of_bf16_peak": tf / tpeak, "bf16_peak": tpeak, "bf16_peak_kind": tkind,
+           "status_word": ctx.status_word(),
+           "roofline": _roof(alg, ms, "cache smaller than L2 stays resident between calls" if alg < L2_BYTES else None)}
+    cache.free()
+    return out
+
+
+def extras_single_gpu(torch, mk, ctx, dev, heads, x1):
+    """Bounded runs of the other workloads of the path for the same JSON line (one GPU)."""
+    out = {}
+
+    def guard(name, fn):
+        t0 = time.time()
+        try:
+            out[name] = fn()
+        except Exception as exc:                      # a failing side workload must not take the headline with it
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"}
+        out[name]["wall_s"] = round(time.time() - t0, 2)
+        torch.cuda.empty_cache()
+
+    def lm_head_b8():
+        x8 = torch.randn((8, HIDDEN), dtype=torch.float32, device=dev)
+        ctx.prof_enable(True)
+        ms = _timed(torch, lambda i: heads[0].matvec(x8, want_argmax=True), 20, 3)
+        n, kms = ctx.prof_read("lm_head")
+        ctx.prof_enable(False)
+        alg = algorithmic_bytes(VOCAB, HIDDEN, 8)
+        return {"workload": f"q8_0 lm_head GEMV {VOCAB}x{HIDDEN}, batch 8 (weights read once)", "ms_per_step": ms,
+                "kernel_ms": kms / max(n, 1), "algorithmic_bytes": alg, "status_word": ctx.status_word(),
+                "roofline": _roof(alg, kms / max(n, 1), "GEMV kernel alone")}
+    guard("lm_head_batch8", lm_head_b8)
+    guard("config1_mxfp4_gemv_7168x2048", lambda: measure_mxfp4_gemv(torch, mk, ctx, dev))
+
+    def moe():
+        layers, gen = build_moe_layers(torch, mk, ctx, dev, 384, 2)
+        try:
+            return {f"batch{b}": measure_moe(torch, mk, ctx, dev, layers, gen, b, st, 3, graph=(b == 1))
+                    for b, st in ((1, 40), (16, 20), (256, 6))}
+        finally:
+            free_moe_layers(layers)
+    guard("config3_moe_layer", moe)
+    guard("config4_mla_absorbed", lambda: {f"ctx{n}_batch{b}": measure_mla(torch, mk, ctx, dev, "absorbed", n, b, 30, 3)
+                                           for n, b in ((4096, 1), (16384, 8), (65536, 8))})
+    guard("mla_per_head_ctx16384_batch8", lambda: measure_mla(torch, mk, ctx, dev, "per_head", 16384, 8, 20, 3))
+    return out
+
+
+def measure_moe_ep(torch, dist, mk, ctx, dev, world, rank, experts, batches, steps, warmup, collective="peer", copies=2):
+    """The MoE layer with its routed experts block-partitioned over the ranks (expert parallelism) and the same token
+    rows on every rank (decode).  peer: one call per layer, output rows travel by peer-memory stores; nccl: the
+    all-to-all form on the same weights (every rank owns batch / world of the rows).  Time = max over ranks."""
+    from microkimi_b200 import dist as mkd
+    E, k, d, inter = experts, 8, 7168, 2048
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)  # the same router and token rows on every rank
+    gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
+    xs = {b: torch.randn((b, d), dtype=torch.float32, device=dev, generator=gen) for b in batches}
+    lo, hi = mkd.local_expert_range(E, world, rank)
+    layers = []
+    for _ in range(copies):
+        mine = [None] * E
+        for e in range(lo, hi):
+            mine[e] = tuple(_rand_mxfp4(torch, mk, ctx, gen, dev, r, c) for r, c in ((inter, d), (d, inter), (inter, d)))
+        shared = tuple(_rand_mxfp4(torch, mk, ctx, gen, dev, r, c) for r, c in ((inter, d), (d, inter), (inter, d)))
+        layers.append(mk.MoeLayer(gw, None, mine, shared, k, ctx=ctx))
+    eps = [mkd.PeerEpMoeLayer(l, max_tokens=16) for l in layers] if collective == "peer" else [mkd.EpMoeLayer(l) for l in layers]
+    res = {}
+    for b in batches:
+        x = xs[b]
+        if collective == "peer":
+            fn = lambda i: eps[i % copies].forward(x)
+        else:
+            per = (b + world - 1) // world
+            xl = x[rank * per:(rank + 1) * per].contiguous()
+            fn = lambda i: eps[i % copies].forward(xl)
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        st = torch.tensor([ctx.status_word()], dtype=torch.int32, device=dev)
+        dist.all_reduce(st, op=dist.ReduceOp.MIN)
+        res[f"batch{b}"] = {"ms_per_layer": float(t.item()), "tokens_per_s": b / (float(t.item()) * 1e-3), "status_word": int(st.item())}
+    for e in eps:
+        if hasattr(e, "free"):
+            e.free()
+    free_moe_layers(layers)
+    return {"workload": f"expert-parallel MoE layer, {E}+1 MXFP4 experts over {world} GPUs ({collective}), top-{k}, {d}x{inter}, "
+                        f"{copies} rotating layers, the same rows on every rank", **res}
 
 
 # ---------------------------------------------------------------- GPU arm
@@ -187,8 +483,8 @@ def run_gpu(args):
     gen.manual_seed(7)
     x = torch.randn((batch, HIDDEN), dtype=torch.float32, device=dev, generator=gen)
     logits = torch.empty((batch, VOCAB), dtype=torch.float32, device=dev) if world > 1 else None
-    # N > 1: the matvec kernel stores its rows straight into every rank's gather buffer (peer memory);
-    # --collective nccl runs the library all-gather instead, for comparison
+    # N > 1: after the matvec ONE exchange kernel pushes the shard's logits into every rank's gather buffer (peer-memory
+    # stores + flags); --collective nccl runs the library all-gather instead, for comparison
     fused = None
     fused_note = None
     if world > 1 and batch <= 2 and args.collective == "peer":
@@ -211,15 +507,13 @@ def run_gpu(args):
         if fused is not None:
             return fused.matvec(x, want_argmax=True, head=heads[i % copies])
         y = heads[i % copies].matvec(x)
-        if world > 1:
-            # vocab-sharded logits -> full logits on every rank
-            if batch == 1:
-                dist.all_gather_into_tensor(logits.view(-1), y.view(-1))
-            else:
-                parts = [logits[:, r * rows:(r + 1) * rows] for r in range(world)]
-                dist.all_gather(parts, y)  # strided destination views
-            return logits, logits.argmax(dim=1)   # the step ends with the token id, as on the other paths
-        return y
+        # vocab-sharded logits -> full logits on every rank
+        if batch == 1:
+            dist.all_gather_into_tensor(logits.view(-1), y.view(-1))
+        else:
+            parts = [logits[:, r * rows:(r + 1) * rows] for r in range(world)]
+            dist.all_gather(parts, y)  # strided destination views
+        return logits, logits.argmax(dim=1)   # the step ends with the token id, as on the other paths
 
     def barrier():
         if world > 1:
@@ -249,30 +543,33 @@ def run_gpu(args):
             barrier()
     launches0 = ctx.launches
     ctx.prof_enable(True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    # `repeats` timed regions of exactly `steps` steps, each between barriers; the line's value is the median region
+    region_ms = []
     t_load0 = time.time()
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
+    for _ in range(args.repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        region_ms.append(float(t.item()))
     kn, kms = ctx.prof_read("lm_head")
     xn_, xms_ = ctx.prof_read("other")     # N > 1, peer path: the exchange kernel (push, flags, wait, token pick)
     ctx.prof_enable(False)
-    launches = ctx.launches - launches0
+    launches = (ctx.launches - launches0) // args.repeats
     st = torch.tensor([ctx.status_word()], dtype=torch.int32, device=dev)   # a bounded device-side wait that ran out sets it
     if world > 1:
-        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        dist.all_reduce(st, op=dist.ReduceOp.MIN)
     status_all = int(st.item())
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    # the timed region may be shorter than nvidia-smi's sampling period: the same steps go on, untimed, for about
-    # a second, and the clocks reported are the samples taken between the start of the timed region and here
+    per_step = sorted(r / args.steps for r in region_ms)
+    ms_step = float(np.median(per_step))
+    # the timed regions may be shorter than nvidia-smi's sampling period: the same steps go on, untimed, for about
+    # a second, and the clocks reported are the samples taken between the start of the first region and here
     for i in range(int(min(20000, max(1, 1.0 / (ms_step * 1e-3))))):
         step(i)
     barrier()
@@ -328,103 +625,68 @@ def run_gpu(args):
     kern_ms = kms / max(kn, 1)
     achieved = algorithmic_bytes(rows, HIDDEN, batch) / (kern_ms * 1e-3) / 1e9 if kn else None
 
+    # ---- the other workloads of the path, bounded, for the same line
+    extra = None
+    used_peer = fused is not None
+    if not args.no_extra:
+        if fused is not None:
+            fused.free()
+        if world == 1:
+            extra = extras_single_gpu(torch, mk, ctx, dev, heads, x)
+        else:
+            for h in heads:
+                h.free()
+            torch.cuda.empty_cache()
+            try:
+                extra = {"moe_expert_parallel_peer": measure_moe_ep(torch, dist, mk, ctx, dev, world, rank, 384, (1, 4, 16), 30, 5)}
+            except Exception as exc:
+                extra = {"moe_expert_parallel_peer": {"error": f"{type(exc).__name__}: {exc}"}}
+
     if rank == 0:
         cb = None
         if world == 1 and not args.no_cpu:
             cb, _ = cpu_leg(8, 2)
+        cfg = workload_config(world, batch)
+        frac = (achieved / peak) if achieved else None
         line = {
-            "metric": "quantized GB/s, q8_0 lm_head GEMV", "value": value, "unit": "GB/s", "n_gpus": world,
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"q8_0 lm_head GEMV {VOCAB}x{HIDDEN} (f32 block scales), batch {batch}, "
-                                   f"vocab-sharded {world} way(s)" + ("" if world == 1 else (
-                                       ", logits stored into every rank's buffer by the matvec kernel (peer memory)"
-                                       if fused is not None else " + f32 logits all-gather (NCCL)")),
-                       "batch": batch, "rows_per_gpu": rows,
-                       "l2": f"inputs larger than L2: {shard_bytes * copies / 1e6:.0f} MB of weights per GPU"
-                             + (f" ({copies} rotating copies of the shard)" if copies > 1 else ""),
-                       "algorithmic_bytes_per_step": alg_step, **({"note": fused_note} if fused_note else {})},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": (achieved / peak) if achieved else None,
-                         "traffic": NCU_TRAFFIC_PER_LAUNCH_N1 / world if batch == 1 else None,
-                         "peak_kind": peak_kind, "kernel": "qgemv_spread_kernel<q8_0>",
+            "config": cfg,
+            "repeats": {"n": args.repeats, "value_from": f"median of {args.repeats} timed regions of {args.steps} steps",
+                        "ms_per_step_each": per_step, "ms_per_step_p10": float(np.percentile(per_step, 10)),
+                        "ms_per_step_p90": float(np.percentile(per_step, 90))},
+            "run": {"weights_mb_per_gpu": shard_bytes * copies / 1e6, "rotating_copies": copies,
+                    "logits_path": ("one GPU" if world == 1 else
+                                    ("one exchange kernel after the matvec pushes the shard's logits into every rank's buffer "
+                                     "(peer-memory stores + flags, no collective library call)" if used_peer
+                                     else "NCCL all-gather of the f32 logits + argmax")),
+                    **({"note": fused_note} if fused_note else {})},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": frac,
+                         "traffic": (NCU_TRAFFIC_PER_LAUNCH_N1 / world) if batch == 1 else None,
+                         "traffic_source": "constant from one ncu capture of this kernel on one GPU holding the whole matrix"
+                                           + ("" if world == 1 else f", divided by {world} (traffic is proportional to the rows of a shard); "
+                                                                    "not captured at this N"),
+                         "peak_kind": peak_kind,
+                         "peak_note": "the peak is a copy (read + write); a read-only stream such as this GEMV can run a little "
+                                      "above it, so frac may exceed 1 - frac_of_nominal_8000 is the bounded figure",
+                         "kernel": "qgemv_spread_kernel<q8_0>",
                          "kernel_ms": kern_ms, "kernel_launches": kn, "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
             "cpu_baseline": cb,
             "e2e": {"value": alg_step / e2e_dt / 1e9, "unit": "GB/s", "ms_per_step": e2e_dt * 1e3,
                     "h2d_bytes_per_step": batch * HIDDEN * 4, "d2h_bytes_per_step": batch * rows * 4 + batch * 4,
-                    "api": "mk_matvec_q8 (host pointers: pinned x, pinned logits and token id)" if fused is None else
+                    "api": "mk_matvec_q8 (host pointers: pinned x, pinned logits and token id)" if not used_peer else
                            "pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank"},
             "gpu_launches": launches,
-            **({"exchange_kernel_ms": xms_ / xn_} if (fused is not None and xn_) else {}),
+            **({"exchange_kernel_ms": xms_ / xn_} if (used_peer and xn_) else {}),
             "status_word": status_all,
             "clocks": clocks,
+            "extra": extra,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
-
-
-def run_case_mxfp4(args):
-    """Side workload for kernel studies and profiler captures: one MXFP4 matvec
-    (rows x cols, synthetic codes) over `copies` rotating matrices.  One JSON line."""
-    import torch
-
-    import microkimi_b200 as mk
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    ctx = mk.Context(0)
-    mk.Context._default = ctx
-    ctx.use_torch_stream()
-    rows, cols, batch = args.rows, args.cols, args.batch
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(11)
-    ws = []
-    for _ in range(args.copies):
-        p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
-        s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
-        ws.append(mk.MxFp4Weight(p, s, rows, cols, ctx=ctx))
-    x = torch.randn((batch, cols), dtype=torch.float32, device=dev, generator=gen)
-    for i in range(args.warmup):
-        ws[i % args.copies].matvec(x, act=args.act)
-    torch.cuda.synchronize()
-    ctx.prof_enable(True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        ws[i % args.copies].matvec(x, act=args.act)
-    e1.record()
-    torch.cuda.synchronize()
-    n, kms = ctx.prof_read("matvec_mxfp4")
-    ctx.prof_enable(False)
-    # the same ring of calls as ONE CUDA graph (activation quantization + GEMV per matrix): what a decode loop that
-    # replays its token pays per call, without the host's launch cost
-    graph_us = None
-    if args.graph:
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for i in range(args.copies):
-                ws[i].matvec(x, act=args.act)
-        ctx.use_torch_stream()
-        reps = max(3, args.steps // args.copies)
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(reps):
-            g.replay()
-        g1.record()
-        torch.cuda.synchronize()
-        graph_us = g0.elapsed_time(g1) / (reps * args.copies) * 1e3
-    alg = rows * cols // 2 + rows * cols // 32 + batch * (cols + rows) * 4
-    peak, kind = measured_peaks()
-    ach = alg / (kms / n * 1e-3) / 1e9
-    print(json.dumps({"case": "mxfp4_gemv", "rows": rows, "cols": cols, "batch": batch, "copies": args.copies,
-                      "act": args.act, "ms_per_step": e0.elapsed_time(e1) / args.steps, "kernel_us": kms / n * 1e3,
-                      "graph_us_per_call": graph_us, "graph_gbs": (alg / (graph_us * 1e-6) / 1e9) if graph_us else None,
-                      "algorithmic_bytes": alg, "status_word": ctx.status_word(),
-                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                   "peak_kind": kind}}), flush=True)
 
 
 def _side_ctx():
@@ -438,93 +700,24 @@ def _side_ctx():
     return torch, mk, ctx, torch.device("cuda", 0)
 
 
-def _timed(torch, fn, steps, warmup):
-    for i in range(warmup):
-        fn(i)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        fn(i)
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps
+def run_case_mxfp4(args):
+    torch, mk, ctx, dev = _side_ctx()
+    print(json.dumps({"case": "mxfp4_gemv", **measure_mxfp4_gemv(torch, mk, ctx, dev, args.rows, args.cols, args.batch, args.copies,
+                                                                 args.steps, args.warmup, args.act, args.graph)}), flush=True)
 
 
 def run_case_moe(args):
-    """Side workload: one MoE FFN layer - `experts` routed MXFP4 experts + 1 shared, top-8,
-    hidden 7168, expert intermediate 2048, sigmoid router; tokens N(0,1), batch --batch.
-    Expert codes are synthetic (uniform codes, scale bytes 118..123): the kernels' speed does
-    not depend on the values.  `layers` rotating copies keep the timed passes cold in L2."""
     torch, mk, ctx, dev = _side_ctx()
-    E, k, d, inter, B = args.experts, 8, 7168, 2048, args.batch
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(3)
-
-    def rand_w(rows, cols):
-        p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
-        s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
-        return mk.MxFp4Weight(p, s, rows, cols, ctx=ctx)
-
-    layers = []
-    for _ in range(args.copies):
-        experts = [(rand_w(inter, d), rand_w(d, inter), rand_w(inter, d)) for _ in range(E + 1)]
-        gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
-        layers.append(mk.MoeLayer(gw, None, experts[:-1], experts[-1], k, ctx=ctx))
-    x = torch.randn((B, d), dtype=torch.float32, device=dev, generator=gen)
-    _, ids, _ = layers[0].moe_forward(x, want_routing=True)
-    distinct = int(torch.unique(ids).numel())
-    per_expert = 3 * (inter * d // 2 + inter * d // 32)
-    alg = E * d * 4 + (distinct + 1) * per_expert + 2 * B * d * 4
-    ms = _timed(torch, lambda i: layers[i % args.copies].moe_forward(x), args.steps, args.warmup)
-    # second pass with the per-category event pairs on (they add a few microseconds of gaps, so
-    # the headline time above is taken without them)
-    l0 = ctx.launches
-    layers[0].moe_forward(x)
-    launches = ctx.launches - l0
-    ctx.prof_enable(True)
-    _timed(torch, lambda i: layers[i % args.copies].moe_forward(x), args.steps, 0)
-    n_e, ms_e = ctx.prof_read("experts")
-    n_r, ms_r = ctx.prof_read("router")
-    ctx.prof_enable(False)
-    graph_ms = None
-    if args.graph:   # `copies` layer calls as one CUDA graph: the layer without the host's launch cost
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for l in layers:
-                l.moe_forward(x)
-        ctx.use_torch_stream()
-        reps = max(3, args.steps // args.copies)
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(reps):
-            g.replay()
-        g1.record()
-        torch.cuda.synchronize()
-        graph_ms = g0.elapsed_time(g1) / (reps * args.copies)
-    peak, kind = measured_peaks()
-    ach = alg / (ms * 1e-3) / 1e9
-    print(json.dumps({"case": "moe", "graph_ms_per_layer": graph_ms, "status_word": ctx.status_word(), "experts": E, "top_k": k, "batch": B, "copies": args.copies,
-                      "distinct_experts_routed": distinct, "ms_per_layer": ms, "tokens_per_s": B / (ms * 1e-3),
-                      "experts_ms": ms_e / args.steps if n_e else None, "router_ms": ms_r / args.steps if n_r else None,
-                      "launches_per_call": launches, "algorithmic_bytes": alg,
-                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                   "peak_kind": kind, "note": "whole layer call, not one kernel"}}), flush=True)
+    layers, gen = build_moe_layers(torch, mk, ctx, dev, args.experts, args.copies)
+    print(json.dumps({"case": "moe", **measure_moe(torch, mk, ctx, dev, layers, gen, args.batch, args.steps, args.warmup, args.graph)}),
+          flush=True)
 
 
 def run_case_moe_ep(args):
-    """Side workload under torchrun: the MoE layer of --case moe with its routed experts block-partitioned
-    over the ranks (expert parallelism) and the same `batch` token rows on every rank (decode).  Times the
-    peer-memory path (one call per layer, no collective library call) and, with --collective nccl, the
-    all-to-all path on the same weights (there every rank owns batch / world of the rows).  Time = max over ranks."""
     import torch
     import torch.distributed as dist
 
     import microkimi_b200 as mk
-    from microkimi_b200 import dist as mkd
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
@@ -534,52 +727,10 @@ def run_case_moe_ep(args):
     ctx = mk.Context(local)
     mk.Context._default = ctx
     ctx.use_torch_stream()
-    E, k, d, inter, B = args.experts, 8, 7168, 2048, args.batch
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(3)  # the same router and token rows on every rank
-
-    def rand_w(rows, cols):
-        p = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev, generator=gen)
-        s = torch.randint(118, 124, (rows, cols // 32), dtype=torch.uint8, device=dev, generator=gen)
-        return mk.MxFp4Weight(p, s, rows, cols, ctx=ctx)
-
-    gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
-    x = torch.randn((B, d), dtype=torch.float32, device=dev, generator=gen)
-    lo, hi = mkd.local_expert_range(E, world, rank)
-    layers = []
-    for _ in range(args.copies):
-        mine = [None] * E
-        for e in range(lo, hi):
-            mine[e] = (rand_w(inter, d), rand_w(d, inter), rand_w(inter, d))
-        shared = (rand_w(inter, d), rand_w(d, inter), rand_w(inter, d))
-        layers.append(mk.MoeLayer(gw, None, mine, shared, k, ctx=ctx))
-    if args.collective == "peer":
-        eps = [mkd.PeerEpMoeLayer(l, max_tokens=16) for l in layers]
-        fn = lambda i: eps[i % args.copies].forward(x)
-    else:
-        eps = [mkd.EpMoeLayer(l) for l in layers]
-        per = (B + world - 1) // world
-        xl = x[rank * per:(rank + 1) * per].contiguous()
-        fn = lambda i: eps[i % args.copies].forward(xl)
-
-    for i in range(args.warmup):
-        fn(i)
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        fn(i)
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    st = ctx.status_word()
+    res = measure_moe_ep(torch, dist, mk, ctx, dev, world, rank, args.experts, (args.batch,), args.steps, args.warmup,
+                         args.collective, args.copies)
     if rank == 0:
-        print(json.dumps({"case": "moe_ep", "collective": args.collective, "n_gpus": world, "experts": E, "top_k": k, "batch": B,
-                          "copies": args.copies, "ms_per_layer": float(t.item()), "tokens_per_s": B / (float(t.item()) * 1e-3),
-                          "status_word": st}), flush=True)
+        print(json.dumps({"case": "moe_ep", "n_gpus": world, **res}), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -610,91 +761,21 @@ def run_case_kda(args):
     ctx.prof_enable(False)
     ms = ms_k / max(n_k, 1)
     alg = H * D * D * 8 + 10 * proj * 4
-    block = None
-    if args.graph:
-        # the whole kda_forward of one layer (model width --rows, f_a rank 128): stacked projections, f_b, the step,
-        # o_proj = 4 launches; `copies` layers in rotation, from a host loop and as one CUDA graph
-        from microkimi_b200.blocks import KdaBlock
-        d, fa = args.rows, 128
-        g32 = lambda *shape: (rng.standard_normal(shape) * 0.05).astype(np.float32)
-        blocks = []
-        for _ in range(args.copies):
-            w = {"q_proj": g32(proj, d), "k_proj": g32(proj, d), "v_proj": g32(proj, d), "g_proj": g32(proj, d), "f_a": g32(fa, d),
-                 "f_b": g32(proj, fa), "b_proj": g32(H, d), "o_proj": g32(d, proj), "q_conv": g32(proj, 4), "k_conv": g32(proj, 4),
-                 "v_conv": g32(proj, 4), "a_log": np.log(rng.uniform(1, 16, D)).astype(np.float32), "dt_bias": g32(proj),
-                 "o_norm": np.ones(D, np.float32)}
-            blocks.append(KdaBlock(H, D, w, ctx=ctx))
-        xb = torch.randn(d, dtype=torch.float32, device=dev, generator=gen)
-        host_ms = _timed(torch, lambda i: blocks[i % args.copies].forward(xb), args.steps, args.warmup)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for b in blocks:
-                b.forward(xb)
-        ctx.use_torch_stream()
-        reps = max(3, args.steps // args.copies)
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(reps):
-            g.replay()
-        g1.record()
-        torch.cuda.synchronize()
-        wbytes = 4 * ((4 * proj + fa + H) * d + proj * fa + d * proj)
-        gus = g0.elapsed_time(g1) / (reps * args.copies) * 1e3
-        block = {"d": d, "launches": 4, "host_loop_us": host_ms * 1e3, "graph_us": gus, "weight_bytes": wbytes,
-                 "graph_gbs": (wbytes + alg) / (gus * 1e-6) / 1e9}
-    peak, kind = measured_peaks()
-    ach = alg / (ms * 1e-3) / 1e9
-    print(json.dumps({"case": "kda_step", "form": "shared memory" if args.kda_smem else "registers", "block": block, "heads": H, "dim": D, "copies": args.copies, "kernel_us": ms * 1e3,
-                      "call_us_host_loop": ms_call * 1e3, "algorithmic_bytes": alg, "status_word": ctx.status_word(),
-                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                   "peak_kind": kind, "note": "latency-bound: one CTA per head"}}), flush=True)
+    print(json.dumps({"case": "kda_step", "form": "shared memory" if args.kda_smem else "registers", "heads": H, "dim": D,
+                      "copies": args.copies, "kernel_us": ms * 1e3, "call_us_host_loop": ms_call * 1e3, "algorithmic_bytes": alg,
+                      "status_word": ctx.status_word(), "roofline": _roof(alg, ms, "latency-bound: one CTA per head")}), flush=True)
 
 
 def run_case_mla(args):
-    """Side workload: q8_0 MLA decode attention, 64 heads.  --layout absorbed: one shared
-    512+64 latent row per position (648 B with f32 scales); --layout per_head: the engine's
-    layout at nope 128 / rope 64 / v 128 (18,688 B per position).  Cache rows N(0,1), context
-    --ctx, --batch independent sequences, softmax scale 1/sqrt(192)."""
     torch, mk, ctx, dev = _side_ctx()
-    H, B, n = 64, args.batch, args.ctx
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(4)
-    if args.layout == "absorbed":
-        cache = mk.MlaCache(H, 576, 0, 512, n, n_seqs=B, layout="absorbed", ctx=ctx)
-        qdim, per_pos = 576, 576 + 18 * 4
-        for s_ in range(B):
-            for lo in range(0, n, 8192):
-                m = min(8192, n - lo)
-                cache.push(torch.randn((m, 576), dtype=torch.float32, device=dev, generator=gen), seq=s_)
-    else:
-        cache = mk.MlaCache(H, 128, 64, 128, n, n_seqs=B, ctx=ctx)
-        qdim, per_pos = 192, H * 128 + H * 4 * 4 + 64 * 4 + H * 128 + H * 4 * 4
-        for s_ in range(B):
-            for lo in range(0, n, 1024):
-                m = min(1024, n - lo)
-                kk = torch.randn((m, H, 192), dtype=torch.float32, device=dev, generator=gen)
-                vv = torch.randn((m, H, 128), dtype=torch.float32, device=dev, generator=gen)
-                cache.push(kk, vv, seq=s_)
-    q = torch.randn((B, H, qdim), dtype=torch.float32, device=dev, generator=gen)
-    scale = 1.0 / np.sqrt(192.0)
-    ms = _timed(torch, lambda i: cache.attend_batch(q, scale), args.steps, args.warmup)
-    alg = B * n * per_pos + B * H * (qdim + cache.vd) * 4
-    flops = B * n * 2 * H * (qdim + cache.vd) if args.layout == "absorbed" else B * n * 2 * H * (192 + 128)
-    peak, kind = measured_peaks()
-    ach = alg / (ms * 1e-3) / 1e9
-    print(json.dumps({"case": "mla", "layout": args.layout, "heads": H, "ctx": n, "batch": B, "ms_per_call": ms,
-                      "algorithmic_bytes": alg, "tflops": flops / (ms * 1e-3) / 1e12,
-                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                                   "peak_kind": kind}}), flush=True)
+    print(json.dumps({"case": "mla", **measure_mla(torch, mk, ctx, dev, args.layout, args.ctx, args.batch, args.steps, args.warmup)}),
+          flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "moe_ep", "mla", "kda"],
-                    help="lm_head is the benchmark proper; the others are side workloads for kernel studies")
+                    help="lm_head is the benchmark proper; the others run one of the side workloads alone")
     ap.add_argument("--rows", type=int, default=7168)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=1)
@@ -707,14 +788,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the value is their median")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the side workloads that follow the headline measurement")
     ap.add_argument("--graph", action="store_true", help="--case mxfp4_gemv / moe: also time the ring of calls as one CUDA graph")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: logits by peer-memory stores from the matvec kernel (default) or by an NCCL all-gather")
+                    help="N > 1: logits by one peer-memory exchange kernel after the matvec (default) or by an NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     if args.impl == "reference":
         run_reference(args)
     elif args.case == "mxfp4_gemv":

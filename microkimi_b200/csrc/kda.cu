@@ -435,11 +435,11 @@ extern "C" int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *k, const float *q_raw, c
     const size_t smem_s = ((size_t)k->dim * k->dim + 4 * (size_t)k->dim + 4) * sizeof(float);
     const bool reg_dim = k->dim == 64 || k->dim == 128;
     if ((ctx->kda_smem || !reg_dim) && k->dim % 4 == 0 && k->dim >= 32 && k->dim <= 224) {
-        static bool attr = false;
-        if (!attr) {
-            cudaFuncSetAttribute(kda_step_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            cudaFuncSetAttribute(kda_step_smem_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            attr = true;
+        static mk_once_per_device attr;
+        if (attr.pending(ctx->device)) {
+            MK_CUDA(cudaFuncSetAttribute(kda_step_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            MK_CUDA(cudaFuncSetAttribute(kda_step_smem_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            attr.mark(ctx->device);
         }
         const unsigned threads = (unsigned)mk_align_up(k->dim, 32);
         if (kc4) kda_step_smem_kernel<4><<<k->heads, threads, smem_s, ctx->stream>>>(a);

@@ -32,6 +32,15 @@ void mk_set_error(const char *fmt, ...);
         }                                                                              \
     } while (0)
 
+// A function attribute (cudaFuncSetAttribute) belongs to one device: one flag per call site AND device
+// ordinal, so that a second context on another GPU of the same process opts in as well.
+#define MK_MAX_DEVICES 64
+struct mk_once_per_device {
+    bool done[MK_MAX_DEVICES];
+    bool pending(int dev) const { return dev < 0 || dev >= MK_MAX_DEVICES || !done[dev]; }
+    void mark(int dev) { if (dev >= 0 && dev < MK_MAX_DEVICES) done[dev] = true; }
+};
+
 // ---------------------------------------------------------------- records
 enum { MK_FMT_MXFP4 = 0, MK_FMT_Q8 = 1, MK_FMT_F32 = 2, MK_FMT_VQ1 = 3 };
 

@@ -767,10 +767,10 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     if (m->layout == MK_MLA_ABSORBED && m->H == mla_t5::H && m->nope == mla_t5::LAT && m->vd == mla_t5::VD && !ctx->mla_no_tc &&
         !ctx->mla_no_t5) {
         // tcgen05 kernel: one CTA per (sequence, KV split), 128 positions per tile, accumulators in tensor memory
-        static bool attr5 = false;
-        if (!attr5) {
+        static mk_once_per_device attr5;
+        if (attr5.pending(ctx->device)) {
             MK_CUDA(cudaFuncSetAttribute(mla_t5::mla_absorbed_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla_t5::SM_TOTAL));
-            attr5 = true;
+            attr5.mark(ctx->device);
         }
         const int nt128 = (max_n + mla_t5::TJ - 1) / mla_t5::TJ;
         int ns = ctx->sm_count / nq;
@@ -791,10 +791,10 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     }
     if (m->layout == MK_MLA_ABSORBED && m->H == mla_tc::H && m->nope == mla_tc::LAT && m->vd == mla_tc::VD && !ctx->mla_no_tc) {
         // mma.sync tensor-core kernel: one CTA per (sequence, KV split), 64 positions per tile
-        static bool attr = false;
-        if (!attr) {
+        static mk_once_per_device attr;
+        if (attr.pending(ctx->device)) {
             MK_CUDA(cudaFuncSetAttribute(mla_tc::mla_absorbed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla_tc::SM_TOTAL));
-            attr = true;
+            attr.mark(ctx->device);
         }
         const int nt64 = (max_n + mla_tc::TJ - 1) / mla_tc::TJ;
         int ns = ctx->sm_count / nq;
@@ -832,16 +832,16 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
                     cph, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, m->rope_scores);
             } else {
                 const size_t smem_rs = ((size_t)m->RC * 32 + (size_t)m->H * m->RC) * 16;
-                static bool attr_rs = false;
-                if (!attr_rs) { MK_CUDA(cudaFuncSetAttribute(mla_rope_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_rs = true; }
+                static mk_once_per_device attr_rs;
+                if (attr_rs.pending(ctx->device)) { MK_CUDA(cudaFuncSetAttribute(mla_rope_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_rs.mark(ctx->device); }
                 MK_CHECK_ARG(smem_rs <= 200 * 1024, "rope dims too large");
                 mla_rope_scores_kernel<<<dim3((unsigned)ntiles_p, (unsigned)nq), 256, smem_rs, ctx->stream>>>(
                     cph, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, m->rope_scores);
             }
             ctx->launches++;
         }
-        static bool attr_ph = false;
-        if (!attr_ph) { MK_CUDA(cudaFuncSetAttribute(mla_attend_ph128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr_ph = true; }
+        static mk_once_per_device attr_ph;
+        if (attr_ph.pending(ctx->device)) { MK_CUDA(cudaFuncSetAttribute(mla_attend_ph128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr_ph.mark(ctx->device); }
         mla_attend_ph128_kernel<<<dim3((unsigned)ns, (unsigned)hgroups, (unsigned)nq), PH_WARPS * 32, smem_ph, ctx->stream>>>(
             cph, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, m->rope_scores, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, scale, ns,
             m->part_m, m->part_l, m->part_o, out, ctx->status_dev);

@@ -818,11 +818,11 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
         mk_prof_scope prof(ctx, MK_PROF_ROUTER);
         const int ewarps = (E + 3) / 4;
         if (m->dx % 4 == 0 && ((uintptr_t)x & 15) == 0) {
-            static bool attr = false;
-            if (!attr) {
-                cudaFuncSetAttribute(moe_router_tile_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtBig::SMEM);
-                cudaFuncSetAttribute(moe_router_tile_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtSmall::SMEM);
-                attr = true;
+            static mk_once_per_device attr;
+            if (attr.pending(ctx->device)) {
+                MK_CUDA(cudaFuncSetAttribute(moe_router_tile_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtBig::SMEM));
+                MK_CUDA(cudaFuncSetAttribute(moe_router_tile_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtSmall::SMEM));
+                attr.mark(ctx->device);
             }
             if (n <= RtSmall::NT)
                 moe_router_tile_kernel<RtSmall><<<dim3((unsigned)mk_ceil_div(E, RtSmall::NE), 1), 256, RtSmall::SMEM, ctx->stream>>>(
@@ -966,11 +966,11 @@ static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const flo
         const unsigned qctas = fused_q ? (unsigned)mk_ceil_div((int64_t)n * m->nbp_d, 8) : 0u;
         {
             mk_prof_scope prof(ctx, MK_PROF_ROUTER);
-            static bool attr = false;
-            if (!attr) {
-                cudaFuncSetAttribute(moe_router_fused_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-                cudaFuncSetAttribute(moe_router_fused_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-                attr = true;
+            static mk_once_per_device attr;
+            if (attr.pending(ctx->device)) {
+                MK_CUDA(cudaFuncSetAttribute(moe_router_fused_kernel<RtBig>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                MK_CUDA(cudaFuncSetAttribute(moe_router_fused_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                attr.mark(ctx->device);
             }
             if (small)
                 moe_router_fused_kernel<RtSmall><<<(unsigned)mk_ceil_div(m->n_experts, RtSmall::NE) + qctas, 256, smem_f, ctx->stream>>>(ra);

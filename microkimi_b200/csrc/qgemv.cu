@@ -369,6 +369,9 @@ static __device__ __align__(256) unsigned char mk_noalloc_scratch[MK_NOALLOC_XQ_
 // Device address of the array above, per device ordinal.  The array's name is only
 // a host-side handle; the address a kernel can use comes from cudaGetSymbolAddress
 // with that device current.
+// The table is written without a lock: two host threads that make their first call on the
+// same device at once both look the address up and both store the SAME value (the address of
+// a symbol is fixed per device), so the race is benign; a context is not re-entrant anyway.
 #define MK_NOALLOC_MAX_DEVICES 64
 static void *g_noalloc_addr[MK_NOALLOC_MAX_DEVICES];
 

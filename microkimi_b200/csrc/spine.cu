@@ -83,11 +83,15 @@ using GemvB8 = mkf::TileShape<4, 8, 256, 3>;
 using GemvB16 = mkf::TileShape<2, 16, 256, 3>;
 
 template <class S>
-void launch_tile(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, const float *x, int n, float *y, int64_t ldy, int accumulate) {
-    static bool attr = false; // one flag per instantiation
-    if (!attr) { cudaFuncSetAttribute(f32_gemv_tile_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM); attr = true; }
+int32_t launch_tile(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, const float *x, int n, float *y, int64_t ldy, int accumulate) {
+    static mk_once_per_device attr; // one per instantiation
+    if (attr.pending(ctx->device)) {
+        MK_CUDA(cudaFuncSetAttribute(f32_gemv_tile_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+        attr.mark(ctx->device);
+    }
     const dim3 grid((unsigned)mk_ceil_div(rows, S::NE), (unsigned)mk_ceil_div(n, S::NT));
     f32_gemv_tile_kernel<S><<<grid, 256, S::SMEM, ctx->stream>>>(w, x, y, (int)rows, (int)cols, n, ldy, accumulate);
+    return MK_OK;
 }
 
 } // namespace
@@ -97,11 +101,13 @@ int32_t mk_launch_f32_gemv(mk_ctx *ctx, const float *w, int64_t rows, int64_t co
     MK_CHECK_ARG(rows > 0 && cols > 0 && rows < (1ll << 31) && cols < (1ll << 31) && n > 0, "f32 matvec: bad shape");
     mk_prof_scope prof(ctx, MK_PROF_OTHER);
     if (cols % 4 == 0 && (((uintptr_t)w | (uintptr_t)x) & 15) == 0) {
-        if (n == 1) launch_tile<GemvB1>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
-        else if (n == 2) launch_tile<GemvB2>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
-        else if (n <= 4) launch_tile<GemvB4>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
-        else if (n <= 8) launch_tile<GemvB8>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
-        else launch_tile<GemvB16>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        int32_t rc;
+        if (n == 1) rc = launch_tile<GemvB1>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        else if (n == 2) rc = launch_tile<GemvB2>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        else if (n <= 4) rc = launch_tile<GemvB4>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        else if (n <= 8) rc = launch_tile<GemvB8>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        else rc = launch_tile<GemvB16>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        if (rc != MK_OK) return rc;
     } else if (n >= 4) {
         const int64_t warps = mk_ceil_div(rows, 4) * mk_ceil_div(n, 4);
         f32_gemv_rows_kernel<4><<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(w, x, y, (int)rows, (int)cols, n, ldy, accumulate);

@@ -34,6 +34,15 @@ int or_num_threads(void) {
     return 1;
 #endif
 }
+/* Thread count of the loops that carry no explicit count (the quantizers).  A launcher may have set
+ * OMP_NUM_THREADS=1 for its children; a caller that wants all cores says so here. */
+void or_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 
 static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }

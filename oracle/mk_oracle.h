@@ -204,6 +204,7 @@ uint16_t or_f32_to_f16(float f);
 float    or_f16_to_f32(uint16_t h);
 
 int or_num_threads(void);
+void or_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

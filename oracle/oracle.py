@@ -31,8 +31,7 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_SO):
-            build()
+        build()          # no-op unless the sources are newer than the library
         _lib = C.CDLL(_SO)
         _declare(_lib)
     return _lib
@@ -125,6 +124,7 @@ def _declare(L):
     sig("or_mla_abs_push", None, C.c_void_p, _f32p)
     sig("or_mla_abs_attn", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f32p)
     sig("or_mla_abs_attn_f64", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f64p)
+    sig("or_set_num_threads", None, C.c_int)
     sig("or_f32_to_f16", C.c_uint16, C.c_float)
     sig("or_f16_to_f32", C.c_float, C.c_uint16)
 
@@ -139,6 +139,20 @@ def _c(a, dt):
 
 def num_threads():
     return int(lib().or_num_threads())
+
+
+def host_threads():
+    """The cores this process may run on.  Unlike num_threads() this does not follow OMP_NUM_THREADS,
+    which launchers such as torchrun set to 1 for their children."""
+    import os
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def set_num_threads(n):
+    lib().or_set_num_threads(int(n))
 
 
 # ---------------------------------------------------------------- RNG

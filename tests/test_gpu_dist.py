@@ -103,3 +103,52 @@ def test_sharded_lm_head_and_expert_parallel_moe_match_single_gpu(world):
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     for r in range(world):
         assert ret[r] == (True, True), f"rank {r}: {ret[r]}"
+
+
+def test_second_context_on_another_gpu_of_the_same_process():
+    """Kernels that opt in to more than 48 KB of dynamic shared memory must do so on every device a
+    process uses: the MoE router, both MLA layouts, the KDA step and the f32 matvec run on GPU 1 after
+    GPU 0 has used them, and give the same bits there."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import microkimi_b200 as mk
+    rng = np.random.default_rng(3)
+    E, k, d, inter = 16, 4, 256, 128
+    gw = (rng.standard_normal((E, d)) * 0.02).astype(np.float32)
+    blobs = [[(rng.integers(0, 256, (r, c // 2), dtype=np.uint8), rng.integers(118, 124, (r, c // 32), dtype=np.uint8), r, c)
+              for r, c in ((inter, d), (d, inter), (inter, d))] for _ in range(E + 1)]
+    x = rng.standard_normal((3, d)).astype(np.float32)
+    rows = rng.standard_normal((300, 576)).astype(np.float32)
+    q = rng.standard_normal((64, 576)).astype(np.float32)
+    kk = rng.standard_normal((40, 8, 192)).astype(np.float32)
+    kk[:, 1:, 128:] = kk[:, :1, 128:]
+    vv = rng.standard_normal((40, 8, 128)).astype(np.float32)
+    qp = rng.standard_normal((8, 192)).astype(np.float32)
+    fw = (rng.standard_normal((96, 512)) * 0.05).astype(np.float32)
+    fx = rng.standard_normal(512).astype(np.float32)
+    kp = 2 * 96
+    kw = [(rng.standard_normal((kp, 4)) * 0.5).astype(np.float32) for _ in range(3)]
+    kw += [np.log(rng.uniform(1, 16, 96)).astype(np.float32), (rng.standard_normal(kp) * 0.3).astype(np.float32), np.ones(96, np.float32)]
+    kin = [rng.standard_normal(n).astype(np.float32) for n in (kp, kp, kp, kp, 2, kp)]
+    outs = []
+    for device in (0, 1):
+        ctx = mk.Context(device)
+        with torch.cuda.device(device):
+            ex = [tuple(mk.MxFp4Weight(*b, ctx=ctx) for b in tri) for tri in blobs]
+            layer = mk.MoeLayer(gw, None, ex[:-1], ex[-1], k, ctx=ctx)
+            o_moe = layer.moe_forward(x)
+            ca = mk.MlaCache(64, 576, 0, 512, 300, layout="absorbed", ctx=ctx)
+            ca.push(rows)
+            o_abs = ca.mla_attn_flash_q8_mqa(q, 299, 1.0 / np.sqrt(192.0))
+            cp = mk.MlaCache(8, 128, 64, 128, 40, ctx=ctx)
+            cp.push(kk, vv)
+            o_ph = cp.mla_attn_flash_q8_mqa(qp, 39, 1.0 / np.sqrt(192.0))
+            o_f32 = mk.matvec(fw, 96, 512, fx, ctx=ctx)
+            kda = mk.KdaLayer(2, 96, *kw, ctx=ctx)                       # width 96: the shared-memory form of the step
+            o_kda = kda.step(*[torch.from_numpy(a).to(f"cuda:{device}") for a in kin]).cpu().numpy()
+            assert ctx.status_word() == 0
+            outs.append((o_moe, o_abs, o_ph, o_f32, o_kda))
+            layer.free(); ca.free(); cp.free(); kda.free()
+        ctx.close()
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))

@@ -36,6 +36,19 @@ def test_noalloc_matvec_matches_regular_entry_point_twice_in_a_row():
     assert torch.equal(got, w.matvec(x2, act="q8x2"))
     got = w.matvec_noalloc(x1, strict=True)
     assert torch.equal(got, w.matvec(x1, strict=True))
+    # the call itself allocates nothing: with the result buffer made beforehand, neither the driver's free
+    # memory nor torch's allocator moves across two calls through the C ABI
+    import ctypes as C
+    y = torch.empty((5, rows), dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+    free0, alloc0, reserved0 = torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev)
+    for x in (x1, x2):
+        mk.lib.check(ctx._L.mk_matvec_mxfp4_noalloc_dev(ctx._h, w._h, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()),
+                                                        x.shape[0], mk.lib.MK_ACT_Q8))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(dev)[0] == free0
+    assert torch.cuda.memory_allocated(dev) == alloc0 and torch.cuda.memory_reserved(dev) == reserved0
+    assert torch.equal(y[:1], w.matvec(x2))
     # beyond the fixed scratch: a clear error, nothing launched
     with pytest.raises(mk.lib.MkError) as e:
         w.matvec_noalloc(torch.zeros((9, cols), dtype=torch.float32, device=dev))
