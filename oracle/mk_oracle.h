@@ -203,6 +203,40 @@ void or_attn_res(size_t d, float eps, const float *prefix, const float *blocks /
 uint16_t or_f32_to_f16(float f);
 float    or_f16_to_f32(uint16_t h);
 
+/* ---- the whole decode token (mk_oracle_model.c) -------------------------------------------
+ * Config (src/config.rs:8-43; explicit layer lists are not supported), the MKIM0001/2 container
+ * (src/weights.rs), `microkimi build` with every tensor on its Gaussian fallback branch
+ * (src/build.rs:344-576) and Model::forward (src/model.rs:2889-3031). */
+typedef struct {
+    uint32_t n_layers, d, vocab, n_experts, top_k, n_shared;
+    uint32_t kda_heads, kda_dim, kda_conv, kda_fa;
+    float    gate_lb;
+    uint32_t mla_heads, mla_qa, mla_kva, mla_nope, mla_rope, mla_v;
+    uint32_t routed_hidden, moe_inter, shared_inter, dense_inter, attn_res_block, first_k_dense;
+    float    rms_eps;
+    uint32_t eos_id, bos_id;
+} or_config;
+void or_config_microkimi(or_config *c);
+int  or_config_is_mla(const or_config *c, uint32_t l);
+int  or_config_is_moe(const or_config *c, uint32_t l);
+/* writes the synthetic model file; 0 on success */
+int  or_build_bin(const char *path, const or_config *c);
+typedef struct or_bin or_bin;
+or_bin *or_bin_open(const char *path);
+void or_bin_close(or_bin *b);
+const or_config *or_bin_config(const or_bin *b);
+size_t or_bin_count(const or_bin *b);
+/* tensor by name: data pointer (NULL if absent), dtype (0 f32, 1 mxfp4), dims2 = {rows, cols or 0}, blob size */
+const void *or_bin_get(const or_bin *b, const char *name, uint8_t *dtype, uint32_t *dims2, uint64_t *size);
+int or_bin_entry(const or_bin *b, size_t i, const char **name, uint8_t *dtype, uint32_t *dims2, uint64_t *off, uint64_t *size);
+typedef struct or_model or_model;
+or_model *or_model_open(const char *path, size_t max_positions, int n_threads);
+void or_model_free(or_model *m);
+void or_model_reset(or_model *m);
+const or_config *or_model_config(const or_model *m);
+/* one token: logits [vocab] (nullable), hidden_out [d] (nullable) = the normed state fed to the lm_head; 0 on success */
+int or_model_forward(or_model *m, uint32_t token, float *logits, float *hidden_out);
+
 int or_num_threads(void);
 void or_set_num_threads(int n);
 

@@ -16,10 +16,9 @@ _SO = os.path.join(_HERE, "libmk_oracle.so")
 
 
 def build(force=False):
-    src = os.path.join(_HERE, "mk_oracle.c")
-    hdr = os.path.join(_HERE, "mk_oracle.h")
+    deps = [os.path.join(_HERE, f) for f in ("mk_oracle.c", "mk_oracle_model.c", "mk_oracle.h", "Makefile")]
     if (not force and os.path.exists(_SO)
-            and os.path.getmtime(_SO) >= max(os.path.getmtime(src), os.path.getmtime(hdr))):
+            and os.path.getmtime(_SO) >= max(os.path.getmtime(p) for p in deps)):
         return _SO
     subprocess.check_call(["make", "-C", _HERE, "-B", "libmk_oracle.so"], stdout=subprocess.DEVNULL)
     return _SO
@@ -125,8 +124,128 @@ def _declare(L):
     sig("or_mla_abs_attn", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f32p)
     sig("or_mla_abs_attn_f64", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f64p)
     sig("or_set_num_threads", None, C.c_int)
+    sig("or_config_microkimi", None, C.c_void_p)
+    sig("or_config_is_mla", C.c_int, C.c_void_p, C.c_uint32)
+    sig("or_config_is_moe", C.c_int, C.c_void_p, C.c_uint32)
+    sig("or_build_bin", C.c_int, C.c_char_p, C.c_void_p)
+    sig("or_bin_open", C.c_void_p, C.c_char_p)
+    sig("or_bin_close", None, C.c_void_p)
+    sig("or_bin_config", C.c_void_p, C.c_void_p)
+    sig("or_bin_count", C.c_size_t, C.c_void_p)
+    sig("or_bin_get", C.c_void_p, C.c_void_p, C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p)
+    sig("or_bin_entry", C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p)
+    sig("or_model_open", C.c_void_p, C.c_char_p, C.c_size_t, C.c_int)
+    sig("or_model_free", None, C.c_void_p)
+    sig("or_model_reset", None, C.c_void_p)
+    sig("or_model_config", C.c_void_p, C.c_void_p)
+    sig("or_model_forward", C.c_int, C.c_void_p, C.c_uint32, _f32p, _f32p)
     sig("or_f32_to_f16", C.c_uint16, C.c_float)
     sig("or_f16_to_f32", C.c_float, C.c_uint16)
+
+
+class Config(C.Structure):
+    """or_config: the engine's Config (src/config.rs:8-43), micro defaults from Config::microkimi."""
+    _fields_ = ([(n, C.c_uint32) for n in ("n_layers", "d", "vocab", "n_experts", "top_k", "n_shared", "kda_heads", "kda_dim",
+                                          "kda_conv", "kda_fa")] + [("gate_lb", C.c_float)] +
+                [(n, C.c_uint32) for n in ("mla_heads", "mla_qa", "mla_kva", "mla_nope", "mla_rope", "mla_v", "routed_hidden",
+                                          "moe_inter", "shared_inter", "dense_inter", "attn_res_block", "first_k_dense")] +
+                [("rms_eps", C.c_float), ("eos_id", C.c_uint32), ("bos_id", C.c_uint32)])
+
+    @classmethod
+    def microkimi(cls, **over):
+        c = cls()
+        lib().or_config_microkimi(C.byref(c))
+        for k, v in over.items():
+            assert hasattr(c, k), k
+            setattr(c, k, v)
+        return c
+
+    def is_mla(self, l):
+        return bool(lib().or_config_is_mla(C.byref(self), l))
+
+    def is_moe(self, l):
+        return bool(lib().or_config_is_moe(C.byref(self), l))
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+def build_bin(path, cfg):
+    """`microkimi build` on the Gaussian fallback branch of every tensor (src/build.rs:344-576): writes the model file."""
+    rc = lib().or_build_bin(str(path).encode(), C.byref(cfg))
+    if rc != 0:
+        raise OSError(f"or_build_bin({path}) failed: {rc}")
+
+
+class BinFile:
+    """The MKIM0001/2 container (src/weights.rs:421-468), read-only."""
+
+    def __init__(self, path):
+        self._h = lib().or_bin_open(str(path).encode())
+        if not self._h:
+            raise OSError(f"cannot open {path}")
+        self.config = Config.from_buffer_copy(C.string_at(lib().or_bin_config(self._h), C.sizeof(Config)))
+
+    def __len__(self):
+        return int(lib().or_bin_count(self._h))
+
+    def entry(self, i):
+        name, dt, dims, off, size = C.c_char_p(), C.c_uint8(), (C.c_uint32 * 2)(), C.c_uint64(), C.c_uint64()
+        if lib().or_bin_entry(self._h, i, C.byref(name), C.byref(dt), dims, C.byref(off), C.byref(size)) != 0:
+            raise IndexError(i)
+        return name.value.decode(), dt.value, (dims[0], dims[1]), off.value, size.value
+
+    def get(self, name):
+        """f32 tensors: float32 array of the directory's shape; mxfp4: (packed [r, c/2], scales [r, c/32]) uint8 arrays."""
+        dt, dims, size = C.c_uint8(), (C.c_uint32 * 2)(), C.c_uint64()
+        p = lib().or_bin_get(self._h, name.encode(), C.byref(dt), dims, C.byref(size))
+        if not p:
+            raise KeyError(name)
+        raw = np.frombuffer(C.string_at(p, size.value), dtype=np.uint8)
+        r, c = dims[0], dims[1]
+        if dt.value == 0:
+            a = raw.view(np.float32)
+            return a.reshape(r, c) if c else a
+        return raw[:r * c // 2].reshape(r, c // 2), raw[r * c // 2:].reshape(r, c // 32)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().or_bin_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+
+class Model:
+    """Model::from_bin + Model::forward (src/model.rs:906-1025, 2889-3031): q8_0 lm_head, q8_0 MLA cache, MXFP4 experts
+    through the q8 integer path - the engine's defaults."""
+
+    def __init__(self, path, max_positions, n_threads=1):
+        self._h = lib().or_model_open(str(path).encode(), int(max_positions), int(n_threads))
+        if not self._h:
+            raise OSError(f"cannot load {path}")
+        self.config = Config.from_buffer_copy(C.string_at(lib().or_model_config(self._h), C.sizeof(Config)))
+
+    def forward(self, token, want_hidden=False):
+        """One token -> logits [vocab] (and the final normed hidden state [d])."""
+        logits = np.empty(self.config.vocab, np.float32)
+        hid = np.empty(self.config.d, np.float32)
+        rc = lib().or_model_forward(self._h, int(token), _p(logits, _f32p), _p(hid, _f32p))
+        if rc != 0:
+            raise ValueError(f"or_model_forward failed: {rc}")
+        return (logits, hid) if want_hidden else logits
+
+    def reset(self):
+        lib().or_model_reset(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().or_model_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
 
 
 def _p(a, t):
