@@ -378,11 +378,104 @@ int32_t mk_mla_attend(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *q, int
 /* All sequences at once, each over all the positions it holds: q f32 [n_seqs, n_heads, qdim],
  * out f32 [n_seqs, n_heads, vd].  DEVICE pointers. */
 int32_t mk_mla_attend_batch_dev(mk_ctx *ctx, mk_mla *mla, const float *q, float scale, float *out);
+/* One decode step of one sequence as launches whose shape does not depend on the position, so that a CUDA graph
+ * holding them can be replayed token after token: MlaCache::push of one position at the sequence's device-side
+ * count, then mla_attn_flash_q8_mqa over everything held (grids sized for max_positions; a full cache is
+ * MK_ERR_STATE from the call, or in the status word when replayed).  DEVICE pointers, shapes as mk_mla_append /
+ * mk_mla_attend.  A caller that replays a captured step must make no other append to that sequence in between. */
+int32_t mk_mla_decode_step_dev(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *k_row, const float *v_row, const float *q,
+                               float scale, float *out);
 /* Cache contents of one sequence back to HOST memory in the engine's layout
  * (src/model.rs:765-781), any pointer may be NULL:
  *  PER_HEAD: kq i8 [n, H, nope], ks f32 [n, H, nope/32], kr f32 [n, rope], vq i8 [n, H, vd], vs f32 [n, H, vd/32]
  *  ABSORBED: kq i8 [n, nope], ks f32 [n, nope/32]; the others are not written. */
 int32_t mk_mla_export(mk_ctx *ctx, const mk_mla *mla, int32_t seq, int8_t *kq, float *ks, float *kr, int8_t *vq, float *vs);
+
+/* ---- the engine's weight file (MKIM0001 / MKIM0002) -------------------------
+ * BinFile::open / read_config / BinWriter (src/weights.rs:1-64, 66-186, 390-590): magic, optional JSON
+ * configuration block, a directory of (name, dtype, dims, offset, size) and the blobs (64-byte aligned,
+ * routed-expert matrices 4096-byte aligned).  The reader maps the file read-only; pointers it hands out
+ * stay valid until mk_bin_close.  MKIM0001 files carry the historical micro configuration. */
+#define MK_DTYPE_F32     0
+#define MK_DTYPE_MXFP4   1   /* blob = packed [r, c/2] then ue8m0 scales [r, c/32] */
+#define MK_DTYPE_I32     2
+#define MK_DTYPE_VQ1     3
+#define MK_DTYPE_MXFP4SQ 4
+/* Config (src/config.rs:8-43).  has_layer_lists / is_deepseek are set by the reader when the file's
+ * configuration names explicit per-layer type lists or the DeepSeek architecture; mk_model_open
+ * refuses such files (MK_ERR_UNSUPPORTED). */
+typedef struct {
+    uint32_t n_layers, d, vocab, n_experts, top_k, n_shared;
+    uint32_t kda_heads, kda_dim, kda_conv, kda_fa;
+    float    gate_lb;
+    uint32_t mla_heads, mla_qa, mla_kva, mla_nope, mla_rope, mla_v;
+    uint32_t routed_hidden, moe_inter, shared_inter, dense_inter, attn_res_block, first_k_dense;
+    float    rms_eps;
+    uint32_t eos_id, bos_id;
+    uint32_t has_layer_lists, is_deepseek;
+} mk_model_config;
+void mk_model_config_default(mk_model_config *c);     /* Config::microkimi (src/config.rs:47-79) */
+typedef struct mk_bin mk_bin;
+typedef struct mk_bin_writer mk_bin_writer;
+int32_t mk_bin_open(const char *path, mk_bin **out);  /* a truncated or malformed file is MK_ERR_ARG, never a crash */
+int32_t mk_bin_close(mk_bin *b);
+int32_t mk_bin_config(const mk_bin *b, mk_model_config *out);
+int64_t mk_bin_count(const mk_bin *b);
+/* Tensor by name / by directory position: dtype, number of dims, dims[4], HOST pointer to the blob, its size.
+ * Any output pointer may be NULL. */
+int32_t mk_bin_find(const mk_bin *b, const char *name, int32_t *dtype, int32_t *ndims, uint32_t *dims, const void **data,
+                    uint64_t *size);
+int32_t mk_bin_entry(const mk_bin *b, int64_t i, const char **name, int32_t *dtype, int32_t *ndims, uint32_t *dims,
+                     const void **data, uint64_t *size);
+/* Writer: add every tensor (directory order = call order), begin (lays the file out and writes header and
+ * directory), put each blob, finish.  cfg == NULL writes MKIM0001, otherwise MKIM0002 with the JSON block. */
+int32_t mk_bin_writer_create(const mk_model_config *cfg, mk_bin_writer **out);
+int32_t mk_bin_writer_add(mk_bin_writer *w, const char *name, int32_t dtype, int32_t ndims, const uint32_t *dims);
+int32_t mk_bin_writer_begin(mk_bin_writer *w, const char *path);
+int32_t mk_bin_writer_put(mk_bin_writer *w, const char *name, const void *data, uint64_t size);
+int32_t mk_bin_writer_finish(mk_bin_writer *w);       /* closes the file and frees the writer */
+
+/* mxfp4::quantize (src/mxfp4.rs:38-138) on the GPU, DEVICE pointers: w f32 [rows, cols] -> packed u8
+ * [rows, cols/2] + ue8m0 scales u8 [rows, cols/32].  search != 0: the three-candidate scale search
+ * (the engine's default), 0: quantize_naive.  Bytes equal the CPU quantizer's. */
+int32_t mk_quantize_mxfp4_dev(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, int32_t search, uint8_t *packed,
+                              uint8_t *scales);
+
+/* ---- the whole decode token ---------------------------------------------------
+ * Model::from_bin + Model::forward (src/model.rs:906-1025, 2889-3031) for the K3 architecture with the
+ * engine's defaults: q8_0 lm_head built at load, q8_0 MLA cache, MXFP4 experts through the q8 integer
+ * path.  All weights and all layer state (KDA conv windows and S, MLA caches, AttnRes block rows) live
+ * on the GPU; a token is a fixed sequence of launches that reads its position counters on the device,
+ * so with use_graph the library captures it once as a CUDA graph and replays it per token. */
+typedef struct mk_model mk_model;
+typedef struct {
+    int32_t max_positions;   /* tokens a sequence may hold (prompt + generated): capacity of every MLA cache */
+    int32_t use_graph;       /* 1: replay the token as a CUDA graph from the second call on */
+    int32_t rank, world;     /* expert parallel + vocabulary-sharded lm_head over `world` GPUs (0 or 1: one GPU):
+                                this rank keeps routed experts [rank E/world, (rank+1) E/world) of every MoE
+                                layer and the same share of the lm_head rows; the rest of the model is replicated */
+} mk_model_opts;
+int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_opts *opts, mk_model **out);
+int32_t mk_model_free(mk_ctx *ctx, mk_model *m);
+int32_t mk_model_reset(mk_ctx *ctx, mk_model *m);              /* new sequence: fresh caches, position 0 */
+int32_t mk_model_positions(mk_ctx *ctx, const mk_model *m);    /* tokens consumed so far, or a negative status */
+int64_t mk_model_weight_bytes(const mk_model *m);              /* device bytes held by weights */
+int64_t mk_model_launches_per_token(const mk_model *m);        /* kernels in one token (as last enqueued) */
+/* world > 1: handles [2][64] of this rank's exchange buffers (expert rows, logits), then connect with the
+ * handles of all ranks [world][2][64] (as mk_gather_connect / mk_moe_ep_connect). */
+int32_t mk_model_ep_handles(mk_ctx *ctx, mk_model *m, uint8_t *handles);
+int32_t mk_model_ep_connect(mk_ctx *ctx, mk_model *m, const uint8_t *all_handles);
+/* One token, enqueued on the context's stream without synchronizing.  token: DEVICE int32 (NULL = the
+ * greedy pick of the previous call, which stays on the device); logits (optional): DEVICE f32 [vocab];
+ * next (optional): DEVICE int32 = first index of the maximum logit (src/model.rs:3277-3290). */
+int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t *token, float *logits, int32_t *next);
+/* HOST variant: copies the token in, runs, copies logits [vocab] (optional) and the pick (optional) out, synchronizes. */
+int32_t mk_model_forward(mk_ctx *ctx, mk_model *m, int32_t token, float *logits, int32_t *next);
+/* The greedy loop of run_turn (src/model.rs:3586-3593): n_prompt prompt tokens one by one, then n_new picks, each
+ * fed back as the next token on the device; out_tokens HOST int32 [n_new]; one synchronization at the end. */
+int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_new, int32_t *out_tokens);
+/* The final normed hidden state of the last token (the input of the lm_head), HOST f32 [d]: for parity checks. */
+int32_t mk_model_last_hidden(mk_ctx *ctx, mk_model *m, float *hidden);
 
 #ifdef __cplusplus
 }

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmk_b200.so")
-SOURCES = ["mk_api.cu", "qgemv.cu", "weights.cu", "moe.cu", "mla.cu", "spine.cu", "gather.cu", "vq.cu", "kda.cu"]
+SOURCES = ["mk_api.cu", "qgemv.cu", "weights.cu", "moe.cu", "mla.cu", "spine.cu", "gather.cu", "vq.cu", "kda.cu", "binfile.cu", "model.cu"]
 HEADERS = [os.path.join(CSRC, "mk_common.cuh"), os.path.join(HERE, "..", "include", "mk_cuda.h")]
 
 NVCC_FLAGS = [

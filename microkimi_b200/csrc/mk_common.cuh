@@ -131,6 +131,7 @@ int32_t mk_launch_rmsnorm(mk_ctx *ctx, const float *x, const float *w, int n, in
 int32_t mk_launch_situ(mk_ctx *ctx, const float *a, const float *u, int64_t count, float *out);
 int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, int batch, int32_t *out, void *scratch);
 size_t mk_argmax_scratch_bytes(int batch);
+void mk_mla_note_replay(mk_mla *m, int seq);   // mla.cu: host-side position count after a graph replay of a decode step
 // weight (re)tiling
 int32_t mk_launch_retile_mxfp4(mk_ctx *ctx, const uint8_t *packed, const uint8_t *scales, mk_weight *w);
 int32_t mk_launch_untile_mxfp4(mk_ctx *ctx, const mk_weight *w, uint8_t *packed, uint8_t *scales);

@@ -83,7 +83,10 @@ struct MlaDev {
 // Absorbed layout: the nb blocks of the latent row go to BOTH sides.
 __global__ void __launch_bounds__(256)
 mla_append_kernel(const MlaDev c, int seq, int pos0, int n, const float *__restrict__ k_rows, const float *__restrict__ v_rows,
-                  int absorbed) {
+                  int absorbed, const int *__restrict__ pos_dev) {
+    // pos_dev: the first position comes from the device-side count of the sequence (a launch that can be
+    // replayed from a CUDA graph); a full cache is reported by the bump kernel that follows, nothing is written
+    if (pos_dev) { pos0 = pos_dev[seq]; if (pos0 + n > c.cap) return; }
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int nblk = absorbed ? c.nb : c.nb + c.nbv;
@@ -124,13 +127,21 @@ mla_append_kernel(const MlaDev c, int seq, int pos0, int n, const float *__restr
     }
 }
 // rope part of K, f32, stored once per position from head 0 (src/model.rs:1592-1593)
-__global__ void mla_append_rope_kernel(const MlaDev c, int seq, int pos0, int n, const float *__restrict__ k_rows) {
+__global__ void mla_append_rope_kernel(const MlaDev c, int seq, int pos0, int n, const float *__restrict__ k_rows,
+                                       const int *__restrict__ pos_dev) {
+    if (pos_dev) { pos0 = pos_dev[seq]; if (pos0 + n > c.cap) return; }
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n * c.rope) return;
     const int i = idx / c.rope, r = idx % c.rope;
     const int j = pos0 + i, tile = j >> 5, p = j & 31;
     const int hd = c.nope + c.rope;
     c.krt[((((int64_t)seq * c.T + tile) * c.RC + (r >> 2)) * 32 + p) * 4 + (r & 3)] = k_rows[(int64_t)i * c.H * hd + c.nope + r];
+}
+// after an append by device position: the sequence holds n more positions (or the status word says it is full)
+__global__ void mla_bump_kernel(int *__restrict__ npos, int seq, int n, int cap, int32_t *__restrict__ status) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (npos[seq] + n > cap) atomicCAS(status, 0, MK_ERR_STATE);
+    else npos[seq] += n;
 }
 
 // ------------------------------------------------------------------ export to the engine's layout
@@ -723,10 +734,10 @@ extern "C" int32_t mk_mla_append_dev(mk_ctx *ctx, mk_mla *m, int32_t seq, const 
     mk_prof_scope prof(ctx, MK_PROF_MLA);
     const int nblk = absorbed ? m->nb : m->nb + m->nbv;
     const int64_t warps = (int64_t)n * m->kvh * nblk;
-    mla_append_kernel<<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(c, seq, m->npos[seq], n, k_rows, v_rows, absorbed ? 1 : 0);
+    mla_append_kernel<<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(c, seq, m->npos[seq], n, k_rows, v_rows, absorbed ? 1 : 0, nullptr);
     ctx->launches++;
     if (m->rope > 0) {
-        mla_append_rope_kernel<<<(unsigned)mk_ceil_div((int64_t)n * m->rope, 128), 128, 0, ctx->stream>>>(c, seq, m->npos[seq], n, k_rows);
+        mla_append_rope_kernel<<<(unsigned)mk_ceil_div((int64_t)n * m->rope, 128), 128, 0, ctx->stream>>>(c, seq, m->npos[seq], n, k_rows, nullptr);
         ctx->launches++;
     }
     MK_CUDA(cudaGetLastError());
@@ -909,6 +920,40 @@ extern "C" int32_t mk_mla_attend_batch_dev(mk_ctx *ctx, mk_mla *m, const float *
     MK_CUDA(cudaSetDevice(ctx->device));
     return mla_attend_launch(ctx, m, q, m->nseq, 0, 0, max_n, scale, out);
 }
+
+// One decode step of one sequence whose launches do not depend on the position: append by the device-side
+// count, bump the count, attend over everything held with grids sized for the cache's capacity.
+extern "C" int32_t mk_mla_decode_step_dev(mk_ctx *ctx, mk_mla *m, int32_t seq, const float *k_row, const float *v_row, const float *q,
+                                          float scale, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && k_row != nullptr && q != nullptr && out != nullptr, "NULL argument");
+    MK_CHECK_ARG(seq >= 0 && seq < m->nseq, "no such sequence");
+    const bool absorbed = m->layout == MK_MLA_ABSORBED;
+    MK_CHECK_ARG(absorbed || v_row != nullptr, "v_row is NULL");
+    if (m->npos[seq] + 1 > m->cap) {
+        mk_set_error("mk_mla_decode_step_dev: sequence %d already holds %d of %d positions", seq, m->npos[seq], m->cap);
+        return MK_ERR_STATE;
+    }
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const MlaDev c = mla_dev(m);
+    {
+        mk_prof_scope prof(ctx, MK_PROF_MLA);
+        const int nblk = absorbed ? m->nb : m->nb + m->nbv;
+        const int64_t warps = (int64_t)m->kvh * nblk;
+        mla_append_kernel<<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(c, seq, 0, 1, k_row, v_row, absorbed ? 1 : 0, m->npos_dev);
+        ctx->launches++;
+        if (m->rope > 0) {
+            mla_append_rope_kernel<<<(unsigned)mk_ceil_div((int64_t)m->rope, 128), 128, 0, ctx->stream>>>(c, seq, 0, 1, k_row, m->npos_dev);
+            ctx->launches++;
+        }
+        mla_bump_kernel<<<1, 32, 0, ctx->stream>>>(m->npos_dev, seq, 1, m->cap, ctx->status_dev);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+    }
+    m->npos[seq] += 1;
+    return mla_attend_launch(ctx, m, q, 1, seq, 0, m->cap, scale, out);
+}
+// The host-side count of a sequence follows a replayed step (the device-side count moved inside the graph).
+void mk_mla_note_replay(mk_mla *m, int seq) { if (m && seq >= 0 && seq < m->nseq && m->npos[seq] < m->cap) m->npos[seq] += 1; }
 
 extern "C" int32_t mk_mla_export(mk_ctx *ctx, const mk_mla *m, int32_t seq, int8_t *kq, float *ks, float *kr, int8_t *vq, float *vs) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr && seq >= 0 && seq < m->nseq, "bad argument");

@@ -1,0 +1,690 @@
+// The whole decode token of the K3 engine on one GPU (or expert-parallel over the GPUs of a node):
+// Model::from_bin + Model::forward (src/model.rs:906-1025, 2889-3031) over the device calls of this library.
+//
+//   embed row -> for every layer: AttnRes + rmsnorm -> KDA block (kda_forward, src/model.rs:1179-1232) or MLA
+//   block (mla_forward, :1939-2022) -> residual -> AttnRes + rmsnorm -> dense MLP (dense_forward, :2382-2396) or
+//   MoE (moe_forward, :2150-2380) -> residual; final AttnRes + rmsnorm -> q8_0 lm_head + greedy pick.
+//
+// Everything a token needs is resident on the GPU, and every launch of a token has the same shape at every
+// position (the MLA caches count their positions on the device), so the token is captured once as a CUDA graph
+// and replayed.  Projections that read the same vector are stacked into one f32 matrix at load: every row of a
+// stacked matvec is the dot() the engine computes for that row, so stacking changes no bit.
+#include <new>
+#include <string>
+#include <vector>
+
+#include "mk_common.cuh"
+
+namespace {
+
+__global__ void embed_row_kernel(const float *__restrict__ embed, const int32_t *__restrict__ token, int vocab, int d,
+                                 float *__restrict__ hidden, int32_t *__restrict__ status) {
+    int t = *token;
+    if (t < 0 || t >= vocab) {   // a token id outside the vocabulary: reported, row 0 stands in
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(status, 0, MK_ERR_ARG);
+        t = 0;
+    }
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < d) hidden[j] = embed[(int64_t)t * d + j];
+}
+// out[j] = a[j] + b[j] (src/model.rs:2943-2952, 2994-2996: p[j] += attn_out[j]; hidden[j] = prefix2[j] + mlp_out[j])
+__global__ void vec_add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int n) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n) out[j] = __fadd_rn(a[j], b[j]);
+}
+// K[h] = kb[h][..nope] ++ k_rot ; V[h] = kb[h][nope..nope+v] (src/model.rs:1964-1973)
+__global__ void mla_assemble_kernel(const float *__restrict__ kb, const float *__restrict__ k_rot, int H, int nope, int rope, int vd,
+                                    float *__restrict__ k_new, float *__restrict__ v_new) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int qh = nope + rope, per = qh + vd;
+    if (i >= H * per) return;
+    const int h = i / per, r = i % per;
+    if (r < nope) k_new[h * qh + r] = kb[h * (nope + vd) + r];
+    else if (r < qh) k_new[h * qh + r] = k_rot[r - nope];
+    else v_new[h * vd + (r - qh)] = kb[h * (nope + vd) + nope + (r - qh)];
+}
+__global__ void copy_i32_kernel(const int32_t *__restrict__ src, int32_t *__restrict__ dst) { *dst = *src; }
+// MXFP4 blobs of one layer (packed then scales, each blob where the file put it inside the staged span) -> the tiled
+// device layout of a weight arena; one grid row per matrix (the arithmetic of retile_mxfp4_kernel in weights.cu).
+__global__ void retile_mxfp4_batch_kernel(const uint8_t *__restrict__ span, const uint64_t *__restrict__ blob_off, uint8_t *__restrict__ arena,
+                                          uint64_t stride_v, uint64_t stride_s, uint64_t scales_base, int first, int step, int64_t rows,
+                                          int64_t cols, int64_t nrt, int64_t nb, int64_t nbp) {
+    const int w = first + (int)blockIdx.y * step;   // entry of the (expert, matrix) list
+    const uint8_t *packed = span + blob_off[w];
+    const uint8_t *scales = packed + rows * cols / 2;
+    uint32_t *tv = (uint32_t *)(arena + (uint64_t)w * stride_v);
+    uint8_t *ts = arena + scales_base + (uint64_t)w * stride_s;
+    const int64_t nwords = nrt * (nbp / 2) * 128;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < nwords) {
+        const int64_t chunk = idx >> 7;
+        const int within = (int)(idx & 127);
+        const int lane = within >> 2, j = within & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const int64_t rt = chunk / (nbp / 2), bp = chunk % (nbp / 2);
+        const int64_t row = rt * 16 + g + ((j & 1) ? 8 : 0);
+        const int64_t b = bp * 2 + (j >> 1);
+        uint32_t v = 0;
+        if (row < rows && b < nb) {
+            const uint8_t *p = packed + row * (cols / 2) + b * 16 + t * 4;   // blobs are only byte-aligned inside the span
+            v = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+        }
+        tv[idx] = v;
+    }
+    const int64_t nsc = nrt * nbp * 16;
+    if (idx < nsc) {
+        const int r16 = (int)(idx & 15);
+        const int64_t rb = idx >> 4;
+        const int64_t rt = rb / nbp, b = rb % nbp;
+        const int64_t row = rt * 16 + r16;
+        ts[mk_scale_off(rt, nbp, b, r16)] = (row < rows && b < nb) ? scales[row * nb + b] : (uint8_t)0;
+    }
+}
+
+struct Layer {
+    bool is_mla = false, is_moe = false;
+    int nb_before = 0;       // AttnRes block rows before this layer's first mix
+    bool pushes = false;     // l % attn_res_block == 0: the layer input becomes a block row
+    float *input_ln = nullptr, *post_ln = nullptr, *sa_w = nullptr, *mlp_w = nullptr;
+    // KDA: rows of w_x = q, k, v, g_proj (proj each), f_a (fa), b_proj (heads)
+    float *w_x = nullptr, *f_b = nullptr, *o_proj = nullptr;
+    int w_x_rows = 0;
+    mk_kda *kda = nullptr;
+    // MLA: rows of w_x = q_a (qa), kv_a (kva + rope), g_proj (H v)
+    float *q_a_ln = nullptr, *q_b = nullptr, *kv_a_ln = nullptr, *kv_b = nullptr;
+    mk_mla *cache = nullptr;
+    // FFN
+    float *dgu = nullptr, *dd = nullptr;     // dense: [gate; up] stacked, down
+    mk_moe *moe = nullptr;
+    void *expert_arena = nullptr;
+    std::vector<mk_weight> expert_w;          // records into the arena (not owners)
+    mk_weight rd, ru, sg, sd, su;             // f32 records for the MoE descriptor (not owners)
+};
+
+} // namespace
+
+struct mk_model {
+    mk_model_config cfg;
+    mk_model_opts opts;
+    int world, rank;
+    std::vector<void *> owned;      // device allocations freed with the model
+    int64_t weight_bytes = 0;
+    std::vector<Layer> layers;
+    float *embed = nullptr, *norm_f = nullptr, *out_w = nullptr;
+    mk_weight *head = nullptr;      // q8_0 rows [head_row0, head_row0 + head_rows) of lm_head
+    int64_t head_row0 = 0, head_rows = 0;
+    mk_gather *gather = nullptr;
+    mk_moe_ep *ep = nullptr;
+    // activations
+    float *hidden = nullptr, *res = nullptr, *x = nullptr, *attn_out = nullptr, *p2 = nullptr, *mlp_out = nullptr, *blocks = nullptr;
+    float *y = nullptr, *g_low = nullptr, *o = nullptr;                                     // KDA
+    float *qan = nullptr, *q = nullptr, *kpn = nullptr, *kb = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr; // MLA
+    float *au = nullptr, *act = nullptr;                                                    // dense
+    float *logits = nullptr;
+    int32_t *tok = nullptr, *next = nullptr;
+    int positions = 0;
+    int64_t launches_per_token = 0;
+    uint8_t handles[128] = {0};     // world > 1: IPC handles of this rank's expert-row table and logits buffer
+    cudaGraphExec_t graph = nullptr;
+    void *graph_ws = nullptr;       // the context's shared workspace as the recorded launches saw it
+    int warm = 0;
+};
+
+namespace {
+
+struct Loader {
+    mk_ctx *ctx;
+    const mk_bin *bin;
+    mk_model *m;
+    int32_t rc = MK_OK;
+    std::string err;
+
+    const void *find(const std::string &name, int dtype, uint64_t bytes) {
+        if (rc != MK_OK) return nullptr;
+        int32_t dt = 0;
+        const void *p = nullptr;
+        uint64_t sz = 0;
+        if (mk_bin_find(bin, name.c_str(), &dt, nullptr, nullptr, &p, &sz) != MK_OK || dt != dtype || sz != bytes) {
+            rc = MK_ERR_ARG;
+            err = "tensor " + name + " is missing or has the wrong type or size";
+            return nullptr;
+        }
+        return p;
+    }
+    void *dev_alloc(size_t bytes) {
+        if (rc != MK_OK) return nullptr;
+        void *d = nullptr;
+        const cudaError_t e = cudaMalloc(&d, bytes ? bytes : 4);
+        if (e != cudaSuccess) { rc = e == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA; err = cudaGetErrorString(e); return nullptr; }
+        m->owned.push_back(d);
+        return d;
+    }
+    float *zeros(size_t count) {
+        float *d = (float *)dev_alloc(count * 4);
+        if (d && cudaMemsetAsync(d, 0, count * 4, ctx->stream) != cudaSuccess) { rc = MK_ERR_CUDA; err = "memset failed"; }
+        return d;
+    }
+    void upload(void *dst, const void *src, size_t bytes) {
+        if (rc != MK_OK) return;
+        // the source is a file mapping (pageable): the copy returns when the bytes have left it
+        if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) { rc = MK_ERR_CUDA; err = "upload failed"; }
+    }
+    // one f32 tensor [count]
+    float *f32(const std::string &name, uint64_t count) {
+        const void *p = find(name, MK_DTYPE_F32, count * 4);
+        float *d = (float *)dev_alloc((size_t)count * 4);
+        if (p && d) { upload(d, p, (size_t)count * 4); m->weight_bytes += (int64_t)count * 4; }
+        return d;
+    }
+    // several f32 matrices [rows_i, cols] stacked by rows
+    float *stacked(const std::vector<std::pair<std::string, uint64_t>> &parts, uint64_t cols, int *rows_out) {
+        uint64_t rows = 0;
+        for (auto &p : parts) rows += p.second;
+        float *d = (float *)dev_alloc((size_t)rows * cols * 4);
+        uint64_t r = 0;
+        for (auto &p : parts) {
+            const void *src = find(p.first, MK_DTYPE_F32, p.second * cols * 4);
+            if (src && d) upload(d + r * cols, src, (size_t)p.second * cols * 4);
+            r += p.second;
+        }
+        m->weight_bytes += (int64_t)rows * cols * 4;
+        if (rows_out) *rows_out = (int)rows;
+        return d;
+    }
+    // norm.weight * proj.weight, combined at load (src/model.rs:911-915)
+    float *combined(const std::string &norm, const std::string &proj, uint64_t d) {
+        const float *a = (const float *)find(norm, MK_DTYPE_F32, d * 4), *b = (const float *)find(proj, MK_DTYPE_F32, d * 4);
+        float *dv = (float *)dev_alloc((size_t)d * 4);
+        if (a && b && dv) {
+            std::vector<float> t(d);
+            for (uint64_t i = 0; i < d; ++i) t[i] = a[i] * b[i];
+            if (cudaMemcpy(dv, t.data(), (size_t)d * 4, cudaMemcpyHostToDevice) != cudaSuccess) { rc = MK_ERR_CUDA; err = "upload failed"; }
+            m->weight_bytes += (int64_t)d * 4;
+        }
+        return dv;
+    }
+};
+
+mk_weight f32_record(float *values, int64_t rows, int64_t cols) {
+    mk_weight w;
+    memset(&w, 0, sizeof(w));
+    w.fmt = MK_FMT_F32; w.rows = rows; w.cols = cols; w.values = values; w.values_bytes = (size_t)rows * cols * 4;
+    return w;
+}
+
+// The routed experts [e0, e1) of one MoE layer: the span of the file that holds their blobs goes to the GPU in one
+// copy and one launch re-tiles all of them into an arena (values of every matrix, then scales of every matrix).
+int32_t load_experts(Loader &L, Layer &ly, int layer, int e0, int e1) {
+    const mk_model_config &c = L.m->cfg;
+    const int64_t I = c.moe_inter, R = c.routed_hidden;
+    const int n = (e1 - e0) * 3;
+    ly.expert_w.assign((size_t)c.n_experts * 3, mk_weight());
+    for (auto &w : ly.expert_w) memset(&w, 0, sizeof(w));
+    if (n <= 0) return MK_OK;
+    static const char *const wn[3] = {"w1", "w2", "w3"};
+    std::vector<const uint8_t *> src((size_t)n);
+    const uint64_t blob = (uint64_t)I * R / 2 + (uint64_t)I * R / 32;
+    const uint8_t *lo = nullptr, *hi = nullptr;
+    for (int e = e0; e < e1; ++e)
+        for (int k = 0; k < 3; ++k) {
+            const std::string name = "layers." + std::to_string(layer) + ".block_sparse_moe.experts." + std::to_string(e) + "." + wn[k];
+            int32_t dt = 0, nd = 0;
+            uint32_t dims[4] = {0, 0, 0, 0};
+            const void *p = nullptr;
+            uint64_t sz = 0;
+            const int64_t rows = k == 1 ? R : I, cols = k == 1 ? I : R;
+            if (mk_bin_find(L.bin, name.c_str(), &dt, &nd, dims, &p, &sz) != MK_OK || dt != MK_DTYPE_MXFP4 || nd != 2 || dims[0] != rows ||
+                dims[1] != cols || sz != blob) {
+                mk_set_error("mk_model_open: expert tensor %s is missing, not MXFP4 or of the wrong shape", name.c_str());
+                return MK_ERR_ARG;
+            }
+            const uint8_t *b = (const uint8_t *)p;
+            src[(size_t)(e - e0) * 3 + k] = b;
+            if (!lo || b < lo) lo = b;
+            if (!hi || b + blob > hi) hi = b + blob;
+        }
+    // w1 / w3 are [I, R], w2 is [R, I]: the same element count, but different tilings; keep one stride for all
+    auto tiled_bytes = [](int64_t rows, int64_t cols, size_t *vb, size_t *sb) {
+        const int64_t nrt = mk_ceil_div(rows, 16), nbp = mk_ceil_div(cols / 32, 4) * 4;
+        *vb = (size_t)nrt * (nbp / 2) * 512;
+        *sb = (size_t)nrt * nbp * 16;
+    };
+    size_t vb13, sb13, vb2, sb2;
+    tiled_bytes(I, R, &vb13, &sb13);
+    tiled_bytes(R, I, &vb2, &sb2);
+    const size_t stride_v = mk_align_up(vb13 > vb2 ? vb13 : vb2, 256), stride_s = mk_align_up(sb13 > sb2 ? sb13 : sb2, 256);
+    const size_t scales_base = stride_v * (size_t)n, arena_bytes = scales_base + stride_s * (size_t)n;
+    const size_t span = (size_t)(hi - lo);
+    cudaError_t e_ = cudaMalloc(&ly.expert_arena, arena_bytes);
+    void *stage = nullptr;
+    uint64_t *off_dev = nullptr;
+    if (e_ == cudaSuccess) e_ = cudaMalloc(&stage, span);
+    if (e_ == cudaSuccess) e_ = cudaMalloc((void **)&off_dev, (size_t)n * 8);
+    std::vector<uint64_t> off((size_t)n);
+    for (int i = 0; i < n; ++i) off[(size_t)i] = (uint64_t)(src[(size_t)i] - lo);
+    if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(stage, lo, span, cudaMemcpyHostToDevice, L.ctx->stream);
+    if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(off_dev, off.data(), (size_t)n * 8, cudaMemcpyHostToDevice, L.ctx->stream);
+    // one launch per matrix kind (w1, w2, w3 of every expert): grid rows = experts
+    for (int k = 0; k < 3 && e_ == cudaSuccess; ++k) {
+        const int64_t rows = k == 1 ? R : I, cols = k == 1 ? I : R;
+        const int64_t nrt = mk_ceil_div(rows, 16), nb = cols / 32, nbp = mk_ceil_div(nb, 4) * 4;
+        const int64_t work = nrt * (nbp / 2) * 128 > nrt * nbp * 16 ? nrt * (nbp / 2) * 128 : nrt * nbp * 16;
+        retile_mxfp4_batch_kernel<<<dim3((unsigned)mk_ceil_div(work, 256), (unsigned)(e1 - e0)), 256, 0, L.ctx->stream>>>(
+            (const uint8_t *)stage, off_dev, (uint8_t *)ly.expert_arena, stride_v, stride_s, scales_base, k, 3, rows, cols, nrt, nb, nbp);
+        L.ctx->launches++;
+        e_ = cudaGetLastError();
+    }
+    if (e_ == cudaSuccess) e_ = cudaStreamSynchronize(L.ctx->stream);
+    if (stage) cudaFree(stage);
+    if (off_dev) cudaFree(off_dev);
+    if (e_ != cudaSuccess) {
+        mk_set_error("mk_model_open: experts of layer %d: %s", layer, cudaGetErrorString(e_));
+        return e_ == cudaErrorMemoryAllocation ? MK_ERR_OOM : MK_ERR_CUDA;
+    }
+    for (int e = e0; e < e1; ++e)
+        for (int k = 0; k < 3; ++k) {
+            const size_t i = (size_t)(e - e0) * 3 + k;
+            mk_weight &w = ly.expert_w[(size_t)e * 3 + k];
+            w.fmt = MK_FMT_MXFP4;
+            w.rows = k == 1 ? R : I; w.cols = k == 1 ? I : R;
+            w.nrt = mk_ceil_div(w.rows, 16); w.nb = w.cols / 32; w.nbp = mk_ceil_div(w.nb, 4) * 4;
+            w.values = (uint8_t *)ly.expert_arena + i * stride_v;
+            w.scales = (uint8_t *)ly.expert_arena + scales_base + i * stride_s;
+            w.values_bytes = k == 1 ? vb2 : vb13; w.scales_bytes = k == 1 ? sb2 : sb13;
+        }
+    L.m->weight_bytes += (int64_t)arena_bytes;
+    return MK_OK;
+}
+
+void free_model(mk_ctx *ctx, mk_model *m) {
+    if (!m) return;
+    cudaStreamSynchronize(ctx->stream);
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    for (Layer &ly : m->layers) {
+        if (ly.kda) mk_kda_free(ctx, ly.kda);
+        if (ly.cache) mk_mla_free(ctx, ly.cache);
+        if (ly.moe) mk_moe_free(ctx, ly.moe);
+        if (ly.expert_arena) cudaFree(ly.expert_arena);
+    }
+    if (m->head) mk_weight_free(ctx, m->head);
+    if (m->gather) mk_gather_free(ctx, m->gather);
+    if (m->ep) mk_moe_ep_free(ctx, m->ep);
+    for (void *p : m->owned) cudaFree(p);
+    delete m;
+}
+
+} // namespace
+
+extern "C" int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_opts *opts, mk_model **out) {
+    MK_CHECK_ARG(ctx != nullptr && bin != nullptr && opts != nullptr && out != nullptr, "NULL argument");
+    *out = nullptr;
+    mk_model_config c;
+    mk_bin_config(bin, &c);
+    if (c.has_layer_lists || c.is_deepseek) {
+        mk_set_error("mk_model_open: explicit per-layer type lists and the DeepSeek architecture are not supported");
+        return MK_ERR_UNSUPPORTED;
+    }
+    const int world = opts->world > 1 ? opts->world : 1, rank = opts->world > 1 ? opts->rank : 0;
+    MK_CHECK_ARG(world <= 8 && rank >= 0 && rank < world, "need 0 <= rank < world <= 8");
+    MK_CHECK_ARG(opts->max_positions >= 1, "max_positions must be positive");
+    const int64_t d = c.d, proj = (int64_t)c.kda_heads * c.kda_dim, qh = c.mla_nope + c.mla_rope, H = c.mla_heads;
+    const int64_t qb = H * qh, kvb = H * (c.mla_nope + c.mla_v), cdim = c.mla_kva + c.mla_rope, hv = H * c.mla_v;
+    MK_CHECK_ARG(c.n_layers >= 1 && d % 32 == 0 && c.vocab >= 1 && c.attn_res_block >= 1, "bad model dims");
+    MK_CHECK_ARG(proj % 4 == 0 && c.kda_fa % 4 == 0 && c.mla_qa % 4 == 0 && cdim % 4 == 0 && c.mla_kva % 4 == 0 && c.dense_inter % 4 == 0,
+                 "projection widths must be multiples of 4 (slices of a stacked result stay 16-byte aligned)");
+    MK_CHECK_ARG(c.n_experts % world == 0 && c.vocab % world == 0, "n_experts and vocab must divide by the number of ranks");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    mk_model *m = new (std::nothrow) mk_model();
+    if (!m) return MK_ERR_OOM;
+    m->cfg = c; m->opts = *opts; m->world = world; m->rank = rank;
+    Loader L{ctx, bin, m};
+    auto fail = [&](int32_t rc, const std::string &why) {
+        if (!why.empty()) mk_set_error("mk_model_open: %s", why.c_str());
+        free_model(ctx, m);
+        return rc;
+    };
+    m->embed = L.f32("embed_tokens.weight", (uint64_t)c.vocab * d);
+    m->norm_f = L.f32("norm.weight", d);
+    m->out_w = L.combined("output_attn_res_norm.weight", "output_attn_res_proj.weight", d);
+    const int max_blocks = (int)(c.n_layers / c.attn_res_block + 2);
+    m->blocks = L.zeros((size_t)max_blocks * d);
+    m->hidden = L.zeros(d); m->res = L.zeros(d); m->x = L.zeros(d); m->attn_out = L.zeros(d); m->p2 = L.zeros(d); m->mlp_out = L.zeros(d);
+    m->y = L.zeros((size_t)(4 * proj + c.kda_fa + c.kda_heads) > (size_t)(c.mla_qa + cdim + hv) ? (size_t)(4 * proj + c.kda_fa + c.kda_heads)
+                                                                                             : (size_t)(c.mla_qa + cdim + hv));
+    m->g_low = L.zeros(proj); m->o = L.zeros(proj);
+    m->qan = L.zeros(c.mla_qa); m->q = L.zeros(qb); m->kpn = L.zeros(c.mla_kva); m->kb = L.zeros(kvb);
+    m->k_new = L.zeros(qb); m->v_new = L.zeros(hv); m->attn = L.zeros(hv);
+    m->au = L.zeros((size_t)2 * c.dense_inter); m->act = L.zeros(c.dense_inter);
+    m->logits = L.zeros(c.vocab);
+    m->tok = (int32_t *)L.zeros(1); m->next = (int32_t *)L.zeros(1);
+    if (L.rc != MK_OK) return fail(L.rc, L.err);
+
+    m->layers.resize(c.n_layers);
+    int nb = 0;
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        Layer &ly = m->layers[l];
+        const std::string p = "layers." + std::to_string(l) + ".";
+        ly.is_mla = l % 4 == 3 || l == c.n_layers - 1;   // Config::is_mla (src/config.rs:127-132)
+        ly.is_moe = l >= c.first_k_dense;                // Config::is_moe (src/config.rs:133-138)
+        ly.nb_before = nb;
+        ly.pushes = l % c.attn_res_block == 0;
+        if (ly.pushes) ++nb;
+        ly.input_ln = L.f32(p + "input_layernorm.weight", d);
+        ly.post_ln = L.f32(p + "post_attention_layernorm.weight", d);
+        ly.sa_w = L.combined(p + "self_attention_res_norm.weight", p + "self_attention_res_proj.weight", d);
+        ly.mlp_w = L.combined(p + "mlp_res_norm.weight", p + "mlp_res_proj.weight", d);
+        if (ly.is_mla) {
+            ly.w_x = L.stacked({{p + "self_attn.q_a_proj.weight", c.mla_qa}, {p + "self_attn.kv_a_proj_with_mqa.weight", (uint64_t)cdim},
+                                {p + "self_attn.g_proj.weight", (uint64_t)hv}}, d, &ly.w_x_rows);
+            ly.q_a_ln = L.f32(p + "self_attn.q_a_layernorm.weight", c.mla_qa);
+            ly.q_b = L.f32(p + "self_attn.q_b_proj.weight", (uint64_t)qb * c.mla_qa);
+            ly.kv_a_ln = L.f32(p + "self_attn.kv_a_layernorm.weight", c.mla_kva);
+            ly.kv_b = L.f32(p + "self_attn.kv_b_proj.weight", (uint64_t)kvb * c.mla_kva);
+            ly.o_proj = L.f32(p + "self_attn.o_proj.weight", (uint64_t)d * hv);
+            if (L.rc != MK_OK) return fail(L.rc, L.err);
+            mk_mla_desc md = {MK_MLA_PER_HEAD, (int32_t)H, (int32_t)c.mla_nope, (int32_t)c.mla_rope, (int32_t)c.mla_v, opts->max_positions, 1};
+            const int32_t rc = mk_mla_create(ctx, &md, &ly.cache);
+            if (rc != MK_OK) return fail(rc, "");
+        } else {
+            ly.w_x = L.stacked({{p + "self_attn.q_proj.weight", (uint64_t)proj}, {p + "self_attn.k_proj.weight", (uint64_t)proj},
+                                {p + "self_attn.v_proj.weight", (uint64_t)proj}, {p + "self_attn.g_proj.weight", (uint64_t)proj},
+                                {p + "self_attn.f_a_proj.weight", c.kda_fa}, {p + "self_attn.b_proj.weight", c.kda_heads}}, d, &ly.w_x_rows);
+            ly.f_b = L.f32(p + "self_attn.f_b_proj.weight", (uint64_t)proj * c.kda_fa);
+            ly.o_proj = L.f32(p + "self_attn.o_proj.weight", (uint64_t)d * proj);
+            mk_kda_desc kd;
+            memset(&kd, 0, sizeof(kd));
+            kd.heads = (int32_t)c.kda_heads; kd.dim = (int32_t)c.kda_dim; kd.kconv = (int32_t)c.kda_conv; kd.gate_lb = c.gate_lb; kd.rms_eps = c.rms_eps;
+            kd.q_conv = (const float *)L.find(p + "self_attn.q_conv1d.weight", MK_DTYPE_F32, (uint64_t)proj * c.kda_conv * 4);
+            kd.k_conv = (const float *)L.find(p + "self_attn.k_conv1d.weight", MK_DTYPE_F32, (uint64_t)proj * c.kda_conv * 4);
+            kd.v_conv = (const float *)L.find(p + "self_attn.v_conv1d.weight", MK_DTYPE_F32, (uint64_t)proj * c.kda_conv * 4);
+            kd.a_log = (const float *)L.find(p + "self_attn.A_log", MK_DTYPE_F32, (uint64_t)c.kda_dim * 4);
+            kd.dt_bias = (const float *)L.find(p + "self_attn.dt_bias", MK_DTYPE_F32, (uint64_t)proj * 4);
+            kd.o_norm = (const float *)L.find(p + "self_attn.o_norm.weight", MK_DTYPE_F32, (uint64_t)c.kda_dim * 4);
+            if (L.rc != MK_OK) return fail(L.rc, L.err);
+            const int32_t rc = mk_kda_create(ctx, &kd, &ly.kda);
+            if (rc != MK_OK) return fail(rc, "");
+        }
+        if (ly.is_moe) {
+            const std::string q = p + "block_sparse_moe.";
+            const float *gate_w = (const float *)L.find(q + "gate.weight", MK_DTYPE_F32, (uint64_t)c.n_experts * d * 4);
+            const float *gate_b = (const float *)L.find(q + "gate.e_score_correction_bias", MK_DTYPE_F32, (uint64_t)c.n_experts * 4);
+            const float *rnorm = (const float *)L.find(q + "routed_expert_norm.weight", MK_DTYPE_F32, (uint64_t)c.routed_hidden * 4);
+            ly.rd = f32_record(L.f32(q + "routed_expert_down_proj.weight", (uint64_t)c.routed_hidden * d), c.routed_hidden, d);
+            ly.ru = f32_record(L.f32(q + "routed_expert_up_proj.weight", (uint64_t)d * c.routed_hidden), d, c.routed_hidden);
+            ly.sg = f32_record(L.f32(q + "shared_experts.gate_proj.weight", (uint64_t)c.shared_inter * d), c.shared_inter, d);
+            ly.su = f32_record(L.f32(q + "shared_experts.up_proj.weight", (uint64_t)c.shared_inter * d), c.shared_inter, d);
+            ly.sd = f32_record(L.f32(q + "shared_experts.down_proj.weight", (uint64_t)d * c.shared_inter), d, c.shared_inter);
+            if (L.rc != MK_OK) return fail(L.rc, L.err);
+            const int per = (int)c.n_experts / world;
+            int32_t rc = load_experts(L, ly, (int)l, rank * per, (rank + 1) * per);
+            if (rc != MK_OK) return fail(rc, "");
+            std::vector<const mk_weight *> table((size_t)c.n_experts * 3, nullptr);
+            for (size_t i = 0; i < table.size(); ++i) table[i] = ly.expert_w[i].values ? &ly.expert_w[i] : nullptr;
+            mk_moe_desc md;
+            memset(&md, 0, sizeof(md));
+            md.n_experts = (int32_t)c.n_experts; md.top_k = (int32_t)c.top_k; md.d = (int32_t)d; md.inter = (int32_t)c.moe_inter;
+            md.activation = MK_MOE_SITU; md.gate_w = gate_w; md.gate_b = gate_b; md.experts = table.data(); md.router = MK_ROUTER_SIGMOID;
+            md.latent = (int32_t)c.routed_hidden; md.rms_eps = c.rms_eps; md.routed_down = &ly.rd; md.routed_up = &ly.ru; md.routed_norm = rnorm;
+            md.shared_f32[0] = &ly.sg; md.shared_f32[1] = &ly.sd; md.shared_f32[2] = &ly.su;
+            rc = mk_moe_create(ctx, &md, &ly.moe);
+            if (rc != MK_OK) return fail(rc, "");
+            m->weight_bytes += (int64_t)c.n_experts * d * 4;
+        } else {
+            ly.dgu = L.stacked({{p + "mlp.gate_proj.weight", c.dense_inter}, {p + "mlp.up_proj.weight", c.dense_inter}}, d, nullptr);
+            ly.dd = L.f32(p + "mlp.down_proj.weight", (uint64_t)d * c.dense_inter);
+        }
+        if (L.rc != MK_OK) return fail(L.rc, L.err);
+    }
+    // q8_0 copy of (this rank's rows of) lm_head, quantized on the GPU (Q8Head::from_f32, src/model.rs:921-925)
+    m->head_rows = c.vocab / world;
+    m->head_row0 = (int64_t)rank * m->head_rows;
+    const float *lm = (const float *)L.find("lm_head.weight", MK_DTYPE_F32, (uint64_t)c.vocab * d * 4);
+    if (L.rc != MK_OK) return fail(L.rc, L.err);
+    int32_t rc = mk_weight_q8_from_f32(ctx, lm + m->head_row0 * d, m->head_rows, d, MK_SCALE_F32, 0, &m->head);
+    if (rc != MK_OK) return fail(rc, "");
+    m->weight_bytes += mk_weight_bytes(m->head);
+    if (world > 1) {
+        rc = mk_gather_create(ctx, rank, world, c.vocab, 1, &m->gather, m->handles + 64);
+        if (rc != MK_OK) return fail(rc, "");
+        mk_moe *first = nullptr;
+        for (Layer &ly : m->layers) if (ly.moe) { first = ly.moe; break; }
+        if (first) {
+            rc = mk_moe_ep_create(ctx, first, rank, world, 1, &m->ep, m->handles);
+            if (rc != MK_OK) return fail(rc, "");
+        }
+    }
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    *out = m;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_model_free(mk_ctx *ctx, mk_model *m) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr, "NULL argument");
+    cudaSetDevice(ctx->device);
+    free_model(ctx, m);
+    return MK_OK;
+}
+extern "C" int32_t mk_model_positions(mk_ctx *ctx, const mk_model *m) {
+    if (!ctx || !m) { mk_set_error("mk_model_positions: NULL argument"); return MK_ERR_ARG; }
+    return m->positions;
+}
+extern "C" int64_t mk_model_weight_bytes(const mk_model *m) { return m ? m->weight_bytes : -1; }
+extern "C" int64_t mk_model_launches_per_token(const mk_model *m) { return m ? m->launches_per_token : -1; }
+
+extern "C" int32_t mk_model_reset(mk_ctx *ctx, mk_model *m) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr, "NULL argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    for (Layer &ly : m->layers) {
+        int32_t rc = MK_OK;
+        if (ly.kda) rc = mk_kda_reset(ctx, ly.kda);
+        if (ly.cache) rc = mk_mla_reset(ctx, ly.cache, -1);
+        if (rc != MK_OK) return rc;
+    }
+    m->positions = 0;
+    return MK_OK;
+}
+
+extern "C" int32_t mk_model_ep_handles(mk_ctx *ctx, mk_model *m, uint8_t *handles) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && handles != nullptr, "NULL argument");
+    MK_CHECK_ARG(m->world > 1 && m->gather != nullptr, "the model was opened for one GPU");
+    memcpy(handles, m->handles, 128);
+    return MK_OK;
+}
+extern "C" int32_t mk_model_ep_connect(mk_ctx *ctx, mk_model *m, const uint8_t *all) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && all != nullptr, "NULL argument");
+    MK_CHECK_ARG(m->world > 1 && m->gather != nullptr, "the model was opened for one GPU");
+    std::vector<uint8_t> a((size_t)m->world * 64), b((size_t)m->world * 64);
+    for (int r = 0; r < m->world; ++r) {
+        memcpy(&a[(size_t)r * 64], all + (size_t)r * 128, 64);
+        memcpy(&b[(size_t)r * 64], all + (size_t)r * 128 + 64, 64);
+    }
+    int32_t rc = m->ep ? mk_moe_ep_connect(ctx, m->ep, a.data()) : MK_OK;
+    if (rc != MK_OK) return rc;
+    return mk_gather_connect(ctx, m->gather, b.data());
+}
+
+namespace {
+
+// Every launch of one token, on the context's stream.  Reads m->tok, leaves m->logits and m->next.
+int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
+    const mk_model_config &c = m->cfg;
+    const int d = (int)c.d, proj = (int)(c.kda_heads * c.kda_dim), H = (int)c.mla_heads, nope = (int)c.mla_nope, rope = (int)c.mla_rope;
+    const int vd = (int)c.mla_v, qh = nope + rope, qa = (int)c.mla_qa, kva = (int)c.mla_kva, cdim = kva + rope, hv = H * vd, fa = (int)c.kda_fa;
+    const float eps = c.rms_eps;
+    cudaStream_t st = ctx->stream;
+    int32_t rc;
+#define RC(call) do { rc = (call); if (rc != MK_OK) return rc; } while (0)
+    embed_row_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->embed, m->tok, (int)c.vocab, d, m->hidden, ctx->status_dev);
+    ctx->launches++;
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        Layer &ly = m->layers[l];
+        int nb = ly.nb_before;
+        const float *normin = m->hidden;
+        if (nb > 0) {
+            RC(mk_attn_res_dev(ctx, m->hidden, m->blocks, d, nb, ly.sa_w, d, eps, m->res));
+            normin = m->res;
+        }
+        bool have_prefix = true;
+        if (ly.pushes) {
+            MK_CUDA(cudaMemcpyAsync(m->blocks + (size_t)nb * d, m->hidden, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+            ++nb;
+            have_prefix = false;
+        }
+        RC(mk_launch_rmsnorm(ctx, normin, ly.input_ln, 1, d, eps, m->x));
+        if (ly.is_mla) {
+            float *y = m->y;
+            RC(mk_launch_f32_gemv(ctx, ly.w_x, ly.w_x_rows, d, m->x, 1, y, ly.w_x_rows, 0));          // q_a, kv_a, g_proj of x
+            RC(mk_launch_rmsnorm(ctx, y, ly.q_a_ln, 1, qa, eps, m->qan));
+            RC(mk_launch_f32_gemv(ctx, ly.q_b, (int64_t)H * qh, qa, m->qan, 1, m->q, (int64_t)H * qh, 0));
+            RC(mk_launch_rmsnorm(ctx, y + qa, ly.kv_a_ln, 1, kva, eps, m->kpn));
+            RC(mk_launch_f32_gemv(ctx, ly.kv_b, (int64_t)H * (nope + vd), kva, m->kpn, 1, m->kb, (int64_t)H * (nope + vd), 0));
+            mla_assemble_kernel<<<(unsigned)mk_ceil_div((int64_t)H * (qh + vd), 256), 256, 0, st>>>(m->kb, y + qa + kva, H, nope, rope, vd, m->k_new, m->v_new);
+            ctx->launches++;
+            const float scale = powf((float)qh, -0.5f);   // (mla_qh as f32).powf(-0.5) (src/model.rs:1977)
+            RC(mk_mla_decode_step_dev(ctx, ly.cache, 0, m->k_new, m->v_new, m->q, scale, m->attn));
+            RC(mk_sigmoid_gate_dev(ctx, m->attn, y + qa + cdim, hv));
+            RC(mk_launch_f32_gemv(ctx, ly.o_proj, d, hv, m->attn, 1, m->attn_out, d, 0));
+        } else {
+            float *y = m->y;
+            RC(mk_launch_f32_gemv(ctx, ly.w_x, ly.w_x_rows, d, m->x, 1, y, ly.w_x_rows, 0));          // q, k, v, g2, f_a, beta of x
+            RC(mk_launch_f32_gemv(ctx, ly.f_b, proj, fa, y + 4 * proj, 1, m->g_low, proj, 0));
+            RC(mk_kda_step_dev(ctx, ly.kda, y, y + proj, y + 2 * proj, m->g_low, y + 4 * proj + fa, y + 3 * proj, m->o));
+            RC(mk_launch_f32_gemv(ctx, ly.o_proj, d, proj, m->o, 1, m->attn_out, d, 0));
+        }
+        const float *p2 = m->attn_out;
+        if (have_prefix) {
+            vec_add_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->hidden, m->attn_out, m->p2, d);
+            ctx->launches++;
+            p2 = m->p2;
+        }
+        RC(mk_attn_res_dev(ctx, p2, m->blocks, d, nb, ly.mlp_w, d, eps, m->res));
+        RC(mk_launch_rmsnorm(ctx, m->res, ly.post_ln, 1, d, eps, m->x));
+        if (ly.is_moe) {
+            if (m->ep) RC(mk_moe_forward_ep_dev(ctx, ly.moe, m->ep, m->x, 1, m->mlp_out, nullptr, nullptr));
+            else RC(mk_moe_forward_dev(ctx, ly.moe, m->x, 1, m->mlp_out, nullptr, nullptr));
+        } else {
+            const int di = (int)c.dense_inter;
+            RC(mk_launch_f32_gemv(ctx, ly.dgu, 2 * di, d, m->x, 1, m->au, 2 * di, 0));
+            RC(mk_launch_situ(ctx, m->au, m->au + di, di, m->act));
+            RC(mk_launch_f32_gemv(ctx, ly.dd, d, di, m->act, 1, m->mlp_out, d, 0));
+        }
+        vec_add_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(p2, m->mlp_out, m->hidden, d);
+        ctx->launches++;
+    }
+    const int nb_final = m->layers.back().nb_before + (m->layers.back().pushes ? 1 : 0);
+    RC(mk_attn_res_dev(ctx, m->hidden, m->blocks, d, nb_final, m->out_w, d, eps, m->res));
+    RC(mk_launch_rmsnorm(ctx, m->res, m->norm_f, 1, d, eps, m->x));
+    if (m->gather) {
+        const float *full = nullptr;
+        RC(mk_matvec_q8_gather_dev(ctx, m->head, m->gather, m->x, 1, m->head_row0, &full, m->next));
+        MK_CUDA(cudaMemcpyAsync(m->logits, full, (size_t)c.vocab * 4, cudaMemcpyDeviceToDevice, st));
+    } else {
+        RC(mk_matvec_q8_dev(ctx, m->head, m->x, m->logits, 1, MK_ACT_Q8, m->next));
+    }
+#undef RC
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+} // namespace
+
+extern "C" int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t *token, float *logits, int32_t *next) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr, "NULL argument");
+    if (m->positions + 1 > m->opts.max_positions) {
+        mk_set_error("mk_model_forward: the sequence already holds max_positions = %d tokens", m->opts.max_positions);
+        return MK_ERR_STATE;
+    }
+    MK_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    // the token of this step: the caller's, or the pick the previous step left on the device
+    copy_i32_kernel<<<1, 1, 0, st>>>(token ? token : m->next, m->tok);
+    ctx->launches++;
+    const bool graph_ok = m->opts.use_graph && m->world == 1 && !ctx->prof_on;
+    int32_t rc = MK_OK;
+    if (m->graph && m->graph_ws != ctx->ws) {
+        // another call on this context grew the shared workspace since the token was recorded: the recorded
+        // launches point at the old buffer, so the recording is dropped and made again
+        cudaGraphExecDestroy(m->graph);
+        m->graph = nullptr;
+    }
+    if (graph_ok && m->graph) {
+        MK_CUDA(cudaGraphLaunch(m->graph, st));
+        ctx->launches += m->launches_per_token;
+        for (Layer &ly : m->layers) if (ly.cache) mk_mla_note_replay(ly.cache, 0);
+    } else if (graph_ok && m->warm >= 1) {
+        // the first token ran eagerly (workspaces grown, attributes set); this one is recorded and then launched
+        const int64_t l0 = ctx->launches;
+        cudaGraph_t g = nullptr;
+        MK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        rc = enqueue_token(ctx, m);
+        const cudaError_t e = cudaStreamEndCapture(st, &g);
+        if (rc != MK_OK || e != cudaSuccess) {
+            if (g) cudaGraphDestroy(g);
+            if (rc == MK_OK) { mk_set_error("mk_model_forward: graph capture failed: %s", cudaGetErrorString(e)); rc = MK_ERR_CUDA; }
+            return rc;
+        }
+        m->launches_per_token = ctx->launches - l0;
+        const cudaError_t e2 = cudaGraphInstantiate(&m->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e2 != cudaSuccess) { mk_set_error("mk_model_forward: graph instantiation failed: %s", cudaGetErrorString(e2)); return MK_ERR_CUDA; }
+        m->graph_ws = ctx->ws;
+        MK_CUDA(cudaGraphLaunch(m->graph, st));
+    } else {
+        const int64_t l0 = ctx->launches;
+        rc = enqueue_token(ctx, m);
+        if (rc != MK_OK) return rc;
+        m->launches_per_token = ctx->launches - l0;
+        m->warm++;
+    }
+    m->positions++;
+    if (logits) MK_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToDevice, st));
+    if (next) { copy_i32_kernel<<<1, 1, 0, st>>>(m->next, next); ctx->launches++; }
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+extern "C" int32_t mk_model_forward(mk_ctx *ctx, mk_model *m, int32_t token, float *logits, int32_t *next) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr, "NULL argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = mk_io_reserve(ctx, 256);
+    if (rc != MK_OK) return rc;
+    int32_t *tdev = (int32_t *)ctx->io_dev;
+    MK_CUDA(cudaMemcpyAsync(tdev, &token, 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = mk_model_forward_dev(ctx, m, tdev, nullptr, nullptr);
+    if (rc != MK_OK) return rc;
+    if (logits) MK_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next) MK_CUDA(cudaMemcpyAsync(next, m->next, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+
+extern "C" int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_new, int32_t *out_tokens) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && prompt != nullptr && n_prompt >= 1 && n_new >= 0 && (n_new == 0 || out_tokens != nullptr),
+                 "bad argument");
+    MK_CHECK_ARG(m->positions + n_prompt + n_new - (n_new > 0 ? 1 : 0) <= m->opts.max_positions, "prompt + new tokens exceed max_positions");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = mk_io_reserve(ctx, mk_align_up((size_t)(n_prompt + n_new) * 4, 256));
+    if (rc != MK_OK) return rc;
+    int32_t *pdev = (int32_t *)ctx->io_dev, *odev = pdev + n_prompt;
+    MK_CUDA(cudaMemcpyAsync(pdev, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, ctx->stream));
+    // prompt tokens one by one (the engine's sequential prefill path), the pick after the last one is the first new token
+    for (int i = 0; i < n_prompt; ++i) {
+        rc = mk_model_forward_dev(ctx, m, pdev + i, nullptr, (i == n_prompt - 1 && n_new > 0) ? odev : nullptr);
+        if (rc != MK_OK) return rc;
+    }
+    for (int i = 1; i < n_new; ++i) {
+        rc = mk_model_forward_dev(ctx, m, nullptr, nullptr, odev + i);
+        if (rc != MK_OK) return rc;
+    }
+    if (n_new > 0) MK_CUDA(cudaMemcpyAsync(out_tokens, odev, (size_t)n_new * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+
+extern "C" int32_t mk_model_last_hidden(mk_ctx *ctx, mk_model *m, float *hidden) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && hidden != nullptr, "NULL argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    MK_CUDA(cudaMemcpyAsync(hidden, m->x, (size_t)m->cfg.d * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}

@@ -247,3 +247,79 @@ extern "C" int32_t mk_dequant_fp8(mk_ctx *ctx, const uint8_t *w, const uint8_t *
     MK_CUDA(cudaStreamSynchronize(ctx->stream));
     return MK_OK;
 }
+
+// ---------------------------------------------------------------- mxfp4::quantize (src/mxfp4.rs:38-138) on the GPU
+// One warp per 32-wide block, lane = element.  Every step keeps the CPU's arithmetic: f32 maximum, the exponent
+// e = ceil(log2(maxabs / 6)) clamped to [-127, 128], the three-candidate search by the f64 squared error summed in
+// element order (the naive exponent first, replaced only by a strictly smaller error), nearest level by the
+// midpoints, the sign taken from the sign bit (so -0.0 keeps code 8).
+namespace {
+__device__ __forceinline__ float q4_exp2_i(int e) {   // exp2_i (src/mxfp4.rs:10-16): exact bit patterns
+    return e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(0x00400000u);
+}
+__device__ __forceinline__ int q4_level(float q) {     // count of the midpoints 0.25 .. 5 that |q| reaches
+    const float mag = fabsf(q);
+    return (mag >= 0.25f) + (mag >= 0.75f) + (mag >= 1.25f) + (mag >= 1.75f) + (mag >= 2.5f) + (mag >= 3.5f) + (mag >= 5.0f);
+}
+__device__ __forceinline__ float q4_clamp6(float q) { return q < -6.0f ? -6.0f : (q > 6.0f ? 6.0f : q); }
+// group_sse (src/mxfp4.rs:51-69): the warp's 32 terms added in element order by every lane (same result in all)
+__device__ __forceinline__ double q4_group_sse(float v, int e) {
+    const float inv = __fdiv_rn(1.0f, q4_exp2_i(e));
+    const double s = (double)q4_exp2_i(e);
+    const float q = q4_clamp6(__fmul_rn(v, inv));
+    const double lvl = (double)fabsf(c_e2m1[q4_level(q)]);
+    const double dq = __dmul_rn((__float_as_uint(q) >> 31) ? -lvl : lvl, s);
+    const double d = __dsub_rn((double)v, dq);
+    const double term = __dmul_rn(d, d);
+    double sse = 0.0;
+#pragma unroll 8
+    for (int i = 0; i < 32; ++i) sse = __dadd_rn(sse, __shfl_sync(0xFFFFFFFFu, term, i));
+    return sse;
+}
+__global__ void __launch_bounds__(256)
+quantize_mxfp4_kernel(const float *__restrict__ w, int64_t nblocks, int search, uint8_t *__restrict__ packed, uint8_t *__restrict__ scales) {
+    const int64_t blk = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (blk >= nblocks) return;
+    const float v = w[blk * 32 + lane];
+    float maxabs = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) maxabs = fmaxf(maxabs, __shfl_xor_sync(0xFFFFFFFFu, maxabs, o));
+    int e = -127;
+    if (maxabs != 0.0f) {
+        // f32 log2 of the CPU's libm, taken as the correctly rounded value: double log2 rounded once
+        const float lg = (float)log2((double)__fdiv_rn(maxabs, 6.0f));
+        const float c = ceilf(lg);
+        e = c >= 2147483648.0f ? 2147483647 : (c <= -2147483648.0f ? (int)0x80000000 : (int)c);   // `as i32` saturates
+        if (c != c) e = 0;
+    }
+    e = e < -127 ? -127 : (e > 128 ? 128 : e);
+    if (search && maxabs != 0.0f) {   // search_mx_scale (src/mxfp4.rs:77-92)
+        int best = e;
+        double best_sse = q4_group_sse(v, e);
+        if (e - 1 >= -127) { const double s1 = q4_group_sse(v, e - 1); if (s1 < best_sse) { best_sse = s1; best = e - 1; } }
+        if (e + 1 <= 128) { const double s2 = q4_group_sse(v, e + 1); if (s2 < best_sse) { best_sse = s2; best = e + 1; } }
+        e = best;
+    }
+    int sb = e + 127;
+    sb = sb < 0 ? 0 : (sb > 255 ? 255 : sb);
+    const float inv = __fdiv_rn(1.0f, q4_exp2_i(e));
+    const float q = q4_clamp6(__fmul_rn(v, inv));
+    uint32_t idx = (uint32_t)q4_level(q) + ((__float_as_uint(q) >> 31) ? 8u : 0u);
+    const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, idx, 1);
+    if ((lane & 1) == 0) packed[blk * 16 + (lane >> 1)] = (uint8_t)(idx | (hi << 4));
+    if (lane == 0) scales[blk] = (uint8_t)sb;
+}
+} // namespace
+
+extern "C" int32_t mk_quantize_mxfp4_dev(mk_ctx *ctx, const float *w, int64_t rows, int64_t cols, int32_t search, uint8_t *packed,
+                                         uint8_t *scales) {
+    MK_CHECK_ARG(ctx != nullptr && w != nullptr && packed != nullptr && scales != nullptr, "NULL argument");
+    MK_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "rows > 0 and cols a positive multiple of 32 required");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const int64_t nblocks = rows * (cols / 32);
+    quantize_mxfp4_kernel<<<grid_for(nblocks * 32, 256), 256, 0, ctx->stream>>>(w, nblocks, search, packed, scales);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}

@@ -55,6 +55,25 @@ class MlaDesc(C.Structure):
                 ("max_positions", _i32), ("n_seqs", _i32)]
 
 
+class ModelConfig(C.Structure):
+    """mk_model_config: the engine's Config (src/config.rs:8-43)."""
+    _fields_ = ([(n, C.c_uint32) for n in ("n_layers", "d", "vocab", "n_experts", "top_k", "n_shared", "kda_heads", "kda_dim",
+                                          "kda_conv", "kda_fa")] + [("gate_lb", C.c_float)] +
+                [(n, C.c_uint32) for n in ("mla_heads", "mla_qa", "mla_kva", "mla_nope", "mla_rope", "mla_v", "routed_hidden",
+                                          "moe_inter", "shared_inter", "dense_inter", "attn_res_block", "first_k_dense")] +
+                [("rms_eps", C.c_float), ("eos_id", C.c_uint32), ("bos_id", C.c_uint32), ("has_layer_lists", C.c_uint32),
+                 ("is_deepseek", C.c_uint32)])
+
+
+class ModelOpts(C.Structure):
+    """mk_model_opts"""
+    _fields_ = [("max_positions", _i32), ("use_graph", _i32), ("rank", _i32), ("world", _i32)]
+
+
+_u32p = C.POINTER(C.c_uint32)
+_u64p = C.POINTER(C.c_uint64)
+_i32p = C.POINTER(_i32)
+
 # name -> (restype, argtypes); every symbol include/mk_cuda.h declares
 SIGNATURES = {
     "mk_init": (_i32, [_i32, C.POINTER(_vp)]),
@@ -123,6 +142,32 @@ SIGNATURES = {
     "mk_mla_attend": (_i32, [_vp, _vp, _i32, _vp, _i32, C.c_float, _vp]),
     "mk_mla_attend_batch_dev": (_i32, [_vp, _vp, _vp, C.c_float, _vp]),
     "mk_mla_export": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mk_mla_decode_step_dev": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, C.c_float, _vp]),
+    "mk_model_config_default": (None, [C.POINTER(ModelConfig)]),
+    "mk_bin_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
+    "mk_bin_close": (_i32, [_vp]),
+    "mk_bin_config": (_i32, [_vp, C.POINTER(ModelConfig)]),
+    "mk_bin_count": (_i64, [_vp]),
+    "mk_bin_find": (_i32, [_vp, C.c_char_p, _i32p, _i32p, _u32p, C.POINTER(_vp), _u64p]),
+    "mk_bin_entry": (_i32, [_vp, _i64, C.POINTER(C.c_char_p), _i32p, _i32p, _u32p, C.POINTER(_vp), _u64p]),
+    "mk_bin_writer_create": (_i32, [C.POINTER(ModelConfig), C.POINTER(_vp)]),
+    "mk_bin_writer_add": (_i32, [_vp, C.c_char_p, _i32, _i32, _u32p]),
+    "mk_bin_writer_begin": (_i32, [_vp, C.c_char_p]),
+    "mk_bin_writer_put": (_i32, [_vp, C.c_char_p, _vp, C.c_uint64]),
+    "mk_bin_writer_finish": (_i32, [_vp]),
+    "mk_quantize_mxfp4_dev": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _vp]),
+    "mk_model_open": (_i32, [_vp, _vp, C.POINTER(ModelOpts), C.POINTER(_vp)]),
+    "mk_model_free": (_i32, [_vp, _vp]),
+    "mk_model_reset": (_i32, [_vp, _vp]),
+    "mk_model_positions": (_i32, [_vp, _vp]),
+    "mk_model_weight_bytes": (_i64, [_vp]),
+    "mk_model_launches_per_token": (_i64, [_vp]),
+    "mk_model_ep_handles": (_i32, [_vp, _vp, _vp]),
+    "mk_model_ep_connect": (_i32, [_vp, _vp, _vp]),
+    "mk_model_forward_dev": (_i32, [_vp, _vp, _vp, _vp, _vp]),
+    "mk_model_forward": (_i32, [_vp, _vp, _i32, _vp, _vp]),
+    "mk_model_generate": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
+    "mk_model_last_hidden": (_i32, [_vp, _vp, _vp]),
 }
 
 

@@ -1,0 +1,146 @@
+"""GPU parity tests of the whole decode token (Model::forward, src/model.rs:2889-3031) through the C ABI against
+the oracle's restatement, on model files written by the restated builder.
+
+  greedy token ids ............ identical to the CPU's, step by step
+  logits / final hidden ....... <= 1e-3 * max|ref| (the spec's bound; the token runs the engine's default q8 paths, the
+                                gaps are exp() ulps and the summation order of the attention and expert kernels)
+  graph replay == eager ....... bit for bit (the same launches)
+  mxfp4::quantize on the GPU .. bytes equal the CPU quantizer's
+"""
+import numpy as np
+import pytest
+
+from conftest import bits
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+SKELETONS = {
+    # 3 KDA + 2 MLA layers (the last layer is always MLA), a dense layer 0 and 4 MoE layers, AttnRes blocks every 2 layers
+    "small": dict(n_layers=5, vocab=2048, n_experts=32, top_k=4, attn_res_block=2),
+    # the engine's MoE shape (896 experts, top-16) on 2 KDA + 1 MLA + 1 MLA layers, default AttnRes block
+    "moe896": dict(n_layers=4, vocab=4096),
+}
+
+
+def rel(a, ref):
+    return np.abs(a.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-12)
+
+
+@pytest.fixture(scope="module")
+def mk():
+    import microkimi_b200 as m
+    m.Context.default()
+    return m
+
+
+@pytest.fixture(scope="module", params=sorted(SKELETONS))
+def skeleton(request, tmp_path_factory):
+    path = str(tmp_path_factory.mktemp("mk") / f"{request.param}.bin")
+    O.build_bin(path, O.Config.microkimi(**SKELETONS[request.param]))
+    return path
+
+
+def test_decode_tokens_match_the_cpu_token(mk, skeleton):
+    from microkimi_b200 import model as M
+    ref = O.Model(skeleton, 32, n_threads=O.host_threads())
+    eager = M.Model(skeleton, 32, use_graph=False)
+    graph = M.Model(skeleton, 32, use_graph=True)
+    tok = 17
+    for step in range(10):
+        want, hid = ref.forward(tok, want_hidden=True)
+        got, nxt = eager.forward(tok)
+        got_g, nxt_g = graph.forward(tok)
+        assert rel(eager.last_hidden(), hid) <= 1e-3, step
+        assert rel(got, want) <= 1e-3, step
+        assert nxt == O.argmax(want), step
+        assert np.array_equal(bits(got), bits(got_g)) and nxt == nxt_g, f"graph replay differs from eager at step {step}"
+        tok = nxt
+    assert eager.positions == graph.positions == 10
+    assert graph.launches_per_token > 0
+    assert mk.Context.default().status_word() == 0
+    # a new sequence on the same objects
+    ref.reset(), eager.reset(), graph.reset()
+    want = ref.forward(99)
+    a, b = eager.forward(99)[0], graph.forward(99)[0]
+    assert rel(a, want) <= 1e-3 and np.array_equal(bits(a), bits(b))
+    for m in (eager, graph):
+        m.free()
+
+
+def test_generate_is_the_greedy_loop(mk, skeleton):
+    from microkimi_b200 import model as M
+    ref = O.Model(skeleton, 32, n_threads=O.host_threads())
+    rng = np.random.default_rng(3)
+    vocab = ref.config.vocab
+    prompt = rng.integers(0, vocab, 6).astype(np.int32)
+    want = []
+    for t in prompt:
+        lg = ref.forward(int(t))
+    for _ in range(8):
+        want.append(O.argmax(lg))
+        lg = ref.forward(want[-1])
+    m = M.Model(skeleton, 32, use_graph=True)
+    got = m.generate(prompt, 8)
+    assert got.tolist() == want
+    assert m.positions == 6 + 8 - 1
+    # the cache capacity is a status, not a fault
+    with pytest.raises(mk.lib.MkError) as e:
+        m.generate(prompt, 40)
+    assert e.value.code == -1
+    m.reset()
+    small = M.Model(skeleton, 2)
+    small.forward(1), small.forward(2)
+    with pytest.raises(mk.lib.MkError) as e:
+        small.forward(3)
+    assert e.value.code == -4
+    # a token id outside the vocabulary is reported through the status word
+    m.forward(vocab + 5, want_logits=False)
+    assert mk.Context.default().status_word() == -1
+    m.free(), small.free()
+
+
+def test_synthetic_builder_file_runs_on_both_sides(mk, tmp_path):
+    """The GPU-side generator of benchmark models writes a file the CPU restatement reads and agrees on."""
+    from microkimi_b200 import model as M
+    path = str(tmp_path / "synth.bin")
+    cfg = M.default_config(n_layers=4, vocab=2048, n_experts=64, top_k=8)
+    M.build_synthetic_bin(path, cfg, seed=5)
+    b = M.BinFile(path)
+    assert [t[0] for t in M.model_tensors(cfg)] == b.names()
+    p, s = b.get("layers.2.block_sparse_moe.experts.9.w1")
+    assert p.shape == (cfg.moe_inter, cfg.routed_hidden // 2) and 100 < int(s.max()) < 130
+    b.close()
+    ref = O.Model(path, 8, n_threads=O.host_threads())
+    m = M.Model(path, 8)
+    tok = 3
+    for _ in range(4):
+        want = ref.forward(tok)
+        got, nxt = m.forward(tok)
+        assert rel(got, want) <= 1e-3 and nxt == O.argmax(want)
+        tok = nxt
+    m.free()
+
+
+@pytest.mark.parametrize("search", [True, False])
+def test_gpu_mxfp4_quantizer_bytes_equal_the_cpu_quantizer(mk, search):
+    import torch
+    from microkimi_b200 import model as M
+    rng = np.random.default_rng(8)
+    w = (rng.standard_normal((96, 1024)) * 0.02).astype(np.float32)
+    w[0, :32] = 0.0                                           # all-zero block -> scale byte 0
+    w[1, :32] = -0.0
+    w[2, :64] = np.float32(6.0) * np.exp2(rng.integers(-20, 20, 64)).astype(np.float32)      # maxabs / 6 an exact power of two
+    w[3, :32] = np.nextafter(np.float32(6.0 * 2.0 ** -5), np.float32(1.0))                   # ... and one ulp above it
+    w[4, :32] = np.nextafter(np.float32(6.0 * 2.0 ** -5), np.float32(0.0))                   # ... and one ulp below
+    w[5, :32] = rng.standard_normal(32).astype(np.float32) * np.float32(1e-38)              # subnormal range
+    w[6, :32] = rng.standard_normal(32).astype(np.float32) * np.float32(1e30)
+    w[7, 5] = np.float32(3.0e38)
+    w[8, :64] = np.repeat(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0], np.float32), 8) * np.float32(2.0 ** -6)  # level midpoints
+    w[9] = rng.standard_normal(1024).astype(np.float32)
+    big = np.concatenate([w, (rng.standard_normal((2048, 1024)) * 0.02).astype(np.float32)])
+    p_ref, s_ref = O.mxfp4_quantize(big, search=search)
+    p, s = M.quantize_mxfp4(torch.from_numpy(big).cuda(), search=search)
+    torch.cuda.synchronize()
+    assert np.array_equal(s.cpu().numpy(), s_ref), "scale bytes"
+    assert np.array_equal(p.cpu().numpy(), p_ref), "packed codes"

@@ -1,0 +1,128 @@
+"""CPU checks around the whole-token path: the weight container (reader and writer of the product library against
+the oracle's own restatement of src/weights.rs), the restated builder, and the oracle's Model::forward."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+SMALL = dict(n_layers=5, vocab=2048, n_experts=32, top_k=4, attn_res_block=2)
+
+
+@pytest.fixture(scope="module")
+def small_bin(tmp_path_factory):
+    path = str(tmp_path_factory.mktemp("mk") / "small.bin")
+    O.build_bin(path, O.Config.microkimi(**SMALL))
+    return path
+
+
+def test_layer_type_rules():
+    c = O.Config.microkimi()
+    mla = [l for l in range(c.n_layers) if c.is_mla(l)]
+    assert len(mla) == 24 and mla[0] == 3 and mla[-1] == 92 and 91 in mla      # src/config.rs:127-132: l % 4 == 3 or the last layer
+    assert [l for l in range(c.n_layers) if not c.is_moe(l)] == [0]            # first_k_dense = 1
+
+
+def test_product_reader_agrees_with_the_restated_container(small_bin):
+    from microkimi_b200 import model as M
+    ob, pb = O.BinFile(small_bin), M.BinFile(small_bin)
+    assert len(ob) == len(pb) > 100
+    want_cfg = ob.config.as_dict()
+    got_cfg = M.config_dict(pb.config)
+    for k, v in want_cfg.items():
+        assert got_cfg[k] == pytest.approx(v), k
+    assert got_cfg["has_layer_lists"] == 0 and got_cfg["is_deepseek"] == 0
+    for i in list(range(0, len(ob), 37)) + [len(ob) - 1]:
+        name, dt, dims, off, size = ob.entry(i)
+        pname, pdt, pshape, raw = pb.entry(i)
+        assert (pname, pdt, raw.size) == (name, dt, size)
+        assert tuple(d for d in dims if d) == pshape
+        a = ob.get(name)
+        b = pb.get(name)
+        if dt == 0:
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        else:
+            assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    # the tensor list of the product side is the builder's registration order
+    assert [t[0] for t in M.model_tensors(pb.config)] == pb.names()
+    pb.close()
+    ob.close()
+
+
+def test_product_writer_lays_the_file_out_like_the_engine(small_bin, tmp_path):
+    """BinWriter::layout (src/weights.rs:107-131): 64-byte alignment, 4096 for routed-expert blobs; the file the product
+    writer makes from the same tensors equals the restated builder's file byte for byte."""
+    from microkimi_b200 import model as M
+    src = M.BinFile(small_bin)
+    out = str(tmp_path / "copy.bin")
+    w = M.BinWriter(src.config)
+    entries = [src.entry(i) for i in range(len(src))]
+    names = {0: "f32", 1: "mxfp4"}
+    for name, dt, shape, raw in entries:
+        w.add(name, names[dt], shape)
+    w.begin(out)
+    for name, dt, shape, raw in entries:
+        w.put(name, raw)
+    w.finish()
+    a, b = np.fromfile(small_bin, dtype=np.uint8), np.fromfile(out, dtype=np.uint8)
+    assert a.size == b.size and np.array_equal(a, b)
+    with pytest.raises(M._l.MkError):
+        M.BinWriter(src.config).put("x", np.zeros(4, np.float32))     # put before begin
+    src.close()
+
+
+def test_truncated_and_foreign_files_are_statuses(small_bin, tmp_path):
+    from microkimi_b200 import model as M
+    raw = np.fromfile(small_bin, dtype=np.uint8)
+    cut = str(tmp_path / "cut.bin")
+    raw[:raw.size // 2].tofile(cut)
+    with pytest.raises(M._l.MkError) as e:
+        M.BinFile(cut)
+    assert e.value.code == -1 and "truncated" in str(e.value)
+    junk = str(tmp_path / "junk.bin")
+    np.arange(4096, dtype=np.uint8).tofile(junk)
+    with pytest.raises(M._l.MkError):
+        M.BinFile(junk)
+    with pytest.raises(M._l.MkError):
+        M.BinFile(str(tmp_path / "absent.bin"))
+
+
+def test_builder_values(small_bin):
+    """The fallback branch of the builder (src/build.rs:444-571): norm weights 1, router bias 0, A_log in ln([1, 16)),
+    projections ~ N(0, 0.02) from the name-seeded generator, experts = mxfp4::quantize of name-seeded values."""
+    b = O.BinFile(small_bin)
+    c = b.config
+    assert np.all(b.get("layers.1.input_layernorm.weight") == 1.0) and np.all(b.get("layers.2.block_sparse_moe.gate.e_score_correction_bias") == 0.0)
+    al = b.get("layers.0.self_attn.A_log")
+    assert al.min() >= 0.0 and al.max() < np.log(16.0)
+    q = b.get("layers.0.self_attn.q_proj.weight")
+    assert np.array_equal(q.ravel(), O.fill_gauss("layers.0.q_proj", 0.02, q.size))
+    assert abs(float(q.std()) - 0.02) < 1e-3
+    name = "layers.3.block_sparse_moe.experts.7.w2"
+    p, s = b.get(name)
+    vals = O.fill_gauss(name, 0.02, c.routed_hidden * c.moe_inter).reshape(c.routed_hidden, c.moe_inter)
+    p2, s2 = O.mxfp4_quantize(vals)
+    assert np.array_equal(p, p2) and np.array_equal(s, s2)
+
+
+def test_oracle_token_is_deterministic_and_resets(small_bin):
+    m = O.Model(small_bin, 16)
+    toks, first = [5], None
+    for i in range(6):
+        lg, h = m.forward(toks[-1], want_hidden=True)
+        assert np.isfinite(lg).all() and lg.shape == (SMALL["vocab"],)
+        if first is None:
+            first = lg.copy()
+        toks.append(O.argmax(lg))
+    m.reset()
+    assert np.array_equal(m.forward(5).view(np.uint32), first.view(np.uint32))
+    # threads do not change a bit (rows are split, never a sum)
+    m2 = O.Model(small_bin, 16, n_threads=4)
+    assert np.array_equal(m2.forward(5).view(np.uint32), first.view(np.uint32))
+    with pytest.raises(ValueError):
+        m2.forward(SMALL["vocab"])            # token id outside the vocabulary
+    m3 = O.Model(small_bin, 2)
+    m3.forward(1), m3.forward(2)
+    with pytest.raises(ValueError):
+        m3.forward(3)                         # the MLA caches are full
