@@ -94,6 +94,8 @@ int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
  *                where the default keeps each column in registers (fully unrolled); same bits.
  *   "mla_no_t5": 1 = absorbed-layout attention on the mma.sync kernel instead of the
  *                tcgen05 (tensor-memory) kernel.
+ *   "mla_strict": 1 = per-head-layout attention on a one-warp-per-head kernel that forms every sum in the CPU's
+ *                order (64-position tiles, src/model.rs:1804-1908): for parity runs, not for speed.
  *   "mla_no_tc": 1 = run attention on the generic one-warp-per-head CUDA-core kernel
  *                instead of the specialised ones (tensor-core kernel of the absorbed
  *                layout, 8-heads-per-CTA kernel of the per-head layout at vd = 128). */
@@ -303,6 +305,9 @@ typedef struct {
     const mk_weight *routed_up;      /* f32 [d, latent] */
     const float *routed_norm;        /* HOST f32 [latent] */
     const mk_weight *shared_f32[3];  /* f32 shared expert: gate [si, d], down [d, si], up [si, d]; all NULL = none */
+    int32_t act_mode;                /* MK_ACT_Q8 (0), or MK_ACT_Q8 | MK_ACT_STRICT: the expert matvecs add their block terms in the
+                                        CPU's order (src/mxfp4.rs:409-418), so no q8 rounding of an activation can differ from the
+                                        CPU's; slower on wide experts (no K split) */
 } mk_moe_desc;
 int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out);
 int32_t mk_moe_free(mk_ctx *ctx, mk_moe *moe);
@@ -451,6 +456,9 @@ typedef struct mk_model mk_model;
 typedef struct {
     int32_t max_positions;   /* tokens a sequence may hold (prompt + generated): capacity of every MLA cache */
     int32_t use_graph;       /* 1: replay the token as a CUDA graph from the second call on */
+    int32_t strict;          /* 1: MoE experts and lm_head in MK_ACT_STRICT order (results closest to the CPU token) */
+    int32_t keep_layer_hidden; /* 1: keep per-layer taps of the last token for mk_model_layer_hidden (the engine's
+                                --dump-hidden / parity dumps, src/model.rs:2749-2823) */
     int32_t rank, world;     /* expert parallel + vocabulary-sharded lm_head over `world` GPUs (0 or 1: one GPU):
                                 this rank keeps routed experts [rank E/world, (rank+1) E/world) of every MoE
                                 layer and the same share of the lm_head rows; the rest of the model is replicated */
@@ -474,6 +482,9 @@ int32_t mk_model_forward(mk_ctx *ctx, mk_model *m, int32_t token, float *logits,
 /* The greedy loop of run_turn (src/model.rs:3586-3593): n_prompt prompt tokens one by one, then n_new picks, each
  * fed back as the next token on the device; out_tokens HOST int32 [n_new]; one synchronization at the end. */
 int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_new, int32_t *out_tokens);
+/* Per-layer taps of the last token, HOST f32 [n_layers][4][d] (needs opts.keep_layer_hidden): the attention block's
+ * output, the residual stream after it, the FFN's output, the residual stream after the layer. */
+int32_t mk_model_layer_hidden(mk_ctx *ctx, mk_model *m, float *out);
 /* The final normed hidden state of the last token (the input of the lm_head), HOST f32 [d]: for parity checks. */
 int32_t mk_model_last_hidden(mk_ctx *ctx, mk_model *m, float *hidden);
 

@@ -133,6 +133,10 @@ extern "C" int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value) {
         ctx->mla_no_t5 = value != 0;
         return MK_OK;
     }
+    if (strcmp(name, "mla_strict") == 0) {
+        ctx->mla_strict = value != 0;
+        return MK_OK;
+    }
     if (strcmp(name, "mla_no_tc") == 0) {
         ctx->mla_no_tc = value != 0;
         return MK_OK;

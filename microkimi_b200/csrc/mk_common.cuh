@@ -91,6 +91,7 @@ struct mk_ctx {
     int mla_max_split;      // > 0: upper bound on the KV splits of an attention call (study / test knob)
     int moe_no_fuse;        // 1 = separate router / top-k / plan / quantize launches also for small batches (study knob)
     int mla_no_tc;
+    int mla_strict;         // 1 = per-head attention by the one-warp-per-head kernel that keeps the CPU's summation order (parity mode)
     int mla_no_t5;          // 1 = absorbed MLA on the mma.sync kernel instead of the tcgen05 one (study knob)
     int kda_smem;           // 1 = KDA step with S staged in shared memory also for dim 64 / 128, where the register form is the default (study knob)
     // optional per-category event timing (mk_prof_*)

@@ -170,6 +170,106 @@ __global__ void mla_export_kernel(const MlaDev c, int seq, int n, int8_t *kq, fl
     }
 }
 
+// ------------------------------------------------------------------ attention in the CPU's own order (parity mode)
+// One warp per (sequence, head), per-head layout only.  Every sum is formed exactly as mla_attn_flash_q8_mqa forms it
+// (src/model.rs:1804-1908): 64-position tiles; per position the rope dot in dot()'s 8-accumulator order
+// (src/model.rs:63-82), the block terms (qs * ks) * idot added in ascending block order, s = rope + 1.0 * acc, then
+// * scale; tile maximum, corr = exp(m - m_new), p_i = exp(s_i - m_new) with the tile's l summed in ascending position
+// order; o *= corr, then o[d] += p_i * (vq * vs) position by position; finally o / l.  Separate multiplies and adds
+// throughout, exp taken in double and rounded once.  Not a fast kernel: it exists so that a whole decode token can be
+// compared with the CPU token without the attention's summation order (and, downstream of it, q8 roundings) differing.
+#define MLA_STRICT_TILE 64
+__global__ void __launch_bounds__(32)
+mla_attend_strict_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__restrict__ qs, int64_t ldq, int64_t q_nbp,
+                         const float *__restrict__ q_f32, const int *__restrict__ npos_arr, int npos_fixed, int seq0, float scale,
+                         float *__restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_strict[];
+    float *q_rope = (float *)smem_strict;                 // [rope]
+    float *sc_s = q_rope + c.rope;                        // [64] scores, then p
+    const int lane = threadIdx.x, h = blockIdx.x, bi = blockIdx.y, seq = seq0 + bi;
+    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int hd = c.nope + c.rope;
+    const int64_t qrow = (int64_t)bi * c.H + h;
+    for (int r = lane; r < c.rope; r += 32) q_rope[r] = q_f32[qrow * hd + c.nope + r];
+    __syncwarp();
+    const int8_t *qh = qq + qrow * ldq;
+    const float *qsh = qs + qrow * q_nbp;
+    float m = -INFINITY, l = 0.0f;
+    float o[16];
+    const int ncol = c.vd / 32;   // columns lane, lane + 32, ... of the head's output
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = 0.0f;
+    for (int t0 = 0; t0 < n; t0 += MLA_STRICT_TILE) {
+        const int tn = min(MLA_STRICT_TILE, n - t0);
+        // scores: lane takes positions lane and lane + 32 of the tile
+        for (int i = lane; i < tn; i += 32) {
+            const int j = t0 + i, tile = j >> 5, p = j & 31;
+            const int64_t th = ((int64_t)seq * c.T + tile) * c.kvh + h;
+            float acc8[8];
+#pragma unroll
+            for (int a = 0; a < 8; ++a) acc8[a] = 0.0f;
+            const float *kr = c.krt + (((int64_t)seq * c.T + tile) * c.RC) * 128 + p * 4;
+            int r = 0;
+            for (; r + 8 <= c.rope; r += 8)
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    const int rr = r + a;
+                    acc8[a] = __fadd_rn(acc8[a], __fmul_rn(q_rope[rr], kr[(rr >> 2) * 128 + (rr & 3)]));
+                }
+            float sr = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc8[0], acc8[1]), __fadd_rn(acc8[2], acc8[3])), __fadd_rn(acc8[4], acc8[5])),
+                                 __fadd_rn(acc8[6], acc8[7]));
+            for (; r < c.rope; ++r) sr = __fadd_rn(sr, __fmul_rn(q_rope[r], kr[(r >> 2) * 128 + (r & 3)]));
+            const int8_t *kq = c.kq_tile(th);
+            const float *ks = c.ks_tile(th);
+            float acc = 0.0f;
+            for (int g = 0; g < c.nb; ++g) {
+                int d = 0;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const uint4 kv = *(const uint4 *)(kq + (((g * 2 + half) * 32 + p) * 16));
+                    const uint4 qv = *(const uint4 *)(qh + g * 32 + half * 16);
+                    d = dp4a_s8(kv.x, qv.x, d); d = dp4a_s8(kv.y, qv.y, d); d = dp4a_s8(kv.z, qv.z, d); d = dp4a_s8(kv.w, qv.w, d);
+                }
+                acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(qsh[g], ks[g * 32 + p]), (float)d));
+            }
+            sc_s[i] = __fmul_rn(__fadd_rn(sr, __fmul_rn(1.0f, acc)), scale);
+        }
+        __syncwarp();
+        // tile softmax step: every lane walks the tile in order, so all lanes hold the same m, corr and l
+        float tm = -INFINITY;
+        for (int i = 0; i < tn; ++i) tm = fmaxf(tm, sc_s[i]);
+        const float m_new = fmaxf(m, tm);
+        const float corr = (float)exp((double)__fsub_rn(m, m_new));
+        float tile_l = 0.0f;
+        for (int i = 0; i < tn; ++i) tile_l = __fadd_rn(tile_l, (float)exp((double)__fsub_rn(sc_s[i], m_new)));
+        __syncwarp();
+        for (int i = lane; i < tn; i += 32) sc_s[i] = (float)exp((double)__fsub_rn(sc_s[i], m_new));
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) if (k < ncol) o[k] = __fmul_rn(o[k], corr);
+        l = __fadd_rn(__fmul_rn(l, corr), tile_l);
+        m = m_new;
+        for (int i = 0; i < tn; ++i) {
+            const int j = t0 + i;
+            const float pw = sc_s[i];
+            const int8_t *vq = c.v_row(seq, j, h);
+            const float *vs = c.vs_row(seq, j, h);
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                if (k < ncol) {
+                    const int dcol = k * 32 + lane;
+                    const int raw = c.recs ? (int)(uint8_t)vq[dcol] - 128 : (int)vq[dcol];   // records keep V biased by +128
+                    const float v = __fmul_rn((float)raw, vs[k]);
+                    o[k] = __fadd_rn(o[k], __fmul_rn(pw, v));
+                }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+        if (k < ncol) out[qrow * c.vd + k * 32 + lane] = __fdiv_rn(o[k], l);
+}
+
 } // namespace
 
 namespace {
@@ -775,6 +875,14 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     int32_t rc = mk_launch_quantize_act(ctx, q, nq * m->H, m->nope, qdim, m->q_nbp, 0, m->qq, m->qs);
     if (rc != MK_OK) return rc;
     mk_prof_scope prof(ctx, MK_PROF_MLA);
+    if (ctx->mla_strict && m->layout == MK_MLA_PER_HEAD && m->vd <= 512) {
+        const MlaDev cs = mla_dev(m);
+        mla_attend_strict_kernel<<<dim3((unsigned)m->H, (unsigned)nq), 32, (size_t)(m->rope + MLA_STRICT_TILE) * 4 + 16, ctx->stream>>>(
+            cs, m->qq, m->qs, m->q_nbp * 32, m->q_nbp, q, npos_fixed > 0 ? nullptr : m->npos_dev, npos_fixed, seq0, scale, out);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+        return MK_OK;
+    }
     if (m->layout == MK_MLA_ABSORBED && m->H == mla_t5::H && m->nope == mla_t5::LAT && m->vd == mla_t5::VD && !ctx->mla_no_tc &&
         !ctx->mla_no_t5) {
         // tcgen05 kernel: one CTA per (sequence, KV split), 128 positions per tile, accumulators in tensor memory

@@ -121,6 +121,7 @@ struct mk_model {
     float *qan = nullptr, *q = nullptr, *kpn = nullptr, *kb = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr; // MLA
     float *au = nullptr, *act = nullptr;                                                    // dense
     float *logits = nullptr;
+    float *layer_hidden = nullptr;   // opts.keep_layer_hidden: [n_layers][4][d] taps of the last token (see mk_model_layer_hidden)
     int32_t *tok = nullptr, *next = nullptr;
     int positions = 0;
     int64_t launches_per_token = 0;
@@ -356,6 +357,7 @@ extern "C" int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_
     m->k_new = L.zeros(qb); m->v_new = L.zeros(hv); m->attn = L.zeros(hv);
     m->au = L.zeros((size_t)2 * c.dense_inter); m->act = L.zeros(c.dense_inter);
     m->logits = L.zeros(c.vocab);
+    if (opts->keep_layer_hidden) m->layer_hidden = L.zeros((size_t)c.n_layers * 4 * d);
     m->tok = (int32_t *)L.zeros(1); m->next = (int32_t *)L.zeros(1);
     if (L.rc != MK_OK) return fail(L.rc, L.err);
 
@@ -426,6 +428,7 @@ extern "C" int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_
             md.activation = MK_MOE_SITU; md.gate_w = gate_w; md.gate_b = gate_b; md.experts = table.data(); md.router = MK_ROUTER_SIGMOID;
             md.latent = (int32_t)c.routed_hidden; md.rms_eps = c.rms_eps; md.routed_down = &ly.rd; md.routed_up = &ly.ru; md.routed_norm = rnorm;
             md.shared_f32[0] = &ly.sg; md.shared_f32[1] = &ly.sd; md.shared_f32[2] = &ly.su;
+            md.act_mode = MK_ACT_Q8 | (opts->strict ? MK_ACT_STRICT : 0);
             rc = mk_moe_create(ctx, &md, &ly.moe);
             if (rc != MK_OK) return fail(rc, "");
             m->weight_bytes += (int64_t)c.n_experts * d * 4;
@@ -541,7 +544,11 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
             mla_assemble_kernel<<<(unsigned)mk_ceil_div((int64_t)H * (qh + vd), 256), 256, 0, st>>>(m->kb, y + qa + kva, H, nope, rope, vd, m->k_new, m->v_new);
             ctx->launches++;
             const float scale = powf((float)qh, -0.5f);   // (mla_qh as f32).powf(-0.5) (src/model.rs:1977)
-            RC(mk_mla_decode_step_dev(ctx, ly.cache, 0, m->k_new, m->v_new, m->q, scale, m->attn));
+            const int strict_was = ctx->mla_strict;
+            if (m->opts.strict) ctx->mla_strict = 1;      // the attention sums in the CPU's order as well
+            rc = mk_mla_decode_step_dev(ctx, ly.cache, 0, m->k_new, m->v_new, m->q, scale, m->attn);
+            ctx->mla_strict = strict_was;
+            if (rc != MK_OK) return rc;
             RC(mk_sigmoid_gate_dev(ctx, m->attn, y + qa + cdim, hv));
             RC(mk_launch_f32_gemv(ctx, ly.o_proj, d, hv, m->attn, 1, m->attn_out, d, 0));
         } else {
@@ -570,6 +577,13 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         }
         vec_add_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(p2, m->mlp_out, m->hidden, d);
         ctx->launches++;
+        if (m->layer_hidden) {
+            float *lo = m->layer_hidden + (size_t)l * 4 * d;
+            MK_CUDA(cudaMemcpyAsync(lo, m->attn_out, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+            MK_CUDA(cudaMemcpyAsync(lo + d, p2, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+            MK_CUDA(cudaMemcpyAsync(lo + 2 * d, m->mlp_out, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+            MK_CUDA(cudaMemcpyAsync(lo + 3 * d, m->hidden, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+        }
     }
     const int nb_final = m->layers.back().nb_before + (m->layers.back().pushes ? 1 : 0);
     RC(mk_attn_res_dev(ctx, m->hidden, m->blocks, d, nb_final, m->out_w, d, eps, m->res));
@@ -579,7 +593,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         RC(mk_matvec_q8_gather_dev(ctx, m->head, m->gather, m->x, 1, m->head_row0, &full, m->next));
         MK_CUDA(cudaMemcpyAsync(m->logits, full, (size_t)c.vocab * 4, cudaMemcpyDeviceToDevice, st));
     } else {
-        RC(mk_matvec_q8_dev(ctx, m->head, m->x, m->logits, 1, MK_ACT_Q8, m->next));
+        RC(mk_matvec_q8_dev(ctx, m->head, m->x, m->logits, 1, MK_ACT_Q8 | (m->opts.strict ? MK_ACT_STRICT : 0), m->next));
     }
 #undef RC
     MK_CUDA(cudaGetLastError());
@@ -677,6 +691,15 @@ extern "C" int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *pr
         if (rc != MK_OK) return rc;
     }
     if (n_new > 0) MK_CUDA(cudaMemcpyAsync(out_tokens, odev, (size_t)n_new * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+
+extern "C" int32_t mk_model_layer_hidden(mk_ctx *ctx, mk_model *m, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && out != nullptr, "NULL argument");
+    MK_CHECK_ARG(m->layer_hidden != nullptr, "the model was opened without keep_layer_hidden");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    MK_CUDA(cudaMemcpyAsync(out, m->layer_hidden, (size_t)m->cfg.n_layers * 4 * m->cfg.d * 4, cudaMemcpyDeviceToHost, ctx->stream));
     MK_CUDA(cudaStreamSynchronize(ctx->stream));
     return MK_OK;
 }

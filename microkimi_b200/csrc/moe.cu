@@ -23,6 +23,7 @@ struct mk_moe {
     float route_scale;
     float limit;
     bool has_router, has_shared;
+    bool strict;                   // MK_ACT_STRICT: expert sums in the CPU's order (one accumulator, ascending blocks, no K split)
     float *gate_w, *gate_b;        // device
     // K3 latent MoE (src/model.rs:2202-2380); the f32 matrices belong to the caller's handles
     int latent;                    // routed_hidden, 0 = none
@@ -415,7 +416,7 @@ struct MoeArgs {
 // SPREAD: items of <= 2 columns (or, without BATCHED, any item by repeated passes) take the
 // spread schedule, 2 columns per pass.  BATCHED: items of more than 2 columns take the
 // batched schedule.  Both give the same bits for a column.
-template <int WF, bool SPREAD, bool BATCHED>
+template <int WF, bool SPREAD, bool BATCHED, bool ORDERED = false>
 __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc, int64_t ngroups, int ks, int KS, int lane,
                                               int n, const int8_t *const *xrow /* [n] */, const float *const *xsrow /* [n] */,
                                               const Consts &k, float (*part)[8]) {
@@ -440,7 +441,7 @@ __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc,
     } else if constexpr (BATCHED) {
         float acc[4];
         const int ca = 2 * t, cb = 2 * t + 1;
-        warp_tile_batched<WF, false, false>(tile, sc, ngroups, ks, KS, lane, g < n ? xrow[g] : nullptr, ca < n ? xsrow[ca] : nullptr,
+        warp_tile_batched<WF, false, ORDERED>(tile, sc, ngroups, ks, KS, lane, g < n ? xrow[g] : nullptr, ca < n ? xsrow[ca] : nullptr,
                                      cb < n ? xsrow[cb] : nullptr, k, acc);
         part[g][ca] = acc[0]; part[g][cb] = acc[1];
         part[g + 8][ca] = acc[2]; part[g + 8][cb] = acc[3];
@@ -461,7 +462,10 @@ __device__ __forceinline__ void warp_tile_any(const uint4 *tile, const void *sc,
 // (calls of a few tokens, where most items are small and the shared expert's big items
 // overlap them).  Large calls launch MOE_BIG_ITEMS (batched schedule with all the registers
 // it wants, 2 CTAs per SM) and MOE_SMALL_ITEMS (items of <= 2 pairs) one after the other.
-enum { MOE_ALL_SPREAD = 0, MOE_SMALL_ITEMS = 1, MOE_BIG_ITEMS = 2, MOE_MIXED = 3 };
+// MOE_STRICT: every item by the batched schedule with ONE accumulator per output, the block terms added in ascending
+// order with a separate multiply and add, and no K split (the other K-slice warps contribute an exact zero): the bits of
+// the CPU's matvec_packed_q8 (src/mxfp4.rs:409-418), so the q8 rounding of the activations cannot flip.
+enum { MOE_ALL_SPREAD = 0, MOE_SMALL_ITEMS = 1, MOE_BIG_ITEMS = 2, MOE_MIXED = 3, MOE_STRICT = 4 };
 #ifndef MK_MOE_BIG_CTAS
 #define MK_MOE_BIG_CTAS 2
 #endif
@@ -469,8 +473,9 @@ enum { MOE_ALL_SPREAD = 0, MOE_SMALL_ITEMS = 1, MOE_BIG_ITEMS = 2, MOE_MIXED = 3
 #define MK_MOE_MIXED_MAX 32   // calls of up to this many token rows use MOE_MIXED
 #endif
 template <int MODE>
-__global__ void __launch_bounds__(MK_G1_KS * 128, MODE == MOE_BIG_ITEMS ? MK_MOE_BIG_CTAS : 8 / MK_G1_KS) moe_gate_up_kernel(const MoeArgs a) {
-    constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED, SPREAD = MODE != MOE_BIG_ITEMS;
+__global__ void __launch_bounds__(MK_G1_KS * 128, (MODE == MOE_BIG_ITEMS || MODE == MOE_STRICT) ? MK_MOE_BIG_CTAS : 8 / MK_G1_KS) moe_gate_up_kernel(const MoeArgs a) {
+    constexpr bool STRICT = MODE == MOE_STRICT;
+    constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED || STRICT, SPREAD = MODE != MOE_BIG_ITEMS && !STRICT;
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
@@ -496,8 +501,12 @@ __global__ void __launch_bounds__(MK_G1_KS * 128, MODE == MOE_BIG_ITEMS ? MK_MOE
         const int mat = (job >> 1) ? 2 : 0, half = job & 1;
         const int64_t rt = (int64_t)blockIdx.x * 2 + half;
         const void *wv = a.wv[e * 3 + mat], *ws = a.wsc[e * 3 + mat];
-        warp_tile_any<W_MXFP4, SPREAD, BATCHED>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, MK_G1_KS,
-                               lane, n, xrow, xsrow, a.k, part[warp]);
+        if (!STRICT)
+            warp_tile_any<W_MXFP4, SPREAD, BATCHED>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, ks, MK_G1_KS,
+                                   lane, n, xrow, xsrow, a.k, part[warp]);
+        else if (ks == 0)   // the whole K range in one warp, in order; the slices ks > 0 are not read below
+            warp_tile_any<W_MXFP4, false, true, true>(tile_values<W_MXFP4>(wv, rt, a.nbp_d), tile_scales<W_MXFP4>(ws, rt, a.nbp_d), a.nbp_d >> 2, 0, 1,
+                                   lane, n, xrow, xsrow, a.k, part[warp]);
     }
     __syncthreads();
     const int c = warp; // column
@@ -505,8 +514,10 @@ __global__ void __launch_bounds__(MK_G1_KS * 128, MODE == MOE_BIG_ITEMS ? MK_MOE
         const int half = lane >> 4, r16 = lane & 15;
         const int jg = (0 + half) * MK_G1_KS, ju = (2 + half) * MK_G1_KS;
         float gate = part[jg][r16][c], up = part[ju][r16][c];
+        if (!STRICT) {
 #pragma unroll
-        for (int q = 1; q < MK_G1_KS; ++q) { gate += part[jg + q][r16][c]; up += part[ju + q][r16][c]; }
+            for (int q = 1; q < MK_G1_KS; ++q) { gate += part[jg + q][r16][c]; up += part[ju + q][r16][c]; }
+        }
         float act;
         if (a.activation == MK_MOE_SITU) {
             act = mk_situ(gate, up); // the routing weight is applied after w2 (src/model.rs:2346-2351)
@@ -532,8 +543,9 @@ __global__ void __launch_bounds__(MK_G1_KS * 128, MODE == MOE_BIG_ITEMS ? MK_MOE
 // ------------------------------------------------------------------ down projection
 // grid = (ceil(d/32), max_items).  CTA: 2 row tiles of w2 x 4 K slices.
 template <int MODE>
-__global__ void __launch_bounds__(256, MODE == MOE_BIG_ITEMS ? MK_MOE_BIG_CTAS : 4) moe_down_kernel(const MoeArgs a) {
-    constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED, SPREAD = MODE != MOE_BIG_ITEMS;
+__global__ void __launch_bounds__(256, (MODE == MOE_BIG_ITEMS || MODE == MOE_STRICT) ? MK_MOE_BIG_CTAS : 4) moe_down_kernel(const MoeArgs a) {
+    constexpr bool STRICT = MODE == MOE_STRICT;
+    constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED || STRICT, SPREAD = MODE != MOE_BIG_ITEMS && !STRICT;
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
@@ -557,15 +569,20 @@ __global__ void __launch_bounds__(256, MODE == MOE_BIG_ITEMS ? MK_MOE_BIG_CTAS :
     const int64_t rt = (int64_t)blockIdx.x * 2 + rt_local;
     if (rt < nrt) {
         const void *wv = a.wv[e * 3 + 1], *ws = a.wsc[e * 3 + 1];
-        warp_tile_any<W_MXFP4, SPREAD, BATCHED>(tile_values<W_MXFP4>(wv, rt, a.nbp_i), tile_scales<W_MXFP4>(ws, rt, a.nbp_i), a.nbp_i >> 2, ks, 4,
-                               lane, n, xrow, xsrow, a.k, part[warp]);
+        if (!STRICT)
+            warp_tile_any<W_MXFP4, SPREAD, BATCHED>(tile_values<W_MXFP4>(wv, rt, a.nbp_i), tile_scales<W_MXFP4>(ws, rt, a.nbp_i), a.nbp_i >> 2, ks, 4,
+                                   lane, n, xrow, xsrow, a.k, part[warp]);
+        else if (ks == 0)
+            warp_tile_any<W_MXFP4, false, true, true>(tile_values<W_MXFP4>(wv, rt, a.nbp_i), tile_scales<W_MXFP4>(ws, rt, a.nbp_i), a.nbp_i >> 2, 0, 1,
+                                   lane, n, xrow, xsrow, a.k, part[warp]);
     }
     __syncthreads();
     // 2 tiles x 16 rows x 8 columns = 256 outputs, one per thread
     const int tl = threadIdx.x >> 7, r16 = (threadIdx.x >> 3) & 15, c = threadIdx.x & 7;
     const int64_t row = ((int64_t)blockIdx.x * 2 + tl) * 16 + r16;
     if (c < n && row < a.d) {
-        float v = ((part[tl * 4 + 0][r16][c] + part[tl * 4 + 1][r16][c]) + part[tl * 4 + 2][r16][c]) + part[tl * 4 + 3][r16][c];
+        float v = part[tl * 4 + 0][r16][c];
+        if (!STRICT) v = ((v + part[tl * 4 + 1][r16][c]) + part[tl * 4 + 2][r16][c]) + part[tl * 4 + 3][r16][c];
         // K3 body: the routing weight multiplies the expert output, y += w_i * o_i (src/model.rs:2346-2351);
         // the product is formed here and the combine step adds the terms in slot order
         if (a.activation == MK_MOE_SITU) v = __fmul_rn(a.pair_weight[pair_s[c]], v);
@@ -707,6 +724,7 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     MK_CHECK_ARG(desc->activation == MK_MOE_SWIGLU_CLAMP || desc->activation == MK_MOE_SITU, "unknown activation");
     MK_CHECK_ARG(desc->router == MK_ROUTER_SIGMOID || desc->router == MK_ROUTER_SQRT_SOFTPLUS, "unknown router kind");
     MK_CHECK_ARG(desc->experts != nullptr, "experts table is NULL");
+    MK_CHECK_ARG((desc->act_mode & ~MK_ACT_STRICT) == MK_ACT_Q8, "the MoE layer takes MK_ACT_Q8, optionally with MK_ACT_STRICT");
     const bool situ = desc->activation == MK_MOE_SITU;
     auto f32ok = [](const mk_weight *w, int rows, int cols) { return w && w->fmt == MK_FMT_F32 && w->rows == rows && w->cols == cols; };
     if (latent != 0) {
@@ -752,6 +770,7 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     m->limit = desc->swiglu_limit;
     m->latent = latent > 0 ? latent : 0;
     m->rms_eps = desc->rms_eps;
+    m->strict = (desc->act_mode & MK_ACT_STRICT) != 0;
     if (latent > 0) { m->routed_down = (const float *)desc->routed_down->values; m->routed_up = (const float *)desc->routed_up->values; }
     if (sh32) {
         m->sh_gate = (const float *)desc->shared_f32[0]->values;
@@ -877,7 +896,10 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     // calls of <= 2 rows have at most 2 pairs per expert: the build without the batched schedule
     // needs fewer registers and keeps 4 CTAs per SM, one wave at batch 1
     const dim3 g1((unsigned)(m->inter / 32), (unsigned)items_ub), g2((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub);
-    if (n_rows <= 2) {
+    if (m->strict) {
+        moe_gate_up_kernel<MOE_STRICT><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
+        moe_down_kernel<MOE_STRICT><<<g2, 256, 0, ctx->stream>>>(a);
+    } else if (n_rows <= 2) {
         moe_gate_up_kernel<MOE_ALL_SPREAD><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
         moe_down_kernel<MOE_ALL_SPREAD><<<g2, 256, 0, ctx->stream>>>(a);
     } else if (n_rows <= MK_MOE_MIXED_MAX) {

@@ -46,7 +46,7 @@ class MoeDesc(C.Structure):
                 ("swiglu_limit", C.c_float), ("activation", _i32),
                 ("gate_w", _vp), ("gate_b", _vp), ("experts", C.POINTER(_vp)), ("shared", _vp * 3),
                 ("router", _i32), ("route_scale", C.c_float), ("latent", _i32), ("rms_eps", C.c_float),
-                ("routed_down", _vp), ("routed_up", _vp), ("routed_norm", _vp), ("shared_f32", _vp * 3)]
+                ("routed_down", _vp), ("routed_up", _vp), ("routed_norm", _vp), ("shared_f32", _vp * 3), ("act_mode", _i32)]
 
 
 class MlaDesc(C.Structure):
@@ -67,7 +67,7 @@ class ModelConfig(C.Structure):
 
 class ModelOpts(C.Structure):
     """mk_model_opts"""
-    _fields_ = [("max_positions", _i32), ("use_graph", _i32), ("rank", _i32), ("world", _i32)]
+    _fields_ = [("max_positions", _i32), ("use_graph", _i32), ("strict", _i32), ("keep_layer_hidden", _i32), ("rank", _i32), ("world", _i32)]
 
 
 _u32p = C.POINTER(C.c_uint32)
@@ -168,6 +168,7 @@ SIGNATURES = {
     "mk_model_forward": (_i32, [_vp, _vp, _i32, _vp, _vp]),
     "mk_model_generate": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_model_last_hidden": (_i32, [_vp, _vp, _vp]),
+    "mk_model_layer_hidden": (_i32, [_vp, _vp, _vp]),
 }
 
 

@@ -142,11 +142,11 @@ class Model:
     """The K3 model resident on one GPU (or this rank's share of it): Model::load + Model::forward with the
     engine's defaults (q8_0 lm_head, q8_0 MLA cache, MXFP4 experts through the q8 integer path)."""
 
-    def __init__(self, path, max_positions, use_graph=True, rank=0, world=1, ctx=None):
+    def __init__(self, path, max_positions, use_graph=True, rank=0, world=1, strict=False, keep_layer_hidden=False, ctx=None):
         self.ctx = ctx or Context.default()
         self.bin = path if isinstance(path, BinFile) else BinFile(path)
         self.config = self.bin.config
-        opts = _l.ModelOpts(int(max_positions), int(bool(use_graph)), int(rank), int(world))
+        opts = _l.ModelOpts(int(max_positions), int(bool(use_graph)), int(bool(strict)), int(bool(keep_layer_hidden)), int(rank), int(world))
         h = C.c_void_p()
         _l.check(self.ctx._L.mk_model_open(self.ctx._h, self.bin._h, C.byref(opts), C.byref(h)))
         self._h = h
@@ -202,6 +202,13 @@ class Model:
     def last_hidden(self):
         h = np.empty(self.config.d, np.float32)
         _l.check(self.ctx._L.mk_model_last_hidden(self.ctx._h, self._h, h.ctypes.data_as(C.c_void_p)))
+        return h
+
+    def layer_hidden(self):
+        """Per-layer taps of the last token [n_layers, 4, d] (keep_layer_hidden=True): the attention block's output, the
+        residual stream after it, the FFN's output, the residual stream after the layer."""
+        h = np.empty((self.config.n_layers, 4, self.config.d), np.float32)
+        _l.check(self.ctx._L.mk_model_layer_hidden(self.ctx._h, self._h, h.ctypes.data_as(C.c_void_p)))
         return h
 
     def reset(self):

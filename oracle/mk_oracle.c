@@ -44,6 +44,16 @@ void or_set_num_threads(int n) {
 #endif
 }
 
+/* exp / tanh / log of the reference are f32 libm calls (Rust's f32::exp, ::tanh, ::ln), whose last bit depends on the
+ * platform's libm.  With or_set_cr_math(1) they are taken in double precision and rounded once - the correctly rounded
+ * value up to double rounding, which is also what the CUDA kernels compute - so that a comparison can separate "same
+ * algorithm, same order" (bit-level agreement under this switch) from the last-ulp freedom of a libm. */
+static int g_cr_math = 0;
+void or_set_cr_math(int on) { g_cr_math = on != 0; }
+float or_m_expf(float x) { return g_cr_math ? (float)exp((double)x) : expf(x); }
+float or_m_tanhf(float x) { return g_cr_math ? (float)tanh((double)x) : tanhf(x); }
+float or_m_logf(float x) { return g_cr_math ? (float)log((double)x) : logf(x); }
+
 static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
 
@@ -357,9 +367,9 @@ void or_rmsnorm(const float *x, const float *w, size_t n, float eps, float *out)
     float inv = 1.0f / sqrtf(ss + eps);
     for (size_t i = 0; i < n; ++i) out[i] = x[i] * inv * w[i];
 }
-float or_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); } /* model.rs:607-610 */
+float or_sigmoid(float x) { return 1.0f / (1.0f + or_m_expf(-x)); } /* model.rs:607-610 */
 float or_situ(float g, float u) { /* model.rs:617-621 */
-    return 4.0f * tanhf(g / 4.0f) * or_sigmoid(g) * (25.0f * tanhf(u / 25.0f));
+    return 4.0f * or_m_tanhf(g / 4.0f) * or_sigmoid(g) * (25.0f * or_m_tanhf(u / 25.0f));
 }
 int or_argmax(const float *v, size_t n) { /* model.rs:3277-3290 with k = 1: first strict maximum */
     int best = 0;
@@ -426,7 +436,7 @@ void or_kda_gate(size_t heads, size_t dim, float gate_lb, const float *a_log, co
     for (size_t h = 0; h < heads; ++h) /* model.rs:1100-1109 */
         for (size_t c = 0; c < dim; ++c) {
             size_t i = h * dim + c;
-            g[i] = gate_lb * or_sigmoid(expf(a_log[c]) * (g_low[i] + dt_bias[i]));
+            g[i] = gate_lb * or_sigmoid(or_m_expf(a_log[c]) * (g_low[i] + dt_bias[i]));
         }
 }
 void or_kda_recur_step(size_t heads, size_t dim, float *s, const float *q, const float *k, const float *v, const float *g,
@@ -436,7 +446,7 @@ void or_kda_recur_step(size_t heads, size_t dim, float *s, const float *q, const
         float *sh = s + h * dim * dim;
         const float *gh = g + h * dim, *kh = k + h * dim, *vh = v + h * dim, *qh = q + h * dim;
         for (size_t i = 0; i < dim; ++i) {
-            float decay = expf(gh[i]);
+            float decay = or_m_expf(gh[i]);
             for (size_t j = 0; j < dim; ++j) sh[i * dim + j] *= decay;
         }
         memcpy(delta, vh, sizeof(float) * dim);
@@ -491,7 +501,7 @@ void or_kda_core(const float *q, const float *k, const float *v, const float *g,
         for (size_t h = 0; h < heads; ++h) {
             size_t base = (t * heads + h) * dim;
             const float *qh = q + base, *kh = k + base, *vh = v + base, *gh = g + base;
-            float bh = 1.0f / (1.0f + expf(-beta[t * heads + h]));
+            float bh = 1.0f / (1.0f + or_m_expf(-beta[t * heads + h]));
             float nq = 0.0f, nk = 0.0f;
             for (size_t i = 0; i < dim; ++i) nq += qh[i] * qh[i];
             for (size_t i = 0; i < dim; ++i) nk += kh[i] * kh[i];
@@ -500,12 +510,12 @@ void or_kda_core(const float *q, const float *k, const float *v, const float *g,
             for (size_t i = 0; i < dim; ++i) qn[i] = qh[i] / nq * scale;
             for (size_t i = 0; i < dim; ++i) kn[i] = kh[i] / nk;
             for (size_t c = 0; c < dim; ++c) {
-                float a = expf(a_log[c]), x = gh[c] + dt_bias[h * dim + c];
-                gg[c] = -5.0f / (1.0f + expf(-a * x));
+                float a = or_m_expf(a_log[c]), x = gh[c] + dt_bias[h * dim + c];
+                gg[c] = -5.0f / (1.0f + or_m_expf(-a * x));
             }
             float *sh = s + h * dim * dim;
             for (size_t i = 0; i < dim; ++i) {
-                float decay = expf(gg[i]);
+                float decay = or_m_expf(gg[i]);
                 for (size_t j = 0; j < dim; ++j) sh[i * dim + j] *= decay;
             }
             memcpy(delta, vh, sizeof(float) * dim);
@@ -535,7 +545,7 @@ void or_attn_res(size_t d, float eps, const float *prefix, const float *blocks, 
     for (size_t i = 0; i <= b; ++i) m = fmaxf(m, scores[i]);
     float z = 0.0f;
     for (size_t i = 0; i <= b; ++i) {
-        scores[i] = expf(scores[i] - m);
+        scores[i] = or_m_expf(scores[i] - m);
         z += scores[i];
     }
     for (size_t i = 0; i <= b; ++i) scores[i] /= z;
@@ -660,7 +670,7 @@ void or_router_k3(const float *gate_w, const float *gate_b, size_t n_experts, si
     if (logits_out) memcpy(logits_out, logits, sizeof(float) * n_experts);
     free(logits); free(sc); free(key); free(sel);
 }
-static float softplus(float x) { return x > 20.0f ? x : logf(1.0f + expf(x)); } /* deepseek.rs:60-68 */
+static float softplus(float x) { return x > 20.0f ? x : or_m_logf(1.0f + or_m_expf(x)); } /* deepseek.rs:60-68 */
 void or_gate_ds(const float *gate_w, const float *bias, size_t n_experts, size_t d, size_t top_k,
                 float route_scale, const float *x, int32_t *ids, float *weights) {
     float *logits = (float *)malloc(sizeof(float) * n_experts);
@@ -693,7 +703,7 @@ void or_expert_ds_f32(const float *w1, const float *w2, const float *w3, const f
     for (size_t i = 0; i < inter; ++i) {
         float g = fminf(gate[i], limit);
         float u = clampf(up[i], -limit, limit);
-        act[i] = (g / (1.0f + expf(-g))) * u; /* deepseek.rs:97-100 silu */
+        act[i] = (g / (1.0f + or_m_expf(-g))) * u; /* deepseek.rs:97-100 silu */
     }
     or_matvec_f32(w2, d, inter, act, out, 1);
     free(gate); free(up); free(act);
@@ -710,7 +720,7 @@ static void expert_ds_mxfp4(const uint8_t *const p[3], const uint8_t *const s[3]
     for (size_t j = 0; j < inter; ++j) {
         float g = fminf(gate[j], limit);
         float u = clampf(up[j], -limit, limit);
-        act[j] = wgt * (g / (1.0f + expf(-g))) * u;
+        act[j] = wgt * (g / (1.0f + or_m_expf(-g))) * u;
     }
     or_mxfp4_matvec(p[1], s[1], d, inter, act, o, 1, use_q8);
     free(gate); free(up); free(act);
@@ -903,9 +913,9 @@ void or_mla_attn_flash_q8(const or_mla_cache *c, const float *qh, size_t h, size
             tm = fmaxf(tm, s);
         }
         float m_new = fmaxf(m, tm);
-        float corr = expf(m - m_new);
+        float corr = or_m_expf(m - m_new);
         float tile_l = 0.0f;
-        for (size_t i = 0; i < tn; ++i) { scores[i] = expf(scores[i] - m_new); tile_l += scores[i]; }
+        for (size_t i = 0; i < tn; ++i) { scores[i] = or_m_expf(scores[i] - m_new); tile_l += scores[i]; }
         for (size_t d = 0; d < vd; ++d) oh[d] *= corr;
         l = l * corr + tile_l;
         for (size_t i = 0; i < tn; ++i) {
@@ -964,9 +974,9 @@ void or_mla_attn_flash_q8_mqa(const or_mla_cache *c, const float *q, size_t pos,
             float tm = -INFINITY;
             for (size_t i = 0; i < tn; ++i) tm = fmaxf(tm, sh[i]);
             float m_new = fmaxf(m[h], tm);
-            float corr = expf(m[h] - m_new);
+            float corr = or_m_expf(m[h] - m_new);
             float tile_l = 0.0f;
-            for (size_t i = 0; i < tn; ++i) { sh[i] = expf(sh[i] - m_new); tile_l += sh[i]; }
+            for (size_t i = 0; i < tn; ++i) { sh[i] = or_m_expf(sh[i] - m_new); tile_l += sh[i]; }
             float *oh = attn + h * vd;
             for (size_t d = 0; d < vd; ++d) oh[d] *= corr;
             l[h] = l[h] * corr + tile_l;
@@ -1007,7 +1017,7 @@ void or_mla_attn_ref_f32(const float *k, const float *v, size_t nh, size_t hd, s
     float m = -INFINITY;
     for (size_t j = 0; j <= pos; ++j) m = fmaxf(m, scores[j]);
     float z = 0.0f;
-    for (size_t j = 0; j <= pos; ++j) { scores[j] = expf(scores[j] - m); z += scores[j]; }
+    for (size_t j = 0; j <= pos; ++j) { scores[j] = or_m_expf(scores[j] - m); z += scores[j]; }
     for (size_t j = 0; j <= pos; ++j) scores[j] /= z;
     for (size_t d = 0; d < vd; ++d) oh[d] = 0.0f;
     for (size_t j = 0; j <= pos; ++j) {
@@ -1032,9 +1042,9 @@ void or_mla_attn_flash_f32(const float *k, const float *v, size_t nh, size_t hd,
             tm = fmaxf(tm, s);
         }
         float m_new = fmaxf(m, tm);
-        float corr = expf(m - m_new);
+        float corr = or_m_expf(m - m_new);
         float tile_l = 0.0f;
-        for (size_t i = 0; i < tn; ++i) { scores[i] = expf(scores[i] - m_new); tile_l += scores[i]; }
+        for (size_t i = 0; i < tn; ++i) { scores[i] = or_m_expf(scores[i] - m_new); tile_l += scores[i]; }
         for (size_t d = 0; d < vd; ++d) oh[d] *= corr;
         l = l * corr + tile_l;
         for (size_t i = 0; i < tn; ++i) {
@@ -1102,9 +1112,9 @@ void or_mla_abs_attn(const or_mla_abs_cache *c, const float *q, size_t nh, size_
             float tm = -INFINITY;
             for (size_t i = 0; i < tn; ++i) tm = fmaxf(tm, sh[i]);
             float m_new = fmaxf(m[h], tm);
-            float corr = expf(m[h] - m_new);
+            float corr = or_m_expf(m[h] - m_new);
             float tile_l = 0.0f;
-            for (size_t i = 0; i < tn; ++i) { sh[i] = expf(sh[i] - m_new); tile_l += sh[i]; }
+            for (size_t i = 0; i < tn; ++i) { sh[i] = or_m_expf(sh[i] - m_new); tile_l += sh[i]; }
             float *oh = out + h * vd;
             for (size_t d = 0; d < vd; ++d) oh[d] *= corr;
             l[h] = l[h] * corr + tile_l;

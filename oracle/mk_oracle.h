@@ -236,7 +236,15 @@ void or_model_reset(or_model *m);
 const or_config *or_model_config(const or_model *m);
 /* one token: logits [vocab] (nullable), hidden_out [d] (nullable) = the normed state fed to the lm_head; 0 on success */
 int or_model_forward(or_model *m, uint32_t token, float *logits, float *hidden_out);
+/* the same, also returning per layer [attention output, residual after it, FFN output, residual after the layer]:
+ * layer_out [n_layers][4][d] (nullable) */
+int or_model_forward_layers(or_model *m, uint32_t token, float *logits, float *hidden_out, float *layer_out);
 
+/* 1: exp / tanh / log taken in double precision and rounded once instead of the f32 libm calls (see mk_oracle.c) */
+void or_set_cr_math(int on);
+float or_m_expf(float x);
+float or_m_tanhf(float x);
+float or_m_logf(float x);
 int or_num_threads(void);
 void or_set_num_threads(int n);
 

@@ -630,7 +630,13 @@ static void dense_forward(or_model *m, or_layer *L, const float *x, float *out) 
 
 /* Model::forward (model.rs:2889-3031): one token through every layer; logits [vocab]; `hidden_out` (optional, [d])
  * receives the final normed hidden state (the input of logits_project). */
+int or_model_forward_layers(or_model *m, uint32_t token, float *logits, float *hidden_out, float *layer_out);
 int or_model_forward(or_model *m, uint32_t token, float *logits, float *hidden_out) {
+    return or_model_forward_layers(m, token, logits, hidden_out, NULL);
+}
+/* layer_out (optional, [n_layers][4][d]): per layer the attention block's output, the residual stream after it, the FFN's
+ * output and the residual stream after the layer (the engine's parity dumps record the last, model.rs:2760) */
+int or_model_forward_layers(or_model *m, uint32_t token, float *logits, float *hidden_out, float *layer_out) {
     const or_config *c = &m->cfg;
     const size_t d = c->d;
     if (token >= c->vocab) return -1;
@@ -657,6 +663,10 @@ int or_model_forward(or_model *m, uint32_t token, float *logits, float *hidden_o
         if (L->is_moe) or_moe_k3_forward(&L->moe, x, mlp_out, NULL, NULL);
         else dense_forward(m, L, x, mlp_out);
         for (size_t j = 0; j < d; ++j) hidden[j] = prefix2[j] + mlp_out[j];
+        if (layer_out) {
+            float *lo = layer_out + (size_t)l * 4 * d;
+            memcpy(lo, attn_out, d * 4); memcpy(lo + d, prefix2, d * 4); memcpy(lo + 2 * d, mlp_out, d * 4); memcpy(lo + 3 * d, hidden, d * 4);
+        }
     }
     memcpy(prefix, hidden, d * 4);
     or_attn_res(d, c->rms_eps, prefix, m->blocks, nb, m->out_res_w, hidden);

@@ -124,6 +124,7 @@ def _declare(L):
     sig("or_mla_abs_attn", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f32p)
     sig("or_mla_abs_attn_f64", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f64p)
     sig("or_set_num_threads", None, C.c_int)
+    sig("or_set_cr_math", None, C.c_int)
     sig("or_config_microkimi", None, C.c_void_p)
     sig("or_config_is_mla", C.c_int, C.c_void_p, C.c_uint32)
     sig("or_config_is_moe", C.c_int, C.c_void_p, C.c_uint32)
@@ -139,6 +140,7 @@ def _declare(L):
     sig("or_model_reset", None, C.c_void_p)
     sig("or_model_config", C.c_void_p, C.c_void_p)
     sig("or_model_forward", C.c_int, C.c_void_p, C.c_uint32, _f32p, _f32p)
+    sig("or_model_forward_layers", C.c_int, C.c_void_p, C.c_uint32, _f32p, _f32p, _f32p)
     sig("or_f32_to_f16", C.c_uint16, C.c_float)
     sig("or_f16_to_f32", C.c_float, C.c_uint16)
 
@@ -236,6 +238,17 @@ class Model:
             raise ValueError(f"or_model_forward failed: {rc}")
         return (logits, hid) if want_hidden else logits
 
+    def forward_layers(self, token):
+        """One token -> (logits, final normed hidden state, taps [n_layers, 4, d]: per layer the attention block's output,
+        the residual stream after it, the FFN's output, the residual stream after the layer)."""
+        logits = np.empty(self.config.vocab, np.float32)
+        hid = np.empty(self.config.d, np.float32)
+        layers = np.empty((self.config.n_layers, 4, self.config.d), np.float32)
+        rc = lib().or_model_forward_layers(self._h, int(token), _p(logits, _f32p), _p(hid, _f32p), _p(layers, _f32p))
+        if rc != 0:
+            raise ValueError(f"or_model_forward failed: {rc}")
+        return logits, hid, layers
+
     def reset(self):
         lib().or_model_reset(self._h)
 
@@ -272,6 +285,12 @@ def host_threads():
 
 def set_num_threads(n):
     lib().or_set_num_threads(int(n))
+
+
+def set_cr_math(on):
+    """True: the oracle takes exp / tanh / log in double precision and rounds once (correctly rounded in practice, and
+    what the CUDA kernels compute) instead of calling the f32 libm functions, whose last bit is the platform's."""
+    lib().or_set_cr_math(int(bool(on)))
 
 
 # ---------------------------------------------------------------- RNG
