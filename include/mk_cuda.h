@@ -455,7 +455,9 @@ int32_t mk_quantize_mxfp4_dev(mk_ctx *ctx, const float *w, int64_t rows, int64_t
 typedef struct mk_model mk_model;
 typedef struct {
     int32_t max_positions;   /* tokens a sequence may hold (prompt + generated): capacity of every MLA cache */
-    int32_t use_graph;       /* 1: replay the token as a CUDA graph from the second call on */
+    int32_t use_graph;       /* 1: replay the token as a CUDA graph from the third call on (the first call runs eagerly, the
+                                second is recorded).  Needs a real stream: on the legacy default stream (mk_set_stream(NULL))
+                                and while mk_prof_enable is on the token is launched kernel by kernel */
     int32_t strict;          /* 1: MoE experts and lm_head in MK_ACT_STRICT order (results closest to the CPU token) */
     int32_t keep_layer_hidden; /* 1: keep per-layer taps of the last token for mk_model_layer_hidden (the engine's
                                 --dump-hidden / parity dumps, src/model.rs:2749-2823) */

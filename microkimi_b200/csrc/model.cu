@@ -613,7 +613,9 @@ extern "C" int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t 
     // the token of this step: the caller's, or the pick the previous step left on the device
     copy_i32_kernel<<<1, 1, 0, st>>>(token ? token : m->next, m->tok);
     ctx->launches++;
-    const bool graph_ok = m->opts.use_graph && m->world == 1 && !ctx->prof_on;
+    // a CUDA graph cannot be recorded from the legacy default stream: there the token is launched kernel by kernel
+    const bool real_stream = st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread;
+    const bool graph_ok = m->opts.use_graph && m->world == 1 && !ctx->prof_on && real_stream;
     int32_t rc = MK_OK;
     if (m->graph && m->graph_ws != ctx->ws) {
         // another call on this context grew the shared workspace since the token was recorded: the recorded
