@@ -350,6 +350,98 @@ def measure_mla(torch, mk, ctx, dev, layout, ctx_len, batch, steps, warmup):
     return out
 
 
+def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=64, n_new=256, cpu_tokens=0, path=None):
+    """Whole-token decode of the 93-layer micro skeleton (the engine's historical configuration: 69 KDA + 24 MLA layers,
+    896 MXFP4 experts top-16 per MoE layer, q8_0 lm_head over 163840 rows, q8_0 MLA caches): a synthetic model file with the
+    builder's shapes and distributions, a seeded 64-token prompt fed token by token, then 256 greedy steps whose token ids
+    never leave the GPU.  One CUDA graph replay per token at N = 1; at N > 1 the experts are block-partitioned over the ranks
+    and the lm_head rows sharded, exchanged by peer-memory stores, launched kernel by kernel."""
+    import tempfile
+
+    from microkimi_b200 import model as M
+    own = mk.Context(local)                       # a context of its own: its stream is a real stream, so the token can be recorded
+    stream = torch.cuda.Stream(device=dev)
+    out = {"workload": f"decode of the 93-layer micro skeleton, {n_prompt}-token prompt + {n_new} greedy steps, "
+                       f"expert-parallel x{world}" if world > 1 else
+                       f"decode of the 93-layer micro skeleton, {n_prompt}-token prompt + {n_new} greedy steps, one GPU"}
+    path = path or os.path.join(tempfile.gettempdir(), "mk_bench_microkimi.bin")
+    t0 = time.time()
+    if rank == 0:
+        with torch.cuda.stream(stream):
+            own.use_torch_stream()
+            M.build_synthetic_bin(path, None, seed=20240, ctx=own)
+            torch.cuda.synchronize()
+    if dist is not None and world > 1:
+        dist.barrier()
+    out["build_s"] = round(time.time() - t0, 2)
+    t0 = time.time()
+    with torch.cuda.stream(stream):
+        own.use_torch_stream()
+        model = M.Model(path, n_prompt + n_new + 8, use_graph=True, rank=rank, world=world, ctx=own)
+        if world > 1:
+            model.connect()
+        out["load_s"] = round(time.time() - t0, 2)
+        out["weight_mb_per_gpu"] = model.weight_bytes / 1e6
+        rng = np.random.default_rng(64)
+        prompt = rng.integers(0, 163584, n_prompt).astype(np.int32)
+        model.generate(prompt[:3], 2)             # warm-up: eager token, recorded token, replays
+        model.reset()
+        torch.cuda.synchronize()
+
+        def sync_all():
+            torch.cuda.synchronize()
+            if dist is not None and world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+        sync_all()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record(stream)
+        first = model.generate(prompt, 1)         # the prompt, token by token (returns after its own synchronization)
+        e1.record(stream)
+        for _ in range(n_new):
+            model.forward_dev(None)               # the previous pick, on the device
+        e2.record(stream)
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1), e1.elapsed_time(e2)], dtype=torch.float64, device=dev)
+        if dist is not None and world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        prefill_ms, decode_ms = float(t[0].item()), float(t[1].item())
+        out.update({"prompt_ms_per_token": prefill_ms / n_prompt, "decode_ms_per_token": decode_ms / n_new,
+                    "decode_tokens_per_s": n_new / (decode_ms * 1e-3), "launches_per_token": model.launches_per_token,
+                    "first_token": int(first[0]), "status_word": own.status_word()})
+        # end to end: every token id goes back to the host before the next step starts (the engine's loop prints and tests it)
+        model.reset()
+        model.generate(prompt[:4], 1)
+        sync_all()
+        tok, n_e2e = 1, min(n_new, 64)
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            _, tok = model.forward(tok, want_logits=False)
+        e2e = (time.perf_counter() - t0) / n_e2e
+        te = torch.tensor([e2e], dtype=torch.float64, device=dev)
+        if dist is not None and world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        out["e2e_tokens_per_s"] = 1.0 / float(te.item())
+        out["e2e_note"] = "mk_model_forward per token: token id H2D, the token, picked id D2H, synchronize"
+        model.free()
+    if cpu_tokens and rank == 0:
+        from oracle import oracle as O
+        threads = O.host_threads()
+        O.set_num_threads(threads)
+        ref = O.Model(path, cpu_tokens + 4, n_threads=threads)
+        tok = int(prompt[0])
+        ref.forward(tok)
+        t0 = time.perf_counter()
+        for _ in range(cpu_tokens):
+            tok = O.argmax(ref.forward(tok))
+        dt = (time.perf_counter() - t0) / cpu_tokens
+        out["cpu_baseline"] = {"value": 1.0 / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                               "sample": f"{cpu_tokens} decode steps of the same model file, C restatement of Model::forward "
+                                         f"(src/model.rs:2889-3031) with {threads} OpenMP threads"}
+    own.close()
+    return out
+
+
 def extras_single_gpu(torch, mk, ctx, dev, heads, x1):
     """Bounded runs of the other workloads of the path for the same JSON line (one GPU)."""
     out = {}
@@ -387,6 +479,10 @@ def extras_single_gpu(torch, mk, ctx, dev, heads, x1):
     guard("config4_mla_absorbed", lambda: {f"ctx{n}_batch{b}": measure_mla(torch, mk, ctx, dev, "absorbed", n, b, 30, 3)
                                            for n, b in ((4096, 1), (16384, 8), (65536, 8))})
     guard("mla_per_head_ctx16384_batch8", lambda: measure_mla(torch, mk, ctx, dev, "per_head", 16384, 8, 20, 3))
+    for h in heads:
+        h.free()
+    torch.cuda.empty_cache()
+    guard("config5_decode", lambda: measure_decode(torch, mk, dev, ctx.device, cpu_tokens=8))
     return out
 
 
@@ -637,10 +733,16 @@ def run_gpu(args):
             for h in heads:
                 h.free()
             torch.cuda.empty_cache()
+            extra = {}
             try:
-                extra = {"moe_expert_parallel_peer": measure_moe_ep(torch, dist, mk, ctx, dev, world, rank, 384, (1, 4, 16), 30, 5)}
+                extra["moe_expert_parallel_peer"] = measure_moe_ep(torch, dist, mk, ctx, dev, world, rank, 384, (1, 4, 16), 30, 5)
             except Exception as exc:
-                extra = {"moe_expert_parallel_peer": {"error": f"{type(exc).__name__}: {exc}"}}
+                extra["moe_expert_parallel_peer"] = {"error": f"{type(exc).__name__}: {exc}"}
+            torch.cuda.empty_cache()
+            try:
+                extra["config5_decode"] = measure_decode(torch, mk, dev, local, world, rank, dist)
+            except Exception as exc:
+                extra["config5_decode"] = {"error": f"{type(exc).__name__}: {exc}"}
 
     if rank == 0:
         cb = None
@@ -681,6 +783,7 @@ def run_gpu(args):
             **({"exchange_kernel_ms": xms_ / xn_} if (used_peer and xn_) else {}),
             "status_word": status_all,
             "clocks": clocks,
+            "decode_tokens_per_s": ((extra or {}).get("config5_decode") or {}).get("decode_tokens_per_s"),
             "extra": extra,
         }
         print(json.dumps(line), flush=True)
@@ -766,6 +869,27 @@ def run_case_kda(args):
                       "status_word": ctx.status_word(), "roofline": _roof(alg, ms, "latency-bound: one CTA per head")}), flush=True)
 
 
+def run_case_decode(args):
+    """The whole-token decode alone (one GPU, or under torchrun expert-parallel over the ranks)."""
+    import torch
+
+    import microkimi_b200 as mk
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29534")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
+    res = measure_decode(torch, mk, torch.device("cuda", local), local, world, rank, dist, cpu_tokens=0 if args.no_cpu else 8)
+    if rank == 0:
+        print(json.dumps({"case": "decode", "n_gpus": world, **res}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_case_mla(args):
     torch, mk, ctx, dev = _side_ctx()
     print(json.dumps({"case": "mla", **measure_mla(torch, mk, ctx, dev, args.layout, args.ctx, args.batch, args.steps, args.warmup)}),
@@ -774,7 +898,7 @@ def run_case_mla(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "moe_ep", "mla", "kda"],
+    ap.add_argument("--case", default="lm_head", choices=["lm_head", "mxfp4_gemv", "moe", "moe_ep", "mla", "kda", "decode"],
                     help="lm_head is the benchmark proper; the others run one of the side workloads alone")
     ap.add_argument("--rows", type=int, default=7168)
     ap.add_argument("--cols", type=int, default=2048)
@@ -811,6 +935,8 @@ def main():
         run_case_mla(args)
     elif args.case == "kda":
         run_case_kda(args)
+    elif args.case == "decode":
+        run_case_decode(args)
     else:
         run_gpu(args)
 
