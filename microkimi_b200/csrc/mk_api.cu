@@ -71,8 +71,33 @@ extern "C" int32_t mk_shutdown(mk_ctx *ctx) {
         }
         delete[] ctx->prof_pairs;
     }
+    if (ctx->side_ready) {
+        for (int i = 0; i < 2; ++i) cudaStreamDestroy(ctx->side[i]);
+        for (int i = 0; i < 4; ++i) cudaEventDestroy(ctx->side_ev[i]);
+    }
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
+    return MK_OK;
+}
+
+static int32_t side_init(mk_ctx *ctx) {
+    if (ctx->side_ready) return MK_OK;
+    MK_CUDA(cudaSetDevice(ctx->device));
+    for (int i = 0; i < 2; ++i) MK_CUDA(cudaStreamCreateWithFlags(&ctx->side[i], cudaStreamNonBlocking));
+    for (int i = 0; i < 4; ++i) MK_CUDA(cudaEventCreateWithFlags(&ctx->side_ev[i], cudaEventDisableTiming));
+    ctx->side_ready = 1;
+    return MK_OK;
+}
+int32_t mk_fork(mk_ctx *ctx, int i) {
+    int32_t rc = side_init(ctx);
+    if (rc != MK_OK) return rc;
+    MK_CUDA(cudaEventRecord(ctx->side_ev[i], ctx->stream));
+    MK_CUDA(cudaStreamWaitEvent(ctx->side[i], ctx->side_ev[i], 0));
+    return MK_OK;
+}
+int32_t mk_join(mk_ctx *ctx, int i) {
+    MK_CUDA(cudaEventRecord(ctx->side_ev[2 + i], ctx->side[i]));
+    MK_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->side_ev[2 + i], 0));
     return MK_OK;
 }
 

@@ -94,6 +94,11 @@ struct mk_ctx {
     int mla_strict;         // 1 = per-head attention by the one-warp-per-head kernel that keeps the CPU's summation order (parity mode)
     int mla_no_t5;          // 1 = absorbed MLA on the mma.sync kernel instead of the tcgen05 one (study knob)
     int kda_smem;           // 1 = KDA step with S staged in shared memory also for dim 64 / 128, where the register form is the default (study knob)
+    // side streams for launches that do not depend on each other (forked from and joined to `stream` with events,
+    // which also works while `stream` is being recorded into a CUDA graph); created on first use
+    cudaStream_t side[2];
+    cudaEvent_t side_ev[4];
+    int side_ready;
     // optional per-category event timing (mk_prof_*)
     int prof_on;
     struct mk_prof_pair *prof_pairs; // pool of event pairs
@@ -111,6 +116,14 @@ struct mk_prof_scope {
 };
 int32_t mk_prof_drain(mk_ctx *ctx); // folds finished pairs into the accumulators (synchronizes)
 
+int32_t mk_fork(mk_ctx *ctx, int i);   // side stream i continues from everything enqueued on ctx->stream so far
+int32_t mk_join(mk_ctx *ctx, int i);   // ctx->stream waits for everything enqueued on side stream i
+// launches made while one of these lives go to side stream i
+struct mk_on_side {
+    mk_ctx *ctx; cudaStream_t saved;
+    mk_on_side(mk_ctx *c, int i) : ctx(c), saved(c->stream) { c->stream = c->side[i]; }
+    ~mk_on_side() { ctx->stream = saved; }
+};
 int32_t mk_ws_reserve(mk_ctx *ctx, size_t bytes);      // activation workspace
 int32_t mk_io_reserve(mk_ctx *ctx, size_t bytes);      // device staging for host-pointer calls
 int32_t mk_pinned_reserve(mk_ctx *ctx, size_t bytes);  // pinned host staging
@@ -132,6 +145,10 @@ int32_t mk_launch_rmsnorm(mk_ctx *ctx, const float *x, const float *w, int n, in
 int32_t mk_launch_situ(mk_ctx *ctx, const float *a, const float *u, int64_t count, float *out);
 int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, int batch, int32_t *out, void *scratch);
 size_t mk_argmax_scratch_bytes(int batch);
+// moe.cu: the K3 latent MoE layer for ONE token with the shared expert on a side stream: out_routed = routed_up(...),
+// out_shared = the f32 shared expert's output, NOT added (the caller adds routed + shared, in that order).
+// MK_ERR_UNSUPPORTED when the layer is not of that kind (the caller then uses mk_moe_forward_dev).
+int32_t mk_moe_forward_k3_split(mk_ctx *ctx, mk_moe *m, const float *x, float *out_routed, float *out_shared);
 void mk_mla_note_replay(mk_mla *m, int seq);   // mla.cu: host-side position count after a graph replay of a decode step
 // weight (re)tiling
 int32_t mk_launch_retile_mxfp4(mk_ctx *ctx, const uint8_t *packed, const uint8_t *scales, mk_weight *w);

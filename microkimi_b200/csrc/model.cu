@@ -13,6 +13,7 @@
 #include <string>
 #include <vector>
 
+#include "f32gemv.cuh"
 #include "mk_common.cuh"
 
 namespace {
@@ -42,6 +43,72 @@ __global__ void mla_assemble_kernel(const float *__restrict__ kb, const float *_
     if (r < nope) k_new[h * qh + r] = kb[h * (nope + vd) + r];
     else if (r < qh) k_new[h * qh + r] = k_rot[r - nope];
     else v_new[h * vd + (r - qh)] = kb[h * (nope + vd) + nope + (r - qh)];
+}
+// The glue between two blocks in ONE launch (src/model.rs:2905-2920, 2943-2959, 2994-2996, 3014-3017):
+//   prefix = a [+ (b [+ c])]     residual adds: hidden = prefix2 + mlp_out with mlp_out = routed + shared, or prefix + attn_out
+//   [push]  = prefix             the layer input becomes an AttnRes block row (after the mix below has used the old rows)
+//   mixed  = attn_res(prefix, blocks[0 .. nb), w)   softmax over the RMS-normed scores, probability-weighted RAW rows;
+//                                                   nb == 0 at the very first mix of a token: mixed = prefix
+//   x      = rmsnorm(mixed, ln)
+// One CTA; every sum in the engine's order: dot() with its 8 accumulators by one warp per row (mkf::reduce8), the
+// softmax sequentially, exp in double precision rounded once.  Shared memory: prefix[d], mixed[d], scores[nb + 1].
+__global__ void __launch_bounds__(512) glue_kernel(const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ c,
+                                                   float *__restrict__ prefix_out, float *__restrict__ push_row,
+                                                   const float *__restrict__ blocks, int nb, const float *__restrict__ w,
+                                                   const float *__restrict__ ln, float eps, int d, float *__restrict__ x_out) {
+    extern __shared__ float gsm[];
+    float *pre = gsm, *mix = gsm + d, *sc = gsm + 2 * d;
+    __shared__ float s_inv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5, j8 = lane & 7, full = d & ~7;
+    for (int j = tid; j < d; j += blockDim.x) {
+        float v = a[j];
+        if (b) v = __fadd_rn(v, c ? __fadd_rn(b[j], c[j]) : b[j]);
+        pre[j] = v;
+        if (prefix_out) prefix_out[j] = v;
+        if (push_row) push_row[j] = v;
+    }
+    __syncthreads();
+    const float *src = pre;
+    if (nb > 0) {
+        for (int row = warp; row <= nb; row += nw) {     // score of block row `row`, the prefix last (as attn_res_score_kernel)
+            const float *v = row < nb ? blocks + (int64_t)row * d : pre;
+            float acc = 0.0f;
+            for (int k = 0; k < full; k += 8) acc = __fadd_rn(acc, __fmul_rn(v[k + j8], v[k + j8]));
+            float ss = mkf::reduce8(acc, lane);
+            for (int k = full; k < d; ++k) ss = __fadd_rn(ss, __fmul_rn(v[k], v[k]));
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)d), eps)));
+            acc = 0.0f;
+            for (int k = 0; k < full; k += 8) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(v[k + j8], inv), w[k + j8]));
+            float s1 = mkf::reduce8(acc, lane);
+            for (int k = full; k < d; ++k) s1 = __fadd_rn(s1, __fmul_rn(__fmul_rn(v[k], inv), w[k]));
+            if (lane == 0) sc[row] = s1;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float mx = -INFINITY;
+            for (int i = 0; i <= nb; ++i) mx = fmaxf(mx, sc[i]);
+            float z = 0.0f;
+            for (int i = 0; i <= nb; ++i) { sc[i] = (float)exp((double)__fsub_rn(sc[i], mx)); z = __fadd_rn(z, sc[i]); }
+            for (int i = 0; i <= nb; ++i) sc[i] = __fdiv_rn(sc[i], z);
+        }
+        __syncthreads();
+        for (int j = tid; j < d; j += blockDim.x) {
+            float o = 0.0f;
+            for (int i = 0; i < nb; ++i) o = __fadd_rn(o, __fmul_rn(sc[i], blocks[(int64_t)i * d + j]));
+            mix[j] = __fadd_rn(o, __fmul_rn(sc[nb], pre[j]));
+        }
+        __syncthreads();
+        src = mix;
+    }
+    if (warp == 0) {
+        float acc = 0.0f;
+        for (int k = 0; k < full; k += 8) acc = __fadd_rn(acc, __fmul_rn(src[k + j8], src[k + j8]));
+        float ss = mkf::reduce8(acc, lane);
+        for (int k = full; k < d; ++k) ss = __fadd_rn(ss, __fmul_rn(src[k], src[k]));
+        if (lane == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)d), eps)));
+    }
+    __syncthreads();
+    for (int j = tid; j < d; j += blockDim.x) x_out[j] = __fmul_rn(__fmul_rn(src[j], s_inv), ln[j]);
 }
 __global__ void copy_i32_kernel(const int32_t *__restrict__ src, int32_t *__restrict__ dst) { *dst = *src; }
 // MXFP4 blobs of one layer (packed then scales, each blob where the file put it inside the staged span) -> the tiled
@@ -117,6 +184,9 @@ struct mk_model {
     mk_moe_ep *ep = nullptr;
     // activations
     float *hidden = nullptr, *res = nullptr, *x = nullptr, *attn_out = nullptr, *p2 = nullptr, *mlp_out = nullptr, *blocks = nullptr;
+    float *sh_out = nullptr;        // the MoE's shared-expert output when it is added by the next glue launch
+    float *embed_row = nullptr;     // the token's embedding row
+    int max_blocks = 0;
     float *y = nullptr, *g_low = nullptr, *o = nullptr;                                     // KDA
     float *qan = nullptr, *q = nullptr, *kpn = nullptr, *kb = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr; // MLA
     float *au = nullptr, *act = nullptr;                                                    // dense
@@ -334,6 +404,7 @@ extern "C" int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_
     MK_CHECK_ARG(proj % 4 == 0 && c.kda_fa % 4 == 0 && c.mla_qa % 4 == 0 && cdim % 4 == 0 && c.mla_kva % 4 == 0 && c.dense_inter % 4 == 0,
                  "projection widths must be multiples of 4 (slices of a stacked result stay 16-byte aligned)");
     MK_CHECK_ARG(c.n_experts % world == 0 && c.vocab % world == 0, "n_experts and vocab must divide by the number of ranks");
+    MK_CHECK_ARG((size_t)(2 * d + c.n_layers / c.attn_res_block + 4) * 4 <= 48 * 1024, "hidden size too large for the residual/AttnRes/norm kernel (two rows in shared memory)");
     MK_CUDA(cudaSetDevice(ctx->device));
     mk_model *m = new (std::nothrow) mk_model();
     if (!m) return MK_ERR_OOM;
@@ -348,7 +419,10 @@ extern "C" int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_
     m->norm_f = L.f32("norm.weight", d);
     m->out_w = L.combined("output_attn_res_norm.weight", "output_attn_res_proj.weight", d);
     const int max_blocks = (int)(c.n_layers / c.attn_res_block + 2);
+    m->max_blocks = max_blocks;
+    m->embed_row = L.zeros(d);
     m->blocks = L.zeros((size_t)max_blocks * d);
+    m->sh_out = L.zeros(d);
     m->hidden = L.zeros(d); m->res = L.zeros(d); m->x = L.zeros(d); m->attn_out = L.zeros(d); m->p2 = L.zeros(d); m->mlp_out = L.zeros(d);
     m->y = L.zeros((size_t)(4 * proj + c.kda_fa + c.kda_heads) > (size_t)(c.mla_qa + cdim + hv) ? (size_t)(4 * proj + c.kda_fa + c.kda_heads)
                                                                                              : (size_t)(c.mla_qa + cdim + hv));
@@ -411,10 +485,13 @@ extern "C" int32_t mk_model_open(mk_ctx *ctx, const mk_bin *bin, const mk_model_
             const float *gate_w = (const float *)L.find(q + "gate.weight", MK_DTYPE_F32, (uint64_t)c.n_experts * d * 4);
             const float *gate_b = (const float *)L.find(q + "gate.e_score_correction_bias", MK_DTYPE_F32, (uint64_t)c.n_experts * 4);
             const float *rnorm = (const float *)L.find(q + "routed_expert_norm.weight", MK_DTYPE_F32, (uint64_t)c.routed_hidden * 4);
-            ly.rd = f32_record(L.f32(q + "routed_expert_down_proj.weight", (uint64_t)c.routed_hidden * d), c.routed_hidden, d);
+            // routed_down, shared gate and shared up read the same vector: one stacked matrix, one launch per token
+            float *stk = L.stacked({{q + "routed_expert_down_proj.weight", c.routed_hidden}, {q + "shared_experts.gate_proj.weight", c.shared_inter},
+                                    {q + "shared_experts.up_proj.weight", c.shared_inter}}, d, nullptr);
+            ly.rd = f32_record(stk, c.routed_hidden, d);
+            ly.sg = f32_record(stk ? stk + (size_t)c.routed_hidden * d : nullptr, c.shared_inter, d);
+            ly.su = f32_record(stk ? stk + (size_t)(c.routed_hidden + c.shared_inter) * d : nullptr, c.shared_inter, d);
             ly.ru = f32_record(L.f32(q + "routed_expert_up_proj.weight", (uint64_t)d * c.routed_hidden), d, c.routed_hidden);
-            ly.sg = f32_record(L.f32(q + "shared_experts.gate_proj.weight", (uint64_t)c.shared_inter * d), c.shared_inter, d);
-            ly.su = f32_record(L.f32(q + "shared_experts.up_proj.weight", (uint64_t)c.shared_inter * d), c.shared_inter, d);
             ly.sd = f32_record(L.f32(q + "shared_experts.down_proj.weight", (uint64_t)d * c.shared_inter), d, c.shared_inter);
             if (L.rc != MK_OK) return fail(L.rc, L.err);
             const int per = (int)c.n_experts / world;
@@ -517,23 +594,25 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
     cudaStream_t st = ctx->stream;
     int32_t rc;
 #define RC(call) do { rc = (call); if (rc != MK_OK) return rc; } while (0)
-    embed_row_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->embed, m->tok, (int)c.vocab, d, m->hidden, ctx->status_dev);
+    // residual inputs of the next glue launch: hidden = ga [+ (gb [+ gc])]
+    const float *ga = m->embed_row, *gb = nullptr, *gc = nullptr;
+    embed_row_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->embed, m->tok, (int)c.vocab, d, m->embed_row, ctx->status_dev);
     ctx->launches++;
+    const size_t gsm_bytes = (size_t)(2 * d + m->max_blocks + 2) * 4;
+    auto tap = [&](uint32_t l, int k, const float *src) -> int32_t {
+        if (m->layer_hidden) MK_CUDA(cudaMemcpyAsync(m->layer_hidden + ((size_t)l * 4 + k) * d, src, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+        return MK_OK;
+    };
     for (uint32_t l = 0; l < c.n_layers; ++l) {
         Layer &ly = m->layers[l];
         int nb = ly.nb_before;
-        const float *normin = m->hidden;
-        if (nb > 0) {
-            RC(mk_attn_res_dev(ctx, m->hidden, m->blocks, d, nb, ly.sa_w, d, eps, m->res));
-            normin = m->res;
-        }
+        // hidden of this layer (the previous layer's residual adds), AttnRes mix over the old block rows, rmsnorm -> x
+        glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, ly.pushes ? m->blocks + (size_t)nb * d : nullptr, m->blocks, nb, ly.sa_w,
+                                               ly.input_ln, eps, d, m->x);
+        ctx->launches++;
+        if (l > 0) RC(tap(l - 1, 3, m->hidden));
         bool have_prefix = true;
-        if (ly.pushes) {
-            MK_CUDA(cudaMemcpyAsync(m->blocks + (size_t)nb * d, m->hidden, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
-            ++nb;
-            have_prefix = false;
-        }
-        RC(mk_launch_rmsnorm(ctx, normin, ly.input_ln, 1, d, eps, m->x));
+        if (ly.pushes) { ++nb; have_prefix = false; }
         if (ly.is_mla) {
             float *y = m->y;
             RC(mk_launch_f32_gemv(ctx, ly.w_x, ly.w_x_rows, d, m->x, 1, y, ly.w_x_rows, 0));          // q_a, kv_a, g_proj of x
@@ -558,36 +637,43 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
             RC(mk_kda_step_dev(ctx, ly.kda, y, y + proj, y + 2 * proj, m->g_low, y + 4 * proj + fa, y + 3 * proj, m->o));
             RC(mk_launch_f32_gemv(ctx, ly.o_proj, d, proj, m->o, 1, m->attn_out, d, 0));
         }
-        const float *p2 = m->attn_out;
-        if (have_prefix) {
-            vec_add_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->hidden, m->attn_out, m->p2, d);
-            ctx->launches++;
-            p2 = m->p2;
-        }
-        RC(mk_attn_res_dev(ctx, p2, m->blocks, d, nb, ly.mlp_w, d, eps, m->res));
-        RC(mk_launch_rmsnorm(ctx, m->res, ly.post_ln, 1, d, eps, m->x));
+        // prefix2 = prefix + attn_out (or attn_out alone when the prefix became a block row), mix, rmsnorm -> x
+        glue_kernel<<<1, 512, gsm_bytes, st>>>(m->attn_out, have_prefix ? m->hidden : nullptr, nullptr, m->p2, nullptr, m->blocks, nb, ly.mlp_w,
+                                               ly.post_ln, eps, d, m->x);
+        ctx->launches++;
+        RC(tap(l, 0, m->attn_out));
+        RC(tap(l, 1, m->p2));
+        gc = nullptr;
         if (ly.is_moe) {
-            if (m->ep) RC(mk_moe_forward_ep_dev(ctx, ly.moe, m->ep, m->x, 1, m->mlp_out, nullptr, nullptr));
-            else RC(mk_moe_forward_dev(ctx, ly.moe, m->x, 1, m->mlp_out, nullptr, nullptr));
+            if (m->ep) {
+                RC(mk_moe_forward_ep_dev(ctx, ly.moe, m->ep, m->x, 1, m->mlp_out, nullptr, nullptr));
+            } else {
+                rc = mk_moe_forward_k3_split(ctx, ly.moe, m->x, m->mlp_out, m->sh_out);
+                if (rc == MK_OK) gc = m->sh_out;          // added by the next glue launch: prefix2 + (routed + shared)
+                else if (rc == MK_ERR_UNSUPPORTED) RC(mk_moe_forward_dev(ctx, ly.moe, m->x, 1, m->mlp_out, nullptr, nullptr));
+                else return rc;
+            }
         } else {
             const int di = (int)c.dense_inter;
             RC(mk_launch_f32_gemv(ctx, ly.dgu, 2 * di, d, m->x, 1, m->au, 2 * di, 0));
             RC(mk_launch_situ(ctx, m->au, m->au + di, di, m->act));
             RC(mk_launch_f32_gemv(ctx, ly.dd, d, di, m->act, 1, m->mlp_out, d, 0));
         }
-        vec_add_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(p2, m->mlp_out, m->hidden, d);
-        ctx->launches++;
         if (m->layer_hidden) {
-            float *lo = m->layer_hidden + (size_t)l * 4 * d;
-            MK_CUDA(cudaMemcpyAsync(lo, m->attn_out, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
-            MK_CUDA(cudaMemcpyAsync(lo + d, p2, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
-            MK_CUDA(cudaMemcpyAsync(lo + 2 * d, m->mlp_out, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
-            MK_CUDA(cudaMemcpyAsync(lo + 3 * d, m->hidden, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
+            if (gc) {   // the tap shows the layer's FFN output as the engine forms it: routed + shared
+                vec_add_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->mlp_out, gc, m->res, d);
+                ctx->launches++;
+                RC(tap(l, 2, m->res));
+            } else {
+                RC(tap(l, 2, m->mlp_out));
+            }
         }
+        ga = m->p2; gb = m->mlp_out;
     }
     const int nb_final = m->layers.back().nb_before + (m->layers.back().pushes ? 1 : 0);
-    RC(mk_attn_res_dev(ctx, m->hidden, m->blocks, d, nb_final, m->out_w, d, eps, m->res));
-    RC(mk_launch_rmsnorm(ctx, m->res, m->norm_f, 1, d, eps, m->x));
+    glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, nullptr, m->blocks, nb_final, m->out_w, m->norm_f, eps, d, m->x);
+    ctx->launches++;
+    RC(tap(c.n_layers - 1, 3, m->hidden));
     if (m->gather) {
         const float *full = nullptr;
         RC(mk_matvec_q8_gather_dev(ctx, m->head, m->gather, m->x, 1, m->head_row0, &full, m->next));

@@ -32,6 +32,9 @@ struct mk_moe {
     float rms_eps;
     const float *sh_gate, *sh_down, *sh_up; // f32 shared expert [si, dx], [dx, si], [si, dx]; nullptr = none
     int shared_inter;
+    bool stack3;                   // routed_down, shared gate and shared up are one contiguous [latent + 2 si, dx] matrix
+    float *stk;                    // [latent + 2 si]: their products with one token (decode fast path)
+    float *sh_out;                 // [cap_rows][dx] shared expert output when it is not accumulated into the layer output
     float *lat_h, *lat_y, *lat_yn; // [cap_rows][latent]: routed_down x, weighted expert sum, its rmsnorm
     float *sh_a, *sh_u;            // [cap_rows][shared_inter]
     const void **wv, **wsc;        // device tables [(n_experts+1)*3] of tiled values / scales (nullptr = not resident)
@@ -662,9 +665,10 @@ __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, 
 
 static void moe_free_ws(mk_moe *m) {
     void *ptrs[] = {m->logits, m->ids, m->wts, m->xq, m->xs, m->pair_row, m->pair_expert, m->pair_weight,
-                    m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs, m->lat_h, m->lat_y, m->lat_yn, m->sh_a, m->sh_u};
+                    m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs, m->lat_h, m->lat_y, m->lat_yn, m->sh_a, m->sh_u,
+                    m->stk, m->sh_out};
     for (void *p : ptrs) if (p) cudaFree(p);
-    m->lat_h = m->lat_y = m->lat_yn = m->sh_a = m->sh_u = nullptr;
+    m->lat_h = m->lat_y = m->lat_yn = m->sh_a = m->sh_u = m->stk = m->sh_out = nullptr;
     m->logits = nullptr; m->ids = nullptr; m->wts = nullptr; m->xq = nullptr; m->xs = nullptr;
     m->pair_row = m->pair_expert = nullptr; m->pair_weight = nullptr; m->sorted = m->items = m->n_items = nullptr;
     m->actq = nullptr; m->acts = nullptr; m->outs = nullptr;
@@ -705,6 +709,8 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     if (m->sh_gate) {
         MK_CUDA(cudaMalloc(&m->sh_a, (size_t)nr * m->shared_inter * 4));
         MK_CUDA(cudaMalloc(&m->sh_u, (size_t)nr * m->shared_inter * 4));
+        MK_CUDA(cudaMalloc(&m->sh_out, (size_t)nr * m->dx * 4));
+        if (m->latent > 0) MK_CUDA(cudaMalloc(&m->stk, (size_t)(m->latent + 2 * m->shared_inter) * 4));
     }
     // padded tails of the q8 rows must read as zero
     MK_CUDA(cudaMemsetAsync(m->actq, 0, (size_t)np * ldq_i, ctx->stream));
@@ -777,6 +783,7 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
         m->sh_down = (const float *)desc->shared_f32[1]->values;
         m->sh_up = (const float *)desc->shared_f32[2]->values;
         m->shared_inter = si;
+        m->stack3 = latent > 0 && m->sh_gate == m->routed_down + (size_t)latent * dx && m->sh_up == m->sh_gate + (size_t)si * dx;
     }
     m->has_router = desc->gate_w != nullptr;
     m->has_shared = hv[(size_t)E * 3] != nullptr;
@@ -952,6 +959,113 @@ extern "C" int32_t mk_moe_experts_dev(mk_ctx *ctx, mk_moe *m, const float *x, in
     return moe_experts_launch(ctx, m, x, n_rows, pair_row, pair_expert, pair_weight, n_pairs, outs);
 }
 
+// out[t][j] = slot-order sum of the pair rows (as moe_combine_kernel), then rmsnorm over the row (src/model.rs:2346-2356):
+// one CTA per token, the row in shared memory, dot(y, y) in the engine's 8-accumulator order by warp 0.
+__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float *__restrict__ outs, int slots, int d, const float *__restrict__ nw,
+                                                              float eps, float *__restrict__ y_out, float *__restrict__ yn_out) {
+    extern __shared__ float ysm[];
+    __shared__ float s_inv;
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = 0.0f;
+        for (int s = 0; s < slots; ++s) v = __fadd_rn(v, outs[((int64_t)t * slots + s) * d + j]);
+        ysm[j] = v;
+        if (y_out) y_out[(int64_t)t * d + j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x, j8 = lane & 7, full = d & ~7;
+        float acc = 0.0f;
+        for (int c = 0; c < full; c += 8) acc = __fadd_rn(acc, __fmul_rn(ysm[c + j8], ysm[c + j8]));
+        float ss = mkf::reduce8(acc, lane);
+        for (int c = full; c < d; ++c) ss = __fadd_rn(ss, __fmul_rn(ysm[c], ysm[c]));
+        if (lane == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)d), eps)));
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < d; j += blockDim.x) yn_out[(int64_t)t * d + j] = __fmul_rn(__fmul_rn(ysm[j], s_inv), nw[j]);
+}
+__global__ void __launch_bounds__(256) moe_add_rows_kernel(float *__restrict__ out, const float *__restrict__ b, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __fadd_rn(out[i], b[i]);
+}
+
+// One token through a narrow router (d <= 2048): 32 experts per CTA, each row's dot by one lane octet.
+using RtOne = mkf::TileShape<32, 1, 128, 4>;
+
+// The K3 latent layer for one token, as independent chains (see mk_moe_forward_k3_split in mk_common.cuh):
+//   main : [routed_down; shared gate; shared up] x  (one stacked matvec) -> q8 of h -> (router done) gate/up -> down ->
+//          slot-order sum + rmsnorm -> routed_up
+//   side0: router logits, top-k and grouping (needs only x)
+//   side1: SiTU of the shared pair -> shared down (needs the stacked matvec)
+static int32_t moe_k3_decode(mk_ctx *ctx, mk_moe *m, const float *x, float *out_routed, float *out_shared) {
+    const int n = 1, slots = m->top_k;
+    int32_t rc = moe_reserve(ctx, m, n, n * slots);
+    if (rc != MK_OK) return rc;
+    const int si = m->shared_inter, lat = m->latent;
+    float *h = m->stk, *sa = m->stk + lat, *su = sa + si;
+    rc = mk_fork(ctx, 0);
+    if (rc != MK_OK) return rc;
+    {   // side 0: the router
+        mk_on_side on(ctx, 0);
+        RouterFusedArgs ra;
+        ra.gate_w = m->gate_w; ra.gate_b = m->gate_b; ra.x = x; ra.logits = m->logits;
+        ra.score = m->logits + (size_t)m->cap_rows * m->n_experts; ra.key = ra.score + (size_t)m->cap_rows * m->n_experts;
+        ra.n_experts = m->n_experts; ra.d = m->dx; ra.n_tokens = n; ra.top_k = m->top_k; ra.shared_slot = 0;
+        ra.router_kind = m->router_kind; ra.route_scale = m->route_scale;
+        ra.ids = m->ids; ra.wts = m->wts; ra.pair_row = m->pair_row; ra.pair_expert = m->pair_expert; ra.pair_weight = m->pair_weight;
+        ra.wv = m->wv; ra.sorted = m->sorted; ra.items = m->items; ra.n_items = m->n_items; ra.max_items = m->max_items;
+        ra.status = ctx->status_dev; ra.counter = m->counter; ra.xq = m->xq; ra.xs = m->xs; ra.nbp = m->nbp_d;
+        ra.ep_rank = 0; ra.ep_world = 0; ra.n_local = nullptr;
+        size_t smem_f = RtOne::SMEM;
+        if ((size_t)8 * m->n_experts * 4 > smem_f) smem_f = (size_t)8 * m->n_experts * 4;
+        mk_prof_scope prof(ctx, MK_PROF_ROUTER);
+        static mk_once_per_device attr;
+        if (attr.pending(ctx->device)) {
+            MK_CUDA(cudaFuncSetAttribute(moe_router_fused_kernel<RtOne>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            attr.mark(ctx->device);
+        }
+        moe_router_fused_kernel<RtOne><<<(unsigned)mk_ceil_div(m->n_experts, RtOne::NE), 256, smem_f, ctx->stream>>>(ra);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+    }
+    rc = mk_launch_f32_gemv(ctx, m->routed_down, lat + 2 * si, m->dx, x, 1, h, lat + 2 * si, 0);
+    if (rc != MK_OK) return rc;
+    rc = mk_fork(ctx, 1);
+    if (rc != MK_OK) return rc;
+    {   // side 1: the f32 shared expert (src/model.rs:2357-2378)
+        mk_on_side on(ctx, 1);
+        rc = mk_launch_situ(ctx, sa, su, si, sa);
+        if (rc == MK_OK) rc = mk_launch_f32_gemv(ctx, m->sh_down, m->dx, si, sa, 1, out_shared, m->dx, 0);
+        if (rc != MK_OK) return rc;
+    }
+    rc = mk_launch_quantize_act(ctx, h, 1, lat, lat, m->nbp_d, 0, m->xq, m->xs);
+    if (rc != MK_OK) return rc;
+    rc = mk_join(ctx, 0);
+    if (rc != MK_OK) return rc;
+    rc = moe_experts_launch(ctx, m, h, 1, m->pair_row, m->pair_expert, m->pair_weight, slots, m->outs, true, true);
+    if (rc != MK_OK) return rc;
+    {
+        mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
+        moe_combine_norm_kernel<<<1, 256, (size_t)lat * 4, ctx->stream>>>(m->outs, slots, lat, m->routed_norm, m->rms_eps, m->lat_y, m->lat_yn);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+    }
+    rc = mk_launch_f32_gemv(ctx, m->routed_up, m->dx, lat, m->lat_yn, 1, out_routed, m->dx, 0);
+    if (rc != MK_OK) return rc;
+    return mk_join(ctx, 1);
+}
+static bool moe_k3_decode_ok(const mk_ctx *ctx, const mk_moe *m, const float *x, int n) {
+    return n == 1 && m->has_router && m->latent > 0 && m->stack3 && m->sh_gate && !m->has_shared && m->dx % 4 == 0 && m->dx <= 2048 &&
+           m->latent % 4 == 0 && m->shared_inter % 4 == 0 && ((uintptr_t)x & 15) == 0 && (size_t)8 * m->n_experts * 4 <= 200 * 1024 &&
+           !ctx->moe_no_fuse;
+}
+int32_t mk_moe_forward_k3_split(mk_ctx *ctx, mk_moe *m, const float *x, float *out_routed, float *out_shared) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && out_routed != nullptr && out_shared != nullptr, "NULL argument");
+    if (!moe_k3_decode_ok(ctx, m, x, 1)) return MK_ERR_UNSUPPORTED;
+    MK_CUDA(cudaSetDevice(ctx->device));
+    return moe_k3_decode(ctx, m, x, out_routed, out_shared);
+}
+
 static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const float *x, int32_t n, float *out, int32_t *ids, float *weights) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr && x != nullptr && out != nullptr && n > 0, "bad argument");
     MK_CHECK_ARG(m->has_router, "this MoE object was created without a router");
@@ -959,6 +1073,17 @@ static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const flo
     const int slots = m->top_k + (m->has_shared ? 1 : 0);
     int32_t rc = moe_reserve(ctx, m, n, n * slots);
     if (rc != MK_OK) return rc;
+    if (ep == nullptr && moe_k3_decode_ok(ctx, m, x, n)) {
+        // one token of the K3 layer: independent chains on side streams, then out = routed + shared (src/model.rs:2375-2377)
+        rc = moe_k3_decode(ctx, m, x, out, m->sh_out);
+        if (rc != MK_OK) return rc;
+        moe_add_rows_kernel<<<(unsigned)mk_ceil_div(m->dx, 256), 256, 0, ctx->stream>>>(out, m->sh_out, m->dx);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+        if (ids) MK_CUDA(cudaMemcpyAsync(ids, m->ids, (size_t)m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        if (weights) MK_CUDA(cudaMemcpyAsync(weights, m->wts, (size_t)m->top_k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        return MK_OK;
+    }
     // K3 latent MoE: the experts work on h = routed_down x (src/model.rs:2202-2204)
     const float *xe = x;
     if (m->latent > 0) {
