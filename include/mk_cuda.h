@@ -151,6 +151,11 @@ int32_t mk_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out);
  * HOST in / HOST out; bit-identical (DeepSeek spine weights; no BASELINE config runs them). */
 int32_t mk_dequant_fp8(mk_ctx *ctx, const uint8_t *w, const uint8_t *scales, int64_t rows, int64_t cols, float *out);
 
+/* mxfp4::dequant_any (src/mxfp4.rs:228-240) on the GPU: a raw blob of either MXFP4 flavour as it sits in a model file
+ * (MK_DTYPE_MXFP4: packed || scales; MK_DTYPE_MXFP4SQ: packed || scales || smax, scale = ((q + 1) / 256)^2 * smax,
+ * src/mxfp4.rs:140-158) -> f32 [rows, cols].  HOST in / HOST out; bit-identical. */
+int32_t mk_dequant_mxfp4_blob(mk_ctx *ctx, int32_t dtype, const uint8_t *blob, int64_t rows, int64_t cols, float *out);
+
 /* ---- activations ------------------------------------------------------ */
 /* q8::quantize_q8_into (src/q8.rs:49-69) on the GPU, HOST in / HOST out:
  * x f32 [n] (n % 32 == 0) -> q i8 [n], scales f32 [n/32].  Bit-identical. */
@@ -489,6 +494,13 @@ int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *prompt, int32
 int32_t mk_model_layer_hidden(mk_ctx *ctx, mk_model *m, float *out);
 /* The final normed hidden state of the last token (the input of the lm_head), HOST f32 [d]: for parity checks. */
 int32_t mk_model_last_hidden(mk_ctx *ctx, mk_model *m, float *hidden);
+
+/* MlaCache::to_f32 / assign_f32 (src/model.rs:1620-1692): the cache of one sequence as f32 rows to HOST memory, and back
+ * (state snapshots, .mkmem files, src/mkmem.rs:1-61).  PER_HEAD: k [n, H, nope + rope] (dequantized nope part, then the
+ * shared rope row), v [n, H, vd]; ABSORBED: k [n, nope], v ignored.  Import empties the sequence and pushes the rows
+ * again: a cache exported and imported lands on the same q8_0 grid (bytes and scales unchanged). */
+int32_t mk_mla_export_f32(mk_ctx *ctx, const mk_mla *mla, int32_t seq, float *k, float *v);
+int32_t mk_mla_import_f32(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *k, const float *v, int32_t n);
 
 #ifdef __cplusplus
 }

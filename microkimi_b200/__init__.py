@@ -5,8 +5,8 @@ the C ABI in include/mk_cuda.h.  `ops` mirrors the engine's operator interface
 (same names and argument meaning as the Rust functions it stands in for).
 """
 from . import lib  # noqa: F401
-from .ops import (Context, F32Weight, KdaLayer, MlaCache, MoeLayer, MxFp4Weight, Q8Head, Vq1Weight, dequant_fp8, matvec, matvec_packed,  # noqa: F401
+from .ops import (Context, F32Weight, KdaLayer, MlaCache, MoeLayer, MxFp4Weight, Q8Head, Vq1Weight, dequant_any, dequant_fp8, matvec, matvec_packed,  # noqa: F401
                   attn_res, quantize_q8, rmsnorm)
 
-__all__ = ["lib", "Context", "F32Weight", "KdaLayer", "MlaCache", "MoeLayer", "MxFp4Weight", "Q8Head", "Vq1Weight", "dequant_fp8", "matvec", "matvec_packed",
+__all__ = ["lib", "Context", "F32Weight", "KdaLayer", "MlaCache", "MoeLayer", "MxFp4Weight", "Q8Head", "Vq1Weight", "dequant_any", "dequant_fp8", "matvec", "matvec_packed",
            "attn_res", "quantize_q8", "rmsnorm"]

@@ -137,6 +137,35 @@ __global__ void mla_append_rope_kernel(const MlaDev c, int seq, int pos0, int n,
     const int hd = c.nope + c.rope;
     c.krt[((((int64_t)seq * c.T + tile) * c.RC + (r >> 2)) * 32 + p) * 4 + (r & 3)] = k_rows[(int64_t)i * c.H * hd + c.nope + r];
 }
+// MlaCache::to_f32 (src/model.rs:1623-1676, no Hadamard): k [n][H][nope + rope] = (kq as f32) * ks, then the shared rope row;
+// v [n][H][vd] = (vq as f32) * vs.  Absorbed layout: k [n][nope] only.
+__global__ void mla_export_f32_kernel(const MlaDev c, int seq, int n, float *__restrict__ k, float *__restrict__ v) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int hd = c.nope + c.rope;
+    const int64_t nk = (int64_t)n * c.kvh * hd;
+    if (k && idx < nk) {
+        const int e = (int)(idx % hd);
+        const int h = (int)((idx / hd) % c.kvh);
+        const int j = (int)(idx / ((int64_t)hd * c.kvh));
+        const int64_t th = ((int64_t)seq * c.T + (j >> 5)) * c.kvh + h;
+        if (e < c.nope) {
+            const int8_t q = c.kq_tile(th)[((e >> 4) * 32 + (j & 31)) * 16 + (e & 15)];
+            k[idx] = __fmul_rn((float)q, c.ks_tile(th)[(e >> 5) * 32 + (j & 31)]);
+        } else {
+            const int r = e - c.nope;
+            k[idx] = c.krt[((((int64_t)seq * c.T + (j >> 5)) * c.RC + (r >> 2)) * 32 + (j & 31)) * 4 + (r & 3)];
+        }
+    }
+    const int64_t nv = (int64_t)n * c.kvh * c.vd;
+    if (v && idx < nv) {
+        const int e = (int)(idx % c.vd);
+        const int h = (int)((idx / c.vd) % c.kvh);
+        const int j = (int)(idx / ((int64_t)c.vd * c.kvh));
+        const int8_t q = c.recs ? (int8_t)(c.v_row(seq, j, h)[e] ^ (int8_t)0x80) : c.v_row(seq, j, h)[e];
+        v[idx] = __fmul_rn((float)q, c.vs_row(seq, j, h)[e >> 5]);
+    }
+}
+
 // after an append by device position: the sequence holds n more positions (or the status word says it is full)
 __global__ void mla_bump_kernel(int *__restrict__ npos, int seq, int n, int cap, int32_t *__restrict__ status) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -1027,6 +1056,42 @@ extern "C" int32_t mk_mla_attend_batch_dev(mk_ctx *ctx, mk_mla *m, const float *
     }
     MK_CUDA(cudaSetDevice(ctx->device));
     return mla_attend_launch(ctx, m, q, m->nseq, 0, 0, max_n, scale, out);
+}
+
+extern "C" int32_t mk_mla_export_f32(mk_ctx *ctx, const mk_mla *m, int32_t seq, float *k, float *v) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && seq >= 0 && seq < m->nseq, "bad argument");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const int n = m->npos[seq];
+    if (n == 0) return MK_OK;
+    const bool absorbed = m->layout == MK_MLA_ABSORBED;
+    const size_t kb = (size_t)n * m->kvh * (m->nope + m->rope) * 4, vb = absorbed ? 0 : (size_t)n * m->kvh * m->vd * 4;
+    int32_t rc = mk_io_reserve(ctx, mk_align_up(kb, 256) + vb + 256);
+    if (rc != MK_OK) return rc;
+    float *dk = (float *)ctx->io_dev, *dv = (float *)((char *)ctx->io_dev + mk_align_up(kb, 256));
+    const MlaDev c = mla_dev(m);
+    const int64_t total = (int64_t)n * m->kvh * (m->nope + m->rope > m->vd ? m->nope + m->rope : m->vd);
+    mla_export_f32_kernel<<<(unsigned)mk_ceil_div(total, 256), 256, 0, ctx->stream>>>(c, seq, n, k ? dk : nullptr, (v && !absorbed) ? dv : nullptr);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    if (k) MK_CUDA(cudaMemcpyAsync(k, dk, kb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (v && !absorbed) MK_CUDA(cudaMemcpyAsync(v, dv, vb, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+// MlaCache::assign_f32 (src/model.rs:1678-1692): the sequence is emptied and the rows are pushed again (requantized)
+extern "C" int32_t mk_mla_import_f32(mk_ctx *ctx, mk_mla *m, int32_t seq, const float *k, const float *v, int32_t n) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && seq >= 0 && seq < m->nseq && k != nullptr && n >= 0, "bad argument");
+    MK_CHECK_ARG(n <= m->cap, "more positions than the cache holds");
+    int32_t rc = mk_mla_reset(ctx, m, seq);
+    if (rc != MK_OK || n == 0) return rc;
+    const bool absorbed = m->layout == MK_MLA_ABSORBED;
+    const int64_t krow = absorbed ? m->nope : (int64_t)m->H * (m->nope + m->rope), vrow = (int64_t)m->H * m->vd;
+    for (int j0 = 0; j0 < n; j0 += 4096) {      // bounded staging
+        const int nn = n - j0 < 4096 ? n - j0 : 4096;
+        rc = mk_mla_append(ctx, m, seq, k + (int64_t)j0 * krow, absorbed ? nullptr : v + (int64_t)j0 * vrow, nn);
+        if (rc != MK_OK) return rc;
+    }
+    return MK_OK;
 }
 
 // One decode step of one sequence whose launches do not depend on the position: append by the device-side

@@ -323,3 +323,44 @@ extern "C" int32_t mk_quantize_mxfp4_dev(mk_ctx *ctx, const float *w, int64_t ro
     MK_CUDA(cudaGetLastError());
     return MK_OK;
 }
+
+// ---------------------------------------------------------------- mxfp4::dequant_any (src/mxfp4.rs:228-240)
+// A raw blob of either MXFP4 flavour -> f32, HOST in / HOST out: packed || scales for MK_DTYPE_MXFP4, packed || scales ||
+// smax (one trailing f32) for MK_DTYPE_MXFP4SQ, whose scale byte decodes as ((q + 1) / 256)^2 * smax (scale_sq, :153-158).
+namespace {
+__global__ void __launch_bounds__(256) dequant_blob_kernel(const uint8_t *__restrict__ blob, int64_t n, int sq, float *__restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint8_t byte = blob[i >> 1], nib = (i & 1) ? (byte >> 4) : (byte & 0x0F);
+    const uint8_t sb = blob[n / 2 + i / 32];
+    float sc;
+    if (sq) {
+        const uint8_t *sp = blob + n / 2 + n / 32;     // the blob is only byte-aligned
+        const float smax = __uint_as_float((uint32_t)sp[0] | ((uint32_t)sp[1] << 8) | ((uint32_t)sp[2] << 16) | ((uint32_t)sp[3] << 24));
+        const float t = __fmul_rn(__fadd_rn((float)sb, 1.0f), 1.0f / 256.0f);
+        sc = __fmul_rn(__fmul_rn(t, t), smax);
+    } else {
+        sc = mk_e8m0(sb);
+    }
+    out[i] = __fmul_rn(c_e2m1[nib], sc);
+}
+} // namespace
+extern "C" int32_t mk_dequant_mxfp4_blob(mk_ctx *ctx, int32_t dtype, const uint8_t *blob, int64_t rows, int64_t cols, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && blob != nullptr && out != nullptr, "NULL argument");
+    MK_CHECK_ARG(dtype == MK_DTYPE_MXFP4 || dtype == MK_DTYPE_MXFP4SQ, "dtype is not an MXFP4 flavour");
+    MK_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "rows > 0 and cols a positive multiple of 32 required");
+    MK_CUDA(cudaSetDevice(ctx->device));
+    const int64_t n = rows * cols;
+    const size_t bb = (size_t)(n / 2 + n / 32 + (dtype == MK_DTYPE_MXFP4SQ ? 4 : 0)), ob = (size_t)n * 4;
+    int32_t rc = mk_io_reserve(ctx, mk_align_up(bb, 256) + ob);
+    if (rc != MK_OK) return rc;
+    uint8_t *db = (uint8_t *)ctx->io_dev;
+    float *dout = (float *)(db + mk_align_up(bb, 256));
+    MK_CUDA(cudaMemcpyAsync(db, blob, bb, cudaMemcpyHostToDevice, ctx->stream));
+    dequant_blob_kernel<<<grid_for(n, 256), 256, 0, ctx->stream>>>(db, n, dtype == MK_DTYPE_MXFP4SQ ? 1 : 0, dout);
+    ctx->launches++;
+    MK_CUDA(cudaGetLastError());
+    MK_CUDA(cudaMemcpyAsync(out, dout, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}

@@ -96,6 +96,7 @@ SIGNATURES = {
     "mk_weight_export": (_i32, [_vp, _vp, _vp, _vp]),
     "mk_dequant_mxfp4": (_i32, [_vp, _vp, _vp]),
     "mk_quantize_q8": (_i32, [_vp, _vp, _i64, _vp, _vp]),
+    "mk_dequant_mxfp4_blob": (_i32, [_vp, _i32, _vp, _i64, _i64, _vp]),
     "mk_matvec_mxfp4": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_matvec_mxfp4_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32]),
     "mk_gather_create": (_i32, [_vp, _i32, _i32, _i64, _i32, C.POINTER(_vp), _vp]),
@@ -142,6 +143,8 @@ SIGNATURES = {
     "mk_mla_attend": (_i32, [_vp, _vp, _i32, _vp, _i32, C.c_float, _vp]),
     "mk_mla_attend_batch_dev": (_i32, [_vp, _vp, _vp, C.c_float, _vp]),
     "mk_mla_export": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mk_mla_export_f32": (_i32, [_vp, _vp, _i32, _vp, _vp]),
+    "mk_mla_import_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32]),
     "mk_mla_decode_step_dev": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, C.c_float, _vp]),
     "mk_model_config_default": (None, [C.POINTER(ModelConfig)]),
     "mk_bin_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),

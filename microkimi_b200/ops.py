@@ -256,6 +256,19 @@ def dequant_fp8(w, scales, rows, cols, ctx=None):
     return out
 
 
+def dequant_any(dtype, blob, rows, cols, ctx=None):
+    """mxfp4::dequant_any (src/mxfp4.rs:228-240) on the GPU: `blob` is the raw bytes of an "mxfp4" (packed || scales) or
+    "mxfp4sq" (packed || scales || smax) tensor of a model file -> f32 [rows, cols]."""
+    ctx = ctx or Context.default()
+    code = {"mxfp4": 1, "mxfp4sq": 4}[dtype] if isinstance(dtype, str) else int(dtype)
+    b = np.ascontiguousarray(blob, dtype=np.uint8).ravel()
+    need = rows * cols // 2 + rows * cols // 32 + (4 if code == 4 else 0)
+    assert b.size == need, "blob has the wrong size for this dtype and shape"
+    out = np.empty((rows, cols), np.float32)
+    _l.check(ctx._L.mk_dequant_mxfp4_blob(ctx._h, code, _np_ptr(b), rows, cols, _np_ptr(out)))
+    return out
+
+
 def matvec(w, rows, cols, x, ctx=None):
     """Drop-in for model::matvec / metal::gpu_matvec with borrowed host slices."""
     h = F32Weight(w, rows, cols, ctx)
@@ -661,6 +674,30 @@ class MlaCache:
             out["vs"] = np.empty((n, kvh, self.vd // 32), np.float32)
         _l.check(self.ctx._L.mk_mla_export(self.ctx._h, self._h, seq, ptr("kq"), ptr("ks"), ptr("kr"), ptr("vq"), ptr("vs")))
         return out
+
+
+def _mla_to_f32(self, seq=0):
+    """MlaCache::to_f32: (k [n, H, nope + rope], v [n, H, vd]) float32 (absorbed: (k [n, nope], None))."""
+    n = self.positions(seq)
+    if self.layout == "absorbed":
+        k, v = np.empty((n, self.nope), np.float32), None
+    else:
+        k, v = np.empty((n, self.H, self.nope + self.rope), np.float32), np.empty((n, self.H, self.vd), np.float32)
+    _l.check(self.ctx._L.mk_mla_export_f32(self.ctx._h, self._h, seq, _np_ptr(k), _np_ptr(v) if v is not None else None))
+    return k, v
+
+
+def _mla_assign_f32(self, k, v=None, seq=0):
+    """MlaCache::assign_f32: replaces the sequence's contents by f32 rows (requantized on the way in)."""
+    k = np.ascontiguousarray(k, dtype=np.float32)
+    kdim = self.nope if self.layout == "absorbed" else self.H * (self.nope + self.rope)
+    n = k.size // kdim
+    vv = None if self.layout == "absorbed" else np.ascontiguousarray(v, dtype=np.float32)
+    _l.check(self.ctx._L.mk_mla_import_f32(self.ctx._h, self._h, seq, _np_ptr(k), _np_ptr(vv) if vv is not None else None, n))
+
+
+MlaCache.to_f32 = _mla_to_f32
+MlaCache.assign_f32 = _mla_assign_f32
 
 
 def quantize_q8(x, ctx=None):

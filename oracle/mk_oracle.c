@@ -186,6 +186,51 @@ void or_mxfp4_quantize(const float *w, size_t rows, size_t cols, int search, uin
     }
 }
 
+/* ---- MXFP4SQ: quadratic scale byte against a per-tensor smax (mxfp4.rs:140-240) ---- */
+float or_scale_sq(uint8_t q, float smax) { /* :153-158 */
+    float t = ((float)q + 1.0f) * (1.0f / 256.0f);
+    return t * t * smax;
+}
+float or_mxfp4sq_quantize(const float *w, size_t rows, size_t cols, uint8_t *packed, uint8_t *scales) { /* :160-210; returns smax */
+    size_t ng = rows * cols / 32;
+    float *ideal = (float *)malloc(sizeof(float) * ng);
+    float smax = 0.0f;
+    for (size_t gi = 0; gi < ng; ++gi) {
+        float maxabs = 0.0f;
+        for (int j = 0; j < 32; ++j) maxabs = fmaxf(maxabs, fabsf(w[gi * 32 + j]));
+        ideal[gi] = maxabs / 6.0f;
+    }
+    for (size_t gi = 0; gi < ng; ++gi) smax = fmaxf(smax, ideal[gi]);
+    memset(packed, 0, rows * cols / 2);
+    for (size_t gi = 0; gi < ng; ++gi) {
+        uint8_t q = 0;
+        if (!(smax == 0.0f || ideal[gi] == 0.0f)) {
+            int v = (int)ceilf(256.0f * sqrtf(ideal[gi] / smax)) - 1;
+            q = (uint8_t)(v < 0 ? 0 : (v > 255 ? 255 : v));
+        }
+        scales[gi] = q;
+        float inv = 1.0f / or_scale_sq(q, smax);
+        for (int j = 0; j < 32; ++j) {
+            float qv = clampf(w[gi * 32 + j] * inv, -6.0f, 6.0f);
+            float mag = fabsf(qv);
+            int idx = 0;
+            while (idx < 7 && mag >= BOUNDS[idx]) idx++;
+            if (signbit(qv)) idx += 8;
+            size_t c = gi * 32 + j;
+            if (c % 2 == 0) packed[c / 2] |= (uint8_t)idx; else packed[c / 2] |= (uint8_t)(idx << 4);
+        }
+    }
+    free(ideal);
+    return smax;
+}
+void or_mxfp4sq_dequant(const uint8_t *packed, const uint8_t *scales, float smax, size_t rows, size_t cols, float *out) { /* :213-226 */
+    for (size_t i = 0; i < rows * cols; ++i) {
+        uint8_t byte = packed[i / 2];
+        uint8_t nib = (i % 2 == 0) ? (byte & 0x0F) : (byte >> 4);
+        out[i] = E2M1[nib] * or_scale_sq(scales[i / 32], smax);
+    }
+}
+
 /* mxfp4.rs:494-505 (one row of the exact f32 path) */
 static inline float mxfp4_row_f32(const uint8_t *prow, const uint8_t *srow, size_t cols, const float *x) {
     float sum = 0.0f;

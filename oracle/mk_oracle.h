@@ -100,6 +100,11 @@ typedef struct {
 void or_moe_ds_forward(const or_moe_ds_desc *m, const float *x, float *out,
                        int32_t *ids_out /* [top_k], nullable */, float *w_out /* nullable */, int n_threads);
 
+/* ---- MXFP4SQ (src/mxfp4.rs:140-240): the scale byte decodes as ((q + 1) / 256)^2 * smax ---- */
+float or_scale_sq(uint8_t q, float smax);
+float or_mxfp4sq_quantize(const float *w, size_t rows, size_t cols, uint8_t *packed, uint8_t *scales); /* returns smax */
+void  or_mxfp4sq_dequant(const uint8_t *packed, const uint8_t *scales, float smax, size_t rows, size_t cols, float *out);
+
 /* ---- FP8 e4m3fn + ue8m0 (128 x 128 blocks) dequant (dequant.rs:10-41) ---- */
 float or_e4m3_to_f32(uint8_t b);
 void or_dequant_fp8(const uint8_t *w, const uint8_t *scales, size_t rows, size_t cols, float *out);

@@ -125,6 +125,8 @@ def _declare(L):
     sig("or_mla_abs_attn_f64", None, C.c_void_p, _f32p, _sz, _sz, C.c_float, _f64p)
     sig("or_set_num_threads", None, C.c_int)
     sig("or_set_cr_math", None, C.c_int)
+    sig("or_mxfp4sq_quantize", C.c_float, _f32p, _sz, _sz, _u8p, _u8p)
+    sig("or_mxfp4sq_dequant", None, _u8p, _u8p, C.c_float, _sz, _sz, _f32p)
     sig("or_config_microkimi", None, C.c_void_p)
     sig("or_config_is_mla", C.c_int, C.c_void_p, C.c_uint32)
     sig("or_config_is_moe", C.c_int, C.c_void_p, C.c_uint32)
@@ -315,6 +317,23 @@ def mxfp4_quantize(w, search=True):
     scales = np.empty((rows, cols // 32), np.uint8)
     lib().or_mxfp4_quantize(_p(w, _f32p), rows, cols, int(search), _p(packed, _u8p), _p(scales, _u8p))
     return packed, scales
+
+
+def mxfp4sq_quantize(w):
+    """mxfp4::quantize_sq: (packed, scales, smax)."""
+    w = _c(w, np.float32)
+    rows, cols = w.shape
+    packed = np.empty((rows, cols // 2), np.uint8)
+    scales = np.empty((rows, cols // 32), np.uint8)
+    smax = lib().or_mxfp4sq_quantize(_p(w, _f32p), rows, cols, _p(packed, _u8p), _p(scales, _u8p))
+    return packed, scales, np.float32(smax)
+
+
+def mxfp4sq_dequant(packed, scales, smax, rows, cols):
+    packed, scales = _c(packed, np.uint8), _c(scales, np.uint8)
+    out = np.empty((rows, cols), np.float32)
+    lib().or_mxfp4sq_dequant(_p(packed, _u8p), _p(scales, _u8p), float(smax), rows, cols, _p(out, _f32p))
+    return out
 
 
 def mxfp4_matvec(packed, scales, x, use_q8, n_threads=1):

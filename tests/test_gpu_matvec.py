@@ -344,3 +344,19 @@ def test_device_calls_replay_from_a_cuda_graph(mk):
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(got, want))
     assert ctx.status_word() == 0
+
+
+def test_dequant_any_both_mxfp4_flavours(mk):
+    """mxfp4::dequant_any (src/mxfp4.rs:228-240): raw blobs as a model file holds them, bit-exact on the GPU."""
+    rng = np.random.default_rng(31)
+    rows, cols = 40, 256
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    w[2, 32:64] = 0.0
+    p, s = O.mxfp4_quantize(w)
+    blob = np.concatenate([p.ravel(), s.ravel()])
+    assert np.array_equal(bits(mk.dequant_any("mxfp4", blob, rows, cols)), bits(O.mxfp4_dequant(p, s, rows, cols)))
+    p2, s2, smax = O.mxfp4sq_quantize(w)
+    blob2 = np.concatenate([p2.ravel(), s2.ravel(), np.array([smax], np.float32).view(np.uint8)])
+    assert np.array_equal(bits(mk.dequant_any("mxfp4sq", blob2, rows, cols)), bits(O.mxfp4sq_dequant(p2, s2, smax, rows, cols)))
+    with pytest.raises(AssertionError):
+        mk.dequant_any("mxfp4sq", blob, rows, cols)          # the trailing smax is missing

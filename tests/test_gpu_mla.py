@@ -227,3 +227,42 @@ def test_cache_errors_are_statuses(mk):
     assert e.value.code == -1
     with pytest.raises(mk.lib.MkError):
         mk.MlaCache(4, 100, 64, 128, 2)      # nope not a multiple of 32
+
+
+def test_f32_snapshot_roundtrip_lands_on_the_same_grid(mk):
+    """MlaCache::to_f32 / assign_f32 (src/model.rs:1620-1692): the f32 export equals the CPU's dequantized cache bit for
+    bit, and a cache restored from it holds the same q8_0 bytes and scales (the property .mkmem snapshots rely on)."""
+    rng = np.random.default_rng(21)
+    nh, nope, rope, vd, n = 4, 128, 64, 128, 75
+    K = rng.standard_normal((n, nh, nope + rope)).astype(np.float32)
+    K[:, 1:, nope:] = K[:, :1, nope:]
+    V = rng.standard_normal((n, nh, vd)).astype(np.float32)
+    V[5, 2, :32] = 0.0
+    ref = O.MlaCache(nh, nope, rope, vd, n)
+    for j in range(n):
+        ref.push(K[j].reshape(-1), V[j].reshape(-1))
+    dev = mk.MlaCache(nh, nope, rope, vd, 128)
+    dev.push(K, V)
+    k32, v32 = dev.to_f32()
+    k_ref, v_ref = ref.to_f32()
+    assert np.array_equal(bits(k32), bits(k_ref.reshape(n, nh, nope + rope))) and np.array_equal(bits(v32), bits(v_ref.reshape(n, nh, vd)))
+    before = dev.export()
+    other = mk.MlaCache(nh, nope, rope, vd, 128)
+    other.push(K[:3], V[:3])                      # contents that the import must replace
+    other.assign_f32(k32, v32)
+    assert other.positions() == n
+    after = other.export()
+    for key in ("kq", "ks", "kr", "vq", "vs"):
+        assert np.array_equal(before[key].view(np.uint8), after[key].view(np.uint8)), key
+    q = rng.standard_normal((nh, nope + rope)).astype(np.float32)
+    sc = np.float32(1.0 / np.sqrt(192.0))
+    assert np.array_equal(bits(other.mla_attn_flash_q8_mqa(q, n - 1, sc)), bits(dev.mla_attn_flash_q8_mqa(q, n - 1, sc)))
+    # absorbed layout
+    rows = rng.standard_normal((40, 576)).astype(np.float32)
+    a = mk.MlaCache(8, 576, 0, 512, 64, layout="absorbed")
+    a.push(rows)
+    ka, _ = a.to_f32()
+    b = mk.MlaCache(8, 576, 0, 512, 64, layout="absorbed")
+    b.assign_f32(ka)
+    ea, eb = a.export(), b.export()
+    assert np.array_equal(ea["kq"], eb["kq"]) and np.array_equal(bits(ea["ks"]), bits(eb["ks"]))

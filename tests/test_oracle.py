@@ -517,3 +517,25 @@ def test_kda_step_is_conv_norm_gate_recurrence_onorm():
         assert np.abs(got - want.reshape(-1)).max() <= 2e-5 * max(1.0, np.abs(want).max())
         assert np.abs(layer.s - S).max() <= 2e-5 * max(1.0, np.abs(S).max())
         assert np.array_equal(layer.conv[0], win[0].astype(np.float32))
+
+
+def test_mxfp4sq_quadratic_scale_roundtrip():
+    """MXFP4SQ (src/mxfp4.rs:140-226): the scale byte is rounded UP on the quadratic grid, so no value clips and every
+    dequantized value is a level times scale_sq; an all-zero tensor keeps smax 0 and decodes to zeros."""
+    rng = np.random.default_rng(12)
+    w = (rng.standard_normal((24, 128)) * 0.02).astype(np.float32)
+    w[3, :32] = 0.0
+    p, s, smax = O.mxfp4sq_quantize(w)
+    assert smax == np.float32(np.abs(w).reshape(-1, 32).max(axis=1).max() / np.float32(6.0))
+    d = O.mxfp4sq_dequant(p, s, smax, 24, 128)
+    t = (s.astype(np.float32) + np.float32(1.0)) * np.float32(1.0 / 256.0)
+    scale = (t * t * smax).astype(np.float32)
+    ideal = (np.abs(w).reshape(24, 4, 32).max(axis=2) / np.float32(6.0)).astype(np.float32)
+    assert np.all(scale[ideal > 0] >= ideal[ideal > 0])                       # never clips
+    levels = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float32)
+    ratio = np.abs(d.reshape(24, 4, 32)) / scale[:, :, None]
+    assert np.all(np.isin(np.round(ratio * 2) / 2, levels))
+    assert np.abs(d - w).max() <= 0.51 * scale.max() * 2                        # within one level step of the largest scale
+    z = np.zeros((2, 64), np.float32)
+    pz, sz, smz = O.mxfp4sq_quantize(z)
+    assert smz == 0 and np.all(O.mxfp4sq_dequant(pz, sz, smz, 2, 64) == 0)
