@@ -53,6 +53,11 @@ typedef struct mk_mla    mk_mla;
  *               (src/mxfp4.rs:488-539) at the same memory traffic. */
 #define MK_ACT_Q8    0
 #define MK_ACT_Q8X2  1
+/* MoE layer only (mk_moe_desc.act_mode): calls of 32 or more token rows run the experts as block-scaled tensor-core
+ * products (tcgen05.mma kind::mxf8f6f4): E2M1 weights with their ue8m0 scales as registered, the activations as three
+ * E4M3 limbs with power-of-two block scales (12 significant bits per element).  Results track the engine's exact-f32
+ * path (src/mxfp4.rs:488-539) to ~1e-5 of max |y|; smaller calls run MK_ACT_Q8. */
+#define MK_ACT_E4M3X3 2
 /* OR into act_mode: accumulate the per-block terms of every output strictly in
  * ascending block order with separate multiply and add, reproducing the CPU
  * result of src/mxfp4.rs:409-418 / src/model.rs:337-347 bit for bit (slower). */
@@ -310,7 +315,7 @@ typedef struct {
     const mk_weight *routed_up;      /* f32 [d, latent] */
     const float *routed_norm;        /* HOST f32 [latent] */
     const mk_weight *shared_f32[3];  /* f32 shared expert: gate [si, d], down [d, si], up [si, d]; all NULL = none */
-    int32_t act_mode;                /* MK_ACT_Q8 (0), or MK_ACT_Q8 | MK_ACT_STRICT: the expert matvecs add their block terms in the
+    int32_t act_mode;                /* MK_ACT_Q8 (0); MK_ACT_E4M3X3 (see above); or MK_ACT_Q8 | MK_ACT_STRICT: the expert matvecs add their block terms in the
                                         CPU's order (src/mxfp4.rs:409-418), so no q8 rounding of an activation can differ from the
                                         CPU's; slower on wide experts (no K split) */
 } mk_moe_desc;

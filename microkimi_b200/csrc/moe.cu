@@ -23,6 +23,8 @@ struct mk_moe {
     float route_scale;
     float limit;
     bool has_router, has_shared;
+    bool tc;                       // MK_ACT_E4M3X3: calls of >= 32 rows run the experts on the block-scaled tcgen05 path
+    uint8_t *xl, *xsf, *actl, *actsf;   // its activation limbs: tokens [3][rows][d] + scales, expert activations [3][pairs][inter] + scales
     bool strict;                   // MK_ACT_STRICT: expert sums in the CPU's order (one accumulator, ascending blocks, no K split)
     float *gate_w, *gate_b;        // device
     // K3 latent MoE (src/model.rs:2202-2380); the f32 matrices belong to the caller's handles
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots /* n_experts + 1 */,
                 const void *const *__restrict__ wv, int32_t *__restrict__ sorted, int32_t *__restrict__ items,
-                int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status) {
+                int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status, int chunk /* pairs per work item: 8, or 32 */) {
     extern __shared__ int sh[];
     int *cnt = sh, *off = sh + n_slots, *ioff = off + n_slots, *cur = ioff + n_slots;
     for (int e = threadIdx.x; e < n_slots; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
@@ -367,7 +369,7 @@ moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slot
             off[e] = o;
             ioff[e] = io;
             o += cnt[e];
-            io += (cnt[e] + 7) >> 3;
+            io += (cnt[e] + chunk - 1) / chunk;
         }
         *n_items = io < max_items ? io : max_items;
         if (io > max_items) atomicCAS(status, 0, MK_ERR_STATE);
@@ -379,13 +381,13 @@ moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slot
         sorted[off[e] + atomicAdd(&cur[e], 1)] = p;
     }
     for (int e = threadIdx.x; e < n_slots; e += blockDim.x) {
-        const int nch = (cnt[e] + 7) >> 3;
+        const int nch = (cnt[e] + chunk - 1) / chunk;
         for (int c = 0; c < nch; ++c) {
             const int it = ioff[e] + c;
             if (it < max_items) {
                 items[it * 3 + 0] = e;
-                items[it * 3 + 1] = off[e] + c * 8;
-                items[it * 3 + 2] = min(8, cnt[e] - c * 8);
+                items[it * 3 + 1] = off[e] + c * chunk;
+                items[it * 3 + 2] = min(chunk, cnt[e] - c * chunk);
             }
         }
     }
@@ -414,6 +416,10 @@ struct MoeArgs {
     float limit;
     Consts k;
 };
+
+} // namespace
+#include "moe_tc.cuh"
+namespace {
 
 // Partial sums of one warp for a 16-row tile and up to 8 columns, into smem part[16][8].
 // SPREAD: items of <= 2 columns (or, without BATCHED, any item by repeated passes) take the
@@ -666,8 +672,9 @@ __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, 
 static void moe_free_ws(mk_moe *m) {
     void *ptrs[] = {m->logits, m->ids, m->wts, m->xq, m->xs, m->pair_row, m->pair_expert, m->pair_weight,
                     m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs, m->lat_h, m->lat_y, m->lat_yn, m->sh_a, m->sh_u,
-                    m->stk, m->sh_out};
+                    m->stk, m->sh_out, m->xl, m->xsf, m->actl, m->actsf};
     for (void *p : ptrs) if (p) cudaFree(p);
+    m->xl = m->xsf = m->actl = m->actsf = nullptr;
     m->lat_h = m->lat_y = m->lat_yn = m->sh_a = m->sh_u = m->stk = m->sh_out = nullptr;
     m->logits = nullptr; m->ids = nullptr; m->wts = nullptr; m->xq = nullptr; m->xs = nullptr;
     m->pair_row = m->pair_expert = nullptr; m->pair_weight = nullptr; m->sorted = m->items = m->n_items = nullptr;
@@ -712,6 +719,12 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
         MK_CUDA(cudaMalloc(&m->sh_out, (size_t)nr * m->dx * 4));
         if (m->latent > 0) MK_CUDA(cudaMalloc(&m->stk, (size_t)(m->latent + 2 * m->shared_inter) * 4));
     }
+    if (m->tc) {
+        MK_CUDA(cudaMalloc(&m->xl, (size_t)3 * nr * m->d));
+        MK_CUDA(cudaMalloc(&m->xsf, (size_t)3 * nr * (m->d / 32)));
+        MK_CUDA(cudaMalloc(&m->actl, (size_t)3 * np * m->inter));
+        MK_CUDA(cudaMalloc(&m->actsf, (size_t)3 * np * (m->inter / 32)));
+    }
     // padded tails of the q8 rows must read as zero
     MK_CUDA(cudaMemsetAsync(m->actq, 0, (size_t)np * ldq_i, ctx->stream));
     MK_CUDA(cudaMemsetAsync(m->acts, 0, (size_t)np * m->nbp_i * 4, ctx->stream));
@@ -730,7 +743,8 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     MK_CHECK_ARG(desc->activation == MK_MOE_SWIGLU_CLAMP || desc->activation == MK_MOE_SITU, "unknown activation");
     MK_CHECK_ARG(desc->router == MK_ROUTER_SIGMOID || desc->router == MK_ROUTER_SQRT_SOFTPLUS, "unknown router kind");
     MK_CHECK_ARG(desc->experts != nullptr, "experts table is NULL");
-    MK_CHECK_ARG((desc->act_mode & ~MK_ACT_STRICT) == MK_ACT_Q8, "the MoE layer takes MK_ACT_Q8, optionally with MK_ACT_STRICT");
+    MK_CHECK_ARG((desc->act_mode & ~MK_ACT_STRICT) == MK_ACT_Q8 || desc->act_mode == MK_ACT_E4M3X3,
+                 "the MoE layer takes MK_ACT_Q8 (optionally with MK_ACT_STRICT) or MK_ACT_E4M3X3");
     const bool situ = desc->activation == MK_MOE_SITU;
     auto f32ok = [](const mk_weight *w, int rows, int cols) { return w && w->fmt == MK_FMT_F32 && w->rows == rows && w->cols == cols; };
     if (latent != 0) {
@@ -777,6 +791,7 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     m->latent = latent > 0 ? latent : 0;
     m->rms_eps = desc->rms_eps;
     m->strict = (desc->act_mode & MK_ACT_STRICT) != 0;
+    m->tc = desc->act_mode == MK_ACT_E4M3X3;
     if (latent > 0) { m->routed_down = (const float *)desc->routed_down->values; m->routed_up = (const float *)desc->routed_up->values; }
     if (sh32) {
         m->sh_gate = (const float *)desc->shared_f32[0]->values;
@@ -880,6 +895,33 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
                                   const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs,
                                   bool prepared = false, bool quantized = false) {
     // prepared: the fused router kernel has already grouped the pairs; quantized: and quantized x
+    const bool use_tc = m->tc && !prepared && n_rows >= mtc::NT && m->d % 128 == 0 && m->inter % 128 == 0;
+    if (use_tc) {
+        // many rows: the experts as block-scaled tensor-core products (moe_tc.cuh); work items of up to 32 pairs
+        mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
+        const int slots = m->n_experts + 1;
+        mtc::act_limbs_kernel<<<(unsigned)mk_ceil_div((int64_t)n_rows * (m->d / 32) * 32, 256), 256, 0, ctx->stream>>>(x, n_rows, m->d, m->d, m->xl, m->xsf);
+        moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted, m->items,
+                                                                                  m->n_items, m->max_items, ctx->status_dev, mtc::NT);
+        mtc::TcArgs t;
+        t.wv = m->wv; t.wsc = m->wsc; t.items = m->items; t.n_items = m->n_items; t.sorted = m->sorted; t.pair_row = pair_row;
+        t.pair_weight = pair_weight; t.xl = m->xl; t.xsf = m->xsf; t.actl = m->actl; t.actsf = m->actsf; t.outs = outs;
+        t.rows = n_rows; t.pairs = m->cap_pairs; t.d = m->d; t.inter = m->inter; t.nbp_d = m->nbp_d; t.nbp_i = m->nbp_i;
+        t.activation = m->activation; t.limit = m->limit; t.status = ctx->status_dev;
+        int items_ub = n_pairs / mtc::NT + (n_pairs < slots ? n_pairs : slots);
+        if (items_ub > m->max_items) items_ub = m->max_items;
+        static mk_once_per_device attr;
+        if (attr.pending(ctx->device)) {
+            MK_CUDA(cudaFuncSetAttribute(mtc::moe_tc_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mtc::SM_TOTAL));
+            MK_CUDA(cudaFuncSetAttribute(mtc::moe_tc_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mtc::SM_TOTAL));
+            attr.mark(ctx->device);
+        }
+        mtc::moe_tc_gate_up_kernel<<<dim3((unsigned)(m->inter / 128), (unsigned)items_ub), mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
+        mtc::moe_tc_down_kernel<<<dim3((unsigned)mk_ceil_div(m->d / 128, 2), (unsigned)items_ub), mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
+        ctx->launches += 4;
+        MK_CUDA(cudaGetLastError());
+        return MK_OK;
+    }
     if (!quantized) {
         int32_t rc = mk_launch_quantize_act(ctx, x, n_rows, m->d, m->d, m->nbp_d, 0, m->xq, m->xs);
         if (rc != MK_OK) return rc;
@@ -888,7 +930,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     const int slots = m->n_experts + 1;
     if (!prepared) {
         moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted,
-                                                                                  m->items, m->n_items, m->max_items, ctx->status_dev);
+                                                                                  m->items, m->n_items, m->max_items, ctx->status_dev, 8);
         ctx->launches++;
     }
     MoeArgs a;

@@ -464,7 +464,7 @@ class MoeLayer:
 
     def __init__(self, gate_w, gate_b, experts, shared, top_k, swiglu_limit=10.0, ctx=None, router="sigmoid",
                  route_scale=1.0, activation="swiglu_clamp", routed_down=None, routed_up=None, routed_norm=None,
-                 rms_eps=1e-6, shared_f32=None, strict=False):
+                 rms_eps=1e-6, shared_f32=None, strict=False, act="q8"):
         ctx = ctx or Context.default()
         self.ctx = ctx
         self.n_experts = len(experts)
@@ -484,7 +484,8 @@ class MoeLayer:
         desc.activation = {"swiglu_clamp": _l.MK_MOE_SWIGLU_CLAMP, "situ": _l.MK_MOE_SITU}[activation]
         desc.router = {"sigmoid": _l.MK_ROUTER_SIGMOID, "sqrt_softplus": _l.MK_ROUTER_SQRT_SOFTPLUS}[router]
         desc.route_scale, desc.rms_eps = float(route_scale), float(rms_eps)
-        desc.act_mode = _l.MK_ACT_Q8 | (_l.MK_ACT_STRICT if strict else 0)
+        # act="e4m3x3": calls of >= 32 rows run the experts on the block-scaled tcgen05 path (three E4M3 limbs per activation)
+        desc.act_mode = _l.MK_ACT_E4M3X3 if act == "e4m3x3" else (_l.MK_ACT_Q8 | (_l.MK_ACT_STRICT if strict else 0))
         if routed_down is not None:
             rn = np.ascontiguousarray(routed_norm, dtype=np.float32)
             assert rn.size == self.d, "routed_norm must hold one weight per latent column"
