@@ -258,7 +258,7 @@ def measure_mxfp4_gemv(torch, mk, ctx, dev, rows=7168, cols=2048, batch=1, copie
     return out
 
 
-def build_moe_layers(torch, mk, ctx, dev, experts, copies, seed=3):
+def build_moe_layers(torch, mk, ctx, dev, experts, copies, seed=3, act="q8"):
     E, k, d, inter = experts, 8, 7168, 2048
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)
@@ -267,8 +267,13 @@ def build_moe_layers(torch, mk, ctx, dev, experts, copies, seed=3):
         ex = [tuple(_rand_mxfp4(torch, mk, ctx, gen, dev, r, c) for r, c in ((inter, d), (d, inter), (inter, d)))
               for _ in range(E + 1)]
         gw = (torch.randn((E, d), generator=gen, device=dev) * 0.02).cpu().numpy()
-        layers.append(mk.MoeLayer(gw, None, ex[:-1], ex[-1], k, ctx=ctx))
+        layers.append(mk.MoeLayer(gw, None, ex[:-1], ex[-1], k, ctx=ctx, act=act))
     return layers, gen
+
+
+def tc_twins(mk, ctx, layers):
+    """The same layers (same registered weights) with the experts of large calls on the block-scaled tcgen05 path."""
+    return [mk.MoeLayer(l._gate_w, None, l._keep[0], l._keep[1], l.top_k, ctx=ctx, act="e4m3x3") for l in layers]
 
 
 def free_moe_layers(layers):
@@ -471,8 +476,14 @@ def extras_single_gpu(torch, mk, ctx, dev, heads, x1):
     def moe():
         layers, gen = build_moe_layers(torch, mk, ctx, dev, 384, 2)
         try:
-            return {f"batch{b}": measure_moe(torch, mk, ctx, dev, layers, gen, b, st, 3, graph=(b == 1))
-                    for b, st in ((1, 40), (16, 20), (256, 6))}
+            res = {f"batch{b}": measure_moe(torch, mk, ctx, dev, layers, gen, b, st, 3, graph=(b == 1))
+                   for b, st in ((1, 40), (16, 20), (256, 6))}
+            twins = tc_twins(mk, ctx, layers)
+            res["batch256_tcgen05_block_scaled"] = measure_moe(torch, mk, ctx, dev, twins, gen, 256, 6, 3)
+            res["batch256_tcgen05_block_scaled"]["act_mode"] = "e4m3x3: E2M1 weights + ue8m0 scales as registered, activations as three E4M3 limbs"
+            for t in twins:
+                t.free()
+            return res
         finally:
             free_moe_layers(layers)
     guard("config3_moe_layer", moe)
@@ -811,8 +822,8 @@ def run_case_mxfp4(args):
 
 def run_case_moe(args):
     torch, mk, ctx, dev = _side_ctx()
-    layers, gen = build_moe_layers(torch, mk, ctx, dev, args.experts, args.copies)
-    print(json.dumps({"case": "moe", **measure_moe(torch, mk, ctx, dev, layers, gen, args.batch, args.steps, args.warmup, args.graph)}),
+    layers, gen = build_moe_layers(torch, mk, ctx, dev, args.experts, args.copies, act=args.moe_act)
+    print(json.dumps({"case": "moe", "act": args.moe_act, **measure_moe(torch, mk, ctx, dev, layers, gen, args.batch, args.steps, args.warmup, args.graph)}),
           flush=True)
 
 
@@ -905,6 +916,7 @@ def main():
     ap.add_argument("--copies", type=int, default=1)
     ap.add_argument("--act", default="q8", choices=["q8", "q8x2"])
     ap.add_argument("--experts", type=int, default=384)
+    ap.add_argument("--moe-act", default="q8", choices=["q8", "e4m3x3"], help="--case moe: e4m3x3 = block-scaled tcgen05 experts for calls of >= 32 rows")
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=4, help="--case kda: KDA heads of width 128")
     ap.add_argument("--kda-smem", action="store_true", help="--case kda: the shared-memory form of the step kernel (default at width 128: registers)")

@@ -493,6 +493,7 @@ class MoeLayer:
             desc.routed_down, desc.routed_up, desc.routed_norm = routed_down._h, routed_up._h, _np_ptr(rn)
         for j in range(3):
             desc.shared_f32[j] = shared_f32[j]._h if shared_f32 is not None else None
+        self._gate_w = gate_w
         if gate_w is not None:
             gw = np.ascontiguousarray(gate_w, dtype=np.float32)
             assert gw.shape == (self.n_experts, self.dx)
