@@ -11,6 +11,8 @@
 // list), plan (group pairs by expert), gate/up (+ activation + q8 of the
 // activation), down, combine.  Up to 16 tokens the first four are ONE launch
 // (moe_router_fused_kernel), 4 launches per layer call in all.
+#include <cuda.h>
+
 #include "qgemv_core.cuh"
 #include "f32gemv.cuh"
 
@@ -24,6 +26,7 @@ struct mk_moe {
     float limit;
     bool has_router, has_shared;
     bool tc;                       // MK_ACT_E4M3X3: calls of >= 32 rows run the experts on the block-scaled tcgen05 path
+    void *tmaps;                   // device [(n_experts+1)*3][2] tensor maps of the registered weights (codes, scales) for that path
     uint8_t *xl, *xsf, *actl, *actsf;   // its activation limbs: tokens [3][rows][d] + scales, expert activations [3][pairs][inter] + scales
     bool strict;                   // MK_ACT_STRICT: expert sums in the CPU's order (one accumulator, ascending blocks, no K split)
     float *gate_w, *gate_b;        // device
@@ -352,7 +355,7 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots /* n_experts + 1 */,
                 const void *const *__restrict__ wv, int32_t *__restrict__ sorted, int32_t *__restrict__ items,
-                int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status, int chunk /* pairs per work item: 8, or 32 */) {
+                int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status, int chunk /* pairs per work item: 8, or 16 */) {
     extern __shared__ int sh[];
     int *cnt = sh, *off = sh + n_slots, *ioff = off + n_slots, *cur = ioff + n_slots;
     for (int e = threadIdx.x; e < n_slots; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
@@ -733,6 +736,24 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     return MK_OK;
 }
 
+// A 2-D tensor map of 32-bit words: `words` per row (contiguous), `rows` rows, box = box_w x box_h, no swizzle; elements
+// outside the tensor read as zero.  The driver entry point is looked up at run time (no link against libcuda).
+static bool moe_encode_tiled(CUtensorMap *map, const void *base, uint64_t words, uint64_t rows, uint32_t box_w, uint32_t box_h) {
+    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess || !fn) return false;
+        encode = (encode_fn)fn;
+    }
+    const cuuint64_t dims[2] = {words, rows}, strides[1] = {words * 4};
+    const cuuint32_t box[2] = {box_w, box_h}, estr[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out) {
     MK_CHECK_ARG(ctx != nullptr && desc != nullptr && out != nullptr, "NULL argument");
     *out = nullptr;
@@ -823,6 +844,26 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
         e_ = cudaMalloc(&m->routed_norm, (size_t)latent * 4);
         if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->routed_norm, desc->routed_norm, (size_t)latent * 4, cudaMemcpyHostToDevice, ctx->stream);
     }
+    if (e_ == cudaSuccess && m->tc && d % 128 == 0 && I % 128 == 0) {
+        // tensor maps over the tiled layouts (src of the TMA boxes of moe_tc.cuh): per matrix a [row tiles][words] view of the
+        // codes (512-byte chunk per 16 rows x 2 blocks, nbp / 2 chunks per row tile) and of the scales (16 bytes per row tile
+        // and block)
+        std::vector<CUtensorMap> maps(hv.size() * 2);
+        memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
+        for (size_t i = 0; i < hv.size() && e_ == cudaSuccess; ++i) {
+            if (!hv[i]) continue;
+            const bool down = i % 3 == 1;
+            const int64_t rows = down ? d : I, nbp = down ? m->nbp_i : m->nbp_d;
+            if (!moe_encode_tiled(&maps[i * 2], hv[i], (uint64_t)(nbp / 2) * 128, (uint64_t)(rows / 16), 256, 8) ||
+                !moe_encode_tiled(&maps[i * 2 + 1], hs[i], (uint64_t)nbp * 4, (uint64_t)(rows / 16), 16, 8)) {
+                mk_set_error("mk_moe_create: cuTensorMapEncodeTiled failed");
+                mk_moe_free(ctx, m);
+                return MK_ERR_CUDA;
+            }
+        }
+        e_ = cudaMalloc(&m->tmaps, maps.size() * sizeof(CUtensorMap));
+        if (e_ == cudaSuccess) e_ = cudaMemcpy(m->tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    }
     if (e_ == cudaSuccess) e_ = cudaMalloc(&m->counter, 4);
     if (e_ == cudaSuccess) e_ = cudaMemsetAsync(m->counter, 0, 4, ctx->stream);
     if (e_ == cudaSuccess) e_ = cudaStreamSynchronize(ctx->stream);
@@ -842,6 +883,7 @@ extern "C" int32_t mk_moe_free(mk_ctx *ctx, mk_moe *m) {
     moe_free_ws(m);
     if (m->wv) cudaFree((void *)m->wv);
     if (m->wsc) cudaFree((void *)m->wsc);
+    if (m->tmaps) cudaFree(m->tmaps);
     if (m->gate_w) cudaFree(m->gate_w);
     if (m->gate_b) cudaFree(m->gate_b);
     if (m->counter) cudaFree(m->counter);
@@ -895,7 +937,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
                                   const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs,
                                   bool prepared = false, bool quantized = false) {
     // prepared: the fused router kernel has already grouped the pairs; quantized: and quantized x
-    const bool use_tc = m->tc && !prepared && n_rows >= mtc::NT && m->d % 128 == 0 && m->inter % 128 == 0;
+    const bool use_tc = m->tc && m->tmaps && !prepared && n_rows >= 32 && m->d % 128 == 0 && m->inter % 128 == 0;
     if (use_tc) {
         // many rows: the experts as block-scaled tensor-core products (moe_tc.cuh); work items of up to 32 pairs
         mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
@@ -904,20 +946,19 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
         moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted, m->items,
                                                                                   m->n_items, m->max_items, ctx->status_dev, mtc::NT);
         mtc::TcArgs t;
-        t.wv = m->wv; t.wsc = m->wsc; t.items = m->items; t.n_items = m->n_items; t.sorted = m->sorted; t.pair_row = pair_row;
+        t.maps = (const unsigned char *)m->tmaps; t.items = m->items; t.n_items = m->n_items; t.sorted = m->sorted; t.pair_row = pair_row;
         t.pair_weight = pair_weight; t.xl = m->xl; t.xsf = m->xsf; t.actl = m->actl; t.actsf = m->actsf; t.outs = outs;
-        t.rows = n_rows; t.pairs = m->cap_pairs; t.d = m->d; t.inter = m->inter; t.nbp_d = m->nbp_d; t.nbp_i = m->nbp_i;
+        t.rows = n_rows; t.pairs = m->cap_pairs; t.d = m->d; t.inter = m->inter;
         t.activation = m->activation; t.limit = m->limit; t.status = ctx->status_dev;
-        int items_ub = n_pairs / mtc::NT + (n_pairs < slots ? n_pairs : slots);
-        if (items_ub > m->max_items) items_ub = m->max_items;
         static mk_once_per_device attr;
         if (attr.pending(ctx->device)) {
-            MK_CUDA(cudaFuncSetAttribute(mtc::moe_tc_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mtc::SM_TOTAL));
-            MK_CUDA(cudaFuncSetAttribute(mtc::moe_tc_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mtc::SM_TOTAL));
+            MK_CUDA(cudaFuncSetAttribute(mtc::moe_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mtc::SM_TOTAL));
+            MK_CUDA(cudaFuncSetAttribute(mtc::moe_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, mtc::SM_TOTAL));
             attr.mark(ctx->device);
         }
-        mtc::moe_tc_gate_up_kernel<<<dim3((unsigned)(m->inter / 128), (unsigned)items_ub), mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
-        mtc::moe_tc_down_kernel<<<dim3((unsigned)mk_ceil_div(m->d / 128, 2), (unsigned)items_ub), mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
+        // persistent CTAs, one per SM; the work units are dealt round-robin inside the kernels
+        mtc::moe_tc_kernel<false><<<(unsigned)ctx->sm_count, mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
+        mtc::moe_tc_kernel<true><<<(unsigned)ctx->sm_count, mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
         ctx->launches += 4;
         MK_CUDA(cudaGetLastError());
         return MK_OK;

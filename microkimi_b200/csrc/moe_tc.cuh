@@ -4,23 +4,31 @@
 // matvecs are a real contraction.  Swap-AB: 128 weight rows are the M dimension, an expert's tokens the N dimension.
 //   A : the E2M1 codes exactly as the registered weight holds them - no decode.  In shared memory a 16-byte chunk carries
 //       16 codes in its low 8 bytes (the tensor core's FP4 operand form: 8 data + 8 padding bytes), rows of 128 bytes
-//       (128 codes) in the 128-byte-swizzled K-major layout.  The chunks of the registered (mma.sync fragment order)
-//       layout are scattered there by 4-byte cp.async copies, so the weights keep ONE resident copy.
+//       (128 codes) in the 128-byte-swizzled K-major layout.  The registered layout (mma.sync fragment order) is brought
+//       in as it lies by tiled TMA copies (cp.async.bulk.tensor.2d: one box = 8 row tiles x 1 KB, completion on an
+//       mbarrier) into a ring of packed stages, and eight warps re-order each stage into the operand form (16-byte
+//       loads, one shuffle, 8-byte stores): the weights keep ONE resident copy.
 //   SFA : the ue8m0 scale bytes of the weight, unchanged, 4 blocks per step, copied into tensor memory (tcgen05.cp
 //       32x128b.warpx4) in the scale-factor layout: lane r, 32-bit column q, byte k = scale of (row r + 32 q, block k).
 //   B : the activations as THREE E4M3 limbs with power-of-two block scales (x = 2^e (h1 + 2^-4 h2 + 2^-8 h3) per block
 //       of 32, each limb the E4M3 rounding of what the previous ones left): 12 significant bits per element, products
-//       exact, f32 accumulation inside the tensor core.  One MMA per limb and block accumulates into the same columns.
+//       exact, f32 accumulation inside the tensor core.  The limbs are further N columns of the same MMA (column
+//       limb * 16 + token, each with its own scale), so a weight tile is read from shared memory once per block; the
+//       epilogue adds the three columns of a token.
 //       This is NOT the engine's q8_0 activation (src/q8.rs:49-69), whose f32 block scale cannot ride on a block-scaled
 //       MMA; it tracks the engine's exact-f32 path (src/mxfp4.rs:488-539) to ~1e-5 of max |y| (tests hold 1e-3).
 //   D : f32 accumulators in tensor memory; the epilogue reads them with tcgen05.ld.
 // Reference semantics: ds_moe / expert_forward (src/deepseek.rs:1038-1108, 74-95), batched as matvec_packed_nt batches
 // (src/model.rs:2412-2447): a (token, expert) result does not depend on which other tokens share the tile.
 //
-// Pipeline per CTA: 8 producer warps fill a ring of 3 stages (128 columns of K each) with cp.async, one thread issues the
-// scale-factor copies and the MMAs, tcgen05.commit hands a stage back.  Every wait is bounded; a wait that runs out sets
-// MK_ERR_TIMEOUT in the status word and the CTA runs to its end (tensor memory is always freed).  No cluster launch, no
-// multicast.
+// Persistent CTAs (one per SM, 14 warps), work unit = (work item of <= 16 pairs, two 128-row weight tiles), units dealt
+// round-robin.  Warp 13 issues the TMA copies of a step (2 boxes of codes, 2 of scales) as soon as a packed stage is free
+// and runs on into the next unit; warps 4-11 fetch the step's activation limbs two steps ahead (cp.async into a ring of
+// B slots), re-order the packed stage into one of three operand buffers and hand it to warp 12, whose first lane copies
+// the scale factors into tensor memory and issues the MMAs into one of two accumulator sets; tcgen05.commit hands the
+// operand buffer back and, at the end of a unit, the accumulators to warps 0-3, which run the epilogue while the next
+// unit's products are under way.  Every wait is bounded; a wait that runs out sets MK_ERR_TIMEOUT in the status word
+// and every role leaves its loop (tensor memory is always freed).  No cluster launch, no multicast.
 #pragma once
 #include <cuda_fp8.h>
 
@@ -28,15 +36,27 @@
 
 namespace mtc {
 
-constexpr int NT = 32;                 // token rows (pairs) per work item
-constexpr int STAGES = 3, KSTEP = 128, NPROD = 256, THREADS = NPROD + 32;   // 8 producer (and epilogue) warps + the MMA warp
-constexpr int A_BYTES = 128 * 128;     // one 128-row tile of a stage: [128 rows][128 B]
-constexpr int B_BYTES = NT * 128;      // one limb of a stage: [32 rows][128 B]
-constexpr int OFF_A0 = 0, OFF_A1 = A_BYTES, OFF_B = 2 * A_BYTES, OFF_SF = OFF_B + 3 * B_BYTES;   // SF: 5 atoms of 512 B
-constexpr int STAGE_BYTES = ((OFF_SF + 5 * 512 + 1023) / 1024) * 1024;
-constexpr int SM_BAR = STAGES * STAGE_BYTES;           // full[3], empty[3], done, tmem slot
-constexpr int SM_TOTAL = SM_BAR + 128 + 1024;          // + slack to align the base to 1024 bytes
-constexpr int TMEM_COLS = 128, COL_D0 = 0, COL_D1 = NT, COL_SF = 2 * NT;   // SF: 2 buffers x 5 atoms x 4 columns
+constexpr int NT = 16;                 // token rows (pairs) per work item
+constexpr int KSTEP = 128;
+constexpr int NEPI = 128, NCONV = 256, THREADS = NEPI + NCONV + 64;   // 4 epilogue + 8 converter warps + the MMA warp + the loader warp
+constexpr int W_CONV = NEPI / 32, W_MMA = (NEPI + NCONV) / 32, W_LOAD = W_MMA + 1;
+constexpr int NS = 5;                  // packed stages (HBM reads in flight)
+constexpr int NM = 3;                  // operand buffers of A
+constexpr int NB = 5, LB = 2;          // slots of B; limbs are fetched LB steps ahead (NB >= NM + LB)
+constexpr int A_BYTES = 128 * 128;     // one 128-row tile in operand form: [128 rows][128 B]
+constexpr int B_BYTES = 3 * NT * 128;  // the three limbs of a step: rows limb * NT + token, [<= 48 rows][128 B]
+constexpr int P_BYTES = 2 * 8192 + 2 * 512;   // a packed stage: two tiles of codes (8 row tiles x 1 KB) + their scales (8 x 64 B each)
+constexpr int OFF_A = 0;                                   // NM x (A0, A1)
+constexpr int OFF_B = OFF_A + NM * 2 * A_BYTES;            // NB x limbs
+constexpr int OFF_SFA = OFF_B + NB * B_BYTES;              // NM x 2 atoms of 512 B
+constexpr int OFF_SFB = OFF_SFA + NM * 1024;               // NB atoms
+constexpr int OFF_P = ((OFF_SFB + NB * 512 + 1023) / 1024) * 1024;   // NS packed stages
+constexpr int SM_BAR = OFF_P + NS * P_BYTES;
+constexpr int BAR_PFULL = 0, BAR_PEMPTY = NS, BAR_MFULL = 2 * NS, BAR_MEMPTY = 2 * NS + NM, BAR_AFULL = 2 * NS + 2 * NM, BAR_AEMPTY = BAR_AFULL + 2;
+constexpr int N_BARS = BAR_AEMPTY + 2;
+constexpr int SM_TOTAL = SM_BAR + 256 + 1024;              // barriers, tensor-memory slot, abort flag; + slack to align the base to 1024 bytes
+constexpr int TMEM_COLS = 256, ACC_COLS = 6 * NT, COL_D1 = 3 * NT, COL_SF = 2 * ACC_COLS;   // 2 accumulator sets; SF: 2 buffers x 3 atoms x 4 columns
+static_assert(N_BARS * 8 <= 192 && SM_TOTAL <= 232448 && NB >= NM + LB, "shared memory of one CTA");
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -61,11 +81,15 @@ __device__ __forceinline__ void sf_copy(uint32_t taddr, uint32_t saddr) {
 __device__ __forceinline__ void commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+// `abort`: a word in shared memory that any role sets when one of its waits ran out; the others then give up at once
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
     uint32_t done = 0;
-    for (uint32_t it = 0; it < WAIT_LIMIT && !done; ++it)
+    for (uint32_t it = 0; it < WAIT_LIMIT && !done; ++it) {
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (!done && (it & 1023u) == 1023u && *abort) break;
+    }
+    if (!done) *abort = 1;
     return done != 0;
 }
 __device__ __forceinline__ void bar_arrive(uint32_t bar) {
@@ -73,6 +97,14 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ void cp4(uint32_t dst, const void *src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp16(uint32_t dst, const void *src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void tma_2d(uint32_t dst, const void *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst), "l"(map),
+                 "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
     uint32_t u[16];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
@@ -127,8 +159,7 @@ __global__ void __launch_bounds__(256) act_limbs_kernel(const float *__restrict_
 }
 
 struct TcArgs {
-    const void *const *wv;       // [(E+1)*3] tiled values of the registered weights
-    const void *const *wsc;      // [(E+1)*3] tiled scales
+    const unsigned char *maps;   // [(E+1)*3][2] tensor maps (128 B each) of the registered weights: tiled codes, tiled scales
     const int32_t *items;        // [n][3] = expert, offset into sorted, count (<= NT)
     const int32_t *n_items;
     const int32_t *sorted;       // pair ids grouped by expert
@@ -138,117 +169,23 @@ struct TcArgs {
     uint8_t *actl, *actsf;       // activation limbs [3][pairs][inter], [3][pairs][inter/32]
     float *outs;                 // [pairs][d]
     int rows, pairs, d, inter;
-    int64_t nbp_d, nbp_i;        // padded block counts of the registered weights
     int activation;
     float limit;
     int32_t *status;
 };
 
-// One CTA: two 128-row tiles of weights (`wa`, `wb`: tiled values of the two matrices, `rta`, `rtb` their first 16-row tile,
-// nbp the padded block count, K the contraction length) against n token rows whose limbs are rows `brow[r]` of (bl, bsf).
-// Leaves D0 / D1 in tensor memory columns COL_D0 / COL_D1 of `tb`.  Returns false if a wait ran out.
-__device__ __forceinline__ bool tile_pair_mma(unsigned char *sm, uint32_t tb, const unsigned char *wa, const unsigned char *sa, int64_t rta,
-                                              const unsigned char *wb, const unsigned char *sb, int64_t rtb, int64_t nbp, int K,
-                                              const uint8_t *__restrict__ bl, const uint8_t *__restrict__ bsf, int64_t b_rows,
-                                              const int *brow /* smem [NT] */, int n, int32_t *status) {
-    const int tid = threadIdx.x, warp = tid >> 5;
-    uint64_t *bars = (uint64_t *)(sm + SM_BAR);
-    const uint32_t full0 = s32(&bars[0]), empty0 = s32(&bars[STAGES]);
-    const int nsteps = K / KSTEP;
-    const int npad = (n + 7) & ~7;
-    bool ok = true;
-    if (warp < NPROD / 32) {
-        // ---------------- producers.  Thread (q, bpl): word q of every chunk of block pair bpl; a chunk of the registered
-        // layout is 512 bytes = 128 words, word q = 4 lane + j: lane (g, t) holds 8 codes (columns 8t .. 8t + 7) of block
-        // 2 bp + (j >> 1), row g + 8 (j & 1) of a 16-row tile.
-        const int p = tid, q = p & 127, bpl = p >> 7;
-        const int ln = q >> 2, j = q & 3, g = ln >> 2, t = ln & 3;
-        const int rowl = g + ((j & 1) ? 8 : 0), blk = bpl * 2 + (j >> 1);
-        const uint32_t cdst = rowl * 128 + ((((blk << 1) + (t >> 1)) ^ (rowl & 7)) << 4) + (t & 1) * 4;
-        const unsigned char *srca = wa + (rta * (nbp >> 1) + bpl) * 512 + (size_t)q * 4;
-        const unsigned char *srcb = wb + (rtb * (nbp >> 1) + bpl) * 512 + (size_t)q * 4;
-        const int64_t tile_stride = (nbp >> 1) * 512;      // next 16-row tile, same block pair
-        const int srow = p & 127, smat = p >> 7;           // scale word of row srow of matrix smat
-        const unsigned char *srcs = (smat ? sb : sa) + (((smat ? rtb : rta) + (srow >> 4)) * nbp) * 16 + (srow & 15) * 4;
-        const uint32_t sdst = smat * 512 + (srow & 31) * 16 + (srow >> 5) * 4;
-        for (int it = 0; it < nsteps + STAGES - 1; ++it) {
-            if (it < nsteps) {
-                const int st = it % STAGES;
-                if (it >= STAGES && ok && !bar_wait(empty0 + st * 8, (uint32_t)((it / STAGES) - 1) & 1u)) ok = false;
-                unsigned char *stage = sm + (size_t)st * STAGE_BYTES;
-                const uint32_t a0 = s32(stage + OFF_A0), a1 = s32(stage + OFF_A1), bb = s32(stage + OFF_B), sf = s32(stage + OFF_SF);
-                if (ok) {
-                    const unsigned char *sa_it = srca + (int64_t)it * 1024, *sb_it = srcb + (int64_t)it * 1024;   // 2 block pairs per step
-#pragma unroll
-                    for (int r8 = 0; r8 < 8; ++r8) {
-                        cp4(a0 + r8 * 2048 + cdst, sa_it + r8 * tile_stride);
-                        cp4(a1 + r8 * 2048 + cdst, sb_it + r8 * tile_stride);
-                    }
-                    cp4(sf + sdst, srcs + (int64_t)it * 64);          // 4 blocks on: 4 * 16 scale bytes per 16-row tile group
-                    // activation limbs: n rows x 128 bytes per limb, and their scale words
-                    for (int w = p; w < 3 * n * 8; w += NPROD) {
-                        const int limb = w / (n * 8), qq = w % (n * 8), r = qq >> 3, c = qq & 7;
-                        cp16(bb + limb * B_BYTES + r * 128 + ((c ^ (r & 7)) << 4), bl + ((int64_t)limb * b_rows + brow[r]) * K + (int64_t)it * KSTEP + c * 16);
-                    }
-                    if (p < 3 * n) {
-                        const int limb = p / n, r = p % n;
-                        cp4(sf + (2 + limb) * 512 + r * 16, bsf + ((int64_t)limb * b_rows + brow[r]) * (K / 32) + (int64_t)it * 4);
-                    }
-                }
-            }
-            asm volatile("cp.async.commit_group;\n" ::: "memory");
-            const int ready = it - (STAGES - 1);
-            if (ready >= 0) {
-                asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1) : "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                bar_arrive(full0 + (ready % STAGES) * 8);
-            }
-        }
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    } else if (tid == NPROD) {
-        // ---------------- the MMA-issuing thread
-        const uint32_t id[4] = {idesc_mx(npad, 0), idesc_mx(npad, 1), idesc_mx(npad, 2), idesc_mx(npad, 3)};
-        for (int it = 0; it < nsteps; ++it) {
-            const int st = it % STAGES;
-            if (ok && !bar_wait(full0 + st * 8, (uint32_t)(it / STAGES) & 1u)) ok = false;
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned char *stage = sm + (size_t)st * STAGE_BYTES;
-            const uint32_t a0 = s32(stage + OFF_A0), a1 = s32(stage + OFF_A1), bb = s32(stage + OFF_B), sf = s32(stage + OFF_SF);
-            const uint32_t tsf = tb + COL_SF + (uint32_t)(it & 1) * 20;
-#pragma unroll
-            for (int a = 0; a < 5; ++a) sf_copy(tsf + a * 4, sf + a * 512);
-#pragma unroll
-            for (int kb = 0; kb < 4; ++kb) {
-                const uint64_t da0 = smem_desc(a0 + kb * 32, 16, 1024, 2), da1 = smem_desc(a1 + kb * 32, 16, 1024, 2);
-#pragma unroll
-                for (int limb = 0; limb < 3; ++limb) {
-                    const uint64_t db = smem_desc(bb + limb * B_BYTES + kb * 32, 16, 1024, 2);
-                    const uint32_t acc = (it > 0 || kb > 0 || limb > 0) ? 1u : 0u;
-                    mma_mx(tb + COL_D0, da0, db, id[kb], acc, tsf + 0, tsf + 8 + limb * 4);
-                    mma_mx(tb + COL_D1, da1, db, id[kb], acc, tsf + 4, tsf + 8 + limb * 4);
-                }
-            }
-            commit(empty0 + st * 8);      // the stage is free once these MMAs have read it
-        }
-        commit(s32(&bars[2 * STAGES]));   // everything issued so far has finished: the accumulators are complete
-    }
-    if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
-    return ok;
-}
-
-// Common set-up: barriers, tensor memory, zeroed stages (padding bytes and unused rows must read as zero).
+// Set-up: barriers, tensor memory, zeroed operand buffers (padding bytes and rows no copy ever writes must read as zero).
 __device__ __forceinline__ uint32_t tc_setup(unsigned char *sm) {
     const int tid = threadIdx.x, warp = tid >> 5;
     uint64_t *bars = (uint64_t *)(sm + SM_BAR);
-    uint32_t *slot = (uint32_t *)(sm + SM_BAR + 64);
-    for (int i = tid; i < STAGES * STAGE_BYTES / 16; i += THREADS) ((uint4 *)sm)[i] = make_uint4(0u, 0u, 0u, 0u);
+    uint32_t *slot = (uint32_t *)(sm + SM_BAR + 192);
+    for (int i = tid; i < OFF_P / 16; i += THREADS) ((uint4 *)sm)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bars[s])), "r"(NPROD));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bars[STAGES + s])));
-        }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bars[2 * STAGES])));
+        auto init = [&](int b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bars[b])), "r"(count)); };
+        for (int s = 0; s < NS; ++s) { init(BAR_PFULL + s, 1); init(BAR_PEMPTY + s, NCONV); }
+        for (int s = 0; s < NM; ++s) { init(BAR_MFULL + s, NCONV); init(BAR_MEMPTY + s, 1); }
+        for (int s = 0; s < 2; ++s) { init(BAR_AFULL + s, 1); init(BAR_AEMPTY + s, NEPI); }
+        slot[1] = 0;     // the abort flag
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -267,114 +204,239 @@ __device__ __forceinline__ void tc_teardown(uint32_t tb) {
     if ((threadIdx.x >> 5) == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(TMEM_COLS) : "memory");
 }
 
-// ---------------------------------------------------------------- gate / up + activation + limbs of the activation
-// grid = (inter / 128, max_items).  D0 = w1 tile x tokens, D1 = w3 tile x tokens; then act (src/deepseek.rs:1083-1087 or
-// the K3 SiTU, src/model.rs:617-621) and its three limbs per 32 rows, the input of the w2 product.
-__global__ void __launch_bounds__(THREADS, 1) moe_tc_gate_up_kernel(const TcArgs a) {
+// DOWN = false: gate / up + activation + limbs of the activation.  Unit = (item, 128 rows of w1 and the same rows of w3),
+//   K = d; D0 = w1 tile x tokens, D1 = w3 tile x tokens; then act (src/deepseek.rs:1083-1087 or the K3 SiTU,
+//   src/model.rs:617-621) and its three limbs per 32 rows, the input of the w2 product.
+// DOWN = true: the down projection.  Unit = (item, two consecutive 128-row tiles of w2), K = inter; a tile past the last
+//   one reads as zeros (TMA fill) and is not stored.
+template <bool DOWN>
+__global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
     extern __shared__ unsigned char sm_raw[];
     unsigned char *sm = (unsigned char *)(((uintptr_t)sm_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ int brow[NT], pair_s[NT];
-    __shared__ float wgt_s[NT];
-    const int item = blockIdx.y;
-    if (item >= *a.n_items) return;
-    const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = min(a.items[item * 3 + 2], NT);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < NT) {
-        const int p = tid < n ? a.sorted[off + tid] : -1;
-        pair_s[tid] = p;
-        brow[tid] = p >= 0 ? a.pair_row[p] : 0;
-        wgt_s[tid] = p >= 0 ? a.pair_weight[p] : 0.0f;
-    }
+    const int K = DOWN ? a.inter : a.d, nsteps = K / KSTEP;
+    const int ntile = (DOWN ? a.d : a.inter) / 128;
+    const int X = DOWN ? (ntile + 1) / 2 : ntile;          // units per item
+    const int U = *a.n_items * X, G = (int)gridDim.x, c = (int)blockIdx.x;
+    if (c >= U) return;
+    const int nunits = (U - c + G - 1) / G;
     const uint32_t tb = tc_setup(sm);
-    const int64_t rt = (int64_t)blockIdx.x * 8;
-    bool ok = tile_pair_mma(sm, tb, (const unsigned char *)a.wv[e * 3 + 0], (const unsigned char *)a.wsc[e * 3 + 0], rt,
-                            (const unsigned char *)a.wv[e * 3 + 2], (const unsigned char *)a.wsc[e * 3 + 2], rt, a.nbp_d, a.d, a.xl, a.xsf, a.rows,
-                            brow, n, a.status);
     uint64_t *bars = (uint64_t *)(sm + SM_BAR);
-    if (!bar_wait(s32(&bars[2 * STAGES]), 0u)) { ok = false; atomicCAS(a.status, 0, MK_ERR_TIMEOUT); }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-        // warp = (lane quadrant q, column half): rows 32 q + lane of the tile, tokens 16 half .. 16 half + 15
-        const int q = warp & 3, half = warp >> 2;
-        if (warp < 8 && half * 16 < n) {
-            float g[16], u[16];
-            const uint32_t taddr = tb + ((uint32_t)(q * 32) << 16) + half * 16;
-            tmem_ld16(taddr + COL_D0, g);
-            tmem_ld16(taddr + COL_D1, u);
-            const int64_t col = (int64_t)blockIdx.x * 128 + q * 32 + lane;     // index into the expert's intermediate vector
-            const int nbi = a.inter / 32;
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const int tk = half * 16 + c;
-                if (tk >= n) break;
-                float act;
-                if (a.activation == MK_MOE_SITU) {
-                    act = mk_situ(g[c], u[c]);
-                } else {
-                    const float gl = fminf(g[c], a.limit);
-                    const float ul = fminf(fmaxf(u[c], -a.limit), a.limit);
-                    const float silu = __fdiv_rn(gl, __fadd_rn(1.0f, (float)exp((double)(-gl))));
-                    act = __fmul_rn(__fmul_rn(wgt_s[tk], silu), ul);
-                }
-                float mx = fabsf(act);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-                uint8_t limb[3], sf[3];
-                limbs_of(act, mx, limb, sf);
-                const int64_t p = pair_s[tk];
-#pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    a.actl[((int64_t)k * a.pairs + p) * a.inter + col] = limb[k];
-                    if (lane == 0) a.actsf[((int64_t)k * a.pairs + p) * nbi + (col >> 5)] = sf[k];
-                }
-            }
-        }
-    }
-    tc_teardown(tb);
-}
+    volatile int *abort = (volatile int *)(sm + SM_BAR + 196);
+    const uint32_t bar0 = s32(bars), smb = s32(sm);
+    bool ok = true;
 
-// ---------------------------------------------------------------- down projection
-// grid = (ceil(d / 256), max_items).  D0 / D1 = two consecutive 128-row tiles of w2 x the activation limbs.
-__global__ void __launch_bounds__(THREADS, 1) moe_tc_down_kernel(const TcArgs a) {
-    extern __shared__ unsigned char sm_raw[];
-    unsigned char *sm = (unsigned char *)(((uintptr_t)sm_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ int brow[NT];
-    const int item = blockIdx.y;
-    if (item >= *a.n_items) return;
-    const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = min(a.items[item * 3 + 2], NT);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < NT) brow[tid] = tid < n ? a.sorted[off + tid] : 0;
-    const uint32_t tb = tc_setup(sm);
-    const int64_t ntile = a.d / 128;
-    const int64_t t0 = (int64_t)blockIdx.x * 2, t1 = t0 + 1 < ntile ? t0 + 1 : t0;   // an odd last tile is computed twice, stored once
-    const unsigned char *wv = (const unsigned char *)a.wv[e * 3 + 1], *ws = (const unsigned char *)a.wsc[e * 3 + 1];
-    bool ok = tile_pair_mma(sm, tb, wv, ws, t0 * 8, wv, ws, t1 * 8, a.nbp_i, a.inter, a.actl, a.actsf, a.pairs, brow, n, a.status);
-    uint64_t *bars = (uint64_t *)(sm + SM_BAR);
-    if (!bar_wait(s32(&bars[2 * STAGES]), 0u)) { ok = false; atomicCAS(a.status, 0, MK_ERR_TIMEOUT); }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-        const int q = warp & 3, half = warp >> 2;
-        if (warp < 8 && half * 16 < n) {
-            const uint32_t taddr = tb + ((uint32_t)(q * 32) << 16) + half * 16;
+    if (warp == W_LOAD) {
+        // ---------------- the loader: one thread, four boxes per step
+        if (lane == 0) {
+            int gs = 0;
+            int e_next = a.items[(c / X) * 3];
+            for (int k = 0; k < nunits && ok; ++k) {
+                const int u = c + k * G, xt = u % X, e = e_next;
+                if (k + 1 < nunits) e_next = a.items[((u + G) / X) * 3];
+                const unsigned char *m0, *m1;
+                int y0, y1;
+                if (DOWN) { m0 = m1 = a.maps + (size_t)(e * 3 + 1) * 256; y0 = xt * 16; y1 = y0 + 8; }
+                else { m0 = a.maps + (size_t)(e * 3 + 0) * 256; m1 = a.maps + (size_t)(e * 3 + 2) * 256; y0 = y1 = xt * 8; }
+                for (int it = 0; it < nsteps; ++it, ++gs) {
+                    const int ps = gs % NS;
+                    if (gs >= NS && !bar_wait(bar0 + (BAR_PEMPTY + ps) * 8, (uint32_t)((gs / NS) - 1) & 1u, abort)) { ok = false; break; }
+                    const uint32_t full = bar0 + (BAR_PFULL + ps) * 8, dst = smb + OFF_P + ps * P_BYTES;
+                    bar_expect(full, (uint32_t)P_BYTES);
+                    tma_2d(dst, m0, it * 256, y0, full);                 // codes: 256 words (2 block pairs) x 8 row tiles
+                    tma_2d(dst + 8192, m1, it * 256, y1, full);
+                    tma_2d(dst + 16384, m0 + 128, it * 16, y0, full);    // scales: 16 words (4 blocks x 16 rows) x 8 row tiles
+                    tma_2d(dst + 16896, m1 + 128, it * 16, y1, full);
+                }
+            }
+        }
+    } else if (warp == W_MMA) {
+        // ---------------- the MMA-issuing thread
+        if (lane == 0) {
+            int gs = 0;
+            for (int k = 0; k < nunits && ok; ++k) {
+                const int nn = 3 * NT, acc = k & 1;   // padding tokens ride along: N a multiple of 16 at M = 128
+                const uint32_t id[4] = {idesc_mx(nn, 0), idesc_mx(nn, 1), idesc_mx(nn, 2), idesc_mx(nn, 3)};
+                if (k >= 2 && !bar_wait(bar0 + (BAR_AEMPTY + acc) * 8, (uint32_t)((k >> 1) - 1) & 1u, abort)) { ok = false; break; }
+                const uint32_t d0 = tb + acc * ACC_COLS, d1 = d0 + COL_D1;
+                for (int it = 0; it < nsteps; ++it, ++gs) {
+                    const int mb = gs % NM, slot = gs % NB;
+                    if (!bar_wait(bar0 + (BAR_MFULL + mb) * 8, (uint32_t)(gs / NM) & 1u, abort)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a0 = smb + OFF_A + mb * 2 * A_BYTES, a1 = a0 + A_BYTES, bb = smb + OFF_B + slot * B_BYTES;
+                    const uint32_t tsf = tb + COL_SF + (uint32_t)(gs & 1) * 12;
+                    sf_copy(tsf + 0, smb + OFF_SFA + mb * 1024);
+                    sf_copy(tsf + 4, smb + OFF_SFA + mb * 1024 + 512);
+                    sf_copy(tsf + 8, smb + OFF_SFB + slot * 512);
 #pragma unroll
-            for (int tile = 0; tile < 2; ++tile) {
-                if (tile == 1 && t1 == t0) break;
-                float v[16];
-                tmem_ld16(taddr + (tile ? COL_D1 : COL_D0), v);
-                const int64_t row = (t0 + tile) * 128 + q * 32 + lane;
+                    for (int kb = 0; kb < 4; ++kb) {
+                        const uint64_t da0 = smem_desc(a0 + kb * 32, 16, 1024, 2), da1 = smem_desc(a1 + kb * 32, 16, 1024, 2);
+                        const uint64_t db = smem_desc(bb + kb * 32, 16, 1024, 2);
+                        const uint32_t accum = (it > 0 || kb > 0) ? 1u : 0u;
+                        mma_mx(d0, da0, db, id[kb], accum, tsf + 0, tsf + 8);
+                        mma_mx(d1, da1, db, id[kb], accum, tsf + 4, tsf + 8);
+                    }
+                    commit(bar0 + (BAR_MEMPTY + mb) * 8);      // the operand buffer and the B slot are free once these MMAs have read them
+                }
+                if (ok) commit(bar0 + (BAR_AFULL + acc) * 8);  // the unit's accumulators are complete
+            }
+        }
+    } else if (warp >= W_CONV) {
+        // ---------------- converters
+        const int p = tid - NEPI, cw = warp - W_CONV;
+        const uint8_t *bl = DOWN ? a.actl : a.xl, *bsf = DOWN ? a.actsf : a.xsf;
+        const int64_t b_rows = DOWN ? a.pairs : a.rows;
+        // a unit's B rows: this thread copies chunk (p & 7) of token (p >> 3), and the scale word of token p % NT, limb p / NT
+        struct Rows { int n; int64_t main, sf; };
+        auto rows_of = [&](int u) {
+            Rows r;
+            const int item = u / X, off = a.items[item * 3 + 1];
+            r.n = min(a.items[item * 3 + 2], NT);
+            const int t0 = p >> 3, t1 = p & (NT - 1);
+            const int p0 = t0 < r.n ? a.sorted[off + t0] : 0, p1 = t1 < r.n ? a.sorted[off + t1] : 0;
+            r.main = DOWN ? p0 : a.pair_row[p0];
+            r.sf = DOWN ? p1 : a.pair_row[p1];
+            return r;
+        };
+        Rows cur = rows_of(c), nxt = cur;
+        if (nunits > 1) nxt = rows_of(c + G);
+        int fk = 0, fit = 0, fs = 0;        // fetch cursor: unit, step within it, global step
+        auto fetch_b = [&]() {
+            if (fk < nunits) {
+                const int slot = fs % NB, npad = NT;
+                const uint32_t bb = smb + OFF_B + slot * B_BYTES, sfb = smb + OFF_SFB + slot * 512;
+                const int t0 = p >> 3, ch = p & 7;
+                if (t0 < cur.n) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int tk = half * 16 + c;
-                    if (tk >= n) break;
-                    const int64_t p = brow[tk];
-                    float o = v[c];
+                    for (int limb = 0; limb < 3; ++limb) {
+                        const int br = limb * npad + t0;
+                        cp16(bb + br * 128 + ((ch ^ (br & 7)) << 4), bl + ((int64_t)limb * b_rows + cur.main) * K + (int64_t)fit * KSTEP + ch * 16);
+                    }
+                }
+                if (p < 3 * NT && (p & (NT - 1)) < cur.n) {
+                    const int limb = p / NT, br = limb * npad + (p & (NT - 1));
+                    cp4(sfb + (br & 31) * 16 + (br >> 5) * 4, bsf + ((int64_t)limb * b_rows + cur.sf) * (K / 32) + (int64_t)fit * 4);
+                }
+                ++fs;
+                if (++fit == nsteps) {
+                    fit = 0; ++fk; cur = nxt;
+                    if (fk + 1 < nunits) nxt = rows_of(c + (fk + 1) * G);
+                }
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        };
+        // Lane (g, t) of a packed 512-byte chunk (16 rows x 2 blocks) holds four words: word j = 8 codes (columns 8t .. 8t + 7)
+        // of block (j >> 1), row g + 8 (j & 1).  Lanes t and t ^ 1 together hold the 16 codes of an operand chunk, so even
+        // lanes take the partner's words 0, 1 and write block 0, odd lanes take words 2, 3 and write block 1.
+        const int g = lane >> 2, t = lane & 3, odd = t & 1;
+        const int cpos = (odd << 1) + (t >> 1);                    // 16-byte chunk of the row within the chunk's 2 blocks
+        const int crt = cw >> 1, cbp = cw & 1;                     // this warp's chunks: row tiles crt and crt + 4, block pair cbp
+        const uint32_t src_off = (uint32_t)(crt * 1024 + cbp * 512 + lane * 16);
+        // row g of the 16-row tile (row g + 8, 1024 bytes on, has the same swizzle phase), chunk 4 cbp + cpos of its 128 bytes
+        const uint32_t d_lo_c = (uint32_t)(g * 128 + ((((cbp << 2) + cpos) ^ g) << 4));
+        for (int i = 0; i < LB; ++i) fetch_b();
+        const int total = nunits * nsteps;
+        for (int gs = 0; gs < total; ++gs) {
+            const int mb = gs % NM, ps = gs % NS;
+            // operand buffer mb and B slot (gs + LB) % NB were last read by the MMAs of step gs - NM
+            if (gs >= NM && ok && !bar_wait(bar0 + (BAR_MEMPTY + mb) * 8, (uint32_t)((gs / NM) - 1) & 1u, abort)) ok = false;
+            fetch_b();
+            if (ok && !bar_wait(bar0 + (BAR_PFULL + ps) * 8, (uint32_t)(gs / NS) & 1u, abort)) ok = false;
+            if (!ok) break;
+            const unsigned char *pk = sm + OFF_P + (size_t)ps * P_BYTES;
+            unsigned char *am = sm + OFF_A + (size_t)mb * 2 * A_BYTES;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 w = *(const uint4 *)(pk + m * 8192 + h * 4096 + src_off);
+                    const uint32_t s0 = odd ? w.x : w.z, s1 = odd ? w.y : w.w;
+                    const uint32_t r0 = __shfl_xor_sync(0xFFFFFFFFu, s0, 1), r1 = __shfl_xor_sync(0xFFFFFFFFu, s1, 1);
+                    // even lane: (mine, partner's) of words 0, 1; odd lane: (partner's, mine) of words 2, 3
+                    const uint2 lo = odd ? make_uint2(r0, w.z) : make_uint2(w.x, r0);
+                    const uint2 hi = odd ? make_uint2(r1, w.w) : make_uint2(w.y, r1);
+                    unsigned char *dst = am + m * A_BYTES + (crt + 4 * h) * 2048 + d_lo_c;
+                    *(uint2 *)dst = lo;
+                    *(uint2 *)(dst + 1024) = hi;
+                }
+            }
+            // scales: packed [matrix][row tile][16 rows][4 blocks of the step]; one word = a row's four scale bytes
+            {
+                const int smat = p >> 7, srow = p & 127;
+                const uint32_t v = *(const uint32_t *)(pk + 16384 + smat * 512 + (srow >> 4) * 64 + (srow & 15) * 4);
+                *(uint32_t *)(sm + OFF_SFA + mb * 1024 + smat * 512 + (srow & 31) * 16 + (srow >> 5) * 4) = v;
+            }
+            bar_arrive(bar0 + (BAR_PEMPTY + ps) * 8);
+            asm volatile("cp.async.wait_group %0;\n" ::"n"(LB) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            bar_arrive(bar0 + (BAR_MFULL + mb) * 8);
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    } else {
+        // ---------------- epilogue: warp q reads lanes 32 q .. 32 q + 31 of the accumulators (rows of the tile), all tokens
+        const int q = warp;
+        for (int k = 0; k < nunits; ++k) {
+            const int u = c + k * G, item = u / X, xt = u % X, acc = k & 1;
+            const int off = a.items[item * 3 + 1], n = min(a.items[item * 3 + 2], NT), npad = NT;
+            if (!bar_wait(bar0 + (BAR_AFULL + acc) * 8, (uint32_t)(k >> 1) & 1u, abort)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tb + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
+            float v0[16], v1[16], l1[16], l2[16];      // a token's three limb products sit npad columns apart
+            tmem_ld16(taddr, v0);
+            tmem_ld16(taddr + npad, l1);
+            tmem_ld16(taddr + 2 * npad, l2);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v0[i] = __fadd_rn(__fadd_rn(v0[i], l1[i]), l2[i]);
+            tmem_ld16(taddr + COL_D1, v1);
+            tmem_ld16(taddr + COL_D1 + npad, l1);
+            tmem_ld16(taddr + COL_D1 + 2 * npad, l2);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v1[i] = __fadd_rn(__fadd_rn(v1[i], l1[i]), l2[i]);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            bar_arrive(bar0 + (BAR_AEMPTY + acc) * 8);            // the accumulator set may be overwritten
+            if (!DOWN) {
+                const int64_t col = (int64_t)xt * 128 + q * 32 + lane;     // index into the expert's intermediate vector
+                const int nbi = a.inter / 32;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (i >= n) break;
+                    const int64_t pid = a.sorted[off + i];
+                    float act;
+                    if (a.activation == MK_MOE_SITU) {
+                        act = mk_situ(v0[i], v1[i]);
+                    } else {
+                        const float gl = fminf(v0[i], a.limit);
+                        const float ul = fminf(fmaxf(v1[i], -a.limit), a.limit);
+                        const float silu = __fdiv_rn(gl, __fadd_rn(1.0f, (float)exp((double)(-gl))));
+                        act = __fmul_rn(__fmul_rn(a.pair_weight[pid], silu), ul);
+                    }
+                    float mx = fabsf(act);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+                    uint8_t limb[3], sf[3];
+                    limbs_of(act, mx, limb, sf);
+#pragma unroll
+                    for (int l = 0; l < 3; ++l) {
+                        a.actl[((int64_t)l * a.pairs + pid) * a.inter + col] = limb[l];
+                        if (lane == 0) a.actsf[((int64_t)l * a.pairs + pid) * nbi + (col >> 5)] = sf[l];
+                    }
+                }
+            } else {
+                const int64_t row0 = (int64_t)(2 * xt) * 128 + q * 32 + lane;
+                const bool second = 2 * xt + 1 < ntile;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (i >= n) break;
+                    const int64_t pid = a.sorted[off + i];
                     // K3 body: the routing weight multiplies the expert output (src/model.rs:2346-2351)
-                    if (a.activation == MK_MOE_SITU) o = __fmul_rn(a.pair_weight[p], o);
-                    a.outs[p * a.d + row] = o;
+                    const float w = a.activation == MK_MOE_SITU ? a.pair_weight[pid] : 1.0f;
+                    a.outs[pid * a.d + row0] = a.activation == MK_MOE_SITU ? __fmul_rn(w, v0[i]) : v0[i];
+                    if (second) a.outs[pid * a.d + row0 + 128] = a.activation == MK_MOE_SITU ? __fmul_rn(w, v1[i]) : v1[i];
                 }
             }
         }
     }
+    if (!ok) atomicCAS(a.status, 0, MK_ERR_TIMEOUT);
     tc_teardown(tb);
 }
 
