@@ -23,12 +23,21 @@
 //
 // Persistent CTAs (one per SM, 14 warps), work unit = (work item of <= 16 pairs, two 128-row weight tiles), units dealt
 // round-robin.  Warp 13 issues the TMA copies of a step (2 boxes of codes, 2 of scales) as soon as a packed stage is free
-// and runs on into the next unit; warps 4-11 fetch the step's activation limbs two steps ahead (cp.async into a ring of
-// B slots), re-order the packed stage into one of three operand buffers and hand it to warp 12, whose first lane copies
-// the scale factors into tensor memory and issues the MMAs into one of two accumulator sets; tcgen05.commit hands the
-// operand buffer back and, at the end of a unit, the accumulators to warps 0-3, which run the epilogue while the next
-// unit's products are under way.  Every wait is bounded; a wait that runs out sets MK_ERR_TIMEOUT in the status word
-// and every role leaves its loop (tensor memory is always freed).  No cluster launch, no multicast.
+// and runs on into the next unit; warps 4-11, two groups that take alternate steps, fetch their step's activation limbs
+// one own step ahead (cp.async into a ring of B slots), re-order the packed stage into one of three operand buffers and
+// hand it to warp 12, whose first lane copies the scale factors into tensor memory and issues the MMAs into one of two
+// accumulator sets; tcgen05.commit hands the operand buffer back and, at the end of a unit, the accumulators to warps
+// 0-3, which run the epilogue while the next unit's products are under way.  Every wait is bounded; a wait that runs
+// out sets MK_ERR_TIMEOUT in the status word and every role leaves its loop (tensor memory is always freed).  No
+// cluster launch, no multicast.
+//
+// What bounds it (measured with per-role cycle counters on the batch-256 layer, 384 + 1 experts of 7168 x 2048): per step
+// of 128 columns (16 KB of codes) the MMA warp is busy ~1000 cycles - a block-scaled MMA of M = 128 costs ~110 cycles
+// whatever N is, and a step needs 8 - and the shared-memory traffic (TMA write 17 KB, re-order read 16 KB, re-order
+// write 16 KB into half the banks, operand reads ~44 KB) is ~900 cycles; HBM alone would allow 712.  Weights as the N
+// operand (N = 256, 4 MMAs per step, one accumulator set) measured no faster: the same shared-memory wall and the
+// epilogue no longer overlaps.  The padded FP4 operand form doubles every byte on its way through shared memory; a
+// weight layout that TMA can unpack itself (row-major nibbles, 16U4_ALIGN16B boxes) would remove the re-order pass.
 #pragma once
 #include <cuda_fp8.h>
 
@@ -38,7 +47,7 @@ namespace mtc {
 
 constexpr int NT = 16;                 // token rows (pairs) per work item
 constexpr int KSTEP = 128;
-constexpr int NEPI = 128, NCONV = 256, THREADS = NEPI + NCONV + 64;   // 4 epilogue + 8 converter warps + the MMA warp + the loader warp
+constexpr int NEPI = 128, NCONV = 256, NGRP = 128, THREADS = NEPI + NCONV + 64;   // 4 epilogue + 8 converter warps (2 groups) + the MMA warp + the loader warp
 constexpr int W_CONV = NEPI / 32, W_MMA = (NEPI + NCONV) / 32, W_LOAD = W_MMA + 1;
 constexpr int NS = 5;                  // packed stages (HBM reads in flight)
 constexpr int NM = 3;                  // operand buffers of A
@@ -93,7 +102,7 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile
     return done != 0;
 }
 __device__ __forceinline__ void bar_arrive(uint32_t bar) {
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp4(uint32_t dst, const void *src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp16(uint32_t dst, const void *src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory"); }
@@ -182,9 +191,9 @@ __device__ __forceinline__ uint32_t tc_setup(unsigned char *sm) {
     for (int i = tid; i < OFF_P / 16; i += THREADS) ((uint4 *)sm)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (tid == 0) {
         auto init = [&](int b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bars[b])), "r"(count)); };
-        for (int s = 0; s < NS; ++s) { init(BAR_PFULL + s, 1); init(BAR_PEMPTY + s, NCONV); }
-        for (int s = 0; s < NM; ++s) { init(BAR_MFULL + s, NCONV); init(BAR_MEMPTY + s, 1); }
-        for (int s = 0; s < 2; ++s) { init(BAR_AFULL + s, 1); init(BAR_AEMPTY + s, NEPI); }
+        for (int s = 0; s < NS; ++s) { init(BAR_PFULL + s, 1); init(BAR_PEMPTY + s, NGRP / 32); }     // one arrival per warp of the group that converts the step
+        for (int s = 0; s < NM; ++s) { init(BAR_MFULL + s, NGRP / 32); init(BAR_MEMPTY + s, 1); }
+        for (int s = 0; s < 2; ++s) { init(BAR_AFULL + s, 1); init(BAR_AEMPTY + s, NEPI / 32); }
         slot[1] = 0;     // the abort flag
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -227,8 +236,9 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
     bool ok = true;
 
     if (warp == W_LOAD) {
-        // ---------------- the loader: one thread, four boxes per step
-        if (lane == 0) {
+        // ---------------- the loader: the whole warp walks the loop (a lone lane beside 31 parked ones runs slowly),
+        // lane 0 issues the four boxes of a step
+        {
             int gs = 0;
             int e_next = a.items[(c / X) * 3];
             for (int k = 0; k < nunits && ok; ++k) {
@@ -242,17 +252,20 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                     const int ps = gs % NS;
                     if (gs >= NS && !bar_wait(bar0 + (BAR_PEMPTY + ps) * 8, (uint32_t)((gs / NS) - 1) & 1u, abort)) { ok = false; break; }
                     const uint32_t full = bar0 + (BAR_PFULL + ps) * 8, dst = smb + OFF_P + ps * P_BYTES;
-                    bar_expect(full, (uint32_t)P_BYTES);
-                    tma_2d(dst, m0, it * 256, y0, full);                 // codes: 256 words (2 block pairs) x 8 row tiles
-                    tma_2d(dst + 8192, m1, it * 256, y1, full);
-                    tma_2d(dst + 16384, m0 + 128, it * 16, y0, full);    // scales: 16 words (4 blocks x 16 rows) x 8 row tiles
-                    tma_2d(dst + 16896, m1 + 128, it * 16, y1, full);
+                    if (lane == 0) {
+                        bar_expect(full, (uint32_t)P_BYTES);
+                        tma_2d(dst, m0, it * 256, y0, full);                 // codes: 256 words (2 block pairs) x 8 row tiles
+                        tma_2d(dst + 8192, m1, it * 256, y1, full);
+                        tma_2d(dst + 16384, m0 + 128, it * 16, y0, full);    // scales: 16 words (4 blocks x 16 rows) x 8 row tiles
+                        tma_2d(dst + 16896, m1 + 128, it * 16, y1, full);
+                    }
+                    __syncwarp();
                 }
             }
         }
     } else if (warp == W_MMA) {
-        // ---------------- the MMA-issuing thread
-        if (lane == 0) {
+        // ---------------- the MMA warp: all lanes wait, lane 0 issues
+        {
             int gs = 0;
             for (int k = 0; k < nunits && ok; ++k) {
                 const int nn = 3 * NT, acc = k & 1;   // padding tokens ride along: N a multiple of 16 at M = 128
@@ -265,6 +278,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a0 = smb + OFF_A + mb * 2 * A_BYTES, a1 = a0 + A_BYTES, bb = smb + OFF_B + slot * B_BYTES;
                     const uint32_t tsf = tb + COL_SF + (uint32_t)(gs & 1) * 12;
+                    if (lane == 0) {
                     sf_copy(tsf + 0, smb + OFF_SFA + mb * 1024);
                     sf_copy(tsf + 4, smb + OFF_SFA + mb * 1024 + 512);
                     sf_copy(tsf + 8, smb + OFF_SFB + slot * 512);
@@ -277,49 +291,55 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                         mma_mx(d1, da1, db, id[kb], accum, tsf + 4, tsf + 8);
                     }
                     commit(bar0 + (BAR_MEMPTY + mb) * 8);      // the operand buffer and the B slot are free once these MMAs have read them
+                    }
+                    __syncwarp();
                 }
-                if (ok) commit(bar0 + (BAR_AFULL + acc) * 8);  // the unit's accumulators are complete
+                if (ok && lane == 0) commit(bar0 + (BAR_AFULL + acc) * 8);  // the unit's accumulators are complete
             }
         }
     } else if (warp >= W_CONV) {
-        // ---------------- converters
-        const int p = tid - NEPI, cw = warp - W_CONV;
+        // ---------------- converters: two groups of four warps, group j takes the steps gs = j (mod 2), so the barrier round
+        // trips and shared-memory latencies of one step overlap with the other group's work
+        const int cw = warp - W_CONV, grp = cw >> 2, gw = cw & 3, gp = (tid - NEPI) & (NGRP - 1);
         const uint8_t *bl = DOWN ? a.actl : a.xl, *bsf = DOWN ? a.actsf : a.xsf;
         const int64_t b_rows = DOWN ? a.pairs : a.rows;
-        // a unit's B rows: this thread copies chunk (p & 7) of token (p >> 3), and the scale word of token p % NT, limb p / NT
-        struct Rows { int n; int64_t main, sf; };
+        // a unit's B rows: this thread copies chunk (gp & 7) of token (gp >> 3), and the scale word of token gp % NT, limb gp / NT
+        struct Rows { int n; const uint8_t *main, *sf; };
         auto rows_of = [&](int u) {
             Rows r;
             const int item = u / X, off = a.items[item * 3 + 1];
             r.n = min(a.items[item * 3 + 2], NT);
-            const int t0 = p >> 3, t1 = p & (NT - 1);
+            const int t0 = gp >> 3, t1 = gp & (NT - 1);
             const int p0 = t0 < r.n ? a.sorted[off + t0] : 0, p1 = t1 < r.n ? a.sorted[off + t1] : 0;
-            r.main = DOWN ? p0 : a.pair_row[p0];
-            r.sf = DOWN ? p1 : a.pair_row[p1];
+            const int64_t r0 = DOWN ? p0 : a.pair_row[p0], r1 = DOWN ? p1 : a.pair_row[p1];
+            r.main = bl + r0 * K + (gp & 7) * 16;
+            r.sf = bsf + ((int64_t)(gp / NT) * b_rows + r1) * (K / 32);
             return r;
         };
-        Rows cur = rows_of(c), nxt = cur;
-        if (nunits > 1) nxt = rows_of(c + G);
-        int fk = 0, fit = 0, fs = 0;        // fetch cursor: unit, step within it, global step
-        auto fetch_b = [&]() {
-            if (fk < nunits) {
-                const int slot = fs % NB, npad = NT;
-                const uint32_t bb = smb + OFF_B + slot * B_BYTES, sfb = smb + OFF_SFB + slot * 512;
-                const int t0 = p >> 3, ch = p & 7;
-                if (t0 < cur.n) {
-#pragma unroll
-                    for (int limb = 0; limb < 3; ++limb) {
-                        const int br = limb * npad + t0;
-                        cp16(bb + br * 128 + ((ch ^ (br & 7)) << 4), bl + ((int64_t)limb * b_rows + cur.main) * K + (int64_t)fit * KSTEP + ch * 16);
-                    }
+        const int total = nunits * nsteps;
+        int fk = 0, fit = grp;              // fetch cursor of this group: unit, step within it
+        while (fit >= nsteps && fk < nunits) { fit -= nsteps; ++fk; }
+        Rows cur = rows_of(c + (fk < nunits ? fk : 0) * G), nxt = cur;
+        if (fk + 1 < nunits) nxt = rows_of(c + (fk + 1) * G);
+        const int64_t limb_stride = b_rows * K;
+        const int bt0 = gp >> 3, bch = gp & 7;
+        const uint32_t bdst = (uint32_t)(bt0 * 128 + ((bch ^ (bt0 & 7)) << 4));       // limb rows 16 apart keep the swizzle phase
+        const bool sf_thread = gp < 3 * NT;
+        const uint32_t sfdst = (uint32_t)((gp & 31) * 16 + (gp >> 5) * 4);            // row limb * 16 + token of the scale atom = gp
+        auto fetch_b = [&](int f) {         // the limbs of global step f (one of this group's) into slot f % NB
+            if (f < total) {
+                const int slot = f % NB;
+                const uint32_t bb = smb + OFF_B + slot * B_BYTES + bdst, sfb = smb + OFF_SFB + slot * 512 + sfdst;
+                if (bt0 < cur.n) {
+                    const uint8_t *src = cur.main + (int64_t)fit * KSTEP;
+                    cp16(bb, src);
+                    cp16(bb + NT * 128, src + limb_stride);
+                    cp16(bb + 2 * NT * 128, src + 2 * limb_stride);
                 }
-                if (p < 3 * NT && (p & (NT - 1)) < cur.n) {
-                    const int limb = p / NT, br = limb * npad + (p & (NT - 1));
-                    cp4(sfb + (br & 31) * 16 + (br >> 5) * 4, bsf + ((int64_t)limb * b_rows + cur.sf) * (K / 32) + (int64_t)fit * 4);
-                }
-                ++fs;
-                if (++fit == nsteps) {
-                    fit = 0; ++fk; cur = nxt;
+                if (sf_thread && (gp & (NT - 1)) < cur.n) cp4(sfb, cur.sf + (int64_t)fit * 4);
+                fit += 2;
+                while (fit >= nsteps && fk < nunits) {
+                    fit -= nsteps; ++fk; cur = nxt;
                     if (fk + 1 < nunits) nxt = rows_of(c + (fk + 1) * G);
                 }
             }
@@ -330,46 +350,49 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
         // lanes take the partner's words 0, 1 and write block 0, odd lanes take words 2, 3 and write block 1.
         const int g = lane >> 2, t = lane & 3, odd = t & 1;
         const int cpos = (odd << 1) + (t >> 1);                    // 16-byte chunk of the row within the chunk's 2 blocks
-        const int crt = cw >> 1, cbp = cw & 1;                     // this warp's chunks: row tiles crt and crt + 4, block pair cbp
-        const uint32_t src_off = (uint32_t)(crt * 1024 + cbp * 512 + lane * 16);
-        // row g of the 16-row tile (row g + 8, 1024 bytes on, has the same swizzle phase), chunk 4 cbp + cpos of its 128 bytes
-        const uint32_t d_lo_c = (uint32_t)(g * 128 + ((((cbp << 2) + cpos) ^ g) << 4));
-        for (int i = 0; i < LB; ++i) fetch_b();
-        const int total = nunits * nsteps;
-        for (int gs = 0; gs < total; ++gs) {
+        // this warp's chunks: row tiles gw and gw + 4, both block pairs, both matrices
+        const uint32_t src_off = (uint32_t)(gw * 1024 + lane * 16);
+        // row g of the 16-row tile (row g + 8, 1024 bytes on, has the same swizzle phase), chunk 4 bp + cpos of its 128 bytes
+        const uint32_t d_c0 = (uint32_t)(gw * 2048 + g * 128 + ((cpos ^ g) << 4)), d_c1 = (uint32_t)(gw * 2048 + g * 128 + (((4 + cpos) ^ g) << 4));
+        fetch_b(grp);
+        for (int gs = grp; gs < total; gs += 2) {
             const int mb = gs % NM, ps = gs % NS;
-            // operand buffer mb and B slot (gs + LB) % NB were last read by the MMAs of step gs - NM
+            // operand buffer mb and B slot (gs + 2) % NB were last read by the MMAs of step gs - NM
             if (gs >= NM && ok && !bar_wait(bar0 + (BAR_MEMPTY + mb) * 8, (uint32_t)((gs / NM) - 1) & 1u, abort)) ok = false;
-            fetch_b();
+            fetch_b(gs + 2);
             if (ok && !bar_wait(bar0 + (BAR_PFULL + ps) * 8, (uint32_t)(gs / NS) & 1u, abort)) ok = false;
             if (!ok) break;
             const unsigned char *pk = sm + OFF_P + (size_t)ps * P_BYTES;
             unsigned char *am = sm + OFF_A + (size_t)mb * 2 * A_BYTES;
+            uint4 w[8];
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
+            for (int i = 0; i < 8; ++i) w[i] = *(const uint4 *)(pk + (i >> 2) * 8192 + ((i >> 1) & 1) * 4096 + (i & 1) * 512 + src_off);
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 w = *(const uint4 *)(pk + m * 8192 + h * 4096 + src_off);
-                    const uint32_t s0 = odd ? w.x : w.z, s1 = odd ? w.y : w.w;
-                    const uint32_t r0 = __shfl_xor_sync(0xFFFFFFFFu, s0, 1), r1 = __shfl_xor_sync(0xFFFFFFFFu, s1, 1);
-                    // even lane: (mine, partner's) of words 0, 1; odd lane: (partner's, mine) of words 2, 3
-                    const uint2 lo = odd ? make_uint2(r0, w.z) : make_uint2(w.x, r0);
-                    const uint2 hi = odd ? make_uint2(r1, w.w) : make_uint2(w.y, r1);
-                    unsigned char *dst = am + m * A_BYTES + (crt + 4 * h) * 2048 + d_lo_c;
-                    *(uint2 *)dst = lo;
-                    *(uint2 *)(dst + 1024) = hi;
-                }
+            for (int i = 0; i < 8; ++i) {          // i = (matrix, row tile half, block pair)
+                const uint32_t s0 = odd ? w[i].x : w[i].z, s1 = odd ? w[i].y : w[i].w;
+                const uint32_t r0 = __shfl_xor_sync(0xFFFFFFFFu, s0, 1), r1 = __shfl_xor_sync(0xFFFFFFFFu, s1, 1);
+                // even lane: (mine, partner's) of words 0, 1; odd lane: (partner's, mine) of words 2, 3
+                const uint2 lo = odd ? make_uint2(r0, w[i].z) : make_uint2(w[i].x, r0);
+                const uint2 hi = odd ? make_uint2(r1, w[i].w) : make_uint2(w[i].y, r1);
+                unsigned char *dst = am + (i >> 2) * A_BYTES + ((i >> 1) & 1) * 4 * 2048 + ((i & 1) ? d_c1 : d_c0);
+                *(uint2 *)dst = lo;
+                *(uint2 *)(dst + 1024) = hi;
             }
             // scales: packed [matrix][row tile][16 rows][4 blocks of the step]; one word = a row's four scale bytes
-            {
-                const int smat = p >> 7, srow = p & 127;
+#pragma unroll
+            for (int smat = 0; smat < 2; ++smat) {
+                const int srow = gp;
                 const uint32_t v = *(const uint32_t *)(pk + 16384 + smat * 512 + (srow >> 4) * 64 + (srow & 15) * 4);
                 *(uint32_t *)(sm + OFF_SFA + mb * 1024 + smat * 512 + (srow & 31) * 16 + (srow >> 5) * 4) = v;
             }
-            bar_arrive(bar0 + (BAR_PEMPTY + ps) * 8);
-            asm volatile("cp.async.wait_group %0;\n" ::"n"(LB) : "memory");
+            // one arrival per warp: the warp's reads of the packed stage are done
+            __syncwarp();
+            if (lane == 0) bar_arrive(bar0 + (BAR_PEMPTY + ps) * 8);
+            // ... and its writes (the stores above, the cp.async of this step) are visible to the tensor core's reads
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bar_arrive(bar0 + (BAR_MFULL + mb) * 8);
+            __syncwarp();
+            if (lane == 0) bar_arrive(bar0 + (BAR_MFULL + mb) * 8);
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     } else {
@@ -393,7 +416,8 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v1[i] = __fadd_rn(__fadd_rn(v1[i], l1[i]), l2[i]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            bar_arrive(bar0 + (BAR_AEMPTY + acc) * 8);            // the accumulator set may be overwritten
+            __syncwarp();
+            if (lane == 0) bar_arrive(bar0 + (BAR_AEMPTY + acc) * 8);            // the accumulator set may be overwritten
             if (!DOWN) {
                 const int64_t col = (int64_t)xt * 128 + q * 32 + lane;     // index into the expert's intermediate vector
                 const int nbi = a.inter / 32;
