@@ -5,6 +5,9 @@
 // with a barrier and one system-wide fence and counts itself in, the last one to arrive
 // publishes this rank's step number in every rank's flag word (st.release.sys) and waits,
 // bounded, until all ranks have published the current step (ld.acquire.sys).
+// Phases of the exchange kernel, stamped with %globaltimer on 4 GPUs (40960 rows per rank): copy 3.8 us, fence + count
+// 4-6.5 us, flag store 2.3 us, wait for the slowest rank 0.4-7 us.  Measured alternative, rejected: no counter, every
+// CTA releasing its own flag to every rank (16 x world st.release.sys) - 28 us against 22 us per step at 4 GPUs.
 // Measured alternative, rejected: storing the rows to the peers from the matvec kernel's own
 // epilogue (4-byte peer stores from every CTA) made the matvec 12 % slower at 2 GPUs (105 vs
 // 94 us) - with or without a system-wide fence per CTA - which costs more than this push.
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
         s_last = prev == (unsigned)ncta - 1 ? 1 : 0;
         if (s_last) {
             *counter = 0u;
-            __threadfence_system();
+            __threadfence();   // acquire side towards the other CTAs of this GPU; the flag's st.release.sys below is the system-wide release
         }
     }
     __syncthreads();
@@ -156,7 +159,7 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
         }
         if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
     }
-    __threadfence_system();
+    // thread r acquired rank r's flag (ld.acquire.sys); the barrier hands what that made visible to the threads that read the pairs
     __syncthreads();
     if (argmax != nullptr && tid < batch) {
         Best best = {-INFINITY, INT64_MAX};
