@@ -153,7 +153,7 @@ int32_t mk_dequant_mxfp4(mk_ctx *ctx, const mk_weight *w, float *out);
 
 /* dequant::dequant_fp8 (src/dequant.rs:12-41) on the GPU: e4m3fn bytes w [rows, cols] with one ue8m0
  * scale byte per 128 x 128 block (scales [ceil(rows/128), ceil(cols/128)]) -> f32 [rows, cols].
- * HOST in / HOST out; bit-identical (DeepSeek spine weights; no BASELINE config runs them). */
+ * HOST in / HOST out; bit-identical (the DeepSeek spine weights, src/dequant.rs). */
 int32_t mk_dequant_fp8(mk_ctx *ctx, const uint8_t *w, const uint8_t *scales, int64_t rows, int64_t cols, float *out);
 
 /* mxfp4::dequant_any (src/mxfp4.rs:228-240) on the GPU: a raw blob of either MXFP4 flavour as it sits in a model file
@@ -262,7 +262,12 @@ int32_t mk_attn_res_dev(mk_ctx *ctx, const float *prefix, const float *blocks, i
  *                      stand-in buffer, its flag never arrives, and every call reports
  *                      MK_ERR_TIMEOUT in the status word after the bounded wait (about half
  *                      a second) instead of hanging
- * world <= 8, max_batch <= 2 (decode).  Every rank must make the same sequence of calls. */
+ * world <= 8, max_batch <= 2 (decode).  Every rank must make the same sequence of calls.
+ * After a timeout: the two-buffer rule (a rank is at most one step ahead of a peer that still reads) holds only while
+ * no wait runs out.  A rank whose wait ran out goes on and could, two steps later, overwrite a buffer that a merely
+ * slow peer still reads - and only the rank that timed out sees MK_ERR_TIMEOUT.  So every rank reads mk_status_word
+ * after each step (or each token); on MK_ERR_TIMEOUT on any rank, all ranks stop calling, free the gather objects
+ * (mk_gather_free) and build new ones.  The same holds for mk_moe_ep below. */
 typedef struct mk_gather mk_gather;
 int32_t mk_gather_create(mk_ctx *ctx, int32_t rank, int32_t world, int64_t vocab, int32_t max_batch, mk_gather **out,
                          uint8_t *handle);

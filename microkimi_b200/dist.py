@@ -126,6 +126,21 @@ class FusedVocabHead:
         self._h = None
 
 
+def check_expert_coverage(resident, group=None, device=None):
+    """`resident`: bool per routed expert, True where this rank holds the expert.  All-gathers the maps and raises on every
+    rank unless each routed expert is resident on exactly one rank: an expert nobody holds would leave its (token, slot)
+    row of the exchange table unwritten and the combine would sum a stale row."""
+    mine = torch.as_tensor(resident, dtype=torch.uint8, device=device).contiguous().view(-1)
+    world = dist.get_world_size(group)
+    allm = torch.empty((world, mine.numel()), dtype=torch.uint8, device=mine.device)
+    dist.all_gather_into_tensor(allm.view(-1), mine, group=group)
+    count = allm.to(torch.int32).sum(0).cpu()
+    missing = torch.nonzero(count == 0).view(-1).tolist()
+    doubled = torch.nonzero(count > 1).view(-1).tolist()
+    if missing or doubled:
+        raise ValueError(f"expert partition is not a cover: resident nowhere {missing[:8]}, on several ranks {doubled[:8]}")
+
+
 class PeerEpMoeLayer:
     """Expert-parallel MoE for decode without a collective library call per layer: token rows are
     replicated on every rank (<= 16), each rank runs the pairs of its resident experts and the
@@ -138,6 +153,7 @@ class PeerEpMoeLayer:
         from . import lib as _l
         self.layer, self.ctx = layer, layer.ctx
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        check_expert_coverage(layer.resident, group, torch.device("cuda", self.ctx.device))
         L = self.ctx._L
         h = C.c_void_p()
         handle = (C.c_uint8 * 64)()

@@ -468,6 +468,7 @@ class MoeLayer:
         ctx = ctx or Context.default()
         self.ctx = ctx
         self.n_experts = len(experts)
+        self.resident = [t is not None for t in experts]     # routed experts held by this GPU (expert parallelism: a subset)
         self.top_k = int(top_k)
         first = next(t for t in list(experts) + [shared] if t is not None)
         self.inter, self.d = first[0].rows, first[0].cols

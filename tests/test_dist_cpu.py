@@ -96,3 +96,32 @@ def test_partitions_cover_everything():
         for r in range(world):
             lo, hi = mkd.local_expert_range(384, world, r)
             assert bool((own[lo:hi] == r).all())
+
+
+def _coverage_worker(rank, world, port, maps, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        try:
+            mkd.check_expert_coverage(maps[rank])
+            ret[rank] = "ok"
+        except ValueError as exc:
+            ret[rank] = str(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("maps,expect", [
+    ([[True, True, False, False], [False, False, True, True]], "ok"),
+    ([[True, True, False, False], [False, False, False, True]], "resident nowhere [2]"),
+    ([[True, True, True, False], [False, False, True, True]], "on several ranks [2]"),
+])
+def test_expert_partition_must_cover_every_routed_expert_once(maps, expect):
+    """A mis-partitioned expert-parallel layer is refused on every rank when the peer exchange is set up."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = _free_port()
+    mp.spawn(_coverage_worker, args=(2, port, maps, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert expect in ret[r], ret[r]
