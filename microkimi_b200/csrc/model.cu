@@ -55,9 +55,17 @@ __global__ void mla_assemble_kernel(const float *__restrict__ kb, const float *_
 __global__ void __launch_bounds__(512) glue_kernel(const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ c,
                                                    float *__restrict__ prefix_out, float *__restrict__ push_row,
                                                    const float *__restrict__ blocks, int nb, const float *__restrict__ w,
-                                                   const float *__restrict__ ln, float eps, int d, float *__restrict__ x_out) {
+                                                   const float *__restrict__ ln, float eps, int d, float *__restrict__ x_out, int stage) {
+    // stage: the nb block rows are copied into shared memory first (one round of coalesced loads for all rows, instead
+    // of one exposed load latency per row and pass) - the launch then reserved room for them behind the scores
     extern __shared__ float gsm[];
     float *pre = gsm, *mix = gsm + d, *sc = gsm + 2 * d;
+    const float *rows = blocks;
+    if (stage && nb > 0) {
+        float *rs = gsm + 2 * d + ((nb + 1 + 3) & ~3);
+        for (int i = threadIdx.x; i < nb * d; i += blockDim.x) rs[i] = blocks[i];
+        rows = rs;
+    }
     __shared__ float s_inv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5, j8 = lane & 7, full = d & ~7;
     for (int j = tid; j < d; j += blockDim.x) {
@@ -71,7 +79,7 @@ __global__ void __launch_bounds__(512) glue_kernel(const float *__restrict__ a, 
     const float *src = pre;
     if (nb > 0) {
         for (int row = warp; row <= nb; row += nw) {     // score of block row `row`, the prefix last (as attn_res_score_kernel)
-            const float *v = row < nb ? blocks + (int64_t)row * d : pre;
+            const float *v = row < nb ? rows + (int64_t)row * d : pre;
             float acc = 0.0f;
             for (int k = 0; k < full; k += 8) acc = __fadd_rn(acc, __fmul_rn(v[k + j8], v[k + j8]));
             float ss = mkf::reduce8(acc, lane);
@@ -94,7 +102,7 @@ __global__ void __launch_bounds__(512) glue_kernel(const float *__restrict__ a, 
         __syncthreads();
         for (int j = tid; j < d; j += blockDim.x) {
             float o = 0.0f;
-            for (int i = 0; i < nb; ++i) o = __fadd_rn(o, __fmul_rn(sc[i], blocks[(int64_t)i * d + j]));
+            for (int i = 0; i < nb; ++i) o = __fadd_rn(o, __fmul_rn(sc[i], rows[(int64_t)i * d + j]));
             mix[j] = __fadd_rn(o, __fmul_rn(sc[nb], pre[j]));
         }
         __syncthreads();
@@ -598,7 +606,9 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
     const float *ga = m->embed_row, *gb = nullptr, *gc = nullptr;
     embed_row_kernel<<<(unsigned)mk_ceil_div(d, 256), 256, 0, st>>>(m->embed, m->tok, (int)c.vocab, d, m->embed_row, ctx->status_dev);
     ctx->launches++;
-    const size_t gsm_bytes = (size_t)(2 * d + m->max_blocks + 2) * 4;
+    const size_t gsm_plain = (size_t)(2 * d + m->max_blocks + 2) * 4, gsm_staged = (size_t)(2 * d + m->max_blocks + 8 + (size_t)m->max_blocks * d) * 4;
+    const int gstage = gsm_staged <= 48 * 1024 ? 1 : 0;      // rows staged when they fit the default shared-memory limit
+    const size_t gsm_bytes = gstage ? gsm_staged : gsm_plain;
     auto tap = [&](uint32_t l, int k, const float *src) -> int32_t {
         if (m->layer_hidden) MK_CUDA(cudaMemcpyAsync(m->layer_hidden + ((size_t)l * 4 + k) * d, src, (size_t)d * 4, cudaMemcpyDeviceToDevice, st));
         return MK_OK;
@@ -608,7 +618,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         int nb = ly.nb_before;
         // hidden of this layer (the previous layer's residual adds), AttnRes mix over the old block rows, rmsnorm -> x
         glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, ly.pushes ? m->blocks + (size_t)nb * d : nullptr, m->blocks, nb, ly.sa_w,
-                                               ly.input_ln, eps, d, m->x);
+                                               ly.input_ln, eps, d, m->x, gstage);
         ctx->launches++;
         if (l > 0) RC(tap(l - 1, 3, m->hidden));
         bool have_prefix = true;
@@ -639,7 +649,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         }
         // prefix2 = prefix + attn_out (or attn_out alone when the prefix became a block row), mix, rmsnorm -> x
         glue_kernel<<<1, 512, gsm_bytes, st>>>(m->attn_out, have_prefix ? m->hidden : nullptr, nullptr, m->p2, nullptr, m->blocks, nb, ly.mlp_w,
-                                               ly.post_ln, eps, d, m->x);
+                                               ly.post_ln, eps, d, m->x, gstage);
         ctx->launches++;
         RC(tap(l, 0, m->attn_out));
         RC(tap(l, 1, m->p2));
@@ -671,7 +681,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         ga = m->p2; gb = m->mlp_out;
     }
     const int nb_final = m->layers.back().nb_before + (m->layers.back().pushes ? 1 : 0);
-    glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, nullptr, m->blocks, nb_final, m->out_w, m->norm_f, eps, d, m->x);
+    glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, nullptr, m->blocks, nb_final, m->out_w, m->norm_f, eps, d, m->x, gstage);
     ctx->launches++;
     RC(tap(c.n_layers - 1, 3, m->hidden));
     if (m->gather) {

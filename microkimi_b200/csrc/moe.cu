@@ -152,28 +152,10 @@ __device__ __forceinline__ uint32_t float_order(float f) {
     const uint32_t b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-__device__ __forceinline__ void topk_token(const float *score, const float *key, int n_experts, int top_k, int tok, int lane, float *kb,
-                                           int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
-                                           int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot,
-                                           int kind, float route_scale) {
-    for (int e = lane; e < n_experts; e += 32) kb[e] = __fadd_rn(__ldcg(key + (size_t)tok * n_experts + e), 0.0f); // -0 -> +0
-    __syncwarp();
-    int my_id = 0;
-    for (int r = 0; r < top_k; ++r) {
-        float bk = -INFINITY;
-        int bi = 0x7FFFFFFF;
-        for (int e = lane; e < n_experts; e += 32) {
-            const float kv = kb[e];
-            if (kv > bk || bi == 0x7FFFFFFF) { bk = kv; bi = e; } // ascending e: the lowest index of the lane's maximum
-        }
-        const uint32_t u = bi == 0x7FFFFFFF ? 0u : float_order(bk);
-        const uint32_t gmax = __reduce_max_sync(0xFFFFFFFFu, u);
-        int gi = __reduce_min_sync(0xFFFFFFFFu, (u == gmax) ? bi : 0x7FFFFFFF);
-        if (gi == 0x7FFFFFFF) gi = 0;
-        if (lane == r) my_id = gi;
-        if (lane == 0) kb[gi] = -INFINITY; // taken; real keys are finite, so they always come first
-        __syncwarp();
-    }
+// weights and pair list of a token from its picks (lane r holds the r-th pick)
+__device__ __forceinline__ void topk_finish(const float *score, int n_experts, int top_k, int tok, int lane, int my_id, int32_t *__restrict__ ids,
+                                            float *__restrict__ wts, int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_expert,
+                                            float *__restrict__ pair_weight, int shared_slot, int kind, float route_scale) {
     const float my_sc = lane < top_k ? __ldcg(score + (size_t)tok * n_experts + my_id) : 0.0f;
     float sumw = 0.0f;
     for (int r = 0; r < top_k; ++r) sumw = __fadd_rn(sumw, __shfl_sync(0xFFFFFFFFu, my_sc, r));
@@ -197,6 +179,76 @@ __device__ __forceinline__ void topk_token(const float *score, const float *key,
         pair_expert[p] = n_experts; // the shared expert, unweighted
         pair_weight[p] = 1.0f;
     }
+}
+__device__ __forceinline__ int topk_token(const float *score, const float *key, int n_experts, int top_k, int tok, int lane, float *kb,
+                                           int32_t *__restrict__ ids, float *__restrict__ wts, int32_t *__restrict__ pair_row,
+                                           int32_t *__restrict__ pair_expert, float *__restrict__ pair_weight, int shared_slot,
+                                           int kind, float route_scale) {
+    int my_id = 0;
+    if (n_experts <= 32 * 32) {
+        // Up to 1024 experts: lane l keeps keys l, l + 32, ... in registers and its own running maximum; a round is two
+        // redux over the lanes' maxima, after which only the winner's registers change (every lane runs the same
+        // predicated code).  Same order as below: larger key first, equal keys by ascending index.
+        float kv[32];
+#pragma unroll
+        for (int s = 0; s < 32; ++s) {
+            const int e = lane + 32 * s;
+            kv[s] = e < n_experts ? __fadd_rn(__ldcg(key + (size_t)tok * n_experts + e), 0.0f) : -INFINITY; // -0 -> +0
+        }
+        for (int r = 0; r < top_k; ++r) {
+            // tournament over the 32 slots (depth 5 instead of a chain of 31): the higher slot wins only with a larger key,
+            // so the lowest index of the lane's maximum survives
+            float tv[16];
+            int ts[16];
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                const bool hi = kv[2 * s + 1] > kv[2 * s];
+                tv[s] = hi ? kv[2 * s + 1] : kv[2 * s];
+                ts[s] = hi ? 2 * s + 1 : 2 * s;
+            }
+#pragma unroll
+            for (int w = 8; w >= 1; w >>= 1) {
+#pragma unroll
+                for (int s = 0; s < w; ++s) {
+                    const bool hi = tv[2 * s + 1] > tv[2 * s];
+                    tv[s] = hi ? tv[2 * s + 1] : tv[2 * s];
+                    ts[s] = hi ? ts[2 * s + 1] : ts[2 * s];
+                }
+            }
+            const float bk = tv[0];
+            const int bs = ts[0];
+            const int bi = lane + 32 * bs;
+            const uint32_t u = bi < n_experts ? float_order(bk) : 0u;
+            const uint32_t gmax = __reduce_max_sync(0xFFFFFFFFu, u);
+            int gi = __reduce_min_sync(0xFFFFFFFFu, (u == gmax) ? bi : 0x7FFFFFFF);
+            if (gi == 0x7FFFFFFF) gi = 0;
+            if (lane == r) my_id = gi;
+            const int ws = (gi & 31) == lane ? (gi >> 5) : -1;  // taken; real keys are finite, so they always come first
+#pragma unroll
+            for (int s = 0; s < 32; ++s)
+                if (s == ws) kv[s] = -INFINITY;
+        }
+    } else {
+    for (int e = lane; e < n_experts; e += 32) kb[e] = __fadd_rn(__ldcg(key + (size_t)tok * n_experts + e), 0.0f); // -0 -> +0
+    __syncwarp();
+    for (int r = 0; r < top_k; ++r) {
+        float bk = -INFINITY;
+        int bi = 0x7FFFFFFF;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float kv = kb[e];
+            if (kv > bk || bi == 0x7FFFFFFF) { bk = kv; bi = e; } // ascending e: the lowest index of the lane's maximum
+        }
+        const uint32_t u = bi == 0x7FFFFFFF ? 0u : float_order(bk);
+        const uint32_t gmax = __reduce_max_sync(0xFFFFFFFFu, u);
+        int gi = __reduce_min_sync(0xFFFFFFFFu, (u == gmax) ? bi : 0x7FFFFFFF);
+        if (gi == 0x7FFFFFFF) gi = 0;
+        if (lane == r) my_id = gi;
+        if (lane == 0) kb[gi] = -INFINITY; // taken; real keys are finite, so they always come first
+        __syncwarp();
+    }
+    }
+    topk_finish(score, n_experts, top_k, tok, lane, my_id, ids, wts, pair_row, pair_expert, pair_weight, shared_slot, kind, route_scale);
+    return my_id;   // lane r: the r-th pick
 }
 
 __global__ void __launch_bounds__(128)
@@ -335,7 +387,35 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    {
+    __shared__ int s_planned;
+    if (threadIdx.x == 0) s_planned = 0;
+    if (n_tokens == 1) {
+        // one token: warp 0 picks, writes weights and pairs and, when every pick is resident here and no shared slot or
+        // expert parallelism is involved, the grouping as well: one work item per pick, ordered by expert (the picks
+        // are distinct)
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (warp == 0) {
+            const int my_id = topk_token(a.score, a.key, n_experts, a.top_k, 0, lane, rsm, a.ids, a.wts, a.pair_row, a.pair_expert,
+                                         a.pair_weight, a.shared_slot, a.router_kind, a.route_scale);
+            const bool res = lane < a.top_k ? a.wv[(size_t)my_id * 3] != nullptr : true;
+            const bool fast = __all_sync(0xFFFFFFFFu, res) && a.shared_slot == 0 && a.ep_world == 0 && a.top_k <= a.max_items;
+            if (fast) {
+                int rank = 0;
+                for (int j = 0; j < a.top_k; ++j) rank += __shfl_sync(0xFFFFFFFFu, my_id, j) < my_id ? 1 : 0;
+                if (lane < a.top_k) {
+                    a.sorted[rank] = lane;
+                    a.items[rank * 3 + 0] = my_id;
+                    a.items[rank * 3 + 1] = rank;
+                    a.items[rank * 3 + 2] = 1;
+                }
+                if (lane == 0) {
+                    *a.n_items = a.top_k;
+                    if (a.n_local) *a.n_local = a.top_k;
+                    s_planned = 1;
+                }
+            }
+        }
+    } else {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
         for (int tok = warp; tok < n_tokens; tok += nw)
             topk_token(a.score, a.key, n_experts, a.top_k, tok, lane, rsm + (size_t)warp * n_experts, a.ids, a.wts, a.pair_row,
@@ -343,9 +423,11 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
     }
     __threadfence_block();
     __syncthreads();
+    if (s_planned) return;
     const int slots = a.top_k + (a.shared_slot ? 1 : 0);
     plan_small(a.pair_expert, n_tokens * slots, n_experts + 1, a.wv, a.sorted, a.items, a.n_items, a.max_items, a.status, (int *)rsm, slots,
                a.ep_rank, a.ep_world, a.n_local);
+    __syncthreads();
 }
 
 // ------------------------------------------------------------------ plan
@@ -1073,7 +1155,7 @@ __global__ void __launch_bounds__(256) moe_add_rows_kernel(float *__restrict__ o
 }
 
 // One token through a narrow router (d <= 2048): 32 experts per CTA, each row's dot by one lane octet.
-using RtOne = mkf::TileShape<32, 1, 128, 4>;
+using RtOne = mkf::TileShape<32, 1, 256, 3>;   // one token: few, long slices - the router rows come cold from HBM and every slice wait is a round trip
 
 // The K3 latent layer for one token, as independent chains (see mk_moe_forward_k3_split in mk_common.cuh):
 //   main : [routed_down; shared gate; shared up] x  (one stacked matvec) -> q8 of h -> (router done) gate/up -> down ->
@@ -1387,3 +1469,4 @@ extern "C" int32_t mk_moe_forward(mk_ctx *ctx, mk_moe *m, const float *x, int32_
     MK_CUDA(cudaStreamSynchronize(ctx->stream));
     return MK_OK;
 }
+
