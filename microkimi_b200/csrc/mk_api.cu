@@ -45,6 +45,8 @@ extern "C" int32_t mk_init(int32_t device, mk_ctx **out) {
     if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int32_t));
     if (e == cudaSuccess) e = cudaMalloc(&c->zeros_dev, 256);
     if (e == cudaSuccess) e = cudaMemset(c->zeros_dev, 0, 256);
+    if (e == cudaSuccess) e = cudaMalloc(&c->argmax_count, 64 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(c->argmax_count, 0, 64 * sizeof(unsigned));
     if (e != cudaSuccess) {
         mk_set_error("mk_init: %s", cudaGetErrorString(e));
         delete c;
@@ -64,6 +66,7 @@ extern "C" int32_t mk_shutdown(mk_ctx *ctx) {
     if (ctx->io_pinned) cudaFreeHost(ctx->io_pinned);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->zeros_dev) cudaFree(ctx->zeros_dev);
+    if (ctx->argmax_count) cudaFree(ctx->argmax_count);
     if (ctx->prof_pairs) {
         for (int i = 0; i < ctx->prof_cap; ++i) {
             cudaEventDestroy(ctx->prof_pairs[i].a);

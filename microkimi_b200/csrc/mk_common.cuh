@@ -79,6 +79,7 @@ struct mk_ctx {
     int64_t launches;
     int32_t *status_dev;    // device status word
     int8_t *zeros_dev;      // 256 zero bytes (B operand of unused MMA columns)
+    unsigned *argmax_count; // 64 counters, 0 between calls: CTAs of the greedy-pick kernel that have finished, per row
     // activation workspace (grown on demand, never per call once warm)
     void *ws;
     size_t ws_bytes;
