@@ -397,20 +397,23 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
         if (warp == 0) {
             const int my_id = topk_token(a.score, a.key, n_experts, a.top_k, 0, lane, rsm, a.ids, a.wts, a.pair_row, a.pair_expert,
                                          a.pair_weight, a.shared_slot, a.router_kind, a.route_scale);
-            const bool res = lane < a.top_k ? a.wv[(size_t)my_id * 3] != nullptr : true;
-            const bool fast = __all_sync(0xFFFFFFFFu, res) && a.shared_slot == 0 && a.ep_world == 0 && a.top_k <= a.max_items;
+            // the shared expert, when the layer has one, is pair top_k with the largest expert number: the last work item
+            const int n_it = a.top_k + (a.shared_slot ? 1 : 0);
+            const int my_e = lane < a.top_k ? my_id : n_experts;
+            const bool res = lane < n_it ? a.wv[(size_t)my_e * 3] != nullptr : true;
+            const bool fast = __all_sync(0xFFFFFFFFu, res) && a.ep_world == 0 && n_it <= a.max_items;
             if (fast) {
                 int rank = 0;
-                for (int j = 0; j < a.top_k; ++j) rank += __shfl_sync(0xFFFFFFFFu, my_id, j) < my_id ? 1 : 0;
-                if (lane < a.top_k) {
+                for (int j = 0; j < a.top_k; ++j) rank += __shfl_sync(0xFFFFFFFFu, my_id, j) < my_e ? 1 : 0;
+                if (lane < n_it) {
                     a.sorted[rank] = lane;
-                    a.items[rank * 3 + 0] = my_id;
+                    a.items[rank * 3 + 0] = my_e;
                     a.items[rank * 3 + 1] = rank;
                     a.items[rank * 3 + 2] = 1;
                 }
                 if (lane == 0) {
-                    *a.n_items = a.top_k;
-                    if (a.n_local) *a.n_local = a.top_k;
+                    *a.n_items = n_it;
+                    if (a.n_local) *a.n_local = n_it;
                     s_planned = 1;
                 }
             }
