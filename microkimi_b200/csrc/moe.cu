@@ -142,6 +142,80 @@ moe_router_tile_kernel(const float *__restrict__ gate_w, const float *__restrict
     if (valid) router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, l, kind);
 }
 
+
+// Register-tiled form for many tokens (>= 128): one CTA = 16 experts x 32 tokens, every lane octet 4 experts x 4 tokens.
+// Each of the 16 (expert, token) pairs of an octet keeps the engine's dot(): lane j sums the columns = j (mod 8) in
+// ascending order with a separate multiply and add, then the 8 partial sums fold in the engine's tree (mkf::reduce8).
+// Against the 2 x 16 shape this reads each router row and token row 6 x less often from L2 (1.6 GB -> 0.26 GB at
+// batch 256), which is what bounded it.  Slices of 128 columns, 3 in flight (cp.async); d % 4 == 0, 16-byte aligned rows.
+constexpr int RG_TE = 16, RG_TT = 32, RG_KC = 128, RG_ST = 3, RG_LD = RG_KC + 8, RG_ROWS = RG_TE + RG_TT;
+constexpr size_t RG_SMEM = (size_t)RG_ST * RG_ROWS * RG_LD * sizeof(float);
+__global__ void __launch_bounds__(256)
+moe_router_gemm_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
+                       float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key, int n_experts, int d,
+                       int n_tokens, int kind) {
+    extern __shared__ __align__(16) float gsm[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, oct = tid >> 3, j = lane & 7;
+    const int e0 = blockIdx.x * RG_TE, t0 = blockIdx.y * RG_TT;
+    const int ne = min(RG_TE, n_experts - e0), nt = min(RG_TT, n_tokens - t0);
+    // octet -> experts eg, eg + 4, eg + 8, eg + 12 and tokens tg, tg + 8, tg + 16, tg + 24: the four octets of a warp share their
+    // router rows (one broadcast read) and read neighbouring token rows (8 banks apart)
+    const int eg = oct >> 3, tg = oct & 7;
+    const int full = d & ~7, nch = (full + RG_KC - 1) / RG_KC;
+    auto issue = [&](int ch) {
+        float *stage = gsm + (size_t)(ch % RG_ST) * RG_ROWS * RG_LD;
+        const int c0 = ch * RG_KC;
+        for (int idx = tid; idx < RG_ROWS * (RG_KC / 4); idx += 256) {
+            const int r = idx / (RG_KC / 4), c = c0 + (idx % (RG_KC / 4)) * 4;
+            if (c >= full) continue;
+            const float *src = r < RG_TE ? gate_w + (size_t)(e0 + min(r, ne - 1)) * d + c : x + (size_t)(t0 + min(r - RG_TE, nt - 1)) * d + c;
+            mkf::cp16(stage + r * RG_LD + (c - c0), src);
+        }
+    };
+    for (int sidx = 0; sidx < RG_ST - 1; ++sidx) {
+        if (sidx < nch) issue(sidx);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+    for (int ch = 0; ch < nch; ++ch) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(RG_ST - 2) : "memory");
+        __syncthreads();
+        if (ch + RG_ST - 1 < nch) issue(ch + RG_ST - 1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const float *stage = gsm + (size_t)(ch % RG_ST) * RG_ROWS * RG_LD;
+        const float *ws = stage + eg * RG_LD + j, *xr = stage + (RG_TE + tg) * RG_LD + j;
+        const int kmax = min(RG_KC, full - ch * RG_KC);
+#pragma unroll 4
+        for (int c = 0; c < kmax; c += 8) {
+            float wv[4], xv[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { wv[a] = ws[(4 * a) * RG_LD + c]; xv[a] = xr[(8 * a) * RG_LD + c]; }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(wv[a], xv[b]));
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            float sres = mkf::reduce8(acc[a][b], lane);
+            const int el = eg + 4 * a, tl = tg + 8 * b;
+            if (j == 0 && el < ne && tl < nt) {
+                const int e = e0 + el, tok = t0 + tl;
+                for (int c = full; c < d; ++c) sres = __fadd_rn(sres, __fmul_rn(__ldg(gate_w + (size_t)e * d + c), __ldg(x + (size_t)tok * d + c)));
+                router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, sres, kind);
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ top-k
 // One warp per token.  The top_k by (key descending, index ascending) in that order is
 // what the engine's running selection ends with (src/model.rs:2157-2171); weights =
@@ -992,10 +1066,18 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
                 MK_CUDA(cudaFuncSetAttribute(moe_router_tile_kernel<RtSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RtSmall::SMEM));
                 attr.mark(ctx->device);
             }
-            if (n <= RtSmall::NT)
+            if (n <= RtSmall::NT) {
                 moe_router_tile_kernel<RtSmall><<<dim3((unsigned)mk_ceil_div(E, RtSmall::NE), 1), 256, RtSmall::SMEM, ctx->stream>>>(
                     m->gate_w, m->gate_b, x, m->logits, score, key, E, m->dx, n, m->router_kind);
-            else
+            } else if (n >= 4 * RG_TT) {   // fewer tokens leave too few CTAs (48 at 64 tokens x 384 experts): the 2 x 16 shape is faster there
+                static mk_once_per_device attr_g;
+                if (attr_g.pending(ctx->device)) {
+                    MK_CUDA(cudaFuncSetAttribute(moe_router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RG_SMEM));
+                    attr_g.mark(ctx->device);
+                }
+                moe_router_gemm_kernel<<<dim3((unsigned)mk_ceil_div(E, RG_TE), (unsigned)mk_ceil_div(n, RG_TT)), 256, RG_SMEM, ctx->stream>>>(
+                    m->gate_w, m->gate_b, x, m->logits, score, key, E, m->dx, n, m->router_kind);
+            } else
                 moe_router_tile_kernel<RtBig><<<dim3((unsigned)mk_ceil_div(E, RtBig::NE), (unsigned)mk_ceil_div(n, RtBig::NT)), 256,
                                                 RtBig::SMEM, ctx->stream>>>(m->gate_w, m->gate_b, x, m->logits, score, key, E, m->dx, n, m->router_kind);
         } else if (n >= 4) {
