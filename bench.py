@@ -358,7 +358,7 @@ def measure_mla(torch, mk, ctx, dev, layout, ctx_len, batch, steps, warmup):
 def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=64, n_new=256, cpu_tokens=0, path=None):
     """Whole-token decode of the 93-layer micro skeleton (the engine's historical configuration: 69 KDA + 24 MLA layers,
     896 MXFP4 experts top-16 per MoE layer, q8_0 lm_head over 163840 rows, q8_0 MLA caches): a synthetic model file with the
-    builder's shapes and distributions, a seeded 64-token prompt fed token by token, then 256 greedy steps whose token ids
+    builder's shapes and distributions, a seeded 64-token prompt prefilled layer by layer (one GPU), then 256 greedy steps whose token ids
     never leave the GPU.  One CUDA graph replay per token at N = 1; at N > 1 the experts are block-partitioned over the ranks
     and the lm_head rows sharded, exchanged by peer-memory stores, launched kernel by kernel."""
     import tempfile
@@ -399,9 +399,20 @@ def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=6
                 dist.barrier()
                 torch.cuda.synchronize()
         sync_all()
+        # the prompt once token by token (the decode path; kept for comparison) ...
+        ptok = torch.from_numpy(prompt).to(dev)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for i in range(n_prompt):
+            model.forward_dev(ptok[i:i + 1])
+        s1.record(stream)
+        sync_all()
+        out["prompt_token_by_token_ms_per_token"] = s0.elapsed_time(s1) / n_prompt
+        model.reset()
+        sync_all()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record(stream)
-        first = model.generate(prompt, 1)         # the prompt, token by token (returns after its own synchronization)
+        first = model.generate(prompt, 1)         # ... and layer by layer (mk_model_generate prefills; returns after its own synchronization)
         e1.record(stream)
         for _ in range(n_new):
             model.forward_dev(None)               # the previous pick, on the device
@@ -411,7 +422,8 @@ def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=6
         if dist is not None and world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         prefill_ms, decode_ms = float(t[0].item()), float(t[1].item())
-        out.update({"prompt_ms_per_token": prefill_ms / n_prompt, "decode_ms_per_token": decode_ms / n_new,
+        out.update({"prompt_ms_per_token": prefill_ms / n_prompt, "prefill_tokens_per_s": n_prompt / (prefill_ms * 1e-3),
+                    "decode_ms_per_token": decode_ms / n_new,
                     "decode_tokens_per_s": n_new / (decode_ms * 1e-3), "launches_per_token": model.launches_per_token,
                     "first_token": int(first[0]), "status_word": own.status_word()})
         # end to end: every token id goes back to the host before the next step starts (the engine's loop prints and tests it)

@@ -234,6 +234,11 @@ int32_t mk_kda_reset(mk_ctx *ctx, mk_kda *kda);   /* zero state: KdaCache::new *
  * practice expf differ (tests hold it to 1e-6 relative). */
 int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *kda, const float *q_raw, const float *k_raw, const float *v_raw,
                         const float *g_low, const float *beta_raw, const float *g2, float *o);
+/* n_tok consecutive positions in one launch (the engine's kda_prefill loop, src/model.rs:1281-1300): token t reads its
+ * q / k / v / g2 / beta rows t * ld_x floats after the given pointers, its g_low row t * ld_g floats on, and writes its
+ * output row t * ld_o floats on.  Bit-identical to n_tok calls of mk_kda_step_dev; the state is read and written once. */
+int32_t mk_kda_steps_dev(mk_ctx *ctx, mk_kda *kda, int32_t n_tok, const float *q_raw, const float *k_raw, const float *v_raw,
+                         const float *g_low, const float *beta_raw, const float *g2, float *o, int64_t ld_x, int64_t ld_g, int64_t ld_o);
 /* State to / from HOST memory (cache snapshots for speculative rollback, src/spec.rs:214, 294-299;
  * .mkmem files): s [heads][dim][dim]; conv [3 (q, k, v)][kconv - 1][heads * dim], oldest input first
  * (the layout of KdaCache::conv_q / conv_k / conv_v). */
@@ -498,6 +503,12 @@ int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t *token, flo
 int32_t mk_model_forward(mk_ctx *ctx, mk_model *m, int32_t token, float *logits, int32_t *next);
 /* The greedy loop of run_turn (src/model.rs:3586-3593): n_prompt prompt tokens one by one, then n_new picks, each
  * fed back as the next token on the device; out_tokens HOST int32 [n_new]; one synchronization at the end. */
+/* Layer-major prefill of n prompt tokens (Model::prefill, src/model.rs:3043-3260): per layer the projections, the
+ * FFN and the AttnRes glue run once for all tokens, the KDA step and the MLA append + attention position by position
+ * (the engine's sequential kda_prefill branch, src/model.rs:1291-1300: bit-identical to n single-token calls, and
+ * so is this).  tokens: HOST int32 [n]; logits (optional, HOST f32 [vocab]) and next (optional, HOST) belong to the
+ * LAST token.  Continues the sequence like mk_model_forward; any n, processed in pieces of 256 tokens. */
+int32_t mk_model_prefill(mk_ctx *ctx, mk_model *m, const int32_t *tokens, int32_t n, float *logits, int32_t *next);
 int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_new, int32_t *out_tokens);
 /* Per-layer taps of the last token, HOST f32 [n_layers][4][d] (needs opts.keep_layer_hidden): the attention block's
  * output, the residual stream after it, the FFN's output, the residual stream after the layer. */

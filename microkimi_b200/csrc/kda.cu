@@ -51,6 +51,10 @@ struct KdaArgs {
     float *conv, *s, *o;
     int heads, dim, kconv;
     float gate_lb, rms_eps, q_scale;
+    // several consecutive positions in one launch (kda_step_kernel only): token t reads its q / k / v / g2 / beta rows
+    // t * ld_x floats on, its low-rank gate row t * ld_g on, and writes its output row t * ld_o on
+    int n_tok;
+    int64_t ld_x, ld_g, ld_o;
 };
 
 // One channel's conv inputs, loaded before any arithmetic so that all global loads of a thread are in flight
@@ -111,29 +115,37 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
     const int64_t cq = 0, ck = (int64_t)(a.kconv - 1) * proj, cv = 2 * (int64_t)(a.kconv - 1) * proj; // their windows
     float *col = a.s + (int64_t)h * dim * dim + c;
     float x[DIM > 0 ? DIM : 1];
+    // n_tok consecutive positions: the column stays in registers from one position to the next (DIM > 0) and is
+    // written back after the last one; each position's arithmetic is that of a launch of its own
+    for (int tt = 0; tt < a.n_tok; ++tt) {
+    const float *q_raw = a.q_raw + tt * a.ld_x, *k_raw = a.k_raw + tt * a.ld_x, *v_raw = a.v_raw + tt * a.ld_x;
+    const float *g2_in = a.g2 + tt * a.ld_x, *beta_in = a.beta_raw + tt * a.ld_x, *glow_in = a.g_low + tt * a.ld_g;
+    const bool last_tok = tt == a.n_tok - 1;
     float vv = 0.0f, g2v = 0.0f, onv = 0.0f, bh = 0.0f;
     if (active) {
         float glow, dtb, alog;
         ConvIn<KC> iq, ik, iv;
         if constexpr (KC > 0) {
-            iq.load(a.conv_w + wq, a.conv + cq, proj, i, a.q_raw);
-            ik.load(a.conv_w + wk, a.conv + ck, proj, i, a.k_raw);
-            iv.load(a.conv_w + wv, a.conv + cv, proj, i, a.v_raw);
+            iq.load(a.conv_w + wq, a.conv + cq, proj, i, q_raw);
+            ik.load(a.conv_w + wk, a.conv + ck, proj, i, k_raw);
+            iv.load(a.conv_w + wv, a.conv + cv, proj, i, v_raw);
         }
-        glow = a.g_low[i]; dtb = a.dt_bias[i]; alog = a.a_log[c];
-        g2v = a.g2[i]; onv = a.o_norm[c]; bh = a.beta_raw[h];
+        glow = glow_in[i]; dtb = a.dt_bias[i]; alog = a.a_log[c];
+        g2v = g2_in[i]; onv = a.o_norm[c]; bh = beta_in[h];
         if constexpr (DIM > 0) {
+            if (tt == 0) {
 #pragma unroll
-            for (int r = 0; r < DIM; ++r) x[r] = col[(int64_t)r * DIM];
+                for (int r = 0; r < DIM; ++r) x[r] = col[(int64_t)r * DIM];
+            }
         }
         if constexpr (KC > 0) {
             qs[c] = iq.apply(a.conv + cq, proj, i);
             ks[c] = ik.apply(a.conv + ck, proj, i);
             vv = iv.apply(a.conv + cv, proj, i);
         } else {
-            qs[c] = conv_channel(a.conv_w + wq, a.conv + cq, proj, i, a.kconv, a.q_raw[i]);
-            ks[c] = conv_channel(a.conv_w + wk, a.conv + ck, proj, i, a.kconv, a.k_raw[i]);
-            vv = conv_channel(a.conv_w + wv, a.conv + cv, proj, i, a.kconv, a.v_raw[i]);
+            qs[c] = conv_channel(a.conv_w + wq, a.conv + cq, proj, i, a.kconv, q_raw[i]);
+            ks[c] = conv_channel(a.conv_w + wk, a.conv + ck, proj, i, a.kconv, k_raw[i]);
+            vv = conv_channel(a.conv_w + wv, a.conv + cv, proj, i, a.kconv, v_raw[i]);
         }
         const float g = __fmul_rn(a.gate_lb, sigmoid_cr(__fmul_rn(exp_cr(alog), __fadd_rn(glow, dtb))));
         ds[c] = exp_cr(g);
@@ -169,7 +181,7 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
             for (int r = 0; r < DIM; ++r) {
                 x[r] = __fadd_rn(x[r], __fmul_rn(__fmul_rn(bh, ks[r]), delta));
                 o = __fadd_rn(o, __fmul_rn(qs[r], x[r]));
-                col[(int64_t)r * DIM] = x[r];
+                if (last_tok) col[(int64_t)r * DIM] = x[r];
             }
         } else {
             for (int r = 0; r < dim; ++r) {
@@ -192,7 +204,9 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
         if (lane == 0) red[2] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ss, a.rms_eps)));
     }
     __syncthreads();
-    if (active) a.o[i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), onv), g2v);
+    if (active) a.o[tt * a.ld_o + i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[2]), onv), g2v);
+    __syncthreads();            // qs, ks, ds and red are rewritten by the next position
+    }
 }
 
 // The same step with the head's S [dim][dim] staged in shared memory by cp.async at kernel start (dim % 4 == 0,
@@ -418,12 +432,34 @@ extern "C" int32_t mk_kda_import(mk_ctx *ctx, mk_kda *k, const float *s, const f
     return kda_state_copy(ctx, k, const_cast<float *>(s), const_cast<float *>(conv), 1);
 }
 
+static int32_t kda_steps(mk_ctx *ctx, mk_kda *k, int n_tok, const float *q_raw, const float *k_raw, const float *v_raw, const float *g_low,
+                         const float *beta_raw, const float *g2, float *o, int64_t ld_x, int64_t ld_g, int64_t ld_o);
 extern "C" int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *k, const float *q_raw, const float *k_raw, const float *v_raw,
                                    const float *g_low, const float *beta_raw, const float *g2, float *o) {
+    return kda_steps(ctx, k, 1, q_raw, k_raw, v_raw, g_low, beta_raw, g2, o, 0, 0, 0);
+}
+extern "C" int32_t mk_kda_steps_dev(mk_ctx *ctx, mk_kda *k, int32_t n_tok, const float *q_raw, const float *k_raw, const float *v_raw,
+                                    const float *g_low, const float *beta_raw, const float *g2, float *o, int64_t ld_x, int64_t ld_g, int64_t ld_o) {
+    MK_CHECK_ARG(n_tok >= 1, "n_tok >= 1 required");
+    return kda_steps(ctx, k, n_tok, q_raw, k_raw, v_raw, g_low, beta_raw, g2, o, ld_x, ld_g, ld_o);
+}
+static int32_t kda_steps(mk_ctx *ctx, mk_kda *k, int n_tok, const float *q_raw, const float *k_raw, const float *v_raw, const float *g_low,
+                         const float *beta_raw, const float *g2, float *o, int64_t ld_x, int64_t ld_g, int64_t ld_o) {
     MK_CHECK_ARG(ctx != nullptr && k != nullptr, "NULL argument");
     MK_CHECK_ARG(q_raw && k_raw && v_raw && g_low && beta_raw && g2 && o, "NULL device pointer");
     MK_CUDA(cudaSetDevice(ctx->device));
+    const bool reg_form = !((ctx->kda_smem || !(k->dim == 64 || k->dim == 128)) && k->dim % 4 == 0 && k->dim >= 32 && k->dim <= 224);
+    if (n_tok > 1 && !reg_form) {
+        // the shared-memory form takes one position per launch
+        for (int t = 0; t < n_tok; ++t) {
+            const int32_t rc = kda_steps(ctx, k, 1, q_raw + t * ld_x, k_raw + t * ld_x, v_raw + t * ld_x, g_low + t * ld_g, beta_raw + t * ld_x,
+                                         g2 + t * ld_x, o + t * ld_o, 0, 0, 0);
+            if (rc != MK_OK) return rc;
+        }
+        return MK_OK;
+    }
     KdaArgs a;
+    a.n_tok = n_tok; a.ld_x = ld_x; a.ld_g = ld_g; a.ld_o = ld_o;
     a.q_raw = q_raw; a.k_raw = k_raw; a.v_raw = v_raw; a.g_low = g_low; a.beta_raw = beta_raw; a.g2 = g2;
     a.conv_w = k->conv_w; a.a_log = k->a_log; a.dt_bias = k->dt_bias; a.o_norm = k->o_norm;
     a.conv = k->conv; a.s = k->s; a.o = o;

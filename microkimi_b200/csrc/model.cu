@@ -9,6 +9,7 @@
 // position (the MLA caches count their positions on the device), so the token is captured once as a CUDA graph
 // and replayed.  Projections that read the same vector are stacked into one f32 matrix at load: every row of a
 // stacked matvec is the dot() the engine computes for that row, so stacking changes no bit.
+#include <algorithm>
 #include <new>
 #include <string>
 #include <vector>
@@ -35,14 +36,31 @@ __global__ void vec_add_kernel(const float *__restrict__ a, const float *__restr
 }
 // K[h] = kb[h][..nope] ++ k_rot ; V[h] = kb[h][nope..nope+v] (src/model.rs:1964-1973)
 __global__ void mla_assemble_kernel(const float *__restrict__ kb, const float *__restrict__ k_rot, int H, int nope, int rope, int vd,
-                                    float *__restrict__ k_new, float *__restrict__ v_new) {
+                                    float *__restrict__ k_new, float *__restrict__ v_new, int64_t ld_rot) {
+    // blockIdx.y = token: kb [tokens][H (nope + v)], k_rot rows ld_rot floats apart, k_new [tokens][H (nope + rope)], v_new [tokens][H v]
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int qh = nope + rope, per = qh + vd;
     if (i >= H * per) return;
+    const int64_t t = blockIdx.y;
+    kb += t * H * (nope + vd);
+    k_rot += t * ld_rot;
+    k_new += t * H * qh;
+    v_new += t * H * vd;
     const int h = i / per, r = i % per;
     if (r < nope) k_new[h * qh + r] = kb[h * (nope + vd) + r];
     else if (r < qh) k_new[h * qh + r] = k_rot[r - nope];
     else v_new[h * vd + (r - qh)] = kb[h * (nope + vd) + nope + (r - qh)];
+}
+// rows of n tokens' embeddings (layer-major prefill)
+__global__ void embed_rows_kernel(const float *__restrict__ embed, const int32_t *__restrict__ tokens, int vocab, int d, float *__restrict__ out,
+                                  int32_t *__restrict__ status) {
+    int t = tokens[blockIdx.y];
+    if (t < 0 || t >= vocab) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(status, 0, MK_ERR_ARG);
+        t = 0;
+    }
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < d) out[(int64_t)blockIdx.y * d + j] = embed[(int64_t)t * d + j];
 }
 // The glue between two blocks in ONE launch (src/model.rs:2905-2920, 2943-2959, 2994-2996, 3014-3017):
 //   prefix = a [+ (b [+ c])]     residual adds: hidden = prefix2 + mlp_out with mlp_out = routed + shared, or prefix + attn_out
@@ -55,7 +73,20 @@ __global__ void mla_assemble_kernel(const float *__restrict__ kb, const float *_
 __global__ void __launch_bounds__(512) glue_kernel(const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ c,
                                                    float *__restrict__ prefix_out, float *__restrict__ push_row,
                                                    const float *__restrict__ blocks, int nb, const float *__restrict__ w,
-                                                   const float *__restrict__ ln, float eps, int d, float *__restrict__ x_out, int stage) {
+                                                   const float *__restrict__ ln, float eps, int d, float *__restrict__ x_out, int stage,
+                                                   int64_t tok_vec, int64_t tok_blocks) {
+    // one CTA per token (layer-major prefill: gridDim.x tokens; decode: one): token t's vectors lie t * tok_vec floats on,
+    // its AttnRes block rows t * tok_blocks floats on
+    {
+        const int64_t ov = (int64_t)blockIdx.x * tok_vec, ob = (int64_t)blockIdx.x * tok_blocks;
+        a += ov;
+        if (b) b += ov;
+        if (c) c += ov;
+        if (prefix_out) prefix_out += ov;
+        if (push_row) push_row += ob;
+        blocks += ob;
+        x_out += ov;
+    }
     // stage: the nb block rows are copied into shared memory first (one round of coalesced loads for all rows, instead
     // of one exposed load latency per row and pass) - the launch then reserved room for them behind the scores
     extern __shared__ float gsm[];
@@ -202,6 +233,13 @@ struct mk_model {
     float *layer_hidden = nullptr;   // opts.keep_layer_hidden: [n_layers][4][d] taps of the last token (see mk_model_layer_hidden)
     int32_t *tok = nullptr, *next = nullptr;
     int positions = 0;
+    // layer-major prefill (mk_model_prefill): activations of up to pf_cap tokens, allocated at the first call
+    int pf_cap = 0;
+    int32_t *pf_tok = nullptr;
+    float *pf_hidden = nullptr, *pf_x = nullptr, *pf_attn_out = nullptr, *pf_p2 = nullptr, *pf_mlp_out = nullptr, *pf_blocks = nullptr, *pf_embed = nullptr;
+    float *pf_y = nullptr, *pf_g_low = nullptr, *pf_o = nullptr, *pf_fa = nullptr;
+    float *pf_qa = nullptr, *pf_qan = nullptr, *pf_q = nullptr, *pf_kva = nullptr, *pf_kpn = nullptr, *pf_kb = nullptr, *pf_k_new = nullptr, *pf_v_new = nullptr, *pf_attn = nullptr;
+    float *pf_au = nullptr, *pf_act = nullptr;
     int64_t launches_per_token = 0;
     uint8_t handles[128] = {0};     // world > 1: IPC handles of this rank's expert-row table and logits buffer
     cudaGraphExec_t graph = nullptr;
@@ -389,6 +427,10 @@ void free_model(mk_ctx *ctx, mk_model *m) {
     if (m->gather) mk_gather_free(ctx, m->gather);
     if (m->ep) mk_moe_ep_free(ctx, m->ep);
     for (void *p : m->owned) cudaFree(p);
+    float *pf[] = {m->pf_hidden, m->pf_x, m->pf_attn_out, m->pf_p2, m->pf_mlp_out, m->pf_blocks, m->pf_embed, m->pf_y, m->pf_g_low, m->pf_o, m->pf_fa,
+                   m->pf_qa, m->pf_qan, m->pf_q, m->pf_kva, m->pf_kpn, m->pf_kb, m->pf_k_new, m->pf_v_new, m->pf_attn, m->pf_au, m->pf_act};
+    for (float *p : pf) if (p) cudaFree(p);
+    if (m->pf_tok) cudaFree(m->pf_tok);
     delete m;
 }
 
@@ -618,7 +660,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         int nb = ly.nb_before;
         // hidden of this layer (the previous layer's residual adds), AttnRes mix over the old block rows, rmsnorm -> x
         glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, ly.pushes ? m->blocks + (size_t)nb * d : nullptr, m->blocks, nb, ly.sa_w,
-                                               ly.input_ln, eps, d, m->x, gstage);
+                                               ly.input_ln, eps, d, m->x, gstage, 0, 0);
         ctx->launches++;
         if (l > 0) RC(tap(l - 1, 3, m->hidden));
         bool have_prefix = true;
@@ -630,7 +672,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
             RC(mk_launch_f32_gemv(ctx, ly.q_b, (int64_t)H * qh, qa, m->qan, 1, m->q, (int64_t)H * qh, 0));
             RC(mk_launch_rmsnorm(ctx, y + qa, ly.kv_a_ln, 1, kva, eps, m->kpn));
             RC(mk_launch_f32_gemv(ctx, ly.kv_b, (int64_t)H * (nope + vd), kva, m->kpn, 1, m->kb, (int64_t)H * (nope + vd), 0));
-            mla_assemble_kernel<<<(unsigned)mk_ceil_div((int64_t)H * (qh + vd), 256), 256, 0, st>>>(m->kb, y + qa + kva, H, nope, rope, vd, m->k_new, m->v_new);
+            mla_assemble_kernel<<<(unsigned)mk_ceil_div((int64_t)H * (qh + vd), 256), 256, 0, st>>>(m->kb, y + qa + kva, H, nope, rope, vd, m->k_new, m->v_new, 0);
             ctx->launches++;
             const float scale = powf((float)qh, -0.5f);   // (mla_qh as f32).powf(-0.5) (src/model.rs:1977)
             const int strict_was = ctx->mla_strict;
@@ -649,7 +691,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         }
         // prefix2 = prefix + attn_out (or attn_out alone when the prefix became a block row), mix, rmsnorm -> x
         glue_kernel<<<1, 512, gsm_bytes, st>>>(m->attn_out, have_prefix ? m->hidden : nullptr, nullptr, m->p2, nullptr, m->blocks, nb, ly.mlp_w,
-                                               ly.post_ln, eps, d, m->x, gstage);
+                                               ly.post_ln, eps, d, m->x, gstage, 0, 0);
         ctx->launches++;
         RC(tap(l, 0, m->attn_out));
         RC(tap(l, 1, m->p2));
@@ -681,7 +723,7 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
         ga = m->p2; gb = m->mlp_out;
     }
     const int nb_final = m->layers.back().nb_before + (m->layers.back().pushes ? 1 : 0);
-    glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, nullptr, m->blocks, nb_final, m->out_w, m->norm_f, eps, d, m->x, gstage);
+    glue_kernel<<<1, 512, gsm_bytes, st>>>(ga, gb, gc, m->hidden, nullptr, m->blocks, nb_final, m->out_w, m->norm_f, eps, d, m->x, gstage, 0, 0);
     ctx->launches++;
     RC(tap(c.n_layers - 1, 3, m->hidden));
     if (m->gather) {
@@ -691,6 +733,128 @@ int32_t enqueue_token(mk_ctx *ctx, mk_model *m) {
     } else {
         RC(mk_matvec_q8_dev(ctx, m->head, m->x, m->logits, 1, MK_ACT_Q8 | (m->opts.strict ? MK_ACT_STRICT : 0), m->next));
     }
+#undef RC
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+
+// Layer-major prefill of n tokens (Model::prefill_impl, src/model.rs:3097-3260, with the sequential recurrence of
+// kda_prefill, src/model.rs:1291-1300, which the engine takes below its chunking threshold and calls bit-identical to
+// kda_forward per position): per layer the projections, the FFN and the AttnRes glue run once for all tokens - every
+// output row is the dot() of the single-token path, so batching changes no bit - while the KDA step and the MLA cache
+// append + attention, which carry state from one position to the next, run token by token inside the layer.
+// Leaves the caches as n single-token calls would, and logits / pick of the LAST token in m->logits / m->next.
+int32_t ensure_prefill_buffers(mk_ctx *ctx, mk_model *m, int n) {
+    if (n <= m->pf_cap) return MK_OK;
+    const mk_model_config &c = m->cfg;
+    const size_t d = c.d, proj = (size_t)c.kda_heads * c.kda_dim, H = c.mla_heads, qh = c.mla_nope + c.mla_rope, hv = H * c.mla_v;
+    const size_t ywidth = std::max<size_t>(4 * proj + c.kda_fa + c.kda_heads, c.mla_qa + c.mla_kva + c.mla_rope + hv);
+    int cap = m->pf_cap ? m->pf_cap : 16;
+    while (cap < n) cap *= 2;
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    struct Want { float **p; size_t count; };
+    const Want wants[] = {
+        {&m->pf_hidden, d}, {&m->pf_x, d}, {&m->pf_attn_out, d}, {&m->pf_p2, d}, {&m->pf_mlp_out, d}, {&m->pf_embed, d},
+        {&m->pf_blocks, (size_t)m->max_blocks * d}, {&m->pf_y, ywidth}, {&m->pf_g_low, proj}, {&m->pf_o, proj}, {&m->pf_fa, c.kda_fa},
+        {&m->pf_qa, c.mla_qa}, {&m->pf_qan, c.mla_qa}, {&m->pf_q, H * qh}, {&m->pf_kva, c.mla_kva}, {&m->pf_kpn, c.mla_kva},
+        {&m->pf_kb, H * (c.mla_nope + c.mla_v)}, {&m->pf_k_new, H * qh}, {&m->pf_v_new, hv}, {&m->pf_attn, hv},
+        {&m->pf_au, 2 * (size_t)c.dense_inter}, {&m->pf_act, c.dense_inter},
+    };
+    for (const Want &w : wants) {
+        if (*w.p) cudaFree(*w.p);
+        *w.p = nullptr;
+        MK_CUDA(cudaMalloc(w.p, std::max<size_t>(w.count, 1) * cap * sizeof(float)));
+        MK_CUDA(cudaMemsetAsync(*w.p, 0, std::max<size_t>(w.count, 1) * cap * sizeof(float), ctx->stream));
+    }
+    if (m->pf_tok) cudaFree(m->pf_tok);
+    m->pf_tok = nullptr;
+    MK_CUDA(cudaMalloc(&m->pf_tok, (size_t)cap * sizeof(int32_t)));
+    m->pf_cap = cap;
+    return MK_OK;
+}
+
+int32_t enqueue_prefill(mk_ctx *ctx, mk_model *m, int n) {
+    const mk_model_config &c = m->cfg;
+    const int d = (int)c.d, proj = (int)(c.kda_heads * c.kda_dim), H = (int)c.mla_heads, nope = (int)c.mla_nope, rope = (int)c.mla_rope;
+    const int vd = (int)c.mla_v, qh = nope + rope, qa = (int)c.mla_qa, kva = (int)c.mla_kva, cdim = kva + rope, hv = H * vd, fa = (int)c.kda_fa;
+    const float eps = c.rms_eps;
+    cudaStream_t st = ctx->stream;
+    int32_t rc;
+#define RC(call) do { rc = (call); if (rc != MK_OK) return rc; } while (0)
+    const int64_t bstride = (int64_t)m->max_blocks * d;      // a token's AttnRes block rows
+    const float *ga = m->pf_embed, *gb = nullptr;
+    embed_rows_kernel<<<dim3((unsigned)mk_ceil_div(d, 256), (unsigned)n), 256, 0, st>>>(m->embed, m->pf_tok, (int)c.vocab, d, m->pf_embed, ctx->status_dev);
+    ctx->launches++;
+    const size_t gsm_plain = (size_t)(2 * d + m->max_blocks + 2) * 4, gsm_staged = (size_t)(2 * d + m->max_blocks + 8 + (size_t)m->max_blocks * d) * 4;
+    const int gstage = gsm_staged <= 48 * 1024 ? 1 : 0;
+    const size_t gsm_bytes = gstage ? gsm_staged : gsm_plain;
+    // a strided slice [n][w] of the stacked projections (row stride ld) as contiguous rows
+    auto slice = [&](float *dst, const float *src, int w, int64_t ld) -> int32_t {
+        MK_CUDA(cudaMemcpy2DAsync(dst, (size_t)w * 4, src, (size_t)ld * 4, (size_t)w * 4, (size_t)n, cudaMemcpyDeviceToDevice, st));
+        return MK_OK;
+    };
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        Layer &ly = m->layers[l];
+        int nb = ly.nb_before;
+        glue_kernel<<<(unsigned)n, 512, gsm_bytes, st>>>(ga, gb, nullptr, m->pf_hidden, ly.pushes ? m->pf_blocks + (size_t)nb * d : nullptr, m->pf_blocks, nb,
+                                                       ly.sa_w, ly.input_ln, eps, d, m->pf_x, gstage, d, bstride);
+        ctx->launches++;
+        bool have_prefix = true;
+        if (ly.pushes) { ++nb; have_prefix = false; }
+        const int64_t ldy = ly.w_x_rows;
+        float *y = m->pf_y;
+        RC(mk_launch_f32_gemv(ctx, ly.w_x, ly.w_x_rows, d, m->pf_x, n, y, ldy, 0));
+        if (ly.is_mla) {
+            RC(slice(m->pf_qa, y, qa, ldy));
+            RC(mk_launch_rmsnorm(ctx, m->pf_qa, ly.q_a_ln, n, qa, eps, m->pf_qan));
+            RC(mk_launch_f32_gemv(ctx, ly.q_b, (int64_t)H * qh, qa, m->pf_qan, n, m->pf_q, (int64_t)H * qh, 0));
+            RC(slice(m->pf_kva, y + qa, kva, ldy));
+            RC(mk_launch_rmsnorm(ctx, m->pf_kva, ly.kv_a_ln, n, kva, eps, m->pf_kpn));
+            RC(mk_launch_f32_gemv(ctx, ly.kv_b, (int64_t)H * (nope + vd), kva, m->pf_kpn, n, m->pf_kb, (int64_t)H * (nope + vd), 0));
+            mla_assemble_kernel<<<dim3((unsigned)mk_ceil_div((int64_t)H * (qh + vd), 256), (unsigned)n), 256, 0, st>>>(
+                m->pf_kb, y + qa + kva, H, nope, rope, vd, m->pf_k_new, m->pf_v_new, ldy);
+            ctx->launches++;
+            const float scale = powf((float)qh, -0.5f);
+            const int strict_was = ctx->mla_strict;
+            if (m->opts.strict) ctx->mla_strict = 1;
+            rc = MK_OK;
+            for (int t = 0; t < n && rc == MK_OK; ++t) {      // append + causal attention, position by position
+                rc = mk_mla_decode_step_dev(ctx, ly.cache, 0, m->pf_k_new + (size_t)t * H * qh, m->pf_v_new + (size_t)t * hv, m->pf_q + (size_t)t * H * qh,
+                                            scale, m->pf_attn + (size_t)t * hv);
+                if (rc == MK_OK) rc = mk_sigmoid_gate_dev(ctx, m->pf_attn + (size_t)t * hv, y + (size_t)t * ldy + qa + cdim, hv);
+            }
+            ctx->mla_strict = strict_was;
+            if (rc != MK_OK) return rc;
+            RC(mk_launch_f32_gemv(ctx, ly.o_proj, d, hv, m->pf_attn, n, m->pf_attn_out, d, 0));
+        } else {
+            RC(slice(m->pf_fa, y + 4 * proj, fa, ldy));
+            RC(mk_launch_f32_gemv(ctx, ly.f_b, proj, fa, m->pf_fa, n, m->pf_g_low, proj, 0));
+            // conv state and recurrence, position by position inside one launch (the state stays in registers)
+            RC(mk_kda_steps_dev(ctx, ly.kda, n, y, y + proj, y + 2 * proj, m->pf_g_low, y + 4 * proj + fa, y + 3 * proj, m->pf_o, ldy, proj, proj));
+            RC(mk_launch_f32_gemv(ctx, ly.o_proj, d, proj, m->pf_o, n, m->pf_attn_out, d, 0));
+        }
+        glue_kernel<<<(unsigned)n, 512, gsm_bytes, st>>>(m->pf_attn_out, have_prefix ? m->pf_hidden : nullptr, nullptr, m->pf_p2, nullptr, m->pf_blocks, nb,
+                                                       ly.mlp_w, ly.post_ln, eps, d, m->pf_x, gstage, d, bstride);
+        ctx->launches++;
+        if (ly.is_moe) {
+            RC(mk_moe_forward_dev(ctx, ly.moe, m->pf_x, n, m->pf_mlp_out, nullptr, nullptr));
+        } else {
+            const int di = (int)c.dense_inter;
+            RC(mk_launch_f32_gemv(ctx, ly.dgu, 2 * di, d, m->pf_x, n, m->pf_au, 2 * di, 0));
+            // gate rows and up rows of a token are the halves of its au row
+            for (int t = 0; t < n; ++t) RC(mk_launch_situ(ctx, m->pf_au + (size_t)t * 2 * di, m->pf_au + (size_t)t * 2 * di + di, di, m->pf_act + (size_t)t * di));
+            RC(mk_launch_f32_gemv(ctx, ly.dd, d, di, m->pf_act, n, m->pf_mlp_out, d, 0));
+        }
+        ga = m->pf_p2; gb = m->pf_mlp_out;
+    }
+    // the last token alone: final AttnRes mix + norm, lm_head, pick
+    const int nb_final = m->layers.back().nb_before + (m->layers.back().pushes ? 1 : 0);
+    const size_t last = (size_t)(n - 1);
+    glue_kernel<<<1, 512, gsm_bytes, st>>>(ga + last * d, gb + last * d, nullptr, m->hidden, nullptr, m->pf_blocks + last * bstride, nb_final, m->out_w,
+                                           m->norm_f, eps, d, m->x, gstage, 0, 0);
+    ctx->launches++;
+    RC(mk_matvec_q8_dev(ctx, m->head, m->x, m->logits, 1, MK_ACT_Q8 | (m->opts.strict ? MK_ACT_STRICT : 0), m->next));
 #undef RC
     MK_CUDA(cudaGetLastError());
     return MK_OK;
@@ -770,6 +934,37 @@ extern "C" int32_t mk_model_forward(mk_ctx *ctx, mk_model *m, int32_t token, flo
     return MK_OK;
 }
 
+
+extern "C" int32_t mk_model_prefill(mk_ctx *ctx, mk_model *m, const int32_t *tokens, int32_t n, float *logits, int32_t *next) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && tokens != nullptr && n >= 1, "bad argument");
+    if (m->positions + n > m->opts.max_positions) {
+        mk_set_error("mk_model_prefill: %d tokens on top of %d exceed max_positions = %d", n, m->positions, m->opts.max_positions);
+        return MK_ERR_STATE;
+    }
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = MK_OK;
+    if (m->world > 1 || m->layer_hidden) {
+        // expert-parallel models and models that keep per-layer taps take the tokens one by one
+        for (int i = 0; i < n && rc == MK_OK; ++i) rc = mk_model_forward(ctx, m, tokens[i], i == n - 1 ? logits : nullptr, i == n - 1 ? next : nullptr);
+        return rc;
+    }
+    const int chunk_max = 256;
+    for (int i0 = 0; i0 < n; i0 += chunk_max) {
+        const int nc = std::min(chunk_max, n - i0);
+        rc = ensure_prefill_buffers(ctx, m, nc);
+        if (rc != MK_OK) return rc;
+        MK_CUDA(cudaMemcpyAsync(m->pf_tok, tokens + i0, (size_t)nc * 4, cudaMemcpyHostToDevice, ctx->stream));
+        rc = enqueue_prefill(ctx, m, nc);
+        if (rc != MK_OK) return rc;
+        m->positions += nc;
+        MK_CUDA(cudaStreamSynchronize(ctx->stream));      // the token ids came from pageable host memory
+    }
+    if (logits) MK_CUDA(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next) MK_CUDA(cudaMemcpyAsync(next, m->next, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MK_OK;
+}
+
 extern "C" int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_new, int32_t *out_tokens) {
     MK_CHECK_ARG(ctx != nullptr && m != nullptr && prompt != nullptr && n_prompt >= 1 && n_new >= 0 && (n_new == 0 || out_tokens != nullptr),
                  "bad argument");
@@ -779,10 +974,25 @@ extern "C" int32_t mk_model_generate(mk_ctx *ctx, mk_model *m, const int32_t *pr
     if (rc != MK_OK) return rc;
     int32_t *pdev = (int32_t *)ctx->io_dev, *odev = pdev + n_prompt;
     MK_CUDA(cudaMemcpyAsync(pdev, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, ctx->stream));
-    // prompt tokens one by one (the engine's sequential prefill path), the pick after the last one is the first new token
-    for (int i = 0; i < n_prompt; ++i) {
-        rc = mk_model_forward_dev(ctx, m, pdev + i, nullptr, (i == n_prompt - 1 && n_new > 0) ? odev : nullptr);
-        if (rc != MK_OK) return rc;
+    if (m->world == 1 && !m->layer_hidden && n_prompt > 1) {
+        // the prompt layer by layer (enqueue_prefill); the pick after its last token is the first new token
+        const int chunk_max = 256;
+        for (int i0 = 0; i0 < n_prompt; i0 += chunk_max) {
+            const int nc = std::min(chunk_max, n_prompt - i0);
+            rc = ensure_prefill_buffers(ctx, m, nc);
+            if (rc != MK_OK) return rc;
+            MK_CUDA(cudaMemcpyAsync(m->pf_tok, pdev + i0, (size_t)nc * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+            rc = enqueue_prefill(ctx, m, nc);
+            if (rc != MK_OK) return rc;
+            m->positions += nc;
+        }
+        if (n_new > 0) { copy_i32_kernel<<<1, 1, 0, ctx->stream>>>(m->next, odev); ctx->launches++; }
+    } else {
+        // prompt tokens one by one (expert-parallel models, models that keep per-layer taps)
+        for (int i = 0; i < n_prompt; ++i) {
+            rc = mk_model_forward_dev(ctx, m, pdev + i, nullptr, (i == n_prompt - 1 && n_new > 0) ? odev : nullptr);
+            if (rc != MK_OK) return rc;
+        }
     }
     for (int i = 1; i < n_new; ++i) {
         rc = mk_model_forward_dev(ctx, m, nullptr, nullptr, odev + i);

@@ -117,6 +117,7 @@ SIGNATURES = {
     "mk_kda_free": (None, [_vp, _vp]),
     "mk_kda_reset": (_i32, [_vp, _vp]),
     "mk_kda_step_dev": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mk_kda_steps_dev": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "mk_kda_export": (_i32, [_vp, _vp, _vp, _vp]),
     "mk_kda_import": (_i32, [_vp, _vp, _vp, _vp]),
     "mk_attn_res_dev": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _i32, C.c_float, _vp]),
@@ -170,6 +171,7 @@ SIGNATURES = {
     "mk_model_ep_connect": (_i32, [_vp, _vp, _vp]),
     "mk_model_forward_dev": (_i32, [_vp, _vp, _vp, _vp, _vp]),
     "mk_model_forward": (_i32, [_vp, _vp, _i32, _vp, _vp]),
+    "mk_model_prefill": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp]),
     "mk_model_generate": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
     "mk_model_last_hidden": (_i32, [_vp, _vp, _vp]),
     "mk_model_layer_hidden": (_i32, [_vp, _vp, _vp]),

@@ -190,6 +190,16 @@ class Model:
         p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
         _l.check(self.ctx._L.mk_model_forward_dev(self.ctx._h, self._h, p(token), p(logits), p(next_out)))
 
+    def prefill(self, tokens, want_logits=True):
+        """A run of prompt tokens, layer by layer (Model::prefill, src/model.rs:3043-3260): the caches end as after one
+        forward() per token - bit for bit - and the logits and greedy pick of the LAST token come back."""
+        tk = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty(self.config.vocab, np.float32) if want_logits else None
+        nxt = C.c_int32()
+        _l.check(self.ctx._L.mk_model_prefill(self.ctx._h, self._h, tk.ctypes.data_as(C.c_void_p), tk.size,
+                                              logits.ctypes.data_as(C.c_void_p) if want_logits else None, C.byref(nxt)))
+        return logits, nxt.value
+
     def generate(self, prompt, n_new):
         """The greedy loop: prompt tokens one by one, then n_new picks (the first one follows the last prompt
         token), each fed back on the device.  Returns int32 [n_new]."""

@@ -337,6 +337,20 @@ class KdaLayer:
         _l.check(self.ctx._L.mk_kda_step_dev(self.ctx._h, self._h, *(C.c_void_p(t.data_ptr()) for t in ins), C.c_void_p(o.data_ptr())))
         return o
 
+    def steps(self, rows, g_low, ld_x, offsets):
+        """Several consecutive positions in one launch (mk_kda_steps_dev).  rows: torch CUDA float32 [n, ld_x], every row holding
+        q, k, v, g2 [heads * dim each] and beta [heads] at `offsets` = (q, k, v, g2, beta); g_low: [n, heads * dim] -> o [n, heads * dim]."""
+        import torch
+        assert _is_torch_cuda(rows) and rows.is_contiguous() and _is_torch_cuda(g_low) and g_low.is_contiguous()
+        self.ctx._follow_torch()
+        n, proj = rows.shape[0], self.heads * self.dim
+        o = torch.empty((n, proj), dtype=torch.float32, device=rows.device)
+        base = rows.data_ptr()
+        oq, ok, ov, og2, ob = (C.c_void_p(base + 4 * int(x)) for x in offsets)
+        _l.check(self.ctx._L.mk_kda_steps_dev(self.ctx._h, self._h, n, oq, ok, ov, C.c_void_p(g_low.data_ptr()), ob, og2,
+                                              C.c_void_p(o.data_ptr()), int(ld_x), proj, proj))
+        return o
+
     def reset(self):
         _l.check(self.ctx._L.mk_kda_reset(self.ctx._h, self._h))
 

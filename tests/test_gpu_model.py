@@ -167,3 +167,41 @@ def test_gpu_mxfp4_quantizer_bytes_equal_the_cpu_quantizer(mk, search):
     torch.cuda.synchronize()
     assert np.array_equal(s.cpu().numpy(), s_ref), "scale bytes"
     assert np.array_equal(p.cpu().numpy(), p_ref), "packed codes"
+
+
+@pytest.mark.parametrize("strict", [True, False])
+def test_layer_major_prefill_equals_token_by_token(mk, skeleton, strict):
+    """Model::prefill (src/model.rs:3043-3260) with the sequential recurrence: the prompt processed layer by layer leaves
+    logits, hidden state and caches as one forward per token does - bit for bit in the parity mode; in the default mode
+    the batched expert kernels sum in another order than the one-token kernels, so a bound - and decoding continues
+    identically.  A prompt cut in two pieces equals the prompt in one piece."""
+    from microkimi_b200 import model as M
+    rng = np.random.default_rng(5)
+    cfg = M.BinFile(skeleton).config
+    prompt = rng.integers(0, cfg.vocab, 21).astype(np.int32)
+    a = M.Model(skeleton, 40, use_graph=False, strict=strict)
+    for t in prompt:
+        la, na = a.forward(int(t))
+    b = M.Model(skeleton, 40, use_graph=False, strict=strict)
+    lb, nb = b.prefill(prompt)
+    c = M.Model(skeleton, 40, use_graph=False, strict=strict)
+    c.prefill(prompt[:13], want_logits=False)
+    lc, nc = c.prefill(prompt[13:])
+    assert np.array_equal(bits(lb), bits(lc)) and nb == nc, "a prompt in two pieces differs from the prompt in one"
+    if strict:
+        assert np.array_equal(bits(lb), bits(la)) and nb == na
+        assert np.array_equal(bits(b.last_hidden()), bits(a.last_hidden()))
+    else:
+        assert rel(lb, la.astype(np.float64)) <= 5e-2
+    ta, tb = na, nb
+    for _ in range(4):      # the caches continue alike
+        la, ta2 = a.forward(ta)
+        lb, tb2 = b.forward(tb)
+        if strict:
+            assert np.array_equal(bits(la), bits(lb)) and ta2 == tb2
+        ta, tb = ta2, tb2
+    one = M.Model(skeleton, 40, use_graph=False, strict=True)
+    l1, n1 = one.prefill(prompt[:1])
+    two = M.Model(skeleton, 40, use_graph=False, strict=True)
+    l2, n2 = two.forward(int(prompt[0]))
+    assert np.array_equal(bits(l1), bits(l2)) and n1 == n2

@@ -157,6 +157,33 @@ def test_kda_step_against_oracle(mk, heads, dim, kconv):
     dev.free()
 
 
+@pytest.mark.parametrize("heads,dim,kconv", [(4, 128, 4), (2, 64, 4), (3, 40, 4), (2, 128, 2)])
+def test_kda_several_positions_in_one_launch_equal_single_steps(mk, heads, dim, kconv):
+    """The engine's kda_prefill loop (src/model.rs:1281-1300) as one launch: outputs and final state equal n single-step
+    launches bit for bit, from strided rows as the stacked projections leave them."""
+    import torch
+    rng = np.random.default_rng(7 * heads + dim + kconv)
+    cw, a_log, dt_bias, o_norm = _kda_params(rng, heads, dim, kconv)
+    proj, n = heads * dim, 9
+    ld = 4 * proj + heads + 5                       # q, k, v, g2, beta and a few unrelated columns
+    rows = torch.from_numpy(rng.standard_normal((n, ld)).astype(np.float32)).cuda()
+    g_low = torch.from_numpy(rng.standard_normal((n, proj)).astype(np.float32)).cuda()
+    off = (0, proj, 2 * proj, 3 * proj, 4 * proj)
+    one = mk.KdaLayer(heads, dim, *cw, a_log, dt_bias, o_norm, kconv=kconv, gate_lb=-5.0, rms_eps=1e-6)
+    many = mk.KdaLayer(heads, dim, *cw, a_log, dt_bias, o_norm, kconv=kconv, gate_lb=-5.0, rms_eps=1e-6)
+    want = []
+    for t in range(n):
+        r = rows[t]
+        want.append(one.step(r[0:proj].contiguous(), r[proj:2 * proj].contiguous(), r[2 * proj:3 * proj].contiguous(), g_low[t].contiguous(),
+                             r[4 * proj:4 * proj + heads].contiguous(), r[3 * proj:4 * proj].contiguous()).cpu().numpy())
+    got = many.steps(rows, g_low, ld, off).cpu().numpy()
+    assert np.array_equal(bits(got), bits(np.stack(want)))
+    (s1, c1), (s2, c2) = one.export_state(), many.export_state()
+    assert np.array_equal(bits(s1), bits(s2)) and np.array_equal(bits(c1), bits(c2))
+    one.free()
+    many.free()
+
+
 def test_kda_state_snapshot_restore_and_reset(mk):
     """Cache snapshot / restore (the engine clones the layer caches before a draft batch and restores them on a
     partial accept, src/spec.rs:214, 294-299): a restored state replays the same bits; reset = a new sequence."""
