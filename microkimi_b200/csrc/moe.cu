@@ -26,7 +26,10 @@ struct mk_moe {
     float limit;
     bool has_router, has_shared;
     bool tc;                       // MK_ACT_E4M3X3: calls of >= 32 rows run the experts on the block-scaled tcgen05 path
-    void *tmaps;                   // device [(n_experts+1)*3][2] tensor maps of the registered weights (codes, scales) for that path
+    void *tmaps;                   // device [(n_experts+1)*3] tensor maps of the row-major copies below
+    int32_t *tc_rows_x, *tc_rows_p; // [max_items][16] token rows / pair ids per work item of that path
+    uint8_t *rm_vals, *rm_atoms;   // that path's own copy of the experts: nibbles [rows][K / 2] and scale atoms, matrix i at i * rm_vstride / rm_astride
+    int64_t rm_vstride, rm_astride;
     uint8_t *xl, *xsf, *actl, *actsf;   // its activation limbs: tokens [3][rows][d] + scales, expert activations [3][pairs][inter] + scales
     bool strict;                   // MK_ACT_STRICT: expert sums in the CPU's order (one accumulator, ascending blocks, no K split)
     float *gate_w, *gate_b;        // device
@@ -834,9 +837,10 @@ __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, 
 static void moe_free_ws(mk_moe *m) {
     void *ptrs[] = {m->logits, m->ids, m->wts, m->xq, m->xs, m->pair_row, m->pair_expert, m->pair_weight,
                     m->sorted, m->items, m->n_items, m->actq, m->acts, m->outs, m->lat_h, m->lat_y, m->lat_yn, m->sh_a, m->sh_u,
-                    m->stk, m->sh_out, m->xl, m->xsf, m->actl, m->actsf};
+                    m->stk, m->sh_out, m->xl, m->xsf, m->actl, m->actsf, m->tc_rows_x, m->tc_rows_p};
     for (void *p : ptrs) if (p) cudaFree(p);
     m->xl = m->xsf = m->actl = m->actsf = nullptr;
+    m->tc_rows_x = m->tc_rows_p = nullptr;
     m->lat_h = m->lat_y = m->lat_yn = m->sh_a = m->sh_u = m->stk = m->sh_out = nullptr;
     m->logits = nullptr; m->ids = nullptr; m->wts = nullptr; m->xq = nullptr; m->xs = nullptr;
     m->pair_row = m->pair_expert = nullptr; m->pair_weight = nullptr; m->sorted = m->items = m->n_items = nullptr;
@@ -886,6 +890,8 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
         MK_CUDA(cudaMalloc(&m->xsf, (size_t)3 * nr * (m->d / 32)));
         MK_CUDA(cudaMalloc(&m->actl, (size_t)3 * np * m->inter));
         MK_CUDA(cudaMalloc(&m->actsf, (size_t)3 * np * (m->inter / 32)));
+        MK_CUDA(cudaMalloc(&m->tc_rows_x, (size_t)m->max_items * mtc::NT * 4));
+        MK_CUDA(cudaMalloc(&m->tc_rows_p, (size_t)m->max_items * mtc::NT * 4));
     }
     // padded tails of the q8 rows must read as zero
     MK_CUDA(cudaMemsetAsync(m->actq, 0, (size_t)np * ldq_i, ctx->stream));
@@ -895,9 +901,11 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     return MK_OK;
 }
 
-// A 2-D tensor map of 32-bit words: `words` per row (contiguous), `rows` rows, box = box_w x box_h, no swizzle; elements
-// outside the tensor read as zero.  The driver entry point is looked up at run time (no link against libcuda).
-static bool moe_encode_tiled(CUtensorMap *map, const void *base, uint64_t words, uint64_t rows, uint32_t box_w, uint32_t box_h) {
+// A 2-D tensor map over E2M1 nibbles [rows][K / 2 bytes] whose boxes (128 codes x 128 rows) land in shared memory
+// as the tensor core's FP4 operand tile: 16 codes per 16-byte chunk (8 data + 8 gap bytes), 128-byte swizzle.  K a multiple
+// of 128, the base 32-byte aligned; rows past the end read as zero.  The driver entry point is looked up at run time (no
+// link against libcuda).
+static bool moe_encode_fp4(CUtensorMap *map, const void *base, uint64_t K, uint64_t rows) {
     typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     static encode_fn encode = nullptr;
@@ -907,10 +915,10 @@ static bool moe_encode_tiled(CUtensorMap *map, const void *base, uint64_t words,
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess || !fn) return false;
         encode = (encode_fn)fn;
     }
-    const cuuint64_t dims[2] = {words, rows}, strides[1] = {words * 4};
-    const cuuint32_t box[2] = {box_w, box_h}, estr[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const cuuint64_t dims[2] = {K, rows}, strides[1] = {K / 2};
+    const cuuint32_t box[2] = {128, 128}, estr[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **out) {
@@ -1004,23 +1012,33 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
         if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->routed_norm, desc->routed_norm, (size_t)latent * 4, cudaMemcpyHostToDevice, ctx->stream);
     }
     if (e_ == cudaSuccess && m->tc && d % 128 == 0 && I % 128 == 0) {
-        // tensor maps over the tiled layouts (src of the TMA boxes of moe_tc.cuh): per matrix a [row tiles][words] view of the
-        // codes (512-byte chunk per 16 rows x 2 blocks, nbp / 2 chunks per row tile) and of the scales (16 bytes per row tile
-        // and block)
-        std::vector<CUtensorMap> maps(hv.size() * 2);
+        // The tensor-core path reads row-major nibbles (what TMA's 16U4_ALIGN16B boxes unpack) and scale atoms: a second
+        // copy of every resident expert, made here on the device from the registered (tiled) one.
+        m->rm_vstride = (int64_t)d * I / 2;
+        m->rm_astride = (int64_t)d * I / 32;
+        const size_t nmat = hv.size();
+        e_ = cudaMalloc(&m->rm_vals, nmat * (size_t)m->rm_vstride);
+        if (e_ == cudaSuccess) e_ = cudaMalloc(&m->rm_atoms, nmat * (size_t)m->rm_astride);
+        std::vector<CUtensorMap> maps(nmat);
         memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
-        for (size_t i = 0; i < hv.size() && e_ == cudaSuccess; ++i) {
+        for (size_t i = 0; i < nmat && e_ == cudaSuccess; ++i) {
             if (!hv[i]) continue;
-            const bool down = i % 3 == 1;
-            const int64_t rows = down ? d : I, nbp = down ? m->nbp_i : m->nbp_d;
-            if (!moe_encode_tiled(&maps[i * 2], hv[i], (uint64_t)(nbp / 2) * 128, (uint64_t)(rows / 16), 256, 8) ||
-                !moe_encode_tiled(&maps[i * 2 + 1], hs[i], (uint64_t)nbp * 4, (uint64_t)(rows / 16), 16, 8)) {
+            const int e = (int)(i / 3), j = (int)(i % 3);
+            const mk_weight *w = e < E ? desc->experts[(size_t)e * 3 + j] : desc->shared[j];
+            uint8_t *vals = m->rm_vals + i * m->rm_vstride, *atoms = m->rm_atoms + i * m->rm_astride;
+            const int64_t nthreads = std::max<int64_t>(w->nrt * (w->nbp / 2) * 128, w->rows * w->nb);
+            mtc::tc_weight_copy_kernel<<<(unsigned)mk_ceil_div(nthreads, 256), 256, 0, ctx->stream>>>((const uint32_t *)w->values, (const uint8_t *)w->scales, w->rows,
+                                                                                                     w->nb, w->nbp, (uint32_t *)vals, atoms);
+            ctx->launches++;
+            // as a tensor: rows of 128 codes (64 bytes), rows * cols / 128 of them; a step's box is 128 consecutive rows
+            if (!moe_encode_fp4(&maps[i], vals, 128, (uint64_t)(w->rows * (w->cols / 128)))) {
                 mk_set_error("mk_moe_create: cuTensorMapEncodeTiled failed");
                 mk_moe_free(ctx, m);
                 return MK_ERR_CUDA;
             }
         }
-        e_ = cudaMalloc(&m->tmaps, maps.size() * sizeof(CUtensorMap));
+        if (e_ == cudaSuccess) e_ = cudaStreamSynchronize(ctx->stream);
+        if (e_ == cudaSuccess) e_ = cudaMalloc(&m->tmaps, maps.size() * sizeof(CUtensorMap));
         if (e_ == cudaSuccess) e_ = cudaMemcpy(m->tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
     }
     if (e_ == cudaSuccess) e_ = cudaMalloc(&m->counter, 4);
@@ -1043,6 +1061,8 @@ extern "C" int32_t mk_moe_free(mk_ctx *ctx, mk_moe *m) {
     if (m->wv) cudaFree((void *)m->wv);
     if (m->wsc) cudaFree((void *)m->wsc);
     if (m->tmaps) cudaFree(m->tmaps);
+    if (m->rm_vals) cudaFree(m->rm_vals);
+    if (m->rm_atoms) cudaFree(m->rm_atoms);
     if (m->gate_w) cudaFree(m->gate_w);
     if (m->gate_b) cudaFree(m->gate_b);
     if (m->counter) cudaFree(m->counter);
@@ -1112,8 +1132,10 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
         mtc::act_limbs_kernel<<<(unsigned)mk_ceil_div((int64_t)n_rows * (m->d / 32) * 32, 256), 256, 0, ctx->stream>>>(x, n_rows, m->d, m->d, m->xl, m->xsf);
         moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted, m->items,
                                                                                   m->n_items, m->max_items, ctx->status_dev, mtc::NT);
+        mtc::tc_rows_kernel<<<(unsigned)mk_ceil_div((int64_t)m->max_items * mtc::NT, 256), 256, 0, ctx->stream>>>(m->items, m->n_items, m->sorted, pair_row,
+                                                                                                              m->tc_rows_x, m->tc_rows_p, m->max_items);
         mtc::TcArgs t;
-        t.maps = (const unsigned char *)m->tmaps; t.items = m->items; t.n_items = m->n_items; t.sorted = m->sorted; t.pair_row = pair_row;
+        t.maps = (const unsigned char *)m->tmaps; t.atoms = m->rm_atoms; t.atom_stride = m->rm_astride; t.rows_x = m->tc_rows_x; t.rows_p = m->tc_rows_p; t.items = m->items; t.n_items = m->n_items; t.sorted = m->sorted; t.pair_row = pair_row;
         t.pair_weight = pair_weight; t.xl = m->xl; t.xsf = m->xsf; t.actl = m->actl; t.actsf = m->actsf; t.outs = outs;
         t.rows = n_rows; t.pairs = m->cap_pairs; t.d = m->d; t.inter = m->inter;
         t.activation = m->activation; t.limit = m->limit; t.status = ctx->status_dev;
@@ -1126,7 +1148,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
         // persistent CTAs, one per SM; the work units are dealt round-robin inside the kernels
         mtc::moe_tc_kernel<false><<<(unsigned)ctx->sm_count, mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
         mtc::moe_tc_kernel<true><<<(unsigned)ctx->sm_count, mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
-        ctx->launches += 4;
+        ctx->launches += 5;
         MK_CUDA(cudaGetLastError());
         return MK_OK;
     }

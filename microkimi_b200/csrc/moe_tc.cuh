@@ -2,12 +2,15 @@
 //
 // For calls with many token rows (the batch-256 layer: ~5 tokens per routed expert, 256 on the shared one) the expert
 // matvecs are a real contraction.  Swap-AB: 128 weight rows are the M dimension, an expert's tokens the N dimension.
-//   A : the E2M1 codes exactly as the registered weight holds them - no decode.  In shared memory a 16-byte chunk carries
-//       16 codes in its low 8 bytes (the tensor core's FP4 operand form: 8 data + 8 padding bytes), rows of 128 bytes
-//       (128 codes) in the 128-byte-swizzled K-major layout.  The registered layout (mma.sync fragment order) is brought
-//       in as it lies by tiled TMA copies (cp.async.bulk.tensor.2d: one box = 8 row tiles x 1 KB, completion on an
-//       mbarrier) into a ring of packed stages, and eight warps re-order each stage into the operand form (16-byte
-//       loads, one shuffle, 8-byte stores): the weights keep ONE resident copy.
+//   A : the E2M1 codes of the weight in the engine's byte order (src/mxfp4.rs:19-31), blocked so that the 128 codes x
+//       128 rows of a step are one contiguous 8 KB run in HBM (tc_weight_copy_kernel).  The tensor core wants FP4 in
+//       shared memory as 16 codes in the low 8 bytes of a 16-byte chunk, rows of 128 bytes (128 codes) in the
+//       128-byte-swizzled K-major layout: exactly what a tiled TMA copy with the 16U4_ALIGN16B element type writes
+//       (cp.async.bulk.tensor.2d, box = 128 codes x 128 rows, SWIZZLE_128B: 8 KB of global bytes land as a 16 KB
+//       operand tile and count as 8192 bytes on the mbarrier; the gap bytes are not written - zeroed once).  The
+//       mma.sync decode kernels read the weights in their fragment order, so a layer created for this path holds
+//       a second copy of its experts (made on the device at mk_moe_create): twice the weight memory, meant for
+//       layers that see prefill-sized batches.
 //   SFA : the ue8m0 scale bytes of the weight, unchanged, 4 blocks per step, copied into tensor memory (tcgen05.cp
 //       32x128b.warpx4) in the scale-factor layout: lane r, 32-bit column q, byte k = scale of (row r + 32 q, block k).
 //   B : the activations as THREE E4M3 limbs with power-of-two block scales (x = 2^e (h1 + 2^-4 h2 + 2^-8 h3) per block
@@ -21,23 +24,29 @@
 // Reference semantics: ds_moe / expert_forward (src/deepseek.rs:1038-1108, 74-95), batched as matvec_packed_nt batches
 // (src/model.rs:2412-2447): a (token, expert) result does not depend on which other tokens share the tile.
 //
-// Persistent CTAs (one per SM, 14 warps), work unit = (work item of <= 16 pairs, two 128-row weight tiles), units dealt
-// round-robin.  Warp 13 issues the TMA copies of a step (2 boxes of codes, 2 of scales) as soon as a packed stage is free
-// and runs on into the next unit; warps 4-11, two groups that take alternate steps, fetch their step's activation limbs
-// one own step ahead (cp.async into a ring of B slots), re-order the packed stage into one of three operand buffers and
-// hand it to warp 12, whose first lane copies the scale factors into tensor memory and issues the MMAs into one of two
-// accumulator sets; tcgen05.commit hands the operand buffer back and, at the end of a unit, the accumulators to warps
-// 0-3, which run the epilogue while the next unit's products are under way.  Every wait is bounded; a wait that runs
-// out sets MK_ERR_TIMEOUT in the status word and every role leaves its loop (tensor memory is always freed).  No
-// cluster launch, no multicast.
+// Persistent CTAs (one per SM, 11 warps), work unit = (work item of <= 16 pairs, two 128-row weight tiles), units dealt
+// round-robin.  Warp 10 asks L2 for a step's boxes 12 steps ahead (cp.async.bulk.prefetch) and issues the copies of a step
+// (2 TMA boxes of codes, 2 bulk copies of 512-byte scale atoms) as soon as a stage is free, running on into the next
+// unit; warps 4-7 fetch the step's activation limbs (cp.async) into the stage's B slot and count themselves in on the
+// same barrier; warps 8 and 9 take alternate steps: wait for the stage, copy the scale factors into tensor memory and
+// issue the MMAs into one of two accumulator sets, handing over through a named barrier so that the MMAs keep the
+// order of the steps; tcgen05.commit hands the stage back and, at the end of a unit, the accumulators to warps 0-3,
+// which run the epilogue while the next unit's products are under way.  Every mbarrier wait is bounded; a wait that
+// runs out sets MK_ERR_TIMEOUT in the status word, the roles stop issuing and run their loops to the end (so nobody is
+// left at a named barrier) and tensor memory is freed.  No cluster launch, no multicast.
 //
-// What bounds it (measured with per-role cycle counters on the batch-256 layer, 384 + 1 experts of 7168 x 2048): per step
-// of 128 columns (16 KB of codes) the MMA warp is busy ~1000 cycles - a block-scaled MMA of M = 128 costs ~110 cycles
-// whatever N is, and a step needs 8 - and the shared-memory traffic (TMA write 17 KB, re-order read 16 KB, re-order
-// write 16 KB into half the banks, operand reads ~44 KB) is ~900 cycles; HBM alone would allow 712.  Weights as the N
-// operand (N = 256, 4 MMAs per step, one accumulator set) measured no faster: the same shared-memory wall and the
-// epilogue no longer overlaps.  The padded FP4 operand form doubles every byte on its way through shared memory; a
-// weight layout that TMA can unpack itself (row-major nibbles, 16U4_ALIGN16B boxes) would remove the re-order pass.
+// What bounds it now (per-role cycle counters, batch-256 layer of 384 + 1 experts of 7168 x 2048, HBM alone 712 cycles
+// per step of 16 KB of codes): the tensor pipe - 8 block-scaled MMAs of M = 128 per step at ~125 cycles each whatever
+// N is (48 here) - about 1010 cycles per step, with the two issuing warps never waiting for data.
+// History of the operand path, all measured on that layer (experts alone; HBM roofline 0.97 ms): weights kept only in
+// the mma.sync fragment order and re-ordered in shared memory by eight warps (TMA boxes of the tiled blob into a packed
+// ring, 16-byte loads, a shuffle, 8-byte stores) 2.55 ms - the shared-memory pipe carried ~145 KB-equivalents per step
+// (69 % busy in ncu); 4-byte cp.async scatter into the operand form, bound by the L1 pipe, 6.4 ms; 1-KB bulk copies,
+// bound by their count (32 per step at ~45 cycles), 4.9 ms; this TMA-unpacked form with row-major nibbles (every box row
+// a separate 64-byte piece of HBM) 2.43 ms, blocked as above 2.17 ms; one issuing warp instead of two: +90 cycles per
+// step (a barrier wait costs ~200 cycles even when the data is there).  Weights as the N operand (N = 256, 4 MMAs per
+// step, one accumulator set) left the epilogue unoverlapped and was no faster.  M = 64 is refused by the hardware for
+// block-scaled kinds with cta_group::1.
 #pragma once
 #include <cuda_fp8.h>
 
@@ -47,25 +56,23 @@ namespace mtc {
 
 constexpr int NT = 16;                 // token rows (pairs) per work item
 constexpr int KSTEP = 128;
-constexpr int NEPI = 128, NCONV = 256, NGRP = 128, THREADS = NEPI + NCONV + 64;   // 4 epilogue + 8 converter warps (2 groups) + the MMA warp + the loader warp
-constexpr int W_CONV = NEPI / 32, W_MMA = (NEPI + NCONV) / 32, W_LOAD = W_MMA + 1;
-constexpr int NS = 5;                  // packed stages (HBM reads in flight)
-constexpr int NM = 3;                  // operand buffers of A
-constexpr int NB = 5, LB = 2;          // slots of B; limbs are fetched LB steps ahead (NB >= NM + LB)
-constexpr int A_BYTES = 128 * 128;     // one 128-row tile in operand form: [128 rows][128 B]
-constexpr int B_BYTES = 3 * NT * 128;  // the three limbs of a step: rows limb * NT + token, [<= 48 rows][128 B]
-constexpr int P_BYTES = 2 * 8192 + 2 * 512;   // a packed stage: two tiles of codes (8 row tiles x 1 KB) + their scales (8 x 64 B each)
-constexpr int OFF_A = 0;                                   // NM x (A0, A1)
-constexpr int OFF_B = OFF_A + NM * 2 * A_BYTES;            // NB x limbs
-constexpr int OFF_SFA = OFF_B + NB * B_BYTES;              // NM x 2 atoms of 512 B
-constexpr int OFF_SFB = OFF_SFA + NM * 1024;               // NB atoms
-constexpr int OFF_P = ((OFF_SFB + NB * 512 + 1023) / 1024) * 1024;   // NS packed stages
-constexpr int SM_BAR = OFF_P + NS * P_BYTES;
-constexpr int BAR_PFULL = 0, BAR_PEMPTY = NS, BAR_MFULL = 2 * NS, BAR_MEMPTY = 2 * NS + NM, BAR_AFULL = 2 * NS + 2 * NM, BAR_AEMPTY = BAR_AFULL + 2;
-constexpr int N_BARS = BAR_AEMPTY + 2;
+constexpr int NEPI = 128, NFETCH = 128, THREADS = NEPI + NFETCH + 96;   // 4 epilogue + 4 limb-fetch warps + 2 MMA warps + the loader warp
+constexpr int W_FETCH = NEPI / 32, W_MMA = (NEPI + NFETCH) / 32, W_LOAD = W_MMA + 2;
+constexpr int NS = 5;                  // stages (HBM reads in flight: NS x 17 KB of global bytes)
+constexpr int PF = 12;                 // the loader asks L2 for a step's boxes PF steps before it loads them: HBM latency is taken there,
+                                       // not in the NS stages (5 x 17 KB in flight per SM would cover ~2 us at the SM's share of the bandwidth)
+constexpr int LAG = 2;                 // the limb fetchers signal a stage LAG steps after issuing its copies
+constexpr int A_BYTES = 128 * 128;     // one 128-row tile in operand form: [128 rows][128 B], 8 KB of codes
+constexpr int B_BYTES = 3 * NT * 128;  // the three limbs of a step: rows limb * NT + token, [48 rows][128 B]
+constexpr int ST_A0 = 0, ST_A1 = A_BYTES, ST_SFA = 2 * A_BYTES, ST_SFB = ST_SFA + 1024, ST_B = 2 * A_BYTES + 2048;
+constexpr int STAGE_BYTES = ((ST_B + B_BYTES + 1023) / 1024) * 1024;
+constexpr uint32_t STEP_TX = 2 * 8192 + 2 * 512;           // bytes the loader's four copies of a step bring (global bytes)
+constexpr int SM_BAR = NS * STAGE_BYTES;
+constexpr int BAR_FULL = 0, BAR_EMPTY = NS, BAR_ACCF = 2 * NS, BAR_ACCE = 2 * NS + 2;
+constexpr int N_BARS = BAR_ACCE + 2;
 constexpr int SM_TOTAL = SM_BAR + 256 + 1024;              // barriers, tensor-memory slot, abort flag; + slack to align the base to 1024 bytes
 constexpr int TMEM_COLS = 256, ACC_COLS = 6 * NT, COL_D1 = 3 * NT, COL_SF = 2 * ACC_COLS;   // 2 accumulator sets; SF: 2 buffers x 3 atoms x 4 columns
-static_assert(N_BARS * 8 <= 192 && SM_TOTAL <= 232448 && NB >= NM + LB, "shared memory of one CTA");
+static_assert(N_BARS * 8 <= 192 && SM_TOTAL <= 232448, "shared memory of one CTA");
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -110,6 +117,17 @@ __device__ __forceinline__ void tma_2d(uint32_t dst, const void *map, int x, int
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst), "l"(map),
                  "r"(x), "r"(y), "r"(bar)
                  : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// requests into L2 only (no shared memory, no completion to wait for): the same box / run a later step will load
+__device__ __forceinline__ void tma_2d_prefetch(const void *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
@@ -167,13 +185,27 @@ __global__ void __launch_bounds__(256) act_limbs_kernel(const float *__restrict_
     }
 }
 
+// after the grouping: the token row (gate / up) and the pair id (down) of every token slot of every work item
+__global__ void __launch_bounds__(256) tc_rows_kernel(const int32_t *__restrict__ items, const int32_t *__restrict__ n_items, const int32_t *__restrict__ sorted,
+                                                      const int32_t *__restrict__ pair_row, int32_t *__restrict__ rows_x, int32_t *__restrict__ rows_p, int max_items) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x, item = idx / NT, t = idx % NT;
+    if (item >= max_items) return;
+    int p = 0;
+    if (item < *n_items && t < min(items[item * 3 + 2], NT)) p = sorted[items[item * 3 + 1] + t];
+    rows_p[idx] = p;
+    rows_x[idx] = pair_row[p];
+}
+
 struct TcArgs {
-    const unsigned char *maps;   // [(E+1)*3][2] tensor maps (128 B each) of the registered weights: tiled codes, tiled scales
+    const unsigned char *maps;   // [(E+1)*3] tensor maps (128 B each) of the row-major nibble copies [rows][K / 2]
+    const uint8_t *atoms;        // scale atoms of matrix i at atoms + i * atom_stride: [rows / 128][K / 128][512]
+    int64_t atom_stride;
     const int32_t *items;        // [n][3] = expert, offset into sorted, count (<= NT)
     const int32_t *n_items;
     const int32_t *sorted;       // pair ids grouped by expert
     const int32_t *pair_row;
     const float *pair_weight;
+    const int32_t *rows_x, *rows_p;   // [items][NT]: token row / pair id of an item's tokens (one load level for the limb fetchers)
     const uint8_t *xl, *xsf;     // token limbs [3][rows][d], [3][rows][d/32]
     uint8_t *actl, *actsf;       // activation limbs [3][pairs][inter], [3][pairs][inter/32]
     float *outs;                 // [pairs][d]
@@ -183,17 +215,42 @@ struct TcArgs {
     int32_t *status;
 };
 
-// Set-up: barriers, tensor memory, zeroed operand buffers (padding bytes and rows no copy ever writes must read as zero).
+// The tensor-core path's copy of a registered (tiled) MXFP4 matrix [rows][cols], rows % 128 == 0, cols % 128 == 0:
+//   vals : nibbles blocked by (128-row tile, 128-column step): [rows / 128][cols / 128][128 rows][64 bytes] - the box a step
+//          loads (128 codes x 128 rows) is one contiguous 8 KB run in HBM; within a row the engine's byte order
+//          (low nibble = even column, src/mxfp4.rs:19-31)
+//   atoms: scale bytes [rows / 128][cols / 128][512]: byte (r % 32) * 16 + (r / 32) * 4 + k = scale of (row r of the tile,
+//          block k of the step), the layout tcgen05.cp 32x128b.warpx4 expects
+// tv / ts: the tiled values and scales (weights.cu: 512-byte chunks per 16 rows x 2 blocks; mk_scale_off).
+__global__ void __launch_bounds__(256) tc_weight_copy_kernel(const uint32_t *__restrict__ tv, const uint8_t *__restrict__ ts, int64_t rows, int64_t nb,
+                                                             int64_t nbp, uint32_t *__restrict__ vals, uint8_t *__restrict__ atoms) {
+    const int64_t nrt = rows / 16, nsteps = nb / 4;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < nrt * (nbp / 2) * 128) {
+        const int64_t chunk = idx >> 7;
+        const int within = (int)(idx & 127), ln = within >> 2, j = within & 3, g = ln >> 2, t = ln & 3;
+        const int64_t rt = chunk / (nbp / 2), bp = chunk % (nbp / 2);
+        const int64_t row = rt * 16 + g + ((j & 1) ? 8 : 0), blk = bp * 2 + (j >> 1);
+        if (blk < nb) vals[(((row >> 7) * nsteps + (blk >> 2)) * 128 + (row & 127)) * 16 + (blk & 3) * 4 + t] = tv[idx];
+    }
+    if (idx < rows * nb) {
+        const int64_t row = idx / nb, blk = idx % nb;
+        const int r = (int)(row & 127);
+        atoms[((row >> 7) * nsteps + (blk >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (blk & 3)] = ts[mk_scale_off(row >> 4, nbp, blk, (int)(row & 15))];
+    }
+}
+
+// Set-up: barriers, tensor memory, zeroed stages (the gap bytes of the FP4 operand form and the rows no copy ever writes
+// must read as zero).
 __device__ __forceinline__ uint32_t tc_setup(unsigned char *sm) {
     const int tid = threadIdx.x, warp = tid >> 5;
     uint64_t *bars = (uint64_t *)(sm + SM_BAR);
     uint32_t *slot = (uint32_t *)(sm + SM_BAR + 192);
-    for (int i = tid; i < OFF_P / 16; i += THREADS) ((uint4 *)sm)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < NS * STAGE_BYTES / 16; i += THREADS) ((uint4 *)sm)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (tid == 0) {
         auto init = [&](int b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bars[b])), "r"(count)); };
-        for (int s = 0; s < NS; ++s) { init(BAR_PFULL + s, 1); init(BAR_PEMPTY + s, NGRP / 32); }     // one arrival per warp of the group that converts the step
-        for (int s = 0; s < NM; ++s) { init(BAR_MFULL + s, NGRP / 32); init(BAR_MEMPTY + s, 1); }
-        for (int s = 0; s < 2; ++s) { init(BAR_AFULL + s, 1); init(BAR_AEMPTY + s, NEPI / 32); }
+        for (int s = 0; s < NS; ++s) { init(BAR_FULL + s, 1 + NFETCH / 32); init(BAR_EMPTY + s, 1); }   // full: the loader's arrival with its byte count + one arrival per fetch warp
+        for (int s = 0; s < 2; ++s) { init(BAR_ACCF + s, 1); init(BAR_ACCE + s, NEPI / 32); }
         slot[1] = 0;     // the abort flag
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -233,166 +290,147 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
     uint64_t *bars = (uint64_t *)(sm + SM_BAR);
     volatile int *abort = (volatile int *)(sm + SM_BAR + 196);
     const uint32_t bar0 = s32(bars), smb = s32(sm);
+    const int total = nunits * nsteps;
     bool ok = true;
 
     if (warp == W_LOAD) {
-        // ---------------- the loader: the whole warp walks the loop (a lone lane beside 31 parked ones runs slowly),
-        // lane 0 issues the four boxes of a step
-        {
-            int gs = 0;
-            int e_next = a.items[(c / X) * 3];
-            for (int k = 0; k < nunits && ok; ++k) {
-                const int u = c + k * G, xt = u % X, e = e_next;
-                if (k + 1 < nunits) e_next = a.items[((u + G) / X) * 3];
-                const unsigned char *m0, *m1;
-                int y0, y1;
-                if (DOWN) { m0 = m1 = a.maps + (size_t)(e * 3 + 1) * 256; y0 = xt * 16; y1 = y0 + 8; }
-                else { m0 = a.maps + (size_t)(e * 3 + 0) * 256; m1 = a.maps + (size_t)(e * 3 + 2) * 256; y0 = y1 = xt * 8; }
-                for (int it = 0; it < nsteps; ++it, ++gs) {
-                    const int ps = gs % NS;
-                    if (gs >= NS && !bar_wait(bar0 + (BAR_PEMPTY + ps) * 8, (uint32_t)((gs / NS) - 1) & 1u, abort)) { ok = false; break; }
-                    const uint32_t full = bar0 + (BAR_PFULL + ps) * 8, dst = smb + OFF_P + ps * P_BYTES;
-                    if (lane == 0) {
-                        bar_expect(full, (uint32_t)P_BYTES);
-                        tma_2d(dst, m0, it * 256, y0, full);                 // codes: 256 words (2 block pairs) x 8 row tiles
-                        tma_2d(dst + 8192, m1, it * 256, y1, full);
-                        tma_2d(dst + 16384, m0 + 128, it * 16, y0, full);    // scales: 16 words (4 blocks x 16 rows) x 8 row tiles
-                        tma_2d(dst + 16896, m1 + 128, it * 16, y1, full);
-                    }
-                    __syncwarp();
+        // ---------------- the loader: the whole warp walks the loop (a lone lane beside 31 parked ones runs slowly), lane 0
+        // issues the four copies of a step
+        int gs = 0;
+        int e_next = a.items[(c / X) * 3];
+        struct Src { const unsigned char *m0, *m1; const uint8_t *s0, *s1; int y0, y1; };      // y: first row of the tile's first step in the blocked copy
+        auto src_of = [&](int e, int xt) {
+            Src r;
+            const int i0 = e * 3 + (DOWN ? 1 : 0), i1 = e * 3 + (DOWN ? 1 : 2);
+            const int t0 = DOWN ? 2 * xt : xt, t1 = DOWN ? 2 * xt + 1 : xt;              // 128-row tiles of the two matrices
+            r.m0 = a.maps + (size_t)i0 * 128; r.m1 = a.maps + (size_t)i1 * 128;
+            r.s0 = a.atoms + i0 * a.atom_stride + (size_t)t0 * nsteps * 512;
+            r.s1 = a.atoms + i1 * a.atom_stride + (size_t)min(t1, ntile - 1) * nsteps * 512;   // a tile past the end: zero codes, any scales
+            r.y0 = t0 * nsteps * 128; r.y1 = t1 * nsteps * 128;
+            return r;
+        };
+        auto prefetch = [&](const Src &r, int it) {
+            tma_2d_prefetch(r.m0, 0, r.y0 + it * 128);
+            tma_2d_prefetch(r.m1, 0, r.y1 + it * 128);
+            bulk_prefetch(r.s0 + (size_t)it * 512, 512);
+            bulk_prefetch(r.s1 + (size_t)it * 512, 512);
+        };
+        Src cur = src_of(e_next, c % X);
+        if (lane == 0) for (int it = 0; it < min(PF, nsteps); ++it) prefetch(cur, it);
+        for (int k = 0; k < nunits && ok; ++k) {
+            const int u = c + k * G;
+            const bool more = k + 1 < nunits;
+            Src nxt = cur;
+            if (more) nxt = src_of(a.items[((u + G) / X) * 3], (u + G) % X);
+            for (int it = 0; it < nsteps; ++it, ++gs) {
+                const int st = gs % NS;
+                if (lane == 0) {
+                    if (it + PF < nsteps) prefetch(cur, it + PF);
+                    else if (more && it + PF - nsteps < nsteps) prefetch(nxt, it + PF - nsteps);
                 }
+                if (gs >= NS && !bar_wait(bar0 + (BAR_EMPTY + st) * 8, (uint32_t)((gs / NS) - 1) & 1u, abort)) { ok = false; break; }
+                if (lane == 0) {
+                    const uint32_t full = bar0 + (BAR_FULL + st) * 8, dst = smb + st * STAGE_BYTES;
+                    bar_expect(full, STEP_TX);
+                    tma_2d(dst + ST_A0, cur.m0, 0, cur.y0 + it * 128, full);    // 128 codes x 128 rows (8 KB, contiguous) -> a 16 KB operand tile
+                    tma_2d(dst + ST_A1, cur.m1, 0, cur.y1 + it * 128, full);
+                    bulk_g2s(dst + ST_SFA, cur.s0 + (size_t)it * 512, 512, full);
+                    bulk_g2s(dst + ST_SFA + 512, cur.s1 + (size_t)it * 512, 512, full);
+                }
+                __syncwarp();
             }
+            cur = nxt;
         }
-    } else if (warp == W_MMA) {
-        // ---------------- the MMA warp: all lanes wait, lane 0 issues
-        {
-            int gs = 0;
-            for (int k = 0; k < nunits && ok; ++k) {
-                const int nn = 3 * NT, acc = k & 1;   // padding tokens ride along: N a multiple of 16 at M = 128
-                const uint32_t id[4] = {idesc_mx(nn, 0), idesc_mx(nn, 1), idesc_mx(nn, 2), idesc_mx(nn, 3)};
-                if (k >= 2 && !bar_wait(bar0 + (BAR_AEMPTY + acc) * 8, (uint32_t)((k >> 1) - 1) & 1u, abort)) { ok = false; break; }
+    } else if (warp == W_MMA || warp == W_MMA + 1) {
+        // ---------------- two MMA warps on alternate steps: a barrier wait costs ~200 cycles even when the data is there, and
+        // issuing a step's MMAs blocks for their ~900 cycles; one warp alone leaves the tensor pipe idle during its waits.
+        // The warp of step gs waits for the stage while the other one issues step gs - 1, then takes over through a named
+        // barrier (the order of the MMAs into one accumulator must be the order of the steps).  All lanes wait, lane 0 issues.
+        const int wid = warp - W_MMA;
+        const uint32_t id[4] = {idesc_mx(3 * NT, 0), idesc_mx(3 * NT, 1), idesc_mx(3 * NT, 2), idesc_mx(3 * NT, 3)};
+        for (int gs = wid; gs < total; gs += 2) {
+            const int k = gs / nsteps, it = gs - k * nsteps, acc = k & 1, st = gs % NS;
+            if (ok && !bar_wait(bar0 + (BAR_FULL + st) * 8, (uint32_t)(gs / NS) & 1u, abort)) ok = false;
+            if (ok && it == 0 && k >= 2 && !bar_wait(bar0 + (BAR_ACCE + acc) * 8, (uint32_t)((k >> 1) - 1) & 1u, abort)) ok = false;
+            if (gs > 0) asm volatile("bar.sync %0, 64;" ::"r"(2 + wid) : "memory");      // the other warp has issued step gs - 1
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ok && lane == 0) {
                 const uint32_t d0 = tb + acc * ACC_COLS, d1 = d0 + COL_D1;
-                for (int it = 0; it < nsteps; ++it, ++gs) {
-                    const int mb = gs % NM, slot = gs % NB;
-                    if (!bar_wait(bar0 + (BAR_MFULL + mb) * 8, (uint32_t)(gs / NM) & 1u, abort)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a0 = smb + OFF_A + mb * 2 * A_BYTES, a1 = a0 + A_BYTES, bb = smb + OFF_B + slot * B_BYTES;
-                    const uint32_t tsf = tb + COL_SF + (uint32_t)(gs & 1) * 12;
-                    if (lane == 0) {
-                    sf_copy(tsf + 0, smb + OFF_SFA + mb * 1024);
-                    sf_copy(tsf + 4, smb + OFF_SFA + mb * 1024 + 512);
-                    sf_copy(tsf + 8, smb + OFF_SFB + slot * 512);
+                const uint32_t base = smb + st * STAGE_BYTES, a0 = base + ST_A0, a1 = base + ST_A1, bb = base + ST_B;
+                const uint32_t tsf = tb + COL_SF + (uint32_t)wid * 12;
+                sf_copy(tsf + 0, base + ST_SFA);
+                sf_copy(tsf + 4, base + ST_SFA + 512);
+                sf_copy(tsf + 8, base + ST_SFB);
 #pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) {
-                        const uint64_t da0 = smem_desc(a0 + kb * 32, 16, 1024, 2), da1 = smem_desc(a1 + kb * 32, 16, 1024, 2);
-                        const uint64_t db = smem_desc(bb + kb * 32, 16, 1024, 2);
-                        const uint32_t accum = (it > 0 || kb > 0) ? 1u : 0u;
-                        mma_mx(d0, da0, db, id[kb], accum, tsf + 0, tsf + 8);
-                        mma_mx(d1, da1, db, id[kb], accum, tsf + 4, tsf + 8);
-                    }
-                    commit(bar0 + (BAR_MEMPTY + mb) * 8);      // the operand buffer and the B slot are free once these MMAs have read them
-                    }
-                    __syncwarp();
+                for (int kb = 0; kb < 4; ++kb) {
+                    const uint64_t da0 = smem_desc(a0 + kb * 32, 16, 1024, 2), da1 = smem_desc(a1 + kb * 32, 16, 1024, 2);
+                    const uint64_t db = smem_desc(bb + kb * 32, 16, 1024, 2);
+                    const uint32_t accum = (it > 0 || kb > 0) ? 1u : 0u;
+                    mma_mx(d0, da0, db, id[kb], accum, tsf + 0, tsf + 8);
+                    mma_mx(d1, da1, db, id[kb], accum, tsf + 4, tsf + 8);
                 }
-                if (ok && lane == 0) commit(bar0 + (BAR_AFULL + acc) * 8);  // the unit's accumulators are complete
+                commit(bar0 + (BAR_EMPTY + st) * 8);                       // the stage is free once these MMAs have read it
+                if (it == nsteps - 1) commit(bar0 + (BAR_ACCF + acc) * 8);  // the unit's accumulators are complete
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (gs + 1 < total) asm volatile("bar.arrive %0, 64;" ::"r"(2 + (1 - wid)) : "memory");   // hand over to the warp of step gs + 1
         }
-    } else if (warp >= W_CONV) {
-        // ---------------- converters: two groups of four warps, group j takes the steps gs = j (mod 2), so the barrier round
-        // trips and shared-memory latencies of one step overlap with the other group's work
-        const int cw = warp - W_CONV, grp = cw >> 2, gw = cw & 3, gp = (tid - NEPI) & (NGRP - 1);
+    } else if (warp >= W_FETCH) {
+        // ---------------- limb fetchers: thread = (token gp >> 3, 16-byte chunk gp & 7) of the three limb rows, and the scale
+        // word of token gp % NT, limb gp / NT
+        const int gp = tid - NEPI;
         const uint8_t *bl = DOWN ? a.actl : a.xl, *bsf = DOWN ? a.actsf : a.xsf;
         const int64_t b_rows = DOWN ? a.pairs : a.rows;
-        // a unit's B rows: this thread copies chunk (gp & 7) of token (gp >> 3), and the scale word of token gp % NT, limb gp / NT
         struct Rows { int n; const uint8_t *main, *sf; };
+        const int32_t *rows_tab = DOWN ? a.rows_p : a.rows_x;
         auto rows_of = [&](int u) {
+            // independent loads only (issued a unit ahead, they never stall the copies of the current unit)
             Rows r;
-            const int item = u / X, off = a.items[item * 3 + 1];
+            const int item = u / X;
             r.n = min(a.items[item * 3 + 2], NT);
-            const int t0 = gp >> 3, t1 = gp & (NT - 1);
-            const int p0 = t0 < r.n ? a.sorted[off + t0] : 0, p1 = t1 < r.n ? a.sorted[off + t1] : 0;
-            const int64_t r0 = DOWN ? p0 : a.pair_row[p0], r1 = DOWN ? p1 : a.pair_row[p1];
+            const int64_t r0 = rows_tab[item * NT + (gp >> 3)], r1 = rows_tab[item * NT + (gp & (NT - 1))];
             r.main = bl + r0 * K + (gp & 7) * 16;
             r.sf = bsf + ((int64_t)(gp / NT) * b_rows + r1) * (K / 32);
             return r;
         };
-        const int total = nunits * nsteps;
-        int fk = 0, fit = grp;              // fetch cursor of this group: unit, step within it
-        while (fit >= nsteps && fk < nunits) { fit -= nsteps; ++fk; }
-        Rows cur = rows_of(c + (fk < nunits ? fk : 0) * G), nxt = cur;
-        if (fk + 1 < nunits) nxt = rows_of(c + (fk + 1) * G);
+        int fk = 0, fit = 0;
+        Rows cur = rows_of(c), nxt = cur;
+        if (nunits > 1) nxt = rows_of(c + G);
         const int64_t limb_stride = b_rows * K;
         const int bt0 = gp >> 3, bch = gp & 7;
         const uint32_t bdst = (uint32_t)(bt0 * 128 + ((bch ^ (bt0 & 7)) << 4));       // limb rows 16 apart keep the swizzle phase
         const bool sf_thread = gp < 3 * NT;
         const uint32_t sfdst = (uint32_t)((gp & 31) * 16 + (gp >> 5) * 4);            // row limb * 16 + token of the scale atom = gp
-        auto fetch_b = [&](int f) {         // the limbs of global step f (one of this group's) into slot f % NB
+        for (int f = 0; f < total + LAG; ++f) {
             if (f < total) {
-                const int slot = f % NB;
-                const uint32_t bb = smb + OFF_B + slot * B_BYTES + bdst, sfb = smb + OFF_SFB + slot * 512 + sfdst;
-                if (bt0 < cur.n) {
-                    const uint8_t *src = cur.main + (int64_t)fit * KSTEP;
-                    cp16(bb, src);
-                    cp16(bb + NT * 128, src + limb_stride);
-                    cp16(bb + 2 * NT * 128, src + 2 * limb_stride);
+                const int st = f % NS;
+                if (f >= NS && ok && !bar_wait(bar0 + (BAR_EMPTY + st) * 8, (uint32_t)((f / NS) - 1) & 1u, abort)) ok = false;
+                if (ok) {
+                    const uint32_t bb = smb + st * STAGE_BYTES + ST_B + bdst, sfb = smb + st * STAGE_BYTES + ST_SFB + sfdst;
+                    if (bt0 < cur.n) {
+                        const uint8_t *src = cur.main + (int64_t)fit * KSTEP;
+                        cp16(bb, src);
+                        cp16(bb + NT * 128, src + limb_stride);
+                        cp16(bb + 2 * NT * 128, src + 2 * limb_stride);
+                    }
+                    if (sf_thread && (gp & (NT - 1)) < cur.n) cp4(sfb, cur.sf + (int64_t)fit * 4);
                 }
-                if (sf_thread && (gp & (NT - 1)) < cur.n) cp4(sfb, cur.sf + (int64_t)fit * 4);
-                fit += 2;
-                while (fit >= nsteps && fk < nunits) {
-                    fit -= nsteps; ++fk; cur = nxt;
+                if (++fit == nsteps) {
+                    fit = 0; ++fk; cur = nxt;
                     if (fk + 1 < nunits) nxt = rows_of(c + (fk + 1) * G);
                 }
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
-        };
-        // Lane (g, t) of a packed 512-byte chunk (16 rows x 2 blocks) holds four words: word j = 8 codes (columns 8t .. 8t + 7)
-        // of block (j >> 1), row g + 8 (j & 1).  Lanes t and t ^ 1 together hold the 16 codes of an operand chunk, so even
-        // lanes take the partner's words 0, 1 and write block 0, odd lanes take words 2, 3 and write block 1.
-        const int g = lane >> 2, t = lane & 3, odd = t & 1;
-        const int cpos = (odd << 1) + (t >> 1);                    // 16-byte chunk of the row within the chunk's 2 blocks
-        // this warp's chunks: row tiles gw and gw + 4, both block pairs, both matrices
-        const uint32_t src_off = (uint32_t)(gw * 1024 + lane * 16);
-        // row g of the 16-row tile (row g + 8, 1024 bytes on, has the same swizzle phase), chunk 4 bp + cpos of its 128 bytes
-        const uint32_t d_c0 = (uint32_t)(gw * 2048 + g * 128 + ((cpos ^ g) << 4)), d_c1 = (uint32_t)(gw * 2048 + g * 128 + (((4 + cpos) ^ g) << 4));
-        fetch_b(grp);
-        for (int gs = grp; gs < total; gs += 2) {
-            const int mb = gs % NM, ps = gs % NS;
-            // operand buffer mb and B slot (gs + 2) % NB were last read by the MMAs of step gs - NM
-            if (gs >= NM && ok && !bar_wait(bar0 + (BAR_MEMPTY + mb) * 8, (uint32_t)((gs / NM) - 1) & 1u, abort)) ok = false;
-            fetch_b(gs + 2);
-            if (ok && !bar_wait(bar0 + (BAR_PFULL + ps) * 8, (uint32_t)(gs / NS) & 1u, abort)) ok = false;
+            const int ready = f - LAG;
+            if (ready >= 0) {
+                // the copies of step `ready` have landed: visible to the tensor core's reads, one arrival per warp
+                asm volatile("cp.async.wait_group %0;\n" ::"n"(LAG) : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) bar_arrive(bar0 + (BAR_FULL + ready % NS) * 8);
+            }
             if (!ok) break;
-            const unsigned char *pk = sm + OFF_P + (size_t)ps * P_BYTES;
-            unsigned char *am = sm + OFF_A + (size_t)mb * 2 * A_BYTES;
-            uint4 w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = *(const uint4 *)(pk + (i >> 2) * 8192 + ((i >> 1) & 1) * 4096 + (i & 1) * 512 + src_off);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {          // i = (matrix, row tile half, block pair)
-                const uint32_t s0 = odd ? w[i].x : w[i].z, s1 = odd ? w[i].y : w[i].w;
-                const uint32_t r0 = __shfl_xor_sync(0xFFFFFFFFu, s0, 1), r1 = __shfl_xor_sync(0xFFFFFFFFu, s1, 1);
-                // even lane: (mine, partner's) of words 0, 1; odd lane: (partner's, mine) of words 2, 3
-                const uint2 lo = odd ? make_uint2(r0, w[i].z) : make_uint2(w[i].x, r0);
-                const uint2 hi = odd ? make_uint2(r1, w[i].w) : make_uint2(w[i].y, r1);
-                unsigned char *dst = am + (i >> 2) * A_BYTES + ((i >> 1) & 1) * 4 * 2048 + ((i & 1) ? d_c1 : d_c0);
-                *(uint2 *)dst = lo;
-                *(uint2 *)(dst + 1024) = hi;
-            }
-            // scales: packed [matrix][row tile][16 rows][4 blocks of the step]; one word = a row's four scale bytes
-#pragma unroll
-            for (int smat = 0; smat < 2; ++smat) {
-                const int srow = gp;
-                const uint32_t v = *(const uint32_t *)(pk + 16384 + smat * 512 + (srow >> 4) * 64 + (srow & 15) * 4);
-                *(uint32_t *)(sm + OFF_SFA + mb * 1024 + smat * 512 + (srow & 31) * 16 + (srow >> 5) * 4) = v;
-            }
-            // one arrival per warp: the warp's reads of the packed stage are done
-            __syncwarp();
-            if (lane == 0) bar_arrive(bar0 + (BAR_PEMPTY + ps) * 8);
-            // ... and its writes (the stores above, the cp.async of this step) are visible to the tensor core's reads
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) bar_arrive(bar0 + (BAR_MFULL + mb) * 8);
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     } else {
@@ -401,7 +439,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
         for (int k = 0; k < nunits; ++k) {
             const int u = c + k * G, item = u / X, xt = u % X, acc = k & 1;
             const int off = a.items[item * 3 + 1], n = min(a.items[item * 3 + 2], NT), npad = NT;
-            if (!bar_wait(bar0 + (BAR_AFULL + acc) * 8, (uint32_t)(k >> 1) & 1u, abort)) { ok = false; break; }
+            if (!bar_wait(bar0 + (BAR_ACCF + acc) * 8, (uint32_t)(k >> 1) & 1u, abort)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tb + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
             float v0[16], v1[16], l1[16], l2[16];      // a token's three limb products sit npad columns apart
@@ -417,7 +455,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
             for (int i = 0; i < 16; ++i) v1[i] = __fadd_rn(__fadd_rn(v1[i], l1[i]), l2[i]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bar_arrive(bar0 + (BAR_AEMPTY + acc) * 8);            // the accumulator set may be overwritten
+            if (lane == 0) bar_arrive(bar0 + (BAR_ACCE + acc) * 8);            // the accumulator set may be overwritten
             if (!DOWN) {
                 const int64_t col = (int64_t)xt * 128 + q * 32 + lane;     // index into the expert's intermediate vector
                 const int nbi = a.inter / 32;
