@@ -56,7 +56,9 @@ typedef struct mk_mla    mk_mla;
 /* MoE layer only (mk_moe_desc.act_mode): calls of 32 or more token rows run the experts as block-scaled tensor-core
  * products (tcgen05.mma kind::mxf8f6f4): E2M1 weights with their ue8m0 scales as registered, the activations as three
  * E4M3 limbs with power-of-two block scales (12 significant bits per element).  Results track the engine's exact-f32
- * path (src/mxfp4.rs:488-539) to ~1e-5 of max |y|; smaller calls run MK_ACT_Q8. */
+ * path (src/mxfp4.rs:488-539) to ~1e-5 of max |y|; smaller calls run MK_ACT_Q8.
+ * A layer created in this mode keeps a second copy of its experts on the device (blocked for TMA's 4-bit unpack):
+ * twice the expert memory.  Calls of fewer than 32 rows run the ordinary q8 kernels. */
 #define MK_ACT_E4M3X3 2
 /* OR into act_mode: accumulate the per-block terms of every output strictly in
  * ascending block order with separate multiply and add, reproducing the CPU
