@@ -273,7 +273,7 @@ def build_moe_layers(torch, mk, ctx, dev, experts, copies, seed=3, act="q8"):
 
 def tc_twins(mk, ctx, layers):
     """The same layers (same registered weights) with the experts of large calls on the block-scaled tcgen05 path."""
-    return [mk.MoeLayer(l._gate_w, None, l._keep[0], l._keep[1], l.top_k, ctx=ctx, act="e4m3x3") for l in layers]
+    return [mk.MoeLayer(l._gate_w, None, l._keep[0], l._keep[1], l.top_k, ctx=ctx, act="fp4x6") for l in layers]
 
 
 def free_moe_layers(layers):
@@ -492,7 +492,7 @@ def extras_single_gpu(torch, mk, ctx, dev, heads, x1):
                    for b, st in ((1, 40), (16, 20), (256, 6))}
             twins = tc_twins(mk, ctx, layers)
             res["batch256_tcgen05_block_scaled"] = measure_moe(torch, mk, ctx, dev, twins, gen, 256, 6, 3)
-            res["batch256_tcgen05_block_scaled"]["act_mode"] = "e4m3x3: E2M1 weights + ue8m0 scales as registered, activations as three E4M3 limbs"
+            res["batch256_tcgen05_block_scaled"]["act_mode"] = "fp4x6: E2M1 weights + ue8m0 scales as registered, activations as six E2M1 limbs (kind::mxf4)"
             for t in twins:
                 t.free()
             return res
@@ -928,7 +928,7 @@ def main():
     ap.add_argument("--copies", type=int, default=1)
     ap.add_argument("--act", default="q8", choices=["q8", "q8x2"])
     ap.add_argument("--experts", type=int, default=384)
-    ap.add_argument("--moe-act", default="q8", choices=["q8", "e4m3x3"], help="--case moe: e4m3x3 = block-scaled tcgen05 experts for calls of >= 32 rows")
+    ap.add_argument("--moe-act", default="q8", choices=["q8", "fp4x6"], help="--case moe: fp4x6 = block-scaled tcgen05 experts for calls of >= 32 rows")
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=4, help="--case kda: KDA heads of width 128")
     ap.add_argument("--kda-smem", action="store_true", help="--case kda: the shared-memory form of the step kernel (default at width 128: registers)")

@@ -54,12 +54,14 @@ typedef struct mk_mla    mk_mla;
 #define MK_ACT_Q8    0
 #define MK_ACT_Q8X2  1
 /* MoE layer only (mk_moe_desc.act_mode): calls of 32 or more token rows run the experts as block-scaled tensor-core
- * products (tcgen05.mma kind::mxf8f6f4): E2M1 weights with their ue8m0 scales as registered, the activations as three
- * E4M3 limbs with power-of-two block scales (12 significant bits per element).  Results track the engine's exact-f32
- * path (src/mxfp4.rs:488-539) to ~1e-5 of max |y|; smaller calls run MK_ACT_Q8.
- * A layer created in this mode keeps a second copy of its experts on the device (blocked for TMA's 4-bit unpack):
- * twice the expert memory.  Calls of fewer than 32 rows run the ordinary q8 kernels. */
-#define MK_ACT_E4M3X3 2
+ * products (tcgen05.mma kind::mxf4, both operands packed FP4): E2M1 weights with their ue8m0 scales as registered, the
+ * activations as six E2M1 limbs with power-of-two block scales (every limb takes the remainder down by a factor of 4;
+ * what is left after six is at most 1/12288 of the block's largest element).  Results track the engine's exact-f32
+ * path (src/mxfp4.rs:488-539) to ~1e-5 of max |y|.  The experts' input width and inter must be multiples of 256
+ * (mk_moe_create refuses the mode otherwise).
+ * A layer created in this mode keeps a second copy of its experts on the device (blocked into the 16 KB boxes a step
+ * loads): twice the expert memory.  Calls of fewer than 32 rows run the ordinary q8 kernels. */
+#define MK_ACT_FP4X6 2
 /* OR into act_mode: accumulate the per-block terms of every output strictly in
  * ascending block order with separate multiply and add, reproducing the CPU
  * result of src/mxfp4.rs:409-418 / src/model.rs:337-347 bit for bit (slower). */
@@ -327,7 +329,7 @@ typedef struct {
     const mk_weight *routed_up;      /* f32 [d, latent] */
     const float *routed_norm;        /* HOST f32 [latent] */
     const mk_weight *shared_f32[3];  /* f32 shared expert: gate [si, d], down [d, si], up [si, d]; all NULL = none */
-    int32_t act_mode;                /* MK_ACT_Q8 (0); MK_ACT_E4M3X3 (see above); or MK_ACT_Q8 | MK_ACT_STRICT: the expert matvecs add their block terms in the
+    int32_t act_mode;                /* MK_ACT_Q8 (0); MK_ACT_FP4X6 (see above); or MK_ACT_Q8 | MK_ACT_STRICT: the expert matvecs add their block terms in the
                                         CPU's order (src/mxfp4.rs:409-418), so no q8 rounding of an activation can differ from the
                                         CPU's; slower on wide experts (no K split) */
 } mk_moe_desc;

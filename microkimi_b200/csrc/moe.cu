@@ -25,10 +25,10 @@ struct mk_moe {
     float route_scale;
     float limit;
     bool has_router, has_shared;
-    bool tc;                       // MK_ACT_E4M3X3: calls of >= 32 rows run the experts on the block-scaled tcgen05 path
+    bool tc;                       // MK_ACT_FP4X6: calls of >= 32 rows run the experts on the block-scaled tcgen05 path
     void *tmaps;                   // device [(n_experts+1)*3] tensor maps of the row-major copies below
     int32_t *tc_rows_x, *tc_rows_p; // [max_items][16] token rows / pair ids per work item of that path
-    uint8_t *rm_vals, *rm_atoms;   // that path's own copy of the experts: nibbles [rows][K / 2] and scale atoms, matrix i at i * rm_vstride / rm_astride
+    uint8_t *rm_vals, *rm_atoms;   // that path's own copy of the experts: blocked nibbles and scale atoms (moe_tc.cuh), matrix i at i * rm_vstride / rm_astride
     int64_t rm_vstride, rm_astride;
     uint8_t *xl, *xsf, *actl, *actsf;   // its activation limbs: tokens [3][rows][d] + scales, expert activations [3][pairs][inter] + scales
     bool strict;                   // MK_ACT_STRICT: expert sums in the CPU's order (one accumulator, ascending blocks, no K split)
@@ -886,10 +886,10 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
         if (m->latent > 0) MK_CUDA(cudaMalloc(&m->stk, (size_t)(m->latent + 2 * m->shared_inter) * 4));
     }
     if (m->tc) {
-        MK_CUDA(cudaMalloc(&m->xl, (size_t)3 * nr * m->d));
-        MK_CUDA(cudaMalloc(&m->xsf, (size_t)3 * nr * (m->d / 32)));
-        MK_CUDA(cudaMalloc(&m->actl, (size_t)3 * np * m->inter));
-        MK_CUDA(cudaMalloc(&m->actsf, (size_t)3 * np * (m->inter / 32)));
+        MK_CUDA(cudaMalloc(&m->xl, (size_t)mtc::NL * nr * (m->d / 2)));
+        MK_CUDA(cudaMalloc(&m->xsf, (size_t)mtc::NL * nr * (m->d / 32)));
+        MK_CUDA(cudaMalloc(&m->actl, (size_t)mtc::NL * np * (m->inter / 2)));
+        MK_CUDA(cudaMalloc(&m->actsf, (size_t)mtc::NL * np * (m->inter / 32)));
         MK_CUDA(cudaMalloc(&m->tc_rows_x, (size_t)m->max_items * mtc::NT * 4));
         MK_CUDA(cudaMalloc(&m->tc_rows_p, (size_t)m->max_items * mtc::NT * 4));
     }
@@ -901,11 +901,10 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     return MK_OK;
 }
 
-// A 2-D tensor map over E2M1 nibbles [rows][K / 2 bytes] whose boxes (128 codes x 128 rows) land in shared memory
-// as the tensor core's FP4 operand tile: 16 codes per 16-byte chunk (8 data + 8 gap bytes), 128-byte swizzle.  K a multiple
-// of 128, the base 32-byte aligned; rows past the end read as zero.  The driver entry point is looked up at run time (no
-// link against libcuda).
-static bool moe_encode_fp4(CUtensorMap *map, const void *base, uint64_t K, uint64_t rows) {
+// A 2-D tensor map over bytes: rows of 128 bytes (256 E2M1 codes), `rows` of them, box = 128 bytes x 128 rows, 128-byte
+// swizzle: what a box lands in shared memory is the K-major FP4 operand tile of a kind::mxf4 MMA.  Rows past the end read
+// as zero.  The driver entry point is looked up at run time (no link against libcuda).
+static bool moe_encode_fp4(CUtensorMap *map, const void *base, uint64_t rows) {
     typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     static encode_fn encode = nullptr;
@@ -915,9 +914,9 @@ static bool moe_encode_fp4(CUtensorMap *map, const void *base, uint64_t K, uint6
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess || !fn) return false;
         encode = (encode_fn)fn;
     }
-    const cuuint64_t dims[2] = {K, rows}, strides[1] = {K / 2};
+    const cuuint64_t dims[2] = {128, rows}, strides[1] = {128};
     const cuuint32_t box[2] = {128, 128}, estr[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -931,8 +930,10 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     MK_CHECK_ARG(desc->activation == MK_MOE_SWIGLU_CLAMP || desc->activation == MK_MOE_SITU, "unknown activation");
     MK_CHECK_ARG(desc->router == MK_ROUTER_SIGMOID || desc->router == MK_ROUTER_SQRT_SOFTPLUS, "unknown router kind");
     MK_CHECK_ARG(desc->experts != nullptr, "experts table is NULL");
-    MK_CHECK_ARG((desc->act_mode & ~MK_ACT_STRICT) == MK_ACT_Q8 || desc->act_mode == MK_ACT_E4M3X3,
-                 "the MoE layer takes MK_ACT_Q8 (optionally with MK_ACT_STRICT) or MK_ACT_E4M3X3");
+    MK_CHECK_ARG((desc->act_mode & ~MK_ACT_STRICT) == MK_ACT_Q8 || desc->act_mode == MK_ACT_FP4X6,
+                 "the MoE layer takes MK_ACT_Q8 (optionally with MK_ACT_STRICT) or MK_ACT_FP4X6");
+    MK_CHECK_ARG(desc->act_mode != MK_ACT_FP4X6 || ((latent > 0 ? latent : dx) % 256 == 0 && I % 256 == 0),
+                 "MK_ACT_FP4X6 needs the experts' input width and inter to be multiples of 256");
     const bool situ = desc->activation == MK_MOE_SITU;
     auto f32ok = [](const mk_weight *w, int rows, int cols) { return w && w->fmt == MK_FMT_F32 && w->rows == rows && w->cols == cols; };
     if (latent != 0) {
@@ -979,7 +980,7 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
     m->latent = latent > 0 ? latent : 0;
     m->rms_eps = desc->rms_eps;
     m->strict = (desc->act_mode & MK_ACT_STRICT) != 0;
-    m->tc = desc->act_mode == MK_ACT_E4M3X3;
+    m->tc = desc->act_mode == MK_ACT_FP4X6;
     if (latent > 0) { m->routed_down = (const float *)desc->routed_down->values; m->routed_up = (const float *)desc->routed_up->values; }
     if (sh32) {
         m->sh_gate = (const float *)desc->shared_f32[0]->values;
@@ -1011,9 +1012,9 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
         e_ = cudaMalloc(&m->routed_norm, (size_t)latent * 4);
         if (e_ == cudaSuccess) e_ = cudaMemcpyAsync(m->routed_norm, desc->routed_norm, (size_t)latent * 4, cudaMemcpyHostToDevice, ctx->stream);
     }
-    if (e_ == cudaSuccess && m->tc && d % 128 == 0 && I % 128 == 0) {
-        // The tensor-core path reads row-major nibbles (what TMA's 16U4_ALIGN16B boxes unpack) and scale atoms: a second
-        // copy of every resident expert, made here on the device from the registered (tiled) one.
+    if (e_ == cudaSuccess && m->tc && d % 256 == 0 && I % 256 == 0) {
+        // The tensor-core path reads the nibbles blocked by (128 rows, 256 columns) - a TMA box each - and scale atoms: a
+        // second copy of every resident expert, made here on the device from the registered (tiled) one.
         m->rm_vstride = (int64_t)d * I / 2;
         m->rm_astride = (int64_t)d * I / 32;
         const size_t nmat = hv.size();
@@ -1030,8 +1031,8 @@ extern "C" int32_t mk_moe_create(mk_ctx *ctx, const mk_moe_desc *desc, mk_moe **
             mtc::tc_weight_copy_kernel<<<(unsigned)mk_ceil_div(nthreads, 256), 256, 0, ctx->stream>>>((const uint32_t *)w->values, (const uint8_t *)w->scales, w->rows,
                                                                                                      w->nb, w->nbp, (uint32_t *)vals, atoms);
             ctx->launches++;
-            // as a tensor: rows of 128 codes (64 bytes), rows * cols / 128 of them; a step's box is 128 consecutive rows
-            if (!moe_encode_fp4(&maps[i], vals, 128, (uint64_t)(w->rows * (w->cols / 128)))) {
+            // as a tensor: rows of 256 codes (128 bytes), rows * cols / 256 of them; a step's box is 128 consecutive rows
+            if (!moe_encode_fp4(&maps[i], vals, (uint64_t)(w->rows * (w->cols / 256)))) {
                 mk_set_error("mk_moe_create: cuTensorMapEncodeTiled failed");
                 mk_moe_free(ctx, m);
                 return MK_ERR_CUDA;
@@ -1124,7 +1125,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
                                   const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs,
                                   bool prepared = false, bool quantized = false) {
     // prepared: the fused router kernel has already grouped the pairs; quantized: and quantized x
-    const bool use_tc = m->tc && m->tmaps && !prepared && n_rows >= 32 && m->d % 128 == 0 && m->inter % 128 == 0;
+    const bool use_tc = m->tc && m->tmaps && !prepared && n_rows >= 32 && m->d % 256 == 0 && m->inter % 256 == 0;
     if (use_tc) {
         // many rows: the experts as block-scaled tensor-core products (moe_tc.cuh); work items of up to 32 pairs
         mk_prof_scope prof(ctx, MK_PROF_EXPERTS);

@@ -1,52 +1,48 @@
-// Batched MoE experts on the 5th-generation tensor cores: tcgen05.mma kind::mxf8f6f4 with block scales (sm_100a).
+// Batched MoE experts on the 5th-generation tensor cores: tcgen05.mma kind::mxf4 with block scales (sm_100a).
 //
 // For calls with many token rows (the batch-256 layer: ~5 tokens per routed expert, 256 on the shared one) the expert
-// matvecs are a real contraction.  Swap-AB: 128 weight rows are the M dimension, an expert's tokens the N dimension.
-//   A : the E2M1 codes of the weight in the engine's byte order (src/mxfp4.rs:19-31), blocked so that the 128 codes x
-//       128 rows of a step are one contiguous 8 KB run in HBM (tc_weight_copy_kernel).  The tensor core wants FP4 in
-//       shared memory as 16 codes in the low 8 bytes of a 16-byte chunk, rows of 128 bytes (128 codes) in the
-//       128-byte-swizzled K-major layout: exactly what a tiled TMA copy with the 16U4_ALIGN16B element type writes
-//       (cp.async.bulk.tensor.2d, box = 128 codes x 128 rows, SWIZZLE_128B: 8 KB of global bytes land as a 16 KB
-//       operand tile and count as 8192 bytes on the mbarrier; the gap bytes are not written - zeroed once).  The
-//       mma.sync decode kernels read the weights in their fragment order, so a layer created for this path holds
-//       a second copy of its experts (made on the device at mk_moe_create): twice the weight memory, meant for
-//       layers that see prefill-sized batches.
-//   SFA : the ue8m0 scale bytes of the weight, unchanged, 4 blocks per step, copied into tensor memory (tcgen05.cp
-//       32x128b.warpx4) in the scale-factor layout: lane r, 32-bit column q, byte k = scale of (row r + 32 q, block k).
-//   B : the activations as THREE E4M3 limbs with power-of-two block scales (x = 2^e (h1 + 2^-4 h2 + 2^-8 h3) per block
-//       of 32, each limb the E4M3 rounding of what the previous ones left): 12 significant bits per element, products
-//       exact, f32 accumulation inside the tensor core.  The limbs are further N columns of the same MMA (column
-//       limb * 16 + token, each with its own scale), so a weight tile is read from shared memory once per block; the
-//       epilogue adds the three columns of a token.
+// matvecs are a real contraction.  Swap-AB: 128 weight rows are the M dimension, an expert's tokens the N dimension,
+// both operands FP4 (E2M1) with ue8m0 scales per 32 - the weight's own format - K = 64 per MMA.
+//   A : the E2M1 codes of the weight in the engine's byte order (two codes per byte, low nibble = even column,
+//       src/mxfp4.rs:19-31), blocked so that the 256 codes x 128 rows of a step are one contiguous 16 KB run in HBM
+//       (tc_weight_copy_kernel); a tiled TMA copy (cp.async.bulk.tensor.2d, box = 128 bytes x 128 rows, SWIZZLE_128B, no
+//       multicast) lands it as the K-major operand tile.  The mma.sync decode kernels read the weights in their fragment
+//       order, so a layer created for this path holds a second copy of its experts (made on the device at
+//       mk_moe_create): twice the weight memory, meant for layers that see prefill-sized batches.
+//   SFA : the ue8m0 scale bytes of the weight, unchanged, as 512-byte atoms per (128-row tile, 4 blocks) in the layout
+//       tcgen05.cp 32x128b.warpx4 expects: lane r, 32-bit column q, byte k = scale of (row r + 32 q, block k); an MMA
+//       (2 blocks) takes bytes 0-1 or 2-3 of the word.
+//   B : the activations as SIX E2M1 limbs with power-of-two block scales: per block of 32, e = the smallest exponent
+//       with max|x| <= 6 * 2^e, limb l = E2M1 rounding of what the previous limbs left, at scale 2^(e - 2l): every
+//       limb takes the remainder down by 4, after six it is <= 2^(e - 10) <= max|x| / 3072, every product exact, f32
+//       accumulation in the tensor core.  The limbs are further N columns of the same MMA (column limb * 16 + token,
+//       each with its own scale); the epilogue adds the six columns of a token.
 //       This is NOT the engine's q8_0 activation (src/q8.rs:49-69), whose f32 block scale cannot ride on a block-scaled
-//       MMA; it tracks the engine's exact-f32 path (src/mxfp4.rs:488-539) to ~1e-5 of max |y| (tests hold 1e-3).
-//   D : f32 accumulators in tensor memory; the epilogue reads them with tcgen05.ld.
+//       MMA; it tracks the engine's exact-f32 path (src/mxfp4.rs:488-539) (tests hold 1e-3 of max |y|).
+//   D : f32 accumulators in tensor memory (two sets); the epilogue reads them with tcgen05.ld.
 // Reference semantics: ds_moe / expert_forward (src/deepseek.rs:1038-1108, 74-95), batched as matvec_packed_nt batches
 // (src/model.rs:2412-2447): a (token, expert) result does not depend on which other tokens share the tile.
 //
-// Persistent CTAs (one per SM, 11 warps), work unit = (work item of <= 16 pairs, two 128-row weight tiles), units dealt
-// round-robin.  Warp 10 asks L2 for a step's boxes 12 steps ahead (cp.async.bulk.prefetch) and issues the copies of a step
-// (2 TMA boxes of codes, 2 bulk copies of 512-byte scale atoms) as soon as a stage is free, running on into the next
-// unit; warps 4-7 fetch the step's activation limbs (cp.async) into the stage's B slot and count themselves in on the
-// same barrier; warps 8 and 9 take alternate steps: wait for the stage, copy the scale factors into tensor memory and
-// issue the MMAs into one of two accumulator sets, handing over through a named barrier so that the MMAs keep the
-// order of the steps; tcgen05.commit hands the stage back and, at the end of a unit, the accumulators to warps 0-3,
-// which run the epilogue while the next unit's products are under way.  Every mbarrier wait is bounded; a wait that
-// runs out sets MK_ERR_TIMEOUT in the status word, the roles stop issuing and run their loops to the end (so nobody is
-// left at a named barrier) and tensor memory is freed.  No cluster launch, no multicast.
+// Persistent CTAs (one per SM, 11 warps), work unit = (work item of <= 16 pairs, two 128-row weight tiles), a step = 256
+// columns (32 KB of codes), units dealt round-robin.  Warp 10 asks L2 for a step's boxes some steps ahead
+// (cp.async.bulk.prefetch) and issues the copies of a step (2 TMA boxes of codes, 2 bulk copies of scale atoms) as soon
+// as a stage is free, running on into the next unit; warps 4-7 fetch the step's activation limbs (cp.async) into the
+// stage's B slot and count themselves in on the same barrier; warps 8 and 9 take alternate steps: wait for the stage,
+// copy the scale factors into tensor memory and issue the 8 MMAs into one of two accumulator sets, handing over
+// through a named barrier so that the MMAs keep the order of the steps; tcgen05.commit hands the stage back and, at
+// the end of a unit, the accumulators to warps 0-3, which run the epilogue while the next unit's products are under
+// way.  Every mbarrier wait is bounded; a wait that runs out sets MK_ERR_TIMEOUT in the status word, the roles stop
+// issuing and run their loops to the end (so nobody is left at a named barrier) and tensor memory is freed.  No
+// cluster launch, no multicast.
 //
-// What bounds it now (per-role cycle counters, batch-256 layer of 384 + 1 experts of 7168 x 2048, HBM alone 712 cycles
-// per step of 16 KB of codes): the tensor pipe - 8 block-scaled MMAs of M = 128 per step at ~125 cycles each whatever
-// N is (48 here) - about 1010 cycles per step, with the two issuing warps never waiting for data.
-// History of the operand path, all measured on that layer (experts alone; HBM roofline 0.97 ms): weights kept only in
-// the mma.sync fragment order and re-ordered in shared memory by eight warps (TMA boxes of the tiled blob into a packed
-// ring, 16-byte loads, a shuffle, 8-byte stores) 2.55 ms - the shared-memory pipe carried ~145 KB-equivalents per step
-// (69 % busy in ncu); 4-byte cp.async scatter into the operand form, bound by the L1 pipe, 6.4 ms; 1-KB bulk copies,
-// bound by their count (32 per step at ~45 cycles), 4.9 ms; this TMA-unpacked form with row-major nibbles (every box row
-// a separate 64-byte piece of HBM) 2.43 ms, blocked as above 2.17 ms; one issuing warp instead of two: +90 cycles per
-// step (a barrier wait costs ~200 cycles even when the data is there).  Weights as the N operand (N = 256, 4 MMAs per
-// step, one accumulator set) left the epilogue unoverlapped and was no faster.  M = 64 is refused by the hardware for
-// block-scaled kinds with cta_group::1.
+// History of the operand path, all measured on the batch-256 layer (384 + 1 experts of 7168 x 2048, experts alone, HBM
+// roofline 0.97 ms, 712 cycles per 16 KB of codes): kind::mxf8f6f4 (weights FP4 in the padded operand form, activations
+// as three E4M3 limbs, K = 32 per MMA, 8 MMAs per 16 KB of codes at ~125 cycles each whatever N is) - weights kept only
+// in the mma.sync fragment order and re-ordered in shared memory by eight warps 2.55 ms (shared-memory pipe 69 % busy),
+// 4-byte cp.async scatter 6.4 ms, 1-KB bulk copies 4.9 ms, TMA's 4-bit unpack (16U4_ALIGN16B boxes) of row-major nibbles
+// 2.43 ms, of a blocked copy 2.13 ms with the tensor pipe as the bound (~1010 cycles per 16 KB).  kind::mxf4 halves the
+// MMAs per byte.  Weights as the N operand (N = 256, one accumulator set) left the epilogue unoverlapped and was no
+// faster; M = 64 is refused by the hardware for block-scaled kinds with cta_group::1.
 #pragma once
 #include <cuda_fp8.h>
 
@@ -55,24 +51,25 @@
 namespace mtc {
 
 constexpr int NT = 16;                 // token rows (pairs) per work item
-constexpr int KSTEP = 128;
+constexpr int NL = 6;                  // E2M1 limbs of an activation
+constexpr int KSTEP = 256;             // columns per step: one 128-byte swizzled row of packed codes
 constexpr int NEPI = 128, NFETCH = 128, THREADS = NEPI + NFETCH + 96;   // 4 epilogue + 4 limb-fetch warps + 2 MMA warps + the loader warp
 constexpr int W_FETCH = NEPI / 32, W_MMA = (NEPI + NFETCH) / 32, W_LOAD = W_MMA + 2;
-constexpr int NS = 5;                  // stages (HBM reads in flight: NS x 17 KB of global bytes)
-constexpr int PF = 12;                 // the loader asks L2 for a step's boxes PF steps before it loads them: HBM latency is taken there,
-                                       // not in the NS stages (5 x 17 KB in flight per SM would cover ~2 us at the SM's share of the bandwidth)
+constexpr int NS = 4;                  // stages (HBM reads in flight: NS x 34 KB)
+constexpr int PF = 6;                  // the loader asks L2 for a step's boxes PF steps before it loads them
 constexpr int LAG = 2;                 // the limb fetchers signal a stage LAG steps after issuing its copies
-constexpr int A_BYTES = 128 * 128;     // one 128-row tile in operand form: [128 rows][128 B], 8 KB of codes
-constexpr int B_BYTES = 3 * NT * 128;  // the three limbs of a step: rows limb * NT + token, [48 rows][128 B]
-constexpr int ST_A0 = 0, ST_A1 = A_BYTES, ST_SFA = 2 * A_BYTES, ST_SFB = ST_SFA + 1024, ST_B = 2 * A_BYTES + 2048;
+constexpr int A_BYTES = 128 * 128;     // one 128-row tile of a step: [128 rows][128 B = 256 codes]
+constexpr int B_BYTES = NL * NT * 128; // the limbs of a step: rows limb * NT + token, [96 rows][128 B]
+constexpr int ST_A0 = 0, ST_A1 = A_BYTES, ST_SFA = 2 * A_BYTES, ST_SFB = ST_SFA + 2048, ST_B = ST_SFB + 1024;   // SFA: 2 tiles x 2 atoms, SFB: 2 atoms
 constexpr int STAGE_BYTES = ((ST_B + B_BYTES + 1023) / 1024) * 1024;
-constexpr uint32_t STEP_TX = 2 * 8192 + 2 * 512;           // bytes the loader's four copies of a step bring (global bytes)
+constexpr uint32_t STEP_TX = 2 * 16384 + 2 * 1024;         // bytes the loader's four copies of a step bring
 constexpr int SM_BAR = NS * STAGE_BYTES;
 constexpr int BAR_FULL = 0, BAR_EMPTY = NS, BAR_ACCF = 2 * NS, BAR_ACCE = 2 * NS + 2;
 constexpr int N_BARS = BAR_ACCE + 2;
 constexpr int SM_TOTAL = SM_BAR + 256 + 1024;              // barriers, tensor-memory slot, abort flag; + slack to align the base to 1024 bytes
-constexpr int TMEM_COLS = 256, ACC_COLS = 6 * NT, COL_D1 = 3 * NT, COL_SF = 2 * ACC_COLS;   // 2 accumulator sets; SF: 2 buffers x 3 atoms x 4 columns
-static_assert(N_BARS * 8 <= 192 && SM_TOTAL <= 232448, "shared memory of one CTA");
+constexpr int NCOL = NL * NT;                              // accumulator columns of one tile: limb * NT + token
+constexpr int TMEM_COLS = 512, ACC_COLS = 2 * NCOL, COL_D1 = NCOL, COL_SF = 2 * ACC_COLS;   // 2 accumulator sets; SF: 2 buffers x 6 atoms x 4 columns
+static_assert(N_BARS * 8 <= 192 && SM_TOTAL <= 232448 && COL_SF + 48 <= TMEM_COLS, "shared and tensor memory of one CTA");
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -80,13 +77,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) |
            (1ull << 46) | (layout << 61);
 }
-// block-scaled instruction descriptor: A = E2M1, B = E4M3, ue8m0 scales, M = 128, N = n, scale bytes `sf` of both operands
+// block-scaled instruction descriptor of kind::mxf4: A = B = E2M1 (format 1), ue8m0 scales, M = 128, N = n, K = 64; `sf` = first
+// of the two scale bytes of both operands' scale words (0 or 2)
 __device__ __forceinline__ uint32_t idesc_mx(int n, int sf) {
-    return (5u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | ((uint32_t)sf << 29) | ((uint32_t)sf << 4);
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | ((uint32_t)sf << 29) | ((uint32_t)sf << 4);
 }
 __device__ __forceinline__ void mma_mx(uint32_t d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc, uint32_t sfa, uint32_t sfb) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(d), "l"(da), "l"(db), "r"(idesc),
+                 "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(d), "l"(da), "l"(db), "r"(idesc),
                  "r"(acc), "r"(sfa), "r"(sfb)
                  : "memory");
 }
@@ -143,29 +141,31 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(u[i]);
 }
 
-// ---------------------------------------------------------------- activations -> three E4M3 limbs per block of 32
-// One warp per (row, block): e = exponent of the block maximum - 7 (so |x| 2^-e < 256), limb k = E4M3(rest * 2^(4k)) with the
-// rest taken exactly in f32; scale bytes e + 127, e + 123, e + 119 (ue8m0).  A zero block gets zero limbs.
-__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
-    const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
-    return __half2float(*(const __half *)&h);
-}
-__device__ __forceinline__ void limbs_of(float v, float mx, uint8_t (&limb)[3], uint8_t (&sf)[3]) {
+// ---------------------------------------------------------------- activations -> six E2M1 limbs per block of 32
+// e = the smallest exponent with mx <= 6 * 2^e; limb l = the E2M1 code nearest to the remainder at scale 2^(e - 2l) (the
+// remainder after a limb is at most 1 at that limb's scale, i.e. 4 <= 6 at the next); scale bytes e + 127 - 2l (ue8m0).
+// Everything exact in f32.  A zero (or non-finite) block gets zero limbs.
+__device__ __forceinline__ void limbs_of(float v, float mx, uint32_t (&code)[NL], uint8_t (&sf)[NL]) {
     if (!(mx > 0.0f) || !(mx < INFINITY)) {
-        limb[0] = limb[1] = limb[2] = 0; sf[0] = sf[1] = sf[2] = 127;
+#pragma unroll
+        for (int l = 0; l < NL; ++l) { code[l] = 0u; sf[l] = 127; }
         return;
     }
-    int e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 - 7;      // mx = m 2^E, 1 <= m < 2 (subnormal maxima read as 2^-127): e = E - 7
-    e = e < -119 ? -119 : (e > 127 ? 127 : e);                          // all three scale bytes stay inside ue8m0
-    const float inv = __uint_as_float((uint32_t)(127 - e) << 23);       // 2^-e, exact (e in [-119, 127] keeps it normal)
-    float r = __fmul_rn(v, inv);
+    const uint32_t mb = __float_as_uint(mx);
+    int e = (int)((mb >> 23) & 0xFF) - 127 - (((mb & 0x7FFFFFu) <= 0x400000u) ? 2 : 1);   // mx = m 2^E: m <= 1.5 -> E - 2, else E - 1
+    e = e < -115 ? -115 : (e > 125 ? 125 : e);                                              // all six scale bytes stay inside ue8m0
+    float r = __fmul_rn(v, __uint_as_float((uint32_t)(127 - e) << 23));                      // v 2^-e, exact
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
-        limb[k] = (uint8_t)__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
-        sf[k] = (uint8_t)(e + 127 - 4 * k);
-        r = __fmul_rn(__fsub_rn(r, e4m3_to_f32(limb[k])), 16.0f);
+    for (int l = 0; l < NL; ++l) {
+        const float a = fabsf(r);
+        const uint32_t idx = a < 0.25f ? 0u : a < 0.75f ? 1u : a < 1.25f ? 2u : a < 1.75f ? 3u : a < 2.5f ? 4u : a < 3.5f ? 5u : a < 5.0f ? 6u : 7u;
+        const float val = idx < 4u ? 0.5f * (float)idx : (idx == 4u ? 2.0f : idx == 5u ? 3.0f : idx == 6u ? 4.0f : 6.0f);
+        code[l] = idx | (r < 0.0f ? 8u : 0u);
+        sf[l] = (uint8_t)(e + 127 - 2 * l);
+        r = __fmul_rn(__fsub_rn(r, copysignf(val, r)), 4.0f);
     }
 }
+// x [rows][cols] f32 -> xl [NL][rows][cols / 2] (two codes per byte, low nibble = even column), xsf [NL][rows][cols / 32]
 __global__ void __launch_bounds__(256) act_limbs_kernel(const float *__restrict__ x, int rows, int cols, int64_t ldx, uint8_t *__restrict__ xl,
                                                         uint8_t *__restrict__ xsf) {
     const int64_t unit = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -176,12 +176,14 @@ __global__ void __launch_bounds__(256) act_limbs_kernel(const float *__restrict_
     float mx = fabsf(v);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-    uint8_t limb[3], sf[3];
-    limbs_of(v, mx, limb, sf);
+    uint32_t code[NL];
+    uint8_t sf[NL];
+    limbs_of(v, mx, code, sf);
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
-        xl[((int64_t)k * rows + r) * cols + b * 32 + lane] = limb[k];
-        if (lane == 0) xsf[((int64_t)k * rows + r) * nb + b] = sf[k];
+    for (int l = 0; l < NL; ++l) {
+        const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, code[l], 1);
+        if (!(lane & 1)) xl[((int64_t)l * rows + r) * (cols / 2) + b * 16 + (lane >> 1)] = (uint8_t)(code[l] | (hi << 4));
+        if (lane == 0) xsf[((int64_t)l * rows + r) * nb + b] = sf[l];
     }
 }
 
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(256) tc_rows_kernel(const int32_t *__restrict_
 }
 
 struct TcArgs {
-    const unsigned char *maps;   // [(E+1)*3] tensor maps (128 B each) of the row-major nibble copies [rows][K / 2]
+    const unsigned char *maps;   // [(E+1)*3] tensor maps (128 B each) of the blocked copies: rows of 128 bytes, a step's box = 128 consecutive rows
     const uint8_t *atoms;        // scale atoms of matrix i at atoms + i * atom_stride: [rows / 128][K / 128][512]
     int64_t atom_stride;
     const int32_t *items;        // [n][3] = expert, offset into sorted, count (<= NT)
@@ -206,8 +208,8 @@ struct TcArgs {
     const int32_t *pair_row;
     const float *pair_weight;
     const int32_t *rows_x, *rows_p;   // [items][NT]: token row / pair id of an item's tokens (one load level for the limb fetchers)
-    const uint8_t *xl, *xsf;     // token limbs [3][rows][d], [3][rows][d/32]
-    uint8_t *actl, *actsf;       // activation limbs [3][pairs][inter], [3][pairs][inter/32]
+    const uint8_t *xl, *xsf;     // token limbs [NL][rows][d / 2], [NL][rows][d / 32]
+    uint8_t *actl, *actsf;       // activation limbs [NL][pairs][inter / 2], [NL][pairs][inter / 32]
     float *outs;                 // [pairs][d]
     int rows, pairs, d, inter;
     int activation;
@@ -215,28 +217,28 @@ struct TcArgs {
     int32_t *status;
 };
 
-// The tensor-core path's copy of a registered (tiled) MXFP4 matrix [rows][cols], rows % 128 == 0, cols % 128 == 0:
-//   vals : nibbles blocked by (128-row tile, 128-column step): [rows / 128][cols / 128][128 rows][64 bytes] - the box a step
-//          loads (128 codes x 128 rows) is one contiguous 8 KB run in HBM; within a row the engine's byte order
+// The tensor-core path's copy of a registered (tiled) MXFP4 matrix [rows][cols], rows % 128 == 0, cols % 256 == 0:
+//   vals : nibbles blocked by (128-row tile, 256-column step): [rows / 128][cols / 256][128 rows][128 bytes] - the box a step
+//          loads (256 codes x 128 rows) is one contiguous 16 KB run in HBM; within a row the engine's byte order
 //          (low nibble = even column, src/mxfp4.rs:19-31)
 //   atoms: scale bytes [rows / 128][cols / 128][512]: byte (r % 32) * 16 + (r / 32) * 4 + k = scale of (row r of the tile,
-//          block k of the step), the layout tcgen05.cp 32x128b.warpx4 expects
+//          block k of the four), the layout tcgen05.cp 32x128b.warpx4 expects; a step takes two consecutive atoms
 // tv / ts: the tiled values and scales (weights.cu: 512-byte chunks per 16 rows x 2 blocks; mk_scale_off).
 __global__ void __launch_bounds__(256) tc_weight_copy_kernel(const uint32_t *__restrict__ tv, const uint8_t *__restrict__ ts, int64_t rows, int64_t nb,
                                                              int64_t nbp, uint32_t *__restrict__ vals, uint8_t *__restrict__ atoms) {
-    const int64_t nrt = rows / 16, nsteps = nb / 4;
+    const int64_t nrt = rows / 16, nsteps = nb / 8;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < nrt * (nbp / 2) * 128) {
         const int64_t chunk = idx >> 7;
         const int within = (int)(idx & 127), ln = within >> 2, j = within & 3, g = ln >> 2, t = ln & 3;
         const int64_t rt = chunk / (nbp / 2), bp = chunk % (nbp / 2);
         const int64_t row = rt * 16 + g + ((j & 1) ? 8 : 0), blk = bp * 2 + (j >> 1);
-        if (blk < nb) vals[(((row >> 7) * nsteps + (blk >> 2)) * 128 + (row & 127)) * 16 + (blk & 3) * 4 + t] = tv[idx];
+        if (blk < nb) vals[(((row >> 7) * nsteps + (blk >> 3)) * 128 + (row & 127)) * 32 + (blk & 7) * 4 + t] = tv[idx];
     }
     if (idx < rows * nb) {
         const int64_t row = idx / nb, blk = idx % nb;
         const int r = (int)(row & 127);
-        atoms[((row >> 7) * nsteps + (blk >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (blk & 3)] = ts[mk_scale_off(row >> 4, nbp, blk, (int)(row & 15))];
+        atoms[((row >> 7) * (nb >> 2) + (blk >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (blk & 3)] = ts[mk_scale_off(row >> 4, nbp, blk, (int)(row & 15))];
     }
 }
 
@@ -272,7 +274,7 @@ __device__ __forceinline__ void tc_teardown(uint32_t tb) {
 
 // DOWN = false: gate / up + activation + limbs of the activation.  Unit = (item, 128 rows of w1 and the same rows of w3),
 //   K = d; D0 = w1 tile x tokens, D1 = w3 tile x tokens; then act (src/deepseek.rs:1083-1087 or the K3 SiTU,
-//   src/model.rs:617-621) and its three limbs per 32 rows, the input of the w2 product.
+//   src/model.rs:617-621) and its six limbs per 32 rows, the input of the w2 product.
 // DOWN = true: the down projection.  Unit = (item, two consecutive 128-row tiles of w2), K = inter; a tile past the last
 //   one reads as zeros (TMA fill) and is not stored.
 template <bool DOWN>
@@ -304,16 +306,16 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
             const int i0 = e * 3 + (DOWN ? 1 : 0), i1 = e * 3 + (DOWN ? 1 : 2);
             const int t0 = DOWN ? 2 * xt : xt, t1 = DOWN ? 2 * xt + 1 : xt;              // 128-row tiles of the two matrices
             r.m0 = a.maps + (size_t)i0 * 128; r.m1 = a.maps + (size_t)i1 * 128;
-            r.s0 = a.atoms + i0 * a.atom_stride + (size_t)t0 * nsteps * 512;
-            r.s1 = a.atoms + i1 * a.atom_stride + (size_t)min(t1, ntile - 1) * nsteps * 512;   // a tile past the end: zero codes, any scales
+            r.s0 = a.atoms + i0 * a.atom_stride + (size_t)t0 * nsteps * 1024;
+            r.s1 = a.atoms + i1 * a.atom_stride + (size_t)min(t1, ntile - 1) * nsteps * 1024;   // a tile past the end: zero codes, any scales
             r.y0 = t0 * nsteps * 128; r.y1 = t1 * nsteps * 128;
             return r;
         };
         auto prefetch = [&](const Src &r, int it) {
             tma_2d_prefetch(r.m0, 0, r.y0 + it * 128);
             tma_2d_prefetch(r.m1, 0, r.y1 + it * 128);
-            bulk_prefetch(r.s0 + (size_t)it * 512, 512);
-            bulk_prefetch(r.s1 + (size_t)it * 512, 512);
+            bulk_prefetch(r.s0 + (size_t)it * 1024, 1024);
+            bulk_prefetch(r.s1 + (size_t)it * 1024, 1024);
         };
         Src cur = src_of(e_next, c % X);
         if (lane == 0) for (int it = 0; it < min(PF, nsteps); ++it) prefetch(cur, it);
@@ -332,10 +334,10 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                 if (lane == 0) {
                     const uint32_t full = bar0 + (BAR_FULL + st) * 8, dst = smb + st * STAGE_BYTES;
                     bar_expect(full, STEP_TX);
-                    tma_2d(dst + ST_A0, cur.m0, 0, cur.y0 + it * 128, full);    // 128 codes x 128 rows (8 KB, contiguous) -> a 16 KB operand tile
+                    tma_2d(dst + ST_A0, cur.m0, 0, cur.y0 + it * 128, full);    // 256 codes x 128 rows: 16 KB, contiguous in HBM
                     tma_2d(dst + ST_A1, cur.m1, 0, cur.y1 + it * 128, full);
-                    bulk_g2s(dst + ST_SFA, cur.s0 + (size_t)it * 512, 512, full);
-                    bulk_g2s(dst + ST_SFA + 512, cur.s1 + (size_t)it * 512, 512, full);
+                    bulk_g2s(dst + ST_SFA, cur.s0 + (size_t)it * 1024, 1024, full);          // the step's two scale atoms of each tile
+                    bulk_g2s(dst + ST_SFA + 1024, cur.s1 + (size_t)it * 1024, 1024, full);
                 }
                 __syncwarp();
             }
@@ -347,7 +349,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
         // The warp of step gs waits for the stage while the other one issues step gs - 1, then takes over through a named
         // barrier (the order of the MMAs into one accumulator must be the order of the steps).  All lanes wait, lane 0 issues.
         const int wid = warp - W_MMA;
-        const uint32_t id[4] = {idesc_mx(3 * NT, 0), idesc_mx(3 * NT, 1), idesc_mx(3 * NT, 2), idesc_mx(3 * NT, 3)};
+        const uint32_t id[2] = {idesc_mx(NCOL, 0), idesc_mx(NCOL, 2)};
         for (int gs = wid; gs < total; gs += 2) {
             const int k = gs / nsteps, it = gs - k * nsteps, acc = k & 1, st = gs % NS;
             if (ok && !bar_wait(bar0 + (BAR_FULL + st) * 8, (uint32_t)(gs / NS) & 1u, abort)) ok = false;
@@ -357,17 +359,18 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
             if (ok && lane == 0) {
                 const uint32_t d0 = tb + acc * ACC_COLS, d1 = d0 + COL_D1;
                 const uint32_t base = smb + st * STAGE_BYTES, a0 = base + ST_A0, a1 = base + ST_A1, bb = base + ST_B;
-                const uint32_t tsf = tb + COL_SF + (uint32_t)wid * 12;
-                sf_copy(tsf + 0, base + ST_SFA);
-                sf_copy(tsf + 4, base + ST_SFA + 512);
-                sf_copy(tsf + 8, base + ST_SFB);
+                const uint32_t tsf = tb + COL_SF + (uint32_t)wid * 24;                     // atoms: A0 x 2, A1 x 2, B x 2
 #pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
+                for (int q = 0; q < 4; ++q) sf_copy(tsf + q * 4, base + ST_SFA + q * 512);
+                sf_copy(tsf + 16, base + ST_SFB);
+                sf_copy(tsf + 20, base + ST_SFB + 512);
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {                                           // 64 columns each: atom kb / 2, scale bytes 0-1 or 2-3
                     const uint64_t da0 = smem_desc(a0 + kb * 32, 16, 1024, 2), da1 = smem_desc(a1 + kb * 32, 16, 1024, 2);
                     const uint64_t db = smem_desc(bb + kb * 32, 16, 1024, 2);
-                    const uint32_t accum = (it > 0 || kb > 0) ? 1u : 0u;
-                    mma_mx(d0, da0, db, id[kb], accum, tsf + 0, tsf + 8);
-                    mma_mx(d1, da1, db, id[kb], accum, tsf + 4, tsf + 8);
+                    const uint32_t accum = (it > 0 || kb > 0) ? 1u : 0u, at = (uint32_t)(kb >> 1) * 4;
+                    mma_mx(d0, da0, db, id[kb & 1], accum, tsf + at, tsf + 16 + at);
+                    mma_mx(d1, da1, db, id[kb & 1], accum, tsf + 8 + at, tsf + 16 + at);
                 }
                 commit(bar0 + (BAR_EMPTY + st) * 8);                       // the stage is free once these MMAs have read it
                 if (it == nsteps - 1) commit(bar0 + (BAR_ACCF + acc) * 8);  // the unit's accumulators are complete
@@ -377,8 +380,8 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
             if (gs + 1 < total) asm volatile("bar.arrive %0, 64;" ::"r"(2 + (1 - wid)) : "memory");   // hand over to the warp of step gs + 1
         }
     } else if (warp >= W_FETCH) {
-        // ---------------- limb fetchers: thread = (token gp >> 3, 16-byte chunk gp & 7) of the three limb rows, and the scale
-        // word of token gp % NT, limb gp / NT
+        // ---------------- limb fetchers: thread = (token gp >> 3, 16-byte chunk gp & 7) of the six limb rows of a step (256 codes =
+        // 128 bytes per row), and, for gp < 96, the eight scale bytes of row gp = limb * NT + token
         const int gp = tid - NEPI;
         const uint8_t *bl = DOWN ? a.actl : a.xl, *bsf = DOWN ? a.actsf : a.xsf;
         const int64_t b_rows = DOWN ? a.pairs : a.rows;
@@ -390,18 +393,18 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
             const int item = u / X;
             r.n = min(a.items[item * 3 + 2], NT);
             const int64_t r0 = rows_tab[item * NT + (gp >> 3)], r1 = rows_tab[item * NT + (gp & (NT - 1))];
-            r.main = bl + r0 * K + (gp & 7) * 16;
+            r.main = bl + r0 * (K / 2) + (gp & 7) * 16;
             r.sf = bsf + ((int64_t)(gp / NT) * b_rows + r1) * (K / 32);
             return r;
         };
         int fk = 0, fit = 0;
         Rows cur = rows_of(c), nxt = cur;
         if (nunits > 1) nxt = rows_of(c + G);
-        const int64_t limb_stride = b_rows * K;
+        const int64_t limb_stride = b_rows * (K / 2);
         const int bt0 = gp >> 3, bch = gp & 7;
         const uint32_t bdst = (uint32_t)(bt0 * 128 + ((bch ^ (bt0 & 7)) << 4));       // limb rows 16 apart keep the swizzle phase
-        const bool sf_thread = gp < 3 * NT;
-        const uint32_t sfdst = (uint32_t)((gp & 31) * 16 + (gp >> 5) * 4);            // row limb * 16 + token of the scale atom = gp
+        const bool sf_thread = gp < NL * NT;
+        const uint32_t sfdst = (uint32_t)((gp & 31) * 16 + (gp >> 5) * 4);            // row gp of a scale atom
         for (int f = 0; f < total + LAG; ++f) {
             if (f < total) {
                 const int st = f % NS;
@@ -409,12 +412,14 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                 if (ok) {
                     const uint32_t bb = smb + st * STAGE_BYTES + ST_B + bdst, sfb = smb + st * STAGE_BYTES + ST_SFB + sfdst;
                     if (bt0 < cur.n) {
-                        const uint8_t *src = cur.main + (int64_t)fit * KSTEP;
-                        cp16(bb, src);
-                        cp16(bb + NT * 128, src + limb_stride);
-                        cp16(bb + 2 * NT * 128, src + 2 * limb_stride);
+                        const uint8_t *src = cur.main + (int64_t)fit * (KSTEP / 2);
+#pragma unroll
+                        for (int l = 0; l < NL; ++l) cp16(bb + l * NT * 128, src + l * limb_stride);
                     }
-                    if (sf_thread && (gp & (NT - 1)) < cur.n) cp4(sfb, cur.sf + (int64_t)fit * 4);
+                    if (sf_thread && (gp & (NT - 1)) < cur.n) {
+                        cp4(sfb, cur.sf + (int64_t)fit * 8);                // blocks 0-3 of the step -> atom 0
+                        cp4(sfb + 512, cur.sf + (int64_t)fit * 8 + 4);      // blocks 4-7 -> atom 1
+                    }
                 }
                 if (++fit == nsteps) {
                     fit = 0; ++fk; cur = nxt;
@@ -438,21 +443,25 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
         const int q = warp;
         for (int k = 0; k < nunits; ++k) {
             const int u = c + k * G, item = u / X, xt = u % X, acc = k & 1;
-            const int off = a.items[item * 3 + 1], n = min(a.items[item * 3 + 2], NT), npad = NT;
+            const int off = a.items[item * 3 + 1], n = min(a.items[item * 3 + 2], NT);
             if (!bar_wait(bar0 + (BAR_ACCF + acc) * 8, (uint32_t)(k >> 1) & 1u, abort)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tb + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
-            float v0[16], v1[16], l1[16], l2[16];      // a token's three limb products sit npad columns apart
-            tmem_ld16(taddr, v0);
-            tmem_ld16(taddr + npad, l1);
-            tmem_ld16(taddr + 2 * npad, l2);
+            float v0[16], v1[16], t[16];      // a token's limb products sit NT columns apart; added from the finest limb up
+            tmem_ld16(taddr + (NL - 1) * NT, v0);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v0[i] = __fadd_rn(__fadd_rn(v0[i], l1[i]), l2[i]);
-            tmem_ld16(taddr + COL_D1, v1);
-            tmem_ld16(taddr + COL_D1 + npad, l1);
-            tmem_ld16(taddr + COL_D1 + 2 * npad, l2);
+            for (int l = NL - 2; l >= 0; --l) {
+                tmem_ld16(taddr + l * NT, t);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v1[i] = __fadd_rn(__fadd_rn(v1[i], l1[i]), l2[i]);
+                for (int i = 0; i < 16; ++i) v0[i] = __fadd_rn(v0[i], t[i]);
+            }
+            tmem_ld16(taddr + COL_D1 + (NL - 1) * NT, v1);
+#pragma unroll
+            for (int l = NL - 2; l >= 0; --l) {
+                tmem_ld16(taddr + COL_D1 + l * NT, t);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v1[i] = __fadd_rn(v1[i], t[i]);
+            }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) bar_arrive(bar0 + (BAR_ACCE + acc) * 8);            // the accumulator set may be overwritten
@@ -475,11 +484,13 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                     float mx = fabsf(act);
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-                    uint8_t limb[3], sf[3];
-                    limbs_of(act, mx, limb, sf);
+                    uint32_t code[NL];
+                    uint8_t sf[NL];
+                    limbs_of(act, mx, code, sf);
 #pragma unroll
-                    for (int l = 0; l < 3; ++l) {
-                        a.actl[((int64_t)l * a.pairs + pid) * a.inter + col] = limb[l];
+                    for (int l = 0; l < NL; ++l) {          // two columns per byte: the even lane stores its code and its neighbour's
+                        const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, code[l], 1);
+                        if (!(lane & 1)) a.actl[((int64_t)l * a.pairs + pid) * (a.inter / 2) + (col >> 1)] = (uint8_t)(code[l] | (hi << 4));
                         if (lane == 0) a.actsf[((int64_t)l * a.pairs + pid) * nbi + (col >> 5)] = sf[l];
                     }
                 }

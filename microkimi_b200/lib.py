@@ -12,7 +12,7 @@ MK_OK = 0
 MK_ERR_ARG, MK_ERR_CUDA, MK_ERR_OOM, MK_ERR_STATE, MK_ERR_TIMEOUT, MK_ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
 MK_ACT_Q8 = 0
 MK_ACT_Q8X2 = 1
-MK_ACT_E4M3X3 = 2
+MK_ACT_FP4X6 = 2
 MK_ACT_STRICT = 0x100
 MK_SCALE_F32 = 0
 MK_SCALE_F16 = 1

@@ -176,7 +176,7 @@ def test_moe_layer_384_experts(mk, big_moe, batch, checked):
         assert np.array_equal(bits(layer.moe_forward(x[t])), bits(out[t]))
     if batch >= 32:
         # the block-scaled tensor-core path on the same weights: held to the engine's exact-f32 path (src/mxfp4.rs:488-539)
-        tc = mk.MoeLayer(gate_w, None, layer._keep[0], layer._keep[1], k, act="e4m3x3")
+        tc = mk.MoeLayer(gate_w, None, layer._keep[0], layer._keep[1], k, act="fp4x6")
         out_tc, ids_tc, _ = tc.moe_forward(x, want_routing=True)
         assert np.array_equal(ids_tc, ids)
         worst_tc = max(rel(out_tc[t], ref.forward(x[t], use_q8=False, n_threads=O.num_threads())[0]) for t in pick)
