@@ -110,10 +110,25 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp4(uint32_t dst, const void *src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory"); }
-__device__ __forceinline__ void cp16(uint32_t dst, const void *src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory"); }
-__device__ __forceinline__ void tma_2d(uint32_t dst, const void *map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst), "l"(map),
-                 "r"(x), "r"(y), "r"(bar)
+// L2 eviction priorities: the weights stream through once (evict_first), the activation limbs are read again by every
+// tile of every expert their token visits (evict_last) - without the hints the stream pushes limb rows out of L2 and
+// they come back from HBM
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void *src, uint64_t pol) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const void *map, int x, int y, uint32_t bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;\n" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol)
                  : "memory");
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -317,6 +332,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
             bulk_prefetch(r.s0 + (size_t)it * 1024, 1024);
             bulk_prefetch(r.s1 + (size_t)it * 1024, 1024);
         };
+        const uint64_t pol = policy_evict_first();
         Src cur = src_of(e_next, c % X);
         if (lane == 0) for (int it = 0; it < min(PF, nsteps); ++it) prefetch(cur, it);
         for (int k = 0; k < nunits && ok; ++k) {
@@ -334,8 +350,8 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                 if (lane == 0) {
                     const uint32_t full = bar0 + (BAR_FULL + st) * 8, dst = smb + st * STAGE_BYTES;
                     bar_expect(full, STEP_TX);
-                    tma_2d(dst + ST_A0, cur.m0, 0, cur.y0 + it * 128, full);    // 256 codes x 128 rows: 16 KB, contiguous in HBM
-                    tma_2d(dst + ST_A1, cur.m1, 0, cur.y1 + it * 128, full);
+                    tma_2d(dst + ST_A0, cur.m0, 0, cur.y0 + it * 128, full, pol);    // 256 codes x 128 rows: 16 KB, contiguous in HBM
+                    tma_2d(dst + ST_A1, cur.m1, 0, cur.y1 + it * 128, full, pol);
                     bulk_g2s(dst + ST_SFA, cur.s0 + (size_t)it * 1024, 1024, full);          // the step's two scale atoms of each tile
                     bulk_g2s(dst + ST_SFA + 1024, cur.s1 + (size_t)it * 1024, 1024, full);
                 }
@@ -404,6 +420,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
         const int bt0 = gp >> 3, bch = gp & 7;
         const uint32_t bdst = (uint32_t)(bt0 * 128 + ((bch ^ (bt0 & 7)) << 4));       // limb rows 16 apart keep the swizzle phase
         const bool sf_thread = gp < NL * NT;
+        const uint64_t pol = policy_evict_last();
         const uint32_t sfdst = (uint32_t)((gp & 31) * 16 + (gp >> 5) * 4);            // row gp of a scale atom
         for (int f = 0; f < total + LAG; ++f) {
             if (f < total) {
@@ -414,7 +431,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tc_kernel(const TcArgs a) {
                     if (bt0 < cur.n) {
                         const uint8_t *src = cur.main + (int64_t)fit * (KSTEP / 2);
 #pragma unroll
-                        for (int l = 0; l < NL; ++l) cp16(bb + l * NT * 128, src + l * limb_stride);
+                        for (int l = 0; l < NL; ++l) cp16(bb + l * NT * 128, src + l * limb_stride, pol);
                     }
                     if (sf_thread && (gp & (NT - 1)) < cur.n) {
                         cp4(sfb, cur.sf + (int64_t)fit * 8);                // blocks 0-3 of the step -> atom 0
