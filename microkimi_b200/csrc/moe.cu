@@ -514,11 +514,10 @@ __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFused
 // Single block: counting sort of the pairs by expert, then one work item per
 // (expert, chunk of <= 8 pairs).  Pairs naming an expert that is not resident are
 // dropped and flagged in the status word.
-__global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots /* n_experts + 1 */,
-                const void *const *__restrict__ wv, int32_t *__restrict__ sorted, int32_t *__restrict__ items,
-                int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status, int chunk /* pairs per work item: 8, or 16 */) {
-    extern __shared__ int sh[];
+__device__ __forceinline__ void
+plan_body(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots /* n_experts + 1 */,
+          const void *const *__restrict__ wv, int32_t *__restrict__ sorted, int32_t *__restrict__ items,
+          int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status, int chunk /* pairs per work item: 8, or 16 */, int *sh) {
     int *cnt = sh, *off = sh + n_slots, *ioff = off + n_slots, *cur = ioff + n_slots;
     for (int e = threadIdx.x; e < n_slots; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
     __syncthreads();
@@ -557,6 +556,12 @@ moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slot
         }
     }
 }
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots, const void *const *__restrict__ wv, int32_t *__restrict__ sorted,
+                int32_t *__restrict__ items, int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status, int chunk) {
+    extern __shared__ int sh[];
+    plan_body(pair_expert, n_pairs, n_slots, wv, sorted, items, n_items, max_items, status, chunk, sh);
+}
 
 } // namespace
 
@@ -585,6 +590,30 @@ struct MoeArgs {
 } // namespace
 #include "moe_tc.cuh"
 namespace {
+
+// Everything the tensor-core expert kernels need, one launch: block 0 groups the pairs by expert (plan_body) and writes
+// the per-item row tables; the other blocks turn the token rows into their E2M1 limbs.  Neither half needs the other.
+__global__ void __launch_bounds__(1024)
+moe_tc_prepare_kernel(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots, const void *const *__restrict__ wv, int32_t *__restrict__ sorted,
+                      int32_t *__restrict__ items, int32_t *__restrict__ n_items, int max_items, int32_t *__restrict__ status,
+                      const int32_t *__restrict__ pair_row, int32_t *__restrict__ rows_x, int32_t *__restrict__ rows_p, const float *__restrict__ x,
+                      int n_rows, int cols, int64_t ldx, uint8_t *__restrict__ xl, uint8_t *__restrict__ xsf) {
+    extern __shared__ int sh[];
+    if (blockIdx.x == 0) {
+        plan_body(pair_expert, n_pairs, n_slots, wv, sorted, items, n_items, max_items, status, mtc::NT, sh);
+        __syncthreads();        // this block's own writes of items / sorted / n_items, read back below
+        const int ni = *n_items;
+        for (int idx = threadIdx.x; idx < max_items * mtc::NT; idx += blockDim.x) {
+            const int item = idx / mtc::NT, t = idx % mtc::NT;
+            int p = 0;
+            if (item < ni && t < min(items[item * 3 + 2], mtc::NT)) p = sorted[items[item * 3 + 1] + t];
+            rows_p[idx] = p;
+            rows_x[idx] = pair_row[p];
+        }
+        return;
+    }
+    mtc::act_limbs_body(x, n_rows, cols, ldx, xl, xsf, (int64_t)(blockIdx.x - 1) * blockDim.x + threadIdx.x, (int64_t)(gridDim.x - 1) * blockDim.x);
+}
 
 // Partial sums of one warp for a 16-row tile and up to 8 columns, into smem part[16][8].
 // SPREAD: items of <= 2 columns (or, without BATCHED, any item by repeated passes) take the
@@ -1130,11 +1159,11 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
         // many rows: the experts as block-scaled tensor-core products (moe_tc.cuh); work items of up to 32 pairs
         mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
         const int slots = m->n_experts + 1;
-        mtc::act_limbs_kernel<<<(unsigned)mk_ceil_div((int64_t)n_rows * (m->d / 32) * 32, 256), 256, 0, ctx->stream>>>(x, n_rows, m->d, m->d, m->xl, m->xsf);
-        moe_plan_kernel<<<1, 1024, (size_t)slots * 4 * sizeof(int), ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted, m->items,
-                                                                                  m->n_items, m->max_items, ctx->status_dev, mtc::NT);
-        mtc::tc_rows_kernel<<<(unsigned)mk_ceil_div((int64_t)m->max_items * mtc::NT, 256), 256, 0, ctx->stream>>>(m->items, m->n_items, m->sorted, pair_row,
-                                                                                                              m->tc_rows_x, m->tc_rows_p, m->max_items);
+        MK_CHECK_ARG(((uintptr_t)x & 15) == 0, "MK_ACT_FP4X6: the token rows must be 16-byte aligned");
+        const int64_t limb_threads = (int64_t)n_rows * (m->d / 8);     // 8 columns per thread
+        moe_tc_prepare_kernel<<<1 + (unsigned)std::min<int64_t>(mk_ceil_div(limb_threads, 1024), 4 * ctx->sm_count), 1024, (size_t)slots * 4 * sizeof(int),
+                                ctx->stream>>>(pair_expert, n_pairs, slots, m->wv, m->sorted, m->items, m->n_items, m->max_items, ctx->status_dev, pair_row,
+                                               m->tc_rows_x, m->tc_rows_p, x, n_rows, m->d, m->d, m->xl, m->xsf);
         mtc::TcArgs t;
         t.maps = (const unsigned char *)m->tmaps; t.atoms = m->rm_atoms; t.atom_stride = m->rm_astride; t.rows_x = m->tc_rows_x; t.rows_p = m->tc_rows_p; t.items = m->items; t.n_items = m->n_items; t.sorted = m->sorted; t.pair_row = pair_row;
         t.pair_weight = pair_weight; t.xl = m->xl; t.xsf = m->xsf; t.actl = m->actl; t.actsf = m->actsf; t.outs = outs;
@@ -1149,7 +1178,7 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
         // persistent CTAs, one per SM; the work units are dealt round-robin inside the kernels
         mtc::moe_tc_kernel<false><<<(unsigned)ctx->sm_count, mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
         mtc::moe_tc_kernel<true><<<(unsigned)ctx->sm_count, mtc::THREADS, mtc::SM_TOTAL, ctx->stream>>>(t);
-        ctx->launches += 5;
+        ctx->launches += 3;
         MK_CUDA(cudaGetLastError());
         return MK_OK;
     }

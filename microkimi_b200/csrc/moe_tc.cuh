@@ -180,37 +180,49 @@ __device__ __forceinline__ void limbs_of(float v, float mx, uint32_t (&code)[NL]
         r = __fmul_rn(__fsub_rn(r, copysignf(val, r)), 4.0f);
     }
 }
-// x [rows][cols] f32 -> xl [NL][rows][cols / 2] (two codes per byte, low nibble = even column), xsf [NL][rows][cols / 32]
-__global__ void __launch_bounds__(256) act_limbs_kernel(const float *__restrict__ x, int rows, int cols, int64_t ldx, uint8_t *__restrict__ xl,
-                                                        uint8_t *__restrict__ xsf) {
-    const int64_t unit = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31, nb = cols / 32;
-    if (unit >= (int64_t)rows * nb) return;
-    const int64_t r = unit / nb, b = unit % nb;
-    const float v = x[r * ldx + b * 32 + lane];
-    float mx = fabsf(v);
+// x [rows][cols] f32 -> xl [NL][rows][cols / 2] (two codes per byte, low nibble = even column), xsf [NL][rows][cols / 32].
+// A thread takes 8 consecutive columns (four threads = a block of 32) and stores one 32-bit word per limb; `first` and
+// `stride` walk the (row, 8 columns) units grid-stride.  cols % 32 == 0, rows of x 16-byte aligned.
+__device__ __forceinline__ void act_limbs_body(const float *__restrict__ x, int rows, int cols, int64_t ldx, uint8_t *__restrict__ xl,
+                                               uint8_t *__restrict__ xsf, int64_t first, int64_t stride) {
+    const int per_row = cols / 8, nb = cols / 32;
+    const int64_t total = (int64_t)rows * per_row, padded = (total + 31) & ~(int64_t)31;   // whole warps walk the loop (shuffles below)
+    for (int64_t unit = first; unit < padded; unit += stride) {
+        const bool live = unit < total;
+        const int64_t r = live ? unit / per_row : 0;
+        const int c8 = live ? (int)(unit % per_row) : 0;
+        float v[8];
+        if (live) {
+            const float4 lo = *(const float4 *)(x + r * ldx + c8 * 8), hi = *(const float4 *)(x + r * ldx + c8 * 8 + 4);
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+        } else {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-    uint32_t code[NL];
-    uint8_t sf[NL];
-    limbs_of(v, mx, code, sf);
+            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        }
+        float mx = 0.0f;
 #pragma unroll
-    for (int l = 0; l < NL; ++l) {
-        const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, code[l], 1);
-        if (!(lane & 1)) xl[((int64_t)l * rows + r) * (cols / 2) + b * 16 + (lane >> 1)] = (uint8_t)(code[l] | (hi << 4));
-        if (lane == 0) xsf[((int64_t)l * rows + r) * nb + b] = sf[l];
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));     // per_row % 4 == 0: the four threads of a block are lanes 4q .. 4q + 3
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+        uint32_t word[NL];
+        uint8_t sf[NL];
+#pragma unroll
+        for (int l = 0; l < NL; ++l) word[l] = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t code[NL];
+            limbs_of(v[i], mx, code, sf);
+#pragma unroll
+            for (int l = 0; l < NL; ++l) word[l] |= code[l] << (4 * i);
+        }
+        if (live) {
+#pragma unroll
+            for (int l = 0; l < NL; ++l) {
+                *(uint32_t *)(xl + ((int64_t)l * rows + r) * (cols / 2) + c8 * 4) = word[l];
+                if ((c8 & 3) == 0) xsf[((int64_t)l * rows + r) * nb + (c8 >> 2)] = sf[l];
+            }
+        }
     }
-}
-
-// after the grouping: the token row (gate / up) and the pair id (down) of every token slot of every work item
-__global__ void __launch_bounds__(256) tc_rows_kernel(const int32_t *__restrict__ items, const int32_t *__restrict__ n_items, const int32_t *__restrict__ sorted,
-                                                      const int32_t *__restrict__ pair_row, int32_t *__restrict__ rows_x, int32_t *__restrict__ rows_p, int max_items) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x, item = idx / NT, t = idx % NT;
-    if (item >= max_items) return;
-    int p = 0;
-    if (item < *n_items && t < min(items[item * 3 + 2], NT)) p = sorted[items[item * 3 + 1] + t];
-    rows_p[idx] = p;
-    rows_x[idx] = pair_row[p];
 }
 
 struct TcArgs {
