@@ -146,7 +146,7 @@ moe_router_tile_kernel(const float *__restrict__ gate_w, const float *__restrict
 }
 
 
-// Register-tiled form for many tokens (>= 128): one CTA (128 threads) = 16 experts x 16 tokens, every lane octet 4 experts x
+// Register-tiled form for many tokens (>= 64): one CTA (128 threads) = 16 experts x 16 tokens, every lane octet 4 experts x
 // 4 tokens.  Each of the 16 (expert, token) pairs of an octet keeps the engine's dot(): lane j sums the columns = j (mod 8)
 // in ascending order with a separate multiply and add, then the 8 partial sums fold in the engine's tree (mkf::reduce8).
 // The products are issued two at a time (mul.rn.f32x2: each half rounded as the scalar instruction rounds it), the sums
@@ -1148,7 +1148,7 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
             if (n <= RtSmall::NT) {
                 moe_router_tile_kernel<RtSmall><<<dim3((unsigned)mk_ceil_div(E, RtSmall::NE), 1), 256, RtSmall::SMEM, ctx->stream>>>(
                     m->gate_w, m->gate_b, x, m->logits, score, key, E, m->dx, n, m->router_kind);
-            } else if (n >= 128) {   // fewer tokens leave too few CTAs: the 2 x 16 shape is faster there
+            } else if (n >= 64) {   // fewer tokens leave too few CTAs (a lone CTA of 4 warps takes ~60 us): the 2 x 16 shape is faster there
                 static mk_once_per_device attr_g;
                 if (attr_g.pending(ctx->device)) {
                     MK_CUDA(cudaFuncSetAttribute(moe_router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RG_SMEM));
