@@ -928,7 +928,7 @@ def main():
     ap.add_argument("--copies", type=int, default=1)
     ap.add_argument("--act", default="q8", choices=["q8", "q8x2"])
     ap.add_argument("--experts", type=int, default=384)
-    ap.add_argument("--moe-act", default="q8", choices=["q8", "fp4x6"], help="--case moe: fp4x6 = block-scaled tcgen05 experts for calls of >= 32 rows")
+    ap.add_argument("--moe-act", default="q8", choices=["q8", "fp4x6"], help="--case moe: fp4x6 = block-scaled tcgen05 experts for calls of >= 4 rows")
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=4, help="--case kda: KDA heads of width 128")
     ap.add_argument("--kda-smem", action="store_true", help="--case kda: the shared-memory form of the step kernel (default at width 128: registers)")

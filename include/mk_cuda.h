@@ -53,14 +53,14 @@ typedef struct mk_mla    mk_mla;
  *               (src/mxfp4.rs:488-539) at the same memory traffic. */
 #define MK_ACT_Q8    0
 #define MK_ACT_Q8X2  1
-/* MoE layer only (mk_moe_desc.act_mode): calls of 32 or more token rows run the experts as block-scaled tensor-core
+/* MoE layer only (mk_moe_desc.act_mode): calls of 4 or more token rows run the experts as block-scaled tensor-core
  * products (tcgen05.mma kind::mxf4, both operands packed FP4): E2M1 weights with their ue8m0 scales as registered, the
  * activations as six E2M1 limbs with power-of-two block scales (every limb takes the remainder down by a factor of 4;
  * what is left after six is at most 1/12288 of the block's largest element).  Results track the engine's exact-f32
  * path (src/mxfp4.rs:488-539) to ~1e-5 of max |y|.  The experts' input width and inter must be multiples of 256
  * (mk_moe_create refuses the mode otherwise).
  * A layer created in this mode keeps a second copy of its experts on the device (blocked into the 16 KB boxes a step
- * loads): twice the expert memory.  Calls of fewer than 32 rows run the ordinary q8 kernels. */
+ * loads): twice the expert memory.  Calls of fewer than 4 rows, and the expert-parallel step, run the ordinary q8 kernels. */
 #define MK_ACT_FP4X6 2
 /* OR into act_mode: accumulate the per-block terms of every output strictly in
  * ascending block order with separate multiply and add, reproducing the CPU

@@ -1178,14 +1178,18 @@ static int32_t moe_route_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n, b
     return MK_OK;
 }
 
+constexpr int MOE_TC_MIN_ROWS = 4;
 // grouped experts over an explicit pair list (device arrays); x rows already on device
 static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_rows, const int32_t *pair_row,
                                   const int32_t *pair_expert, const float *pair_weight, int n_pairs, float *outs,
-                                  bool prepared = false, bool quantized = false) {
+                                  bool prepared = false, bool quantized = false, bool expert_parallel = false) {
     // prepared: the fused router kernel has already grouped the pairs; quantized: and quantized x
-    const bool use_tc = m->tc && m->tmaps && !prepared && n_rows >= 32 && m->d % 256 == 0 && m->inter % 256 == 0;
+    // MK_ACT_FP4X6: from MOE_TC_MIN_ROWS rows up the experts run on the tensor cores (measured at 384 + 1 experts of 7168 x 2048:
+    // 4 rows 0.223 -> 0.206 ms, 16 rows 0.657 -> 0.556 ms, 1 row 0.085 -> 0.098 ms, hence not below 4).  The expert-parallel
+    // step keeps the q8 kernels (its pair lists and counters are theirs).
+    const bool use_tc = m->tc && m->tmaps && !expert_parallel && n_rows >= MOE_TC_MIN_ROWS && m->d % 256 == 0 && m->inter % 256 == 0;
     if (use_tc) {
-        // many rows: the experts as block-scaled tensor-core products (moe_tc.cuh); work items of up to 32 pairs
+        // the experts as block-scaled tensor-core products (moe_tc.cuh); work items of up to 16 pairs
         mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
         const int slots = m->n_experts + 1;
         MK_CHECK_ARG(((uintptr_t)x & 15) == 0, "MK_ACT_FP4X6: the token rows must be 16-byte aligned");
@@ -1430,7 +1434,8 @@ static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const flo
     const bool fused = n <= 16 && m->dx % 4 == 0 && ((uintptr_t)x & 15) == 0 && smem_f <= 200 * 1024 && (!ctx->moe_no_fuse || ep);
     MK_CHECK_ARG(ep == nullptr || (fused && n <= ep->max_tokens && slots == ep->slots && m->d == ep->d && (ep->connected || ep->world == 1)),
                  "expert-parallel call: needs <= max_tokens (<= 16) aligned rows and a connected exchange object made for this layer");
-    const bool fused_q = fused && m->latent == 0; // the router's rows are the experts' rows: quantize them in the same launch
+    const bool tc_call = m->tc && m->tmaps && ep == nullptr && n >= MOE_TC_MIN_ROWS;   // the tensor-core experts make their own limbs
+    const bool fused_q = fused && m->latent == 0 && !tc_call; // the router's rows are the experts' rows: quantize them in the same launch
     if (fused) {
         RouterFusedArgs ra;
         ra.gate_w = m->gate_w; ra.gate_b = m->gate_b; ra.x = x; ra.logits = m->logits;
@@ -1468,7 +1473,7 @@ static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const flo
         ep->step++;
         const uint32_t par = ep->step & 1u;
         outs = (float *)((char *)ep->blob + 256 + (size_t)par * ep->par_bytes);
-        rc = moe_experts_launch(ctx, m, xe, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, outs, true, fused_q);
+        rc = moe_experts_launch(ctx, m, xe, n, m->pair_row, m->pair_expert, m->pair_weight, n * slots, outs, true, fused_q, true);
         if (rc != MK_OK) return rc;
         EpPeers pe;
         memset(&pe, 0, sizeof(pe));

@@ -499,7 +499,7 @@ class MoeLayer:
         desc.activation = {"swiglu_clamp": _l.MK_MOE_SWIGLU_CLAMP, "situ": _l.MK_MOE_SITU}[activation]
         desc.router = {"sigmoid": _l.MK_ROUTER_SIGMOID, "sqrt_softplus": _l.MK_ROUTER_SQRT_SOFTPLUS}[router]
         desc.route_scale, desc.rms_eps = float(route_scale), float(rms_eps)
-        # act="fp4x6": calls of >= 32 rows run the experts on the block-scaled tcgen05 path (six E2M1 limbs per activation; widths must be multiples of 256)
+        # act="fp4x6": calls of >= 4 rows run the experts on the block-scaled tcgen05 path (six E2M1 limbs per activation; widths must be multiples of 256)
         desc.act_mode = _l.MK_ACT_FP4X6 if act == "fp4x6" else (_l.MK_ACT_Q8 | (_l.MK_ACT_STRICT if strict else 0))
         if routed_down is not None:
             rn = np.ascontiguousarray(routed_norm, dtype=np.float32)

@@ -174,7 +174,7 @@ def test_moe_layer_384_experts(mk, big_moe, batch, checked):
     # a token's result does not depend on the batch it travels in (src/model.rs:2398-2411)
     for t in pick[:4]:
         assert np.array_equal(bits(layer.moe_forward(x[t])), bits(out[t]))
-    if batch >= 32:
+    if batch >= 4:
         # the block-scaled tensor-core path on the same weights: held to the engine's exact-f32 path (src/mxfp4.rs:488-539)
         tc = mk.MoeLayer(gate_w, None, layer._keep[0], layer._keep[1], k, act="fp4x6")
         out_tc, ids_tc, _ = tc.moe_forward(x, want_routing=True)
