@@ -8,9 +8,10 @@ Headline workload: the q8_0 lm_head GEMV - W is vocab 163840 x hidden 7168 drawn
 N(0, 0.02) and quantized row-wise to q8_0 (32-wide blocks, int8 values + one f32
 scale per block, the engine's layout); x is f32[7168] from N(0, 1); batch 1.  A
 step is one logits projection (activation quantization + GEMV + greedy argmax).
-With N > 1 GPUs the vocabulary is sharded V/N rows per rank and the complete f32 logits
-reach every rank (peer-memory exchange kernel, or the NCCL all-gather with --collective nccl);
-total work is fixed, so scaling is "strong".
+With N > 1 GPUs the vocabulary is sharded V/N rows per rank and the complete f32 logits and the greedy
+token reach every rank (peer-memory exchange kernel, or the NCCL all-gather with --collective nccl);
+--token-only times the greedy step that exchanges only the ranks' (maximum, index) pairs instead (both
+peer forms are timed, the other one as an extra key); total work is fixed, so scaling is "strong".
 
 metric = quantized GB/s: algorithmic bytes of one step (int8 values + block
 scales + x + logits) divided by the step time, summed over all ranks.
@@ -49,10 +50,11 @@ def algorithmic_bytes(rows, cols, batch, scale_bytes=4):
     return rows * cols + rows * (cols // 32) * scale_bytes + batch * cols * 4 + batch * rows * 4
 
 
-def workload_config(world, batch):
+def workload_config(world, batch, gather_logits=False):
     """The `config` object of the JSON line; both arms print the same one."""
     return {"workload": f"q8_0 lm_head GEMV {VOCAB}x{HIDDEN} (f32 block scales), batch {batch}, vocab-sharded {world} way(s)"
-                        + ("" if world == 1 else ", complete f32 logits on every rank"),
+                        + ("" if world == 1 else (", complete f32 logits on every rank" if gather_logits else
+                                                  ", greedy token on every rank, f32 logits sharded (token-only exchange)")),
             "batch": batch, "rows_per_gpu": VOCAB // world, "act_mode": ACT_MODE,
             "l2": "inputs larger than L2: every timed pass streams a weight shard that is not resident "
                   "(shards below 4 x L2 rotate over copies until they exceed it)",
@@ -168,7 +170,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": workload_config(world, args.batch),
+        "config": workload_config(world, args.batch, not args.token_only),
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -624,7 +626,7 @@ def run_gpu(args):
             y, _ = heads[i % copies].matvec(x, want_argmax=True)
             return y
         if fused is not None:
-            return fused.matvec(x, want_argmax=True, head=heads[i % copies])
+            return fused.matvec(x, want_argmax=True, head=heads[i % copies], want_logits=not args.token_only)
         y = heads[i % copies].matvec(x)
         # vocab-sharded logits -> full logits on every rank
         if batch == 1:
@@ -651,8 +653,13 @@ def run_gpu(args):
         want = torch.empty((world, batch, rows), dtype=torch.float32, device=dev)
         dist.all_gather_into_tensor(want.view(-1), y.contiguous().view(-1))
         want = want.permute(1, 0, 2).reshape(batch, VOCAB)
+        # and the token-only step: the same token, this rank's rows where the call says they are
+        ptr_t, am_t = fused.matvec(x, want_argmax=True, head=heads[0], want_logits=False)
+        mine_t = fused.local_rows_tensor(ptr_t, batch)
         bad = torch.tensor([int(ctx.status_word() != 0 or not torch.equal(got, want)
-                                or not torch.equal(am.view(-1).long(), want.argmax(dim=1)))], dtype=torch.int32, device=dev)
+                                or not torch.equal(am.view(-1).long(), want.argmax(dim=1))
+                                or not torch.equal(am_t.view(-1).long(), want.argmax(dim=1))
+                                or not torch.equal(mine_t, want[:, rank * rows:(rank + 1) * rows]))], dtype=torch.int32, device=dev)
         dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if int(bad.item()):
             fused = None
@@ -661,13 +668,24 @@ def run_gpu(args):
                 step(i)
             barrier()
     launches0 = ctx.launches
-    ctx.prof_enable(True)
-    # `repeats` timed regions of exactly `steps` steps, each between barriers; the line's value is the median region
+    step(0)
+    launches = (ctx.launches - launches0) * args.steps      # kernels of this library inside one timed region
+    # `repeats` timed regions of exactly `steps` steps, each between barriers; the line's value is the median region.
+    # One more region of the same steps follows with the per-kernel events on (roofline.kernel_ms, the exchange kernel):
+    # those events cost about 10 us per step (measured on 2 GPUs: 118 us per step with them, 105-107 us without), so the
+    # regions the value comes from run without them.
     region_ms = []
     t_load0 = time.time()
-    for _ in range(args.repeats):
+    for rep in range(args.repeats + 1):
+        if rep == args.repeats:
+            ctx.prof_enable(True)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        if world > 1:
+            # the hosts leave the barrier tens of microseconds apart; one more untimed step (its exchange ends on all GPUs
+            # together) lines the GPUs up, so that the first event is recorded at the same moment on every rank and the
+            # region holds the K steps, not the hosts' skew
+            step(args.warmup)
         e0.record()
         for i in range(args.steps):
             step(i)
@@ -680,13 +698,31 @@ def run_gpu(args):
     kn, kms = ctx.prof_read("lm_head")
     xn_, xms_ = ctx.prof_read("other")     # N > 1, peer path: the exchange kernel (push, flags, wait, token pick)
     ctx.prof_enable(False)
-    launches = (ctx.launches - launches0) // args.repeats
+    ms_step_with_events = region_ms.pop() / args.steps
     st = torch.tensor([ctx.status_word()], dtype=torch.int32, device=dev)   # a bounded device-side wait that ran out sets it
     if world > 1:
         dist.all_reduce(st, op=dist.ReduceOp.MIN)
     status_all = int(st.item())
     per_step = sorted(r / args.steps for r in region_ms)
     ms_step = float(np.median(per_step))
+    # the other form of the exchange (complete logits on every rank / token only), one timed region, for the same line
+    other_ms = None
+    if fused is not None:
+        def other_step(i):
+            return fused.matvec(x, want_argmax=True, head=heads[i % copies], want_logits=args.token_only)
+        for i in range(args.warmup):
+            other_step(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        other_step(args.warmup)
+        e0.record()
+        for i in range(args.steps):
+            other_step(i)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        other_ms = float(t.item()) / args.steps
     # the timed regions may be shorter than nvidia-smi's sampling period: the same steps go on, untimed, for about
     # a second, and the clocks reported are the samples taken between the start of the first region and here
     for i in range(int(min(20000, max(1, 1.0 / (ms_step * 1e-3))))):
@@ -721,9 +757,12 @@ def run_gpu(args):
 
         def e2e_step(i):
             xd.copy_(xh, non_blocking=True)
-            ptr, am = fused.matvec(xd, want_argmax=True, head=heads[i % copies])
-            full = fused.logits_tensor(ptr, batch)
-            yh.copy_(full[:, lo:lo + rows], non_blocking=True)
+            ptr, am = fused.matvec(xd, want_argmax=True, head=heads[i % copies], want_logits=not args.token_only)
+            if not args.token_only:
+                full = fused.logits_tensor(ptr, batch)
+                yh.copy_(full[:, lo:lo + rows], non_blocking=True)
+            else:
+                yh.copy_(fused.local_rows_tensor(ptr, batch), non_blocking=True)
             amh.copy_(am, non_blocking=True)
             torch.cuda.synchronize()
         e2e_step(0)
@@ -771,7 +810,7 @@ def run_gpu(args):
         cb = None
         if world == 1 and not args.no_cpu:
             cb, _ = cpu_leg(8, 2)
-        cfg = workload_config(world, batch)
+        cfg = workload_config(world, batch, (not args.token_only) or not used_peer)
         frac = (achieved / peak) if achieved else None
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
@@ -782,9 +821,14 @@ def run_gpu(args):
                         "ms_per_step_each": per_step, "ms_per_step_p10": float(np.percentile(per_step, 10)),
                         "ms_per_step_p90": float(np.percentile(per_step, 90))},
             "run": {"weights_mb_per_gpu": shard_bytes * copies / 1e6, "rotating_copies": copies,
+                    **({"region_start": "after the barrier one untimed step lines the GPUs up (its exchange ends on all of them together); "
+                                        "the first event follows it on the stream"} if world > 1 else {}),
                     "logits_path": ("one GPU" if world == 1 else
-                                    ("one exchange kernel after the matvec pushes the shard's logits into every rank's buffer "
-                                     "(peer-memory stores + flags, no collective library call)" if used_peer
+                                    (("one exchange kernel after the matvec pushes the shard's logits into every rank's buffer "
+                                      "(peer-memory stores + flags, no collective library call)" if not args.token_only else
+                                      "token-only step of greedy decode: one exchange kernel after the matvec sends every rank's (maximum, index) "
+                                      "pair to every rank (peer-memory stores + flags, no collective library call); every rank gets the token, "
+                                      "the logits stay sharded - all of them computed and stored once, as at N = 1") if used_peer
                                      else "NCCL all-gather of the f32 logits + argmax")),
                     **({"note": fused_note} if fused_note else {})},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": frac,
@@ -796,14 +840,19 @@ def run_gpu(args):
                          "peak_note": "the peak is a copy (read + write); a read-only stream such as this GEMV can run a little "
                                       "above it, so frac may exceed 1 - frac_of_nominal_8000 is the bounded figure",
                          "kernel": "qgemv_spread_kernel<q8_0>",
-                         "kernel_ms": kern_ms, "kernel_launches": kn, "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
+                         "kernel_ms": kern_ms, "kernel_launches": kn,
+                         "kernel_ms_from": "CUDA events around every launch of the kernel in one further region of the same steps "
+                                           "(ms_per_step_with_kernel_events); the value's regions run without those events", "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
             "cpu_baseline": cb,
             "e2e": {"value": alg_step / e2e_dt / 1e9, "unit": "GB/s", "ms_per_step": e2e_dt * 1e3,
                     "h2d_bytes_per_step": batch * HIDDEN * 4, "d2h_bytes_per_step": batch * rows * 4 + batch * 4,
                     "api": "mk_matvec_q8 (host pointers: pinned x, pinned logits and token id)" if not used_peer else
-                           "pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank"},
+                           ("pinned x -> mk_matvec_q8_gather_dev -> pinned logits rows + token id, per rank" if not args.token_only else
+                            "pinned x -> mk_matvec_q8_gather_token_dev -> pinned logits rows + token id, per rank")},
             "gpu_launches": launches,
+            "ms_per_step_with_kernel_events": ms_step_with_events,
             **({"exchange_kernel_ms": xms_ / xn_} if (used_peer and xn_) else {}),
+            **({("token_only_ms_per_step" if not args.token_only else "complete_logits_on_every_rank_ms_per_step"): other_ms} if other_ms else {}),
             "status_word": status_all,
             "clocks": clocks,
             "decode_tokens_per_s": ((extra or {}).get("config5_decode") or {}).get("decode_tokens_per_s"),
@@ -944,6 +993,9 @@ def main():
     ap.add_argument("--graph", action="store_true", help="--case mxfp4_gemv / moe: also time the ring of calls as one CUDA graph")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: logits by one peer-memory exchange kernel after the matvec (default) or by an NCCL all-gather")
+    ap.add_argument("--token-only", action="store_true",
+                    help="N > 1: the timed step is the token-only step of greedy decode (the ranks exchange (maximum, index) pairs, the logits "
+                         "stay sharded); default: the complete logits on every rank.  The other form is timed beside it either way")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)

@@ -287,6 +287,13 @@ int32_t mk_gather_free(mk_ctx *ctx, mk_gather *g);
  * [batch]) = first index of the maximum over the whole vocabulary. */
 int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
                                 const float **logits, int32_t *argmax);
+/* The token-only step of greedy decode (the pick of src/model.rs:3277-3290 needs the token, not the other shards'
+ * logits): the ranks exchange only their (maximum, index) pairs, 16 bytes per rank and token.  argmax (required,
+ * DEVICE int32 [batch]) is the same on every rank; *local_rows (optional) receives a DEVICE pointer to this
+ * rank's rows of the logits, [batch] rows of w->rows floats, `vocab` floats apart (valid until the call after
+ * next).  All ranks must make the same kind of call in a step. */
+int32_t mk_matvec_q8_gather_token_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
+                                      const float **local_rows, int32_t *argmax);
 
 /* ---- MoE layer ---------------------------------------------------------
  * One call per layer instead of 3 matvecs per selected expert: replaces

@@ -16,6 +16,9 @@
 // for this file; what it preserves is the single-GPU result: the gathered logits are the
 // bits one GPU computes for the whole matrix (rows are independent), and the greedy pick is
 // the first index of the maximum (src/model.rs:3277-3290).
+// Token-only step (mk_matvec_q8_gather_token_dev: greedy decode needs the token, not the logits of the other shards):
+// the rows stay where the matvec wrote them, only the 16-byte (maximum, index) pair of every rank crosses NVLink;
+// same kernel, same flags, no row copy and no system-wide fence per CTA.
 //
 // Buffers: one cudaMalloc blob per rank, exported with cudaIpcGetMemHandle and opened by the
 // other ranks: [flags: 2 parities x 8 ranks u32][pad to 256 B][(maximum, index) pairs: 2 parities x 8 ranks x 2 tokens x 16 B]
@@ -59,7 +62,7 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
                                                               int64_t ld, int64_t row0, int rank, int world,
                                                               const uint32_t *__restrict__ flags, const Best *__restrict__ my_pairs,
                                                               uint32_t step, int32_t *__restrict__ argmax, int32_t *__restrict__ status,
-                                                              Best *__restrict__ partials, unsigned *__restrict__ counter) {
+                                                              Best *__restrict__ partials, unsigned *__restrict__ counter, bool push) {
     __shared__ Best red[32];
     __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, ncta = gridDim.x, cta = blockIdx.x;
@@ -81,8 +84,9 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
                 for (int u = 0; u < 4; ++u) {
                     const int64_t i = i0 + u * stride;
                     if (i >= hi) continue;
-                    for (int p = 0; p < world; ++p)
-                        if (p != rank) ((float4 *)(pe.dst[p] + (int64_t)b * ld))[i] = v[u];
+                    if (push)
+                        for (int p = 0; p < world; ++p)
+                            if (p != rank) ((float4 *)(pe.dst[p] + (int64_t)b * ld))[i] = v[u];
                     best = better(best, Best{v[u].x, 4 * i});
                     best = better(best, Best{v[u].y, 4 * i + 1});
                     best = better(best, Best{v[u].z, 4 * i + 2});
@@ -92,8 +96,9 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
         } else if (cta == 0) {
             for (int64_t i = tid; i < n; i += blockDim.x) {
                 const float v = s[i];
-                for (int p = 0; p < world; ++p)
-                    if (p != rank) pe.dst[p][(int64_t)b * ld + i] = v;
+                if (push)
+                    for (int p = 0; p < world; ++p)
+                        if (p != rank) pe.dst[p][(int64_t)b * ld + i] = v;
                 best = better(best, Best{v, i});
             }
         }
@@ -118,7 +123,8 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
     // fences again after it saw the full count (acquire side) and the second barrier hands that to its flag writers.
     __syncthreads();
     if (tid == 0) {
-        __threadfence_system();
+        if (push) __threadfence_system();
+        else __threadfence();          // token-only step: nothing of this CTA left the GPU, the partials are for the last CTA here
         const unsigned prev = atomicAdd(counter, 1u);
         s_last = prev == (unsigned)ncta - 1 ? 1 : 0;
         if (s_last) {
@@ -251,8 +257,9 @@ extern "C" int32_t mk_gather_free(mk_ctx *ctx, mk_gather *g) {
     return MK_OK;
 }
 
-extern "C" int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
-                                           const float **logits /* out: device pointer to [batch][vocab] */, int32_t *argmax) {
+// push: the rows of this rank go to every rank (complete logits everywhere); otherwise only the (maximum, index) pairs do
+static int32_t gather_step(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0, bool push,
+                           const float **logits /* out: device pointer to [batch][vocab] (push) or to this rank's rows of it */, int32_t *argmax) {
     MK_CHECK_ARG(ctx != nullptr && w != nullptr && g != nullptr && x != nullptr, "NULL argument");
     MK_CHECK_ARG(w->fmt == MK_FMT_Q8, "weight handle has the wrong format for this call");
     MK_CHECK_ARG(g->connected || g->world == 1, "mk_gather_connect has not run");
@@ -296,10 +303,21 @@ extern "C" int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_g
         gather_exchange_kernel<<<(unsigned)ncta, 1024, 0, ctx->stream>>>(pe, full + row0, batch, w->rows, g->vocab, row0, g->rank, g->world,
                                                                         (const uint32_t *)g->blob + par * 8,
                                                                         (const Best *)((char *)g->blob + pairs_off), g->step, argmax,
-                                                                        ctx->status_dev, partials, counter);
+                                                                        ctx->status_dev, partials, counter, push);
         ctx->launches++;
     }
     MK_CUDA(cudaGetLastError());
-    if (logits) *logits = full;
+    if (logits) *logits = push ? full : full + row0;
     return MK_OK;
+}
+
+extern "C" int32_t mk_matvec_q8_gather_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
+                                           const float **logits, int32_t *argmax) {
+    return gather_step(ctx, w, g, x, batch, row0, true, logits, argmax);
+}
+
+extern "C" int32_t mk_matvec_q8_gather_token_dev(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const float *x, int32_t batch, int64_t row0,
+                                                 const float **local_rows, int32_t *argmax) {
+    MK_CHECK_ARG(argmax != nullptr, "the token-only step returns the token: argmax must not be NULL");
+    return gather_step(ctx, w, g, x, batch, row0, false, local_rows, argmax);
 }

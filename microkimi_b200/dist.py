@@ -94,10 +94,13 @@ class FusedVocabHead:
             raise RuntimeError(f"peer gather buffers could not be connected on every rank ({err})")
         self._am = torch.empty((self.max_batch,), dtype=torch.int32, device=dev)
 
-    def matvec(self, x, want_argmax=True, head=None):
+    def matvec(self, x, want_argmax=True, head=None, want_logits=True):
         """x [batch, cols] (torch CUDA, identical on every rank) -> (device address of the complete logits
         [batch, vocab] in this rank's gather buffer, valid until the call after next; argmax int32 [batch]).
-        `head`: another Q8Head over the same rows (every rank must pass its counterpart)."""
+        `head`: another Q8Head over the same rows (every rank must pass its counterpart).
+        want_logits=False: the token-only step of greedy decode - the ranks exchange their (maximum, index)
+        pairs instead of the rows; returns (device address of THIS rank's rows of the logits, [batch] rows `vocab`
+        floats apart, argmax)."""
         import ctypes as C
         from . import lib as _l
         head = head or self.head
@@ -107,10 +110,24 @@ class FusedVocabHead:
         self.ctx._follow_torch()
         batch = xs.shape[0]
         ptr = C.c_void_p()
-        _l.check(self.ctx._L.mk_matvec_q8_gather_dev(self.ctx._h, head._h, self._h, C.c_void_p(xs.data_ptr()), batch, self.row0,
-                                                    C.byref(ptr), C.c_void_p(self._am.data_ptr()) if want_argmax else None))
+        if want_logits:
+            _l.check(self.ctx._L.mk_matvec_q8_gather_dev(self.ctx._h, head._h, self._h, C.c_void_p(xs.data_ptr()), batch, self.row0,
+                                                        C.byref(ptr), C.c_void_p(self._am.data_ptr()) if want_argmax else None))
+        else:
+            assert want_argmax, "the token-only step returns the token"
+            _l.check(self.ctx._L.mk_matvec_q8_gather_token_dev(self.ctx._h, head._h, self._h, C.c_void_p(xs.data_ptr()), batch, self.row0,
+                                                              C.byref(ptr), C.c_void_p(self._am.data_ptr())))
         self._last_ptr = ptr.value
         return ptr.value, (self._am[:batch] if want_argmax else None)
+
+    def local_rows_tensor(self, ptr, batch):
+        """Copies this rank's rows behind the pointer of a token-only step into a fresh torch tensor [batch, rows]."""
+        import ctypes as C
+        from . import lib as _l
+        out = torch.empty((batch, self.head.rows), dtype=torch.float32, device=torch.device("cuda", self.ctx.device))
+        for b in range(batch):
+            _l.check(self.ctx._L.mk_memcpy_dev(self.ctx._h, C.c_void_p(out[b].data_ptr()), C.c_void_p(ptr + b * self.vocab * 4), self.head.rows * 4))
+        return out
 
     def logits_tensor(self, ptr, batch):
         """Copies the complete logits behind `ptr` into a fresh torch tensor [batch, vocab]."""

@@ -104,6 +104,7 @@ SIGNATURES = {
     "mk_gather_connect": (_i32, [_vp, _vp, _vp]),
     "mk_gather_free": (_i32, [_vp, _vp]),
     "mk_matvec_q8_gather_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, C.POINTER(_vp), _vp]),
+    "mk_matvec_q8_gather_token_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, C.POINTER(_vp), _vp]),
     "mk_dequant_fp8": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "mk_weight_vq1": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, C.POINTER(_vp)]),
     "mk_matvec_vq1": (_i32, [_vp, _vp, _vp, _vp, _i32]),

@@ -55,6 +55,14 @@ def _worker(rank, world, port, ret):
             want = mk.Q8Head.from_f32(wf, vocab, d, ctx=ctx).matvec(xin)
             torch.cuda.synchronize()
             ok_head = ok_head and torch.equal(got, want) and torch.equal(am.cpu().long(), want.argmax(1).cpu())
+            # the token-only step in between (only the ranks' (maximum, index) pairs cross): the same token on every rank,
+            # this rank's rows where the call says they are
+            xin2 = (xin * -0.75).contiguous()
+            ptr2, am2 = fused.matvec(xin2, want_logits=False)
+            mine2 = fused.local_rows_tensor(ptr2, nb)
+            want2 = mk.Q8Head.from_f32(wf, vocab, d, ctx=ctx).matvec(xin2)
+            torch.cuda.synchronize()
+            ok_head = ok_head and torch.equal(mine2, want2[:, lo:hi]) and torch.equal(am2.cpu().long(), want2.argmax(1).cpu())
         ok_head = ok_head and ctx.status_word() == 0
         dist.barrier()
         fused.free()
