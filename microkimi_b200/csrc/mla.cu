@@ -747,6 +747,22 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(int H, int vd, int nspli
     float acc0 = 0.0f, acc1 = 0.0f;
     const float *po = part_o + bh * nsplit * vd + col;
     int s = 0;
+    // 16 independent loads in flight per thread (with the splits of a long context - 148 at 65536 positions - a loop of
+    // dependent round trips to L2 took longer than the attention itself); the sums keep their order: even splits into
+    // acc0, odd ones into acc1, ascending
+    for (; s + 16 <= nsplit; s += 16) {
+        float w[16], v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            w[u] = wgt[s + u];
+            v[u] = w[u] != 0.0f ? __ldcg(po + (int64_t)(s + u) * vd) : 0.0f;       // an empty split's partial is never read
+        }
+#pragma unroll
+        for (int u = 0; u < 16; u += 2) {
+            if (w[u] != 0.0f) acc0 += v[u] * w[u];
+            if (w[u + 1] != 0.0f) acc1 += v[u + 1] * w[u + 1];
+        }
+    }
     for (; s + 1 < nsplit; s += 2) {
         const float w0 = wgt[s], w1 = wgt[s + 1];
         if (w0 != 0.0f) acc0 += po[(int64_t)s * vd] * w0;       // an empty split's partial is never read
