@@ -391,7 +391,10 @@ def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=6
         out["weight_mb_per_gpu"] = model.weight_bytes / 1e6
         rng = np.random.default_rng(64)
         prompt = rng.integers(0, 163584, n_prompt).astype(np.int32)
-        model.generate(prompt[:3], 2)             # warm-up: eager token, recorded token, replays
+        # warm-up: the whole prompt once (the layers' row buffers grow to the prompt's size here, not inside the timed
+        # prefill: ~2000 cudaFree / cudaMalloc calls, which took 0.9 s late in a process that holds thousands of
+        # allocations), then eager token, recorded token, replays
+        model.generate(prompt, 3)
         model.reset()
         torch.cuda.synchronize()
 

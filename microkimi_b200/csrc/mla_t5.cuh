@@ -28,6 +28,14 @@
 //     mbarrier.  Every wait is bounded: a wait that runs out sets MK_ERR_TIMEOUT in the
 //     status word and the kernel carries on to its end (tensor memory is always freed).
 //
+// Measured and set aside: a 17th warp that only issues the MMAs, the second product committed per 128-row group, the next
+// tile converted pair of atoms by pair as the groups finish, the first product's K steps issued per pair (named barriers,
+// workers never wait for the issuer).  Correct, but 17 warps are allocated registers as 20, which caps a thread at 96: at
+// that cap this kernel, unchanged, goes from 0.191 to 0.260 ms (ctx 65536, batch 8) and the overlapped form reaches
+// 0.256 ms.  With the issuing thread inside one of the 16 warps that warp's share of the conversion waits for its issue
+// loop (an issue blocks for about as long as the MMA runs) and the whole CTA waits for that warp.  Quantizing the query
+// rows in this kernel's prologue instead of a launch of its own was also no faster (28.8 -> 30.8 us at ctx 4096).
+//
 // Reference recipe: mla_attn_flash_q8_mqa (src/model.rs:1804-1908) applied to one shared
 // q8_0 row per position; operands carry one f16 rounding each.
 #pragma once
