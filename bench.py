@@ -361,8 +361,8 @@ def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=6
     """Whole-token decode of the 93-layer micro skeleton (the engine's historical configuration: 69 KDA + 24 MLA layers,
     896 MXFP4 experts top-16 per MoE layer, q8_0 lm_head over 163840 rows, q8_0 MLA caches): a synthetic model file with the
     builder's shapes and distributions, a seeded 64-token prompt prefilled layer by layer (one GPU), then 256 greedy steps whose token ids
-    never leave the GPU.  One CUDA graph replay per token at N = 1; at N > 1 the experts are block-partitioned over the ranks
-    and the lm_head rows sharded, exchanged by peer-memory stores, launched kernel by kernel."""
+    never leave the GPU.  One CUDA graph replay per token; at N > 1 the experts are block-partitioned over the ranks and the
+    lm_head rows sharded, exchanged by peer-memory stores (the token is recorded once per buffer parity of the exchanges)."""
     import tempfile
 
     from microkimi_b200 import model as M

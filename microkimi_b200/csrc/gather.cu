@@ -40,8 +40,12 @@ struct mk_gather {
     void *absent;      // stand-in target for ranks that have not joined (all-zero handle): local scratch
     bool is_absent[8];
     bool connected;
-    uint32_t step;
+    uint32_t step;     // host mirror of the device step count: picks the buffer parity of a call
 };
+
+// a recorded token replays exchange steps that the host did not issue one by one: keep the mirror in step
+uint32_t mk_gather_steps(const mk_gather *g) { return g->step; }
+void mk_gather_note_replay(mk_gather *g, uint32_t n) { g->step += n; }
 
 namespace {
 constexpr uint32_t GATHER_WAIT_LIMIT = 1u << 22; // polls of >= 100 ns each: about half a second
@@ -61,10 +65,14 @@ struct GatherPeers { float *dst[8]; uint32_t *flag[8]; Best *pairs[8]; };
 __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers pe, const float *__restrict__ src, int batch, int64_t n,
                                                               int64_t ld, int64_t row0, int rank, int world,
                                                               const uint32_t *__restrict__ flags, const Best *__restrict__ my_pairs,
-                                                              uint32_t step, int32_t *__restrict__ argmax, int32_t *__restrict__ status,
+                                                              int32_t *__restrict__ argmax, int32_t *__restrict__ status,
                                                               Best *__restrict__ partials, unsigned *__restrict__ counter, bool push) {
     __shared__ Best red[32];
     __shared__ int s_last;
+    // the step number lives on the device (counter[1] = steps finished so far), not in the launch arguments: a recorded
+    // launch (CUDA graph) must publish a new number at every replay.  Every thread reads it here; the last CTA, which
+    // writes the new value at its end, is the one that saw all other CTAs count in after this read.
+    const uint32_t step = *(volatile const unsigned *)(counter + 1) + 1u;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, ncta = gridDim.x, cta = blockIdx.x;
     const bool vec = (n % 4 == 0) && (ld % 4 == 0) && (row0 % 4 == 0) && (((uintptr_t)src & 15) == 0);
     for (int b = 0; b < batch; ++b) {
@@ -177,6 +185,7 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
         }
         argmax[tid] = (int32_t)best.i;
     }
+    if (tid == 0) counter[1] = step;
 }
 } // namespace
 
@@ -302,7 +311,7 @@ static int32_t gather_step(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const 
         unsigned *counter = (unsigned *)((char *)g->scratch + (size_t)GATHER_MAX_CTAS * 2 * sizeof(Best));
         gather_exchange_kernel<<<(unsigned)ncta, 1024, 0, ctx->stream>>>(pe, full + row0, batch, w->rows, g->vocab, row0, g->rank, g->world,
                                                                         (const uint32_t *)g->blob + par * 8,
-                                                                        (const Best *)((char *)g->blob + pairs_off), g->step, argmax,
+                                                                        (const Best *)((char *)g->blob + pairs_off), argmax,
                                                                         ctx->status_dev, partials, counter, push);
         ctx->launches++;
     }

@@ -151,6 +151,12 @@ size_t mk_argmax_scratch_bytes(int batch);
 // MK_ERR_UNSUPPORTED when the layer is not of that kind (the caller then uses mk_moe_forward_dev).
 int32_t mk_moe_forward_k3_split(mk_ctx *ctx, mk_moe *m, const float *x, float *out_routed, float *out_shared);
 void mk_mla_note_replay(mk_mla *m, int seq);   // mla.cu: host-side position count after a graph replay of a decode step
+struct mk_moe_ep;
+struct mk_gather;
+uint32_t mk_moe_ep_steps(const mk_moe_ep *ep);            // moe.cu: exchange steps issued so far (host mirror of the device count)
+void mk_moe_ep_note_replay(mk_moe_ep *ep, uint32_t n);    //         n more steps ran from a recorded token
+uint32_t mk_gather_steps(const mk_gather *g);             // gather.cu: the same for the sharded lm_head
+void mk_gather_note_replay(mk_gather *g, uint32_t n);
 // weight (re)tiling
 int32_t mk_launch_retile_mxfp4(mk_ctx *ctx, const uint8_t *packed, const uint8_t *scales, mk_weight *w);
 int32_t mk_launch_untile_mxfp4(mk_ctx *ctx, const mk_weight *w, uint8_t *packed, uint8_t *scales);

@@ -242,7 +242,11 @@ struct mk_model {
     float *pf_au = nullptr, *pf_act = nullptr;
     int64_t launches_per_token = 0;
     uint8_t handles[128] = {0};     // world > 1: IPC handles of this rank's expert-row table and logits buffer
-    cudaGraphExec_t graph = nullptr;
+    // the recorded token.  With several GPUs the exchange kernels alternate between two buffer parities by step number, and
+    // the recorded launches carry the pointers of the parities they were recorded with: one recording per combination of
+    // (expert exchange parity, lm_head exchange parity) at the start of a token, made when first needed
+    cudaGraphExec_t graphs[4] = {nullptr, nullptr, nullptr, nullptr};
+    uint32_t ep_steps_per_token = 0, gather_steps_per_token = 0;
     void *graph_ws = nullptr;       // the context's shared workspace as the recorded launches saw it
     int warm = 0;
 };
@@ -416,7 +420,7 @@ int32_t load_experts(Loader &L, Layer &ly, int layer, int e0, int e1) {
 void free_model(mk_ctx *ctx, mk_model *m) {
     if (!m) return;
     cudaStreamSynchronize(ctx->stream);
-    if (m->graph) cudaGraphExecDestroy(m->graph);
+    for (cudaGraphExec_t &g : m->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     for (Layer &ly : m->layers) {
         if (ly.kda) mk_kda_free(ctx, ly.kda);
         if (ly.cache) mk_mla_free(ctx, ly.cache);
@@ -875,18 +879,21 @@ extern "C" int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t 
     ctx->launches++;
     // a CUDA graph cannot be recorded from the legacy default stream: there the token is launched kernel by kernel
     const bool real_stream = st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread;
-    const bool graph_ok = m->opts.use_graph && m->world == 1 && !ctx->prof_on && real_stream;
+    const bool graph_ok = m->opts.use_graph && !ctx->prof_on && real_stream;
     int32_t rc = MK_OK;
-    if (m->graph && m->graph_ws != ctx->ws) {
+    if (m->graph_ws != ctx->ws) {
         // another call on this context grew the shared workspace since the token was recorded: the recorded
-        // launches point at the old buffer, so the recording is dropped and made again
-        cudaGraphExecDestroy(m->graph);
-        m->graph = nullptr;
+        // launches point at the old buffer, so the recordings are dropped and made again
+        for (cudaGraphExec_t &g : m->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     }
-    if (graph_ok && m->graph) {
-        MK_CUDA(cudaGraphLaunch(m->graph, st));
+    const uint32_t ep0 = m->ep ? mk_moe_ep_steps(m->ep) : 0u, ga0 = m->gather ? mk_gather_steps(m->gather) : 0u;
+    cudaGraphExec_t &graph = m->graphs[(ep0 & 1u) * 2 + (ga0 & 1u)];
+    if (graph_ok && graph) {
+        MK_CUDA(cudaGraphLaunch(graph, st));
         ctx->launches += m->launches_per_token;
         for (Layer &ly : m->layers) if (ly.cache) mk_mla_note_replay(ly.cache, 0);
+        if (m->ep) mk_moe_ep_note_replay(m->ep, m->ep_steps_per_token);
+        if (m->gather) mk_gather_note_replay(m->gather, m->gather_steps_per_token);
     } else if (graph_ok && m->warm >= 1) {
         // the first token ran eagerly (workspaces grown, attributes set); this one is recorded and then launched
         const int64_t l0 = ctx->launches;
@@ -900,11 +907,13 @@ extern "C" int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t 
             return rc;
         }
         m->launches_per_token = ctx->launches - l0;
-        const cudaError_t e2 = cudaGraphInstantiate(&m->graph, g, 0);
+        m->ep_steps_per_token = m->ep ? mk_moe_ep_steps(m->ep) - ep0 : 0u;
+        m->gather_steps_per_token = m->gather ? mk_gather_steps(m->gather) - ga0 : 0u;
+        const cudaError_t e2 = cudaGraphInstantiate(&graph, g, 0);
         cudaGraphDestroy(g);
         if (e2 != cudaSuccess) { mk_set_error("mk_model_forward: graph instantiation failed: %s", cudaGetErrorString(e2)); return MK_ERR_CUDA; }
         m->graph_ws = ctx->ws;
-        MK_CUDA(cudaGraphLaunch(m->graph, st));
+        MK_CUDA(cudaGraphLaunch(graph, st));
     } else {
         const int64_t l0 = ctx->launches;
         rc = enqueue_token(ctx, m);

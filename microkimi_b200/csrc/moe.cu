@@ -76,10 +76,14 @@ struct mk_moe_ep {
     void *absent;       // stand-in target for ranks that have not joined (all-zero handle): local scratch
     bool is_absent[8];
     bool connected;
-    uint32_t step;
+    uint32_t step;      // host mirror of the device step count (counter[1]): picks the table parity of a call
     int32_t *n_local;   // device: pairs computed by this rank in the current call
-    uint32_t *counter;  // device: exchange kernel's finished CTAs, 0 between calls
+    uint32_t *counter;  // device: [0] exchange kernel's finished CTAs, 0 between calls; [1] steps finished
 };
+
+// a recorded token replays `n` exchange steps that the host did not issue one by one: keep the mirror in step
+uint32_t mk_moe_ep_steps(const mk_moe_ep *ep) { return ep->step; }
+void mk_moe_ep_note_replay(mk_moe_ep *ep, uint32_t n) { ep->step += n; }
 
 namespace {
 
@@ -841,9 +845,13 @@ constexpr uint32_t EP_WAIT_LIMIT = 1u << 22; // polls of >= 100 ns: about half a
 struct EpPeers { float *outs[8]; uint32_t *flag[8]; };
 __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, const float *__restrict__ local_outs,
                                                              const int32_t *__restrict__ sorted, const int32_t *__restrict__ n_local, int d,
-                                                             int rank, int world, const uint32_t *__restrict__ flags, uint32_t step,
-                                                             uint32_t *__restrict__ counter, int32_t *__restrict__ status) {
+                                                             int rank, int world, const uint32_t *__restrict__ flags, uint32_t *__restrict__ counter,
+                                                             int32_t *__restrict__ status) {
     __shared__ int s_last;
+    // the step number lives on the device (counter[1] = steps finished so far), not in the launch arguments: a recorded
+    // launch (CUDA graph) must publish a new number at every replay.  Every thread reads it here; the last CTA, which
+    // writes the new value at its end, is by construction the one that saw all other CTAs count in after this read.
+    const uint32_t step = *(volatile const uint32_t *)(counter + 1) + 1u;
     if ((int)blockIdx.x < *n_local) {
         const int64_t p = sorted[blockIdx.x];
         const float4 *src = (const float4 *)(local_outs + p * d);
@@ -883,6 +891,7 @@ __global__ void __launch_bounds__(256) moe_ep_exchange_kernel(const EpPeers pe, 
         }
         if (!ok) atomicCAS(status, 0, MK_ERR_TIMEOUT);
     }
+    if (threadIdx.x == 0) counter[1] = step;
     __threadfence_system();
 }
 
@@ -1483,8 +1492,7 @@ static int32_t moe_forward_impl(mk_ctx *ctx, mk_moe *m, mk_moe_ep *ep, const flo
         }
         mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
         moe_ep_exchange_kernel<<<(unsigned)(n * slots), 256, 0, ctx->stream>>>(pe, outs, m->sorted, ep->n_local, m->d, ep->rank, ep->world,
-                                                                             (const uint32_t *)ep->blob + par * 8, ep->step, ep->counter,
-                                                                             ctx->status_dev);
+                                                                             (const uint32_t *)ep->blob + par * 8, ep->counter, ctx->status_dev);
         ctx->launches++;
         MK_CUDA(cudaGetLastError());
     } else {
@@ -1544,9 +1552,9 @@ extern "C" int32_t mk_moe_ep_create(mk_ctx *ctx, const mk_moe *m, int32_t rank, 
     cudaError_t e = cudaMalloc(&ep->blob, ep->blob_bytes);
     if (e == cudaSuccess) e = cudaMemset(ep->blob, 0, ep->blob_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ep->n_local, 4);
-    if (e == cudaSuccess) e = cudaMalloc(&ep->counter, 4);
+    if (e == cudaSuccess) e = cudaMalloc(&ep->counter, 8);      // [0] finished CTAs of the running exchange, [1] steps finished
     if (e == cudaSuccess) e = cudaMemset(ep->n_local, 0, 4);
-    if (e == cudaSuccess) e = cudaMemset(ep->counter, 0, 4);
+    if (e == cudaSuccess) e = cudaMemset(ep->counter, 0, 8);
     cudaIpcMemHandle_t h;
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ep->blob);
     if (e != cudaSuccess) {
