@@ -102,6 +102,51 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
+def _decode_worker(rank, world, port, path, ret):
+    import torch.distributed as dist
+
+    import microkimi_b200 as mk
+    from microkimi_b200 import model as M
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dev = torch.device("cuda", rank)
+        ctx = mk.Context(rank)
+        stream = torch.cuda.Stream(device=dev)           # a real stream: the token can be recorded
+        prompt = np.array([5, 900, 17, 1203, 44], np.int32)
+        with torch.cuda.stream(stream):
+            ctx.use_torch_stream()
+            whole = M.Model(path, 40, use_graph=False, ctx=ctx)          # one GPU, launched kernel by kernel
+            want = whole.generate(prompt, 14)
+            split = M.Model(path, 40, use_graph=True, rank=rank, world=world, ctx=ctx)
+            split.connect()
+            got = split.generate(prompt, 14)             # eager token, one recording per exchange parity, replays
+            torch.cuda.synchronize()
+            ret[rank] = (bool(np.array_equal(got, want)), int(ctx.status_word()))
+            dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_decode_with_experts_and_vocabulary_split_over_the_ranks_equals_one_gpu(world, tmp_path):
+    """The whole decode token with the routed experts block-partitioned over the ranks and the lm_head rows sharded,
+    replayed as a CUDA graph (the exchange kernels keep their step numbers on the device): the greedy continuation of a
+    prompt is the one a single GPU produces (every partial result is bit-identical, so the token ids are)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    from oracle import oracle as O
+    path = str(tmp_path / "split.bin")
+    O.build_bin(path, O.Config.microkimi(n_layers=5, vocab=2048, n_experts=32, top_k=4, attn_res_block=2))
+    ret = mp.Manager().dict()
+    mp.spawn(_decode_worker, args=(world, _free_port(), path, ret), nprocs=world, join=True)
+    for r in range(world):
+        assert ret[r] == (True, 0), f"rank {r}: {ret[r]}"
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_sharded_lm_head_and_expert_parallel_moe_match_single_gpu(world):
     if torch.cuda.device_count() < world:
