@@ -421,6 +421,14 @@ int32_t mk_mla_attend_batch_dev(mk_ctx *ctx, mk_mla *mla, const float *q, float 
  * mk_mla_attend.  A caller that replays a captured step must make no other append to that sequence in between. */
 int32_t mk_mla_decode_step_dev(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *k_row, const float *v_row, const float *q,
                                float scale, float *out);
+/* n consecutive positions of one sequence in one go - the cache and attention part of mla_prefill
+ * (src/model.rs:2033-2115): k_rows / v_rows [n] rows as mk_mla_append takes them are appended at the sequence's
+ * device-side count, then query row b (q_rows [n][n_heads][nope + rope]) attends to the positions up to its own;
+ * out [n][n_heads * vd].  Per (row, head) the arithmetic of n calls of mk_mla_decode_step_dev - the same bits in
+ * the strict attention mode - with the launches shared.  DEVICE pointers.  May grow the object's scratch buffers
+ * (allocates; not for stream capture). */
+int32_t mk_mla_prefill_dev(mk_ctx *ctx, mk_mla *mla, int32_t seq, const float *k_rows, const float *v_rows, const float *q_rows,
+                           int32_t n, float scale, float *out);
 /* Cache contents of one sequence back to HOST memory in the engine's layout
  * (src/model.rs:765-781), any pointer may be NULL:
  *  PER_HEAD: kq i8 [n, H, nope], ks f32 [n, H, nope/32], kr f32 [n, rope], vq i8 [n, H, vd], vs f32 [n, H, vd/32]

@@ -42,6 +42,9 @@ struct mk_mla {
     int8_t *qq; float *qs; int64_t q_nbp;
     float *part_m, *part_l, *part_o;
     int max_split;
+    int causal_nq;                         // set around a causal call (mk_mla_prefill_dev), 0 otherwise
+    int64_t q_rows;                        // query rows (sequence x head) the per-call scratch buffers hold
+    int64_t part_slots;                    // (query row, KV split) partial results part_m / part_l / part_o hold
 };
 
 namespace {
@@ -53,6 +56,8 @@ __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
 }
 
 struct MlaDev {
+    int causal;                            // 0, or the number of query rows of a causal call: all rows belong to sequence seq0, row b sees
+                                           // the positions up to that of the b-th last one (the prompt's rows appended together, attended at once)
     int H, kvh, nope, rope, vd, cap, T, nb, nbv, NC, RC, vrow, vsrow;
     int8_t *kqt; float *kst; float *krt; int8_t *vq; float *vs;
     // per-head layout: ONE contiguous record per (position tile, head) instead of the arrays above:
@@ -207,6 +212,13 @@ __global__ void mla_export_kernel(const MlaDev c, int seq, int n, int8_t *kq, fl
 // order; o *= corr, then o[d] += p_i * (vq * vs) position by position; finally o / l.  Separate multiplies and adds
 // throughout, exp taken in double and rounded once.  Not a fast kernel: it exists so that a whole decode token can be
 // compared with the CPU token without the attention's summation order (and, downstream of it, q8 roundings) differing.
+// the sequence and the number of visible positions of query row bi (see MlaDev::causal)
+__device__ __forceinline__ int mla_seq(const MlaDev &c, int seq0, int bi) { return c.causal ? seq0 : seq0 + bi; }
+__device__ __forceinline__ int mla_len(const MlaDev &c, const int *npos_arr, int npos_fixed, int seq, int bi) {
+    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    return c.causal ? n - (c.causal - 1 - bi) : n;
+}
+
 #define MLA_STRICT_TILE 64
 __global__ void __launch_bounds__(32)
 mla_attend_strict_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__restrict__ qs, int64_t ldq, int64_t q_nbp,
@@ -215,8 +227,8 @@ mla_attend_strict_kernel(const MlaDev c, const int8_t *__restrict__ qq, const fl
     extern __shared__ __align__(16) unsigned char smem_strict[];
     float *q_rope = (float *)smem_strict;                 // [rope]
     float *sc_s = q_rope + c.rope;                        // [64] scores, then p
-    const int lane = threadIdx.x, h = blockIdx.x, bi = blockIdx.y, seq = seq0 + bi;
-    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int lane = threadIdx.x, h = blockIdx.x, bi = blockIdx.y, seq = mla_seq(c, seq0, bi);
+    const int n = mla_len(c, npos_arr, npos_fixed, seq, bi);
     const int hd = c.nope + c.rope;
     const int64_t qrow = (int64_t)bi * c.H + h;
     for (int r = lane; r < c.rope; r += 32) q_rope[r] = q_f32[qrow * hd + c.nope + r];
@@ -317,7 +329,7 @@ mla_attend_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, bi = blockIdx.z; // bi: index into q/out; sequence = seq0 + bi
-    const int seq = seq0 + bi;
+    const int seq = mla_seq(c, seq0, bi);
     const int split = blockIdx.x * MLA_WARPS + warp;
     const int hk = c.kvh == 1 ? 0 : h;
     const int hd = c.nope + c.rope;
@@ -331,7 +343,7 @@ mla_attend_kernel(const MlaDev c, const int8_t *__restrict__ qq, const float *__
         for (int i = threadIdx.x; i < c.RC; i += blockDim.x) qr_s[i] = ((const float4 *)(q_f32 + qrow * hd + c.nope))[i];
     }
     __syncthreads();
-    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int n = mla_len(c, npos_arr, npos_fixed, seq, bi);
     const int ntiles = (n + 31) >> 5;
     const int tps = (ntiles + nsplit - 1) / nsplit;
     const int t0 = split * tps, t1 = min(t0 + tps, ntiles);
@@ -438,8 +450,8 @@ __global__ void __launch_bounds__(256)
 mla_rope_scores_kernel(const MlaDev c, const float *__restrict__ q_f32, const int *__restrict__ npos_arr, int npos_fixed,
                        int seq0, float *__restrict__ rs) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int tile = blockIdx.x, bi = blockIdx.y, seq = seq0 + bi;
-    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int tile = blockIdx.x, bi = blockIdx.y, seq = mla_seq(c, seq0, bi);
+    const int n = mla_len(c, npos_arr, npos_fixed, seq, bi);
     if (tile * 32 >= n) return;
     float4 *kr_s = (float4 *)smem;                       // [RC][32]
     float4 *q_s = kr_s + c.RC * 32;                      // [H][RC]
@@ -478,8 +490,8 @@ __global__ void __launch_bounds__(256)
 mla_rope_scores_reg_kernel(const MlaDev c, const float *__restrict__ q_f32, const int *__restrict__ npos_arr, int npos_fixed,
                            int seq0, float *__restrict__ rs) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int tile = blockIdx.x, bi = blockIdx.y, seq = seq0 + bi;
-    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int tile = blockIdx.x, bi = blockIdx.y, seq = mla_seq(c, seq0, bi);
+    const int n = mla_len(c, npos_arr, npos_fixed, seq, bi);
     if (tile * 32 >= n) return;
     float4 *q_s = (float4 *)smem;                        // [H][RC]
     const int hd = c.nope + c.rope;
@@ -555,7 +567,7 @@ mla_attend_ph128_kernel(const MlaDev c, const int8_t *__restrict__ qq, const flo
                         float *__restrict__ part_o, float *__restrict__ out, int32_t *__restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y * PH_WARPS + warp, bi = blockIdx.z, seq = seq0 + bi, split = blockIdx.x;
+    const int h = blockIdx.y * PH_WARPS + warp, bi = blockIdx.z, seq = mla_seq(c, seq0, bi), split = blockIdx.x;
     const bool hv = h < c.H;
     const int hh = hv ? h : c.H - 1;
     // shared memory: [warp][record: K half | V half] | [warp][query staging] | [warp][2] mbarriers (K, V)
@@ -579,7 +591,7 @@ mla_attend_ph128_kernel(const MlaDev c, const int8_t *__restrict__ qq, const flo
         for (int i = lane; i < c.nb; i += 32) qs_s[i] = qs[qrow * q_nbp + i];
     }
     __syncwarp();
-    const int n = npos_arr ? npos_arr[seq] : npos_fixed;
+    const int n = mla_len(c, npos_arr, npos_fixed, seq, bi);
     const int ntiles = (n + 31) >> 5;
     const int tps = (ntiles + nsplit - 1) / nsplit;
     const int t0 = split * tps, t1 = min(t0 + tps, ntiles);
@@ -775,6 +787,7 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(int H, int vd, int nspli
 } // namespace
 
 // ====================================================================== host side
+#include <algorithm>
 #include <new>
 
 static MlaDev mla_dev(const mk_mla *m) {
@@ -783,6 +796,7 @@ static MlaDev mla_dev(const mk_mla *m) {
     c.nb = m->nb; c.nbv = m->nbv; c.NC = m->NC; c.RC = m->RC; c.vrow = m->vrow; c.vsrow = m->vsrow;
     c.kqt = m->kqt; c.kst = m->kst; c.krt = m->krt; c.vq = m->vq; c.vs = m->vs;
     c.recs = m->recs; c.rec_bytes = m->rec_bytes;
+    c.causal = m->causal_nq;
     c.off_ks = m->nope * 32; c.off_vq = c.off_ks + m->nb * 128; c.off_vs = c.off_vq + m->vd * 32;
     return c;
 }
@@ -842,6 +856,8 @@ extern "C" int32_t mk_mla_create(mk_ctx *ctx, const mk_mla_desc *d, mk_mla **out
     if (e == cudaSuccess) e = cudaMalloc(&m->part_m, bh * m->max_split * 4);
     if (e == cudaSuccess) e = cudaMalloc(&m->part_l, bh * m->max_split * 4);
     if (e == cudaSuccess) e = cudaMalloc(&m->part_o, bh * m->max_split * m->vd * 4);
+    m->q_rows = (int64_t)bh;
+    m->part_slots = (int64_t)bh * m->max_split;
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
         mk_set_error("mk_mla_create: %s", cudaGetErrorString(e));
@@ -985,6 +1001,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
         if (ns > ntiles_p) ns = ntiles_p;
         if (ns > m->max_split) ns = m->max_split;
         if (ctx->mla_max_split > 0 && ns > ctx->mla_max_split) ns = ctx->mla_max_split;
+        if ((int64_t)ns * nq * m->H > m->part_slots) ns = (int)(m->part_slots / ((int64_t)nq * m->H));
         if (ns < 1) ns = 1;
         const MlaDev cph = mla_dev(m);
         const size_t qw = (size_t)m->nope + mk_align_up((size_t)m->nb * 4, 16);
@@ -1022,6 +1039,7 @@ static int32_t mla_attend_launch(mk_ctx *ctx, mk_mla *m, const float *q, int nq,
     if (nsplit > ntiles) nsplit = ntiles;
     if (nsplit > m->max_split) nsplit = m->max_split;
     if (ctx->mla_max_split > 0 && nsplit > ctx->mla_max_split) nsplit = ctx->mla_max_split;
+    if ((int64_t)nsplit * nq * m->H > m->part_slots) nsplit = (int)(m->part_slots / ((int64_t)nq * m->H));
     if (nsplit < 1) nsplit = 1;
     const MlaDev c = mla_dev(m);
     const dim3 grid((unsigned)mk_ceil_div(nsplit, MLA_WARPS), (unsigned)m->H, (unsigned)nq);
@@ -1141,6 +1159,71 @@ extern "C" int32_t mk_mla_decode_step_dev(mk_ctx *ctx, mk_mla *m, int32_t seq, c
     m->npos[seq] += 1;
     return mla_attend_launch(ctx, m, q, 1, seq, 0, m->cap, scale, out);
 }
+// Scratch of the attention calls (quantized queries, rope scores, split partials) for `rows` query rows (row = sequence x
+// head, or prompt position x head in a causal call) with up to 32 KV splits each; grows, never shrinks.
+static int32_t mla_reserve_rows(mk_ctx *ctx, mk_mla *m, int64_t rows) {
+    if (rows <= m->q_rows && rows * 32 <= m->part_slots) return MK_OK;
+    MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    const int64_t r = std::max(rows, m->q_rows), slots = std::max(rows * 32, m->part_slots);
+    void **bufs[] = {(void **)&m->rope_scores, (void **)&m->qq, (void **)&m->qs, (void **)&m->part_m, (void **)&m->part_l, (void **)&m->part_o};
+    const size_t sizes[] = {m->layout == MK_MLA_ABSORBED ? 0 : (size_t)r * m->T * 32 * 4, (size_t)r * m->q_nbp * 32, (size_t)r * m->q_nbp * 4,
+                            (size_t)slots * 4, (size_t)slots * 4, (size_t)slots * m->vd * 4};
+    for (int i = 0; i < 6; ++i) {
+        if (*bufs[i]) { cudaFree(*bufs[i]); *bufs[i] = nullptr; }
+        if (sizes[i]) MK_CUDA(cudaMalloc(bufs[i], sizes[i]));
+    }
+    m->q_rows = r;
+    m->part_slots = slots;
+    return MK_OK;
+}
+
+// A run of n consecutive positions of one sequence in one go (the attention part of mla_prefill, src/model.rs:2033-2115):
+// the n rows are appended at the device-side count, then query row b attends to everything up to its own position - the
+// same arithmetic per (row, head) as n calls of mk_mla_decode_step_dev (in the strict mode the same bits: one warp walks
+// a row's positions in order), with the launches shared.  The absorbed layout takes the steps one by one.
+extern "C" int32_t mk_mla_prefill_dev(mk_ctx *ctx, mk_mla *m, int32_t seq, const float *k_rows, const float *v_rows, const float *q_rows, int32_t n,
+                                      float scale, float *out) {
+    MK_CHECK_ARG(ctx != nullptr && m != nullptr && k_rows != nullptr && q_rows != nullptr && out != nullptr && n >= 1, "bad argument");
+    MK_CHECK_ARG(seq >= 0 && seq < m->nseq, "no such sequence");
+    const bool absorbed = m->layout == MK_MLA_ABSORBED;
+    MK_CHECK_ARG(absorbed || v_rows != nullptr, "v_rows is NULL");
+    if (m->npos[seq] + n > m->cap) {
+        mk_set_error("mk_mla_prefill_dev: sequence %d holds %d of %d positions, %d more do not fit", seq, m->npos[seq], m->cap, n);
+        return MK_ERR_STATE;
+    }
+    const int64_t qrow = (int64_t)m->H * (m->nope + m->rope), krow = absorbed ? m->nope : qrow, vrow = (int64_t)m->H * m->vd;
+    if (absorbed || n == 1) {
+        for (int t = 0; t < n; ++t) {
+            int32_t rc = mk_mla_decode_step_dev(ctx, m, seq, k_rows + t * krow, absorbed ? nullptr : v_rows + t * vrow, q_rows + t * qrow, scale,
+                                                out + t * vrow);
+            if (rc != MK_OK) return rc;
+        }
+        return MK_OK;
+    }
+    MK_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc = mla_reserve_rows(ctx, m, (int64_t)n * m->H);
+    if (rc != MK_OK) return rc;
+    const MlaDev c = mla_dev(m);
+    {
+        mk_prof_scope prof(ctx, MK_PROF_MLA);
+        const int64_t warps = (int64_t)n * m->kvh * (m->nb + m->nbv);
+        mla_append_kernel<<<(unsigned)mk_ceil_div(warps * 32, 256), 256, 0, ctx->stream>>>(c, seq, 0, n, k_rows, v_rows, 0, m->npos_dev);
+        ctx->launches++;
+        if (m->rope > 0) {
+            mla_append_rope_kernel<<<(unsigned)mk_ceil_div((int64_t)n * m->rope, 128), 128, 0, ctx->stream>>>(c, seq, 0, n, k_rows, m->npos_dev);
+            ctx->launches++;
+        }
+        mla_bump_kernel<<<1, 32, 0, ctx->stream>>>(m->npos_dev, seq, n, m->cap, ctx->status_dev);
+        ctx->launches++;
+        MK_CUDA(cudaGetLastError());
+    }
+    m->npos[seq] += n;
+    m->causal_nq = n;
+    rc = mla_attend_launch(ctx, m, q_rows, n, seq, 0, m->npos[seq], scale, out);
+    m->causal_nq = 0;
+    return rc;
+}
+
 // The host-side count of a sequence follows a replayed step (the device-side count moved inside the graph).
 void mk_mla_note_replay(mk_mla *m, int seq) { if (m && seq >= 0 && seq < m->nseq && m->npos[seq] < m->cap) m->npos[seq] += 1; }
 

@@ -19,6 +19,15 @@
 
 namespace {
 
+// a[t][i] *= sigmoid(g[t * ldg + i]) for the rows of a prompt (the gate of mla_forward, src/model.rs:2017-2019; exp in double
+// precision, rounded once, as mk_sigmoid_gate_dev takes it)
+__global__ void __launch_bounds__(256) sigmoid_gate_rows_kernel(float *__restrict__ a, const float *__restrict__ g, int64_t count, int64_t ldg) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (i >= count) return;
+    const float x = g[t * ldg + i];
+    a[t * count + i] = __fmul_rn(a[t * count + i], __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-x)))));
+}
+
 __global__ void embed_row_kernel(const float *__restrict__ embed, const int32_t *__restrict__ token, int vocab, int d,
                                  float *__restrict__ hidden, int32_t *__restrict__ status) {
     int t = *token;
@@ -822,11 +831,11 @@ int32_t enqueue_prefill(mk_ctx *ctx, mk_model *m, int n) {
             const float scale = powf((float)qh, -0.5f);
             const int strict_was = ctx->mla_strict;
             if (m->opts.strict) ctx->mla_strict = 1;
-            rc = MK_OK;
-            for (int t = 0; t < n && rc == MK_OK; ++t) {      // append + causal attention, position by position
-                rc = mk_mla_decode_step_dev(ctx, ly.cache, 0, m->pf_k_new + (size_t)t * H * qh, m->pf_v_new + (size_t)t * hv, m->pf_q + (size_t)t * H * qh,
-                                            scale, m->pf_attn + (size_t)t * hv);
-                if (rc == MK_OK) rc = mk_sigmoid_gate_dev(ctx, m->pf_attn + (size_t)t * hv, y + (size_t)t * ldy + qa + cdim, hv);
+            // the n rows appended together, then every row's causal attention in shared launches
+            rc = mk_mla_prefill_dev(ctx, ly.cache, 0, m->pf_k_new, m->pf_v_new, m->pf_q, n, scale, m->pf_attn);
+            if (rc == MK_OK) {
+                sigmoid_gate_rows_kernel<<<dim3((unsigned)mk_ceil_div(hv, 256), (unsigned)n), 256, 0, st>>>(m->pf_attn, y + qa + cdim, hv, ldy);
+                ctx->launches++;
             }
             ctx->mla_strict = strict_was;
             if (rc != MK_OK) return rc;

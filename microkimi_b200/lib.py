@@ -149,6 +149,7 @@ SIGNATURES = {
     "mk_mla_export_f32": (_i32, [_vp, _vp, _i32, _vp, _vp]),
     "mk_mla_import_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32]),
     "mk_mla_decode_step_dev": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, C.c_float, _vp]),
+    "mk_mla_prefill_dev": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, C.c_float, _vp]),
     "mk_model_config_default": (None, [C.POINTER(ModelConfig)]),
     "mk_bin_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
     "mk_bin_close": (_i32, [_vp]),

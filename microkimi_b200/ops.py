@@ -679,6 +679,29 @@ class MlaCache:
                                                      C.c_void_p(out.data_ptr())))
         return out
 
+    def decode_step(self, k_row, v_row, q, scale, seq=0):
+        """One position appended at the device-side count, then attention over everything held (torch CUDA tensors;
+        per_head: k_row [H, nope+rope], v_row [H, vd], q [H, nope+rope]) -> [H, vd]."""
+        import torch
+        self.ctx._follow_torch()
+        out = torch.empty((self.H, self.vd), dtype=torch.float32, device=q.device)
+        vp = C.c_void_p(v_row.data_ptr()) if v_row is not None else None
+        _l.check(self.ctx._L.mk_mla_decode_step_dev(self.ctx._h, self._h, seq, C.c_void_p(k_row.data_ptr()), vp, C.c_void_p(q.data_ptr()),
+                                                    float(scale), C.c_void_p(out.data_ptr())))
+        return out
+
+    def prefill(self, k_rows, v_rows, q_rows, scale, seq=0):
+        """n consecutive positions in one go: rows appended together, row b attends up to its own position (torch CUDA
+        tensors; per_head: k_rows [n, H, nope+rope], v_rows [n, H, vd], q_rows [n, H, nope+rope]) -> [n, H, vd]."""
+        import torch
+        self.ctx._follow_torch()
+        n = q_rows.shape[0]
+        out = torch.empty((n, self.H, self.vd), dtype=torch.float32, device=q_rows.device)
+        vp = C.c_void_p(v_rows.data_ptr()) if v_rows is not None else None
+        _l.check(self.ctx._L.mk_mla_prefill_dev(self.ctx._h, self._h, seq, C.c_void_p(k_rows.data_ptr()), vp, C.c_void_p(q_rows.data_ptr()),
+                                                int(n), float(scale), C.c_void_p(out.data_ptr())))
+        return out
+
     def export(self, seq=0):
         """Cache contents in the engine's layout: dict of kq, ks (, kr, vq, vs)."""
         n = self.positions(seq)

@@ -266,3 +266,47 @@ def test_f32_snapshot_roundtrip_lands_on_the_same_grid(mk):
     b.assign_f32(ka)
     ea, eb = a.export(), b.export()
     assert np.array_equal(ea["kq"], eb["kq"]) and np.array_equal(bits(ea["ks"]), bits(eb["ks"]))
+
+
+@pytest.mark.parametrize("heads,rope,vd,base,n", [(4, 64, 128, 0, 37), (4, 64, 128, 29, 70), (8, 32, 256, 5, 33)])
+def test_a_run_of_positions_in_one_go_equals_single_steps(mk, heads, rope, vd, base, n):
+    """mk_mla_prefill_dev (the cache and attention part of mla_prefill, src/model.rs:2033-2115): n rows appended together,
+    row b attending up to its own position, against n calls of mk_mla_decode_step_dev on a second cache - bit for bit in
+    the strict attention mode (one warp walks a row's positions in order), within 2e-4 of max |out| with the split
+    kernels (another split count, another merge order); the caches end identical."""
+    import torch
+    nope, cap = 128, 128
+    rng = np.random.default_rng(heads * 100 + n)
+    ctx = mk.Context.default()
+    dev = torch.device("cuda", ctx.device)
+    tot = base + n
+    k = torch.from_numpy(rng.standard_normal((tot, heads, nope + rope)).astype(np.float32)).to(dev)
+    v = torch.from_numpy(rng.standard_normal((tot, heads, vd)).astype(np.float32)).to(dev)
+    q = torch.from_numpy(rng.standard_normal((tot, heads, nope + rope)).astype(np.float32)).to(dev)
+    scale = 1.0 / np.sqrt(nope + rope)
+    for strict in (1, 0):
+        ctx.set_option("mla_strict", strict)
+        try:
+            a = mk.MlaCache(heads, nope, rope, vd, cap)
+            b = mk.MlaCache(heads, nope, rope, vd, cap)
+            want = torch.stack([a.decode_step(k[t], v[t], q[t], scale) for t in range(tot)])
+            for t in range(base):
+                b.decode_step(k[t], v[t], q[t], scale)
+            got = b.prefill(k[base:], v[base:], q[base:], scale)
+            torch.cuda.synchronize()
+            assert a.positions() == b.positions() == tot
+            ea, eb = a.export(), b.export()
+            for key in ea:
+                assert np.array_equal(ea[key], eb[key]), key
+            w = want[base:].cpu().numpy()
+            g = got.cpu().numpy()
+            if strict:
+                assert np.array_equal(bits(g), bits(w))
+            else:
+                assert np.abs(g - w).max() <= 2e-4 * np.abs(w).max()
+            # and one more single step on both continues alike
+            assert ctx.status_word() == 0
+            a.free()
+            b.free()
+        finally:
+            ctx.set_option("mla_strict", 0)
