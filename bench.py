@@ -496,8 +496,10 @@ def extras_single_gpu(torch, mk, ctx, dev, heads, x1):
             res = {f"batch{b}": measure_moe(torch, mk, ctx, dev, layers, gen, b, st, 3, graph=(b == 1))
                    for b, st in ((1, 40), (16, 20), (256, 6))}
             twins = tc_twins(mk, ctx, layers)
-            res["batch256_tcgen05_block_scaled"] = measure_moe(torch, mk, ctx, dev, twins, gen, 256, 6, 3)
-            res["batch256_tcgen05_block_scaled"]["act_mode"] = "fp4x6: E2M1 weights + ue8m0 scales as registered, activations as six E2M1 limbs (kind::mxf4)"
+            for b, st in ((16, 20), (256, 6)):
+                res[f"batch{b}_tcgen05_block_scaled"] = measure_moe(torch, mk, ctx, dev, twins, gen, b, st, 3)
+                res[f"batch{b}_tcgen05_block_scaled"]["act_mode"] = ("fp4x6: E2M1 weights + ue8m0 scales as registered, activations as six "
+                                                                    "E2M1 limbs (kind::mxf4)")
             for t in twins:
                 t.free()
             return res
