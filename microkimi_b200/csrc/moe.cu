@@ -560,16 +560,45 @@ plan_body(const int32_t *__restrict__ pair_expert, int n_pairs, int n_slots /* n
         atomicAdd(&cnt[e], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int o = 0, io = 0;
-        for (int e = 0; e < n_slots; ++e) {
+    {
+        // exclusive prefix sums over the slots of the pair counts (off) and of the work items (ioff): every thread sums a
+        // run of consecutive slots, the runs are scanned across the block (a single thread walking 897 slots took 50 us)
+        __shared__ int wsum[2][32];
+        const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = (blockDim.x + 31) >> 5;
+        const int per = (n_slots + (int)blockDim.x - 1) / (int)blockDim.x;
+        const int e0 = min(tid * per, n_slots), e1 = min(e0 + per, n_slots);
+        int so = 0, si = 0;
+        for (int e = e0; e < e1; ++e) { so += cnt[e]; si += (cnt[e] + chunk - 1) / chunk; }
+        int xo = so, xi = si;                                   // inclusive scan inside the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int yo = __shfl_up_sync(0xFFFFFFFFu, xo, d), yi = __shfl_up_sync(0xFFFFFFFFu, xi, d);
+            if (lane >= d) { xo += yo; xi += yi; }
+        }
+        if (lane == 31) { wsum[0][warp] = xo; wsum[1][warp] = xi; }
+        __syncthreads();
+        if (warp == 0) {
+            int to = lane < nwarp ? wsum[0][lane] : 0, ti = lane < nwarp ? wsum[1][lane] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int yo = __shfl_up_sync(0xFFFFFFFFu, to, d), yi = __shfl_up_sync(0xFFFFFFFFu, ti, d);
+                if (lane >= d) { to += yo; ti += yi; }
+            }
+            wsum[0][lane] = to; wsum[1][lane] = ti;             // inclusive over the warps
+        }
+        __syncthreads();
+        int o = xo - so + (warp > 0 ? wsum[0][warp - 1] : 0), io = xi - si + (warp > 0 ? wsum[1][warp - 1] : 0);
+        for (int e = e0; e < e1; ++e) {
             off[e] = o;
             ioff[e] = io;
             o += cnt[e];
             io += (cnt[e] + chunk - 1) / chunk;
         }
-        *n_items = io < max_items ? io : max_items;
-        if (io > max_items) atomicCAS(status, 0, MK_ERR_STATE);
+        if (tid == 0) {
+            const int total = wsum[1][nwarp - 1];
+            *n_items = total < max_items ? total : max_items;
+            if (total > max_items) atomicCAS(status, 0, MK_ERR_STATE);
+        }
     }
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
