@@ -209,6 +209,137 @@ __global__ void __launch_bounds__(DIM > 0 ? DIM : 1024) kda_step_kernel(KdaArgs 
     }
 }
 
+// ---------------------------------------------------------------- a run of positions as three launches
+// Of a position's work only the recurrence (decay, delta, update, output) depends on the position before it.  For a run
+// of n positions (prefill) the rest is done for all positions side by side:
+//   kda_run_pre_kernel  (heads x n CTAs): conv + SiLU of q, k, v (position t reads the rows t-1 .. t-(kconv-1) of this call,
+//       or the layer's window for what came before it), the decay exp(g), the two sigmoids, the per-head L2 norms of q, k;
+//   kda_run_rec_kernel  (heads CTAs): the state column in registers from position to position, the position's q, k and
+//       decay vectors double-buffered in shared memory (cp.async one position ahead), two passes per position;
+//   kda_run_post_kernel (heads x n CTAs): the head's output RMS norm, o_norm and the gate; the last kconv-1 rows become
+//       the layer's conv window.
+// Every value is formed by the expressions of kda_step_kernel in the same order, so the bits are those of n single steps.
+struct KdaRun {
+    float *qn, *kn, *vv, *ds, *g2s, *oraw;   // [n][heads * dim]
+    float *bhs;                              // [n][heads]
+};
+__device__ __forceinline__ float kda_run_conv(const float *__restrict__ w, const float *__restrict__ win, const float *__restrict__ rows, int64_t ld,
+                                              int64_t proj, int64_t i, int kconv, int t) {
+    float acc = 0.0f;
+    for (int j = 0; j < kconv - 1; ++j) {
+        const int p = t - (kconv - 1) + j;                       // the position whose raw input weight j multiplies
+        const float old = p >= 0 ? rows[(int64_t)p * ld + i] : win[(int64_t)(t + j) * proj + i];
+        acc = __fadd_rn(acc, __fmul_rn(w[i * kconv + j], old));
+    }
+    acc = __fadd_rn(acc, __fmul_rn(w[i * kconv + kconv - 1], rows[(int64_t)t * ld + i]));
+    return __fmul_rn(acc, sigmoid_cr(acc));
+}
+__global__ void __launch_bounds__(256) kda_run_pre_kernel(KdaArgs a, KdaRun r) {
+    extern __shared__ float sm[];
+    const int dim = a.dim;
+    float *qs = sm, *ks = sm + dim, *red = sm + 2 * dim;
+    const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x, lane = c & 31, warp = c >> 5, nwarps = blockDim.x >> 5;
+    const bool active = c < dim;
+    const int64_t proj = (int64_t)a.heads * dim, i = (int64_t)h * dim + c, row = (int64_t)t * proj + i;
+    const int64_t wq = 0, wk = proj * a.kconv, wv = 2 * proj * a.kconv;
+    const int64_t cq = 0, ck = (int64_t)(a.kconv - 1) * proj, cv = 2 * (int64_t)(a.kconv - 1) * proj;
+    if (active) {
+        qs[c] = kda_run_conv(a.conv_w + wq, a.conv + cq, a.q_raw, a.ld_x, proj, i, a.kconv, t);
+        ks[c] = kda_run_conv(a.conv_w + wk, a.conv + ck, a.k_raw, a.ld_x, proj, i, a.kconv, t);
+        r.vv[row] = kda_run_conv(a.conv_w + wv, a.conv + cv, a.v_raw, a.ld_x, proj, i, a.kconv, t);
+        const float glow = a.g_low[(int64_t)t * a.ld_g + i], dtb = a.dt_bias[i], alog = a.a_log[c];
+        const float g = __fmul_rn(a.gate_lb, sigmoid_cr(__fmul_rn(exp_cr(alog), __fadd_rn(glow, dtb))));
+        r.ds[row] = exp_cr(g);
+        r.g2s[row] = sigmoid_cr(a.g2[(int64_t)t * a.ld_x + i]);
+        if (c == 0) r.bhs[(int64_t)t * a.heads + h] = sigmoid_cr(a.beta_raw[(int64_t)t * a.ld_x + h]);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float n2 = warp_sumsq(qs, dim, lane);
+        if (lane == 0) red[0] = __fdiv_rn(a.q_scale, fmaxf(__fsqrt_rn(n2), 1e-12f));
+    }
+    if (warp == nwarps - 1) {
+        const float n2 = warp_sumsq(ks, dim, lane);
+        if (lane == 0) red[1] = __fdiv_rn(1.0f, fmaxf(__fsqrt_rn(n2), 1e-12f));
+    }
+    __syncthreads();
+    if (active) {
+        r.qn[row] = __fmul_rn(qs[c], red[0]);
+        r.kn[row] = __fmul_rn(ks[c], red[1]);
+    }
+}
+template <int DIM>
+__global__ void __launch_bounds__(DIM) kda_run_rec_kernel(KdaRun r, float *__restrict__ s, int heads, int n_tok) {
+    __shared__ float buf[2][3][DIM];                 // q, k, decay of a position, two positions
+    const int h = blockIdx.x, c = threadIdx.x;
+    const int64_t proj = (int64_t)heads * DIM, i = (int64_t)h * DIM + c;
+    float *col = s + (int64_t)h * DIM * DIM + c;
+    auto fetch = [&](int t) {
+        float (*b)[DIM] = buf[t & 1];
+        const int64_t row = (int64_t)t * proj + i;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&b[0][c])), "l"(r.qn + row) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&b[1][c])), "l"(r.kn + row) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&b[2][c])), "l"(r.ds + row) : "memory");
+    };
+    fetch(0);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    float x[DIM];
+#pragma unroll
+    for (int q = 0; q < DIM; ++q) x[q] = col[(int64_t)q * DIM];
+    float vv = r.vv[i], bh = r.bhs[h];
+    for (int t = 0; t < n_tok; ++t) {
+        if (t + 1 < n_tok) fetch(t + 1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        float vv_next = 0.0f, bh_next = 0.0f;
+        if (t + 1 < n_tok) { vv_next = r.vv[(int64_t)(t + 1) * proj + i]; bh_next = r.bhs[(int64_t)(t + 1) * heads + h]; }
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        __syncthreads();
+        const float *qs = buf[t & 1][0], *ks = buf[t & 1][1], *ds = buf[t & 1][2];
+        float delta = vv, o = 0.0f;
+#pragma unroll
+        for (int q = 0; q < DIM; ++q) {
+            x[q] = __fmul_rn(x[q], ds[q]);
+            delta = __fsub_rn(delta, __fmul_rn(ks[q], x[q]));
+        }
+#pragma unroll
+        for (int q = 0; q < DIM; ++q) {
+            x[q] = __fadd_rn(x[q], __fmul_rn(__fmul_rn(bh, ks[q]), delta));
+            o = __fadd_rn(o, __fmul_rn(qs[q], x[q]));
+        }
+        r.oraw[(int64_t)t * proj + i] = o;
+        vv = vv_next; bh = bh_next;
+        __syncthreads();            // this position's vectors may be overwritten by the fetch after next
+    }
+#pragma unroll
+    for (int q = 0; q < DIM; ++q) col[(int64_t)q * DIM] = x[q];
+}
+__global__ void __launch_bounds__(256) kda_run_post_kernel(KdaArgs a, KdaRun r) {
+    extern __shared__ float sm[];
+    const int dim = a.dim;
+    float *qs = sm, *red = sm + dim;
+    const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x, lane = c & 31, warp = c >> 5;
+    const bool active = c < dim;
+    const int64_t proj = (int64_t)a.heads * dim, i = (int64_t)h * dim + c, row = (int64_t)t * proj + i;
+    float o = 0.0f;
+    if (active) { o = r.oraw[row]; qs[c] = o; }
+    __syncthreads();
+    if (warp == 0) {
+        const float ss = __fdiv_rn(warp_sumsq(qs, dim, lane), (float)dim);
+        if (lane == 0) red[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ss, a.rms_eps)));
+    }
+    __syncthreads();
+    if (!active) return;
+    a.o[(int64_t)t * a.ld_o + i] = __fmul_rn(__fmul_rn(__fmul_rn(o, red[0]), a.o_norm[c]), r.g2s[row]);
+    // the layer's conv window after the run: the raw inputs of the last kconv - 1 positions, oldest first
+    const int j = t - (a.n_tok - (a.kconv - 1));
+    if (j >= 0) {
+        const int64_t w = (int64_t)j * proj + i, cq = 0, ck = (int64_t)(a.kconv - 1) * proj, cv = 2 * (int64_t)(a.kconv - 1) * proj;
+        a.conv[cq + w] = a.q_raw[(int64_t)t * a.ld_x + i];
+        a.conv[ck + w] = a.k_raw[(int64_t)t * a.ld_x + i];
+        a.conv[cv + w] = a.v_raw[(int64_t)t * a.ld_x + i];
+    }
+}
+
 // The same step with the head's S [dim][dim] staged in shared memory by cp.async at kernel start (dim % 4 == 0,
 // dim <= 224): both passes become short loops that stay in the instruction cache, the column is read from shared
 // memory twice (conflict-free: consecutive threads, consecutive words) and written to global memory once.  The
@@ -466,6 +597,24 @@ static int32_t kda_steps(mk_ctx *ctx, mk_kda *k, int n_tok, const float *q_raw, 
     a.heads = k->heads; a.dim = k->dim; a.kconv = k->kconv;
     a.gate_lb = k->gate_lb; a.rms_eps = k->rms_eps; a.q_scale = k->q_scale;
     const size_t smem = (size_t)(3 * k->dim + 4) * sizeof(float);
+    if (n_tok >= 4 && n_tok >= k->kconv - 1 && k->kconv >= 2 && (k->dim == 64 || k->dim == 128) && !ctx->kda_smem) {
+        // a run of positions: everything but the recurrence for all positions side by side (three launches)
+        const size_t per = (size_t)n_tok * k->heads * k->dim;
+        int32_t rc = mk_ws_reserve(ctx, (6 * per + (size_t)n_tok * k->heads) * sizeof(float) + 256);
+        if (rc != MK_OK) return rc;
+        KdaRun r;
+        float *w = (float *)ctx->ws;
+        r.qn = w; r.kn = w + per; r.vv = w + 2 * per; r.ds = w + 3 * per; r.g2s = w + 4 * per; r.oraw = w + 5 * per; r.bhs = w + 6 * per;
+        mk_prof_scope prof(ctx, MK_PROF_OTHER);
+        const unsigned threads = (unsigned)mk_align_up(k->dim, 32);
+        kda_run_pre_kernel<<<dim3((unsigned)k->heads, (unsigned)n_tok), threads, (size_t)(2 * k->dim + 4) * sizeof(float), ctx->stream>>>(a, r);
+        if (k->dim == 128) kda_run_rec_kernel<128><<<k->heads, 128, 0, ctx->stream>>>(r, k->s, k->heads, n_tok);
+        else kda_run_rec_kernel<64><<<k->heads, 64, 0, ctx->stream>>>(r, k->s, k->heads, n_tok);
+        kda_run_post_kernel<<<dim3((unsigned)k->heads, (unsigned)n_tok), threads, (size_t)(k->dim + 4) * sizeof(float), ctx->stream>>>(a, r);
+        ctx->launches += 3;
+        MK_CUDA(cudaGetLastError());
+        return MK_OK;
+    }
     mk_prof_scope prof(ctx, MK_PROF_OTHER);
     const bool kc4 = k->kconv == 4;
     const size_t smem_s = ((size_t)k->dim * k->dim + 4 * (size_t)k->dim + 4) * sizeof(float);
