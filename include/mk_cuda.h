@@ -238,9 +238,12 @@ int32_t mk_kda_reset(mk_ctx *ctx, mk_kda *kda);   /* zero state: KdaCache::new *
  * practice expf differ (tests hold it to 1e-6 relative). */
 int32_t mk_kda_step_dev(mk_ctx *ctx, mk_kda *kda, const float *q_raw, const float *k_raw, const float *v_raw,
                         const float *g_low, const float *beta_raw, const float *g2, float *o);
-/* n_tok consecutive positions in one launch (the engine's kda_prefill loop, src/model.rs:1281-1300): token t reads its
+/* n_tok consecutive positions in one call (the engine's kda_prefill loop, src/model.rs:1281-1300): token t reads its
  * q / k / v / g2 / beta rows t * ld_x floats after the given pointers, its g_low row t * ld_g floats on, and writes its
- * output row t * ld_o floats on.  Bit-identical to n_tok calls of mk_kda_step_dev; the state is read and written once. */
+ * output row t * ld_o floats on.  Bit-identical to n_tok calls of mk_kda_step_dev; the state is read and written once.
+ * From 4 positions on (widths 64 and 128) the work that does not depend on the previous position runs for all positions
+ * side by side and only the recurrence walks them (three launches); that form keeps its intermediates in the
+ * context's workspace, which may grow on the first call of a size (an allocation: not inside stream capture). */
 int32_t mk_kda_steps_dev(mk_ctx *ctx, mk_kda *kda, int32_t n_tok, const float *q_raw, const float *k_raw, const float *v_raw,
                          const float *g_low, const float *beta_raw, const float *g2, float *o, int64_t ld_x, int64_t ld_g, int64_t ld_o);
 /* State to / from HOST memory (cache snapshots for speculative rollback, src/spec.rs:214, 294-299;
