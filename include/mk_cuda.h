@@ -95,6 +95,9 @@ int32_t mk_status_word(mk_ctx *ctx, int32_t *out);
 
 /* Tuning knobs, for measurement only (defaults are chosen per shape):
  *   "force_ks" : K split of the matvec kernels, one of 0 (auto), 1, 2, 4, 8.
+ *   "pdl": 1 (default) = the one-token matvec is launched behind its activation quantizer with programmatic stream
+ *             serialization: its first weight loads run while the quantizer still does, it waits (griddepcontrol.wait)
+ *             before its first read of the quantized activations.  0 = ordinary launch order (same results).
  *   "moe_no_fuse": 1 = small-batch MoE calls use the separate router / top-k / plan /
  *                quantize launches of large batches instead of the fused router kernel.
  *   "mla_max_split": upper bound on the KV splits of an attention call, 0 = automatic

@@ -36,6 +36,7 @@ extern "C" int32_t mk_init(int32_t device, mk_ctx **out) {
     if (!c) return MK_ERR_OOM;
     memset(c, 0, sizeof(*c));
     c->device = device;
+    c->pdl = 1;
     c->sm_count = p.multiProcessorCount;
     c->cc_major = p.major;
     c->cc_minor = p.minor;
@@ -142,6 +143,10 @@ extern "C" int32_t mk_set_option(mk_ctx *ctx, const char *name, int64_t value) {
     if (strcmp(name, "force_ks") == 0) {
         MK_CHECK_ARG(value == 0 || value == 1 || value == 2 || value == 4 || value == 8, "force_ks must be 0, 1, 2, 4 or 8");
         ctx->force_ks = (int)value;
+        return MK_OK;
+    }
+    if (strcmp(name, "pdl") == 0) {
+        ctx->pdl = value != 0;
         return MK_OK;
     }
     if (strcmp(name, "moe_no_fuse") == 0) {

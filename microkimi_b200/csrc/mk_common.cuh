@@ -89,6 +89,7 @@ struct mk_ctx {
     void *io_pinned;
     size_t io_pinned_bytes;
     int force_ks;           // 0 = choose per shape
+    int pdl;                // 1 = the one-token matvec starts behind its activation quantizer by programmatic stream serialization
     int mla_max_split;      // > 0: upper bound on the KV splits of an attention call (study / test knob)
     int moe_no_fuse;        // 1 = separate router / top-k / plan / quantize launches also for small batches (study knob)
     int mla_no_tc;

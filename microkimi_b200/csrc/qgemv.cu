@@ -144,6 +144,8 @@ template <bool X2>
 __global__ void __launch_bounds__(256)
 quantize_act_kernel(const float *__restrict__ x, int ntok, int64_t cols, int64_t ldx, int64_t nbp,
                     int8_t *__restrict__ xq, float *__restrict__ xs) {
+    // a matvec launched behind this kernel with programmatic stream serialization may start its weight loads now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (w >= (int64_t)ntok * nbp) return;
@@ -254,11 +256,24 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ y
 // ------------------------------------------------------------------ dispatch
 template <int WF, int KS>
 void launch_spread(const mk_weight *w, cudaStream_t st, const Consts &k, const int8_t *xq, const float *xs, int nslot, bool x2, float *y,
-                   int64_t ldy) {
+                   int64_t ldy, bool pdl) {
     constexpr int RT = 8 / KS;
     const unsigned grid = (unsigned)mk_ceil_div(w->nrt, RT);
     const int64_t ldq = w->nbp * 32;
     const void *wt = w->values;
+    if (pdl && !x2 && nslot == 1) {
+        // one token behind its activation quantizer: programmatic stream serialization, the kernel waits
+        // (griddepcontrol.wait) between its first weight loads and its first read of the quantized activations
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, qgemv_spread_kernel<WF, KS, 1, false>, wt, (const void *)w->scales, xq, xs, ldq, (int64_t)w->nbp, y, ldy,
+                           (int64_t)w->rows, (int64_t)w->nrt, k);
+        return;
+    }
     if (x2)
         qgemv_spread_kernel<WF, KS, 2, true><<<grid, 256, 0, st>>>(wt, w->scales, xq, xs, ldq, w->nbp, y, ldy, w->rows, w->nrt, k);
     else if (nslot == 2)
@@ -289,10 +304,10 @@ void launch_batched(const mk_weight *w, cudaStream_t st, const Consts &k, const 
 }
 template <int WF>
 void launch_wf(const mk_weight *w, cudaStream_t st, const Consts &k, int ks, bool spread, bool ordered, const int8_t *xq,
-               const float *xs, int ntok, bool x2, float *y, int64_t ldy) {
+               const float *xs, int ntok, bool x2, float *y, int64_t ldy, bool pdl) {
 #define MK_KS_CASE(K)                                                         \
     case K:                                                                   \
-        if (spread) launch_spread<WF, K>(w, st, k, xq, xs, ntok, x2, y, ldy);    \
+        if (spread) launch_spread<WF, K>(w, st, k, xq, xs, ntok, x2, y, ldy, pdl);    \
         else launch_batched<WF, K>(w, st, k, xq, xs, ntok, x2, ordered, y, ldy);          \
         break;
     switch (ks) {
@@ -343,10 +358,12 @@ int32_t mk_launch_qgemv(mk_ctx *ctx, const mk_weight *w, const int8_t *xq, const
     const int wf = w->fmt == MK_FMT_MXFP4 ? W_MXFP4 : (w->scale_type == MK_SCALE_F16 ? W_Q8_F16 : W_Q8_F32);
     mk_prof_scope prof(ctx, w->fmt == MK_FMT_MXFP4 ? MK_PROF_MATVEC_MXFP4 : MK_PROF_LM_HEAD);
     const Consts k = {65536u, 0xFFFFFFFFu, ctx->zeros_dev};
+    // the callers of this function launch the activation quantizer directly before it on the same stream
+    const bool pdl = ctx->pdl != 0;
     switch (wf) {
-    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy); break;
-    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy); break;
-    default: launch_wf<W_Q8_F16>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy); break;
+    case W_MXFP4: launch_wf<W_MXFP4>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy, pdl); break;
+    case W_Q8_F32: launch_wf<W_Q8_F32>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy, pdl); break;
+    default: launch_wf<W_Q8_F16>(w, ctx->stream, k, ks, spread, strict != 0, xq, xs, ntok, x2 != 0, y, ldy, pdl); break;
     }
     ctx->launches++;
     MK_CUDA(cudaGetLastError());

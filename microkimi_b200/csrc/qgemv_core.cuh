@@ -265,6 +265,9 @@ __device__ __forceinline__ void warp_tile_spread(const uint4 *__restrict__ tile,
     Group<WF> ga, gb;
     int64_t i = ks;
     if (i < ngroups) load_group<WF>(ga, tile, i, lane);
+    // a launch with programmatic stream serialization starts while the kernel that quantizes the activations still runs:
+    // the weights above do not depend on it, the activations below do (returns at once in an ordinary launch)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     while (i < ngroups) {
         const int64_t i1 = i + KS;
         if (i1 < ngroups) load_group<WF>(gb, tile, i1, lane);
