@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(1024) gather_exchange_kernel(const GatherPeers
     // the step number lives on the device (counter[1] = steps finished so far), not in the launch arguments: a recorded
     // launch (CUDA graph) must publish a new number at every replay.  Every thread reads it here; the last CTA, which
     // writes the new value at its end, is the one that saw all other CTAs count in after this read.
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // launched behind the matvec with programmatic stream serialization
     const uint32_t step = *(volatile const unsigned *)(counter + 1) + 1u;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, ncta = gridDim.x, cta = blockIdx.x;
     const bool vec = (n % 4 == 0) && (ld % 4 == 0) && (row0 % 4 == 0) && (((uintptr_t)src & 15) == 0);
@@ -309,10 +310,15 @@ static int32_t gather_step(mk_ctx *ctx, const mk_weight *w, mk_gather *g, const 
         if (ncta < 1) ncta = 1;
         Best *partials = (Best *)g->scratch;
         unsigned *counter = (unsigned *)((char *)g->scratch + (size_t)GATHER_MAX_CTAS * 2 * sizeof(Best));
-        gather_exchange_kernel<<<(unsigned)ncta, 1024, 0, ctx->stream>>>(pe, full + row0, batch, w->rows, g->vocab, row0, g->rank, g->world,
-                                                                        (const uint32_t *)g->blob + par * 8,
-                                                                        (const Best *)((char *)g->blob + pairs_off), argmax,
-                                                                        ctx->status_dev, partials, counter, push);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)ncta); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = 0; cfg.stream = ctx->stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = ctx->pdl ? 1 : 0;
+        cudaLaunchKernelEx(&cfg, gather_exchange_kernel, pe, (const float *)(full + row0), (int)batch, (int64_t)w->rows, (int64_t)g->vocab, (int64_t)row0,
+                           (int)g->rank, (int)g->world, (const uint32_t *)g->blob + par * 8, (const Best *)((char *)g->blob + pairs_off), argmax,
+                           ctx->status_dev, partials, counter, push);
         ctx->launches++;
     }
     MK_CUDA(cudaGetLastError());

@@ -43,6 +43,9 @@ qgemv_spread_kernel(const void *__restrict__ wt, const void *__restrict__ wscale
     float acc[2][NOUT];
 #pragma unroll
     for (int o = 0; o < NOUT; ++o) acc[0][o] = acc[1][o] = 0.0f;
+    // a small kernel launched behind this one with programmatic stream serialization (the greedy pick, the exchange of a
+    // sharded head) may become resident now; it waits for this grid's results itself
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (rt < nrt) {
         const int slot = g & 1;
         const int8_t *xrow = slot < NSLOT ? xq + (int64_t)slot * ldq : nullptr;
@@ -228,6 +231,8 @@ __device__ __forceinline__ ArgPair arg_block_reduce(ArgPair p) {
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ y, int64_t n, int64_t ldy, float *__restrict__ pv,
                                                     int32_t *__restrict__ pi, int32_t *__restrict__ out, unsigned *__restrict__ count) {
     __shared__ int s_last;
+    // launched behind the matvec with programmatic stream serialization, this grid is resident before the logits exist
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int row = blockIdx.y;
     const float *yr = y + (int64_t)row * ldy;
     ArgPair p = {0.0f, -1};
@@ -376,7 +381,17 @@ int32_t mk_launch_argmax(mk_ctx *ctx, const float *y, int64_t n, int64_t ldy, in
     float *pv = (float *)scratch;
     int32_t *pi = (int32_t *)(pv + (size_t)batch * ARGMAX_PARTS);
     if (batch > 64) { mk_set_error("greedy pick: more than 64 rows"); return MK_ERR_ARG; }
-    argmax_kernel<<<dim3(ARGMAX_PARTS, batch), 256, 0, ctx->stream>>>(y, n, ldy, pv, pi, out, ctx->argmax_count);
+    if (ctx->pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ARGMAX_PARTS, (unsigned)batch); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = ctx->stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, argmax_kernel, y, n, ldy, pv, pi, out, ctx->argmax_count);
+    } else {
+        argmax_kernel<<<dim3(ARGMAX_PARTS, batch), 256, 0, ctx->stream>>>(y, n, ldy, pv, pi, out, ctx->argmax_count);
+    }
     ctx->launches += 1;
     MK_CUDA(cudaGetLastError());
     return MK_OK;
