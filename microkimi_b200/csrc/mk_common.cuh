@@ -219,3 +219,18 @@ __device__ __forceinline__ uint4 mk_ldg_stream(const uint4 *p) {
 #define MK_LUT2_LO 0x03020100u
 #define MK_LUT2_HI 0x0C080604u
 #endif
+
+// A launch that may start behind the previous launch of the stream by programmatic stream serialization (`dep`): the
+// kernel itself waits (griddepcontrol.wait) before it touches what that launch produces.  Otherwise an ordinary launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t mk_launch_dep(bool dep, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = dep ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+__device__ __forceinline__ void mk_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void mk_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -456,6 +456,7 @@ struct RouterFusedArgs {
 template <class S>
 __global__ void __launch_bounds__(256) moe_router_fused_kernel(const RouterFusedArgs a) {
     extern __shared__ __align__(16) float rsm[];
+    mk_dep_trigger();       // the expert kernel launched behind this one may become resident; it waits for the routing itself
     const int d = a.d, n_tokens = a.n_tokens, n_experts = a.n_experts;
     const int logit_ctas = (n_experts + S::NE - 1) / S::NE;
     if ((int)blockIdx.x >= logit_ctas) {
@@ -741,6 +742,10 @@ template <int MODE>
 __global__ void __launch_bounds__(MK_G1_KS * 128, (MODE == MOE_BIG_ITEMS || MODE == MOE_STRICT) ? MK_MOE_BIG_CTAS : 8 / MK_G1_KS) moe_gate_up_kernel(const MoeArgs a) {
     constexpr bool STRICT = MODE == MOE_STRICT;
     constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED || STRICT, SPREAD = MODE != MOE_BIG_ITEMS && !STRICT;
+    // behind the router by programmatic stream serialization: resident early, waits for the routing; the trigger comes after
+    // the wait, so that a kernel launched behind this one finds the routing complete whenever it starts
+    mk_dep_wait();
+    mk_dep_trigger();
     const int item = blockIdx.y;
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
@@ -812,6 +817,24 @@ __global__ void __launch_bounds__(256, (MODE == MOE_BIG_ITEMS || MODE == MOE_STR
     constexpr bool STRICT = MODE == MOE_STRICT;
     constexpr bool BATCHED = MODE == MOE_BIG_ITEMS || MODE == MOE_MIXED || STRICT, SPREAD = MODE != MOE_BIG_ITEMS && !STRICT;
     const int item = blockIdx.y;
+    // Behind the gate / up kernel by programmatic stream serialization, this CTA may be resident while that kernel's last
+    // CTAs still run.  The routing is complete by then (the gate / up kernel triggers after its own wait), so the work
+    // item is known: the CTA asks L2 for its two weight tiles (32 KB + 2 KB of scales), which do not depend on the
+    // activations, and only then waits for them.
+    if (item < *a.n_items) {
+        const int e0 = a.items[item * 3];
+        const int64_t nrt0 = (a.d + 15) >> 4, rt0 = (int64_t)blockIdx.x * 2;
+        if (rt0 < nrt0) {
+            const char *wv0 = (const char *)tile_values<W_MXFP4>(a.wv[e0 * 3 + 1], rt0, a.nbp_i);
+            const char *ws0 = (const char *)tile_scales<W_MXFP4>(a.wsc[e0 * 3 + 1], rt0, a.nbp_i);
+            const int64_t tile_bytes = a.nbp_i * 256, scale_bytes = a.nbp_i * 16, ntile = rt0 + 1 < nrt0 ? 2 : 1;
+            for (int64_t o = (int64_t)threadIdx.x * 128; o < ntile * tile_bytes; o += 256 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(wv0 + o));
+            if ((int64_t)threadIdx.x * 128 < ntile * scale_bytes) asm volatile("prefetch.global.L2 [%0];" ::"l"(ws0 + (int64_t)threadIdx.x * 128));
+        }
+    }
+    mk_dep_wait();
+    mk_dep_trigger();
     if (item >= *a.n_items) return;
     const int e = a.items[item * 3], off = a.items[item * 3 + 1], n = a.items[item * 3 + 2];
     if ((MODE == MOE_SMALL_ITEMS && n > 2) || (MODE == MOE_BIG_ITEMS && n <= 2)) return;
@@ -858,6 +881,7 @@ __global__ void __launch_bounds__(256, (MODE == MOE_BIG_ITEMS || MODE == MOE_STR
 // out[t][j] = ((0 + outs[t,0][j]) + outs[t,1][j]) + ... in slot order (src/deepseek.rs:1095-1106)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ outs, int n_tokens, int slots, int d,
                                                          float *__restrict__ out) {
+    mk_dep_wait();      // behind the down kernel by programmatic stream serialization
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)n_tokens * d) return;
     const int64_t t = idx / d, j = idx % d;
@@ -1276,15 +1300,17 @@ static int32_t moe_experts_launch(mk_ctx *ctx, mk_moe *m, const float *x, int n_
     // calls of <= 2 rows have at most 2 pairs per expert: the build without the batched schedule
     // needs fewer registers and keeps 4 CTAs per SM, one wave at batch 1
     const dim3 g1((unsigned)(m->inter / 32), (unsigned)items_ub), g2((unsigned)mk_ceil_div(m->d, 32), (unsigned)items_ub);
+    // the kernels of a small call are chained by programmatic stream serialization (each waits for its predecessor itself)
+    const bool dep = ctx->pdl != 0;
     if (m->strict) {
         moe_gate_up_kernel<MOE_STRICT><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
         moe_down_kernel<MOE_STRICT><<<g2, 256, 0, ctx->stream>>>(a);
     } else if (n_rows <= 2) {
-        moe_gate_up_kernel<MOE_ALL_SPREAD><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
-        moe_down_kernel<MOE_ALL_SPREAD><<<g2, 256, 0, ctx->stream>>>(a);
+        mk_launch_dep(dep, moe_gate_up_kernel<MOE_ALL_SPREAD>, g1, dim3(MK_G1_KS * 128), 0, ctx->stream, a);
+        mk_launch_dep(dep, moe_down_kernel<MOE_ALL_SPREAD>, g2, dim3(256), 0, ctx->stream, a);
     } else if (n_rows <= MK_MOE_MIXED_MAX) {
-        moe_gate_up_kernel<MOE_MIXED><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
-        moe_down_kernel<MOE_MIXED><<<g2, 256, 0, ctx->stream>>>(a);
+        mk_launch_dep(dep, moe_gate_up_kernel<MOE_MIXED>, g1, dim3(MK_G1_KS * 128), 0, ctx->stream, a);
+        mk_launch_dep(dep, moe_down_kernel<MOE_MIXED>, g2, dim3(256), 0, ctx->stream, a);
     } else {
         moe_gate_up_kernel<MOE_BIG_ITEMS><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
         moe_gate_up_kernel<MOE_SMALL_ITEMS><<<g1, MK_G1_KS * 128, 0, ctx->stream>>>(a);
@@ -1301,7 +1327,7 @@ extern "C" int32_t mk_moe_combine_dev(mk_ctx *ctx, const float *outs, int32_t n_
     MK_CHECK_ARG(ctx != nullptr && outs != nullptr && out != nullptr && n_tokens > 0 && slots > 0 && d > 0, "bad argument");
     MK_CUDA(cudaSetDevice(ctx->device));
     mk_prof_scope prof(ctx, MK_PROF_EXPERTS);
-    moe_combine_kernel<<<(unsigned)mk_ceil_div((int64_t)n_tokens * d, 256), 256, 0, ctx->stream>>>(outs, n_tokens, slots, d, out);
+    mk_launch_dep(ctx->pdl != 0, moe_combine_kernel, dim3((unsigned)mk_ceil_div((int64_t)n_tokens * d, 256)), dim3(256), 0, ctx->stream, outs, n_tokens, slots, d, out);
     ctx->launches++;
     MK_CUDA(cudaGetLastError());
     return MK_OK;
