@@ -150,106 +150,20 @@ moe_router_tile_kernel(const float *__restrict__ gate_w, const float *__restrict
 }
 
 
-// Register-tiled form for many tokens (>= 64): one CTA (128 threads) = 16 experts x 16 tokens, every lane octet 4 experts x
-// 4 tokens.  Each of the 16 (expert, token) pairs of an octet keeps the engine's dot(): lane j sums the columns = j (mod 8)
-// in ascending order with a separate multiply and add, then the 8 partial sums fold in the engine's tree (mkf::reduce8).
-// The products are issued two at a time (mul.rn.f32x2: each half rounded as the scalar instruction rounds it), the sums
-// stay scalar: a packed multiply feeding a packed add came back a few ulps off the engine's bits - contracted into a
-// packed multiply-add - so the two are kept in different forms.  A quarter fewer instructions in an issue-bound kernel.  Against the 2 x 16 shape
-// this reads each router row and token row 4 x less often from L2.  384 experts x 256 tokens are 384 CTAs, all resident
-// at once (52 KB of shared memory each), 2 or 3 per SM.  Slices of 128 columns, 3 in flight (cp.async); d % 4 == 0,
-// 16-byte aligned rows.
-constexpr int RG_TE = 16, RG_TT = 16, RG_KC = 128, RG_ST = 3, RG_LD = RG_KC + 8, RG_ROWS = RG_TE + RG_TT, RG_THREADS = 128;
-constexpr size_t RG_SMEM = (size_t)RG_ST * RG_ROWS * RG_LD * sizeof(float);
-__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t f32x2_mul(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ void f32x2_unpack(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+// The router's logits for many tokens: mkf::reg_tile_product (16 experts x 16 tokens per CTA of 128 threads, every pair the
+// engine's dot()) with the router's epilogue.
+using mkf::RG_TE;
+using mkf::RG_TT;
+using mkf::RG_THREADS;
+using mkf::RG_SMEM;
 __global__ void __launch_bounds__(RG_THREADS)
 moe_router_gemm_kernel(const float *__restrict__ gate_w, const float *__restrict__ gate_b, const float *__restrict__ x,
                        float *__restrict__ logits, float *__restrict__ score, float *__restrict__ key, int n_experts, int d,
                        int n_tokens, int kind) {
     extern __shared__ __align__(16) float gsm[];
-    const int tid = threadIdx.x, lane = tid & 31, oct = tid >> 3, j = lane & 7;
-    const int e0 = blockIdx.x * RG_TE, t0 = blockIdx.y * RG_TT;
-    const int ne = min(RG_TE, n_experts - e0), nt = min(RG_TT, n_tokens - t0);
-    // octet -> experts eg, eg + 4, eg + 8, eg + 12 and tokens tg, tg + 4, tg + 8, tg + 12: the four octets of a warp share their
-    // router rows (one broadcast read) and read neighbouring token rows (8 banks apart)
-    const int eg = oct >> 2, tg = oct & 3;
-    const int full = d & ~7, nch = (full + RG_KC - 1) / RG_KC;
-    // this thread's part of a slice: column (tid & 31) * 4 of rows (tid >> 5) + 4 k
-    constexpr int NCP = RG_ROWS * (RG_KC / 4) / RG_THREADS;
-    const float *src[NCP];
-#pragma unroll
-    for (int k = 0; k < NCP; ++k) {
-        const int r = (tid >> 5) + 4 * k;
-        src[k] = (r < RG_TE ? gate_w + (size_t)(e0 + min(r, ne - 1)) * d : x + (size_t)(t0 + min(r - RG_TE, nt - 1)) * d) + (tid & 31) * 4;
-    }
-    const int dst0 = (tid >> 5) * RG_LD + (tid & 31) * 4;
-    auto issue = [&](int ch) {
-        float *stage = gsm + (size_t)(ch % RG_ST) * RG_ROWS * RG_LD + dst0;
-        const int c0 = ch * RG_KC;
-        if (c0 + (tid & 31) * 4 >= full) return;
-#pragma unroll
-        for (int k = 0; k < NCP; ++k) mkf::cp16(stage + 4 * k * RG_LD, src[k] + c0);
-    };
-    for (int sidx = 0; sidx < RG_ST - 1; ++sidx) {
-        if (sidx < nch) issue(sidx);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-    }
-    float acc[4][4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
-    for (int ch = 0; ch < nch; ++ch) {
-        asm volatile("cp.async.wait_group %0;\n" ::"n"(RG_ST - 2) : "memory");
-        __syncthreads();
-        if (ch + RG_ST - 1 < nch) issue(ch + RG_ST - 1);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        const float *stage = gsm + (size_t)(ch % RG_ST) * RG_ROWS * RG_LD;
-        const float *ws = stage + eg * RG_LD + j, *xr = stage + (RG_TE + tg) * RG_LD + j;
-        const int kmax = min(RG_KC, full - ch * RG_KC);
-#pragma unroll 4
-        for (int c = 0; c < kmax; c += 8) {
-            float wv[4], xv[4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a) { wv[a] = ws[(4 * a) * RG_LD + c]; xv[a] = xr[(4 * a) * RG_LD + c]; }
-            const uint64_t x01 = f32x2_pack(xv[0], xv[1]), x23 = f32x2_pack(xv[2], xv[3]);
-#pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const uint64_t w2 = f32x2_pack(wv[a], wv[a]);
-                float p0, p1, p2, p3;
-                f32x2_unpack(f32x2_mul(w2, x01), p0, p1);
-                f32x2_unpack(f32x2_mul(w2, x23), p2, p3);
-                acc[a][0] = __fadd_rn(acc[a][0], p0);
-                acc[a][1] = __fadd_rn(acc[a][1], p1);
-                acc[a][2] = __fadd_rn(acc[a][2], p2);
-                acc[a][3] = __fadd_rn(acc[a][3], p3);
-            }
-        }
-    }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-#pragma unroll
-    for (int a = 0; a < 4; ++a) {
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            float sres = mkf::reduce8(acc[a][b], lane);
-            const int el = eg + 4 * a, tl = tg + 4 * b;
-            if (j == 0 && el < ne && tl < nt) {
-                const int e = e0 + el, tok = t0 + tl;
-                for (int c = full; c < d; ++c) sres = __fadd_rn(sres, __fmul_rn(__ldg(gate_w + (size_t)e * d + c), __ldg(x + (size_t)tok * d + c)));
-                router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, sres, kind);
-            }
-        }
-    }
+    mkf::reg_tile_product(gate_w, x, n_experts, d, n_tokens, blockIdx.x * RG_TE, blockIdx.y * RG_TT, gsm, [&](int e, int tok, float v) {
+        router_store(logits, score, key, gate_b, (int64_t)tok * n_experts + e, e, v, kind);
+    });
 }
 
 // ------------------------------------------------------------------ top-k

@@ -24,6 +24,17 @@ f32_gemv_tile_kernel(const float *__restrict__ w, const float *__restrict__ x, f
     }
 }
 
+// many tokens (a prompt's rows): 16 matrix rows x 16 tokens per CTA, every pair the engine's dot() (mkf::reg_tile_product)
+__global__ void __launch_bounds__(mkf::RG_THREADS)
+f32_gemm_reg_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ y, int rows, int d, int n, int64_t ldy,
+                    int accumulate) {
+    extern __shared__ __align__(16) float gsm[];
+    mkf::reg_tile_product(w, x, rows, d, n, blockIdx.x * mkf::RG_TE, blockIdx.y * mkf::RG_TT, gsm, [&](int row, int tok, float v) {
+        float *o = y + (int64_t)tok * ldy + row;
+        *o = accumulate ? __fadd_rn(*o, v) : v;
+    });
+}
+
 template <int T>
 __global__ void __launch_bounds__(256)
 f32_gemv_rows_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ y, int rows, int d, int n,
@@ -106,7 +117,16 @@ int32_t mk_launch_f32_gemv(mk_ctx *ctx, const float *w, int64_t rows, int64_t co
         else if (n == 2) rc = launch_tile<GemvB2>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
         else if (n <= 4) rc = launch_tile<GemvB4>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
         else if (n <= 8) rc = launch_tile<GemvB8>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
-        else rc = launch_tile<GemvB16>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
+        else if (n >= 48) {
+            static mk_once_per_device attr;
+            if (attr.pending(ctx->device)) {
+                MK_CUDA(cudaFuncSetAttribute(f32_gemm_reg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mkf::RG_SMEM));
+                attr.mark(ctx->device);
+            }
+            f32_gemm_reg_kernel<<<dim3((unsigned)mk_ceil_div(rows, mkf::RG_TE), (unsigned)mk_ceil_div(n, mkf::RG_TT)), mkf::RG_THREADS, mkf::RG_SMEM,
+                                  ctx->stream>>>(w, x, y, (int)rows, (int)cols, n, ldy, accumulate);
+            rc = MK_OK;
+        } else rc = launch_tile<GemvB16>(ctx, w, rows, cols, x, n, y, ldy, accumulate);
         if (rc != MK_OK) return rc;
     } else if (n >= 4) {
         const int64_t warps = mk_ceil_div(rows, 4) * mk_ceil_div(n, 4);

@@ -30,7 +30,7 @@ def oracle_matvec(w, x):
 # shapes: the tiled path (cols % 4 == 0) with and without a tail of cols % 8, one row tile that
 # is not full, and the generic path (cols % 4 != 0)
 @pytest.mark.parametrize("rows,cols", [(128, 512), (512, 128), (37, 200), (64, 36), (5, 8), (33, 1028), (19, 101), (7, 3)])
-@pytest.mark.parametrize("batch", [1, 2, 3, 5, 9, 17])
+@pytest.mark.parametrize("batch", [1, 2, 3, 5, 9, 17, 50, 64])     # from 48 rows on: the register-tiled 16 x 16 product
 def test_f32_matvec_bit_exact(mk, rows, cols, batch):
     rng = np.random.default_rng(rows * 1000 + cols + batch)
     w = (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32)
