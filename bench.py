@@ -357,7 +357,7 @@ def measure_mla(torch, mk, ctx, dev, layout, ctx_len, batch, steps, warmup):
     return out
 
 
-def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=64, n_new=256, cpu_tokens=0, path=None):
+def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=64, n_new=256, cpu_tokens=0, path=None, profile_prefill=False):
     """Whole-token decode of the 93-layer micro skeleton (the engine's historical configuration: 69 KDA + 24 MLA layers,
     896 MXFP4 experts top-16 per MoE layer, q8_0 lm_head over 163840 rows, q8_0 MLA caches): a synthetic model file with the
     builder's shapes and distributions, a seeded 64-token prompt prefilled layer by layer (one GPU), then 256 greedy steps whose token ids
@@ -417,7 +417,11 @@ def measure_decode(torch, mk, dev, local, world=1, rank=0, dist=None, n_prompt=6
         sync_all()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record(stream)
+        if profile_prefill:
+            torch.cuda.profiler.start()           # for `ncu --profile-from-start off`: the launch list of the warm prefill alone
         first = model.generate(prompt, 1)         # ... and layer by layer (mk_model_generate prefills; returns after its own synchronization)
+        if profile_prefill:
+            torch.cuda.profiler.stop()
         e1.record(stream)
         for _ in range(n_new):
             model.forward_dev(None)               # the previous pick, on the device
@@ -959,7 +963,8 @@ def run_case_decode(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29534")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
-    res = measure_decode(torch, mk, torch.device("cuda", local), local, world, rank, dist, cpu_tokens=0 if args.no_cpu else 8)
+    res = measure_decode(torch, mk, torch.device("cuda", local), local, world, rank, dist, n_new=args.decode_steps,
+                         cpu_tokens=0 if args.no_cpu else 8, profile_prefill=args.profile_prefill)
     if rank == 0:
         print(json.dumps({"case": "decode", "n_gpus": world, **res}), flush=True)
     if world > 1:
@@ -995,6 +1000,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the side workloads that follow the headline measurement")
+    ap.add_argument("--decode-steps", type=int, default=256, help="--case decode: greedy steps after the prompt")
+    ap.add_argument("--profile-prefill", action="store_true",
+                    help="--case decode: cudaProfilerStart / Stop around the timed prefill (for a profiler that starts with profiling off)")
     ap.add_argument("--graph", action="store_true", help="--case mxfp4_gemv / moe: also time the ring of calls as one CUDA graph")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: logits by one peer-memory exchange kernel after the matvec (default) or by an NCCL all-gather")
