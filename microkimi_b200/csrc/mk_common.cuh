@@ -77,6 +77,8 @@ struct mk_ctx {
     cudaStream_t own_stream;
     cudaStream_t stream;
     int64_t launches;
+    uint64_t alloc_epoch;   // counts the re-allocations of buffers that recorded launches (CUDA graphs) may point into: an
+                            // object that grows its per-call buffers bumps it, a holder of a recording compares and re-records
     int32_t *status_dev;    // device status word
     int8_t *zeros_dev;      // 256 zero bytes (B operand of unused MMA columns)
     unsigned *argmax_count; // 64 counters, 0 between calls: CTAs of the greedy-pick kernel that have finished, per row

@@ -1164,6 +1164,7 @@ extern "C" int32_t mk_mla_decode_step_dev(mk_ctx *ctx, mk_mla *m, int32_t seq, c
 static int32_t mla_reserve_rows(mk_ctx *ctx, mk_mla *m, int64_t rows) {
     if (rows <= m->q_rows && rows * 32 <= m->part_slots) return MK_OK;
     MK_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->alloc_epoch++;         // recorded decode steps point into the old buffers: their holder re-records
     const int64_t r = std::max(rows, m->q_rows), slots = std::max(rows * 32, m->part_slots);
     void **bufs[] = {(void **)&m->rope_scores, (void **)&m->qq, (void **)&m->qs, (void **)&m->part_m, (void **)&m->part_l, (void **)&m->part_o};
     const size_t sizes[] = {m->layout == MK_MLA_ABSORBED ? 0 : (size_t)r * m->T * 32 * 4, (size_t)r * m->q_nbp * 32, (size_t)r * m->q_nbp * 4,

@@ -257,6 +257,8 @@ struct mk_model {
     cudaGraphExec_t graphs[4] = {nullptr, nullptr, nullptr, nullptr};
     uint32_t ep_steps_per_token = 0, gather_steps_per_token = 0;
     void *graph_ws = nullptr;       // the context's shared workspace as the recorded launches saw it
+    uint64_t graph_epoch = 0;       // the context's allocation epoch at the recording: a layer that grew its buffers since (a
+                                    // longer prompt chunk than any before) left the recorded launches with stale pointers
     int warm = 0;
 };
 
@@ -890,9 +892,10 @@ extern "C" int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t 
     const bool real_stream = st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread;
     const bool graph_ok = m->opts.use_graph && !ctx->prof_on && real_stream;
     int32_t rc = MK_OK;
-    if (m->graph_ws != ctx->ws) {
-        // another call on this context grew the shared workspace since the token was recorded: the recorded
-        // launches point at the old buffer, so the recordings are dropped and made again
+    if (m->graph_ws != ctx->ws || m->graph_epoch != ctx->alloc_epoch) {
+        // since the token was recorded another call on this context grew the shared workspace, or a layer re-allocated its
+        // per-call buffers (a prompt chunk longer than any before): the recorded launches point at freed memory, so
+        // the recordings are dropped and made again
         for (cudaGraphExec_t &g : m->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     }
     const uint32_t ep0 = m->ep ? mk_moe_ep_steps(m->ep) : 0u, ga0 = m->gather ? mk_gather_steps(m->gather) : 0u;
@@ -922,6 +925,7 @@ extern "C" int32_t mk_model_forward_dev(mk_ctx *ctx, mk_model *m, const int32_t 
         cudaGraphDestroy(g);
         if (e2 != cudaSuccess) { mk_set_error("mk_model_forward: graph instantiation failed: %s", cudaGetErrorString(e2)); return MK_ERR_CUDA; }
         m->graph_ws = ctx->ws;
+        m->graph_epoch = ctx->alloc_epoch;
         MK_CUDA(cudaGraphLaunch(graph, st));
     } else {
         const int64_t l0 = ctx->launches;

@@ -891,6 +891,7 @@ static int32_t moe_reserve(mk_ctx *ctx, mk_moe *m, int rows, int pairs) {
     while (nr < rows) nr *= 2;
     while (np < pairs) np *= 2;
     moe_free_ws(m);
+    ctx->alloc_epoch++;         // recorded launches that point into the old buffers are stale
     const int E = m->n_experts, k = m->top_k;
     m->max_items = np / 8 + (np < E + 1 ? np : E + 1) + 1;
     const size_t ldq_d = (size_t)m->nbp_d * 32, ldq_i = (size_t)m->nbp_i * 32;

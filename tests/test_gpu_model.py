@@ -205,3 +205,31 @@ def test_layer_major_prefill_equals_token_by_token(mk, skeleton, strict):
     two = M.Model(skeleton, 40, use_graph=False, strict=True)
     l2, n2 = two.forward(int(prompt[0]))
     assert np.array_equal(bits(l1), bits(l2)) and n1 == n2
+
+
+def test_recorded_token_survives_a_longer_prompt_chunk(mk, skeleton):
+    """A model that has recorded its token (CUDA graph) and then prefills a chunk longer than any call before: the layers
+    re-allocate their per-call buffers for the longer chunk, the recorded launches would point at freed memory, so the
+    model drops the recording and records again.  The graph model and a model launched kernel by kernel, fed the same
+    tokens, agree bit for bit before and after."""
+    from microkimi_b200 import model as M
+    rng = np.random.default_rng(17)
+    cfg = M.BinFile(skeleton).config
+    a = M.Model(skeleton, 96, use_graph=True)
+    b = M.Model(skeleton, 96, use_graph=False)
+    for t in rng.integers(0, cfg.vocab, 4):              # a: eager token, recorded token, replays
+        la, na = a.forward(int(t))
+        lb, nb = b.forward(int(t))
+        assert np.array_equal(bits(la), bits(lb)) and na == nb
+    chunk = rng.integers(0, cfg.vocab, 40).astype(np.int32)
+    la, na = a.prefill(chunk)
+    lb, nb = b.prefill(chunk)
+    assert np.array_equal(bits(la), bits(lb)) and na == nb
+    for _ in range(5):                                   # a records again, then replays
+        la, na2 = a.forward(na)
+        lb, nb2 = b.forward(nb)
+        assert np.array_equal(bits(la), bits(lb)) and na2 == nb2
+        na, nb = na2, nb2
+    assert a.positions == b.positions == 4 + 40 + 5
+    assert mk.Context.default().status_word() == 0
+    a.free(), b.free()
