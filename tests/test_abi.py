@@ -25,6 +25,13 @@ def test_header_symbols_are_exported_and_bound():
     assert sorted(lib.SIGNATURES) == names
 
 
+def test_reference_side_binding_lists_every_entry_point():
+    """The `src/cuda.rs` block a maintainer of the engine would add declares every function of the header."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    missing = [n for n in _declared() if not re.search(r"\bfn %s\(" % n, text)]
+    assert not missing, missing
+
+
 def test_no_cpu_fallback_without_gpu():
     import torch
     if torch.cuda.is_available():
